@@ -1,0 +1,407 @@
+"""Host-side mirror of the C API of libfuthark_b200.so (ctypes).
+
+The product is the shared library; this package only loads it and gives its
+`futhark_*` functions Python spellings, one to one: a `Context` wraps
+`futhark_context_config_new` / `futhark_context_new`, `Context.new_<t>_<n>d` wraps
+`futhark_new_<t>_<n>d`, `Context.entry_<name>` wraps `futhark_entry_<name>`, and so
+on (docs/c-api.rst of the reference describes the contract).  There is no CPU
+fallback: if the library is missing or the context cannot be set up, an exception
+is raised.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfuthark_b200.so")
+
+FUTHARK_SUCCESS = 0
+FUTHARK_PROGRAM_ERROR = 2
+FUTHARK_OUT_OF_MEMORY = 3
+
+# array type name -> (numpy dtype, rank, ctypes element type)
+ARRAY_TYPES = {
+    "i32_1d": (np.int32, 1, ctypes.c_int32),
+    "i64_1d": (np.int64, 1, ctypes.c_int64),
+    "u32_1d": (np.uint32, 1, ctypes.c_uint32),
+    "f32_1d": (np.float32, 1, ctypes.c_float),
+    "bool_1d": (np.bool_, 1, ctypes.c_bool),
+    "f32_2d": (np.float32, 2, ctypes.c_float),
+    "f32_3d": (np.float32, 3, ctypes.c_float),
+    "f16_3d": (np.uint16, 3, ctypes.c_uint16),
+}
+
+PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
+
+_lib = None
+
+
+class FutharkError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__("futhark error %d: %s" % (code, message))
+        self.code = code
+        self.message = message
+
+
+def load():
+    """Load libfuthark_b200.so (built by futhark_b200.build) and declare its signatures."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("%s is missing: run `python -m futhark_b200.build` (needs nvcc)" % LIB_PATH)
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i64, ci = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    L.futhark_context_config_new.restype = vp
+    L.futhark_context_config_free.argtypes = [vp]
+    for f in ("debugging", "profiling", "logging", "unified_memory", "default_thread_block_size",
+              "default_group_size", "default_grid_size", "default_num_groups", "default_tile_size",
+              "default_reg_tile_size", "default_registers", "default_cache", "default_threshold"):
+        getattr(L, "futhark_context_config_set_" + f).argtypes = [vp, ci]
+        getattr(L, "futhark_context_config_set_" + f).restype = None
+    for f in ("device", "cache_file", "program"):
+        getattr(L, "futhark_context_config_set_" + f).argtypes = [vp, ctypes.c_char_p]
+        getattr(L, "futhark_context_config_set_" + f).restype = None
+    for f in ("add_nvrtc_option", "dump_ptx_to", "load_ptx_from"):
+        getattr(L, "futhark_context_config_" + f).argtypes = [vp, ctypes.c_char_p]
+        getattr(L, "futhark_context_config_" + f).restype = None
+    L.futhark_context_config_get_program.argtypes = [vp]
+    L.futhark_context_config_get_program.restype = ctypes.c_char_p
+    L.futhark_context_config_set_tuning_param.argtypes = [vp, ctypes.c_char_p, ctypes.c_size_t]
+    L.futhark_get_tuning_param_count.restype = ci
+    L.futhark_get_tuning_param_name.restype = ctypes.c_char_p
+    L.futhark_get_tuning_param_name.argtypes = [ci]
+    L.futhark_get_tuning_param_class.restype = ctypes.c_char_p
+    L.futhark_get_tuning_param_class.argtypes = [ci]
+    L.futhark_context_new.restype = vp
+    L.futhark_context_new.argtypes = [vp]
+    L.futhark_context_free.argtypes = [vp]
+    L.futhark_context_free.restype = None
+    L.futhark_context_sync.argtypes = [vp]
+    L.futhark_context_get_error.argtypes = [vp]
+    L.futhark_context_get_error.restype = vp          # malloc'd char*: freed by us
+    L.futhark_context_report.argtypes = [vp]
+    L.futhark_context_report.restype = vp
+    L.futhark_context_clear_caches.argtypes = [vp]
+    L.futhark_context_pause_profiling.argtypes = [vp]
+    L.futhark_context_unpause_profiling.argtypes = [vp]
+    for name, (_, rank, ct) in ARRAY_TYPES.items():
+        getattr(L, "futhark_new_" + name).restype = vp
+        getattr(L, "futhark_new_" + name).argtypes = [vp, vp] + [i64] * rank
+        getattr(L, "futhark_new_raw_" + name).restype = vp
+        getattr(L, "futhark_new_raw_" + name).argtypes = [vp, ctypes.c_uint64] + [i64] * rank
+        getattr(L, "futhark_free_" + name).argtypes = [vp, vp]
+        getattr(L, "futhark_values_" + name).argtypes = [vp, vp, vp]
+        getattr(L, "futhark_values_raw_" + name).restype = ctypes.c_uint64
+        getattr(L, "futhark_values_raw_" + name).argtypes = [vp, vp]
+        getattr(L, "futhark_shape_" + name).restype = ctypes.POINTER(i64)
+        getattr(L, "futhark_shape_" + name).argtypes = [vp, vp]
+        getattr(L, "futhark_index_" + name).argtypes = [vp, vp, vp] + [i64] * rank
+    getattr(L, "futhark_free_" + PAIR).argtypes = [vp, vp]
+    getattr(L, "futhark_new_" + PAIR).argtypes = [vp, ctypes.POINTER(vp), vp, vp]
+    getattr(L, "futhark_project_" + PAIR + "_0").argtypes = [vp, ctypes.POINTER(vp), vp]
+    getattr(L, "futhark_project_" + PAIR + "_1").argtypes = [vp, ctypes.POINTER(vp), vp]
+    getattr(L, "futhark_store_" + PAIR).argtypes = [vp, vp, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
+    getattr(L, "futhark_restore_" + PAIR).restype = vp
+    getattr(L, "futhark_restore_" + PAIR).argtypes = [vp, vp]
+    pvp = ctypes.POINTER(vp)
+    L.futhark_entry_scan_i32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_reduce_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+    L.futhark_entry_segscan_f32.argtypes = [vp, pvp, vp, vp]
+    L.futhark_entry_segreduce_f32.argtypes = [vp, pvp, vp, vp, vp]
+    L.futhark_entry_rowsum_f32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_hist_add_i32.argtypes = [vp, pvp, i64, vp, vp]
+    L.futhark_entry_hist_max_f32.argtypes = [vp, pvp, i64, vp, vp]
+    L.futhark_entry_filter_u32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_partition_u32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_bmm_f16.argtypes = [vp, pvp, vp, vp]
+    _lib = L
+    return L
+
+
+_libc = ctypes.CDLL(None)
+_libc.free.argtypes = [ctypes.c_void_p]
+
+
+def _take_string(ptr):
+    if not ptr:
+        return None
+    s = ctypes.string_at(ptr).decode("utf-8", "replace")
+    _libc.free(ptr)
+    return s
+
+
+class Array:
+    """A device array owned by a context (struct futhark_<t>_<n>d *)."""
+
+    def __init__(self, ctx, tname, ptr):
+        self.ctx, self.tname, self.ptr = ctx, tname, ptr
+
+    @property
+    def shape(self):
+        rank = ARRAY_TYPES[self.tname][1]
+        p = getattr(self.ctx.lib, "futhark_shape_" + self.tname)(self.ctx.ptr, self.ptr)
+        return tuple(int(p[i]) for i in range(rank))
+
+    @property
+    def raw(self):
+        """Device address (futhark_values_raw_*)."""
+        return int(getattr(self.ctx.lib, "futhark_values_raw_" + self.tname)(self.ctx.ptr, self.ptr))
+
+    @property
+    def __cuda_array_interface__(self):
+        dt = np.dtype(ARRAY_TYPES[self.tname][0])
+        return {"shape": self.shape, "typestr": dt.str, "data": (self.raw, False), "version": 2}
+
+    def values_into(self, out):
+        """Asynchronous copy to a host buffer (futhark_values_*); call ctx.sync() before reading."""
+        rc = getattr(self.ctx.lib, "futhark_values_" + self.tname)(self.ctx.ptr, self.ptr, out.ctypes.data)
+        self.ctx._check(rc)
+        return out
+
+    def values(self):
+        out = np.empty(self.shape, dtype=ARRAY_TYPES[self.tname][0])
+        self.values_into(out)
+        self.ctx.sync()
+        return out
+
+    def index(self, *idx):
+        ct = ARRAY_TYPES[self.tname][2]()
+        rc = getattr(self.ctx.lib, "futhark_index_" + self.tname)(self.ctx.ptr, ctypes.byref(ct), self.ptr, *idx)
+        self.ctx._check(rc)
+        self.ctx.sync()
+        return ct.value
+
+    def free(self):
+        if self.ptr:
+            getattr(self.ctx.lib, "futhark_free_" + self.tname)(self.ctx.ptr, self.ptr)
+            self.ptr = None
+
+
+class Pair:
+    """The opaque (selected, rejected) record returned by partition."""
+
+    def __init__(self, ctx, ptr):
+        self.ctx, self.ptr = ctx, ptr
+
+    def project(self, i):
+        out = ctypes.c_void_p()
+        rc = getattr(self.ctx.lib, "futhark_project_%s_%d" % (PAIR, i))(self.ctx.ptr, ctypes.byref(out), self.ptr)
+        self.ctx._check(rc)
+        return Array(self.ctx, "u32_1d", out.value)
+
+    def store(self):
+        n = ctypes.c_size_t()
+        p = ctypes.c_void_p()
+        rc = getattr(self.ctx.lib, "futhark_store_" + PAIR)(self.ctx.ptr, self.ptr, ctypes.byref(p), ctypes.byref(n))
+        self.ctx._check(rc)
+        self.ctx.sync()
+        data = ctypes.string_at(p.value, n.value)
+        _libc.free(p)
+        return data
+
+    def free(self):
+        if self.ptr:
+            getattr(self.ctx.lib, "futhark_free_" + PAIR)(self.ctx.ptr, self.ptr)
+            self.ptr = None
+
+
+class Context:
+    """futhark_context_config + futhark_context."""
+
+    def __init__(self, device=None, profiling=False, logging=False, debugging=False, tuning=None,
+                 unified_memory=False):
+        self.lib = load()
+        self.cfg = self.lib.futhark_context_config_new()
+        if device is not None:
+            self.lib.futhark_context_config_set_device(self.cfg, str(device).encode())
+        if debugging:
+            self.lib.futhark_context_config_set_debugging(self.cfg, 1)
+        if profiling:
+            self.lib.futhark_context_config_set_profiling(self.cfg, 1)
+        if logging:
+            self.lib.futhark_context_config_set_logging(self.cfg, 1)
+        if unified_memory:
+            self.lib.futhark_context_config_set_unified_memory(self.cfg, 1)
+        for k, v in (tuning or {}).items():
+            if self.lib.futhark_context_config_set_tuning_param(self.cfg, k.encode(), int(v)) != 0:
+                raise ValueError("unknown tuning parameter %r" % k)
+        self.ptr = self.lib.futhark_context_new(self.cfg)
+        if not self.ptr:
+            raise MemoryError("futhark_context_new returned NULL")
+        err = self.get_error()
+        if err is not None:            # set-up failed (docs/c-api.rst:161-166)
+            self.lib.futhark_context_free(self.ptr)
+            self.lib.futhark_context_config_free(self.cfg)
+            self.ptr = self.cfg = None
+            raise FutharkError(1, err)
+
+    # ---- life cycle, errors, reports
+    def close(self):
+        if self.ptr:
+            self.lib.futhark_context_free(self.ptr)
+            self.lib.futhark_context_config_free(self.cfg)
+            self.ptr = self.cfg = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def get_error(self):
+        return _take_string(self.lib.futhark_context_get_error(self.ptr))
+
+    def _check(self, rc):
+        if rc != 0:
+            raise FutharkError(rc, self.get_error() or "")
+
+    def sync(self):
+        self._check(self.lib.futhark_context_sync(self.ptr))
+
+    def report(self):
+        return _take_string(self.lib.futhark_context_report(self.ptr))
+
+    def clear_caches(self):
+        self._check(self.lib.futhark_context_clear_caches(self.ptr))
+
+    def pause_profiling(self):
+        self.lib.futhark_context_pause_profiling(self.ptr)
+
+    def unpause_profiling(self):
+        self.lib.futhark_context_unpause_profiling(self.ptr)
+
+    # ---- arrays
+    def new(self, tname, data):
+        dt, rank, _ = ARRAY_TYPES[tname]
+        a = np.ascontiguousarray(data, dtype=dt)
+        if a.ndim != rank:
+            raise ValueError("%s wants rank %d, got %d" % (tname, rank, a.ndim))
+        p = getattr(self.lib, "futhark_new_" + tname)(self.ptr, a.ctypes.data, *a.shape)
+        if not p:
+            raise FutharkError(1, self.get_error() or "futhark_new_%s failed" % tname)
+        arr = Array(self, tname, p)
+        arr._keepalive = a     # the copy is asynchronous: keep the host buffer until freed
+        return arr
+
+    def new_raw(self, tname, devptr, *shape):
+        p = getattr(self.lib, "futhark_new_raw_" + tname)(self.ptr, int(devptr), *shape)
+        if not p:
+            raise FutharkError(1, self.get_error() or "futhark_new_raw_%s failed" % tname)
+        return Array(self, tname, p)
+
+    # ---- entry points (one out-parameter each, as in the C API)
+    def _entry_arr(self, name, out_t, *args):
+        out = ctypes.c_void_p()
+        rc = getattr(self.lib, "futhark_entry_" + name)(self.ptr, ctypes.byref(out), *args)
+        self._check(rc)
+        return Array(self, out_t, out.value)
+
+    def entry_scan_i32(self, xs):
+        return self._entry_arr("scan_i32", "i32_1d", xs.ptr)
+
+    def entry_reduce_i32(self, xs):
+        out = ctypes.c_int32()
+        self._check(self.lib.futhark_entry_reduce_i32(self.ptr, ctypes.byref(out), xs.ptr))
+        return int(out.value)
+
+    def entry_segscan_f32(self, flags, xs):
+        return self._entry_arr("segscan_f32", "f32_1d", flags.ptr, xs.ptr)
+
+    def entry_segreduce_f32(self, offsets, flags, xs):
+        return self._entry_arr("segreduce_f32", "f32_1d", offsets.ptr, flags.ptr, xs.ptr)
+
+    def entry_rowsum_f32(self, xss):
+        return self._entry_arr("rowsum_f32", "f32_1d", xss.ptr)
+
+    def entry_hist_add_i32(self, B, bins, ws):
+        return self._entry_arr("hist_add_i32", "i32_1d", int(B), bins.ptr, ws.ptr)
+
+    def entry_hist_max_f32(self, B, bins, ws):
+        return self._entry_arr("hist_max_f32", "f32_1d", int(B), bins.ptr, ws.ptr)
+
+    def entry_filter_u32(self, ks):
+        return self._entry_arr("filter_u32", "u32_1d", ks.ptr)
+
+    def entry_partition_u32(self, ks):
+        out = ctypes.c_void_p()
+        self._check(self.lib.futhark_entry_partition_u32(self.ptr, ctypes.byref(out), ks.ptr))
+        return Pair(self, out.value)
+
+    def entry_bmm_f16(self, A, B):
+        return self._entry_arr("bmm_f16", "f32_3d", A.ptr, B.ptr)
+
+
+# ---- host-buffer conveniences: new -> entry -> values -> free, as a C caller would ----
+
+def _run(ctx, ins, fn, n_out=1):
+    arrs = [ctx.new(t, d) for t, d in ins]
+    try:
+        out = fn(*arrs)
+        try:
+            return out.values()
+        finally:
+            out.free()
+    finally:
+        for a in arrs:
+            a.free()
+
+
+def scan_i32(ctx, xs):
+    return _run(ctx, [("i32_1d", xs)], ctx.entry_scan_i32)
+
+
+def reduce_i32(ctx, xs):
+    a = ctx.new("i32_1d", xs)
+    try:
+        return ctx.entry_reduce_i32(a)
+    finally:
+        a.free()
+
+
+def segscan_f32(ctx, flags, xs):
+    return _run(ctx, [("bool_1d", flags), ("f32_1d", xs)], ctx.entry_segscan_f32)
+
+
+def segreduce_f32(ctx, offsets, flags, xs):
+    return _run(ctx, [("i64_1d", offsets), ("bool_1d", flags), ("f32_1d", xs)], ctx.entry_segreduce_f32)
+
+
+def rowsum_f32(ctx, xss):
+    return _run(ctx, [("f32_2d", xss)], ctx.entry_rowsum_f32)
+
+
+def hist_add_i32(ctx, B, bins, ws):
+    return _run(ctx, [("i32_1d", bins), ("i32_1d", ws)], lambda b, w: ctx.entry_hist_add_i32(B, b, w))
+
+
+def hist_max_f32(ctx, B, bins, ws):
+    return _run(ctx, [("i32_1d", bins), ("f32_1d", ws)], lambda b, w: ctx.entry_hist_max_f32(B, b, w))
+
+
+def filter_u32(ctx, ks):
+    return _run(ctx, [("u32_1d", ks)], ctx.entry_filter_u32)
+
+
+def partition_u32(ctx, ks):
+    a = ctx.new("u32_1d", ks)
+    try:
+        pair = ctx.entry_partition_u32(a)
+        try:
+            s, r = pair.project(0), pair.project(1)
+            try:
+                return s.values(), r.values()
+            finally:
+                s.free()
+                r.free()
+        finally:
+            pair.free()
+    finally:
+        a.free()
+
+
+def bmm_f16(ctx, A, B):
+    A = np.asarray(A).view(np.uint16)
+    B = np.asarray(B).view(np.uint16)
+    return _run(ctx, [("f16_3d", A), ("f16_3d", B)], ctx.entry_bmm_f16)

@@ -1,0 +1,221 @@
+// Generalised histogram (reduce_by_index) for two operators: (+) on i32 weights and
+// max on f32 weights.  Replaces the generated seghist_local / seghist_global kernels
+// of the reference (src/Futhark/CodeGen/ImpGen/GPU/SegHist.hs:377-1188).
+//
+// Both operators become a 32-bit integer atomic: add, or unsigned max on an
+// order-preserving key of the float (so no compare-and-swap loop as in
+// ImpGen/GPU/Base.hs:844-905).  Indices outside [0,B) are skipped
+// (SegHist.hs:450-455); NaN weights are skipped by max, as fmaxf drops them
+// (rts/c/scalar.h:932).
+//
+// Strategies, by number of bins B (CAP = 57344 bins = 224 KiB of shared memory):
+//   B <= CAP      one CTA per SM holds C = 2^k <= 32 private copies of the histogram in
+//                 shared memory, laid out [bin][copy] with copy = lane mod C; for C = 32
+//                 every lane owns a bank, so a warp never conflicts with itself no matter
+//                 how skewed the indices are.  Copies are folded and flushed to the
+//                 result with one global atomic per non-neutral bin.
+//   B <= 4*CAP    the bins are cut into P = ceil(B/CAP) ranges; P consecutive CTAs read
+//                 the same input chunk at the same time (the re-reads are served by L2)
+//                 and each keeps only the indices of its range: one pass over HBM.
+//   larger        global atomics straight into the result, which stays L2-resident for
+//                 the sizes of interest (2^20 bins = 4 MiB).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fb {
+
+constexpr int HIST_THREADS = 1024;
+constexpr int64_t HIST_CAP_BINS = 57344;        // 224 KiB / 4
+constexpr uint32_t KEY_NEG_INF = 0x007FFFFFu;   // key of -inf
+
+__device__ __forceinline__ uint32_t f32_key(uint32_t bits) {
+  return bits ^ ((bits >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+}
+__device__ __forceinline__ uint32_t key_f32(uint32_t key) {
+  return (key & 0x80000000u) ? (key ^ 0x80000000u) : ~key;
+}
+__device__ __forceinline__ bool is_nan_bits(uint32_t bits) { return (bits & 0x7FFFFFFFu) > 0x7F800000u; }
+
+template <int OP>
+__device__ __forceinline__ uint32_t neutral() { return OP == 0 ? 0u : KEY_NEG_INF; }
+
+// update of a shared-memory bin
+template <int OP>
+__device__ __forceinline__ void upd_shared(uint32_t *p, uint32_t w) {
+  if (OP == 0) atomicAdd(p, w);
+  else atomicMax(p, w);
+}
+template <int OP>
+__device__ __forceinline__ void upd_global(uint32_t *p, uint32_t w) {
+  if (OP == 0) atomicAdd(p, w);    // result unused: compiles to a reduction
+  else atomicMax(p, w);
+}
+// weight as stored in the accumulator; `skip` set for a NaN under max
+template <int OP>
+__device__ __forceinline__ uint32_t prep(uint32_t wbits, bool &skip) {
+  if (OP == 0) { skip = false; return wbits; }
+  skip = is_nan_bits(wbits);
+  return f32_key(wbits);
+}
+
+// ---- shared-memory path ------------------------------------------------------------------
+// grid = groups * P CTAs; CTA (g, p) streams the vectors of group g and keeps bins in
+// [p*range, min(B, (p+1)*range)).  log2c = log2 of the number of private copies.
+template <int OP, bool VEC>
+__global__ void __launch_bounds__(HIST_THREADS, 1)
+hist_smem_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ ws, int64_t n, int64_t B,
+                 int P, int64_t range, int log2c, uint32_t *__restrict__ out) {
+  extern __shared__ __align__(16) uint32_t s_hist[];
+  const int tid = threadIdx.x;
+  const int p = blockIdx.x % P;
+  const int64_t g = blockIdx.x / P, groups = gridDim.x / P;
+  const int64_t bin_lo = (int64_t)p * range;
+  const int64_t bin_hi = (bin_lo + range < B) ? bin_lo + range : B;
+  const uint32_t nb = (uint32_t)(bin_hi - bin_lo);
+  const uint32_t C = 1u << log2c;
+  const uint32_t copy = (uint32_t)(tid & 31) & (C - 1);
+  const uint32_t total = nb << log2c;
+  for (uint32_t i = tid; i < total; i += HIST_THREADS) s_hist[i] = neutral<OP>();
+  __syncthreads();
+
+  if (VEC) {
+    const int4 *bv = reinterpret_cast<const int4 *>(bins);
+    const int4 *wv = reinterpret_cast<const int4 *>(ws);
+    const int64_t nvec = n >> 2;
+    const int64_t stride = groups * HIST_THREADS;
+    int64_t i = g * HIST_THREADS + tid;
+    for (; i + stride < nvec; i += 2 * stride) {
+      int4 b0 = ld_stream_v4(bv + i), w0 = ld_stream_v4(wv + i);
+      int4 b1 = ld_stream_v4(bv + i + stride), w1 = ld_stream_v4(wv + i + stride);
+      const int bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const int ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const int64_t b = (int64_t)bb[k] - bin_lo;
+        bool skip;
+        const uint32_t w = prep<OP>((uint32_t)ww[k], skip);
+        if (b >= 0 && b < (int64_t)nb && !skip) upd_shared<OP>(&s_hist[((uint32_t)b << log2c) + copy], w);
+      }
+    }
+    for (; i < nvec; i += stride) {
+      int4 b0 = ld_stream_v4(bv + i), w0 = ld_stream_v4(wv + i);
+      const int bb[4] = {b0.x, b0.y, b0.z, b0.w};
+      const int ww[4] = {w0.x, w0.y, w0.z, w0.w};
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int64_t b = (int64_t)bb[k] - bin_lo;
+        bool skip;
+        const uint32_t w = prep<OP>((uint32_t)ww[k], skip);
+        if (b >= 0 && b < (int64_t)nb && !skip) upd_shared<OP>(&s_hist[((uint32_t)b << log2c) + copy], w);
+      }
+    }
+    // fewer than four trailing elements: the first group's CTAs take them
+    if (g == 0) {
+      const int64_t j = (nvec << 2) + tid;
+      if (j < n) {
+        const int64_t b = (int64_t)bins[j] - bin_lo;
+        bool skip;
+        const uint32_t w = prep<OP>(ws[j], skip);
+        if (b >= 0 && b < (int64_t)nb && !skip) upd_shared<OP>(&s_hist[((uint32_t)b << log2c) + copy], w);
+      }
+    }
+  } else {
+    const int64_t stride = groups * HIST_THREADS;
+    for (int64_t i = g * HIST_THREADS + tid; i < n; i += stride) {
+      const int64_t b = (int64_t)bins[i] - bin_lo;
+      bool skip;
+      const uint32_t w = prep<OP>(ws[i], skip);
+      if (b >= 0 && b < (int64_t)nb && !skip) upd_shared<OP>(&s_hist[((uint32_t)b << log2c) + copy], w);
+    }
+  }
+  __syncthreads();
+  // fold the copies and flush
+  for (uint32_t b = tid; b < nb; b += HIST_THREADS) {
+    uint32_t acc = neutral<OP>();
+    for (uint32_t c = 0; c < C; c++) {
+      // rotate the starting copy per bin so the lanes of a warp hit different banks
+      const uint32_t v = s_hist[(b << log2c) + ((c + b) & (C - 1))];
+      acc = (OP == 0) ? acc + v : (v > acc ? v : acc);
+    }
+    if (acc != neutral<OP>()) upd_global<OP>(&out[bin_lo + b], acc);
+  }
+}
+
+// ---- global-atomic path ---------------------------------------------------------------------
+template <int OP>
+__global__ void __launch_bounds__(256)
+hist_global_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ ws, int64_t n, int64_t B,
+                   uint32_t *__restrict__ out) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+    const int64_t b = (int64_t)ld_stream_b32(bins + i);
+    bool skip;
+    const uint32_t w = prep<OP>((uint32_t)ld_stream_b32(ws + i), skip);
+    if (b >= 0 && b < B && !skip) upd_global<OP>(&out[b], w);
+  }
+}
+
+__global__ void fill_u32_kernel(uint32_t *p, int64_t n, uint32_t v) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
+}
+__global__ void decode_keys_kernel(uint32_t *p, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = key_f32(p[i]);
+}
+
+static int grid_for(int64_t n, int threads, int cap) {
+  int64_t want = (n + threads - 1) / threads;
+  if (want < 1) want = 1;
+  return (int)(want < cap ? want : cap);
+}
+
+template <int OP>
+static cudaError_t launch_hist_op(int64_t B, const int32_t *bins, const uint32_t *ws, int64_t n, uint32_t *out,
+                                  int num_sms, cudaStream_t stream) {
+  // the result starts at the neutral element (prelude/soacs.fut:132-133)
+  fill_u32_kernel<<<grid_for(B, 256, num_sms * 8), 256, 0, stream>>>(out, B, OP == 0 ? 0u : KEY_NEG_INF);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  if (n > 0) {
+    const int64_t P64 = (B + HIST_CAP_BINS - 1) / HIST_CAP_BINS;
+    if (P64 <= 4 && P64 <= num_sms) {
+      const int P = (int)P64;
+      const int64_t range = (B + P - 1) / P;
+      int log2c = 0;
+      while (log2c < 5 && (range << (log2c + 1)) <= HIST_CAP_BINS) log2c++;
+      const size_t smem = (size_t)(range << log2c) * sizeof(uint32_t);
+      const bool vec = ((((uintptr_t)bins) | ((uintptr_t)ws)) & 15) == 0;
+      int64_t max_groups = (n / 4 + HIST_THREADS - 1) / HIST_THREADS;
+      if (max_groups < 1) max_groups = 1;
+      int64_t groups = num_sms / P;
+      if (groups > max_groups) groups = max_groups;
+      const int grid = (int)groups * P;
+      auto kern = vec ? hist_smem_kernel<OP, true> : hist_smem_kernel<OP, false>;
+      err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(HIST_CAP_BINS * 4));
+      if (err != cudaSuccess) return err;
+      kern<<<grid, HIST_THREADS, smem, stream>>>(bins, ws, n, B, P, range, log2c, out);
+    } else {
+      hist_global_kernel<OP><<<grid_for(n, 256, num_sms * 16), 256, 0, stream>>>(bins, ws, n, B, out);
+    }
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+  }
+  if (OP == 1) {
+    decode_keys_kernel<<<grid_for(B, 256, num_sms * 8), 256, 0, stream>>>(out, B);
+    err = cudaGetLastError();
+  }
+  return err;
+}
+
+cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
+                        int num_sms, cudaStream_t stream) {
+  if (B <= 0) return cudaSuccess;
+  if (op == 0)
+    return launch_hist_op<0>(B, bins, reinterpret_cast<const uint32_t *>(weights), n,
+                             reinterpret_cast<uint32_t *>(out), num_sms, stream);
+  return launch_hist_op<1>(B, bins, reinterpret_cast<const uint32_t *>(weights), n,
+                           reinterpret_cast<uint32_t *>(out), num_sms, stream);
+}
+
+}  // namespace fb

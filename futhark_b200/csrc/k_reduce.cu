@@ -1,0 +1,238 @@
+// Reductions: reduce (+) over i32, row sums of a regular [rows][cols] f32 array, and
+// the irregular segmented sum over f32 with segments given by offsets.  They replace
+// the generated segred_nonseg / segred_small / segred_large kernels of the reference
+// (src/Futhark/CodeGen/ImpGen/GPU/SegRed.hs:327-636) and the scan-then-gather form
+// the reference uses for irregular segments
+// (src/Futhark/Pass/Flatten/Builtins.hs:582-602).
+//
+// All three are one pass over HBM with 128-bit streaming loads where alignment
+// allows, several independent loads in flight per thread, and warp shuffles instead
+// of shared-memory trees.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fb {
+
+constexpr int RED_THREADS = 256;
+constexpr int RED_MAX_BLOCKS = 4096;
+
+size_t reduce_scratch_bytes() { return 256 + RED_MAX_BLOCKS * sizeof(uint32_t); }
+
+// ---- reduce (+) 0 over i32 ----------------------------------------------------------
+// Stage one: grid-stride over 16-byte vectors, four loads in flight per thread.
+// Stage two: the CTA that draws the last ticket folds the per-CTA partials
+// (same election as reductionStageTwo, SegRed.hs:923-1047, without the extra barrier
+// rounds).  Integer addition wraps, so any order gives the reference's bits.
+__global__ void __launch_bounds__(RED_THREADS)
+reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict__ d_out,
+                  uint32_t *ticket, uint32_t *partials) {
+  __shared__ uint32_t s_warp[RED_THREADS / 32];
+  __shared__ uint32_t s_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t gtid = (int64_t)blockIdx.x * RED_THREADS + tid;
+  const int64_t gthreads = (int64_t)gridDim.x * RED_THREADS;
+
+  // peel to a 16-byte boundary
+  const uintptr_t addr = (uintptr_t)in;
+  int64_t head = (int64_t)(((16 - (addr & 15)) & 15) >> 2);
+  if (head > n) head = n;
+  const int4 *vec = reinterpret_cast<const int4 *>(in + head);
+  const int64_t nvec = (n - head) >> 2;
+  const int64_t tail_start = head + (nvec << 2);
+
+  uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+  int64_t i = gtid;
+  for (; i + 3 * gthreads < nvec; i += 4 * gthreads) {
+    int4 v0 = ld_stream_v4(vec + i);
+    int4 v1 = ld_stream_v4(vec + i + gthreads);
+    int4 v2 = ld_stream_v4(vec + i + 2 * gthreads);
+    int4 v3 = ld_stream_v4(vec + i + 3 * gthreads);
+    a0 += (uint32_t)v0.x + (uint32_t)v0.y + (uint32_t)v0.z + (uint32_t)v0.w;
+    a1 += (uint32_t)v1.x + (uint32_t)v1.y + (uint32_t)v1.z + (uint32_t)v1.w;
+    a2 += (uint32_t)v2.x + (uint32_t)v2.y + (uint32_t)v2.z + (uint32_t)v2.w;
+    a3 += (uint32_t)v3.x + (uint32_t)v3.y + (uint32_t)v3.z + (uint32_t)v3.w;
+  }
+  for (; i < nvec; i += gthreads) {
+    int4 v0 = ld_stream_v4(vec + i);
+    a0 += (uint32_t)v0.x + (uint32_t)v0.y + (uint32_t)v0.z + (uint32_t)v0.w;
+  }
+  uint32_t acc = a0 + a1 + a2 + a3;
+  if (gtid < head) acc += (uint32_t)in[gtid];
+  if (tail_start + gtid < n) acc += (uint32_t)in[tail_start + gtid];   // fewer than 4 elements
+
+  acc = warp_sum(acc);
+  if (lane == 0) s_warp[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t b = (lane < RED_THREADS / 32) ? s_warp[lane] : 0u;
+    b = warp_sum(b);
+    if (lane == 0) {
+      partials[blockIdx.x] = b;
+      __threadfence();
+      uint32_t t = atomicAdd(ticket, 1u);
+      s_last = (t == gridDim.x - 1) ? 1u : 0u;
+    }
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    uint32_t s = 0;
+    for (int j = tid; j < (int)gridDim.x; j += RED_THREADS)
+      s += *reinterpret_cast<volatile uint32_t *>(&partials[j]);
+    s = warp_sum(s);
+    __syncthreads();
+    if (lane == 0) s_warp[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t b = (lane < RED_THREADS / 32) ? s_warp[lane] : 0u;
+      b = warp_sum(b);
+      if (lane == 0) { *d_out = (int32_t)b; *ticket = 0u; }
+    }
+  }
+}
+
+cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void *scratch, int num_sms,
+                              cudaStream_t stream) {
+  if (n <= 0) return cudaMemsetAsync(d_out, 0, sizeof(int32_t), stream);   // the neutral element
+  uint32_t *ticket = reinterpret_cast<uint32_t *>(scratch);
+  uint32_t *partials = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(scratch) + 256);
+  int64_t want = (n / 4 + RED_THREADS - 1) / RED_THREADS;
+  int blocks = num_sms * 8;
+  if (blocks > RED_MAX_BLOCKS) blocks = RED_MAX_BLOCKS;
+  if (want < blocks) blocks = want < 1 ? 1 : (int)want;
+  reduce_i32_kernel<<<blocks, RED_THREADS, 0, stream>>>(in, n, d_out, ticket, partials);
+  return cudaGetLastError();
+}
+
+// ---- map (reduce (+) 0) over the rows of [rows][cols] f32 -------------------------------
+// One warp per row (persistent, grid-stride over rows): lane l adds the 16-byte
+// vectors l, l+32, ... of the row into four running sums, then a shuffle tree.
+template <bool VEC>
+__global__ void __launch_bounds__(RED_THREADS)
+rowsum_warp_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, float *__restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = ((int64_t)blockIdx.x * RED_THREADS + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * RED_THREADS) >> 5;
+  for (int64_t r = warp_global; r < rows; r += nwarps) {
+    const float *row = in + r * cols;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (VEC) {
+      const int4 *v = reinterpret_cast<const int4 *>(row);
+      const int64_t nv = cols >> 2;
+      int64_t i = lane;
+#pragma unroll 1
+      for (; i + 96 < nv; i += 128) {
+        int4 q0 = ld_stream_v4(v + i), q1 = ld_stream_v4(v + i + 32);
+        int4 q2 = ld_stream_v4(v + i + 64), q3 = ld_stream_v4(v + i + 96);
+        s0 += __int_as_float(q0.x); s1 += __int_as_float(q0.y); s2 += __int_as_float(q0.z); s3 += __int_as_float(q0.w);
+        s0 += __int_as_float(q1.x); s1 += __int_as_float(q1.y); s2 += __int_as_float(q1.z); s3 += __int_as_float(q1.w);
+        s0 += __int_as_float(q2.x); s1 += __int_as_float(q2.y); s2 += __int_as_float(q2.z); s3 += __int_as_float(q2.w);
+        s0 += __int_as_float(q3.x); s1 += __int_as_float(q3.y); s2 += __int_as_float(q3.z); s3 += __int_as_float(q3.w);
+      }
+      for (; i < nv; i += 32) {
+        int4 q0 = ld_stream_v4(v + i);
+        s0 += __int_as_float(q0.x); s1 += __int_as_float(q0.y); s2 += __int_as_float(q0.z); s3 += __int_as_float(q0.w);
+      }
+    } else {
+      for (int64_t i = lane; i < cols; i += 32) s0 += row[i];
+    }
+    float s = warp_sum_down((s0 + s1) + (s2 + s3));
+    if (lane == 0) out[r] = s;
+  }
+}
+
+// One CTA per row, for rows too long for a single warp to stream efficiently.
+__global__ void __launch_bounds__(RED_THREADS)
+rowsum_block_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, float *__restrict__ out) {
+  __shared__ float s_warp[RED_THREADS / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float *row = in + r * cols;
+    float s0 = 0.f, s1 = 0.f;
+    int64_t i = tid;
+    for (; i + RED_THREADS < cols; i += 2 * RED_THREADS) { s0 += row[i]; s1 += row[i + RED_THREADS]; }
+    if (i < cols) s0 += row[i];
+    float s = warp_sum_down(s0 + s1);
+    __syncthreads();
+    if (lane == 0) s_warp[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+      float b = (lane < RED_THREADS / 32) ? s_warp[lane] : 0.f;
+      b = warp_sum_down(b);
+      if (lane == 0) out[r] = b;
+    }
+  }
+}
+
+// One thread per row, for very short rows.
+__global__ void __launch_bounds__(RED_THREADS)
+rowsum_thread_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, float *__restrict__ out) {
+  const int64_t gthreads = (int64_t)gridDim.x * RED_THREADS;
+  for (int64_t r = (int64_t)blockIdx.x * RED_THREADS + threadIdx.x; r < rows; r += gthreads) {
+    const float *row = in + r * cols;
+    float s = 0.f;
+    for (int64_t i = 0; i < cols; i++) s += row[i];
+    out[r] = s;
+  }
+}
+
+cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float *out, int num_sms,
+                              cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  if (cols <= 0) return cudaMemsetAsync(out, 0, (size_t)rows * sizeof(float), stream);
+  if (cols < 16) {
+    int64_t want = (rows + RED_THREADS - 1) / RED_THREADS;
+    int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
+    rowsum_thread_kernel<<<blocks, RED_THREADS, 0, stream>>>(in, rows, cols, out);
+  } else if (cols <= 16384) {
+    int64_t want = (rows * 32 + RED_THREADS - 1) / RED_THREADS;
+    int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
+    const bool vec = (cols % 4 == 0) && ((((uintptr_t)in) & 15) == 0);
+    if (vec) rowsum_warp_kernel<true><<<blocks, RED_THREADS, 0, stream>>>(in, rows, cols, out);
+    else rowsum_warp_kernel<false><<<blocks, RED_THREADS, 0, stream>>>(in, rows, cols, out);
+  } else {
+    int blocks = (int)(rows < (int64_t)num_sms * 8 ? rows : (int64_t)num_sms * 8);
+    rowsum_block_kernel<<<blocks, RED_THREADS, 0, stream>>>(in, rows, cols, out);
+  }
+  return cudaGetLastError();
+}
+
+// ---- irregular segmented sum: out[s] = sum xs[offsets[s] .. offsets[s+1]) ------------------
+// One warp per segment, persistent over the segments.  Segment starts are arbitrary,
+// so loads are 4-byte but contiguous across the warp; four in flight per lane.  Offsets
+// are clamped to [0,n], so a malformed offsets array cannot cause an out-of-range read.
+__global__ void __launch_bounds__(RED_THREADS)
+segreduce_f32_kernel(const int64_t *__restrict__ offsets, int64_t nseg, const float *__restrict__ xs, int64_t n,
+                     float *__restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = ((int64_t)blockIdx.x * RED_THREADS + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * RED_THREADS) >> 5;
+  for (int64_t s = warp_global; s < nseg; s += nwarps) {
+    int64_t lo = offsets[s], hi = offsets[s + 1];
+    lo = lo < 0 ? 0 : (lo > n ? n : lo);
+    hi = hi < lo ? lo : (hi > n ? n : hi);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int64_t i = lo + lane;
+    for (; i + 96 < hi; i += 128) {
+      float q0 = __int_as_float(ld_stream_b32(xs + i));
+      float q1 = __int_as_float(ld_stream_b32(xs + i + 32));
+      float q2 = __int_as_float(ld_stream_b32(xs + i + 64));
+      float q3 = __int_as_float(ld_stream_b32(xs + i + 96));
+      s0 += q0; s1 += q1; s2 += q2; s3 += q3;
+    }
+    for (; i < hi; i += 32) s0 += __int_as_float(ld_stream_b32(xs + i));
+    float t = warp_sum_down((s0 + s1) + (s2 + s3));
+    if (lane == 0) out[s] = t;
+  }
+}
+
+cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
+                                 int num_sms, cudaStream_t stream) {
+  if (nseg <= 0) return cudaSuccess;
+  int64_t want = (nseg * 32 + RED_THREADS - 1) / RED_THREADS;
+  int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
+  segreduce_f32_kernel<<<blocks, RED_THREADS, 0, stream>>>(offsets, nseg, xs, n, out);
+  return cudaGetLastError();
+}
+
+}  // namespace fb

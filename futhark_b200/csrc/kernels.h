@@ -1,0 +1,42 @@
+// Host-callable launchers of the sm_100a kernels.  Plain pointers and sizes only;
+// every launcher enqueues on the given stream and returns the launch status.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fb {
+
+// ---- look-back family (k_scan.cu) ---------------------------------------------------
+// `scratch` must hold lookback_scratch_bytes(n) bytes, zeroed once when allocated;
+// `epoch` must differ from the epochs of earlier launches that used the same scratch
+// (1 .. 2^29-1); `failure` is the context's device failure word.
+size_t lookback_scratch_bytes(int64_t n);
+cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in, void *scratch,
+                            uint32_t epoch, int *failure, cudaStream_t stream);
+cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
+                               void *scratch, uint32_t epoch, int *failure, cudaStream_t stream);
+cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out_true, uint32_t *out_false,
+                               int64_t n, int64_t *d_count, void *scratch, uint32_t epoch, int *failure,
+                               cudaStream_t stream);
+
+// ---- reductions (k_reduce.cu) ---------------------------------------------------------
+// `scratch` must hold reduce_scratch_bytes() bytes, zeroed once when allocated.
+size_t reduce_scratch_bytes();
+cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void *scratch, int num_sms,
+                              cudaStream_t stream);
+cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float *out, int num_sms,
+                              cudaStream_t stream);
+cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
+                                 int num_sms, cudaStream_t stream);
+
+// ---- histograms (k_hist.cu) -------------------------------------------------------------
+// op 0: (+) on i32 weights; op 1: max on f32 weights (result in f32 bits).  `out` holds
+// B 4-byte bins and is fully overwritten.
+cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
+                        int num_sms, cudaStream_t stream);
+
+// ---- batched f16 contraction (k_bmm.cu) ------------------------------------------------
+cudaError_t launch_bmm_f16(const uint16_t *A, const uint16_t *B, float *C, int64_t nb, int64_t m, int64_t k,
+                           int64_t n, int *failure, cudaStream_t stream);
+
+}  // namespace fb

@@ -1,0 +1,238 @@
+/* futhark_b200.h -- C API of the B200-native SegOp core.
+ *
+ * The symbols below are the ones `futhark cuda --library` generates for a program
+ * with the nine entry points listed at the end of this file; each declaration
+ * cites the place in the reference (diku-dk/futhark v0.28.0) that defines the
+ * interface it replaces.  A host program written against the generated header of
+ * that program links against libfuthark_b200.so unchanged.
+ *
+ * Conventions (docs/c-api.rst):
+ *  - every function is asynchronous with respect to the device unless stated;
+ *    results are valid after futhark_context_sync() returns 0      (:176-180, :580-596)
+ *  - values are reference counted; every value returned by a `new`, an entry
+ *    point or a projection must be freed exactly once               (:249-254, :598-601)
+ *  - all public calls on one context are serialised by a lock
+ *    (src/Futhark/CodeGen/Backends/GenericC/Monad.hs:707-714)
+ *  - f16 data crosses the API as uint16_t binary16 bits             (:229-233)
+ *  - bool is one byte, 0 or 1 (docs/binary-data-format.rst)
+ *  - multi-dimensional arrays are row-major                         (:262-266)
+ */
+#ifndef FUTHARK_B200_H
+#define FUTHARK_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#ifdef FUTHARK_B200_NO_CUDA_H
+typedef unsigned long long CUdeviceptr;   /* same underlying type as in <cuda.h> */
+#else
+#include <cuda.h>                          /* the generated header includes it too
+                                              (src/Futhark/CodeGen/Backends/CCUDA.hs:134-138) */
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)   /* the library is built with hidden visibility */
+#endif
+
+/* ---- error codes: rts/c/errors.h:1-3, docs/c-api.rst:37-58 ----------------- */
+#define FUTHARK_SUCCESS 0
+#define FUTHARK_PROGRAM_ERROR 2
+#define FUTHARK_OUT_OF_MEMORY 3
+
+/* ---- configuration: rts/c/context.h:95-163, docs/c-api.rst:60-145 ---------- */
+struct futhark_context_config;
+struct futhark_context_config *futhark_context_config_new(void);
+void futhark_context_config_free(struct futhark_context_config *cfg);
+void futhark_context_config_set_debugging(struct futhark_context_config *cfg, int flag);
+void futhark_context_config_set_profiling(struct futhark_context_config *cfg, int flag);
+void futhark_context_config_set_logging(struct futhark_context_config *cfg, int flag);
+int futhark_context_config_set_tuning_param(struct futhark_context_config *cfg,
+                                            const char *param_name, size_t new_value);
+int futhark_get_tuning_param_count(void);
+const char *futhark_get_tuning_param_name(int i);
+const char *futhark_get_tuning_param_class(int i);
+void futhark_context_config_set_cache_file(struct futhark_context_config *cfg, const char *f);
+
+/* GPU configuration: rts/c/backends/cuda.h:134-179, rts/c/gpu.h:54-91,
+ * src/Futhark/CodeGen/Backends/CCUDA.hs:46-51.  The kernels of this library are
+ * compiled ahead of time for sm_100a, so the NVRTC / PTX / program-text setters
+ * are accepted and ignored. */
+void futhark_context_config_set_device(struct futhark_context_config *cfg, const char *s);
+void futhark_context_config_set_unified_memory(struct futhark_context_config *cfg, int flag);
+void futhark_context_config_set_default_thread_block_size(struct futhark_context_config *cfg, int size);
+void futhark_context_config_set_default_group_size(struct futhark_context_config *cfg, int size);
+void futhark_context_config_set_default_grid_size(struct futhark_context_config *cfg, int num);
+void futhark_context_config_set_default_num_groups(struct futhark_context_config *cfg, int num);
+void futhark_context_config_set_default_tile_size(struct futhark_context_config *cfg, int size);
+void futhark_context_config_set_default_reg_tile_size(struct futhark_context_config *cfg, int size);
+void futhark_context_config_set_default_registers(struct futhark_context_config *cfg, int size);
+void futhark_context_config_set_default_cache(struct futhark_context_config *cfg, int size);
+void futhark_context_config_set_default_threshold(struct futhark_context_config *cfg, int size);
+const char *futhark_context_config_get_program(struct futhark_context_config *cfg);
+void futhark_context_config_set_program(struct futhark_context_config *cfg, const char *s);
+void futhark_context_config_add_nvrtc_option(struct futhark_context_config *cfg, const char *opt);
+void futhark_context_config_dump_ptx_to(struct futhark_context_config *cfg, const char *s);
+void futhark_context_config_load_ptx_from(struct futhark_context_config *cfg, const char *s);
+
+/* ---- context: rts/c/context.h:89-211, rts/c/backends/cuda.h:719-861,
+ *      src/Futhark/CodeGen/Backends/GenericC.hs:603-640 ---------------------- */
+struct futhark_context;
+struct futhark_context *futhark_context_new(struct futhark_context_config *cfg);
+void futhark_context_free(struct futhark_context *ctx);
+int futhark_context_sync(struct futhark_context *ctx);
+char *futhark_context_get_error(struct futhark_context *ctx);   /* caller frees; clears */
+void futhark_context_set_logging_file(struct futhark_context *ctx, FILE *f);
+void futhark_context_pause_profiling(struct futhark_context *ctx);
+void futhark_context_unpause_profiling(struct futhark_context *ctx);
+char *futhark_context_report(struct futhark_context *ctx);      /* caller frees; JSON */
+int futhark_context_clear_caches(struct futhark_context *ctx);
+
+/* ---- arrays: src/Futhark/CodeGen/Backends/GenericC/Types.hs:61-250,
+ *      docs/c-api.rst:256-315; raw pointers are CUdeviceptr (CCUDA.hs:105-107) - */
+#define FUTHARK_B200_ARRAY_COMMON(NAME, CT)                                                    \
+  struct futhark_##NAME;                                                                       \
+  int futhark_free_##NAME(struct futhark_context *ctx, struct futhark_##NAME *arr);            \
+  int futhark_values_##NAME(struct futhark_context *ctx, struct futhark_##NAME *arr, CT *data);\
+  CUdeviceptr futhark_values_raw_##NAME(struct futhark_context *ctx, struct futhark_##NAME *arr);\
+  const int64_t *futhark_shape_##NAME(struct futhark_context *ctx, struct futhark_##NAME *arr);
+
+#define FUTHARK_B200_ARRAY_1D(NAME, CT)                                                        \
+  FUTHARK_B200_ARRAY_COMMON(NAME, CT)                                                          \
+  struct futhark_##NAME *futhark_new_##NAME(struct futhark_context *ctx, const CT *data,       \
+                                            int64_t dim0);                                     \
+  struct futhark_##NAME *futhark_new_raw_##NAME(struct futhark_context *ctx, CUdeviceptr data, \
+                                                int64_t dim0);                                 \
+  int futhark_index_##NAME(struct futhark_context *ctx, CT *out, struct futhark_##NAME *arr,   \
+                           int64_t i0);
+
+#define FUTHARK_B200_ARRAY_2D(NAME, CT)                                                        \
+  FUTHARK_B200_ARRAY_COMMON(NAME, CT)                                                          \
+  struct futhark_##NAME *futhark_new_##NAME(struct futhark_context *ctx, const CT *data,       \
+                                            int64_t dim0, int64_t dim1);                       \
+  struct futhark_##NAME *futhark_new_raw_##NAME(struct futhark_context *ctx, CUdeviceptr data, \
+                                                int64_t dim0, int64_t dim1);                   \
+  int futhark_index_##NAME(struct futhark_context *ctx, CT *out, struct futhark_##NAME *arr,   \
+                           int64_t i0, int64_t i1);
+
+#define FUTHARK_B200_ARRAY_3D(NAME, CT)                                                        \
+  FUTHARK_B200_ARRAY_COMMON(NAME, CT)                                                          \
+  struct futhark_##NAME *futhark_new_##NAME(struct futhark_context *ctx, const CT *data,       \
+                                            int64_t dim0, int64_t dim1, int64_t dim2);         \
+  struct futhark_##NAME *futhark_new_raw_##NAME(struct futhark_context *ctx, CUdeviceptr data, \
+                                                int64_t dim0, int64_t dim1, int64_t dim2);     \
+  int futhark_index_##NAME(struct futhark_context *ctx, CT *out, struct futhark_##NAME *arr,   \
+                           int64_t i0, int64_t i1, int64_t i2);
+
+FUTHARK_B200_ARRAY_1D(i32_1d, int32_t)
+FUTHARK_B200_ARRAY_1D(i64_1d, int64_t)
+FUTHARK_B200_ARRAY_1D(u32_1d, uint32_t)
+FUTHARK_B200_ARRAY_1D(f32_1d, float)
+FUTHARK_B200_ARRAY_1D(bool_1d, bool)
+FUTHARK_B200_ARRAY_2D(f32_2d, float)
+FUTHARK_B200_ARRAY_3D(f32_3d, float)
+FUTHARK_B200_ARRAY_3D(f16_3d, uint16_t)
+
+/* ---- opaque tuple returned by partition: naming per
+ *      src/Futhark/CodeGen/Backends/SimpleRep.hs:152-158; functions per
+ *      docs/c-api.rst:317-438 (free, store, restore, new, project) ------------ */
+struct futhark_opaque_tup2_arr1d_u32_arr1d_u32;
+int futhark_free_opaque_tup2_arr1d_u32_arr1d_u32(struct futhark_context *ctx,
+                                                 struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *obj);
+int futhark_store_opaque_tup2_arr1d_u32_arr1d_u32(struct futhark_context *ctx,
+                                                  const struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *obj,
+                                                  void **p, size_t *n);
+struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *
+futhark_restore_opaque_tup2_arr1d_u32_arr1d_u32(struct futhark_context *ctx, const void *p);
+int futhark_new_opaque_tup2_arr1d_u32_arr1d_u32(struct futhark_context *ctx,
+                                                struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 **out,
+                                                const struct futhark_u32_1d *v0,
+                                                const struct futhark_u32_1d *v1);
+int futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_0(struct futhark_context *ctx,
+                                                      struct futhark_u32_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *obj);
+int futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(struct futhark_context *ctx,
+                                                      struct futhark_u32_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *obj);
+
+/* ---- entry points: src/Futhark/CodeGen/Backends/GenericC/EntryPoints.hs:133-223.
+ * One out-parameter each; array results are allocated by the callee and owned by
+ * the caller; on error the out-parameter is untouched.  The Futhark source of each
+ * entry is given; the kernels that implement them replace what
+ * src/Futhark/CodeGen/ImpGen/GPU/{SegRed,SegScan/SinglePass,SegHist,SegMap}.hs
+ * would have generated. */
+
+/* entry scan_i32 (xs: []i32): []i32 = scan (+) 0 xs
+ * replaces the segscan kernel of ImpGen/GPU/SegScan/SinglePass.hs:327-879 */
+int futhark_entry_scan_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                           const struct futhark_i32_1d *in0);
+
+/* entry reduce_i32 (xs: []i32): i32 = reduce (+) 0 xs
+ * replaces segred_nonseg, ImpGen/GPU/SegRed.hs:327-394.  The scalar result is read
+ * back, so this call synchronises (Backends/GPU.hs:269-281). */
+int futhark_entry_reduce_i32(struct futhark_context *ctx, int32_t *out0,
+                             const struct futhark_i32_1d *in0);
+
+/* entry segscan_f32 (flags: []bool) (xs: []f32): []f32
+ *   = (unzip (scan (\(f1,x) (f2,y) -> (f1||f2, if f2 then y else x+y)) (false,0) (zip flags xs))).1
+ * (the idiom of tests/soacs/scan2.fut:7-17); replaces the pair scan through
+ * SinglePass.hs:327-879. */
+int futhark_entry_segscan_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0,
+                              const struct futhark_bool_1d *in0, const struct futhark_f32_1d *in1);
+
+/* entry segreduce_f32 (offsets: []i64) (flags: []bool) (xs: []f32): []f32
+ * Segment s covers xs[offsets[s] .. offsets[s+1]); result length = length offsets - 1;
+ * an empty segment gives 0.  Replaces the flagged scan + gather of
+ * src/Futhark/Pass/Flatten/Builtins.hs:582-602. */
+int futhark_entry_segreduce_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0,
+                                const struct futhark_i64_1d *in0, const struct futhark_bool_1d *in1,
+                                const struct futhark_f32_1d *in2);
+
+/* entry rowsum_f32 (xss: [][]f32): []f32 = map (reduce (+) 0) xss
+ * (tests/segredomap/segsum-comm.fut:9-10); replaces segred_small / segred_large,
+ * ImpGen/GPU/SegRed.hs:396-636. */
+int futhark_entry_rowsum_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0,
+                             const struct futhark_f32_2d *in0);
+
+/* entry hist_add_i32 (B: i64) (is: []i32) (ws: []i32): [B]i32
+ *   = hist (+) 0 B (map i64.i32 is) ws            (prelude/soacs.fut:132-133)
+ * entry hist_max_f32 (B: i64) (is: []i32) (ws: []f32): [B]f32
+ *   = hist f32.max f32.lowest B (map i64.i32 is) ws
+ * Indices outside [0,B) are ignored.  Replace seghist_local / seghist_global,
+ * ImpGen/GPU/SegHist.hs:377-1188. */
+int futhark_entry_hist_add_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                               const int64_t in0, const struct futhark_i32_1d *in1,
+                               const struct futhark_i32_1d *in2);
+int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0,
+                               const int64_t in0, const struct futhark_i32_1d *in1,
+                               const struct futhark_f32_1d *in2);
+
+/* entry filter_u32 (ks: []u32): []u32 = filter (\k -> (k & 7) < 3) ks
+ * entry partition_u32 (ks: []u32): ([]u32, []u32) = partition (\k -> (k & 7) < 3) ks
+ * (prelude/soacs.fut:241-286: stable; the split count is shape[0] of field 0).
+ * Both read the result size back, so they synchronise. */
+int futhark_entry_filter_u32(struct futhark_context *ctx, struct futhark_u32_1d **out0,
+                             const struct futhark_u32_1d *in0);
+int futhark_entry_partition_u32(struct futhark_context *ctx,
+                                struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 **out0,
+                                const struct futhark_u32_1d *in0);
+
+/* entry bmm_f16 (A: [b][m][k]f16) (B: [b][k][n]f16): [b][m][n]f32
+ *   = map2 (\a b -> map (\ar -> map (\bc -> f32.sum (map2 (\x y -> f32.f16 x * f32.f16 y) ar bc))
+ *                                   (transpose b)) a) A B
+ * (shape of tests/reg-tiling/mmm.fut:17-21); replaces the block/register-tiled
+ * segmap_intrablock of src/Futhark/Optimise/BlkRegTiling.hs:68-140. */
+int futhark_entry_bmm_f16(struct futhark_context *ctx, struct futhark_f32_3d **out0,
+                          const struct futhark_f16_3d *in0, const struct futhark_f16_3d *in1);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUTHARK_B200_H */

@@ -1,0 +1,202 @@
+"""numpy front-end of the CPU oracle (test infrastructure, not product code).
+
+Only the tests, the smoke check and the bench's CPU-baseline leg import this
+package.  Each function runs the C restatement in oracle/oracle.c on numpy arrays
+and returns fresh numpy arrays shaped like the results of the corresponding
+`futhark_entry_*` call.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path) or os.path.getmtime(path) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
+            _build.build()
+        L = ctypes.CDLL(path)
+        i64, i32, vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+        L.orc_max_threads.restype = ctypes.c_int
+        L.orc_reduce_i32.restype = ctypes.c_int32
+        L.orc_reduce_i32.argtypes = [vp, i64, i32]
+        L.orc_scan_i32.argtypes = [vp, i64, vp, i32]
+        L.orc_segscan_f32.argtypes = [vp, vp, i64, vp, i32]
+        L.orc_segscan_f32_seq64.argtypes = [vp, vp, i64, vp]
+        L.orc_segreduce_f32.argtypes = [vp, i64, vp, vp, i32]
+        L.orc_rowsum_f32.argtypes = [vp, i64, i64, vp, i32]
+        L.orc_hist_add_i32.argtypes = [i64, vp, vp, i64, vp, i32]
+        L.orc_hist_max_f32.argtypes = [i64, vp, vp, i64, vp, i32]
+        L.orc_reduce_by_index_add_i32.argtypes = [vp, i64, vp, vp, i64]
+        L.orc_filter_u32.restype = i64
+        L.orc_filter_u32.argtypes = [vp, i64, vp, i32]
+        L.orc_partition_u32.restype = i64
+        L.orc_partition_u32.argtypes = [vp, i64, vp, i32]
+        L.orc_bmm_f16.argtypes = [vp, vp, i64, i64, i64, i64, vp, i32]
+        L.orc_mm_f32.argtypes = [vp, vp, i64, i64, i64, vp]
+        L.orc_half_to_float.restype = ctypes.c_float
+        L.orc_half_to_float.argtypes = [ctypes.c_uint16]
+        L.orc_add32.restype = ctypes.c_uint32
+        L.orc_add32.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
+        L.orc_fmax32.restype = ctypes.c_float
+        L.orc_fmax32.argtypes = [ctypes.c_float, ctypes.c_float]
+        _lib = L
+    return _lib
+
+
+def ref_scalar():
+    """The reference's own scalar primitives (oracle/_ref), or None if not built."""
+    global _ref
+    if _ref is None:
+        path = os.path.join(_HERE, "_ref", "libref_scalar.so")
+        if not os.path.exists(path):
+            try:
+                _build.build()
+            except Exception:
+                pass
+        if not os.path.exists(path):
+            return None
+        R = ctypes.CDLL(path)
+        R.ref_add32.restype = ctypes.c_uint32
+        R.ref_add32.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
+        for f in ("ref_fadd32", "ref_fmul32", "ref_fmax32"):
+            getattr(R, f).restype = ctypes.c_float
+            getattr(R, f).argtypes = [ctypes.c_float, ctypes.c_float]
+        R.ref_halfbits2float.restype = ctypes.c_float
+        R.ref_halfbits2float.argtypes = [ctypes.c_uint16]
+        R.ref_float2halfbits.restype = ctypes.c_uint16
+        R.ref_float2halfbits.argtypes = [ctypes.c_float]
+        R.ref_ult32.restype = ctypes.c_bool
+        R.ref_ult32.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
+        R.ref_sext_i32_i64.restype = ctypes.c_int64
+        R.ref_sext_i32_i64.argtypes = [ctypes.c_int32]
+        _ref = R
+    return _ref
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def max_threads():
+    return int(lib().orc_max_threads())
+
+
+def reduce_i32(xs, threads=0):
+    xs = _c(xs, np.int32)
+    return int(lib().orc_reduce_i32(_p(xs), xs.size, threads))
+
+
+def scan_i32(xs, threads=0):
+    xs = _c(xs, np.int32)
+    out = np.empty_like(xs)
+    lib().orc_scan_i32(_p(xs), xs.size, _p(out), threads)
+    return out
+
+
+def segscan_f32(flags, xs, threads=0):
+    flags = _c(flags, np.uint8)
+    xs = _c(xs, np.float32)
+    assert flags.size == xs.size
+    out = np.empty_like(xs)
+    lib().orc_segscan_f32(_p(flags), _p(xs), xs.size, _p(out), threads)
+    return out
+
+
+def segscan_f32_seq64(flags, xs):
+    flags = _c(flags, np.uint8)
+    xs = _c(xs, np.float32)
+    out = np.empty(xs.size, dtype=np.float64)
+    lib().orc_segscan_f32_seq64(_p(flags), _p(xs), xs.size, _p(out))
+    return out
+
+
+def segreduce_f32(offsets, xs, threads=0):
+    offsets = _c(offsets, np.int64)
+    xs = _c(xs, np.float32)
+    nseg = max(offsets.size - 1, 0)
+    out = np.empty(nseg, dtype=np.float32)
+    if nseg:
+        lib().orc_segreduce_f32(_p(offsets), nseg, _p(xs), _p(out), threads)
+    return out
+
+
+def rowsum_f32(xss, threads=0):
+    xss = _c(xss, np.float32)
+    rows, cols = xss.shape
+    out = np.empty(rows, dtype=np.float32)
+    if rows:
+        lib().orc_rowsum_f32(_p(xss), rows, cols, _p(out), threads)
+    return out
+
+
+def hist_add_i32(B, bins, ws, threads=0):
+    bins = _c(bins, np.int32)
+    ws = _c(ws, np.int32)
+    out = np.zeros(B, dtype=np.int32)
+    lib().orc_hist_add_i32(B, _p(bins), _p(ws), bins.size, _p(out), threads)
+    return out
+
+
+def hist_max_f32(B, bins, ws, threads=0):
+    bins = _c(bins, np.int32)
+    ws = _c(ws, np.float32)
+    out = np.full(B, -np.inf, dtype=np.float32)
+    lib().orc_hist_max_f32(B, _p(bins), _p(ws), bins.size, _p(out), threads)
+    return out
+
+
+def reduce_by_index_add_i32(dest, bins, ws):
+    dest = np.array(dest, dtype=np.int32)
+    bins = _c(bins, np.int32)
+    ws = _c(ws, np.int32)
+    lib().orc_reduce_by_index_add_i32(_p(dest), dest.size, _p(bins), _p(ws), bins.size)
+    return dest
+
+
+def filter_u32(ks, threads=0):
+    ks = _c(ks, np.uint32)
+    out = np.empty_like(ks)
+    cnt = lib().orc_filter_u32(_p(ks), ks.size, _p(out), threads)
+    return out[:cnt].copy()
+
+
+def partition_u32(ks, threads=0):
+    ks = _c(ks, np.uint32)
+    out = np.empty_like(ks)
+    cnt = lib().orc_partition_u32(_p(ks), ks.size, _p(out), threads)
+    return out[:cnt].copy(), out[cnt:].copy()
+
+
+def bmm_f16(A, B, threads=0):
+    """A: [b][m][k] binary16 bits (uint16 or float16), B: [b][k][n]; returns f32 [b][m][n]."""
+    A = _c(np.asarray(A).view(np.uint16), np.uint16)
+    B = _c(np.asarray(B).view(np.uint16), np.uint16)
+    nb, m, kk = A.shape
+    nb2, kk2, n = B.shape
+    assert nb == nb2 and kk == kk2
+    out = np.empty((nb, m, n), dtype=np.float32)
+    lib().orc_bmm_f16(_p(A), _p(B), nb, m, kk, n, _p(out), threads)
+    return out
+
+
+def mm_f32(A, B):
+    A = _c(A, np.float32)
+    B = _c(B, np.float32)
+    m, kk = A.shape
+    _, n = B.shape
+    out = np.empty((m, n), dtype=np.float32)
+    lib().orc_mm_f32(_p(A), _p(B), m, kk, n, _p(out))
+    return out

@@ -1,0 +1,47 @@
+"""Build recipe for the CPU oracle (test infrastructure, not product code).
+
+`build()` compiles oracle/oracle.c into oracle/liboracle.so and, when a checkout of
+the reference is present, the scalar shim oracle/ref_scalar.c against the
+reference's own rts/c headers into oracle/_ref/libref_scalar.so.  Nothing from the
+reference is copied: the headers are included from where they lie.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REFERENCE_RTS = os.environ.get("FUTHARK_REFERENCE_RTS", "/root/reference/rts/c")
+
+
+def _stale(target, sources):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def build(force=False, verbose=False):
+    src = os.path.join(HERE, "oracle.c")
+    lib = os.path.join(HERE, "liboracle.so")
+    if force or _stale(lib, [src]):
+        cmd = ["gcc", "-O3", "-std=c99", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC",
+               src, "-o", lib, "-lm"]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.check_call(cmd)
+    ref_src = os.path.join(HERE, "ref_scalar.c")
+    ref_dir = os.path.join(HERE, "_ref")
+    ref_lib = os.path.join(ref_dir, "libref_scalar.so")
+    if os.path.isfile(os.path.join(REFERENCE_RTS, "scalar.h")):
+        if force or _stale(ref_lib, [ref_src]):
+            os.makedirs(ref_dir, exist_ok=True)
+            cmd = ["gcc", "-O2", "-std=c99", "-w", "-shared", "-fPIC", "-I", REFERENCE_RTS,
+                   ref_src, "-o", ref_lib, "-lm"]
+            if verbose:
+                print(" ".join(cmd))
+            subprocess.check_call(cmd)
+    return lib
+
+
+if __name__ == "__main__":
+    build(force="--force" in sys.argv, verbose=True)

@@ -1,0 +1,172 @@
+"""Pins the CPU oracle against the known-answer vectors of the reference's own tests
+(tests/golden/reference_vectors.json, extracted from the reference's .fut files by
+tests/golden/extract_reference_vectors.py) and against the reference's own scalar
+primitives where they were compiled (oracle/_ref)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
+
+
+def cases(name):
+    return [pytest.param(c, id="%s:%d" % (os.path.basename(name), c["line"])) for c in GOLD[name]]
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/scan0.fut"))
+def test_scan0_last_element_of_prefix_sum_of_iota(c):
+    n = c["input"][0]
+    xs = np.arange(n, dtype=np.int64).astype(np.int32)
+    out = oracle.scan_i32(xs)
+    assert int(out[n - 1]) == c["output"][0]
+    # every element, against numpy's wrapping cumsum
+    assert np.array_equal(out, np.cumsum(xs.astype(np.int64)).astype(np.int32))
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/reduce0.fut"))
+def test_reduce0_sum_of_range_wraps(c):
+    n = c["input"][0]
+    xs = np.arange(n, dtype=np.int32)
+    for threads in (1, 3, 0):
+        assert oracle.reduce_i32(xs, threads) == c["output"][0]
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/filter1.fut"))
+def test_filter1_order_and_empty(c):
+    # the reference program filters with (0 <); the oracle's predicate is fixed to
+    # (k & 7) < 3, so the vector is replayed through a monotone re-encoding:
+    # positive -> a key that satisfies the predicate, others -> one that does not.
+    xs = np.array(c["input"][0], dtype=np.int64)
+    keys = np.where(xs > 0, xs * 8 + 1, np.abs(xs) * 8 + 5).astype(np.uint32)
+    got = oracle.filter_u32(keys)
+    want = np.array([v * 8 + 1 for v in c["output"][0]], dtype=np.uint32)
+    assert np.array_equal(got, want)
+
+
+def test_partition1_stable_two_groups():
+    # tests/soacs/partition1.fut:3-11 uses partition2 (three groups); its first group and
+    # the order-preservation of the rest pin the two-way partition contract.
+    c = GOLD["tests/soacs/partition1.fut"][0]
+    xs = np.array(c["input"][0], dtype=np.int64)
+    keys = np.where(xs % 2 == 0, xs * 8 + 0, xs * 8 + 7).astype(np.uint32)
+    sel, rej = oracle.partition_u32(keys)
+    assert [int(k) // 8 for k in sel] == c["output"][0]
+    rest = [v for v in c["input"][0] if v % 2 != 0]      # [3,9] and [1,5,7] interleaved in input order
+    assert [int(k) // 8 for k in rej] == rest
+    assert sorted(rest) == sorted(c["output"][1] + c["output"][2])
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/segreduce-iota.fut"))
+def test_segreduce_iota_rows_incl_empty(c):
+    n, m = c["input"]
+    xss = np.repeat(np.arange(n, dtype=np.float32)[:, None], m, axis=1).reshape(n, m)
+    got = oracle.rowsum_f32(xss)
+    assert np.array_equal(got, np.array(c["output"][0], dtype=np.float32))
+    # same through the offsets form
+    offs = np.arange(n + 1, dtype=np.int64) * m
+    assert np.array_equal(oracle.segreduce_f32(offs, xss.reshape(-1)), np.array(c["output"][0], dtype=np.float32))
+
+
+@pytest.mark.parametrize("c", cases("tests/segredomap/segsum-comm.fut"))
+def test_segsum_rows(c):
+    xss = np.array(c["input"][0], dtype=np.float32)
+    assert np.array_equal(oracle.rowsum_f32(xss), np.array(c["output"][0], dtype=np.float32))
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/simple.fut"))
+def test_hist_simple_add_with_out_of_range_and_empties(c):
+    dest, image = c["input"]
+    got = oracle.reduce_by_index_add_i32(dest, image, image)
+    assert np.array_equal(got, np.array(c["output"][0], dtype=np.int32))
+    # hist (+) 0 B is ws == reduce_by_index over a zero destination
+    B = len(dest)
+    h = oracle.hist_add_i32(B, np.array(image, dtype=np.int32), np.array(image, dtype=np.int32))
+    assert np.array_equal(h + np.array(dest, dtype=np.int32), np.array(c["output"][0], dtype=np.int32))
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/max.fut"))
+def test_hist_max(c):
+    B, is_, image = c["input"]
+    # reference: reduce_by_index (replicate n 0) i32.max i32.lowest; replayed through the
+    # f32 max histogram (neutral -inf) followed by max with the zero destination
+    h = oracle.hist_max_f32(B, np.array(is_, dtype=np.int32), np.array(image, dtype=np.float32))
+    assert np.array_equal(np.maximum(h, 0).astype(np.int32), np.array(c["output"][0], dtype=np.int32))
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/large.fut")[:2])
+def test_hist_large_sparse(c):
+    n, m = c["input"]
+    idx = (np.arange(m, dtype=np.int64) % n).astype(np.int32)
+    h = oracle.hist_add_i32(n, idx, np.arange(m, dtype=np.int64).astype(np.int32))
+    assert int(h.astype(np.int64).sum().astype(np.int32)) == c["output"][0]
+
+
+@pytest.mark.parametrize("c", cases("tests/reg-tiling/mmm.fut"))
+def test_mmm_small(c):
+    A, B = (np.array(v, dtype=np.float32) for v in c["input"])
+    assert np.array_equal(oracle.mm_f32(A, B), np.array(c["output"][0], dtype=np.float32))
+    # the f16 entry on the same (exactly representable) values
+    got = oracle.bmm_f16(A.astype(np.float16)[None], B.astype(np.float16)[None])[0]
+    assert np.array_equal(got, np.array(c["output"][0], dtype=np.float32))
+
+
+def test_hist_max_drops_nan_and_starts_at_minus_inf():
+    # fmax32 = fmaxf drops NaN operands (rts/c/scalar.h:932); neutral is f32.lowest = -inf
+    h = oracle.hist_max_f32(3, np.array([0, 0, 1], np.int32), np.array([np.nan, 2.0, np.nan], np.float32))
+    assert h[0] == 2.0 and h[1] == -np.inf and h[2] == -np.inf
+
+
+def test_scalar_rules_match_reference_headers():
+    R = oracle.ref_scalar()
+    if R is None:
+        pytest.skip("reference checkout not present: oracle/_ref not built")
+    L = oracle.lib()
+    rng = np.random.default_rng(0)
+    for a, b in rng.integers(0, 2**32, size=(200, 2), dtype=np.uint64):
+        assert L.orc_add32(int(a), int(b)) == R.ref_add32(int(a), int(b))
+    specials = [0.0, -0.0, 1.5, -2.25, float("inf"), float("-inf"), float("nan")]
+    for a in specials:
+        for b in specials:
+            x, y = L.orc_fmax32(a, b), R.ref_fmax32(a, b)
+            assert (np.isnan(x) and np.isnan(y)) or x == y
+    # every binary16 bit pattern widens to the same float
+    for h in range(0, 65536):
+        x, y = L.orc_half_to_float(h), R.ref_halfbits2float(h)
+        assert (np.isnan(x) and np.isnan(y)) or (x == y and np.signbit(x) == np.signbit(y)), h
+    # numpy's float16 -> float32 is the same widening (used by the data generator)
+    allh = np.arange(65536, dtype=np.uint16)
+    wide = allh.view(np.float16).astype(np.float32)
+    mine = np.array([L.orc_half_to_float(int(h)) for h in allh], dtype=np.float32)
+    ok = (wide == mine) | (np.isnan(wide) & np.isnan(mine))
+    assert ok.all()
+
+
+def test_segscan_matches_sequential_definition():
+    # lifted operator of tests/soacs/scan2.fut:7-17, folded left to right
+    rng = np.random.default_rng(1)
+    for n in (0, 1, 7, 1000, 40000):
+        xs = rng.standard_normal(n).astype(np.float32)
+        flags = (rng.random(n) < 0.05).astype(np.uint8)
+        want = np.empty(n, dtype=np.float32)
+        acc = np.float32(0)
+        for i in range(n):
+            acc = xs[i] if flags[i] else np.float32(acc + xs[i])
+            want[i] = acc
+        got = oracle.segscan_f32(flags, xs, threads=1)
+        if n <= 13107:      # single block: identical association
+            assert np.array_equal(got, want)
+        ref64 = oracle.segscan_f32_seq64(flags, xs)
+        assert np.allclose(got, ref64, rtol=1e-5, atol=1e-4)
+
+
+def test_partition_is_filter_plus_complement():
+    rng = np.random.default_rng(2)
+    ks = rng.integers(0, 2**32, size=100003, dtype=np.uint64).astype(np.uint32)
+    sel, rej = oracle.partition_u32(ks)
+    m = (ks & 7) < 3
+    assert np.array_equal(sel, ks[m]) and np.array_equal(rej, ks[~m])
+    assert np.array_equal(oracle.filter_u32(ks), ks[m])
