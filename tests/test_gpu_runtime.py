@@ -1,0 +1,99 @@
+"""GPU checks of the runtime behind the C API: array objects, indexing, raw pointers,
+error reporting, the out-of-memory path, the profiling report, pool reuse."""
+import json
+
+import numpy as np
+import pytest
+
+import futhark_b200 as fb
+
+pytestmark = pytest.mark.gpu
+
+
+def test_array_round_trip_shapes_and_index(ctx):
+    x = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    a = ctx.new("f32_3d", x)
+    assert a.shape == (2, 3, 4)
+    assert np.array_equal(a.values(), x)
+    assert a.index(1, 2, 3) == 23.0
+    with pytest.raises(fb.FutharkError) as e:
+        a.index(2, 0, 0)
+    assert "out of bounds" in e.value.message.lower()
+    a.free()
+    b = ctx.new("bool_1d", np.array([True, False, True]))
+    assert b.values().tolist() == [True, False, True]
+    b.free()
+
+
+def test_raw_arrays_borrow_memory(ctx):
+    x = np.arange(10, dtype=np.int64)
+    a = ctx.new("i64_1d", x)
+    r = ctx.new_raw("i64_1d", a.raw + 16, 8)
+    assert np.array_equal(r.values(), x[2:])
+    r.free()                       # must not free the borrowed memory
+    assert np.array_equal(a.values(), x)
+    a.free()
+
+
+def test_error_string_is_cleared_after_read(ctx):
+    f = ctx.new("bool_1d", np.zeros(2, dtype=bool))
+    x = ctx.new("f32_1d", np.zeros(3, dtype=np.float32))
+    rc_err = None
+    try:
+        ctx.entry_segscan_f32(f, x)
+    except fb.FutharkError as e:
+        rc_err = e
+    assert rc_err is not None and rc_err.code != 0
+    assert ctx.get_error() is None
+    f.free(); x.free()
+    ctx.sync()
+
+
+def test_out_of_memory_is_reported_not_fatal(ctx):
+    lib = ctx.lib
+    p = lib.futhark_new_raw_i32_1d(ctx.ptr, 0, 1 << 46)      # a fake 256 TiB input: never touched
+    big = fb.Array(ctx, "i32_1d", p)
+    with pytest.raises(fb.FutharkError) as e:
+        ctx.entry_scan_i32(big)                               # result allocation must fail cleanly
+    assert e.value.code == fb.FUTHARK_OUT_OF_MEMORY
+    big.free()
+    # the context is still usable
+    assert fb.reduce_i32(ctx, np.arange(10, dtype=np.int32)) == 45
+
+
+def test_profiling_report_is_json_with_events():
+    with fb.Context(profiling=True) as c:
+        fb.scan_i32(c, np.arange(100000, dtype=np.int32))
+        c.pause_profiling()
+        fb.reduce_i32(c, np.arange(10, dtype=np.int32))
+        c.unpause_profiling()
+        fb.rowsum_f32(c, np.ones((8, 64), dtype=np.float32))
+        rep = json.loads(c.report())
+        names = [e["name"] for e in rep["events"]]
+        assert names == ["scan_i32.segscan", "rowsum_f32.segred"]
+        assert all(e["duration"] > 0 for e in rep["events"])
+        assert rep["memory"]["device"] > 0
+        assert json.loads(c.report())["events"] == []          # events are consumed
+
+
+def test_pool_reuses_blocks_and_clear_caches(ctx):
+    xs = np.arange(1 << 16, dtype=np.int32)
+    a = ctx.new("i32_1d", xs)
+    p1 = a.raw
+    a.free()
+    b = ctx.new("i32_1d", xs)
+    assert b.raw == p1                                         # served from the free list
+    b.free()
+    ctx.clear_caches()
+    assert fb.reduce_i32(ctx, xs) == int(xs.astype(np.int64).sum().astype(np.int32))
+
+
+def test_two_contexts_coexist():
+    with fb.Context() as c1, fb.Context(device="#0") as c2:
+        x = np.arange(1000, dtype=np.int32)
+        assert fb.reduce_i32(c1, x) == fb.reduce_i32(c2, x) == 499500
+
+
+def test_unknown_device_is_an_error():
+    with pytest.raises(fb.FutharkError):
+        fb.Context(device="no such device name")
