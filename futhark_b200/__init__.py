@@ -84,6 +84,11 @@ def load():
     L.futhark_context_report.argtypes = [vp]
     L.futhark_context_report.restype = vp
     L.futhark_context_clear_caches.argtypes = [vp]
+    L.futhark_b200_context_get_stream.restype = vp
+    L.futhark_b200_context_get_stream.argtypes = [vp]
+    L.futhark_b200_context_get_device.argtypes = [vp]
+    L.futhark_b200_context_get_launch_count.restype = i64
+    L.futhark_b200_context_get_launch_count.argtypes = [vp]
     L.futhark_context_pause_profiling.argtypes = [vp]
     L.futhark_context_unpause_profiling.argtypes = [vp]
     for name, (_, rank, ct) in ARRAY_TYPES.items():
@@ -265,6 +270,19 @@ class Context:
 
     def clear_caches(self):
         self._check(self.lib.futhark_context_clear_caches(self.ptr))
+
+    @property
+    def stream(self):
+        """The context's CUDA stream handle (futhark_b200_context_get_stream)."""
+        return int(self.lib.futhark_b200_context_get_stream(self.ptr) or 0)
+
+    @property
+    def device(self):
+        return int(self.lib.futhark_b200_context_get_device(self.ptr))
+
+    @property
+    def launch_count(self):
+        return int(self.lib.futhark_b200_context_get_launch_count(self.ptr))
 
     def pause_profiling(self):
         self.lib.futhark_context_pause_profiling(self.ptr)

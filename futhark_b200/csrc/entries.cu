@@ -52,7 +52,7 @@ int futhark_entry_scan_i32(struct futhark_context *ctx, struct futhark_i32_1d **
     rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(n));
     if (rc == 0) {
       LaunchScope ls(ctx, "scan_i32.segscan", PROV("scan (+) 0 xs"), "{" + kv("n", n) + "}");
-      rc = fb_cuda_check(ctx, fb::launch_scan_i32(dptr<int32_t>(in0->mem), dptr<int32_t>(out->mem), n, 0, ctx->lookback_scratch,
+      rc = fb_cuda_check(ctx, fb::launch_scan_i32(dptr<int32_t>(in0->mem), dptr<int32_t>(out->mem), n, 0, nullptr, 0, ctx->lookback_scratch,
                                                   fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "scan_i32");
       ctx->failure_is_an_option = true;
     }
@@ -155,6 +155,7 @@ static int hist_common(futhark_context *ctx, int op, void **out_arr, int64_t B, 
   if (out == nullptr) return rc;
   if (B > 0) {
     LaunchScope ls(ctx, name, PROV("hist op ne B (map i64.i32 is) ws"), "{" + kv("n", n) + "," + kv("bins", B) + "}");
+    ctx->launch_count += (op == 1 ? 2 : 1);   // the fill (and, for max, the key decode) besides the histogram kernel
     rc = fb_cuda_check(ctx, fb::launch_hist(op, B, dptr<int32_t>(is->mem), dptr<void>(ws), n, dptr<void>(out->mem), ctx->num_sms, ctx->stream), name);
     if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
   }
@@ -272,6 +273,61 @@ int futhark_entry_bmm_f16(struct futhark_context *ctx, struct futhark_f32_3d **o
   if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
   *out0 = out;
   return FUTHARK_SUCCESS;
+}
+
+// ---- shard-local pieces for arrays split across several contexts (extensions) -------------------
+
+int futhark_b200_reduce_i32_to_device(struct futhark_context *ctx, CUdeviceptr dst, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  LaunchScope ls(ctx, "reduce_i32.segred_nonseg", PROV("reduce (+) 0 xs"), "{" + kv("n", in0->shape[0]) + "}");
+  return fb_cuda_check(ctx, fb::launch_reduce_i32(dptr<int32_t>(in0->mem), in0->shape[0], reinterpret_cast<int32_t *>((uintptr_t)dst),
+                                                  ctx->reduce_scratch, ctx->num_sms, ctx->stream), "reduce_i32");
+}
+
+int futhark_b200_entry_scan_i32_carried(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_1d *in0,
+                                        CUdeviceptr carries, int num_carries) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  int rc;
+  futhark_i32_1d *out = make_1d<futhark_i32_1d>(ctx, n, 4, "scan_i32.out", &rc);
+  if (out == nullptr) return rc;
+  if (n > 0) {
+    rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(n));
+    if (rc == 0) {
+      LaunchScope ls(ctx, "scan_i32.segscan", PROV("scan (+) carry xs"), "{" + kv("n", n) + "}");
+      rc = fb_cuda_check(ctx, fb::launch_scan_i32(dptr<int32_t>(in0->mem), dptr<int32_t>(out->mem), n, 0,
+                                                  reinterpret_cast<const int32_t *>((uintptr_t)carries), num_carries,
+                                                  ctx->lookback_scratch, fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "scan_i32");
+      ctx->failure_is_an_option = true;
+    }
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_b200_entry_segscan_f32_shard(struct futhark_context *ctx, struct futhark_f32_1d **out0, CUdeviceptr summary_dst,
+                                         const struct futhark_bool_1d *in0, const struct futhark_f32_1d *in1) {
+  int rc = futhark_entry_segscan_f32(ctx, out0, in0, in1);
+  if (rc != 0) return rc;
+  CtxGuard g(ctx);
+  ctx->launch_count++;
+  return fb_cuda_check(ctx, fb::launch_segscan_summary(ctx->lookback_scratch, in1->shape[0], reinterpret_cast<uint32_t *>((uintptr_t)summary_dst),
+                                                       ctx->stream), "segscan summary");
+}
+
+int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct futhark_f32_1d *out, const struct futhark_bool_1d *in0,
+                                           CUdeviceptr summaries, int rank) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  if (out->shape[0] != in0->shape[0]) return bad_sizes(ctx);
+  if (rank > 0 && out->shape[0] > 0) ctx->launch_count += 2;
+  return fb_cuda_check(ctx, fb::launch_segscan_apply_carry(dptr<float>(out->mem), dptr<uint8_t>(in0->mem), out->shape[0],
+                                                           reinterpret_cast<const uint32_t *>((uintptr_t)summaries), rank,
+                                                           reinterpret_cast<unsigned long long *>(ctx->d_scalar + 4), ctx->num_sms, ctx->stream),
+                       "segscan carry");
 }
 
 }  // extern "C"

@@ -147,7 +147,8 @@ __device__ __forceinline__ bool aligned16(const void *p) { return (((uintptr_t)p
 // ---- inclusive scan (+) over i32 -------------------------------------------------------
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_i32_kernel(const int32_t *__restrict__ in, int32_t *__restrict__ out, int64_t n, uint32_t num_tiles,
-                uint32_t *ticket, uint64_t *status, uint32_t epoch, int *failure, uint32_t carry_in) {
+                uint32_t *ticket, uint64_t *status, uint32_t epoch, int *failure, uint32_t carry_in,
+                const uint32_t *__restrict__ carry_vals, int carry_n) {
   __shared__ __align__(128) uint32_t s_tile[SCAN_TILE];
   __shared__ __align__(8) uint64_t s_bar;
   __shared__ uint32_t s_warp[SCAN_WARPS];
@@ -204,6 +205,9 @@ scan_i32_kernel(const int32_t *__restrict__ in, int32_t *__restrict__ out, int64
 
   if (warp == 0) {
     uint32_t ev, ef;
+    // carry of a sharded scan: the totals of the shards before this one, summed here
+    if (carry_vals != nullptr && tile < 32u)
+      for (int q = 0; q < carry_n; q++) carry_in += carry_vals[q];
     bool ok = tile_lookback<OpAddU32>(status, tile, epoch, tile_agg, 0u, carry_in, failure, ev, ef);
     if (lane == 0) { s_prefix = ev; s_ok = ok ? 1u : 0u; }
   }
@@ -468,14 +472,16 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
   *status = reinterpret_cast<uint64_t *>(reinterpret_cast<char *>(scratch) + 256);
 }
 
-cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in, void *scratch,
+cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in,
+                            const int32_t *carry_vals, int carry_n, void *scratch,
                             uint32_t epoch, int *failure, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
   uint32_t *ticket; uint64_t *status;
   split_scratch(scratch, &ticket, &status);
   const uint32_t nt = tiles_for(n);
   scan_i32_kernel<<<nt, SCAN_THREADS, 0, stream>>>(in, out, n, nt, ticket, status, epoch, failure,
-                                                   (uint32_t)carry_in);
+                                                   (uint32_t)carry_in, reinterpret_cast<const uint32_t *>(carry_vals),
+                                                   carry_n);
   return cudaGetLastError();
 }
 
@@ -487,6 +493,64 @@ cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out
   const uint32_t nt = tiles_for(n);
   segscan_f32_kernel<<<nt, SCAN_THREADS, 0, stream>>>(flags, in, out, n, nt, ticket, status, epoch, failure,
                                                       carry_in);
+  return cudaGetLastError();
+}
+
+// ---- pieces of a segmented scan whose array is split across several devices ---------------
+// Summary of a shard = inclusive prefix of its last tile: (value, "a segment starts somewhere
+// in the shard").  Written as two 32-bit words {f32 bits, flag}.
+__global__ void segscan_summary_kernel(const uint64_t *status, uint32_t last_tile, uint32_t *dst) {
+  const uint64_t w = status[last_tile];
+  dst[0] = status_value(w);
+  dst[1] = status_flag(w);
+}
+
+// Position of the first segment start (n if none): CTAs walk 16 KiB chunks in ascending
+// order and stop as soon as a start before their chunk is known.
+__global__ void __launch_bounds__(256)
+first_flag_kernel(const uint8_t *__restrict__ flags, int64_t n, unsigned long long *first) {
+  constexpr int64_t CHUNK = 16384;
+  for (int64_t c = blockIdx.x; c * CHUNK < n; c += gridDim.x) {
+    const int64_t lo = c * CHUNK;
+    if ((int64_t)*reinterpret_cast<volatile unsigned long long *>(first) < lo) return;
+    const int64_t hi = lo + CHUNK < n ? lo + CHUNK : n;
+    int64_t best = n;
+    for (int64_t i = lo + threadIdx.x; i < hi; i += 256)
+      if (flags[i]) { best = i; break; }
+    if (best < n) atomicMin(first, (unsigned long long)best);
+  }
+}
+
+// out[i] += carry for i before the first segment start, where carry is the fold of the
+// summaries of the shards before this one under the lifted operator.
+__global__ void __launch_bounds__(256)
+apply_carry_kernel(float *__restrict__ out, const unsigned long long *first, const uint32_t *summaries, int rank) {
+  uint32_t cv = 0, cf = 0;
+  for (int q = 0; q < rank; q++) OpSegAddF32::combine(cv, cf, summaries[2 * q], summaries[2 * q + 1], cv, cf);
+  const float carry = __uint_as_float(cv);
+  const int64_t end = (int64_t)*first;
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < end; i += stride) out[i] = carry + out[i];
+}
+
+cudaError_t launch_segscan_summary(void *scratch, int64_t n, uint32_t *dst, cudaStream_t stream) {
+  if (n <= 0) return cudaMemsetAsync(dst, 0, 8, stream);   // (0, no flag): the identity
+  uint32_t *ticket; uint64_t *status;
+  split_scratch(scratch, &ticket, &status);
+  segscan_summary_kernel<<<1, 1, 0, stream>>>(status, tiles_for(n) - 1, dst);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
+                                       int rank, unsigned long long *d_first, int num_sms, cudaStream_t stream) {
+  if (n <= 0 || rank <= 0) return cudaSuccess;
+  const unsigned long long init = (unsigned long long)n;
+  cudaError_t err = cudaMemcpyAsync(d_first, &init, sizeof(init), cudaMemcpyHostToDevice, stream);
+  if (err != cudaSuccess) return err;
+  int64_t chunks = (n + 16383) / 16384;
+  int grid = (int)(chunks < (int64_t)num_sms * 4 ? chunks : (int64_t)num_sms * 4);
+  first_flag_kernel<<<grid, 256, 0, stream>>>(flags, n, d_first);
+  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, d_first, summaries, rank);
   return cudaGetLastError();
 }
 

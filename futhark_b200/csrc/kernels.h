@@ -11,8 +11,16 @@ namespace fb {
 // `epoch` must differ from the epochs of earlier launches that used the same scratch
 // (1 .. 2^29-1); `failure` is the context's device failure word.
 size_t lookback_scratch_bytes(int64_t n);
-cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in, void *scratch,
+// The scan starts from carry_in plus, when carry_vals is not NULL, the sum of the carry_n
+// device values it points to.
+cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in,
+                            const int32_t *carry_vals, int carry_n, void *scratch,
                             uint32_t epoch, int *failure, cudaStream_t stream);
+// After launch_segscan_f32 on the same scratch: writes the shard summary {f32 bits, flag}.
+cudaError_t launch_segscan_summary(void *scratch, int64_t n, uint32_t *dst, cudaStream_t stream);
+// Adds the fold of summaries[0..rank) to out[0 .. first segment start).
+cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
+                                       int rank, unsigned long long *d_first, int num_sms, cudaStream_t stream);
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
                                void *scratch, uint32_t epoch, int *failure, cudaStream_t stream);
 cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out_true, uint32_t *out_false,

@@ -74,6 +74,7 @@ CtxGuard::~CtxGuard() {
 
 LaunchScope::LaunchScope(futhark_context *c, const char *name, const char *provenance, const std::string &details)
     : ctx(c) {
+  ctx->launch_count++;
   if (ctx->logging) fprintf(ctx->log, "Event: %s\n  at: %s\n  %s\n", name, provenance, details.c_str());
   if (!ctx->profiling || ctx->profiling_paused) return;
   rec.name = name;
@@ -391,6 +392,10 @@ int futhark_context_sync(struct futhark_context *ctx) {
   }
   return FUTHARK_SUCCESS;
 }
+
+void *futhark_b200_context_get_stream(struct futhark_context *ctx) { return (void *)ctx->stream; }
+int futhark_b200_context_get_device(struct futhark_context *ctx) { return ctx->device; }
+int64_t futhark_b200_context_get_launch_count(struct futhark_context *ctx) { return ctx->launch_count; }
 
 char *futhark_context_get_error(struct futhark_context *ctx) {
   std::lock_guard<std::mutex> g(ctx->error_lock);

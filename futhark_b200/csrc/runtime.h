@@ -71,7 +71,6 @@ struct futhark_context {
   // released and the allocation retried)
   std::multimap<size_t, void *> free_blocks;
   int64_t cur_mem = 0, peak_mem = 0;
-  int64_t fail_alloc_after = -1;   // test hook: >= 0 makes the n-th next driver allocation fail
 
   // device words shared by the kernels
   int *d_failure = nullptr;        // 0 = ok, else fb::FailureCode
@@ -82,6 +81,7 @@ struct futhark_context {
   int64_t *d_scalar = nullptr;     // device staging for scalar results (8 x 8 bytes)
   int64_t *h_scalar = nullptr;     // pinned host mirror
   uint32_t epoch = 0;
+  int64_t launch_count = 0;       // kernels launched so far
 
   std::vector<LaunchRecord> events;
 };

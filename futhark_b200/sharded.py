@@ -1,0 +1,185 @@
+"""One logical array split into contiguous shards over several GPUs, one process and one
+futhark context per GPU (`torch.distributed` supplies the process group and the
+collectives; NCCL over NVLink on GPUs, gloo in the CPU tests of this layer).
+
+The reference is single-device; this layer is new.  Per operation:
+
+  reduce          local reduce -> all_reduce(SUM) of one i32
+  scan            local reduce -> all_gather of the shard totals -> local scan started from
+                  the sum of the totals of the earlier shards (12 B/element instead of the
+                  16 B/element of scan + carry-add)
+  segmented scan  local scan -> all_gather of one (value, has-segment-start) summary per
+                  shard -> the carry is added only to the elements before the shard's first
+                  segment start
+  segmented / row reduce   sharded by whole segments / rows: no exchange
+  histogram       local histogram -> all_reduce(SUM | MAX) over the B bins
+  filter / partition   local compaction -> all_gather of the counts -> global offsets; the
+                  result stays sharded (shard r holds out[offset_r : offset_r + count_r])
+  contraction     batch-sharded: no exchange
+
+`Group` takes a *local executor*: `LibLocal` drives libfuthark_b200.so; the CPU tests pass
+their own executor with the same methods, so the exchange logic is tested without a GPU.
+"""
+import ctypes
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n, world, rank):
+    """Contiguous split of n items: the first n % world shards get one extra."""
+    base, rem = divmod(n, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def split_segments(offsets, world, rank):
+    """Whole segments per shard, cut nearest to an even split of the ELEMENTS: returns the
+    half-open segment range [s_lo, s_hi) of this rank."""
+    nseg = len(offsets) - 1
+    total = int(offsets[-1]) if nseg >= 0 and len(offsets) else 0
+    cuts = [0]
+    for r in range(1, world):
+        cuts.append(int(np.searchsorted(offsets, total * r / world, side="left")))
+    cuts.append(nseg)
+    cuts = np.maximum.accumulate(np.minimum(cuts, nseg))
+    return int(cuts[rank]), int(cuts[rank + 1])
+
+
+def fold_summaries(summaries, rank):
+    """Carry into shard `rank`: the fold of the (value, flag) summaries of shards 0..rank-1
+    under (f1,v1) (+) (f2,v2) = (f1|f2, f2 ? v2 : v1+v2), in f32."""
+    v, f = np.float32(0), 0
+    for q in range(rank):
+        qv, qf = np.float32(summaries[q][0]), int(summaries[q][1])
+        v = qv if qf else np.float32(v + qv)
+        f |= qf
+    return v, f
+
+
+class LibLocal:
+    """Local executor on libfuthark_b200.so.  Exchange buffers are CUDA tensors; collectives
+    run on the context's own stream, so they are ordered with the kernels without host syncs."""
+
+    def __init__(self, ctx, stream):
+        self.ctx, self.stream = ctx, stream
+        self.device = torch.device("cuda", ctx.device)
+        L = ctx.lib
+        vp, pvp = ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)
+        L.futhark_b200_reduce_i32_to_device.argtypes = [vp, ctypes.c_uint64, vp]
+        L.futhark_b200_entry_scan_i32_carried.argtypes = [vp, pvp, vp, ctypes.c_uint64, ctypes.c_int]
+        L.futhark_b200_entry_segscan_f32_shard.argtypes = [vp, pvp, ctypes.c_uint64, vp, vp]
+        L.futhark_b200_segscan_f32_apply_carries.argtypes = [vp, vp, vp, ctypes.c_uint64, ctypes.c_int]
+
+    def empty(self, n, dtype):
+        return torch.empty(n, dtype=dtype, device=self.device)
+
+    def collective_stream(self):
+        return torch.cuda.stream(self.stream)
+
+    def as_tensor(self, arr, dtype):
+        """A torch view of a library array (no copy)."""
+        return torch.as_tensor(arr, device=self.device).view(dtype)
+
+    def reduce_i32_into(self, xs, slot):
+        self.ctx._check(self.ctx.lib.futhark_b200_reduce_i32_to_device(self.ctx.ptr, slot.data_ptr(), xs.ptr))
+
+    def scan_i32_carried(self, xs, totals, rank):
+        from . import Array
+        out = ctypes.c_void_p()
+        self.ctx._check(self.ctx.lib.futhark_b200_entry_scan_i32_carried(self.ctx.ptr, ctypes.byref(out), xs.ptr, totals.data_ptr(), rank))
+        return Array(self.ctx, "i32_1d", out.value)
+
+    def segscan_shard(self, flags, xs, slot):
+        from . import Array
+        out = ctypes.c_void_p()
+        self.ctx._check(self.ctx.lib.futhark_b200_entry_segscan_f32_shard(self.ctx.ptr, ctypes.byref(out), slot.data_ptr(), flags.ptr, xs.ptr))
+        return Array(self.ctx, "f32_1d", out.value)
+
+    def segscan_apply(self, out, flags, summaries, rank):
+        self.ctx._check(self.ctx.lib.futhark_b200_segscan_f32_apply_carries(self.ctx.ptr, out.ptr, flags.ptr, summaries.data_ptr(), rank))
+
+    def hist(self, op, B, bins, ws):
+        return self.ctx.entry_hist_add_i32(B, bins, ws) if op == "add" else self.ctx.entry_hist_max_f32(B, bins, ws)
+
+    def hist_tensor(self, out, op):
+        return self.as_tensor(out, torch.int32 if op == "add" else torch.float32)
+
+    def filter(self, ks):
+        out = self.ctx.entry_filter_u32(ks)
+        return out, out.shape[0]
+
+    def partition(self, ks):
+        pair = self.ctx.entry_partition_u32(ks)
+        s, r = pair.project(0), pair.project(1)
+        pair.free()
+        return s, r, s.shape[0], r.shape[0]
+
+
+class Group:
+    """The sharded operations of one rank."""
+
+    def __init__(self, ctx=None, stream=None, local=None, pg=None):
+        self.local = local if local is not None else LibLocal(ctx, stream)
+        self.pg = pg
+        self.rank = dist.get_rank(pg)
+        self.world = dist.get_world_size(pg)
+
+    # -- reduce (+) i32: one value per rank, summed (wrapping) by the collective
+    def reduce_i32(self, xs):
+        buf = self.local.empty(1, torch.int32)
+        self.local.reduce_i32_into(xs, buf)
+        with self.local.collective_stream():
+            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.pg)
+        return int(buf.item())
+
+    # -- scan (+) i32: totals first, then one seeded pass
+    def scan_i32(self, xs):
+        totals = self.local.empty(self.world, torch.int32)
+        self.local.reduce_i32_into(xs, totals[self.rank:self.rank + 1])
+        with self.local.collective_stream():
+            dist.all_gather_into_tensor(totals, totals[self.rank:self.rank + 1].clone(), group=self.pg)
+        return self.local.scan_i32_carried(xs, totals, self.rank)
+
+    # -- flagged segmented scan (+) f32
+    def segscan_f32(self, flags, xs):
+        summaries = self.local.empty(2 * self.world, torch.int32)
+        mine = summaries[2 * self.rank:2 * self.rank + 2]
+        out = self.local.segscan_shard(flags, xs, mine)
+        with self.local.collective_stream():
+            dist.all_gather_into_tensor(summaries, mine.clone(), group=self.pg)
+        self.local.segscan_apply(out, flags, summaries, self.rank)
+        return out
+
+    # -- histograms: every rank ends with the full result
+    def hist(self, op, B, bins, ws):
+        out = self.local.hist(op, B, bins, ws)
+        if B > 0:
+            t = self.local.hist_tensor(out, op)
+            with self.local.collective_stream():
+                dist.all_reduce(t, op=dist.ReduceOp.SUM if op == "add" else dist.ReduceOp.MAX, group=self.pg)
+        return out
+
+    # -- compaction: local result + where it sits in the logical concatenation
+    def filter_u32(self, ks):
+        out, count = self.local.filter(ks)
+        counts = self._gather_counts([count])
+        offset = int(counts[:self.rank, 0].sum())
+        return out, offset, int(counts[:, 0].sum())
+
+    def partition_u32(self, ks):
+        sel, rej, ns, nr = self.local.partition(ks)
+        counts = self._gather_counts([ns, nr])
+        total_sel = int(counts[:, 0].sum())
+        sel_off = int(counts[:self.rank, 0].sum())
+        rej_off = total_sel + int(counts[:self.rank, 1].sum())
+        return sel, rej, sel_off, rej_off, total_sel
+
+    def _gather_counts(self, vals):
+        mine = self.local.empty(len(vals), torch.int64)
+        mine.copy_(torch.tensor(vals, dtype=torch.int64))
+        allc = self.local.empty(len(vals) * self.world, torch.int64)
+        with self.local.collective_stream():
+            dist.all_gather_into_tensor(allc, mine, group=self.pg)
+        return allc.cpu().numpy().reshape(self.world, len(vals))

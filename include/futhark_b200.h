@@ -229,6 +229,45 @@ int futhark_entry_partition_u32(struct futhark_context *ctx,
 int futhark_entry_bmm_f16(struct futhark_context *ctx, struct futhark_f32_3d **out0,
                           const struct futhark_f16_3d *in0, const struct futhark_f16_3d *in1);
 
+/* ---- extensions (prefix futhark_b200_): not part of the reference's generated API ----
+ * The reference keeps its one CUDA stream private (rts/c/backends/cuda.h:219); a host
+ * program that shares a process with other CUDA code needs it to order its own work
+ * (events, copies, collectives) against the entry points. */
+
+/* The context's stream, as a cudaStream_t / CUstream handle.  Every entry point, copy and
+ * kernel of the context is enqueued on it. */
+void *futhark_b200_context_get_stream(struct futhark_context *ctx);
+/* Ordinal of the CUDA device the context runs on. */
+int futhark_b200_context_get_device(struct futhark_context *ctx);
+/* Number of kernel launches issued by the context so far. */
+int64_t futhark_b200_context_get_launch_count(struct futhark_context *ctx);
+
+/* Shard-local pieces, for one logical array split into contiguous shards over several
+ * contexts (one per GPU).  The reference is single-device (rts/c/backends/cuda.h:219) and has
+ * no counterpart.  All are asynchronous; device pointers passed in must belong to the
+ * context's device and be ordered on the context's stream.
+ *
+ *  reduce_i32_to_device    writes reduce (+) 0 of the shard to *dst (one i32 on the device)
+ *  entry_scan_i32_carried  scan (+) of the shard started from the sum of the num_carries i32
+ *                          values at `carries` (the totals of the shards before this one)
+ *  entry_segscan_f32_shard the segmented scan of the shard alone, plus its 8-byte summary at
+ *                          summary_dst: {f32 bits of the last element, 1 if any segment starts
+ *                          in the shard else 0}
+ *  segscan_f32_apply_carries  given the summaries of all shards (2 x u32 each, in rank order),
+ *                          adds the carry of shards 0..rank-1 to the elements of `out` that
+ *                          precede the shard's first segment start */
+int futhark_b200_reduce_i32_to_device(struct futhark_context *ctx, CUdeviceptr dst,
+                                      const struct futhark_i32_1d *in0);
+int futhark_b200_entry_scan_i32_carried(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                                        const struct futhark_i32_1d *in0, CUdeviceptr carries,
+                                        int num_carries);
+int futhark_b200_entry_segscan_f32_shard(struct futhark_context *ctx, struct futhark_f32_1d **out0,
+                                         CUdeviceptr summary_dst, const struct futhark_bool_1d *in0,
+                                         const struct futhark_f32_1d *in1);
+int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct futhark_f32_1d *out,
+                                           const struct futhark_bool_1d *in0, CUdeviceptr summaries,
+                                           int rank);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif
