@@ -20,6 +20,11 @@
 //      or are compacted in shared memory and written as contiguous runs (compaction).
 // A tile that is ragged (the last one) or whose global addresses are not 16-byte
 // aligned uses plain guarded loads and stores instead of the bulk copies.
+#include <stdio.h>
+
+#include <mutex>
+
+#include "../../include/futhark_b200.h"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -570,4 +575,80 @@ cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out
   return cudaGetLastError();
 }
 
+// ---- scan (+) i32 without any allocation ---------------------------------------------------------
+// Some hosts hand this library a GPU whose memory is already fully parcelled out by their
+// own arena allocator, or run it inside a region of their program where a call that may
+// synchronise the whole device or fail for lack of memory (cudaMalloc does both) is not
+// acceptable, for instance a latency-bound service loop after start-up.  For them the tile
+// ticket, the tile status words and the failure word of the look-back scan live in the
+// fixed array below instead of in pooled memory.  The array is part of the loaded library
+// image: every GPU that loads the library holds these ~103 KiB until the process exits.
+constexpr int64_t NOALLOC_MAX_N = (int64_t)1 << 26;
+constexpr uint32_t NOALLOC_MAX_TILES = (uint32_t)((NOALLOC_MAX_N + SCAN_TILE - 1) / SCAN_TILE);
+constexpr size_t NOALLOC_HEAD = 512;     // [0,4) ticket, [256,260) failure word
+constexpr size_t NOALLOC_BYTES = NOALLOC_HEAD + (size_t)NOALLOC_MAX_TILES * sizeof(uint64_t);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+// In host code `g_noalloc_scratch` names a host-side shadow of the array, not device
+// memory; the device address is asked for once per device, with that device current.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static std::mutex g_noalloc_lock;
+static unsigned char *g_noalloc_ptr[NOALLOC_MAX_DEVICES];
+static uint32_t g_noalloc_epoch[NOALLOC_MAX_DEVICES];
+
+}  // namespace fb
+
+extern "C" int futhark_b200_scan_i32_noalloc(const int32_t *in, int32_t *out, int64_t n, void *stream,
+                                             int32_t *status_dev, char *errbuf, size_t errbuf_len) {
+  using namespace fb;
+  auto fail = [&](int code, const char *msg, const char *detail) {
+    if (errbuf != nullptr && errbuf_len > 0) snprintf(errbuf, errbuf_len, "%s%s%s", msg, detail ? ": " : "", detail ? detail : "");
+    return code;
+  };
+  if (n < 0) return fail(1, "futhark_b200_scan_i32_noalloc: negative length", nullptr);
+  if (n > NOALLOC_MAX_N) {
+    char d[96];
+    snprintf(d, sizeof(d), "%lld elements requested, at most %lld fit the fixed scratch array", (long long)n, (long long)NOALLOC_MAX_N);
+    return fail(1, "futhark_b200_scan_i32_noalloc: input too long", d);
+  }
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: cudaGetDevice", cudaGetErrorString(err));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fail(1, "futhark_b200_scan_i32_noalloc: device ordinal out of range", nullptr);
+  unsigned char *base;
+  uint32_t epoch;
+  {
+    std::lock_guard<std::mutex> g(g_noalloc_lock);
+    if (g_noalloc_ptr[dev] == nullptr) {           // first call on this device: set-up
+      void *p = nullptr;
+      err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: cudaGetSymbolAddress", cudaGetErrorString(err));
+      g_noalloc_ptr[dev] = static_cast<unsigned char *>(p);
+    }
+    base = g_noalloc_ptr[dev];
+    g_noalloc_epoch[dev] = (g_noalloc_epoch[dev] % ((1u << 29) - 1)) + 1;
+    epoch = g_noalloc_epoch[dev];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps what the previous call left: the ticket and the failure word must start
+  // at zero (an aborted call may have left either set); status words need no clearing, the
+  // epoch tells this call's words from older ones.
+  err = cudaMemsetAsync(base, 0, NOALLOC_HEAD, st);
+  if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: cudaMemsetAsync", cudaGetErrorString(err));
+  int *failure = reinterpret_cast<int *>(base + 256);
+  if (n > 0) {
+    const uint32_t nt = (uint32_t)((n + SCAN_TILE - 1) / SCAN_TILE);
+    scan_i32_kernel<<<nt, SCAN_THREADS, 0, st>>>(in, out, n, nt, reinterpret_cast<uint32_t *>(base),
+                                                 reinterpret_cast<uint64_t *>(base + NOALLOC_HEAD), epoch, failure, 0u, nullptr, 0);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: kernel launch", cudaGetErrorString(err));
+  }
+  if (status_dev != nullptr) {
+    err = cudaMemcpyAsync(status_dev, failure, sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+    if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: status copy", cudaGetErrorString(err));
+  }
+  return 0;
+}
+
+namespace fb {
 }  // namespace fb

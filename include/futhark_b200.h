@@ -268,6 +268,34 @@ int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct f
                                            const struct futhark_bool_1d *in0, CUdeviceptr summaries,
                                            int rank);
 
+/* Inclusive scan (+) over n i32 values in device memory, in -> out, with no allocation of
+ * any kind.  It has no counterpart in the reference, whose entry points always allocate
+ * their results and temporaries from the context's pool (rts/c/gpu.h:240-316).
+ *
+ * Who needs it: a host that cannot let this library allocate -- because the GPU's memory is
+ * already divided up by the host's own allocator, or because the call sits in a part of the
+ * host program (a latency-bound loop after start-up, say) where a device-wide
+ * synchronisation or an out-of-memory failure from cudaMalloc cannot be tolerated.  The
+ * caller supplies `in` and `out` (device pointers, 4-byte aligned; 16-byte alignment is
+ * faster); the scan's temporaries (a tile counter and one 8-byte status word per tile of
+ * 5120 elements) live in a fixed ~103 KiB array inside the library image, which every GPU
+ * that loads the library keeps until the process exits.
+ *
+ * Limits and rules:
+ *  - n must be <= 2^26 = 67108864 (what the fixed array has room for); a longer input is
+ *    refused with a non-zero return and a message in errbuf;
+ *  - the work is enqueued on `stream` (a cudaStream_t; NULL = the default stream) of the
+ *    CURRENT device and the function returns without waiting;
+ *  - if status_dev is not NULL, one i32 is written there (device memory) after the scan:
+ *    0 = complete, otherwise a wait inside the kernel hit its limit and `out` is incomplete;
+ *  - the first call on each device looks up the array's device address; make that first
+ *    call before starting any stream capture;
+ *  - all calls share the one array: two calls whose GPU work may overlap (different
+ *    streams, different threads) race on it and give wrong results -- serialise them;
+ *  - errbuf (may be NULL) receives a NUL-terminated message when the return value is not 0. */
+int futhark_b200_scan_i32_noalloc(const int32_t *in, int32_t *out, int64_t n, void *stream,
+                                  int32_t *status_dev, char *errbuf, size_t errbuf_len);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif
