@@ -139,8 +139,107 @@ def workload_config():
             "parallelism": "contiguous shards, one carry exchange for the scan"}
 
 
+# ---- single-SOAC cases: every configuration of the baseline, inputs resident ---------------------
+
+CASES = {
+    # name: (default n, algorithmic bytes(n, extra) or flops)
+    "scan_i32": 1 << 26, "reduce_i32": 1 << 26, "segscan_f32": 1 << 27, "segreduce_f32": 1 << 27,
+    "rowsum_f32": 1 << 27, "hist_add_i32": 1 << 28, "hist_max_f32": 1 << 28, "filter_u32": 1 << 28,
+    "partition_u32": 1 << 28, "bmm_f16": 64,
+}
+
+
+def run_case(args):
+    """One entry point, inputs resident, `--reps` launches timed with CUDA event pairs on the
+    library's stream.  Prints one JSON line.  Used for the per-SOAC table and as the small
+    workload of ncu captures (`--n` shrinks it)."""
+    import futhark_b200 as fb
+    from futhark_b200 import datagen
+    names = list(CASES) if args.case == "all" else [args.case]
+    peak, peak_kind = measured_peaks()
+    ctx = fb.Context(profiling=True)
+    for name in names:
+        n = args.n if args.n else CASES[name]
+        B, dist_name = args.bins, args.dist
+        flops = None
+        if name in ("scan_i32", "reduce_i32"):
+            a = [ctx.new("i32_1d", datagen.workload_i32(n))]
+            fn = (lambda: ctx.entry_scan_i32(a[0])) if name == "scan_i32" else (lambda: ctx.entry_reduce_i32(a[0]))
+            nbytes = 8 * n if name == "scan_i32" else 4 * n
+        elif name in ("segscan_f32", "segreduce_f32"):
+            offsets, flags, xs = datagen.workload_seg_f32(n)
+            a = [ctx.new("i64_1d", offsets), ctx.new("bool_1d", flags.view(np.bool_)), ctx.new("f32_1d", xs)]
+            S = offsets.size - 1
+            if name == "segscan_f32":
+                fn, nbytes = (lambda: ctx.entry_segscan_f32(a[1], a[2])), 9 * n
+            else:
+                fn, nbytes = (lambda: ctx.entry_segreduce_f32(a[0], a[1], a[2])), 4 * n + 8 * (S + 1) + 4 * S
+        elif name == "rowsum_f32":
+            rows = n // COLS
+            a = [ctx.new("f32_2d", datagen.workload_rows_f32(rows, COLS))]
+            fn, nbytes = (lambda: ctx.entry_rowsum_f32(a[0])), 4 * rows * COLS + 4 * rows
+        elif name in ("hist_add_i32", "hist_max_f32"):
+            bins, wi, wf = datagen.workload_hist(n, B, dist_name)
+            a = [ctx.new("i32_1d", bins), ctx.new("i32_1d", wi) if name == "hist_add_i32" else ctx.new("f32_1d", wf)]
+            fn = (lambda: ctx.entry_hist_add_i32(B, a[0], a[1])) if name == "hist_add_i32" else (lambda: ctx.entry_hist_max_f32(B, a[0], a[1]))
+            nbytes = 8 * n + 4 * B
+        elif name in ("filter_u32", "partition_u32"):
+            ks = datagen.workload_keys_u32(n)
+            a = [ctx.new("u32_1d", ks)]
+            sel = int(((ks & 7) < 3).sum())
+            if name == "filter_u32":
+                fn, nbytes = (lambda: ctx.entry_filter_u32(a[0])), 4 * n + 4 * sel
+            else:
+                fn, nbytes = (lambda: ctx.entry_partition_u32(a[0])), 8 * n
+        elif name == "bmm_f16":
+            m = args.bmm_dim
+            A, Bm = datagen.workload_bmm(n, m, m, m)
+            a = [ctx.new("f16_3d", A), ctx.new("f16_3d", Bm)]
+            fn, nbytes, flops = (lambda: ctx.entry_bmm_f16(a[0], a[1])), 2 * n * m * m * 2 + 4 * n * m * m, 2 * n * m * m * m
+        ctx.sync()
+        ctx.pause_profiling()
+        for _ in range(args.warmup):
+            o = fn()
+            if hasattr(o, "free"):
+                o.free()
+        ctx.sync()
+        ctx.unpause_profiling()
+        ctx.report()
+        for _ in range(args.reps):
+            o = fn()
+            if hasattr(o, "free"):
+                o.free()
+        ctx.sync()
+        ev = json.loads(ctx.report())["events"]
+        us = [e["duration"] for e in ev]
+        avg = float(np.mean(us))
+        line = {"case": name, "n": n, "launches": len(us), "avg_us": avg, "min_us": float(np.min(us)),
+                "kernel_event": ev[0]["name"], "algorithmic_bytes": int(nbytes)}
+        if name.startswith("hist"):
+            line.update({"bins": B, "dist": dist_name})
+        if flops:
+            tf = flops / (avg * 1e-6) / 1e12
+            pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"] if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1590.0
+            line.update({"tflops": tf, "peak_tflops": pk, "frac": tf / pk, "elements_per_s": None})
+        else:
+            gbs = nbytes / (avg * 1e-6) / 1e9
+            line.update({"gbs": gbs, "peak_gbs": peak, "peak_kind": peak_kind, "frac": gbs / peak,
+                         "elements_per_s": n / (avg * 1e-6)})
+        print(json.dumps(line), flush=True)
+        for x in a:
+            x.free()
+        ctx.clear_caches()
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, help="run one entry point (or 'all') instead of the step")
+    ap.add_argument("--n", type=int, default=0)
+    ap.add_argument("--bins", type=int, default=256)
+    ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"])
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--bmm-dim", type=int, default=1024)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -155,6 +254,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.case is not None:
+        run_case(args)
         return
 
     import torch
