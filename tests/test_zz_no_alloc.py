@@ -33,7 +33,7 @@ def test_noalloc_scan_matches_pooled_entry_point_twice(ctx):
     status = ctx.new("i32_1d", np.array([-1], dtype=np.int32))
     # two calls in a row, the second shorter than the first and not a multiple of the tile,
     # so it meets status words and a rewound ticket left behind by the first
-    for n, seed in ((7 * 5120 + 123, 21), (3 * 5120 + 5, 22), (1 << 22, 23)):
+    for n, seed in ((7 * 10240 + 123, 21), (3 * 10240 + 5, 22), (1 << 22, 23)):
         xs = datagen.uniform_i32(seed, 0, n, -1000, 1000)
         a = ctx.new("i32_1d", xs)
         want_arr = ctx.entry_scan_i32(a)             # the existing, pool-allocating entry point
