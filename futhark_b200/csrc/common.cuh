@@ -118,6 +118,8 @@ __device__ __forceinline__ void bulk_s2g(void *gdst, const void *smem_src, uint3
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the bulk stores of this thread have finished READING shared memory.
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Same, but the most recently committed group may still be reading.
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
 // ---- packed tile status of the single-pass look-back scans ------------------------
 // One 64-bit word per tile: low 32 bits = value, high 32 bits = tag.  The tag is

@@ -1,40 +1,51 @@
-// Single-pass decoupled look-back kernels: inclusive scan (+) over i32, flagged
-// segmented inclusive scan (+) over f32, and filter / partition compaction of u32
-// keys.  They replace the generated `segscan` kernel of the reference
-// (src/Futhark/CodeGen/ImpGen/GPU/SegScan/SinglePass.hs:327-879) and, for
-// compaction, the scan + scatter that prelude/soacs.fut:241-286 expands into.
+// Single-pass scan kernels: inclusive scan (+) over i32, flagged segmented inclusive scan
+// (+) over f32, and filter / partition compaction of u32 keys.  They replace the generated
+// `segscan` kernel of the reference
+// (src/Futhark/CodeGen/ImpGen/GPU/SegScan/SinglePass.hs:327-879) and, for compaction, the
+// scan + scatter that prelude/soacs.fut:241-286 expands into.
 //
-// One persistent kernel, templated on what a tile computes.  Tiles hold 512 x 20 = 10240
-// elements; every CTA owns two shared-memory stages, so the bulk load of its next tile is
-// in flight while the current tile is processed:
-//   1. thread 0 draws tile numbers from a ticket counter, so tile i starts only after
-//      every tile < i has started -- the property that makes waiting on predecessors safe
-//      (the reference draws its `dyn_id` the same way, :444-461).  A CTA draws the ticket
-//      of its NEXT tile when it starts working on the current one, so the tiles being
-//      worked on across the GPU at any moment are (nearly) consecutive;
-//   2. a tile comes into shared memory with ONE bulk async copy (TMA) per array, awaited on
-//      an mbarrier; a thread then owns 20 CONSECUTIVE elements = 5 x 16 bytes, a stride of
-//      5 sixteen-byte units, which is odd, so the 128-bit shared-memory accesses are
-//      bank-conflict free without padding;
-//   3. per-thread sequential scan, warp-shuffle scan of thread totals, a second shuffle
-//      scan over the 16 warp totals;
-//   4. warp 0 publishes the tile aggregate and looks back over its predecessors, 128
-//      status words per round trip (4 per lane); it waits only for the predecessors it
-//      needs (up to the nearest one with a known prefix); every wait is bounded and polls
-//      the failure word;
-//   5. results go back into the stage and leave with one bulk async store (scan), or are
-//      compacted in the stage and written as contiguous runs (compaction).
-// A tile that is ragged (the last one) or whose global addresses are not 16-byte
-// aligned uses plain guarded loads and stores instead of the bulk copies.
+// One persistent kernel, templated on what a tile computes; one CTA per SM.  A tile holds
+// 512 x 20 = 10240 elements.  Like the reference's kernel it makes a single pass over
+// memory and hands prefixes between tiles through one status word per tile (value and
+// state in one 64-bit word, no fence in between, :628-660 there), and tiles are numbered
+// by a ticket counter so that tile i is claimed only after every tile < i (:444-461).
+// Where it differs:
 //
-// Why tiles are this large and the look-back this wide: a tile at distance d from the
-// nearest known prefix needs ceil(d / window) dependent L2 round trips, so the GPU as a
-// whole cannot retire more than about window / round-trip tiles per unit time; at HBM
-// speed that bound has to stay well above the tile rate.
+//   * A CTA keeps a ring of shared-memory stages (5, or 4 for the segmented scan) and has
+//     a tile in every one of them: being loaded (one bulk async copy, TMA, per array,
+//     awaited on an mbarrier), scanned and waiting for its prefix, or being written out
+//     (one bulk async store).  A tile that waits for its prefix costs no registers and no
+//     thread: the CTA scans its next tile meanwhile.  So the wait for predecessors, which
+//     grows with the number of tiles in flight, is covered by ~200 KB of tiles per SM.
+//
+//   * No tile looks back over its predecessors.  The first CTA to arrive does no tiles
+//     at all: its warp 0 is the PROPAGATOR, which walks the status words once, in order,
+//     256 per round trip, turning the published tile aggregates into inclusive prefixes
+//     as soon as a contiguous run of them is there.  A tile therefore waits on one word
+//     only (its predecessor's prefix).  The classic scheme -- every tile folds the
+//     aggregates of all unresolved predecessors itself -- needs a number of dependent L2
+//     round trips per tile that grows with the tiles in flight, and on 148 SMs the
+//     re-reading of the same few cache lines by hundreds of warps saturates the L2 slice
+//     that holds them.
+//
+//   * A thread owns 20 CONSECUTIVE elements = 5 x 16 bytes, an odd stride in 16-byte
+//     units, so the 128-bit shared-memory accesses are conflict-free without padding;
+//     in-thread sequential scan, shuffle scan of the thread totals, second shuffle scan
+//     over the 16 warp totals.
+//
+// Progress: the propagator exists as soon as any CTA runs.  It needs the aggregates in
+// tile order; a claimed tile always has a stage and a load in flight and is scanned
+// without waiting for anything else, and a CTA whose stages are all taken by tiles that
+// wait for prefixes holds only tiles whose predecessors are all claimed.  Every wait is
+// bounded and polls the failure word.
+//
+// A tile that is ragged (the last one) or whose global addresses are not 16-byte aligned
+// uses plain guarded loads and stores instead of the bulk copies.
 #include <stdio.h>
 #include <string.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "../../include/futhark_b200.h"
 #include "common.cuh"
@@ -46,9 +57,9 @@ constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_ITEMS = 20;
 constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;  // 10240 elements
 constexpr int SCAN_WARPS = SCAN_THREADS / 32;         // 16
-constexpr int LB_PER_LANE = 8;                        // status words per lane per round
-constexpr int LB_WINDOW = 32 * LB_PER_LANE;
-constexpr uint32_t LOOKBACK_MAX_ROUNDS = 1u << 21;
+constexpr int PROP_PER_LANE = 8;                      // status words per lane per round of the propagator
+constexpr int PROP_WINDOW = 32 * PROP_PER_LANE;
+constexpr uint32_t WAIT_MAX_ROUNDS = 1u << 22;        // idle polls before a wait gives up
 
 // ---- operators on (value bits, flag) pairs -----------------------------------------
 struct OpAddU32 {  // wrapping integer add; the flag is unused (always 0)
@@ -68,151 +79,99 @@ struct OpSegAddF32 {  // (f1,v1) (+) (f2,v2) = (f1|f2, f2 ? v2 : v1+v2) on f32 b
   static constexpr bool kHasFlag = true;
 };
 
-// ---- look-back (warp 0 only, all 32 lanes) ---------------------------------------
-// Publishes this tile's aggregate (or, when the tile's own prefix does not depend on
-// its predecessors, its inclusive prefix), then combines predecessors from the
-// nearest one backwards until one with a known inclusive prefix (or, for the
-// segmented operator, one containing a segment start) is met.  Lane l looks at the
-// predecessors j-8l .. j-8l-7 of each window.  Returns the exclusive prefix of the tile
-// in (ev, ef) -- valid in every lane -- or false after a timeout.
-template <typename Op>
-__device__ __forceinline__ bool tile_lookback(uint64_t *status, uint32_t tile, uint32_t epoch,
-                                              uint32_t agg_v, uint32_t agg_f,
-                                              uint32_t carry_v, int *failure,
-                                              uint32_t &ev, uint32_t &ef) {
-  const int lane = threadIdx.x & 31;
-  if (tile == 0) {
-    ev = carry_v; ef = 0;
-    uint32_t iv, iflag;
-    Op::combine(ev, ef, agg_v, agg_f, iv, iflag);
-    if (lane == 0) st_status(&status[0], pack_status(iv, epoch, iflag, ST_PREFIX));
-    return true;
-  }
-  // A tile containing a segment start has an inclusive prefix equal to its aggregate.
-  const bool self_contained = Op::kHasFlag && agg_f;
-  if (lane == 0)
-    st_status(&status[tile], pack_status(agg_v, epoch, agg_f, self_contained ? ST_PREFIX : ST_AGG));
-
-  uint32_t acc_v = 0, acc_f = 0;        // identity of both operators
-  bool have_acc = false;
-  int64_t j = (int64_t)tile - 1;        // nearest predecessor of the current window
-  uint32_t rounds = 0;
-  // Waiting is done by ONE lane on ONE word (the nearest entry still missing): hundreds of
-  // warps re-reading whole windows of the same few cache lines would saturate the L2
-  // slice that holds them and delay the very stores they are waiting for.
-  int64_t wait_idx = j;
-  while (true) {
-    // ---- wait until status[wait_idx] holds something (bounded)
-    {
-      uint32_t st = ST_PREFIX;
-      while (true) {
-        if (lane == 0 && wait_idx >= 0) st = status_state(ld_status(&status[wait_idx]), epoch);
-        st = __shfl_sync(kFull, st, 0);
-        if (st != ST_NONE) break;
-        rounds++;
-        if ((rounds & 63u) == 0) {
-          int fl = (lane == 0) ? ld_failure(failure) : 0;
-          fl = __shfl_sync(kFull, fl, 0);
-          if (fl != FAIL_NONE) return false;
-          if (rounds >= LOOKBACK_MAX_ROUNDS) {
-            if (lane == 0) atomicCAS(failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT);
-            return false;
-          }
-        }
-        __nanosleep(rounds < 8 ? 20 : (rounds < 64 ? 100 : 400));
-      }
-    }
-    // ---- one wide read of the window: lane l takes the predecessors j-8l .. j-8l-7
-    uint32_t v = 0, f = 0;              // this lane's ordered partial
-    uint64_t w_q[LB_PER_LANE];
-    const int64_t lane_first = j - (int64_t)(LB_PER_LANE * lane);
-#pragma unroll
-    for (int q = 0; q < LB_PER_LANE; q++) {
-      const int64_t idx = lane_first - q;
-      if (idx >= 0) w_q[q] = ld_status(&status[idx]);
-      else           // before the array: virtual tile -1 carries the seed, the rest are identities
-        w_q[q] = pack_status((idx == -1) ? carry_v : 0u, epoch, 0u, ST_PREFIX);
-    }
-    // nearest-first walk over the lane's entries
-    bool lane_ready = true, lane_stop = false;
-    int qend = LB_PER_LANE - 1, qhole = 0;
-#pragma unroll
-    for (int q = 0; q < LB_PER_LANE; q++) {
-      if (lane_ready && !lane_stop) {
-        const uint32_t st = status_state(w_q[q], epoch);
-        if (st == ST_NONE) { lane_ready = false; qhole = q; }
-        else if (st == ST_PREFIX || (Op::kHasFlag && status_flag(w_q[q]))) { lane_stop = true; qend = q; }
-      }
-    }
-    const unsigned stop_mask = __ballot_sync(kFull, lane_ready && lane_stop);
-    const unsigned not_ready = ~__ballot_sync(kFull, lane_ready);
-    const int first_bad = not_ready ? (__ffs(not_ready) - 1) : 32;   // nearest lane with a hole
-    const int p = stop_mask ? (__ffs(stop_mask) - 1) : 32;           // nearest lane with a stop
-    if (first_bad < 32 && first_bad < p) {
-      // a hole lies before any stop: wait for exactly that entry, then read the window again
-      const int hole_q = __shfl_sync(kFull, qhole, first_bad);
-      wait_idx = j - (int64_t)(LB_PER_LANE * first_bad + hole_q);
-      continue;
-    }
-    {
-      // ordered fold of this lane's entries: farther (higher q) on the left
-      bool started = false;
-#pragma unroll
-      for (int q = LB_PER_LANE - 1; q >= 0; q--) {
-        if (q <= qend) {
-          const uint32_t qv = status_value(w_q[q]), qf = Op::kHasFlag ? status_flag(w_q[q]) : 0u;
-          if (!started) { v = qv; f = qf; started = true; }
-          else Op::combine(v, f, qv, qf, v, f);
-        }
-      }
-    }
-    if (lane > p) { v = 0; f = 0; }
-    // ordered fold across lanes: lane l holds positions nearer than lane l+1, so the LEFT
-    // operand comes from the higher lane.
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t ov = __shfl_down_sync(kFull, v, o);
-      uint32_t of = __shfl_down_sync(kFull, f, o);
-      if (lane + o < 32) Op::combine(ov, of, v, f, v, f);
-    }
-    v = __shfl_sync(kFull, v, 0);
-    f = __shfl_sync(kFull, f, 0);
-    if (have_acc) Op::combine(v, f, acc_v, acc_f, acc_v, acc_f);
-    else { acc_v = v; acc_f = f; have_acc = true; }
-    if (p < 32) break;
-    j -= LB_WINDOW;
-    wait_idx = j;
-  }
-  ev = acc_v; ef = acc_f;
-  if (!self_contained && lane == 0) {
-    uint32_t iv, iflag;
-    Op::combine(ev, ef, agg_v, agg_f, iv, iflag);
-    st_status(&status[tile], pack_status(iv, epoch, iflag, ST_PREFIX));
-  }
-  return true;
-}
-
 __device__ __forceinline__ bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
 
-// ---- the persistent look-back kernel -------------------------------------------------------------
-// Progress: tickets are drawn in increasing order and a CTA processes its tiles in the
-// order it drew them, so the smallest unfinished tile is always some CTA's current tile and
-// waits only on finished ones.  The grid never exceeds what is resident at once.
 #ifdef FB_TRACE
 __device__ unsigned long long g_trace[32768 * 8];
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot) do { if (tid == 0 && tile < 32768u) g_trace[tile * 8 + (slot)] = gtime(); } while (0)
-#define TRACEV(slot, val) do { if (tid == 0 && tile < 32768u) g_trace[tile * 8 + (slot)] = (val); } while (0)
+#define TRACE(tile, slot) do { if (threadIdx.x == 0 && (tile) < 32768u) g_trace[(tile) * 8 + (slot)] = gtime(); } while (0)
 #else
-#define TRACE(slot) do {} while (0)
-#define TRACEV(slot, val) do {} while (0)
+#define TRACE(tile, slot) do {} while (0)
 #endif
 
-enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3 };
-constexpr int NSTAGE = 2;
+// ---- the propagator (one warp in the whole grid) --------------------------------------------
+// Walks the status words in tile order.  For every contiguous run of published aggregates
+// it writes the inclusive prefixes back.  `seed` is the exclusive prefix of tile 0.
+template <typename Op>
+__device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, uint32_t seed, int *failure) {
+  const int lane = threadIdx.x & 31;
+  uint32_t run_v = seed, run_f = 0;     // inclusive prefix of tile pos-1
+  uint32_t pos = 0, idle = 0;
+  while (pos < nt) {
+    uint64_t w[PROP_PER_LANE];
+    const uint32_t first = pos + PROP_PER_LANE * lane;
+    int ready = 0;                      // leading published entries of this lane
+    bool open = true;
+#pragma unroll
+    for (int q = 0; q < PROP_PER_LANE; q++) {
+      const uint32_t idx = first + q;
+      w[q] = (idx < nt) ? ld_status(&status[idx]) : 0ull;
+    }
+#pragma unroll
+    for (int q = 0; q < PROP_PER_LANE; q++) {
+      const bool ok = (first + q < nt) && (status_state(w[q], epoch) != ST_NONE);
+      if (open && ok) ready++; else open = false;
+    }
+    const unsigned partial = __ballot_sync(kFull, ready < PROP_PER_LANE);
+    const int stop_lane = partial ? (__ffs(partial) - 1) : 32;      // first lane with a gap
+    const int stop_ready = __shfl_sync(kFull, ready, stop_lane & 31);
+    const uint32_t run = (stop_lane == 32) ? (uint32_t)PROP_WINDOW : (uint32_t)(PROP_PER_LANE * stop_lane + stop_ready);
+    if (run == 0) {
+      idle++;
+      if ((idle & 255u) == 0) {
+        int fl = (lane == 0) ? ld_failure(failure) : 0;
+        if (__shfl_sync(kFull, fl, 0) != FAIL_NONE) return;
+        if (idle >= WAIT_MAX_ROUNDS) {
+          if (lane == 0) atomicCAS(failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT);
+          return;
+        }
+      }
+      __nanosleep(idle < 16 ? 40 : 200);
+      continue;
+    }
+    idle = 0;
+    const int mine = (lane < stop_lane) ? PROP_PER_LANE : (lane == stop_lane ? stop_ready : 0);
+    // in-lane inclusive fold of the aggregates, then exclusive scan across lanes
+    uint32_t iv[PROP_PER_LANE], iflag[PROP_PER_LANE];
+    uint32_t tv = 0, tf = 0;            // lane total (identity if the lane has nothing)
+#pragma unroll
+    for (int q = 0; q < PROP_PER_LANE; q++) {
+      if (q < mine) {
+        const uint32_t av = status_value(w[q]), af = Op::kHasFlag ? status_flag(w[q]) : 0u;
+        if (q == 0) { tv = av; tf = af; } else Op::combine(tv, tf, av, af, tv, tf);
+      }
+      iv[q] = tv; iflag[q] = tf;
+    }
+    uint32_t sv = tv, sf = tf;          // inclusive scan of lane totals
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t lv = __shfl_up_sync(kFull, sv, o), lf = __shfl_up_sync(kFull, sf, o);
+      if (lane >= o) Op::combine(lv, lf, sv, sf, sv, sf);
+    }
+    uint32_t ev = __shfl_up_sync(kFull, sv, 1), ef = __shfl_up_sync(kFull, sf, 1);
+    if (lane == 0) { ev = run_v; ef = run_f; } else Op::combine(run_v, run_f, ev, ef, ev, ef);
+    // ev/ef: inclusive prefix of the tile just before this lane's first entry
+#pragma unroll
+    for (int q = 0; q < PROP_PER_LANE; q++) {
+      if (q < mine) {
+        uint32_t pv, pf;
+        Op::combine(ev, ef, iv[q], iflag[q], pv, pf);
+        st_status(&status[first + q], pack_status(pv, epoch, pf, ST_PREFIX));
+      }
+    }
+    // new running prefix = inclusive prefix of the last tile of the run
+    uint32_t lastv, lastf;
+    Op::combine(run_v, run_f, __shfl_sync(kFull, sv, 31), __shfl_sync(kFull, sf, 31), lastv, lastf);
+    run_v = lastv; run_f = lastf;
+    pos += run;
+  }
+}
 
-template <int KIND> struct StageBytes { static constexpr int value = SCAN_TILE * 4; };
-template <> struct StageBytes<K_SEGSCAN_F32> { static constexpr int value = SCAN_TILE * 4 + SCAN_TILE; };
+// ---- the persistent kernel ---------------------------------------------------------------------------
+enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3 };
+
+template <int KIND> struct StageCfg { static constexpr int bytes = SCAN_TILE * 4; static constexpr int stages = 5; };
+template <> struct StageCfg<K_SEGSCAN_F32> { static constexpr int bytes = SCAN_TILE * 4 + SCAN_TILE; static constexpr int stages = 4; };
 
 struct LookbackArgs {
   const void *in;          // values / keys
@@ -221,7 +180,7 @@ struct LookbackArgs {
   uint32_t *out_false;     // partition: the rejected keys
   int64_t n;
   uint32_t num_tiles;
-  uint32_t *ticket;
+  uint32_t *ticket;        // [0] tile tickets, [1] role counter
   uint64_t *status;
   uint32_t epoch;
   int *failure;
@@ -231,28 +190,50 @@ struct LookbackArgs {
   int64_t *d_count;        // compaction: number of selected keys
 };
 
+enum : uint32_t { ACT_IDLE = 0, ACT_SCAN = 1, ACT_FINISH = 2, ACT_DONE = 3, ACT_FAIL = 4 };
+
 template <int KIND>
-__global__ void __launch_bounds__(SCAN_THREADS, 2)
+__global__ void __launch_bounds__(SCAN_THREADS, 1)
 lookback_kernel(const LookbackArgs a) {
-  constexpr int SB = StageBytes<KIND>::value;
+  constexpr int SB = StageCfg<KIND>::bytes;
+  constexpr int NST = StageCfg<KIND>::stages;
+  using Op = typename std::conditional<KIND == K_SEGSCAN_F32, OpSegAddF32, OpAddU32>::type;
   extern __shared__ __align__(128) unsigned char s_stages[];
-  __shared__ __align__(8) uint64_t s_bar[NSTAGE];
-  __shared__ uint32_t s_tid[NSTAGE];
-  __shared__ uint32_t s_wv[SCAN_WARPS], s_wf[SCAN_WARPS];
-  __shared__ uint32_t s_pv, s_pf, s_ok;
+  __shared__ __align__(8) uint64_t s_bar[NST];
+  __shared__ uint32_t s_tile_of[NST];      // tile in the slot
+  __shared__ uint32_t s_meta[NST];         // after the scan: segmented scan = index of the first segment
+                                           // start in the tile (SCAN_TILE if none); compaction = selected count
+  __shared__ uint32_t s_wv[SCAN_WARPS], s_wf[SCAN_WARPS], s_ff[SCAN_WARPS];
+  __shared__ uint32_t s_act, s_slot, s_pv, s_pf, s_role, s_agg_v, s_agg_f;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (ld_failure(a.failure) != FAIL_NONE) return;
   const uint32_t nt = a.num_tiles;
-  // every CTA draws one ticket up front, one per tile it works on, and stops at its first
-  // invalid ticket: nt valid draws + gridDim.x invalid ones in total
-  const uint32_t last_draw = nt + gridDim.x - 1;
+
+  // ---- role: the first CTA to arrive propagates prefixes, all others work on tiles
+  if (tid == 0) {
+    const uint32_t r = atomicAdd(&a.ticket[1], 1u);
+    if (r == gridDim.x - 1) atomicExch(&a.ticket[1], 0u);     // rewind for the next launch
+    s_role = r;
+  }
+  __syncthreads();
+  if (s_role == 0 && gridDim.x > 1) {
+    if (warp == 0) {
+      uint32_t seed = a.carry_in;
+      if (KIND == K_SCAN_I32 && a.carry_vals != nullptr)
+        for (int q = 0; q < a.carry_n; q++) seed += a.carry_vals[q];
+      run_propagator<Op>(a.status, nt, a.epoch, seed, a.failure);
+    }
+    return;
+  }
+  // (a grid of one CTA has no propagator: the single worker resolves prefixes itself, below)
+  const bool self_propagate = (gridDim.x == 1);
+
+  const uint32_t workers = self_propagate ? 1u : gridDim.x - 1;
+  const uint32_t last_draw = nt + workers - 1;   // every worker ends on exactly one invalid ticket
   const bool ptr_aligned = aligned16(a.in) && (KIND == K_FILTER || KIND == K_PARTITION || aligned16(a.out)) &&
                            (KIND != K_SEGSCAN_F32 || aligned16(a.flags));
-
-  auto tile_is_bulk = [&](uint32_t t) -> bool {
-    return ptr_aligned && ((int64_t)(t + 1) * SCAN_TILE <= a.n);
-  };
+  auto tile_is_bulk = [&](uint32_t t) -> bool { return ptr_aligned && ((int64_t)(t + 1) * SCAN_TILE <= a.n); };
   auto issue_load = [&](int s, uint32_t t) {   // one thread
     unsigned char *st = s_stages + s * SB;
     const int64_t base = (int64_t)t * SCAN_TILE;
@@ -260,227 +241,324 @@ lookback_kernel(const LookbackArgs a) {
     bulk_g2s(st, reinterpret_cast<const uint32_t *>(a.in) + base, SCAN_TILE * 4, &s_bar[s]);
     if (KIND == K_SEGSCAN_F32) bulk_g2s(st + SCAN_TILE * 4, a.flags + base, SCAN_TILE, &s_bar[s]);
   };
-  auto draw_and_load = [&](int s) {             // one thread
-    uint32_t t = atomicAdd(a.ticket, 1u);
-    if (t == last_draw) atomicExch(a.ticket, 0u);     // rewind for the next launch
-    s_tid[s] = t;
-    if (t < nt && tile_is_bulk(t)) issue_load(s, t);
-  };
+
+  // Ring bookkeeping, thread 0 only.  Slots are used in FIFO order:
+  //   filled .. scanned .. finished .. stored;  counters only grow, slot = counter % NST.
+  uint32_t n_filled = 0, n_scanned = 0, n_finished = 0, n_refillable = 0;
+  bool exhausted = false;
+  uint32_t phases = 0;      // bit s: parity of the next completion of slot s's barrier (thread 0's view)
+  uint32_t self_v = a.carry_in, self_f = 0;     // running prefix when the CTA propagates for itself
+  uint32_t idle = 0;
+  // The status word of the oldest waiting tile's predecessor is read at the START of every
+  // action and looked at when the action is over, so the L2 round trip overlaps the work.
+  uint64_t polled_w = 0;
+  uint32_t polled_idx = 0xffffffffu;
 
   if (tid == 0) {
-    for (int s = 0; s < NSTAGE; s++) mbar_init(&s_bar[s], 1);
+    for (int s = 0; s < NST; s++) mbar_init(&s_bar[s], 1);
     fence_mbar_init();
-    draw_and_load(0);
+    if (self_propagate && KIND == K_SCAN_I32 && a.carry_vals != nullptr)
+      for (int q = 0; q < a.carry_n; q++) self_v += a.carry_vals[q];
   }
   __syncthreads();
 
-  uint32_t phases = 0;     // bit s: parity of stage s's next barrier completion
-  for (uint32_t k = 0;; k++) {
-    const int s = k % NSTAGE;
-    const uint32_t tile = s_tid[s];
-    if (tile >= nt) break;
-    TRACE(0);
-    TRACE(1);
+  while (true) {
+    // ================= thread 0 decides what the CTA does next =================
+    if (tid == 0) {
+      // refill: a slot is free once the bulk store that read it has finished; stores finish
+      // in order, so "all but the newest" is known after wait_group.read 1 (done at FINISH)
+      while (!exhausted && n_filled < n_refillable + NST && n_filled - n_finished < NST) {
+        const uint32_t t = atomicAdd(&a.ticket[0], 1u);
+        if (t == last_draw) atomicExch(&a.ticket[0], 0u);
+        if (t >= nt) { exhausted = true; break; }
+        const int s = n_filled % NST;
+        s_tile_of[s] = t;
+        if (tile_is_bulk(t)) issue_load(s, t);
+        n_filled++;
+      }
+      uint32_t act = ACT_IDLE, slot = 0;
+      // oldest tile waiting for its prefix?
+      if (n_finished < n_scanned) {
+        const int s = n_finished % NST;
+        const uint32_t t = s_tile_of[s];
+        if (self_propagate) { s_pv = self_v; s_pf = self_f; act = ACT_FINISH; slot = s; }
+        else if (t == 0) { s_pv = a.carry_in; s_pf = 0;
+          if (KIND == K_SCAN_I32 && a.carry_vals != nullptr) for (int q = 0; q < a.carry_n; q++) s_pv += a.carry_vals[q];
+          act = ACT_FINISH; slot = s; }
+        else {
+          // use the word read during the previous action if it is the right one and already a
+          // prefix; read afresh only when there is nothing to scan meanwhile
+          uint64_t w = (polled_idx == t - 1) ? polled_w : 0ull;
+          const bool can_scan = n_scanned < n_filled;
+          if (status_state(w, a.epoch) != ST_PREFIX && !can_scan) w = ld_status(&a.status[t - 1]);
+          if (status_state(w, a.epoch) == ST_PREFIX) {
+            s_pv = status_value(w); s_pf = Op::kHasFlag ? status_flag(w) : 0u;
+            act = ACT_FINISH; slot = s;
+          }
+        }
+      }
+      // otherwise: next loaded tile ready to be scanned?
+      if (act == ACT_IDLE && n_scanned < n_filled) {
+        const int s = n_scanned % NST;
+        const uint32_t t = s_tile_of[s];
+        if (!tile_is_bulk(t)) { act = ACT_SCAN; slot = s; }
+        else if (mbar_try_wait(&s_bar[s], (phases >> s) & 1u)) { phases ^= (1u << s); act = ACT_SCAN; slot = s; }
+      }
+      if (act == ACT_IDLE) {
+        if (exhausted && n_finished == n_filled) act = ACT_DONE;
+        else {
+          idle++;
+          if ((idle & 255u) == 0 && ld_failure(a.failure) != FAIL_NONE) act = ACT_FAIL;
+          if (idle >= WAIT_MAX_ROUNDS) { atomicCAS(a.failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT); act = ACT_FAIL; }
+          if (act == ACT_IDLE) __nanosleep(idle < 8 ? 20 : 100);
+        }
+      } else idle = 0;
+      s_act = act; s_slot = slot;
+    }
+    __syncthreads();
+    const uint32_t act = s_act;
+    const int s = (int)s_slot;
+    if (act == ACT_DONE) break;
+    if (act == ACT_FAIL) {
+      // drain: bulk stores must finish reading shared memory; loads in flight are awaited with a limit
+      if (tid == 0) {
+        bulk_wait_read0();
+        for (uint32_t c = n_scanned; c < n_filled; c++) {
+          const int q = c % NST;
+          if (tile_is_bulk(s_tile_of[q])) { (void)mbar_wait_bounded(&s_bar[q], (phases >> q) & 1u, 1u << 16); phases ^= (1u << q); }
+        }
+      }
+      return;
+    }
+    if (act == ACT_IDLE) { __syncthreads(); continue; }
+    if (tid == 0 && !self_propagate) {
+      // which tile will be the oldest one waiting once this action is over?
+      uint32_t c = n_finished + (act == ACT_FINISH ? 1u : 0u);
+      const uint32_t scanned_after = n_scanned + (act == ACT_SCAN ? 1u : 0u);
+      polled_idx = 0xffffffffu;
+      if (c < scanned_after) {
+        const uint32_t t = s_tile_of[c % NST];
+        if (t > 0) { polled_idx = t - 1; polled_w = ld_status(&a.status[t - 1]); }
+      }
+    }
 
     unsigned char *stage = s_stages + s * SB;
     uint32_t *s_tile = reinterpret_cast<uint32_t *>(stage);
+    const uint32_t tile = s_tile_of[s];
     const int64_t base = (int64_t)tile * SCAN_TILE;
     const int count = (int)((a.n - base) < SCAN_TILE ? (a.n - base) : SCAN_TILE);
     const bool bulk = tile_is_bulk(tile);
 
-    if (bulk) {
-      const bool arrived = mbar_wait_bounded(&s_bar[s], (phases >> s) & 1u);
-      phases ^= (1u << s);
-      if (!__syncthreads_and(arrived)) {
-        if (tid == 0) { atomicCAS(a.failure, FAIL_NONE, FAIL_BULK_COPY_TIMEOUT); bulk_wait_read0(); }
-        return;
+    if (act == ACT_SCAN) {
+      // ================= local scan of a freshly loaded tile =================
+      TRACE(tile, 0);
+      if (!bulk) {
+        const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
+        for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS) s_tile[i] = (i < count) ? gin[i] : 0u;
+        if (KIND == K_SEGSCAN_F32) {
+          uint8_t *sf = stage + SCAN_TILE * 4;
+          for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS) sf[i] = (i < count) ? a.flags[base + i] : (uint8_t)0;
+        }
+        __syncthreads();
       }
-    } else {
-      const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
-      for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS) s_tile[i] = (i < count) ? gin[i] : 0u;
-      if (KIND == K_SEGSCAN_F32) {
-        uint8_t *sf = stage + SCAN_TILE * 4;
-        for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS) sf[i] = (i < count) ? a.flags[base + i] : (uint8_t)0;
+      uint32_t x[SCAN_ITEMS];
+      {
+        const int4 *src = reinterpret_cast<const int4 *>(s_tile) + tid * (SCAN_ITEMS / 4);
+#pragma unroll
+        for (int j = 0; j < SCAN_ITEMS / 4; j++) {
+          int4 v = src[j];
+          x[4 * j + 0] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
+        }
       }
-      __syncthreads();
-    }
-
-    TRACE(2);
-    // ---- each thread takes its 20 consecutive elements
-    uint32_t x[SCAN_ITEMS];
-    {
-      const int4 *src = reinterpret_cast<const int4 *>(s_tile) + tid * (SCAN_ITEMS / 4);
-#pragma unroll
-      for (int j = 0; j < SCAN_ITEMS / 4; j++) {
-        int4 v = src[j];
-        x[4 * j + 0] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
-      }
-    }
-    const int first_local = tid * SCAN_ITEMS;
-
-    // ---- in-thread pass: (pv, pf) = the thread's aggregate
-    uint32_t pv, pf = 0, bits = 0;   // bits: segment starts (segmented scan) / selected keys (compaction)
-    if (KIND == K_SCAN_I32) {
-      uint32_t sum = 0;
-#pragma unroll
-      for (int q = 0; q < SCAN_ITEMS; q++) { sum += x[q]; x[q] = sum; }
-      pv = sum;
-    } else if (KIND == K_SEGSCAN_F32) {
-      const uint32_t *s_flag = reinterpret_cast<const uint32_t *>(stage + SCAN_TILE * 4) + tid * (SCAN_ITEMS / 4);
-      uint32_t fw[SCAN_ITEMS / 4];
-#pragma unroll
-      for (int j = 0; j < SCAN_ITEMS / 4; j++) fw[j] = s_flag[j];
-      float acc = 0.0f;
-#pragma unroll
-      for (int q = 0; q < SCAN_ITEMS; q++) {
-        const uint32_t fl = (fw[q >> 2] >> (8 * (q & 3))) & 0xffu;
-        const float v = __uint_as_float(x[q]);
-        if (fl) { acc = v; bits |= (1u << q); } else acc = acc + v;
-        x[q] = __float_as_uint(acc);
-      }
-      pv = __float_as_uint(acc);
-      pf = bits ? 1u : 0u;
-    } else {
-#pragma unroll
-      for (int q = 0; q < SCAN_ITEMS; q++)
-        if ((first_local + q < count) && ((x[q] & 7u) < 3u)) bits |= (1u << q);
-      pv = __popc(bits);
-    }
-
-    // ---- block scan of the thread aggregates: shuffle scan in the warp, then every warp
-    //      scans the 16 warp totals with shuffles
-    uint32_t thv, thf = 0, tv, tf = 0;    // thread's exclusive prefix in the tile; tile aggregate
-    if (KIND == K_SEGSCAN_F32) {
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        uint32_t lv = __shfl_up_sync(kFull, pv, o);
-        uint32_t lf = __shfl_up_sync(kFull, pf, o);
-        if (lane >= o) OpSegAddF32::combine(lv, lf, pv, pf, pv, pf);
-      }
-      if (lane == 31) { s_wv[warp] = pv; s_wf[warp] = pf; }
-      uint32_t xv = __shfl_up_sync(kFull, pv, 1), xf = __shfl_up_sync(kFull, pf, 1);
-      if (lane == 0) { xv = 0; xf = 0; }
-      __syncthreads();
-      uint32_t wv = (lane < SCAN_WARPS) ? s_wv[lane] : 0u, wf = (lane < SCAN_WARPS) ? s_wf[lane] : 0u;
-#pragma unroll
-      for (int o = 1; o < SCAN_WARPS; o <<= 1) {
-        uint32_t lv = __shfl_up_sync(kFull, wv, o);
-        uint32_t lf = __shfl_up_sync(kFull, wf, o);
-        if (lane >= o) OpSegAddF32::combine(lv, lf, wv, wf, wv, wf);
-      }
-      tv = __shfl_sync(kFull, wv, SCAN_WARPS - 1);
-      tf = __shfl_sync(kFull, wf, SCAN_WARPS - 1);
-      uint32_t bv = __shfl_sync(kFull, wv, warp > 0 ? warp - 1 : 0), bf = __shfl_sync(kFull, wf, warp > 0 ? warp - 1 : 0);
-      if (warp == 0) { bv = 0; bf = 0; }
-      OpSegAddF32::combine(bv, bf, xv, xf, thv, thf);
-    } else {
-      const uint32_t own_v = pv;
-      const uint32_t incl = warp_incl_scan_add(pv, lane);
-      if (lane == 31) s_wv[warp] = incl;
-      __syncthreads();
-      uint32_t wv = (lane < SCAN_WARPS) ? s_wv[lane] : 0u;
-      wv = warp_incl_scan_add(wv, lane);
-      tv = __shfl_sync(kFull, wv, SCAN_WARPS - 1);
-      uint32_t bv = __shfl_sync(kFull, wv, warp > 0 ? warp - 1 : 0);
-      if (warp == 0) bv = 0;
-      thv = bv + incl - own_v;
-    }
-
-    TRACE(3);
-    // ---- look-back (warp 0); the other warps go on to whatever does not need the prefix
-    if (warp == 0) {
-      uint32_t ev, ef, cin = a.carry_in;
-      if (KIND == K_SCAN_I32 && a.carry_vals != nullptr && tile < (uint32_t)LB_WINDOW)
-        for (int q = 0; q < a.carry_n; q++) cin += a.carry_vals[q];
-      bool ok;
-      if (KIND == K_SEGSCAN_F32) ok = tile_lookback<OpSegAddF32>(a.status, tile, a.epoch, tv, tf, cin, a.failure, ev, ef);
-      else ok = tile_lookback<OpAddU32>(a.status, tile, a.epoch, tv, 0u, cin, a.failure, ev, ef);
-      if (lane == 0) { s_pv = ev; s_pf = ef; s_ok = ok ? 1u : 0u; }
-      TRACE(4);
-      // Only now is the next ticket drawn: this CTA will start that tile within about a
-      // microsecond (the write-out below), so no tile is claimed long before it is worked
-      // on -- a tile claimed early by a CTA that is still waiting in a look-back would
-      // hold up every tile after it.  The other stage's last bulk store must have finished
-      // reading shared memory before the stage is refilled.
-      if (tid == 0 && ok) {
-        bulk_wait_read0();
-        draw_and_load(s ^ 1);
-      }
-    }
-
-    if (KIND == K_FILTER || KIND == K_PARTITION) {
-      // compact inside the stage (every thread holds its keys in registers since the barrier
-      // above): selected keys first, in order, then the rejected ones
-      uint32_t t_pos = thv;
-      const int valid_before = first_local < count ? first_local : count;
-      uint32_t f_pos = tv + (uint32_t)valid_before - thv;
-#pragma unroll
-      for (int q = 0; q < SCAN_ITEMS; q++) {
-        if (bits & (1u << q)) s_tile[t_pos++] = x[q];
-        else if (KIND == K_PARTITION && (first_local + q < count)) s_tile[f_pos++] = x[q];
-      }
-    }
-    __syncthreads();
-    if (!s_ok) {
-      if (tid == 0) bulk_wait_read0();
-      return;
-    }
-
-    if (KIND == K_SCAN_I32 || KIND == K_SEGSCAN_F32) {
-      int4 *dst = reinterpret_cast<int4 *>(s_tile) + tid * (SCAN_ITEMS / 4);
+      const int first_local = tid * SCAN_ITEMS;
+      uint32_t pv, pf = 0, bits = 0;   // bits: segment starts (segmented scan) / selected keys (compaction)
       if (KIND == K_SCAN_I32) {
-        const uint32_t start = s_pv + thv;
+        uint32_t sum = 0;
 #pragma unroll
-        for (int j = 0; j < SCAN_ITEMS / 4; j++) {
-          int4 v;
-          v.x = start + x[4 * j + 0]; v.y = start + x[4 * j + 1]; v.z = start + x[4 * j + 2]; v.w = start + x[4 * j + 3];
-          dst[j] = v;
+        for (int q = 0; q < SCAN_ITEMS; q++) { sum += x[q]; x[q] = sum; }
+        pv = sum;
+      } else if (KIND == K_SEGSCAN_F32) {
+        const uint32_t *s_flag = reinterpret_cast<const uint32_t *>(stage + SCAN_TILE * 4) + tid * (SCAN_ITEMS / 4);
+        uint32_t fw[SCAN_ITEMS / 4];
+#pragma unroll
+        for (int j = 0; j < SCAN_ITEMS / 4; j++) fw[j] = s_flag[j];
+        float acc = 0.0f;
+#pragma unroll
+        for (int q = 0; q < SCAN_ITEMS; q++) {
+          const uint32_t fl = (fw[q >> 2] >> (8 * (q & 3))) & 0xffu;
+          const float v = __uint_as_float(x[q]);
+          if (fl) { acc = v; bits |= (1u << q); } else acc = acc + v;
+          x[q] = __float_as_uint(acc);
         }
+        pv = __float_as_uint(acc);
+        pf = bits ? 1u : 0u;
       } else {
-        uint32_t sv, sf2;
-        OpSegAddF32::combine(s_pv, s_pf, thv, thf, sv, sf2);
-        const float start = __uint_as_float(sv);
-        // elements before the thread's first segment start receive the incoming prefix
-        const int first = bits ? (__ffs(bits) - 1) : SCAN_ITEMS;
 #pragma unroll
-        for (int j = 0; j < SCAN_ITEMS / 4; j++) {
-          float r[4];
+        for (int q = 0; q < SCAN_ITEMS; q++)
+          if ((first_local + q < count) && ((x[q] & 7u) < 3u)) bits |= (1u << q);
+        pv = __popc(bits);
+      }
+
+      // block scan of the thread aggregates
+      uint32_t thv, thf = 0, tv, tf = 0;    // thread's exclusive prefix in the tile; tile aggregate
+      if (KIND == K_SEGSCAN_F32) {
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const float v = __uint_as_float(x[4 * j + e]);
-            r[e] = (4 * j + e < first) ? start + v : v;
+        for (int o = 1; o < 32; o <<= 1) {
+          uint32_t lv = __shfl_up_sync(kFull, pv, o);
+          uint32_t lf = __shfl_up_sync(kFull, pf, o);
+          if (lane >= o) OpSegAddF32::combine(lv, lf, pv, pf, pv, pf);
+        }
+        if (lane == 31) { s_wv[warp] = pv; s_wf[warp] = pf; }
+        uint32_t xv = __shfl_up_sync(kFull, pv, 1), xf = __shfl_up_sync(kFull, pf, 1);
+        if (lane == 0) { xv = 0; xf = 0; }
+        __syncthreads();
+        uint32_t wv = (lane < SCAN_WARPS) ? s_wv[lane] : 0u, wf = (lane < SCAN_WARPS) ? s_wf[lane] : 0u;
+#pragma unroll
+        for (int o = 1; o < SCAN_WARPS; o <<= 1) {
+          uint32_t lv = __shfl_up_sync(kFull, wv, o);
+          uint32_t lf = __shfl_up_sync(kFull, wf, o);
+          if (lane >= o) OpSegAddF32::combine(lv, lf, wv, wf, wv, wf);
+        }
+        tv = __shfl_sync(kFull, wv, SCAN_WARPS - 1);
+        tf = __shfl_sync(kFull, wf, SCAN_WARPS - 1);
+        uint32_t bv = __shfl_sync(kFull, wv, warp > 0 ? warp - 1 : 0), bf = __shfl_sync(kFull, wf, warp > 0 ? warp - 1 : 0);
+        if (warp == 0) { bv = 0; bf = 0; }
+        OpSegAddF32::combine(bv, bf, xv, xf, thv, thf);
+      } else {
+        const uint32_t own_v = pv;
+        const uint32_t incl = warp_incl_scan_add(pv, lane);
+        if (lane == 31) s_wv[warp] = incl;
+        __syncthreads();
+        uint32_t wv = (lane < SCAN_WARPS) ? s_wv[lane] : 0u;
+        wv = warp_incl_scan_add(wv, lane);
+        tv = __shfl_sync(kFull, wv, SCAN_WARPS - 1);
+        uint32_t bv = __shfl_sync(kFull, wv, warp > 0 ? warp - 1 : 0);
+        if (warp == 0) bv = 0;
+        thv = bv + incl - own_v;
+      }
+
+      // publish the tile aggregate (or keep the running prefix when there is no propagator)
+      if (tid == 0) {
+        if (self_propagate) { s_agg_v = tv; s_agg_f = tf; }   // folded into the running prefix when the tile is finished
+        else st_status(&a.status[tile], pack_status(tv, a.epoch, tf, ST_AGG));
+      }
+
+      // tile-local results back into the stage
+      if (KIND == K_SCAN_I32 || KIND == K_SEGSCAN_F32) {
+        int4 *dst = reinterpret_cast<int4 *>(s_tile) + tid * (SCAN_ITEMS / 4);
+        if (KIND == K_SCAN_I32) {
+#pragma unroll
+          for (int j = 0; j < SCAN_ITEMS / 4; j++) {
+            int4 v;
+            v.x = thv + x[4 * j + 0]; v.y = thv + x[4 * j + 1]; v.z = thv + x[4 * j + 2]; v.w = thv + x[4 * j + 3];
+            dst[j] = v;
           }
-          int4 v; v.x = __float_as_int(r[0]); v.y = __float_as_int(r[1]); v.z = __float_as_int(r[2]); v.w = __float_as_int(r[3]);
-          dst[j] = v;
-        }
-      }
-      uint32_t *gout = reinterpret_cast<uint32_t *>(a.out) + base;
-      if (bulk) {
-        fence_proxy_async_smem();
-        __syncthreads();
-        if (tid == 0) {
-          bulk_s2g(gout, s_tile, SCAN_TILE * 4);
-          bulk_commit();                       // waited for (read side) before the stage is refilled
+        } else {
+          // elements before the thread's first segment start continue the thread's exclusive prefix
+          const float start = __uint_as_float(thv);
+          const int first = bits ? (__ffs(bits) - 1) : SCAN_ITEMS;
+#pragma unroll
+          for (int j = 0; j < SCAN_ITEMS / 4; j++) {
+            float r[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const float v = __uint_as_float(x[4 * j + e]);
+              r[e] = (4 * j + e < first) ? start + v : v;
+            }
+            int4 v; v.x = __float_as_int(r[0]); v.y = __float_as_int(r[1]); v.z = __float_as_int(r[2]); v.w = __float_as_int(r[3]);
+            dst[j] = v;
+          }
+          // index of the first segment start in the tile: the incoming prefix applies before it
+          uint32_t ff = bits ? (uint32_t)(first_local + first) : (uint32_t)SCAN_TILE;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) { uint32_t t2 = __shfl_xor_sync(kFull, ff, o); ff = t2 < ff ? t2 : ff; }
+          if (lane == 0) s_ff[warp] = ff;
         }
       } else {
-        __syncthreads();
-        for (int i = tid; i < count; i += SCAN_THREADS) gout[i] = s_tile[i];
+        // compact inside the stage: selected keys first, in order, then the rejected ones
+        // (every thread took its keys into registers before the barrier of the block scan)
+        uint32_t t_pos = thv;
+        const int valid_before = first_local < count ? first_local : count;
+        uint32_t f_pos = tv + (uint32_t)valid_before - thv;
+#pragma unroll
+        for (int q = 0; q < SCAN_ITEMS; q++) {
+          if (bits & (1u << q)) s_tile[t_pos++] = x[q];
+          else if (KIND == K_PARTITION && (first_local + q < count)) s_tile[f_pos++] = x[q];
+        }
       }
+      __syncthreads();
+      if (tid == 0) {
+        uint32_t meta = tv;
+        if (KIND == K_SEGSCAN_F32) {
+          meta = SCAN_TILE;
+          for (int wq = 0; wq < SCAN_WARPS; wq++) meta = s_ff[wq] < meta ? s_ff[wq] : meta;
+        }
+        s_meta[s] = meta;
+        n_scanned++;
+      }
+      TRACE(tile, 1);
+      // (no barrier needed here: the next iteration starts with thread 0's decision + barrier)
     } else {
-      const int64_t true_before = (int64_t)s_pv;        // selected keys in earlier tiles
-      uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
-      for (uint32_t i = tid; i < tv; i += SCAN_THREADS) dst[i] = s_tile[i];
-      if (KIND == K_PARTITION) {
-        uint32_t *dstf = a.out_false + (base - true_before);
-        const uint32_t nf = (uint32_t)count - tv;
-        for (uint32_t i = tid; i < nf; i += SCAN_THREADS) dstf[i] = s_tile[tv + i];
+      // ================= finish: apply the incoming prefix and write out =================
+      TRACE(tile, 2);
+      const uint32_t pv_in = s_pv, pf_in = s_pf;
+      (void)pf_in;
+      if (KIND == K_SCAN_I32) {
+        int4 *p4 = reinterpret_cast<int4 *>(s_tile);
+#pragma unroll
+        for (int j = 0; j < SCAN_ITEMS / 4; j++) {
+          int4 v = p4[tid + j * SCAN_THREADS];
+          v.x += pv_in; v.y += pv_in; v.z += pv_in; v.w += pv_in;
+          p4[tid + j * SCAN_THREADS] = v;
+        }
+      } else if (KIND == K_SEGSCAN_F32) {
+        const uint32_t upto = s_meta[s];
+        const float add = __uint_as_float(pv_in);
+        float *pf32 = reinterpret_cast<float *>(s_tile);
+        for (uint32_t i = tid; i < upto; i += SCAN_THREADS) pf32[i] = add + pf32[i];
       }
-      if (tile == nt - 1 && tid == 0) *a.d_count = true_before + (int64_t)tv;
+      if (KIND == K_SCAN_I32 || KIND == K_SEGSCAN_F32) {
+        uint32_t *gout = reinterpret_cast<uint32_t *>(a.out) + base;
+        if (bulk) {
+          fence_proxy_async_smem();
+          __syncthreads();
+          if (tid == 0) {
+            bulk_s2g(gout, s_tile, SCAN_TILE * 4);
+            bulk_commit();
+            bulk_wait_read1();                 // every store but this one has finished reading
+            n_refillable = n_finished;         // slots of tiles finished before this one are free
+          }
+        } else {
+          __syncthreads();
+          for (int i = tid; i < count; i += SCAN_THREADS) gout[i] = s_tile[i];
+          __syncthreads();
+          if (tid == 0) { bulk_wait_read0(); n_refillable = n_finished + 1; }
+        }
+      } else {
+        const uint32_t tile_true = s_meta[s];
+        const int64_t true_before = (int64_t)pv_in;       // selected keys in earlier tiles
+        uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
+        for (uint32_t i = tid; i < tile_true; i += SCAN_THREADS) dst[i] = s_tile[i];
+        if (KIND == K_PARTITION) {
+          uint32_t *dstf = a.out_false + (base - true_before);
+          const uint32_t nf = (uint32_t)count - tile_true;
+          for (uint32_t i = tid; i < nf; i += SCAN_THREADS) dstf[i] = s_tile[tile_true + i];
+        }
+        if (tile == nt - 1 && tid == 0) *a.d_count = true_before + (int64_t)tile_true;
+        __syncthreads();
+        if (tid == 0) n_refillable = n_finished + 1;
+      }
+      if (tid == 0) {
+        if (self_propagate) {
+          uint32_t nv, nf2;
+          Op::combine(self_v, self_f, s_agg_v, s_agg_f, nv, nf2);   // a lone worker finishes each tile right after scanning it
+          self_v = nv; self_f = nf2;
+          st_status(&a.status[tile], pack_status(nv, a.epoch, nf2, ST_PREFIX));   // the shard summary reads the last one
+        }
+        n_finished++;
+      }
+      TRACE(tile, 3);
     }
-    TRACE(5);
-    TRACEV(6, (unsigned long long)blockIdx.x);
-    // No barrier here: s_tid[s ^ 1] was written before the barrier that followed the look-back,
-    // and the stage just used is refilled only after the barriers of the next iteration.
   }
   if (tid == 0) bulk_wait_read0();     // shared memory must outlive the last bulk store's reads
 }
@@ -502,8 +580,7 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
 // CTA per tile.  The occupancy query allocates nothing and is cached per kind.
 template <int KIND>
 static cudaError_t launch_lookback(LookbackArgs a, cudaStream_t stream) {
-  constexpr int SB = StageBytes<KIND>::value;
-  constexpr size_t smem = (size_t)NSTAGE * SB;
+  constexpr size_t smem = (size_t)StageCfg<KIND>::stages * StageCfg<KIND>::bytes;
   static int ctas_per_sm_dev[64], num_sms_dev[64];     // per device ordinal (function attributes are per device)
   int dev = 0;
   cudaGetDevice(&dev);
@@ -521,8 +598,10 @@ static cudaError_t launch_lookback(LookbackArgs a, cudaStream_t stream) {
     num_sms = sms;
     ctas_per_sm = occ;
   }
+  // one propagator CTA + workers; a single tile runs as one self-propagating worker
   const uint32_t resident = (uint32_t)(ctas_per_sm * num_sms);
-  const uint32_t grid = a.num_tiles < resident ? a.num_tiles : resident;
+  uint32_t grid = a.num_tiles + 1 < resident ? a.num_tiles + 1 : resident;
+  if (a.num_tiles <= 1 || grid < 2) grid = 1;
   lookback_kernel<KIND><<<grid, SCAN_THREADS, smem, stream>>>(a);
   return cudaGetLastError();
 }
