@@ -126,7 +126,7 @@ __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, ui
           return;
         }
       }
-      __nanosleep(idle < 16 ? 40 : 200);
+      if (idle > 64) __nanosleep(100);
       continue;
     }
     idle = 0;
@@ -157,6 +157,9 @@ __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, ui
         uint32_t pv, pf;
         Op::combine(ev, ef, iv[q], iflag[q], pv, pf);
         st_status(&status[first + q], pack_status(pv, epoch, pf, ST_PREFIX));
+#ifdef FB_TRACE
+        if (first + q < 32768u) g_trace[(first + q) * 8 + 7] = gtime();
+#endif
       }
     }
     // new running prefix = inclusive prefix of the last tile of the run
@@ -172,6 +175,13 @@ enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITI
 
 template <int KIND> struct StageCfg { static constexpr int bytes = SCAN_TILE * 4; static constexpr int stages = 5; };
 template <> struct StageCfg<K_SEGSCAN_F32> { static constexpr int bytes = SCAN_TILE * 4 + SCAN_TILE; static constexpr int stages = 4; };
+
+// 32-bit load that goes to L2 (never served from a stale L1 line)
+__device__ __forceinline__ int ld_stream_relaxed(const void *p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 struct LookbackArgs {
   const void *in;          // values / keys
@@ -190,7 +200,19 @@ struct LookbackArgs {
   int64_t *d_count;        // compaction: number of selected keys
 };
 
-enum : uint32_t { ACT_IDLE = 0, ACT_SCAN = 1, ACT_FINISH = 2, ACT_DONE = 3, ACT_FAIL = 4 };
+enum : uint32_t { ACT_IDLE = 0, ACT_SCAN = 1, ACT_FINISH = 2, ACT_FIXUP = 3, ACT_DONE = 4, ACT_FAIL = 5 };
+enum : uint32_t { SLOT_FREE = 0, SLOT_LOADING = 1, SLOT_LOADED = 2, SLOT_WAITING = 3, SLOT_STORING = 4 };
+constexpr int PENDING_MAX = 32;           // scanned tiles of one CTA that may wait for their prefix
+constexpr uint32_t HEAD_MAX = 2048;       // segmented scan: longest head patched in global memory
+
+// Bulk-store groups complete in order; waits for all but the newest `newer` groups to be
+// complete (written, not only read).
+__device__ __forceinline__ void bulk_wait_all_but(uint32_t newer) {
+  if (newer == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  else if (newer == 1) asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+  else if (newer == 2) asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");
+  else asm volatile("cp.async.bulk.wait_group 3;" ::: "memory");
+}
 
 template <int KIND>
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
@@ -200,11 +222,13 @@ lookback_kernel(const LookbackArgs a) {
   using Op = typename std::conditional<KIND == K_SEGSCAN_F32, OpSegAddF32, OpAddU32>::type;
   extern __shared__ __align__(128) unsigned char s_stages[];
   __shared__ __align__(8) uint64_t s_bar[NST];
-  __shared__ uint32_t s_tile_of[NST];      // tile in the slot
-  __shared__ uint32_t s_meta[NST];         // after the scan: segmented scan = index of the first segment
-                                           // start in the tile (SCAN_TILE if none); compaction = selected count
+  // bookkeeping, touched by thread 0 only (shared memory because it is indexed dynamically)
+  __shared__ uint32_t s_slot_state[NST], s_slot_tile[NST], s_slot_phase[NST];
+  __shared__ uint32_t s_lq[NST];                       // slots in the order their tiles were claimed
+  __shared__ uint32_t s_pq_tile[PENDING_MAX], s_pq_info[PENDING_MAX], s_pq_seq[PENDING_MAX];
+  // per-action communication
   __shared__ uint32_t s_wv[SCAN_WARPS], s_wf[SCAN_WARPS], s_ff[SCAN_WARPS];
-  __shared__ uint32_t s_act, s_slot, s_pv, s_pf, s_role, s_agg_v, s_agg_f;
+  __shared__ uint32_t s_act, s_slot, s_tile_id, s_info, s_pv, s_pf, s_role, s_agg_v, s_agg_f, s_fix, s_fix_tile;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (ld_failure(a.failure) != FAIL_NONE) return;
@@ -226,28 +250,24 @@ lookback_kernel(const LookbackArgs a) {
     }
     return;
   }
-  // (a grid of one CTA has no propagator: the single worker resolves prefixes itself, below)
+  // A grid of one CTA has no propagator: the lone worker carries the running prefix itself.
   const bool self_propagate = (gridDim.x == 1);
-
   const uint32_t workers = self_propagate ? 1u : gridDim.x - 1;
   const uint32_t last_draw = nt + workers - 1;   // every worker ends on exactly one invalid ticket
   const bool ptr_aligned = aligned16(a.in) && (KIND == K_FILTER || KIND == K_PARTITION || aligned16(a.out)) &&
                            (KIND != K_SEGSCAN_F32 || aligned16(a.flags));
   auto tile_is_bulk = [&](uint32_t t) -> bool { return ptr_aligned && ((int64_t)(t + 1) * SCAN_TILE <= a.n); };
-  auto issue_load = [&](int s, uint32_t t) {   // one thread
-    unsigned char *st = s_stages + s * SB;
-    const int64_t base = (int64_t)t * SCAN_TILE;
-    mbar_expect_tx(&s_bar[s], SB);
-    bulk_g2s(st, reinterpret_cast<const uint32_t *>(a.in) + base, SCAN_TILE * 4, &s_bar[s]);
-    if (KIND == K_SEGSCAN_F32) bulk_g2s(st + SCAN_TILE * 4, a.flags + base, SCAN_TILE, &s_bar[s]);
-  };
 
-  // Ring bookkeeping, thread 0 only.  Slots are used in FIFO order:
-  //   filled .. scanned .. finished .. stored;  counters only grow, slot = counter % NST.
-  uint32_t n_filled = 0, n_scanned = 0, n_finished = 0, n_refillable = 0;
+  // thread 0's private counters
+  uint32_t lq_head = 0, lq_tail = 0;          // claimed tiles not yet scanned: s_lq[lq_head % NST ..]
+  uint32_t pq_head = 0, pq_tail = 0;          // scanned tiles waiting for their prefix
+  uint32_t stores_committed = 0;              // bulk-store groups committed so far
+  uint32_t last_store_slot = 0;
+  uint32_t n_storing = 0, store_age = 0;      // slots in SLOT_STORING; decisions since the last store was committed
+  bool in_hand = false;                       // a ticket has been drawn but not yet given a stage
+  uint32_t next_ticket = 0;
   bool exhausted = false;
-  uint32_t phases = 0;      // bit s: parity of the next completion of slot s's barrier (thread 0's view)
-  uint32_t self_v = a.carry_in, self_f = 0;     // running prefix when the CTA propagates for itself
+  uint32_t self_v = a.carry_in, self_f = 0;   // running prefix of a lone worker
   uint32_t idle = 0;
   // The status word of the oldest waiting tile's predecessor is read at the START of every
   // action and looked at when the action is over, so the L2 round trip overlaps the work.
@@ -255,7 +275,7 @@ lookback_kernel(const LookbackArgs a) {
   uint32_t polled_idx = 0xffffffffu;
 
   if (tid == 0) {
-    for (int s = 0; s < NST; s++) mbar_init(&s_bar[s], 1);
+    for (int s = 0; s < NST; s++) { mbar_init(&s_bar[s], 1); s_slot_state[s] = SLOT_FREE; s_slot_phase[s] = 0; }
     fence_mbar_init();
     if (self_propagate && KIND == K_SCAN_I32 && a.carry_vals != nullptr)
       for (int q = 0; q < a.carry_n; q++) self_v += a.carry_vals[q];
@@ -265,52 +285,122 @@ lookback_kernel(const LookbackArgs a) {
   while (true) {
     // ================= thread 0 decides what the CTA does next =================
     if (tid == 0) {
-      // refill: a slot is free once the bulk store that read it has finished; stores finish
-      // in order, so "all but the newest" is known after wait_group.read 1 (done at FINISH)
-      while (!exhausted && n_filled < n_refillable + NST && n_filled - n_finished < NST) {
-        const uint32_t t = atomicAdd(&a.ticket[0], 1u);
-        if (t == last_draw) atomicExch(&a.ticket[0], 0u);
-        if (t >= nt) { exhausted = true; break; }
-        const int s = n_filled % NST;
-        s_tile_of[s] = t;
-        if (tile_is_bulk(t)) issue_load(s, t);
-        n_filled++;
+      // Stages whose bulk store was committed before the action that just ended have had time
+      // to be read; this wait is then (nearly) free.
+      // (stores finish in order: wait_group.read 1 leaves only the newest one possibly reading)
+      if (n_storing > 0 && store_age > 0) {
+        bulk_wait_read0();
+        for (int s = 0; s < NST; s++) if (s_slot_state[s] == SLOT_STORING) s_slot_state[s] = SLOT_FREE;
+        n_storing = 0;
+      } else if (n_storing >= 2) {
+        bulk_wait_read1();
+        for (int s = 0; s < NST; s++)
+          if (s_slot_state[s] == SLOT_STORING && s != (int)last_store_slot) s_slot_state[s] = SLOT_FREE;
+        n_storing = 1;
       }
+      store_age++;
+      // Put the ticket drawn during the last action (if any) into a free stage.
+      auto place_ticket = [&]() {
+        const uint32_t t = next_ticket;
+        if (t == last_draw) { atomicExch(&a.ticket[0], 0u); }   // rewind for the next launch (once)
+        if (t >= nt) { exhausted = true; in_hand = false; return; }
+        int fs = -1;
+        for (int s = 0; s < NST; s++) if (s_slot_state[s] == SLOT_FREE) { fs = s; break; }
+        if (fs < 0) return;
+        in_hand = false;
+        s_slot_state[fs] = SLOT_LOADING; s_slot_tile[fs] = t;
+        TRACE(t, 4);
+#ifdef FB_TRACE
+        if (t < 32768u) g_trace[t * 8 + 6] = blockIdx.x;
+#endif
+        if (tile_is_bulk(t)) {
+          unsigned char *st = s_stages + fs * SB;
+          const int64_t tb = (int64_t)t * SCAN_TILE;
+          mbar_expect_tx(&s_bar[fs], SB);
+          bulk_g2s(st, reinterpret_cast<const uint32_t *>(a.in) + tb, SCAN_TILE * 4, &s_bar[fs]);
+          if (KIND == K_SEGSCAN_F32) bulk_g2s(st + SCAN_TILE * 4, a.flags + tb, SCAN_TILE, &s_bar[fs]);
+        }
+        s_lq[lq_tail % NST] = fs; lq_tail++;
+      };
+      if (in_hand) place_ticket();
       uint32_t act = ACT_IDLE, slot = 0;
-      // oldest tile waiting for its prefix?
-      if (n_finished < n_scanned) {
-        const int s = n_finished % NST;
-        const uint32_t t = s_tile_of[s];
-        if (self_propagate) { s_pv = self_v; s_pf = self_f; act = ACT_FINISH; slot = s; }
-        else if (t == 0) { s_pv = a.carry_in; s_pf = 0;
-          if (KIND == K_SCAN_I32 && a.carry_vals != nullptr) for (int q = 0; q < a.carry_n; q++) s_pv += a.carry_vals[q];
-          act = ACT_FINISH; slot = s; }
-        else {
-          // use the word read during the previous action if it is the right one and already a
-          // prefix; read afresh only when there is nothing to scan meanwhile
-          uint64_t w = (polled_idx == t - 1) ? polled_w : 0ull;
-          const bool can_scan = n_scanned < n_filled;
-          if (status_state(w, a.epoch) != ST_PREFIX && !can_scan) w = ld_status(&a.status[t - 1]);
-          if (status_state(w, a.epoch) == ST_PREFIX) {
-            s_pv = status_value(w); s_pf = Op::kHasFlag ? status_flag(w) : 0u;
-            act = ACT_FINISH; slot = s;
-          }
+      // is the next claimed tile loaded?
+      int scan_slot = -1;
+      if (lq_head != lq_tail) {
+        const int s = (int)s_lq[lq_head % NST];
+        if (s_slot_state[s] == SLOT_LOADING &&
+            (!tile_is_bulk(s_slot_tile[s]) || mbar_try_wait(&s_bar[s], s_slot_phase[s]))) {
+          if (tile_is_bulk(s_slot_tile[s])) s_slot_phase[s] ^= 1u;   // the barrier's next completion has the other parity
+          s_slot_state[s] = SLOT_LOADED;
+          TRACE(s_slot_tile[s], 5);
+        }
+        if (s_slot_state[s] == SLOT_LOADED) scan_slot = s;
+      }
+      // Oldest tile waiting for its prefix: is the prefix there?  (The inclusive prefix of the
+      // predecessor; for the segmented operator a predecessor that contains a segment start
+      // supplies it with its aggregate alone.)
+      bool have = false;
+      uint32_t ptile = 0, pinfo = 0;
+      if (pq_head != pq_tail) {
+        const uint32_t e = pq_head % PENDING_MAX;
+        ptile = s_pq_tile[e]; pinfo = s_pq_info[e];
+        if (self_propagate) { s_pv = self_v; s_pf = self_f; have = true; }
+        else if (ptile == 0) {
+          uint32_t seed = a.carry_in;
+          if (KIND == K_SCAN_I32 && a.carry_vals != nullptr) for (int q = 0; q < a.carry_n; q++) seed += a.carry_vals[q];
+          s_pv = seed; s_pf = 0; have = true;
+        } else {
+          // the word read during the previous action, or a fresh read when there is nothing to scan
+          uint64_t w = (polled_idx == ptile - 1) ? polled_w : 0ull;
+          auto usable = [&](uint64_t ww) -> bool {
+            const uint32_t st = status_state(ww, a.epoch);
+            return st == ST_PREFIX || (Op::kHasFlag && st == ST_AGG && status_flag(ww));
+          };
+          if (!usable(w) && scan_slot < 0) w = ld_status(&a.status[ptile - 1]);
+          if (usable(w)) { s_pv = status_value(w); s_pf = Op::kHasFlag ? status_flag(w) : 0u; have = true; }
         }
       }
-      // otherwise: next loaded tile ready to be scanned?
-      if (act == ACT_IDLE && n_scanned < n_filled) {
-        const int s = n_scanned % NST;
-        const uint32_t t = s_tile_of[s];
-        if (!tile_is_bulk(t)) { act = ACT_SCAN; slot = s; }
-        else if (mbar_try_wait(&s_bar[s], (phases >> s) & 1u)) { phases ^= (1u << s); act = ACT_SCAN; slot = s; }
+      s_fix = 0;
+      if (scan_slot >= 0 && !(have && !(pinfo & 0x80000000u))) {
+        // Scan, unless a tile that still sits in a stage can be finished: finishing frees the
+        // stage for the next load (measured: better than scanning first).
+        act = ACT_SCAN; slot = (uint32_t)scan_slot; s_tile_id = s_slot_tile[scan_slot];
+        if (have && (pinfo & 0x80000000u)) {
+          // a stored tile's head can be patched along the way (its loads overlap the scan)
+          const uint32_t newer = stores_committed - s_pq_seq[pq_head % PENDING_MAX];
+          bulk_wait_all_but(newer > 3 ? 3 : newer);
+          s_fix = 1; s_fix_tile = ptile; s_info = pinfo;
+        }
+      } else if (have) {
+        s_tile_id = ptile; s_info = pinfo;
+        if (pinfo & 0x80000000u) {             // already stored: patch its head in global memory
+          act = ACT_FIXUP;
+          const uint32_t newer = stores_committed - s_pq_seq[pq_head % PENDING_MAX];
+          bulk_wait_all_but(newer > 3 ? 3 : newer);
+        } else { act = ACT_FINISH; slot = pinfo & 0xffu; }
       }
       if (act == ACT_IDLE) {
-        if (exhausted && n_finished == n_filled) act = ACT_DONE;
+        if (exhausted && !in_hand && pq_head == pq_tail && lq_head == lq_tail) act = ACT_DONE;
         else {
-          idle++;
-          if ((idle & 255u) == 0 && ld_failure(a.failure) != FAIL_NONE) act = ACT_FAIL;
-          if (idle >= WAIT_MAX_ROUNDS) { atomicCAS(a.failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT); act = ACT_FAIL; }
-          if (act == ACT_IDLE) __nanosleep(idle < 8 ? 20 : 100);
+          // nothing to compute: this is the time for the blocking bits of housekeeping
+          bool did = false;
+          if (n_storing > 0) {
+            bulk_wait_read0();
+            for (int s = 0; s < NST; s++) if (s_slot_state[s] == SLOT_STORING) s_slot_state[s] = SLOT_FREE;
+            n_storing = 0; did = true;
+          }
+          if (!in_hand && !exhausted && pq_tail - pq_head + (lq_tail - lq_head) < PENDING_MAX) {
+            bool any_free = false;
+            for (int s = 0; s < NST; s++) any_free |= (s_slot_state[s] == SLOT_FREE);
+            if (any_free) { next_ticket = atomicAdd(&a.ticket[0], 1u); in_hand = true; }
+          }
+          if (in_hand) { place_ticket(); did = did || !in_hand; }
+          if (!did) {
+            idle++;
+            if ((idle & 255u) == 0 && ld_failure(a.failure) != FAIL_NONE) act = ACT_FAIL;
+            if (idle >= WAIT_MAX_ROUNDS) { atomicCAS(a.failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT); act = ACT_FAIL; }
+            if (act == ACT_IDLE && idle > 4) __nanosleep(idle < 64 ? 20 : 100);
+          }
         }
       } else idle = 0;
       s_act = act; s_slot = slot;
@@ -323,28 +413,37 @@ lookback_kernel(const LookbackArgs a) {
       // drain: bulk stores must finish reading shared memory; loads in flight are awaited with a limit
       if (tid == 0) {
         bulk_wait_read0();
-        for (uint32_t c = n_scanned; c < n_filled; c++) {
-          const int q = c % NST;
-          if (tile_is_bulk(s_tile_of[q])) { (void)mbar_wait_bounded(&s_bar[q], (phases >> q) & 1u, 1u << 16); phases ^= (1u << q); }
+        for (uint32_t c = lq_head; c != lq_tail; c++) {
+          const int q = (int)s_lq[c % NST];
+          if (s_slot_state[q] == SLOT_LOADING && tile_is_bulk(s_slot_tile[q])) (void)mbar_wait_bounded(&s_bar[q], s_slot_phase[q], 1u << 16);
         }
       }
       return;
     }
     if (act == ACT_IDLE) { __syncthreads(); continue; }
+    const uint32_t tile = s_tile_id;
+    if (tid == 0 && !in_hand && !exhausted && pq_tail - pq_head + (lq_tail - lq_head) < PENDING_MAX) {
+      // Draw the next ticket now if a stage is (or is about to be) free: the atomic's round trip
+      // overlaps the action, and the tile gets its stage at the next decision.
+      bool room = (act == ACT_FINISH) || n_storing > 0;
+      for (int q = 0; q < NST; q++) room |= (s_slot_state[q] == SLOT_FREE);
+      if (room) {
+        next_ticket = atomicAdd(&a.ticket[0], 1u);     // looked at only when the action is over
+        in_hand = true;
+      }
+    }
     if (tid == 0 && !self_propagate) {
       // which tile will be the oldest one waiting once this action is over?
-      uint32_t c = n_finished + (act == ACT_FINISH ? 1u : 0u);
-      const uint32_t scanned_after = n_scanned + (act == ACT_SCAN ? 1u : 0u);
       polled_idx = 0xffffffffu;
-      if (c < scanned_after) {
-        const uint32_t t = s_tile_of[c % NST];
-        if (t > 0) { polled_idx = t - 1; polled_w = ld_status(&a.status[t - 1]); }
-      }
+      uint32_t t = 0xffffffffu;
+      const uint32_t h = pq_head + ((act == ACT_FINISH || act == ACT_FIXUP || s_fix) ? 1u : 0u);
+      if (h != pq_tail) t = s_pq_tile[h % PENDING_MAX];
+      else if (act == ACT_SCAN) t = tile;
+      if (t != 0xffffffffu && t > 0) { polled_idx = t - 1; polled_w = ld_status(&a.status[t - 1]); }
     }
 
     unsigned char *stage = s_stages + s * SB;
     uint32_t *s_tile = reinterpret_cast<uint32_t *>(stage);
-    const uint32_t tile = s_tile_of[s];
     const int64_t base = (int64_t)tile * SCAN_TILE;
     const int count = (int)((a.n - base) < SCAN_TILE ? (a.n - base) : SCAN_TILE);
     const bool bulk = tile_is_bulk(tile);
@@ -352,6 +451,22 @@ lookback_kernel(const LookbackArgs a) {
     if (act == ACT_SCAN) {
       // ================= local scan of a freshly loaded tile =================
       TRACE(tile, 0);
+      // piggy-backed fix-up of an already stored tile: read its head now, write it at the end
+      const bool fix = (KIND == K_SEGSCAN_F32) && s_fix;
+      float fixv[HEAD_MAX / SCAN_THREADS];
+      float *fixg = nullptr;
+      uint32_t fix_head = 0;
+      float fix_add = 0.f;
+      if (fix) {
+        fix_head = s_info & 0x7fffffffu;
+        fix_add = __uint_as_float(s_pv);
+        fixg = reinterpret_cast<float *>(a.out) + (int64_t)s_fix_tile * SCAN_TILE;
+#pragma unroll
+        for (int q = 0; q < (int)(HEAD_MAX / SCAN_THREADS); q++) {
+          const uint32_t i = tid + q * SCAN_THREADS;
+          fixv[q] = (i < fix_head) ? __uint_as_float((uint32_t)ld_stream_relaxed(&fixg[i])) : 0.f;
+        }
+      }
       if (!bulk) {
         const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
         for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS) s_tile[i] = (i < count) ? gin[i] : 0u;
@@ -437,7 +552,7 @@ lookback_kernel(const LookbackArgs a) {
         thv = bv + incl - own_v;
       }
 
-      // publish the tile aggregate (or keep the running prefix when there is no propagator)
+      // publish the tile aggregate as early as possible
       if (tid == 0) {
         if (self_propagate) { s_agg_v = tv; s_agg_f = tf; }   // folded into the running prefix when the tile is finished
         else st_status(&a.status[tile], pack_status(tv, a.epoch, tf, ST_AGG));
@@ -473,6 +588,7 @@ lookback_kernel(const LookbackArgs a) {
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) { uint32_t t2 = __shfl_xor_sync(kFull, ff, o); ff = t2 < ff ? t2 : ff; }
           if (lane == 0) s_ff[warp] = ff;
+          fence_proxy_async_smem();            // the stage may be bulk-stored right after the barrier
         }
       } else {
         // compact inside the stage: selected keys first, in order, then the rejected ones
@@ -486,23 +602,47 @@ lookback_kernel(const LookbackArgs a) {
           else if (KIND == K_PARTITION && (first_local + q < count)) s_tile[f_pos++] = x[q];
         }
       }
+      if (fix) {
+#pragma unroll
+        for (int q = 0; q < (int)(HEAD_MAX / SCAN_THREADS); q++) {
+          const uint32_t i = tid + q * SCAN_THREADS;
+          if (i < fix_head) fixg[i] = fix_add + fixv[q];
+        }
+      }
       __syncthreads();
       if (tid == 0) {
-        uint32_t meta = tv;
+        if (fix) pq_head++;
+        uint32_t info = (uint32_t)s;            // waits in its stage
+        uint32_t state = SLOT_WAITING;
         if (KIND == K_SEGSCAN_F32) {
-          meta = SCAN_TILE;
-          for (int wq = 0; wq < SCAN_WARPS; wq++) meta = s_ff[wq] < meta ? s_ff[wq] : meta;
+          uint32_t head = SCAN_TILE;
+          for (int wq = 0; wq < SCAN_WARPS; wq++) head = s_ff[wq] < head ? s_ff[wq] : head;
+          if (bulk && head <= HEAD_MAX && !self_propagate) {
+            // Only the `head` elements before the first segment start depend on the incoming
+            // prefix: write the tile out now and patch those few in global memory later, so
+            // that the stage is free again at once.
+            bulk_s2g(reinterpret_cast<uint32_t *>(a.out) + base, s_tile, SCAN_TILE * 4);
+            bulk_commit();
+            stores_committed++;
+            state = SLOT_STORING; n_storing++; store_age = 0; last_store_slot = (uint32_t)s;
+            info = 0x80000000u | head;
+          } else {
+            info = (uint32_t)s | (head << 8);    // finish from the stage: prefix applies to [0, head)
+          }
+        } else if (KIND == K_FILTER || KIND == K_PARTITION) {
+          info = (uint32_t)s | (tv << 8);        // selected count of the tile
         }
-        s_meta[s] = meta;
-        n_scanned++;
+        s_slot_state[s] = state;
+        const uint32_t e = pq_tail % PENDING_MAX;
+        s_pq_tile[e] = tile; s_pq_info[e] = info; s_pq_seq[e] = stores_committed;
+        pq_tail++; lq_head++;
       }
       TRACE(tile, 1);
-      // (no barrier needed here: the next iteration starts with thread 0's decision + barrier)
-    } else {
-      // ================= finish: apply the incoming prefix and write out =================
+    } else if (act == ACT_FINISH) {
+      // ================= finish from the stage: apply the incoming prefix and write out =================
       TRACE(tile, 2);
-      const uint32_t pv_in = s_pv, pf_in = s_pf;
-      (void)pf_in;
+      const uint32_t pv_in = s_pv;
+      const uint32_t extra = s_info >> 8;       // segmented scan: head length; compaction: selected count
       if (KIND == K_SCAN_I32) {
         int4 *p4 = reinterpret_cast<int4 *>(s_tile);
 #pragma unroll
@@ -512,10 +652,9 @@ lookback_kernel(const LookbackArgs a) {
           p4[tid + j * SCAN_THREADS] = v;
         }
       } else if (KIND == K_SEGSCAN_F32) {
-        const uint32_t upto = s_meta[s];
         const float add = __uint_as_float(pv_in);
         float *pf32 = reinterpret_cast<float *>(s_tile);
-        for (uint32_t i = tid; i < upto; i += SCAN_THREADS) pf32[i] = add + pf32[i];
+        for (uint32_t i = tid; i < extra; i += SCAN_THREADS) pf32[i] = add + pf32[i];
       }
       if (KIND == K_SCAN_I32 || KIND == K_SEGSCAN_F32) {
         uint32_t *gout = reinterpret_cast<uint32_t *>(a.out) + base;
@@ -525,17 +664,17 @@ lookback_kernel(const LookbackArgs a) {
           if (tid == 0) {
             bulk_s2g(gout, s_tile, SCAN_TILE * 4);
             bulk_commit();
-            bulk_wait_read1();                 // every store but this one has finished reading
-            n_refillable = n_finished;         // slots of tiles finished before this one are free
+            stores_committed++;
+            s_slot_state[s] = SLOT_STORING; n_storing++; store_age = 0; last_store_slot = (uint32_t)s;
           }
         } else {
           __syncthreads();
           for (int i = tid; i < count; i += SCAN_THREADS) gout[i] = s_tile[i];
           __syncthreads();
-          if (tid == 0) { bulk_wait_read0(); n_refillable = n_finished + 1; }
+          if (tid == 0) s_slot_state[s] = SLOT_FREE;
         }
       } else {
-        const uint32_t tile_true = s_meta[s];
+        const uint32_t tile_true = extra;
         const int64_t true_before = (int64_t)pv_in;       // selected keys in earlier tiles
         uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
         for (uint32_t i = tid; i < tile_true; i += SCAN_THREADS) dst[i] = s_tile[i];
@@ -546,7 +685,7 @@ lookback_kernel(const LookbackArgs a) {
         }
         if (tile == nt - 1 && tid == 0) *a.d_count = true_before + (int64_t)tile_true;
         __syncthreads();
-        if (tid == 0) n_refillable = n_finished + 1;
+        if (tid == 0) s_slot_state[s] = SLOT_FREE;
       }
       if (tid == 0) {
         if (self_propagate) {
@@ -555,8 +694,24 @@ lookback_kernel(const LookbackArgs a) {
           self_v = nv; self_f = nf2;
           st_status(&a.status[tile], pack_status(nv, a.epoch, nf2, ST_PREFIX));   // the shard summary reads the last one
         }
-        n_finished++;
+        pq_head++;
       }
+      TRACE(tile, 3);
+    } else {
+      // ================= fix-up: the tile was stored already; add the prefix to its head =================
+      TRACE(tile, 2);
+      if (KIND == K_SEGSCAN_F32) {
+        const uint32_t head = s_info & 0x7fffffffu;
+        const float add = __uint_as_float(s_pv);
+        float *g = reinterpret_cast<float *>(a.out) + base;
+        // thread 0 waited for the tile's bulk store to complete before the barrier above
+        for (uint32_t i = tid; i < head; i += SCAN_THREADS) {
+          const float old = __uint_as_float((uint32_t)ld_stream_relaxed(&g[i]));
+          g[i] = add + old;
+        }
+      }
+      __syncthreads();
+      if (tid == 0) pq_head++;
       TRACE(tile, 3);
     }
   }
