@@ -132,7 +132,7 @@ class Group:
         self.local.reduce_i32_into(xs, buf)
         with self.local.collective_stream():
             dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.pg)
-        return int(buf.item())
+            return int(buf.item())
 
     # -- scan (+) i32: totals first, then one seeded pass
     def scan_i32(self, xs):
@@ -177,9 +177,12 @@ class Group:
         return sel, rej, sel_off, rej_off, total_sel
 
     def _gather_counts(self, vals):
-        mine = self.local.empty(len(vals), torch.int64)
-        mine.copy_(torch.tensor(vals, dtype=torch.int64))
-        allc = self.local.empty(len(vals) * self.world, torch.int64)
+        # everything on the collective stream: the host-to-device copy of the counts must be
+        # ordered before the gather, and the read-back after it
         with self.local.collective_stream():
+            mine = self.local.empty(len(vals), torch.int64)
+            mine.copy_(torch.tensor(vals, dtype=torch.int64))
+            allc = self.local.empty(len(vals) * self.world, torch.int64)
             dist.all_gather_into_tensor(allc, mine, group=self.pg)
-        return allc.cpu().numpy().reshape(self.world, len(vals))
+            host = allc.cpu()
+        return host.numpy().reshape(self.world, len(vals))
