@@ -34,7 +34,9 @@ constexpr int B_STAGE_BYTES = BK * BN * 2;            // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int B_NBLOCK_BYTES = BK * 64 * 2;           // one 64-wide slab of N: 8 KiB
 constexpr int BMM_THREADS = 192;
-constexpr int BMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_PITCH = 36;                         // floats per staged row: 32 + 4 of padding (conflict-free both ways)
+constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;     // one 32 x 32 f32 chunk per epilogue warp
+constexpr int BMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------------------
@@ -115,6 +117,7 @@ bmm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   BmmBarriers *bars = reinterpret_cast<BmmBarriers *>(smem + STAGES * STAGE_BYTES);
+  float *epi = reinterpret_cast<float *>(smem + STAGES * STAGE_BYTES + 256);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
@@ -207,28 +210,44 @@ bmm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // warp-uniform outcome: the TMEM loads below need the whole warp
         if (!__all_sync(kFull, mbar_wait_bounded(&bars->tmem_full[acc], acc_ph))) { ok = false; break; }
         tc_fence_after();
-        const int row = m0 + quarter * 32 + lane;
-        float *crow = C + ((int64_t)batch * M + row) * (int64_t)N + n0;
+        // A thread receives 32 consecutive columns of ONE row from TMEM; written out like
+        // that, every store instruction would touch 32 different cache lines.  The chunk is
+        // therefore turned through shared memory so that 8 lanes write one full 128-byte line.
+        float *stg = epi + (warp - 2) * 32 * EPI_PITCH;
+        const int rsub = lane >> 3, c4 = (lane & 7) * 4;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; c++) {
           uint32_t v[32];
           const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c * 32;
           tmem_ld_32x32(taddr, v);
           tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * q]); o.y = __uint_as_float(v[4 * q + 1]);
+            o.z = __uint_as_float(v[4 * q + 2]); o.w = __uint_as_float(v[4 * q + 3]);
+            *reinterpret_cast<float4 *>(stg + lane * EPI_PITCH + 4 * q) = o;
+          }
+          __syncwarp();
           const int col0 = n0 + c * 32;
-          if (row < M) {
-            if (vec_ok && col0 + 32 <= N) {
 #pragma unroll
-              for (int q = 0; q < 8; q++) {
-                int4 o; o.x = v[4 * q]; o.y = v[4 * q + 1]; o.z = v[4 * q + 2]; o.w = v[4 * q + 3];
-                *reinterpret_cast<int4 *>(crow + c * 32 + 4 * q) = o;
+          for (int p = 0; p < 8; p++) {
+            const int rloc = p * 4 + rsub;
+            const int row = m0 + quarter * 32 + rloc;
+            const float4 o = *reinterpret_cast<const float4 *>(stg + rloc * EPI_PITCH + c4);
+            if (row < M) {
+              float *dst = C + ((int64_t)batch * M + row) * (int64_t)N + col0 + c4;
+              if (vec_ok && col0 + c4 + 4 <= N) {
+                asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
+              } else {
+                if (col0 + c4 + 0 < N) dst[0] = o.x;
+                if (col0 + c4 + 1 < N) dst[1] = o.y;
+                if (col0 + c4 + 2 < N) dst[2] = o.z;
+                if (col0 + c4 + 3 < N) dst[3] = o.w;
               }
-            } else {
-#pragma unroll
-              for (int q = 0; q < 32; q++)
-                if (col0 + q < N) crow[c * 32 + q] = __uint_as_float(v[q]);
             }
           }
+          __syncwarp();
         }
         tc_fence_before();
         mbar_arrive(&bars->tmem_empty[acc]);
