@@ -198,38 +198,78 @@ cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float
 }
 
 // ---- irregular segmented sum: out[s] = sum xs[offsets[s] .. offsets[s+1]) ------------------
-// One warp per segment, persistent over the segments.  Segment starts are arbitrary,
-// so loads are 4-byte but contiguous across the warp; four in flight per lane.  Offsets
-// are clamped to [0,n], so a malformed offsets array cannot cause an out-of-range read.
+// One warp per segment, persistent over the segments, two segments at a time: the chain
+// offsets -> data -> shuffle tree -> store is latency-bound per segment, so a warp issues
+// the loads of two segments (8 + 8 per lane, predicated on the segment length) before it
+// reduces either, and the offsets of its next pair are already in flight.  Segment starts
+// are arbitrary, so loads are 4-byte, contiguous across the warp.  Offsets are clamped to
+// [0,n], so a malformed offsets array cannot cause an out-of-range read.
+constexpr int SEG_U = 8;   // loads per lane and segment issued up front (covers 256 elements)
+
+__device__ __forceinline__ void clamp_range(int64_t &lo, int64_t &hi, int64_t n) {
+  lo = lo < 0 ? 0 : (lo > n ? n : lo);
+  hi = hi < lo ? lo : (hi > n ? n : hi);
+}
+
 __global__ void __launch_bounds__(RED_THREADS)
 segreduce_f32_kernel(const int64_t *__restrict__ offsets, int64_t nseg, const float *__restrict__ xs, int64_t n,
                      float *__restrict__ out) {
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = ((int64_t)blockIdx.x * RED_THREADS + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * RED_THREADS) >> 5;
-  for (int64_t s = warp_global; s < nseg; s += nwarps) {
-    int64_t lo = offsets[s], hi = offsets[s + 1];
-    lo = lo < 0 ? 0 : (lo > n ? n : lo);
-    hi = hi < lo ? lo : (hi > n ? n : hi);
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    int64_t i = lo + lane;
-    for (; i + 96 < hi; i += 128) {
-      float q0 = __int_as_float(ld_stream_b32(xs + i));
-      float q1 = __int_as_float(ld_stream_b32(xs + i + 32));
-      float q2 = __int_as_float(ld_stream_b32(xs + i + 64));
-      float q3 = __int_as_float(ld_stream_b32(xs + i + 96));
-      s0 += q0; s1 += q1; s2 += q2; s3 += q3;
+  int64_t sA = warp_global, sB = warp_global + nwarps;
+  int64_t loA = 0, hiA = 0, loB = 0, hiB = 0;
+  if (sA < nseg) { loA = offsets[sA]; hiA = offsets[sA + 1]; }
+  if (sB < nseg) { loB = offsets[sB]; hiB = offsets[sB + 1]; }
+  while (sA < nseg) {
+    const int64_t nA = sA + 2 * nwarps, nB = sB + 2 * nwarps;
+    int64_t nloA = 0, nhiA = 0, nloB = 0, nhiB = 0;
+    if (nA < nseg) { nloA = offsets[nA]; nhiA = offsets[nA + 1]; }
+    if (nB < nseg) { nloB = offsets[nB]; nhiB = offsets[nB + 1]; }
+    clamp_range(loA, hiA, n);
+    clamp_range(loB, hiB, n);
+    float a[SEG_U], b[SEG_U];
+#pragma unroll
+    for (int u = 0; u < SEG_U; u++) {
+      const int64_t ia = loA + lane + 32 * u, ib = loB + lane + 32 * u;
+      a[u] = (ia < hiA) ? __int_as_float(ld_stream_b32(xs + ia)) : 0.f;
+      b[u] = (ib < hiB) ? __int_as_float(ld_stream_b32(xs + ib)) : 0.f;
     }
-    for (; i < hi; i += 32) s0 += __int_as_float(ld_stream_b32(xs + i));
-    float t = warp_sum_down((s0 + s1) + (s2 + s3));
-    if (lane == 0) out[s] = t;
+    float tA = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+    float tB = ((b[0] + b[1]) + (b[2] + b[3])) + ((b[4] + b[5]) + (b[6] + b[7]));
+    // the rest of segments longer than 256 elements
+    for (int64_t i = loA + lane + 32 * SEG_U; i < hiA; i += 128) {
+      const float q0 = __int_as_float(ld_stream_b32(xs + i));
+      const float q1 = (i + 32 < hiA) ? __int_as_float(ld_stream_b32(xs + i + 32)) : 0.f;
+      const float q2 = (i + 64 < hiA) ? __int_as_float(ld_stream_b32(xs + i + 64)) : 0.f;
+      const float q3 = (i + 96 < hiA) ? __int_as_float(ld_stream_b32(xs + i + 96)) : 0.f;
+      tA += (q0 + q1) + (q2 + q3);
+    }
+    for (int64_t i = loB + lane + 32 * SEG_U; i < hiB; i += 128) {
+      const float q0 = __int_as_float(ld_stream_b32(xs + i));
+      const float q1 = (i + 32 < hiB) ? __int_as_float(ld_stream_b32(xs + i + 32)) : 0.f;
+      const float q2 = (i + 64 < hiB) ? __int_as_float(ld_stream_b32(xs + i + 64)) : 0.f;
+      const float q3 = (i + 96 < hiB) ? __int_as_float(ld_stream_b32(xs + i + 96)) : 0.f;
+      tB += (q0 + q1) + (q2 + q3);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      tA += __shfl_down_sync(kFull, tA, o);
+      tB += __shfl_down_sync(kFull, tB, o);
+    }
+    if (lane == 0) {
+      out[sA] = tA;
+      if (sB < nseg) out[sB] = tB;
+    }
+    sA = nA; sB = nB; loA = nloA; hiA = nhiA; loB = nloB; hiB = nhiB;
   }
 }
 
 cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
                                  int num_sms, cudaStream_t stream) {
   if (nseg <= 0) return cudaSuccess;
-  int64_t want = (nseg * 32 + RED_THREADS - 1) / RED_THREADS;
+  int64_t want = (nseg * 16 + RED_THREADS - 1) / RED_THREADS;     // a warp takes two segments at a time
+  if (want < 1) want = 1;
   int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
   segreduce_f32_kernel<<<blocks, RED_THREADS, 0, stream>>>(offsets, nseg, xs, n, out);
   return cudaGetLastError();
