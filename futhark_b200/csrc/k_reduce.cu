@@ -270,7 +270,19 @@ cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const flo
   if (nseg <= 0) return cudaSuccess;
   int64_t want = (nseg * 16 + RED_THREADS - 1) / RED_THREADS;     // a warp takes two segments at a time
   if (want < 1) want = 1;
-  int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
+  // persistent warps: exactly what is resident at once, so that no CTA waits for a second wave
+  static int occ_dev[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (occ_dev[dev] == 0) {
+    int occ = 0;
+    cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, segreduce_f32_kernel, RED_THREADS, 0);
+    if (err != cudaSuccess) return err;
+    occ_dev[dev] = occ < 1 ? 1 : occ;
+  }
+  const int64_t resident = (int64_t)num_sms * occ_dev[dev];
+  int blocks = (int)(want < resident ? want : resident);
   segreduce_f32_kernel<<<blocks, RED_THREADS, 0, stream>>>(offsets, nseg, xs, n, out);
   return cudaGetLastError();
 }
