@@ -55,16 +55,17 @@ namespace fb {
 
 constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_WARPS = SCAN_THREADS / 32;
-constexpr int SCAN_V = 4;                                 // 16-byte vectors per thread
-constexpr int SCAN_TILE = SCAN_THREADS * SCAN_V * 4;      // 4096 elements
+constexpr int SCAN_V = 5;                                 // 16-byte vectors per thread: odd, see the kernel
+constexpr int SCAN_ITEMS = SCAN_V * 4;                    // consecutive elements per thread
+constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;      // 5120 elements
 #ifndef FB_LEAD
 #define FB_LEAD 1024
 #endif
 constexpr int SCAN_LEAD = FB_LEAD;                        // tiles by which visit A runs ahead of visit B (16 MiB of input)
 #ifndef FB_CTAS
-#define FB_CTAS 5
+#define FB_CTAS 4
 #endif
-constexpr int SCAN_CTAS_PER_SM = FB_CTAS;                  // register budget: 65536 / (256 * 5) = 51 -> 48
+constexpr int SCAN_CTAS_PER_SM = FB_CTAS;                  // register budget: 65536 / (256 * 4) = 64
 constexpr int PROP_PER_LANE = 8;                          // status words per lane per round of the propagator
 constexpr int PROP_WINDOW = 32 * PROP_PER_LANE;
 constexpr uint32_t WAIT_MAX_ROUNDS = 1u << 22;            // idle polls before a wait gives up
@@ -226,14 +227,17 @@ struct WorkMap {
 template <int KIND>
 __global__ void __launch_bounds__(SCAN_THREADS, SCAN_CTAS_PER_SM)
 stream_kernel(const LookbackArgs a) {
-  constexpr int V = SCAN_V;
+  constexpr int V = SCAN_V, ITEMS = SCAN_ITEMS;
   constexpr bool SEG = (KIND == K_SEGSCAN_F32);
   constexpr bool COMPACT = (KIND == K_FILTER || KIND == K_PARTITION);
+  constexpr int SB = SCAN_TILE * 4 + (SEG ? SCAN_TILE : 0);      // bytes of a tile buffer
   using Op = typename std::conditional<SEG, OpSegAddF32, OpAddU32>::type;
-  __shared__ uint32_t s_keys[COMPACT ? SCAN_TILE : 1];
+  extern __shared__ __align__(128) unsigned char s_buf[];   // two tile buffers
+  __shared__ __align__(8) uint64_t s_bar[2];
+  __shared__ uint32_t s_item[3];         // work items of iterations it, it+1, it+2 (slot = iteration mod 3)
   __shared__ uint32_t s_wv[2][SCAN_WARPS], s_wf[2][SCAN_WARPS];
-  __shared__ uint32_t s_next[2];         // the work item of the next iteration
   __shared__ uint32_t s_role;
+  __shared__ volatile uint32_t s_fail;
   __shared__ uint32_t s_ev[2], s_ok[2];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -245,6 +249,7 @@ stream_kernel(const LookbackArgs a) {
     const uint32_t r = atomicAdd(&a.ticket[1], 1u);
     if (r == gridDim.x - 1) atomicExch(&a.ticket[1], 0u);     // rewind for the next launch
     s_role = r;
+    s_fail = 0;
   }
   __syncthreads();
   uint32_t seed = a.carry_in;
@@ -262,121 +267,139 @@ stream_kernel(const LookbackArgs a) {
   // Every worker draws work items until it meets one past the end, so the counter ends at
   // total + workers; whoever draws that last value rewinds it for the next launch.
   const uint32_t last_value = wm.total() + workers - 1;
-  const bool in_aligned = aligned16(a.in) && (!SEG || ((((uintptr_t)a.flags) & 3u) == 0));
-  const bool out_aligned = COMPACT || aligned16(a.out);
+  const bool in_bulk = aligned16(a.in) && (!SEG || aligned16(a.flags));
+  const bool out_bulk = !COMPACT && aligned16(a.out);
   uint32_t self_v = seed, self_f = 0;    // thread 0 of a lone CTA: running inclusive prefix
 
+  // The tile of the next iteration is fetched while this iteration computes: one bulk async
+  // copy (TMA) per array into the buffer the iteration before last used, awaited on an
+  // mbarrier.  Work items are therefore drawn two iterations ahead.
+  auto item_is_bulk = [&](uint32_t w, uint32_t &tile) -> bool {
+    if (w >= wm.total()) return false;
+    bool ia;
+    wm.decode(w, ia, tile);
+    return in_bulk && ((int64_t)(tile + 1) * SCAN_TILE <= a.n);
+  };
+  auto arm = [&](int b, uint32_t tile) {   // thread 0: start the copies of a tile into buffer b
+    unsigned char *dst = s_buf + b * SB;
+    const int64_t tb = (int64_t)tile * SCAN_TILE;
+    mbar_expect_tx(&s_bar[b], SB);
+    bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, SCAN_TILE * 4, &s_bar[b]);
+    if (SEG) bulk_g2s(dst + SCAN_TILE * 4, a.flags + tb, SCAN_TILE, &s_bar[b]);
+  };
+  auto draw = [&]() -> uint32_t {          // thread 0
+    const uint32_t w = atomicAdd(&a.ticket[0], 1u);
+    if (w == last_value) atomicExch(&a.ticket[0], 0u);
+    return w;
+  };
+  uint32_t armed = 0;                    // thread 0: buffers with a copy that has not been consumed
   if (tid == 0) {
-    const uint32_t w0 = atomicAdd(&a.ticket[0], 1u);
-    if (w0 == last_value) atomicExch(&a.ticket[0], 0u);
-    s_next[0] = w0;
+    mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1);
+    fence_mbar_init();
+    const uint32_t w0 = draw();
+    const uint32_t w1 = (w0 < wm.total()) ? draw() : 0xffffffffu;   // a worker stops at its first item past the end
+    s_item[0] = w0; s_item[1] = w1;
+    uint32_t t0;
+    if (item_is_bulk(w0, t0)) { arm(0, t0); armed |= 1u; }
   }
   __syncthreads();
-  const int vrow = warp * V;             // this thread's vector in row j: (vrow + j) * 32 + lane
+  uint32_t phases = 0;                   // bit b: parity the next completion of buffer b's barrier will have
 
   for (uint32_t it = 0;; it++) {
     const int par = (int)(it & 1u);
-    const uint32_t w = s_next[par];
+    const uint32_t w = s_item[it % 3];
     if (w >= wm.total()) break;
     bool is_a;
     uint32_t tile;
     wm.decode(w, is_a, tile);
-    uint32_t drawn = 0;
-    if (tid == 0) drawn = atomicAdd(&a.ticket[0], 1u);            // the next work item; looked at before the barrier
-    uint64_t pw = 0;                                              // visit B: status word of the tile before
-    if (!is_a && tile > 0 && tid == 0) pw = ld_status(&a.status[tile - 1]);
+    uint32_t drawn = 0xffffffffu;
+    uint64_t pw = 0;                     // visit B: status word of the tile before
+    if (tid == 0) {
+      bulk_wait_read0();                 // the bulk store of the previous iteration has read its buffer
+      const uint32_t w1 = s_item[(it + 1) % 3];
+      uint32_t t1;
+      if (item_is_bulk(w1, t1)) { arm(par ^ 1, t1); armed |= 1u << (par ^ 1); }
+      if (w1 < wm.total()) drawn = draw();                        // the item after next; stored before the barrier
+      if (!is_a && tile > 0) pw = ld_status(&a.status[tile - 1]);
+    }
 
-    // ---- the tile into registers (visit A: from HBM; visit B: from L2, where visit A left it)
+    // ---- the tile: in the buffer, by the bulk copy or (ragged / unaligned) copied in by the threads
+    unsigned char *buf = s_buf + par * SB;
+    uint32_t *s_tile = reinterpret_cast<uint32_t *>(buf);
     const int64_t base = (int64_t)tile * SCAN_TILE;
     const int count = (int)((a.n - base) < SCAN_TILE ? (a.n - base) : SCAN_TILE);
     const bool full = (count == SCAN_TILE);
-    const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
-    uint32_t x[V][4], fw[V];
-    if (full && in_aligned) {
-      const int4 *in4 = reinterpret_cast<const int4 *>(gin);
-#pragma unroll
-      for (int j = 0; j < V; j++) {
-        const int4 q = is_a ? ld_keep_v4(in4 + (vrow + j) * 32 + lane) : ld_stream_v4(in4 + (vrow + j) * 32 + lane);
-        x[j][0] = q.x; x[j][1] = q.y; x[j][2] = q.z; x[j][3] = q.w;
+    if (full && in_bulk) {
+      if (!mbar_wait_bounded(&s_bar[par], (phases >> par) & 1u)) {
+        atomicCAS(a.failure, FAIL_NONE, FAIL_BULK_COPY_TIMEOUT);
+        s_fail = 1;
       }
-      if (SEG) {
-        const uint32_t *f4 = reinterpret_cast<const uint32_t *>(a.flags + base);
-#pragma unroll
-        for (int j = 0; j < V; j++) fw[j] = (uint32_t)(is_a ? ld_keep_b32(f4 + (vrow + j) * 32 + lane) : ld_stream_b32(f4 + (vrow + j) * 32 + lane));
-      }
+      phases ^= 1u << par;
+      if (tid == 0) armed &= ~(1u << par);
     } else {
+      const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
+      for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS)
+        s_tile[i] = (i < count) ? gin[i] : (COMPACT ? 0xffffffffu : 0u);     // padding: never selected / identity
+      if (SEG) {
+        unsigned char *sfb = buf + SCAN_TILE * 4;
+        for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS) sfb[i] = (i < count) ? a.flags[base + i] : (unsigned char)0;
+      }
+      __syncthreads();
+    }
+    // A thread owns ITEMS consecutive elements = V 16-byte vectors; V is odd, so the 128-bit
+    // shared-memory accesses of a warp are conflict-free.
+    uint32_t x[ITEMS];
+    {
+      const int4 *s4 = reinterpret_cast<const int4 *>(s_tile) + tid * V;
 #pragma unroll
       for (int j = 0; j < V; j++) {
-        fw[j] = 0;
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-          const int i = ((vrow + j) * 32 + lane) * 4 + k;
-          x[j][k] = (i < count) ? gin[i] : (COMPACT ? 0xffffffffu : 0u);   // padding: identity / never selected
-          if (SEG && i < count && a.flags[base + i]) fw[j] |= (0xffu << (8 * k));
-        }
+        const int4 q = s4[j];
+        x[4 * j + 0] = q.x; x[4 * j + 1] = q.y; x[4 * j + 2] = q.z; x[4 * j + 3] = q.w;
       }
     }
-
-    // ---- scan inside the warp
-    uint32_t pv[V], pf[V];               // exclusive prefix of (thread, row) within the warp
-    uint32_t anyb = 0;                   // segmented scan: bit 4j+k = a segment starts in vector j at or before k
-    uint32_t sel = 0;                    // compaction: bit 4j+k = key k of vector j is selected
-    uint32_t ov = 0, of = 0;             // warp aggregate
-    if (is_a && !SEG) {
-      // only the aggregate is wanted
+    uint32_t bits = 0;                   // segment starts (segmented scan) / selected keys (compaction)
+    uint32_t tv_thread, tf_thread = 0;   // the thread's aggregate
+    if (SEG) {
+      const uint32_t *sf = reinterpret_cast<const uint32_t *>(buf + SCAN_TILE * 4) + tid * V;
+      uint32_t fw[V];
+#pragma unroll
+      for (int j = 0; j < V; j++) fw[j] = sf[j];
+      float acc = 0.0f;
+#pragma unroll
+      for (int q = 0; q < ITEMS; q++) {
+        const bool fl = ((fw[q >> 2] >> (8 * (q & 3))) & 0xffu) != 0;
+        const float v = __uint_as_float(x[q]);
+        if (fl) { acc = v; bits |= 1u << q; } else acc = acc + v;
+        x[q] = __float_as_uint(acc);
+      }
+      tv_thread = __float_as_uint(acc);
+      tf_thread = bits ? 1u : 0u;
+    } else if (COMPACT) {
+#pragma unroll
+      for (int q = 0; q < ITEMS; q++)
+        if ((x[q] & 7u) < 3u) bits |= 1u << q;
+      tv_thread = __popc(bits);
+    } else if (is_a) {
       uint32_t s = 0;
 #pragma unroll
-      for (int j = 0; j < V; j++)
-#pragma unroll
-        for (int k = 0; k < 4; k++) s += COMPACT ? (((x[j][k] & 7u) < 3u) ? 1u : 0u) : x[j][k];
-      ov = warp_sum(s);
+      for (int q = 0; q < ITEMS; q++) s += x[q];
+      tv_thread = s;
     } else {
-      uint32_t rv[V], rf[V];             // inclusive scan of the vector totals along each row
 #pragma unroll
-      for (int j = 0; j < V; j++) {
-        if (SEG) {
-          float acc = __uint_as_float(x[j][0]);
-          uint32_t any = (fw[j] & 0xffu) ? 1u : 0u;
-          anyb |= any << (4 * j);
-#pragma unroll
-          for (int k = 1; k < 4; k++) {
-            const bool fl = ((fw[j] >> (8 * k)) & 0xffu) != 0;
-            const float v = __uint_as_float(x[j][k]);
-            acc = fl ? v : acc + v;
-            any |= fl ? 1u : 0u;
-            anyb |= any << (4 * j + k);
-            x[j][k] = __float_as_uint(acc);
-          }
-          rv[j] = x[j][3]; rf[j] = any;
-        } else if (COMPACT) {
-#pragma unroll
-          for (int k = 0; k < 4; k++)
-            if ((x[j][k] & 7u) < 3u) sel |= 1u << (4 * j + k);
-          rv[j] = __popc((sel >> (4 * j)) & 0xfu); rf[j] = 0;
-        } else {
-          x[j][1] += x[j][0]; x[j][2] += x[j][1]; x[j][3] += x[j][2];
-          rv[j] = x[j][3]; rf[j] = 0;
-        }
-      }
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-          const uint32_t lv = __shfl_up_sync(kFull, rv[j], o);
-          const uint32_t lf = SEG ? __shfl_up_sync(kFull, rf[j], o) : 0u;
-          if (lane >= o) Op::combine(lv, lf, rv[j], rf[j], rv[j], rf[j]);
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < V; j++) {
-        uint32_t xv = __shfl_up_sync(kFull, rv[j], 1), xf = SEG ? __shfl_up_sync(kFull, rf[j], 1) : 0u;
-        if (lane == 0) { xv = 0; xf = 0; }
-        Op::combine(ov, of, xv, xf, pv[j], pf[j]);
-        const uint32_t tvr = __shfl_sync(kFull, rv[j], 31), tfr = SEG ? __shfl_sync(kFull, rf[j], 31) : 0u;
-        Op::combine(ov, of, tvr, tfr, ov, of);
-      }
+      for (int q = 1; q < ITEMS; q++) x[q] += x[q - 1];
+      tv_thread = x[ITEMS - 1];
     }
-    if (lane == 0) { s_wv[par][warp] = ov; if (SEG) s_wf[par][warp] = of; }
+    // scan of the thread aggregates across the warp
+    uint32_t iv = tv_thread, ifl = tf_thread;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t lv = __shfl_up_sync(kFull, iv, o);
+      const uint32_t lf = SEG ? __shfl_up_sync(kFull, ifl, o) : 0u;
+      if (lane >= o) Op::combine(lv, lf, iv, ifl, iv, ifl);
+    }
+    uint32_t xv = __shfl_up_sync(kFull, iv, 1), xf = SEG ? __shfl_up_sync(kFull, ifl, 1) : 0u;   // exclusive, within the warp
+    if (lane == 0) { xv = 0; xf = 0; }
+    if (lane == 31) { s_wv[par][warp] = iv; if (SEG) s_wf[par][warp] = ifl; }
 
     if (tid == 0) {
       // visit B: the exclusive prefix of the tile (normally there long ago: visit A runs `lead` tiles ahead)
@@ -398,11 +421,10 @@ stream_kernel(const LookbackArgs a) {
         ev = status_value(pw);
       }
       s_ev[par] = ev; s_ok[par] = ok;
-      if (drawn == last_value) atomicExch(&a.ticket[0], 0u);
-      s_next[par ^ 1] = drawn;
+      s_item[(it + 2) % 3] = drawn;
     }
     __syncthreads();
-    if (!s_ok[par]) break;
+    if (!s_ok[par] || s_fail) break;
 
     uint32_t tv, tf, bv, bf;
     fold_warp_totals<Op>(s_wv[par], s_wf[par], lane, warp, tv, tf, bv, bf);
@@ -418,58 +440,66 @@ stream_kernel(const LookbackArgs a) {
       continue;
     }
     const uint32_t ev = s_ev[par];
+    uint32_t lv, lf;
+    Op::combine(bv, bf, xv, xf, lv, lf);                           // what precedes this thread inside the tile
     if (!COMPACT) {
-      const bool vec_store = out_aligned && full;
-      uint32_t *gout = reinterpret_cast<uint32_t *>(a.out) + base;
+      if (SEG) {
+        // before the thread's first segment start its left neighbours count, and before the
+        // tile's first segment start the incoming prefix as well
+        const float left = lf ? __uint_as_float(lv) : __uint_as_float(ev) + __uint_as_float(lv);
+        const int first = bits ? (__ffs(bits) - 1) : ITEMS;
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++)
+          if (q < first) x[q] = __float_as_uint(left + __uint_as_float(x[q]));
+      } else {
+        const uint32_t left = ev + lv;
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) x[q] += left;
+      }
+      int4 *s4 = reinterpret_cast<int4 *>(s_tile) + tid * V;
 #pragma unroll
       for (int j = 0; j < V; j++) {
-        const int vi = (vrow + j) * 32 + lane;
-        uint32_t lv, lf;
-        Op::combine(bv, bf, pv[j], pf[j], lv, lf);                 // what precedes this vector inside the tile
-        uint32_t r[4];
-        if (SEG) {
-          // before the first segment start of the tile the incoming prefix applies as well
-          const float left = lf ? __uint_as_float(lv) : __uint_as_float(ev) + __uint_as_float(lv);
-#pragma unroll
-          for (int k = 0; k < 4; k++)
-            r[k] = ((anyb >> (4 * j + k)) & 1u) ? x[j][k] : __float_as_uint(left + __uint_as_float(x[j][k]));
-        } else {
-          const uint32_t left = ev + lv;
-#pragma unroll
-          for (int k = 0; k < 4; k++) r[k] = left + x[j][k];
-        }
-        if (vec_store) {
-          int4 o4; o4.x = r[0]; o4.y = r[1]; o4.z = r[2]; o4.w = r[3];
-          st_stream_v4(reinterpret_cast<int4 *>(gout) + vi, o4);
-        } else {
-#pragma unroll
-          for (int k = 0; k < 4; k++) if (vi * 4 + k < count) gout[vi * 4 + k] = r[k];
-        }
+        int4 q; q.x = x[4 * j + 0]; q.y = x[4 * j + 1]; q.z = x[4 * j + 2]; q.w = x[4 * j + 3];
+        s4[j] = q;
+      }
+      uint32_t *gout = reinterpret_cast<uint32_t *>(a.out) + base;
+      if (full && out_bulk) {
+        fence_proxy_async_smem();        // the bulk store reads what the threads just wrote
+        __syncthreads();
+        if (tid == 0) { bulk_s2g(gout, s_tile, SCAN_TILE * 4); bulk_commit(); }
+      } else {
+        __syncthreads();
+        for (int i = tid; i < count; i += SCAN_THREADS) gout[i] = s_tile[i];
+        __syncthreads();                 // the buffer is filled again at the top of the next iteration
       }
     } else {
-      // keys into shared memory, selected first, each group in tile order; then out as runs
+      // keys back into the buffer, selected first, each group in order; then out as runs
       const uint32_t tile_true = tv;
+      uint32_t rank = lv;
+      const uint32_t first_ord = (uint32_t)tid * ITEMS;
 #pragma unroll
-      for (int j = 0; j < V; j++) {
-        uint32_t rank = bv + pv[j];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-          const uint32_t ord = (uint32_t)((vrow + j) * 32 + lane) * 4 + k;
-          if ((sel >> (4 * j + k)) & 1u) s_keys[rank++] = x[j][k];
-          else if (KIND == K_PARTITION && ord < (uint32_t)count) s_keys[tile_true + ord - rank] = x[j][k];
-        }
+      for (int q = 0; q < ITEMS; q++) {
+        if ((bits >> q) & 1u) s_tile[rank++] = x[q];
+        else if (KIND == K_PARTITION && first_ord + q < (uint32_t)count) s_tile[tile_true + first_ord + q - rank] = x[q];
       }
       __syncthreads();
       const int64_t true_before = (int64_t)ev;                    // selected keys in earlier tiles (n < 2^31)
       uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
-      for (uint32_t i = tid; i < tile_true; i += SCAN_THREADS) dst[i] = s_keys[i];
+      for (uint32_t i = tid; i < tile_true; i += SCAN_THREADS) dst[i] = s_tile[i];
       if (KIND == K_PARTITION) {
         uint32_t *dstf = a.out_false + (base - true_before);
         const uint32_t nf = (uint32_t)count - tile_true;
-        for (uint32_t i = tid; i < nf; i += SCAN_THREADS) dstf[i] = s_keys[tile_true + i];
+        for (uint32_t i = tid; i < nf; i += SCAN_THREADS) dstf[i] = s_tile[tile_true + i];
       }
       if (tile == nt - 1 && tid == 0) *a.d_count = true_before + (int64_t)tile_true;
+      __syncthreads();                   // the buffer is filled again at the top of the next iteration
     }
+  }
+  if (tid == 0) {
+    bulk_wait_read0();                   // shared memory must outlive the last bulk store's reads
+    // A failing grid leaves early: a copy still in flight must land before the CTA's shared memory goes.
+    for (int b = 0; b < 2; b++)
+      if (armed & (1u << b)) (void)mbar_wait_bounded(&s_bar[b], (phases >> b) & 1u, 1u << 16);
   }
 }
 
@@ -491,16 +521,19 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
 // cached per kind and device.
 template <int KIND>
 static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
+  constexpr size_t smem = 2 * (size_t)(SCAN_TILE * 4 + (KIND == K_SEGSCAN_F32 ? SCAN_TILE : 0));
   static int ctas_per_sm_dev[64], num_sms_dev[64];     // per device ordinal (function attributes are per device)
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
   int &ctas_per_sm = ctas_per_sm_dev[dev], &num_sms = num_sms_dev[dev];
   if (ctas_per_sm == 0) {
-    int occ = 0, sms = 0;
-    cudaError_t err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t err = cudaFuncSetAttribute(stream_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, stream_kernel<KIND>, SCAN_THREADS, 0);
+    int occ = 0, sms = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, stream_kernel<KIND>, SCAN_THREADS, smem);
     if (err != cudaSuccess) return err;
     if (occ < 1) return cudaErrorLaunchOutOfResources;
     num_sms = sms;
@@ -509,7 +542,7 @@ static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
   const uint32_t resident = (uint32_t)(ctas_per_sm * num_sms);
   uint32_t grid = 2 * a.num_tiles + 1 < resident ? 2 * a.num_tiles + 1 : resident;
   if (a.num_tiles <= 1 || grid < 2) grid = 1;          // a single tile: one CTA that propagates for itself
-  stream_kernel<KIND><<<grid, SCAN_THREADS, 0, stream>>>(a);
+  stream_kernel<KIND><<<grid, SCAN_THREADS, smem, stream>>>(a);
   return cudaGetLastError();
 }
 
@@ -619,7 +652,7 @@ cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out
 // acceptable, for instance a latency-bound service loop after start-up.  For them the tile
 // ticket, the tile status words and the failure word of the look-back scan live in the
 // fixed array below instead of in pooled memory.  The array is part of the loaded library
-// image: every GPU that loads the library holds these ~129 KiB until the process exits.
+// image: every GPU that loads the library holds these ~103 KiB until the process exits.
 constexpr int64_t NOALLOC_MAX_N = (int64_t)1 << 26;
 constexpr uint32_t NOALLOC_MAX_TILES = (uint32_t)((NOALLOC_MAX_N + SCAN_TILE - 1) / SCAN_TILE);
 constexpr size_t NOALLOC_HEAD = 512;     // [0,4) ticket, [256,260) failure word

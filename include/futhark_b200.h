@@ -278,7 +278,7 @@ int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct f
  * synchronisation or an out-of-memory failure from cudaMalloc cannot be tolerated.  The
  * caller supplies `in` and `out` (device pointers, 4-byte aligned; 16-byte alignment is
  * faster); the scan's temporaries (a tile counter and one 8-byte status word per tile of
- * 4096 elements) live in a fixed ~129 KiB array inside the library image, which every GPU
+ * 5120 elements) live in a fixed ~103 KiB array inside the library image, which every GPU
  * that loads the library keeps until the process exits.
  *
  * Limits and rules:

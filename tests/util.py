@@ -1,7 +1,7 @@
 """Shared helpers of the GPU parity tests."""
 import numpy as np
 
-TILE = 4096          # elements per look-back tile of the scan kernels
+TILE = 5120          # elements per look-back tile of the scan kernels
 SIZES = [0, 1, 2, 31, 32, 33, 255, 256, 257, 1000, TILE - 1, TILE, TILE + 1, 2 * TILE, 3 * TILE + 17, 100003]
 
 
