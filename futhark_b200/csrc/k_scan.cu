@@ -230,7 +230,7 @@ stream_kernel(const LookbackArgs a) {
   constexpr int V = SCAN_V, ITEMS = SCAN_ITEMS;
   constexpr bool SEG = (KIND == K_SEGSCAN_F32);
   constexpr bool COMPACT = (KIND == K_FILTER || KIND == K_PARTITION);
-  constexpr int SB = SCAN_TILE * 4 + (SEG ? SCAN_TILE : 0);      // bytes of a tile buffer
+  constexpr int SB = SCAN_TILE * 4 + (SEG ? SCAN_TILE : 64);     // bytes of a tile buffer (compaction stages with up to 9 words of padding)
   using Op = typename std::conditional<SEG, OpSegAddF32, OpAddU32>::type;
   extern __shared__ __align__(128) unsigned char s_buf[];   // two tile buffers
   __shared__ __align__(8) uint64_t s_bar[2];
@@ -283,7 +283,7 @@ stream_kernel(const LookbackArgs a) {
   auto arm = [&](int b, uint32_t tile) {   // thread 0: start the copies of a tile into buffer b
     unsigned char *dst = s_buf + b * SB;
     const int64_t tb = (int64_t)tile * SCAN_TILE;
-    mbar_expect_tx(&s_bar[b], SB);
+    mbar_expect_tx(&s_bar[b], SCAN_TILE * 4 + (SEG ? SCAN_TILE : 0));
     bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, SCAN_TILE * 4, &s_bar[b]);
     if (SEG) bulk_g2s(dst + SCAN_TILE * 4, a.flags + tb, SCAN_TILE, &s_bar[b]);
   };
@@ -473,24 +473,37 @@ stream_kernel(const LookbackArgs a) {
         __syncthreads();                 // the buffer is filled again at the top of the next iteration
       }
     } else {
-      // keys back into the buffer, selected first, each group in order; then out as runs
+      // Keys back into the buffer, selected first, each group in order; then out as runs.  Each
+      // group is staged at the same offset modulo 4 as its destination, so that the body of a
+      // run moves as aligned 16-byte vectors on both sides.
       const uint32_t tile_true = tv;
+      const int64_t true_before = (int64_t)ev;                    // selected keys in earlier tiles (n < 2^31)
+      uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
+      uint32_t *dstf = (KIND == K_PARTITION) ? a.out_false + (base - true_before) : nullptr;
+      const uint32_t pad_t = (uint32_t)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3u);
+      const uint32_t pad_f = (KIND == K_PARTITION) ? (uint32_t)((reinterpret_cast<uintptr_t>(dstf) >> 2) & 3u) : 0u;
+      const uint32_t start_f = ((pad_t + tile_true + 3u) & ~3u) + pad_f;     // first rejected key in the buffer
       uint32_t rank = lv;
       const uint32_t first_ord = (uint32_t)tid * ITEMS;
 #pragma unroll
       for (int q = 0; q < ITEMS; q++) {
-        if ((bits >> q) & 1u) s_tile[rank++] = x[q];
-        else if (KIND == K_PARTITION && first_ord + q < (uint32_t)count) s_tile[tile_true + first_ord + q - rank] = x[q];
+        if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
+        else if (KIND == K_PARTITION && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
       }
       __syncthreads();
-      const int64_t true_before = (int64_t)ev;                    // selected keys in earlier tiles (n < 2^31)
-      uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
-      for (uint32_t i = tid; i < tile_true; i += SCAN_THREADS) dst[i] = s_tile[i];
-      if (KIND == K_PARTITION) {
-        uint32_t *dstf = a.out_false + (base - true_before);
-        const uint32_t nf = (uint32_t)count - tile_true;
-        for (uint32_t i = tid; i < nf; i += SCAN_THREADS) dstf[i] = s_tile[tile_true + i];
-      }
+      auto copy_run = [&](uint32_t *g, uint32_t s0, uint32_t len) {
+        // g and s_tile + s0 are congruent modulo 16 bytes
+        uint32_t h = (4u - (s0 & 3u)) & 3u;
+        if (h > len) h = len;
+        const uint32_t nvec = (len - h) >> 2, tail0 = h + (nvec << 2);
+        if ((uint32_t)tid < h) g[tid] = s_tile[s0 + tid];
+        const int4 *sv = reinterpret_cast<const int4 *>(s_tile + s0 + h);
+        int4 *gv = reinterpret_cast<int4 *>(g + h);
+        for (uint32_t v = tid; v < nvec; v += SCAN_THREADS) gv[v] = sv[v];
+        if ((uint32_t)tid < len - tail0) g[tail0 + tid] = s_tile[s0 + tail0 + tid];
+      };
+      copy_run(dst, pad_t, tile_true);
+      if (KIND == K_PARTITION) copy_run(dstf, start_f, (uint32_t)count - tile_true);
       if (tile == nt - 1 && tid == 0) *a.d_count = true_before + (int64_t)tile_true;
       __syncthreads();                   // the buffer is filled again at the top of the next iteration
     }
@@ -521,7 +534,7 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
 // cached per kind and device.
 template <int KIND>
 static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
-  constexpr size_t smem = 2 * (size_t)(SCAN_TILE * 4 + (KIND == K_SEGSCAN_F32 ? SCAN_TILE : 0));
+  constexpr size_t smem = 2 * (size_t)(SCAN_TILE * 4 + (KIND == K_SEGSCAN_F32 ? SCAN_TILE : 64));
   static int ctas_per_sm_dev[64], num_sms_dev[64];     // per device ordinal (function attributes are per device)
   int dev = 0;
   cudaGetDevice(&dev);
