@@ -16,9 +16,18 @@
 //                 result with one global atomic per non-neutral bin.
 //   B <= 4*CAP    the bins are cut into P = ceil(B/CAP) ranges; P consecutive CTAs read
 //                 the same input chunk at the same time (the re-reads are served by L2)
-//                 and each keeps only the indices of its range: one pass over HBM.
-//   larger        global atomics straight into the result, which stays L2-resident for
-//                 the sizes of interest (2^20 bins = 4 MiB).
+//                 and each keeps only the indices of its range: one pass over HBM, P
+//                 passes over L2, whose bandwidth bounds this path.  (One histogram per
+//                 cluster of P CTAs in distributed shared memory, every element handled
+//                 once, was measured three times slower at P = 2: shared-memory atomics
+//                 across a cluster run at about one per three cycles and SM.)
+//   larger        global atomics into the result, which stays L2-resident for the sizes of
+//                 interest (2^20 bins = 4 MiB), behind a per-CTA cache in shared memory:
+//                 16384 (bin, value) slots, a bin owning the slot it hashes to if it gets
+//                 there first.  With skewed indices the hot bins claim their slots at once
+//                 and are accumulated on chip; their updates would otherwise queue up on
+//                 single L2 addresses.  A CTA that sees few hits (uniform indices over many
+//                 more bins than slots) stops looking into the cache.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -141,17 +150,76 @@ hist_smem_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ 
   }
 }
 
-// ---- global-atomic path ---------------------------------------------------------------------
+// ---- global atomics behind a per-CTA cache of hot bins ---------------------------------------------
+constexpr int HC_LOG2_SLOTS = 14;
+constexpr uint32_t HC_SLOTS = 1u << HC_LOG2_SLOTS;       // 16384 x (tag, value) = 128 KiB
+constexpr int32_t HC_EMPTY = -1;
+constexpr int HC_PROBE_ROUNDS = 8;                       // grid-stride rounds after which the hit rate is judged
+
 template <int OP>
-__global__ void __launch_bounds__(256)
-hist_global_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ ws, int64_t n, int64_t B,
+__global__ void __launch_bounds__(HIST_THREADS, 1)
+hist_cached_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ ws, int64_t n, int64_t B,
                    uint32_t *__restrict__ out) {
-  const int64_t stride = (int64_t)gridDim.x * 256;
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
-    const int64_t b = (int64_t)ld_stream_b32(bins + i);
+  extern __shared__ __align__(16) uint32_t s_mem[];
+  int32_t *s_tag = reinterpret_cast<int32_t *>(s_mem);
+  uint32_t *s_val = s_mem + HC_SLOTS;
+  __shared__ uint32_t s_hits, s_seen;
+  const int tid = threadIdx.x;
+  for (uint32_t i = tid; i < HC_SLOTS; i += HIST_THREADS) { s_tag[i] = HC_EMPTY; s_val[i] = neutral<OP>(); }
+  if (tid == 0) { s_hits = 0; s_seen = 0; }
+  __syncthreads();
+
+  uint32_t hits = 0, seen = 0;
+  auto update = [&](int32_t bin, uint32_t wbits, bool use_cache) {
     bool skip;
-    const uint32_t w = prep<OP>((uint32_t)ld_stream_b32(ws + i), skip);
-    if (b >= 0 && b < B && !skip) upd_global<OP>(&out[b], w);
+    const uint32_t w = prep<OP>(wbits, skip);
+    if (bin < 0 || (int64_t)bin >= B || skip) return;
+    if (use_cache) {
+      seen++;
+      const uint32_t slot = ((uint32_t)bin * 0x9E3779B1u) >> (32 - HC_LOG2_SLOTS);
+      int32_t t = *reinterpret_cast<volatile int32_t *>(&s_tag[slot]);
+      if (t == HC_EMPTY) {
+        const int32_t old = atomicCAS(&s_tag[slot], HC_EMPTY, bin);
+        t = (old == HC_EMPTY) ? bin : old;
+      }
+      if (t == bin) { upd_shared<OP>(&s_val[slot], w); hits++; return; }
+    }
+    upd_global<OP>(&out[bin], w);
+  };
+
+  const bool vec = ((((uintptr_t)bins) | ((uintptr_t)ws)) & 15) == 0;
+  const int64_t stride = (int64_t)gridDim.x * HIST_THREADS;
+  bool use_cache = true;
+  if (vec) {
+    const int4 *bv = reinterpret_cast<const int4 *>(bins);
+    const int4 *wv = reinterpret_cast<const int4 *>(ws);
+    const int64_t nvec = n >> 2;
+    int64_t i = (int64_t)blockIdx.x * HIST_THREADS + tid;
+    int round = 0;
+    // the hit rate is judged only where every thread of the CTA makes that many rounds
+    const bool probe = (int64_t)blockIdx.x * HIST_THREADS + (HIST_THREADS - 1) + (int64_t)HC_PROBE_ROUNDS * stride < nvec;
+    for (; i < nvec; i += stride, round++) {
+      if (probe && round == HC_PROBE_ROUNDS) {
+        atomicAdd(&s_hits, hits); atomicAdd(&s_seen, seen);
+        __syncthreads();
+        use_cache = (uint64_t)s_hits * 4u >= (uint64_t)s_seen;       // keep the cache if >= 25% of the updates hit
+      }
+      const int4 b0 = ld_stream_v4(bv + i), w0 = ld_stream_v4(wv + i);
+      update(b0.x, w0.x, use_cache); update(b0.y, w0.y, use_cache);
+      update(b0.z, w0.z, use_cache); update(b0.w, w0.w, use_cache);
+    }
+    if (blockIdx.x == 0) {               // fewer than four trailing elements
+      const int64_t j = (nvec << 2) + tid;
+      if (j < n) update(bins[j], ws[j], false);
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * HIST_THREADS + tid; i < n; i += stride) update(bins[i], ws[i], true);
+  }
+  __syncthreads();
+  for (uint32_t i = tid; i < HC_SLOTS; i += HIST_THREADS) {
+    const int32_t t = s_tag[i];
+    const uint32_t v = s_val[i];
+    if (t != HC_EMPTY && v != neutral<OP>()) upd_global<OP>(&out[t], v);
   }
 }
 
@@ -196,7 +264,14 @@ static cudaError_t launch_hist_op(int64_t B, const int32_t *bins, const uint32_t
       if (err != cudaSuccess) return err;
       kern<<<grid, HIST_THREADS, smem, stream>>>(bins, ws, n, B, P, range, log2c, out);
     } else {
-      hist_global_kernel<OP><<<grid_for(n, 256, num_sms * 16), 256, 0, stream>>>(bins, ws, n, B, out);
+      auto kern = hist_cached_kernel<OP>;
+      const size_t smem = (size_t)HC_SLOTS * 8;
+      err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return err;
+      int64_t want = (n / 4 + HIST_THREADS - 1) / HIST_THREADS;
+      if (want < 1) want = 1;
+      const int grid = (int)(want < num_sms ? want : num_sms);
+      kern<<<grid, HIST_THREADS, smem, stream>>>(bins, ws, n, B, out);
     }
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;

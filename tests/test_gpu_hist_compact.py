@@ -30,6 +30,26 @@ def test_hist_max_f32_bit_exact(ctx, n, B, dist):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("B,dist", [(150000, "uniform"), (200000, "zipf"), (229376, "uniform"), (229377, "zipf")])
+def test_hist_bin_ranges_and_first_size_beyond(ctx, B, dist):
+    # 2, 3 and 4 bin ranges up to 4 x 57344 bins; one more bin takes the cached path
+    n = (1 << 21) + 3
+    bins, wi, wf = datagen.workload_hist(n, B, dist)
+    assert np.array_equal(fb.hist_add_i32(ctx, B, bins, wi), oracle.hist_add_i32(B, bins, wi))
+    got = fb.hist_max_f32(ctx, B, bins, wf)
+    assert np.array_equal(got.view(np.uint32), oracle.hist_max_f32(B, bins, wf).view(np.uint32))
+
+
+@pytest.mark.parametrize("dist", ["uniform", "zipf"])
+def test_hist_many_bins_long_input(ctx, dist):
+    # long enough for every CTA to judge its cache's hit rate (uniform: gives the cache up; zipf: keeps it)
+    n, B = (1 << 24) + 1, 1 << 20
+    bins, wi, wf = datagen.workload_hist(n, B, dist)
+    assert np.array_equal(fb.hist_add_i32(ctx, B, bins, wi), oracle.hist_add_i32(B, bins, wi))
+    got = fb.hist_max_f32(ctx, B, bins, wf)
+    assert np.array_equal(got.view(np.uint32), oracle.hist_max_f32(B, bins, wf).view(np.uint32))
+
+
 def test_hist_reference_known_answers(ctx):
     # tests/hist/simple.fut:4-50 with a zero destination; index 10000000 is out of range
     assert np.array_equal(fb.hist_add_i32(ctx, 5, [1, 1, 1, 1, 1], [1, 1, 1, 1, 1]), [0, 5, 0, 0, 0])
