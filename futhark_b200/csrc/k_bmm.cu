@@ -11,8 +11,10 @@
 //               tcgen05.mma M128 N256 K16; tcgen05.commit hands stages back to the
 //               producer and finished accumulators to the epilogue
 //   warps 2-5   epilogue: tcgen05.ld of the accumulator (one TMEM lane = one row per
-//               thread), f32 stores to C; runs while the next tile's MMAs fill the other
-//               accumulator
+//               thread, the next 32-column chunk in flight while this one is handled),
+//               staged in shared memory and written to C by bulk tensor stores (TMA), so
+//               the warps never wait for the memory system; runs while the next tile's
+//               MMAs fill the other accumulator
 // B is consumed as it lies in memory ([K][N], N contiguous) through the "MN-major"
 // operand layout, so no transpose pass is needed.  No multicast is used anywhere.
 // Every mbarrier wait is bounded; a wait that runs out stores a failure code, and all
@@ -34,9 +36,10 @@ constexpr int B_STAGE_BYTES = BK * BN * 2;            // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int B_NBLOCK_BYTES = BK * 64 * 2;           // one 64-wide slab of N: 8 KiB
 constexpr int BMM_THREADS = 192;
-constexpr int EPI_PITCH = 36;                         // floats per staged row: 32 + 4 of padding (conflict-free both ways)
-constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;     // one 32 x 32 f32 chunk per epilogue warp
-constexpr int BMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
+constexpr int EPI_PITCH = 36;                         // plain-store path: floats per staged row, 32 + 4 of padding
+constexpr int EPI_CHUNK_BYTES = 32 * 32 * 4;          // one 32 x 32 f32 chunk
+constexpr int EPI_BYTES = 4 * 2 * EPI_CHUNK_BYTES;    // two chunk buffers per epilogue warp (the plain path needs 4.5 KiB of them)
+constexpr int BMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 1024 /*barriers*/ + EPI_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------------------
@@ -46,6 +49,10 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *t
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
       : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, const void *smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(tm), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_slot, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -113,11 +120,12 @@ struct BmmBarriers {
 
 __global__ void __launch_bounds__(BMM_THREADS, 1)
 bmm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmC, int c_by_tma,
                   float *__restrict__ C, int nb, int M, int N, int K, int *failure) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   BmmBarriers *bars = reinterpret_cast<BmmBarriers *>(smem + STAGES * STAGE_BYTES);
-  float *epi = reinterpret_cast<float *>(smem + STAGES * STAGE_BYTES + 256);
+  float *epi = reinterpret_cast<float *>(smem + STAGES * STAGE_BYTES + 1024);    // 1024-byte aligned
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
@@ -213,14 +221,11 @@ bmm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // A thread receives 32 consecutive columns of ONE row from TMEM; written out like
         // that, every store instruction would touch 32 different cache lines.  The chunk is
         // therefore turned through shared memory so that 8 lanes write one full 128-byte line.
-        float *stg = epi + (warp - 2) * 32 * EPI_PITCH;
+        float *stg = epi + (warp - 2) * (2 * EPI_CHUNK_BYTES / 4);
         const int rsub = lane >> 3, c4 = (lane & 7) * 4;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; c++) {
-          uint32_t v[32];
-          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c * 32;
-          tmem_ld_32x32(taddr, v);
-          tmem_ld_wait();
+        // The TMEM load of the next chunk is in flight while this one is staged and stored.
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+        auto emit = [&](const uint32_t (&v)[32], int c) {
 #pragma unroll
           for (int q = 0; q < 8; q++) {
             float4 o;
@@ -248,10 +253,45 @@ bmm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
           }
           __syncwarp();
+        };
+        // With a tensor map for C the chunk leaves as one bulk tensor store (TMA) issued by lane
+        // 0: the warp does not wait for the memory system at all.  The chunk is staged as the
+        // 128-byte swizzle wants it (16-byte piece q of row r at position q ^ (r & 7)), which
+        // also keeps the staging stores conflict-free.  Two buffers per warp: a buffer is
+        // written again once the store issued from it two chunks ago has read it.
+        auto emit_tma = [&](const uint32_t (&v)[32], int c) {
+          float *buf = stg + (c & 1) * (EPI_CHUNK_BYTES / 4);
+          if (lane == 0) bulk_wait_read1();
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * q]); o.y = __uint_as_float(v[4 * q + 1]);
+            o.z = __uint_as_float(v[4 * q + 2]); o.w = __uint_as_float(v[4 * q + 3]);
+            *reinterpret_cast<float4 *>(buf + lane * 32 + ((q ^ (lane & 7)) << 2)) = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmC, buf, n0 + c * 32, m0 + quarter * 32, batch);
+            bulk_commit();
+          }
+        };
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(taddr0, va);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c += 2) {
+          tmem_ld_wait();
+          tmem_ld_32x32(taddr0 + (c + 1) * 32, vb);
+          if (c_by_tma) emit_tma(va, c); else emit(va, c);
+          tmem_ld_wait();
+          if (c + 2 < BN / 32) tmem_ld_32x32(taddr0 + (c + 2) * 32, va);
+          if (c_by_tma) emit_tma(vb, c + 1); else emit(vb, c + 1);
         }
         tc_fence_before();
         mbar_arrive(&bars->tmem_empty[acc]);
       }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the bulk stores of this warp are complete
       if (!ok) { atomicCAS(failure, FAIL_NONE, FAIL_MMA_TIMEOUT); bars->failed = 1; }
     }
   }
@@ -301,14 +341,15 @@ static EncodeTiledFn get_encode_fn() {
 
 // dims are innermost first; strides (bytes) for dims 1..2
 static bool make_map_3d(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0,
-                        uint32_t b1) {
+                        uint32_t b1, bool f32 = false) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return false;
+  const uint64_t es = f32 ? 4 : 2;
   cuuint64_t dims[3] = {d0, d1, d2};
-  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint64_t strides[2] = {d0 * es, d0 * d1 * es};
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+  CUresult r = enc(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -332,7 +373,11 @@ cudaError_t launch_bmm_f16(const uint16_t *A, const uint16_t *B, float *C, int64
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * nb;
       const int grid = (int)(tiles < sms ? tiles : sms);
-      bmm_f16_tc_kernel<<<grid, BMM_THREADS, BMM_SMEM, stream>>>(tmA, tmB, C, (int)nb, (int)m, (int)n, (int)k, failure);
+      // C leaves by bulk tensor stores where a map can describe it (rows a multiple of 16 bytes, aligned base)
+      CUtensorMap tmC = tmA;
+      const int c_by_tma = ((n % 4 == 0) && ((((uintptr_t)C) & 15) == 0) &&
+                            make_map_3d(&tmC, C, (uint64_t)n, (uint64_t)m, (uint64_t)nb, 32, 32, true)) ? 1 : 0;
+      bmm_f16_tc_kernel<<<grid, BMM_THREADS, BMM_SMEM, stream>>>(tmA, tmB, tmC, c_by_tma, C, (int)nb, (int)m, (int)n, (int)k, failure);
       return cudaGetLastError();
     }
   }

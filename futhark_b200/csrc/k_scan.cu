@@ -234,7 +234,7 @@ stream_kernel(const LookbackArgs a) {
   using Op = typename std::conditional<SEG, OpSegAddF32, OpAddU32>::type;
   extern __shared__ __align__(128) unsigned char s_buf[];   // two tile buffers
   __shared__ __align__(8) uint64_t s_bar[2];
-  __shared__ uint32_t s_item[3];         // work items of iterations it, it+1, it+2 (slot = iteration mod 3)
+  __shared__ uint32_t s_item[3];         // decoded work items of iterations it, it+1, it+2: tile << 1 | visit A, or ITEM_NONE
   __shared__ uint32_t s_wv[2][SCAN_WARPS], s_wf[2][SCAN_WARPS];
   __shared__ uint32_t s_role;
   __shared__ volatile uint32_t s_fail;
@@ -274,11 +274,16 @@ stream_kernel(const LookbackArgs a) {
   // The tile of the next iteration is fetched while this iteration computes: one bulk async
   // copy (TMA) per array into the buffer the iteration before last used, awaited on an
   // mbarrier.  Work items are therefore drawn two iterations ahead.
-  auto item_is_bulk = [&](uint32_t w, uint32_t &tile) -> bool {
-    if (w >= wm.total()) return false;
+  constexpr uint32_t ITEM_NONE = 0xffffffffu;
+  auto encode = [&](uint32_t w) -> uint32_t {     // thread 0: work item -> what the threads need of it
+    if (w >= wm.total()) return ITEM_NONE;
     bool ia;
-    wm.decode(w, ia, tile);
-    return in_bulk && ((int64_t)(tile + 1) * SCAN_TILE <= a.n);
+    uint32_t t;
+    wm.decode(w, ia, t);
+    return (t << 1) | (ia ? 1u : 0u);
+  };
+  auto item_is_bulk = [&](uint32_t item) -> bool {
+    return item != ITEM_NONE && in_bulk && ((int64_t)((item >> 1) + 1) * SCAN_TILE <= a.n);
   };
   auto arm = [&](int b, uint32_t tile) {   // thread 0: start the copies of a tile into buffer b
     unsigned char *dst = s_buf + b * SB;
@@ -298,28 +303,26 @@ stream_kernel(const LookbackArgs a) {
     fence_mbar_init();
     const uint32_t w0 = draw();
     const uint32_t w1 = (w0 < wm.total()) ? draw() : 0xffffffffu;   // a worker stops at its first item past the end
-    s_item[0] = w0; s_item[1] = w1;
-    uint32_t t0;
-    if (item_is_bulk(w0, t0)) { arm(0, t0); armed |= 1u; }
+    const uint32_t i0 = encode(w0);
+    s_item[0] = i0; s_item[1] = encode(w1);
+    if (item_is_bulk(i0)) { arm(0, i0 >> 1); armed |= 1u; }
   }
   __syncthreads();
   uint32_t phases = 0;                   // bit b: parity the next completion of buffer b's barrier will have
 
   for (uint32_t it = 0;; it++) {
     const int par = (int)(it & 1u);
-    const uint32_t w = s_item[it % 3];
-    if (w >= wm.total()) break;
-    bool is_a;
-    uint32_t tile;
-    wm.decode(w, is_a, tile);
-    uint32_t drawn = 0xffffffffu;
+    const uint32_t item = s_item[it % 3];
+    if (item == ITEM_NONE) break;
+    const bool is_a = (item & 1u) != 0;
+    const uint32_t tile = item >> 1;
+    uint32_t drawn = ITEM_NONE;
     uint64_t pw = 0;                     // visit B: status word of the tile before
     if (tid == 0) {
       bulk_wait_read0();                 // the bulk store of the previous iteration has read its buffer
-      const uint32_t w1 = s_item[(it + 1) % 3];
-      uint32_t t1;
-      if (item_is_bulk(w1, t1)) { arm(par ^ 1, t1); armed |= 1u << (par ^ 1); }
-      if (w1 < wm.total()) drawn = draw();                        // the item after next; stored before the barrier
+      const uint32_t i1 = s_item[(it + 1) % 3];
+      if (item_is_bulk(i1)) { arm(par ^ 1, i1 >> 1); armed |= 1u << (par ^ 1); }
+      if (i1 != ITEM_NONE) drawn = encode(draw());                // the item after next; stored before the barrier
       if (!is_a && tile > 0) pw = ld_status(&a.status[tile - 1]);
     }
 
@@ -389,17 +392,24 @@ stream_kernel(const LookbackArgs a) {
       for (int q = 1; q < ITEMS; q++) x[q] += x[q - 1];
       tv_thread = x[ITEMS - 1];
     }
-    // scan of the thread aggregates across the warp
-    uint32_t iv = tv_thread, ifl = tf_thread;
+    uint32_t xv = 0, xf = 0;             // what precedes this thread inside its warp
+    if (!SEG && is_a) {
+      // only the tile's aggregate is wanted
+      const uint32_t t = warp_sum(tv_thread);
+      if (lane == 31) s_wv[par][warp] = t;
+    } else {
+      // scan of the thread aggregates across the warp
+      uint32_t iv = tv_thread, ifl = tf_thread;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t lv = __shfl_up_sync(kFull, iv, o);
-      const uint32_t lf = SEG ? __shfl_up_sync(kFull, ifl, o) : 0u;
-      if (lane >= o) Op::combine(lv, lf, iv, ifl, iv, ifl);
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t lv = __shfl_up_sync(kFull, iv, o);
+        const uint32_t lf = SEG ? __shfl_up_sync(kFull, ifl, o) : 0u;
+        if (lane >= o) Op::combine(lv, lf, iv, ifl, iv, ifl);
+      }
+      xv = __shfl_up_sync(kFull, iv, 1); xf = SEG ? __shfl_up_sync(kFull, ifl, 1) : 0u;
+      if (lane == 0) { xv = 0; xf = 0; }
+      if (lane == 31) { s_wv[par][warp] = iv; if (SEG) s_wf[par][warp] = ifl; }
     }
-    uint32_t xv = __shfl_up_sync(kFull, iv, 1), xf = SEG ? __shfl_up_sync(kFull, ifl, 1) : 0u;   // exclusive, within the warp
-    if (lane == 0) { xv = 0; xf = 0; }
-    if (lane == 31) { s_wv[par][warp] = iv; if (SEG) s_wf[par][warp] = ifl; }
 
     if (tid == 0) {
       // visit B: the exclusive prefix of the tile (normally there long ago: visit A runs `lead` tiles ahead)
