@@ -285,12 +285,13 @@ def main():
     ctx.sync()
 
     def step_resident():
-        if group is not None:
-            o1 = group.segscan_f32(d_flags, d_xs)
-        else:
-            o1 = ctx.entry_segscan_f32(d_flags, d_xs)
+        # with several GPUs the exchange of the scan's shard summaries runs beside the two reductions
+        pending = group.segscan_f32_begin(d_flags, d_xs) if group is not None else None
+        o1 = ctx.entry_segscan_f32(d_flags, d_xs) if group is None else None
         o2 = ctx.entry_segreduce_f32(d_off, d_flags, d_xs)
         o3 = ctx.entry_rowsum_f32(d_rows)
+        if group is not None:
+            o1 = group.segscan_f32_finish(pending)
         o1.free(); o2.free(); o3.free()
 
     def barrier():

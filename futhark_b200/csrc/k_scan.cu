@@ -4,43 +4,44 @@
 // (src/Futhark/CodeGen/ImpGen/GPU/SegScan/SinglePass.hs:327-879) and, for compaction, the
 // scan + scatter that prelude/soacs.fut:241-286 expands into.
 //
-// One persistent kernel, templated on what a tile computes; 256 threads per CTA, several
-// CTAs per SM.  A tile holds 256 x 16 = 4096 elements.  Like the reference's kernel it
-// makes a single pass over memory and hands prefixes between tiles through one status word
-// per tile (value and state in one 64-bit word, :628-660 there), and tiles are numbered by
-// a ticket counter so that tile i is claimed only after every tile < i (:444-461).  Where
-// it differs:
+// One persistent kernel, templated on what a tile computes; 256 threads per CTA, 4 CTAs
+// per SM.  A tile holds 256 x 20 = 5120 elements.  Like the reference's kernel it hands
+// prefixes between tiles through one status word per tile (value and state in one 64-bit
+// word, :628-660 there) and numbers its work by a global counter, so that what a tile
+// depends on has always been claimed by a running CTA before it (:444-461).  Where it
+// differs:
 //
-//   * Loads run ahead of the computation.  A CTA owns a ring of 4 shared-memory stages and
-//     keeps a tile in each: one bulk async copy (TMA) per array, awaited on an mbarrier.
-//     HBM reads are therefore in flight all the time, whatever the threads wait for.
-//
-//   * A tile is visited twice, two iterations apart.  Visit A takes it from its stage into
-//     registers, scans it there (a thread owns 4 vectors of 4 consecutive elements, vector
-//     j of lane l of warp w being vector (w*4+j)*32+l of the tile, so every shared- and
-//     global-memory access of a warp is contiguous; in-vector scan, one shuffle scan per
-//     vector row, row totals chained, 8 warp totals through shared memory), publishes the
-//     tile aggregate, and parks what still depends on the tiles before it back in the
-//     stage.  Visit B, two iterations later, picks up the tile's exclusive prefix -- by
-//     then normally there -- adds it and stores straight from registers.  One
-//     __syncthreads per iteration.  For the segmented scan only the elements before the
-//     tile's first segment start wait for visit B; the rest is stored in visit A.
+//   * A tile is visited twice.  Visit A only computes the tile's aggregate and publishes
+//     it.  Visit B, drawn from the same counter about SCAN_LEAD tiles later, scans the
+//     tile, adds its exclusive prefix and stores.  Visit A reads the tile from HBM and
+//     leaves it in L2, where visit B finds it, so HBM traffic stays at one read and one
+//     write per element.  Because the aggregates run that far ahead, the prefix a visit B
+//     needs has long been published: in the steady state no tile waits for another, which
+//     the look-back of the classic single-visit scheme cannot avoid once ~200 tiles finish
+//     per microsecond (every resident tile then sits in that wait).
 //
 //   * No tile looks back over its predecessors.  The first CTA to arrive does no tiles:
-//     its warp 0 is the PROPAGATOR, which walks the status words once, in order, 512 per
-//     round trip, turning published aggregates into inclusive prefixes.  A tile waits on
-//     one word only, its predecessor's prefix.  With ~200 tiles finishing per microsecond
-//     a look-back by every tile (32 predecessors per round trip) needs several dependent
-//     round trips per tile and holds every resident tile in that wait.
+//     its warp 0 is the PROPAGATOR, which walks the status words once, in order, 256 per
+//     round trip, turning published aggregates into inclusive prefixes.  Visit B reads one
+//     word, its predecessor's prefix.
+//
+//   * Loads run ahead of the threads.  Thread 0 draws work items two iterations ahead and
+//     starts a bulk async copy (TMA) per array of the next item's tile into the other of
+//     two shared-memory buffers; an mbarrier tells the threads when it has landed.  A
+//     thread owns 20 CONSECUTIVE elements = 5 x 16 bytes, an odd stride in 16-byte units,
+//     so the 128-bit shared-memory accesses are conflict-free without padding: sequential
+//     scan in the thread, one shuffle scan of the thread totals, 8 warp totals through
+//     shared memory.  Visit B writes its results back into the buffer and thread 0 sends
+//     it off with one bulk store; compaction ranks the keys, stages them in the buffer at
+//     the 16-byte phase of their destination and copies the runs out as aligned vectors.
 //
 // Progress: the propagator exists as soon as any CTA runs and needs the aggregates in
-// tile order.  A CTA visits its tiles in ticket order and visit A never waits for another
-// tile, so the lowest tile whose aggregate is missing is always one whose CTA can get to
-// it: that CTA can only be held up in visit B of a lower tile, whose predecessors have
-// all published.  Every wait is bounded and polls the failure word.
+// tile order.  Visit A waits for nothing, and visit B of tile t is drawn after visit A of
+// every tile <= t, so the lowest tile whose aggregate is missing always belongs to a CTA
+// that is on its way to it.  Every wait is bounded and polls the failure word.
 //
 // A tile that is ragged (the last one) or whose global addresses are not 16-byte aligned
-// is read with guarded loads in visit A instead of the bulk copy, and stored element-wise.
+// is copied into the buffer by the threads with guarded loads, and copied out likewise.
 #include <stdio.h>
 #include <string.h>
 

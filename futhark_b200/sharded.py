@@ -78,6 +78,17 @@ class LibLocal:
     def collective_stream(self):
         return torch.cuda.stream(self.stream)
 
+    def exchange_stream(self):
+        """A second stream, ordered after everything enqueued so far on the kernels' stream."""
+        if getattr(self, "side", None) is None:
+            self.side = torch.cuda.Stream(device=self.device)
+        self.side.wait_stream(self.stream)
+        return torch.cuda.stream(self.side)
+
+    def exchange_done(self):
+        """The kernels' stream waits for what was enqueued on the second stream."""
+        self.stream.wait_stream(self.side)
+
     def as_tensor(self, arr, dtype):
         """A torch view of a library array (no copy)."""
         return torch.as_tensor(arr, device=self.device).view(dtype)
@@ -144,11 +155,22 @@ class Group:
 
     # -- flagged segmented scan (+) f32
     def segscan_f32(self, flags, xs):
+        return self.segscan_f32_finish(self.segscan_f32_begin(flags, xs))
+
+    def segscan_f32_begin(self, flags, xs):
+        """Local scan and the exchange of the shard summaries.  The exchange runs beside the
+        stream of the kernels (where the executor has a second stream), so whatever the
+        caller launches before `segscan_f32_finish` overlaps it."""
         summaries = self.local.empty(2 * self.world, torch.int32)
         mine = summaries[2 * self.rank:2 * self.rank + 2]
         out = self.local.segscan_shard(flags, xs, mine)
-        with self.local.collective_stream():
+        with self.local.exchange_stream():
             dist.all_gather_into_tensor(summaries, mine.clone(), group=self.pg)
+        return out, flags, summaries
+
+    def segscan_f32_finish(self, pending):
+        out, flags, summaries = pending
+        self.local.exchange_done()
         self.local.segscan_apply(out, flags, summaries, self.rank)
         return out
 

@@ -25,6 +25,12 @@ class NumpyLocal:
     def collective_stream(self):
         return contextlib.nullcontext()
 
+    def exchange_stream(self):
+        return contextlib.nullcontext()
+
+    def exchange_done(self):
+        pass
+
     def reduce_i32_into(self, xs, slot):
         slot[0] = oracle.reduce_i32(xs)
 
