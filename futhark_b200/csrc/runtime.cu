@@ -158,7 +158,13 @@ void fb_unref(futhark_context *ctx, memblock_device *mb) {
   if (mb->references == nullptr) return;   // borrowed memory is never freed by us
   if (--(*mb->references) == 0) {
     // Stream order makes immediate reuse safe: every consumer of the old contents was
-    // enqueued on the one stream before any producer of the new contents will be.
+    // enqueued on the main stream before any producer of the new contents will be -- except
+    // a value copy still pending on the copy stream, which the main stream now waits for.
+    if (ctx->copies_pending) {
+      cudaEventRecord(ctx->ev_copy, ctx->copy_stream);
+      cudaStreamWaitEvent(ctx->stream, ctx->ev_copy, 0);
+      ctx->copies_pending = false;
+    }
     ctx->free_blocks.emplace((size_t)mb->size, (void *)(uintptr_t)mb->mem);
     ctx->cur_mem -= mb->size;
     free(mb->references);
@@ -301,6 +307,12 @@ static int backend_setup(futhark_context *ctx) {
             prop.sharedMemPerBlockOptin >> 10, prop.l2CacheSize >> 10);
   rc = fb_cuda_check(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate");
   if (rc) return rc;
+  rc = fb_cuda_check(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  if (rc) return rc;
+  rc = fb_cuda_check(ctx, cudaEventCreateWithFlags(&ctx->ev_main, cudaEventDisableTiming), "cudaEventCreate");
+  if (rc) return rc;
+  rc = fb_cuda_check(ctx, cudaEventCreateWithFlags(&ctx->ev_copy, cudaEventDisableTiming), "cudaEventCreate");
+  if (rc) return rc;
   rc = fb_cuda_check(ctx, cudaMalloc((void **)&ctx->d_failure, 256), "failure word");
   if (rc) return rc;
   rc = fb_cuda_check(ctx, cudaMemsetAsync(ctx->d_failure, 0, 256, ctx->stream), "failure word clear");
@@ -350,6 +362,10 @@ void futhark_context_free(struct futhark_context *ctx) {
     cudaFree(ctx->lookback_scratch);
     cudaFree(ctx->d_scalar);
     cudaFreeHost(ctx->h_scalar);
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+    cudaEventDestroy(ctx->ev_main);
+    cudaEventDestroy(ctx->ev_copy);
     cudaStreamDestroy(ctx->stream);
     if (prev >= 0 && prev != ctx->device) cudaSetDevice(prev);
   }
@@ -372,6 +388,9 @@ int futhark_context_sync(struct futhark_context *ctx) {
   CtxGuard g(ctx);
   int rc = fb_cuda_check(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
   if (rc) return rc;
+  rc = fb_cuda_check(ctx, cudaStreamSynchronize(ctx->copy_stream), "cudaStreamSynchronize");
+  if (rc) return rc;
+  ctx->copies_pending = false;
   if (ctx->failure_is_an_option) {
     // Same protocol as rts/c/backends/cuda.h:719-754: read the failure word, and if it
     // is set, reset it and report a program error.
@@ -505,7 +524,13 @@ static int array_values(futhark_context *ctx, ARR *arr, void *out, size_t elem) 
   int64_t n = 1;
   for (int i = 0; i < RANK; i++) n *= arr->shape[i];
   if (n == 0) return 0;
-  return fb_cuda_check(ctx, cudaMemcpyAsync(out, (const void *)(uintptr_t)arr->mem.mem, (size_t)n * elem, cudaMemcpyDeviceToHost, ctx->stream),
+  // after everything enqueued so far, beside everything enqueued later
+  int rc = fb_cuda_check(ctx, cudaEventRecord(ctx->ev_main, ctx->stream), "cudaEventRecord");
+  if (rc) return rc;
+  rc = fb_cuda_check(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_main, 0), "cudaStreamWaitEvent");
+  if (rc) return rc;
+  ctx->copies_pending = true;
+  return fb_cuda_check(ctx, cudaMemcpyAsync(out, (const void *)(uintptr_t)arr->mem.mem, (size_t)n * elem, cudaMemcpyDeviceToHost, ctx->copy_stream),
                        "device-to-host copy");
 }
 

@@ -64,6 +64,13 @@ struct futhark_context {
   int device = 0;
   int num_sms = 0;
   cudaStream_t stream = nullptr;
+  // Device-to-host copies of array values run on a stream of their own, ordered after the
+  // work enqueued so far, so that they overlap later uploads and kernels; futhark_context_sync
+  // waits for both streams, and a block freed while such a copy is pending makes the main
+  // stream wait for it before the block can be reused.
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev_main = nullptr, ev_copy = nullptr;
+  bool copies_pending = false;
   std::string device_name;
 
   // pool: freed blocks by size (rts/c/gpu.h:240-316 semantics: smallest block that fits,
