@@ -33,6 +33,10 @@ N_SEG = 1 << 27
 ROWS, COLS = 131072, 1024
 ELEMS_PER_STEP = 2 * N_SEG + ROWS * COLS          # scan + segmented reduce + row reduce
 ALG_BYTES_SEGSCAN = 9 * N_SEG                      # read 4n + 1n, write 4n
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the segmented-scan kernel, from the
+# ncu capture of a 2^25-element case (profiles/stream_kernel_segscan_f32_2p25.md: 181.5 MB read,
+# 91.4 MB written), scaled by the number of elements; traffic grows in proportion to them.
+NCU_TRAFFIC_SEGSCAN_2P25 = 181.5e6 + 91.4e6
 
 
 def measured_peaks():
@@ -150,52 +154,16 @@ CASES = {
 
 
 def run_case(args):
-    """One entry point, inputs resident, `--reps` launches timed with CUDA event pairs on the
-    library's stream.  Prints one JSON line.  Used for the per-SOAC table and as the small
-    workload of ncu captures (`--n` shrinks it)."""
+    """One entry point (or, with `--case sweep`, every configuration of the baseline), inputs
+    resident, `--reps` launches timed with CUDA event pairs on the library's stream.  One JSON
+    line per case.  Used for the per-SOAC table and as the small workload of ncu captures
+    (`--n` shrinks it)."""
     import futhark_b200 as fb
     from futhark_b200 import datagen
-    names = list(CASES) if args.case == "all" else [args.case]
     peak, peak_kind = measured_peaks()
     ctx = fb.Context(profiling=True)
-    for name in names:
-        n = args.n if args.n else CASES[name]
-        B, dist_name = args.bins, args.dist
-        flops = None
-        if name in ("scan_i32", "reduce_i32"):
-            a = [ctx.new("i32_1d", datagen.workload_i32(n))]
-            fn = (lambda: ctx.entry_scan_i32(a[0])) if name == "scan_i32" else (lambda: ctx.entry_reduce_i32(a[0]))
-            nbytes = 8 * n if name == "scan_i32" else 4 * n
-        elif name in ("segscan_f32", "segreduce_f32"):
-            offsets, flags, xs = datagen.workload_seg_f32(n)
-            a = [ctx.new("i64_1d", offsets), ctx.new("bool_1d", flags.view(np.bool_)), ctx.new("f32_1d", xs)]
-            S = offsets.size - 1
-            if name == "segscan_f32":
-                fn, nbytes = (lambda: ctx.entry_segscan_f32(a[1], a[2])), 9 * n
-            else:
-                fn, nbytes = (lambda: ctx.entry_segreduce_f32(a[0], a[1], a[2])), 4 * n + 8 * (S + 1) + 4 * S
-        elif name == "rowsum_f32":
-            rows = n // COLS
-            a = [ctx.new("f32_2d", datagen.workload_rows_f32(rows, COLS))]
-            fn, nbytes = (lambda: ctx.entry_rowsum_f32(a[0])), 4 * rows * COLS + 4 * rows
-        elif name in ("hist_add_i32", "hist_max_f32"):
-            bins, wi, wf = datagen.workload_hist(n, B, dist_name)
-            a = [ctx.new("i32_1d", bins), ctx.new("i32_1d", wi) if name == "hist_add_i32" else ctx.new("f32_1d", wf)]
-            fn = (lambda: ctx.entry_hist_add_i32(B, a[0], a[1])) if name == "hist_add_i32" else (lambda: ctx.entry_hist_max_f32(B, a[0], a[1]))
-            nbytes = 8 * n + 4 * B
-        elif name in ("filter_u32", "partition_u32"):
-            ks = datagen.workload_keys_u32(n)
-            a = [ctx.new("u32_1d", ks)]
-            sel = int(((ks & 7) < 3).sum())
-            if name == "filter_u32":
-                fn, nbytes = (lambda: ctx.entry_filter_u32(a[0])), 4 * n + 4 * sel
-            else:
-                fn, nbytes = (lambda: ctx.entry_partition_u32(a[0])), 8 * n
-        elif name == "bmm_f16":
-            m = args.bmm_dim
-            A, Bm = datagen.workload_bmm(n, m, m, m)
-            a = [ctx.new("f16_3d", A), ctx.new("f16_3d", Bm)]
-            fn, nbytes, flops = (lambda: ctx.entry_bmm_f16(a[0], a[1])), 2 * n * m * m * 2 + 4 * n * m * m, 2 * n * m * m * m
+
+    def timed(name, fn, nbytes, n, extra=None, flops=None):
         ctx.sync()
         ctx.pause_profiling()
         for _ in range(args.warmup):
@@ -215,8 +183,7 @@ def run_case(args):
         avg = float(np.mean(us))
         line = {"case": name, "n": n, "launches": len(us), "avg_us": avg, "min_us": float(np.min(us)),
                 "kernel_event": ev[0]["name"], "algorithmic_bytes": int(nbytes)}
-        if name.startswith("hist"):
-            line.update({"bins": B, "dist": dist_name})
+        line.update(extra or {})
         if flops:
             tf = flops / (avg * 1e-6) / 1e12
             pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"] if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1590.0
@@ -226,15 +193,75 @@ def run_case(args):
             line.update({"gbs": gbs, "peak_gbs": peak, "peak_kind": peak_kind, "frac": gbs / peak,
                          "elements_per_s": n / (avg * 1e-6)})
         print(json.dumps(line), flush=True)
+
+    def hist_cases(n, grid):
+        """Both operators for every (bins, distribution) of `grid`; weights are made once."""
+        wi = ctx.new("i32_1d", datagen.uniform_i32(datagen.SEEDS["hist"], 0, n, 0, 100, stream=5))
+        wf = ctx.new("f32_1d", datagen.normal_f32(datagen.SEEDS["hist"], 0, n, stream=6))
+        for B, dist_name in grid:
+            bins = ctx.new("i32_1d", datagen.hist_bins(datagen.SEEDS["hist"], 0, n, B, dist_name))
+            extra = {"bins": B, "dist": dist_name}
+            if args.case in ("hist_add_i32", "sweep", "all"):
+                timed("hist_add_i32", lambda: ctx.entry_hist_add_i32(B, bins, wi), 8 * n + 4 * B, n, extra)
+            if args.case in ("hist_max_f32", "sweep", "all"):
+                timed("hist_max_f32", lambda: ctx.entry_hist_max_f32(B, bins, wf), 8 * n + 4 * B, n, extra)
+            bins.free()
+        wi.free(); wf.free()
+        ctx.clear_caches()
+
+    names = [c for c in CASES if not c.startswith("hist")] if args.case in ("all", "sweep") else [args.case]
+    for name in names:
+        n = args.n if args.n else CASES[name]
+        if name.startswith("hist"):
+            continue
+        a = []
+        if name in ("scan_i32", "reduce_i32"):
+            a = [ctx.new("i32_1d", datagen.workload_i32(n))]
+            if name == "scan_i32":
+                timed(name, lambda: ctx.entry_scan_i32(a[0]), 8 * n, n)
+            else:
+                timed(name, lambda: ctx.entry_reduce_i32(a[0]), 4 * n, n)
+        elif name in ("segscan_f32", "segreduce_f32"):
+            offsets, flags, xs = datagen.workload_seg_f32(n)
+            a = [ctx.new("i64_1d", offsets), ctx.new("bool_1d", flags.view(np.bool_)), ctx.new("f32_1d", xs)]
+            S = offsets.size - 1
+            if name == "segscan_f32":
+                timed(name, lambda: ctx.entry_segscan_f32(a[1], a[2]), 9 * n, n)
+            else:
+                timed(name, lambda: ctx.entry_segreduce_f32(a[0], a[1], a[2]), 4 * n + 8 * (S + 1) + 4 * S, n)
+        elif name == "rowsum_f32":
+            rows = n // COLS
+            a = [ctx.new("f32_2d", datagen.workload_rows_f32(rows, COLS))]
+            timed(name, lambda: ctx.entry_rowsum_f32(a[0]), 4 * rows * COLS + 4 * rows, n)
+        elif name in ("filter_u32", "partition_u32"):
+            ks = datagen.workload_keys_u32(n)
+            a = [ctx.new("u32_1d", ks)]
+            sel = int(((ks & 7) < 3).sum())
+            if name == "filter_u32":
+                timed(name, lambda: ctx.entry_filter_u32(a[0]), 4 * n + 4 * sel, n)
+            else:
+                timed(name, lambda: ctx.entry_partition_u32(a[0]), 8 * n, n)
+        elif name == "bmm_f16":
+            m = args.bmm_dim
+            A, Bm = datagen.workload_bmm(n, m, m, m)
+            a = [ctx.new("f16_3d", A), ctx.new("f16_3d", Bm)]
+            timed(name, lambda: ctx.entry_bmm_f16(a[0], a[1]), 2 * n * m * m * 2 + 4 * n * m * m, n, flops=2 * n * m * m * m)
         for x in a:
             x.free()
         ctx.clear_caches()
+    if args.case in ("hist_add_i32", "hist_max_f32"):
+        hist_cases(args.n if args.n else CASES[args.case], [(args.bins, args.dist)])
+    elif args.case == "sweep":
+        hist_cases(args.n if args.n else CASES["hist_add_i32"],
+                   [(B, d) for B in (256, 65536, 1 << 20) for d in ("uniform", "zipf")])
+    elif args.case == "all":
+        hist_cases(args.n if args.n else CASES["hist_add_i32"], [(args.bins, args.dist)])
     ctx.close()
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, help="run one entry point (or 'all') instead of the step")
+    ap.add_argument("--case", default=None, help="run one entry point, 'all', or 'sweep' (every baseline configuration) instead of the step")
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--bins", type=int, default=256)
     ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"])
@@ -393,7 +420,9 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(),
             "roofline": {"bound": "hbm", "kernel": "stream_kernel<K_SEGSCAN_F32>", "achieved": achieved, "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_SEGSCAN_2P25 * (N_SEG / float(1 << 25)),
+                         "traffic_note": "ncu capture of a 2^25-element launch scaled by elements; the write-back of the L2-resident tail of the output is not in it",
                          "algorithmic_bytes_per_launch": ALG_BYTES_SEGSCAN, "avg_launch_us": seg_us},
             "kernels": kernels,
             "cpu_baseline": cpu,

@@ -6,6 +6,9 @@ can be produced independently -- this is what lets each rank of a multi-GPU run
 generate exactly its own shard of the same logical array.  All functions take a
 half-open index range [lo, hi) and return numpy arrays.
 """
+import concurrent.futures
+import os
+
 import numpy as np
 
 _GOLD = np.uint64(0x9E3779B97F4A7C15)
@@ -27,7 +30,7 @@ def mix64(seed, lo, hi, stream=0):
     return z
 
 
-def _chunks(lo, hi, step=1 << 24):
+def _chunks(lo, hi, step=1 << 22):
     a = lo
     while a < hi:
         b = min(a + step, hi)
@@ -35,21 +38,34 @@ def _chunks(lo, hi, step=1 << 24):
         a = b
 
 
+def _fill(out, lo, hi, fn):
+    """out[a-lo:b-lo] = fn(a, b) for every chunk [a, b) of [lo, hi), chunks in parallel
+    (numpy releases the interpreter lock inside its loops; values depend on indices only)."""
+    chunks = list(_chunks(lo, hi))
+    def work(ab):
+        a, b = ab
+        out[a - lo:b - lo] = fn(a, b)
+    workers = min(len(chunks), os.cpu_count() or 1, 32)
+    if workers <= 1:
+        for ab in chunks:
+            work(ab)
+    else:
+        with concurrent.futures.ThreadPoolExecutor(max_workers=workers) as ex:
+            list(ex.map(work, chunks))
+    return out
+
+
 def uniform_i32(seed, lo, hi, vmin, vmax, stream=0):
     """int32 uniform in [vmin, vmax] (inclusive)."""
-    out = np.empty(hi - lo, dtype=np.int32)
     span = np.uint64(vmax - vmin + 1)
-    for a, b in _chunks(lo, hi):
-        out[a - lo:b - lo] = ((mix64(seed, a, b, stream) >> np.uint64(16)) % span).astype(np.int64) + vmin
-    return out
+    return _fill(np.empty(hi - lo, dtype=np.int32), lo, hi,
+                 lambda a, b: ((mix64(seed, a, b, stream) >> np.uint64(16)) % span).astype(np.int64) + vmin)
 
 
 def full_u32(seed, lo, hi, stream=0):
     """uint32 uniform over the full 32-bit range."""
-    out = np.empty(hi - lo, dtype=np.uint32)
-    for a, b in _chunks(lo, hi):
-        out[a - lo:b - lo] = (mix64(seed, a, b, stream) >> np.uint64(32)).astype(np.uint32)
-    return out
+    return _fill(np.empty(hi - lo, dtype=np.uint32), lo, hi,
+                 lambda a, b: (mix64(seed, a, b, stream) >> np.uint64(32)).astype(np.uint32))
 
 
 def uniform01(seed, lo, hi, stream=0):
@@ -59,20 +75,17 @@ def uniform01(seed, lo, hi, stream=0):
 
 def normal_f32(seed, lo, hi, stream=0):
     """float32 N(0,1) by Box-Muller on two mixer streams."""
-    out = np.empty(hi - lo, dtype=np.float32)
-    for a, b in _chunks(lo, hi):
+    def chunk(a, b):
         u1 = 1.0 - uniform01(seed, a, b, 2 * stream + 100)      # (0,1]
         u2 = uniform01(seed, a, b, 2 * stream + 101)
-        out[a - lo:b - lo] = (np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)).astype(np.float32)
-    return out
+        return (np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)).astype(np.float32)
+    return _fill(np.empty(hi - lo, dtype=np.float32), lo, hi, chunk)
 
 
 def uniform_f16(seed, lo, hi, stream=0):
     """binary16 bits (uint16) of round-to-nearest(uniform(-1,1))."""
-    out = np.empty(hi - lo, dtype=np.uint16)
-    for a, b in _chunks(lo, hi):
-        out[a - lo:b - lo] = (2.0 * uniform01(seed, a, b, stream) - 1.0).astype(np.float16).view(np.uint16)
-    return out
+    return _fill(np.empty(hi - lo, dtype=np.uint16), lo, hi,
+                 lambda a, b: (2.0 * uniform01(seed, a, b, stream) - 1.0).astype(np.float16).view(np.uint16))
 
 
 def geometric_segments(seed, n, mean=256):
@@ -120,7 +133,7 @@ def hist_bins(seed, lo, hi, B, dist="uniform", oor_fraction=0.01, zipf_s=1.1):
         cdf = np.cumsum(w)
         cdf /= cdf[-1]
     pow2 = B > 0 and (B & (B - 1)) == 0
-    for a, b in _chunks(lo, hi):
+    def chunk(a, b):
         if dist == "uniform":
             bins = ((mix64(seed, a, b, 0) >> np.uint64(20)) % np.uint64(max(B, 1))).astype(np.int64)
         elif dist == "zipf":
@@ -134,8 +147,8 @@ def hist_bins(seed, lo, hi, B, dist="uniform", oor_fraction=0.01, zipf_s=1.1):
         mag = ((sel >> np.uint64(8)) & np.uint64(0xFFFF)).astype(np.int64)
         neg = (sel & np.uint64(1)).astype(bool)
         bad = np.where(neg, -1 - mag, B + mag)
-        out[a - lo:b - lo] = np.where(oor, bad, bins).astype(np.int32)
-    return out
+        return np.where(oor, bad, bins).astype(np.int32)
+    return _fill(out, lo, hi, chunk)
 
 
 # ---- the five workloads, by name -------------------------------------------------
