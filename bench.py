@@ -95,6 +95,15 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def host_threads():
+    """Host cores this process may use (a launcher may have set OMP_NUM_THREADS=1: the CPU arm
+    asks for its thread count explicitly)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def make_inputs(rank):
     """This rank's shard: the same generator, a different index range per rank."""
     from futhark_b200 import datagen
@@ -110,12 +119,12 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     import oracle
-    threads = oracle.max_threads()
+    threads = host_threads()
     offsets, flags, xs, rows = make_inputs(0)
     def step():
-        oracle.segscan_f32(flags, xs)
-        oracle.segreduce_f32(offsets, xs)
-        oracle.rowsum_f32(rows)
+        oracle.segscan_f32(flags, xs, threads)
+        oracle.segreduce_f32(offsets, xs, threads)
+        oracle.rowsum_f32(rows, threads)
     for _ in range(max(args.warmup, 1)):
         step()
     t0 = time.perf_counter()
@@ -401,13 +410,13 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
-        threads = oracle.max_threads()
+        threads = host_threads()
         best = None
         for i in range(3):
             t0 = time.perf_counter()
-            oracle.segscan_f32(flags, xs)
-            oracle.segreduce_f32(offsets, xs)
-            oracle.rowsum_f32(rows)
+            oracle.segscan_f32(flags, xs, threads)
+            oracle.segreduce_f32(offsets, xs, threads)
+            oracle.rowsum_f32(rows, threads)
             dt = time.perf_counter() - t0
             best = dt if best is None or dt < best else best
         cpu = {"value": ELEMS_PER_STEP / best, "unit": "elements/s", "cores": threads, "kind": "port",
