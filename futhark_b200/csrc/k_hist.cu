@@ -67,6 +67,20 @@ __device__ __forceinline__ uint32_t prep(uint32_t wbits, bool &skip) {
   return f32_key(wbits);
 }
 
+// One update of a bin range [lo, lo + nb) held in shared memory (nb <= 57344, lo < 2^31).  A
+// single unsigned comparison covers "below the range", "above it" and negative indices; the
+// weight is only looked at for an index inside the range.
+template <int OP>
+__device__ __forceinline__ void upd_range(uint32_t *s_hist, int32_t bin, uint32_t wbits, int32_t lo, uint32_t nb,
+                                          int log2c, uint32_t copy) {
+  const uint32_t b = (uint32_t)(bin - lo);
+  if (b < nb) {
+    bool skip;
+    const uint32_t w = prep<OP>(wbits, skip);
+    if (!skip) upd_shared<OP>(&s_hist[(b << log2c) + copy], w);
+  }
+}
+
 // ---- shared-memory path ------------------------------------------------------------------
 // grid = groups * P CTAs; CTA (g, p) streams the vectors of group g and keeps bins in
 // [p*range, min(B, (p+1)*range)).  log2c = log2 of the number of private copies.
@@ -99,24 +113,14 @@ hist_smem_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ 
       const int bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
       const int ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-      for (int k = 0; k < 8; k++) {
-        const int64_t b = (int64_t)bb[k] - bin_lo;
-        bool skip;
-        const uint32_t w = prep<OP>((uint32_t)ww[k], skip);
-        if (b >= 0 && b < (int64_t)nb && !skip) upd_shared<OP>(&s_hist[((uint32_t)b << log2c) + copy], w);
-      }
+      for (int k = 0; k < 8; k++) upd_range<OP>(s_hist, bb[k], (uint32_t)ww[k], (int32_t)bin_lo, nb, log2c, copy);
     }
     for (; i < nvec; i += stride) {
       int4 b0 = ld_stream_v4(bv + i), w0 = ld_stream_v4(wv + i);
       const int bb[4] = {b0.x, b0.y, b0.z, b0.w};
       const int ww[4] = {w0.x, w0.y, w0.z, w0.w};
 #pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const int64_t b = (int64_t)bb[k] - bin_lo;
-        bool skip;
-        const uint32_t w = prep<OP>((uint32_t)ww[k], skip);
-        if (b >= 0 && b < (int64_t)nb && !skip) upd_shared<OP>(&s_hist[((uint32_t)b << log2c) + copy], w);
-      }
+      for (int k = 0; k < 4; k++) upd_range<OP>(s_hist, bb[k], (uint32_t)ww[k], (int32_t)bin_lo, nb, log2c, copy);
     }
     // fewer than four trailing elements: the first group's CTAs take them
     if (g == 0) {
@@ -213,12 +217,7 @@ hist_smem_async_kernel(const int32_t *__restrict__ bins, const uint32_t *__restr
     const int bb[4] = {b0.x, b0.y, b0.z, b0.w};
     const int ww[4] = {w0.x, w0.y, w0.z, w0.w};
 #pragma unroll
-    for (int k = 0; k < 4; k++) {
-      const int64_t b = (int64_t)bb[k] - bin_lo;
-      bool skip;
-      const uint32_t w = prep<OP>((uint32_t)ww[k], skip);
-      if (b >= 0 && b < (int64_t)nb && !skip) upd_shared<OP>(&s_hist[(uint32_t)b], w);
-    }
+    for (int k = 0; k < 4; k++) upd_range<OP>(s_hist, bb[k], (uint32_t)ww[k], (int32_t)bin_lo, nb, 0, 0u);
     if (++s == HIST_STAGES) s = 0;
   }
   cp_async_wait<0>();
