@@ -97,3 +97,26 @@ def test_two_contexts_coexist():
 def test_unknown_device_is_an_error():
     with pytest.raises(fb.FutharkError):
         fb.Context(device="no such device name")
+
+
+def test_values_pending_when_the_array_is_freed_and_its_block_reused(ctx):
+    """futhark_values_* copies on a stream of their own.  Freeing the array right after asking for
+    its values, and producing new data into the block the pool hands out again, must not
+    change what arrives in the host buffer."""
+    import oracle
+    from futhark_b200 import datagen
+    n = (1 << 24) + 5
+    xs = datagen.uniform_i32(31, 0, n, -1000, 1000)
+    ys = datagen.uniform_i32(32, 0, n, -1000, 1000)
+    a, b = ctx.new("i32_1d", xs), ctx.new("i32_1d", ys)
+    out = ctx.entry_scan_i32(a)
+    host = np.empty(n, dtype=np.int32)
+    out.values_into(host)              # asynchronous
+    out.free()                         # the block goes back to the pool while the copy may be pending
+    out2 = ctx.entry_scan_i32(b)       # same size: takes that block and overwrites it
+    host2 = np.empty(n, dtype=np.int32)
+    out2.values_into(host2)
+    ctx.sync()
+    assert np.array_equal(host, oracle.scan_i32(xs))
+    assert np.array_equal(host2, oracle.scan_i32(ys))
+    a.free(); b.free(); out2.free()
