@@ -158,7 +158,7 @@ CASES = {
     # name: (default n, algorithmic bytes(n, extra) or flops)
     "scan_i32": 1 << 26, "reduce_i32": 1 << 26, "segscan_f32": 1 << 27, "segreduce_f32": 1 << 27,
     "rowsum_f32": 1 << 27, "hist_add_i32": 1 << 28, "hist_max_f32": 1 << 28, "filter_u32": 1 << 28,
-    "partition_u32": 1 << 28, "bmm_f16": 64,
+    "partition_u32": 1 << 28, "bmm_f16": 64, "transpose_f32": 1 << 27,
 }
 
 
@@ -250,6 +250,10 @@ def run_case(args):
                 timed(name, lambda: ctx.entry_filter_u32(a[0]), 4 * n + 4 * sel, n)
             else:
                 timed(name, lambda: ctx.entry_partition_u32(a[0]), 8 * n, n)
+        elif name == "transpose_f32":
+            rows = n // COLS
+            a = [ctx.new("f32_2d", datagen.workload_rows_f32(rows, COLS))]
+            timed(name, lambda: ctx.entry_transpose_f32(a[0]), 8 * rows * COLS, n)
         elif name == "bmm_f16":
             m = args.bmm_dim
             A, Bm = datagen.workload_bmm(n, m, m, m)

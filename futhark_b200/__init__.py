@@ -121,6 +121,8 @@ def load():
     L.futhark_entry_filter_u32.argtypes = [vp, pvp, vp]
     L.futhark_entry_partition_u32.argtypes = [vp, pvp, vp]
     L.futhark_entry_bmm_f16.argtypes = [vp, pvp, vp, vp]
+    L.futhark_entry_transpose_f32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_transpose_f32_3d.argtypes = [vp, pvp, vp]
     _lib = L
     return L
 
@@ -350,6 +352,12 @@ class Context:
     def entry_bmm_f16(self, A, B):
         return self._entry_arr("bmm_f16", "f32_3d", A.ptr, B.ptr)
 
+    def entry_transpose_f32(self, xss):
+        return self._entry_arr("transpose_f32", "f32_2d", xss.ptr)
+
+    def entry_transpose_f32_3d(self, xsss):
+        return self._entry_arr("transpose_f32_3d", "f32_3d", xsss.ptr)
+
 
 # ---- host-buffer conveniences: new -> entry -> values -> free, as a C caller would ----
 
@@ -423,3 +431,10 @@ def bmm_f16(ctx, A, B):
     A = np.asarray(A).view(np.uint16)
     B = np.asarray(B).view(np.uint16)
     return _run(ctx, [("f16_3d", A), ("f16_3d", B)], ctx.entry_bmm_f16)
+
+
+def transpose_f32(ctx, xs):
+    xs = np.ascontiguousarray(xs, dtype=np.float32)
+    if xs.ndim == 2:
+        return _run(ctx, [("f32_2d", xs)], ctx.entry_transpose_f32)
+    return _run(ctx, [("f32_3d", xs)], ctx.entry_transpose_f32_3d)

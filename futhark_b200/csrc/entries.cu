@@ -275,6 +275,42 @@ int futhark_entry_bmm_f16(struct futhark_context *ctx, struct futhark_f32_3d **o
   return FUTHARK_SUCCESS;
 }
 
+static int transpose_common(futhark_context *ctx, int64_t nb, int64_t rows, int64_t cols, const memblock_device &in, memblock_device *out) {
+  int rc = fb_alloc(ctx, (size_t)(nb * rows * cols) * 4, "transpose_f32.out", out);
+  if (rc != 0) return rc;
+  if (nb * rows * cols > 0) {
+    LaunchScope ls(ctx, "transpose_f32.map_transpose_4b", PROV("map transpose xsss"),
+                   "{" + kv("batch", nb) + "," + kv("rows", rows) + "," + kv("cols", cols) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_transpose_b32(dptr<void>(in), dptr<void>(*out), nb, rows, cols, ctx->num_sms, ctx->stream), "transpose_f32");
+    if (rc != 0) fb_unref(ctx, out);
+  }
+  return rc;
+}
+
+int futhark_entry_transpose_f32(struct futhark_context *ctx, struct futhark_f32_2d **out0, const struct futhark_f32_2d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  futhark_f32_2d *out = (futhark_f32_2d *)malloc(sizeof(futhark_f32_2d));
+  if (out == nullptr) return 1;
+  out->shape[0] = in0->shape[1]; out->shape[1] = in0->shape[0];
+  int rc = transpose_common(ctx, 1, in0->shape[0], in0->shape[1], in0->mem, &out->mem);
+  if (rc != 0) { free(out); return rc; }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f32_3d **out0, const struct futhark_f32_3d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  futhark_f32_3d *out = (futhark_f32_3d *)malloc(sizeof(futhark_f32_3d));
+  if (out == nullptr) return 1;
+  out->shape[0] = in0->shape[0]; out->shape[1] = in0->shape[2]; out->shape[2] = in0->shape[1];
+  int rc = transpose_common(ctx, in0->shape[0], in0->shape[1], in0->shape[2], in0->mem, &out->mem);
+  if (rc != 0) { free(out); return rc; }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
 // ---- shard-local pieces for arrays split across several contexts (extensions) -------------------
 
 int futhark_b200_reduce_i32_to_device(struct futhark_context *ctx, CUdeviceptr dst, const struct futhark_i32_1d *in0) {

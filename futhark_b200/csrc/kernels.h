@@ -43,6 +43,11 @@ cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const flo
 cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
                         int num_sms, cudaStream_t stream);
 
+// ---- layout operations (k_layout.cu) ----------------------------------------------------------
+// out[b][c][r] = in[b][r][c] for 4-byte elements.
+cudaError_t launch_transpose_b32(const void *in, void *out, int64_t nb, int64_t rows, int64_t cols, int num_sms,
+                                 cudaStream_t stream);
+
 // ---- batched f16 contraction (k_bmm.cu) ------------------------------------------------
 cudaError_t launch_bmm_f16(const uint16_t *A, const uint16_t *B, float *C, int64_t nb, int64_t m, int64_t k,
                            int64_t n, int *failure, cudaStream_t stream);

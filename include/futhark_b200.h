@@ -229,6 +229,17 @@ int futhark_entry_partition_u32(struct futhark_context *ctx,
 int futhark_entry_bmm_f16(struct futhark_context *ctx, struct futhark_f32_3d **out0,
                           const struct futhark_f16_3d *in0, const struct futhark_f16_3d *in1);
 
+/* entry transpose_f32 (xss: [][]f32): [][]f32 = transpose xss
+ * entry transpose_f32_3d (xsss: [][][]f32): [][][]f32 = map transpose xsss
+ * A manifest transposition: the reference's compiler turns it into a call of the runtime's
+ * map_transpose_4b kernels (rts/opencl/transpose.cl:3-275, launched through
+ * rts/c/gpu.h gpu_map_transpose_4b), which it also inserts around SegOps (row-major
+ * coalescing, the transposed operand of a matrix product). */
+int futhark_entry_transpose_f32(struct futhark_context *ctx, struct futhark_f32_2d **out0,
+                                const struct futhark_f32_2d *in0);
+int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f32_3d **out0,
+                                   const struct futhark_f32_3d *in0);
+
 /* ---- extensions (prefix futhark_b200_): not part of the reference's generated API ----
  * The reference keeps its one CUDA stream private (rts/c/backends/cuda.h:219); a host
  * program that shares a process with other CUDA code needs it to order its own work

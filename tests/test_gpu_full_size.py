@@ -192,3 +192,19 @@ def test_bmm_f16_64x1024(ctx, dev):
     assert float(((C - ref).abs() / bound.clamp_min(1e-6)).max()) <= 1e-2
     assert float(((C - ref).abs() / bound.clamp_min(1e-6)).max()) <= 1e-4
     out.free(); Aa.free(); Ba.free()
+
+
+def test_transpose_f32_131072x1024(ctx, dev):
+    rows, cols = 131072, 1024
+    x = torch.randn(rows, cols, device=dev, generator=gen(dev, 7))
+    ready()
+    a = ctx.new_raw("f32_2d", x.data_ptr(), rows, cols)
+    out = ctx.entry_transpose_f32(a)
+    ctx.sync()
+    o = view(out, dev, torch.float32)
+    assert tuple(o.shape) == (cols, rows)
+    assert torch.equal(o, x.t())
+    back = ctx.entry_transpose_f32(out)                             # transposing twice gives the input back
+    ctx.sync()
+    assert torch.equal(view(back, dev, torch.float32), x)
+    out.free(); back.free(); a.free()
