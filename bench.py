@@ -325,10 +325,13 @@ def main():
     ctx.sync()
 
     def step_resident():
-        # with several GPUs the exchange of the scan's shard summaries runs beside the two reductions
-        pending = group.segscan_f32_begin(d_flags, d_xs) if group is not None else None
+        # with several GPUs the exchange of the scan's shard summaries runs beside the row reduction
+        # (not beside the segmented reduction: its persistent grid fills every CTA slot)
+        pending = group.segscan_f32_begin(d_flags, d_xs, exchange=False) if group is not None else None
         o1 = ctx.entry_segscan_f32(d_flags, d_xs) if group is None else None
         o2 = ctx.entry_segreduce_f32(d_off, d_flags, d_xs)
+        if group is not None:
+            group.segscan_f32_exchange(pending)
         o3 = ctx.entry_rowsum_f32(d_rows)
         if group is not None:
             o1 = group.segscan_f32_finish(pending)

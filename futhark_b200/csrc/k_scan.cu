@@ -611,30 +611,38 @@ __global__ void segscan_summary_kernel(const uint64_t *status, uint32_t last_til
   dst[1] = status_flag(w);
 }
 
-// Position of the first segment start (n if none): CTAs walk 16 KiB chunks in ascending
-// order and stop as soon as a start before their chunk is known.
+// Position of the first segment start (all ones if none): CTAs take 16 KiB chunks in ascending
+// order and stop as soon as a start before their chunk is known.  A chunk is looked at in
+// rounds of 4 KiB, 16 independent byte loads per thread and round, and left at the first
+// round that contains a start: with segments of a few hundred elements that is one round trip.
 __global__ void __launch_bounds__(256)
 first_flag_kernel(const uint8_t *__restrict__ flags, int64_t n, unsigned long long *first) {
-  constexpr int64_t CHUNK = 16384;
+  constexpr int64_t CHUNK = 16384, ROUND = 256 * 16;
   for (int64_t c = blockIdx.x; c * CHUNK < n; c += gridDim.x) {
     const int64_t lo = c * CHUNK;
-    if ((int64_t)*reinterpret_cast<volatile unsigned long long *>(first) < lo) return;
+    if (*reinterpret_cast<volatile unsigned long long *>(first) < (unsigned long long)lo) return;
     const int64_t hi = lo + CHUNK < n ? lo + CHUNK : n;
-    int64_t best = n;
-    for (int64_t i = lo + threadIdx.x; i < hi; i += 256)
-      if (flags[i]) { best = i; break; }
-    if (best < n) atomicMin(first, (unsigned long long)best);
+    for (int64_t base = lo; base < hi; base += ROUND) {
+      const int64_t i0 = base + (int64_t)threadIdx.x * 16;
+      uint32_t mask = 0;
+#pragma unroll
+      for (int k = 0; k < 16; k++)
+        if (i0 + k < hi && flags[i0 + k]) mask |= 1u << k;
+      if (mask) atomicMin(first, (unsigned long long)(i0 + __ffs(mask) - 1));
+      if (__syncthreads_or(mask != 0)) break;       // later rounds and chunks only hold later positions
+    }
   }
 }
 
 // out[i] += carry for i before the first segment start, where carry is the fold of the
 // summaries of the shards before this one under the lifted operator.
 __global__ void __launch_bounds__(256)
-apply_carry_kernel(float *__restrict__ out, const unsigned long long *first, const uint32_t *summaries, int rank) {
+apply_carry_kernel(float *__restrict__ out, int64_t n, const unsigned long long *first, const uint32_t *summaries, int rank) {
   uint32_t cv = 0, cf = 0;
   for (int q = 0; q < rank; q++) OpSegAddF32::combine(cv, cf, summaries[2 * q], summaries[2 * q + 1], cv, cf);
   const float carry = __uint_as_float(cv);
-  const int64_t end = (int64_t)*first;
+  const unsigned long long f = *first;
+  const int64_t end = f < (unsigned long long)n ? (int64_t)f : n;
   const int64_t stride = (int64_t)gridDim.x * 256;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < end; i += stride) out[i] = carry + out[i];
 }
@@ -650,13 +658,14 @@ cudaError_t launch_segscan_summary(void *scratch, int64_t n, uint32_t *dst, cuda
 cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
                                        int rank, unsigned long long *d_first, int num_sms, cudaStream_t stream) {
   if (n <= 0 || rank <= 0) return cudaSuccess;
-  const unsigned long long init = (unsigned long long)n;
-  cudaError_t err = cudaMemcpyAsync(d_first, &init, sizeof(init), cudaMemcpyHostToDevice, stream);
+  // all ones = "no segment start found" (a memset, not a copy from pageable host memory, which
+  // would make the host wait for the stream)
+  cudaError_t err = cudaMemsetAsync(d_first, 0xff, sizeof(unsigned long long), stream);
   if (err != cudaSuccess) return err;
   int64_t chunks = (n + 16383) / 16384;
   int grid = (int)(chunks < (int64_t)num_sms * 4 ? chunks : (int64_t)num_sms * 4);
   first_flag_kernel<<<grid, 256, 0, stream>>>(flags, n, d_first);
-  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, d_first, summaries, rank);
+  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, n, d_first, summaries, rank);
   return cudaGetLastError();
 }
 

@@ -157,19 +157,31 @@ class Group:
     def segscan_f32(self, flags, xs):
         return self.segscan_f32_finish(self.segscan_f32_begin(flags, xs))
 
-    def segscan_f32_begin(self, flags, xs):
-        """Local scan and the exchange of the shard summaries.  The exchange runs beside the
-        stream of the kernels (where the executor has a second stream), so whatever the
-        caller launches before `segscan_f32_finish` overlaps it."""
+    def segscan_f32_begin(self, flags, xs, exchange=True):
+        """Local scan and (unless `exchange` is False: then call `segscan_f32_exchange` later)
+        the exchange of the shard summaries.  The exchange runs beside the stream of the
+        kernels (where the executor has a second stream), so whatever the caller launches
+        between the exchange and `segscan_f32_finish` overlaps it.  A collective's kernel takes
+        a few CTA slots: a persistent kernel sized to fill the GPU should not be what overlaps it."""
         summaries = self.local.empty(2 * self.world, torch.int32)
         mine = summaries[2 * self.rank:2 * self.rank + 2]
         out = self.local.segscan_shard(flags, xs, mine)
+        pending = [out, flags, summaries, False]
+        if exchange:
+            self.segscan_f32_exchange(pending)
+        return pending
+
+    def segscan_f32_exchange(self, pending):
+        summaries = pending[2]
+        mine = summaries[2 * self.rank:2 * self.rank + 2]
         with self.local.exchange_stream():
             dist.all_gather_into_tensor(summaries, mine.clone(), group=self.pg)
-        return out, flags, summaries
+        pending[3] = True
 
     def segscan_f32_finish(self, pending):
-        out, flags, summaries = pending
+        if not pending[3]:
+            self.segscan_f32_exchange(pending)
+        out, flags, summaries, _ = pending
         self.local.exchange_done()
         self.local.segscan_apply(out, flags, summaries, self.rank)
         return out
