@@ -89,6 +89,7 @@ def load():
     L.futhark_b200_context_get_device.argtypes = [vp]
     L.futhark_b200_context_get_launch_count.restype = i64
     L.futhark_b200_context_get_launch_count.argtypes = [vp]
+    L.futhark_b200_debug_expire_wait.argtypes = [vp, ci]
     L.futhark_context_pause_profiling.argtypes = [vp]
     L.futhark_context_unpause_profiling.argtypes = [vp]
     for name, (_, rank, ct) in ARRAY_TYPES.items():
@@ -281,6 +282,10 @@ class Context:
     @property
     def device(self):
         return int(self.lib.futhark_b200_context_get_device(self.ptr))
+
+    def debug_expire_wait(self, max_polls=1000):
+        """Enqueue a bounded wait that runs out (futhark_b200_debug_expire_wait)."""
+        self._check(self.lib.futhark_b200_debug_expire_wait(self.ptr, max_polls))
 
     @property
     def launch_count(self):

@@ -311,6 +311,18 @@ int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f
   return FUTHARK_SUCCESS;
 }
 
+int futhark_b200_debug_expire_wait(struct futhark_context *ctx, int max_polls) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  int rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(1));
+  if (rc != 0) return rc;
+  ctx->launch_count++;
+  rc = fb_cuda_check(ctx, fb::launch_expire_wait(ctx->lookback_scratch, fb_next_epoch(ctx), (uint32_t)(max_polls < 1 ? 1 : max_polls),
+                                                 ctx->d_failure, ctx->stream), "expire_wait");
+  ctx->failure_is_an_option = true;
+  return rc;
+}
+
 // ---- shard-local pieces for arrays split across several contexts (extensions) -------------------
 
 int futhark_b200_reduce_i32_to_device(struct futhark_context *ctx, CUdeviceptr dst, const struct futhark_i32_1d *in0) {

@@ -678,6 +678,28 @@ cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out
   return partition ? launch_stream<K_PARTITION>(a, stream) : launch_stream<K_FILTER>(a, stream);
 }
 
+// ---- a wait that runs out, on purpose -------------------------------------------------------------
+// One warp waits, as visit B of a tile does, for a status word that nothing will publish
+// under this epoch, with a small poll limit; when the limit is reached it records
+// FAIL_LOOKBACK_TIMEOUT in the failure word and returns.  This is how the failure protocol
+// (failure word -> futhark_context_sync -> FUTHARK_PROGRAM_ERROR -> scratch reset) is exercised
+// on a GPU without faulting, trapping or hanging anything.
+__global__ void expire_wait_kernel(const uint64_t *status, uint32_t epoch, uint32_t max_polls, int *failure) {
+  if (threadIdx.x != 0) return;
+  for (uint32_t polls = 0; polls < max_polls; polls++) {
+    if (status_state(ld_status(status), epoch) != ST_NONE) return;      // never happens: nobody publishes under this epoch
+    __nanosleep(100);
+  }
+  atomicCAS(failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT);
+}
+
+cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls, int *failure, cudaStream_t stream) {
+  uint32_t *ticket; uint64_t *status;
+  split_scratch(scratch, &ticket, &status);
+  expire_wait_kernel<<<1, 32, 0, stream>>>(status, epoch, max_polls > 100000u ? 100000u : max_polls, failure);
+  return cudaGetLastError();
+}
+
 // ---- scan (+) i32 without any allocation ---------------------------------------------------------
 // Some hosts hand this library a GPU whose memory is already fully parcelled out by their
 // own arena allocator, or run it inside a region of their program where a call that may

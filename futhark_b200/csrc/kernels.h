@@ -17,6 +17,8 @@ cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t 
                             const int32_t *carry_vals, int carry_n, void *scratch,
                             uint32_t epoch, int *failure, cudaStream_t stream);
 // After launch_segscan_f32 on the same scratch: writes the shard summary {f32 bits, flag}.
+// A bounded wait on a status word that is never published: records FAIL_LOOKBACK_TIMEOUT.
+cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls, int *failure, cudaStream_t stream);
 cudaError_t launch_segscan_summary(void *scratch, int64_t n, uint32_t *dst, cudaStream_t stream);
 // Adds the fold of summaries[0..rank) to out[0 .. first segment start).
 cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,

@@ -253,6 +253,14 @@ int futhark_b200_context_get_device(struct futhark_context *ctx);
 /* Number of kernel launches issued by the context so far. */
 int64_t futhark_b200_context_get_launch_count(struct futhark_context *ctx);
 
+/* Failure-path check that faults nothing: enqueues one warp that waits, like a scan tile,
+ * for a tile status word that is never published, gives up after `max_polls` polls of
+ * ~100 ns (at most 100000) and records the look-back time-out in the context's failure
+ * word.  The next futhark_context_sync then returns FUTHARK_PROGRAM_ERROR with a message,
+ * clears the failure and resets the scan scratch, as after a real time-out
+ * (the global_failure protocol of rts/c/backends/cuda.h:719-754); the context stays usable. */
+int futhark_b200_debug_expire_wait(struct futhark_context *ctx, int max_polls);
+
 /* Shard-local pieces, for one logical array split into contiguous shards over several
  * contexts (one per GPU).  The reference is single-device (rts/c/backends/cuda.h:219) and has
  * no counterpart.  All are asynchronous; device pointers passed in must belong to the

@@ -120,3 +120,33 @@ def test_values_pending_when_the_array_is_freed_and_its_block_reused(ctx):
     assert np.array_equal(host, oracle.scan_i32(xs))
     assert np.array_equal(host2, oracle.scan_i32(ys))
     a.free(); b.free(); out2.free()
+
+
+def test_a_wait_that_runs_out_is_reported_at_sync_and_the_context_stays_usable(ctx):
+    """The failure protocol end to end, without faulting anything: a warp waits (bounded) for a
+    tile status word that nobody publishes, records the time-out in the failure word;
+    futhark_context_sync reports it as a program error with a message, clears it and resets the
+    scan scratch; the next entry points work."""
+    import oracle
+    from futhark_b200 import datagen
+    ctx.debug_expire_wait(500)
+    with pytest.raises(fb.FutharkError) as e:
+        ctx.sync()
+    assert e.value.code == fb.FUTHARK_PROGRAM_ERROR
+    assert "waited too long" in e.value.message
+    ctx.sync()                                   # the failure has been consumed
+    xs = datagen.workload_i32(5 * 5120 + 3)
+    assert np.array_equal(fb.scan_i32(ctx, xs), oracle.scan_i32(xs))
+    ks = datagen.workload_keys_u32(100003)
+    assert np.array_equal(fb.filter_u32(ctx, ks), oracle.filter_u32(ks))
+    # an entry point launched while the failure is pending does nothing; after the sync it works again
+    ctx.debug_expire_wait(500)
+    a = ctx.new("i32_1d", xs)
+    out = ctx.entry_scan_i32(a)
+    with pytest.raises(fb.FutharkError):
+        ctx.sync()
+    out.free()
+    out = ctx.entry_scan_i32(a)
+    got = out.values()
+    assert np.array_equal(got, oracle.scan_i32(xs))
+    out.free(); a.free()
