@@ -12,7 +12,7 @@
 // differs:
 //
 //   * A tile is visited twice.  Visit A only computes the tile's aggregate and publishes
-//     it.  Visit B, drawn from the same counter about SCAN_LEAD tiles later, scans the
+//     it.  Visit B, drawn from the same counter about 20 MiB of input later, scans the
 //     tile, adds its exclusive prefix and stores.  Visit A reads the tile from HBM and
 //     leaves it in L2, where visit B finds it, so HBM traffic stays at one read and one
 //     write per element.  Because the aggregates run that far ahead, the prefix a visit B
@@ -56,17 +56,22 @@ namespace fb {
 
 constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_WARPS = SCAN_THREADS / 32;
-constexpr int SCAN_V = 5;                                 // 16-byte vectors per thread: odd, see the kernel
-constexpr int SCAN_ITEMS = SCAN_V * 4;                    // consecutive elements per thread
-constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;      // 5120 elements
-#ifndef FB_LEAD
-#define FB_LEAD 1024
-#endif
-constexpr int SCAN_LEAD = FB_LEAD;                        // tiles by which visit A runs ahead of visit B (16 MiB of input)
-#ifndef FB_CTAS
-#define FB_CTAS 4
-#endif
-constexpr int SCAN_CTAS_PER_SM = FB_CTAS;                  // register budget: 65536 / (256 * 4) = 64
+enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3 };
+
+// Tile geometry per kind.  A thread owns V 16-byte vectors = 4V consecutive elements; V is odd
+// (see the kernel).  The scans take 5 (tiles of 5120 elements, 4 CTAs per SM); compaction,
+// whose second visit has three barriers, amortises them over 7 (7168 keys, 3 CTAs per SM).
+// LEAD = tiles by which visit A runs ahead of visit B: about 20 MiB of input either way (with
+// a quarter of it visit B waits; with twice as much the tile has left L2 before visit B).
+template <int KIND> struct TileCfg {
+  static constexpr bool kCompact = (KIND == K_FILTER || KIND == K_PARTITION);
+  static constexpr int V = kCompact ? 7 : 5;
+  static constexpr int ITEMS = V * 4;
+  static constexpr int TILE = SCAN_THREADS * ITEMS;
+  static constexpr int LEAD = kCompact ? 736 : 1024;
+  static constexpr int CTAS = kCompact ? 3 : 4;
+};
+constexpr int SCAN_TILE_MIN = TileCfg<K_SCAN_I32>::TILE;     // the smallest tile: bounds the number of status words
 constexpr int PROP_PER_LANE = 8;                          // status words per lane per round of the propagator
 constexpr int PROP_WINDOW = 32 * PROP_PER_LANE;
 constexpr uint32_t WAIT_MAX_ROUNDS = 1u << 22;            // idle polls before a wait gives up
@@ -171,7 +176,6 @@ __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, ui
 }
 
 // ---- the persistent tile kernel ------------------------------------------------------------------
-enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3 };
 
 struct LookbackArgs {
   const void *in;          // values / keys
@@ -226,12 +230,12 @@ struct WorkMap {
 };
 
 template <int KIND>
-__global__ void __launch_bounds__(SCAN_THREADS, SCAN_CTAS_PER_SM)
+__global__ void __launch_bounds__(SCAN_THREADS, TileCfg<KIND>::CTAS)
 stream_kernel(const LookbackArgs a) {
-  constexpr int V = SCAN_V, ITEMS = SCAN_ITEMS;
+  constexpr int V = TileCfg<KIND>::V, ITEMS = TileCfg<KIND>::ITEMS, TILE = TileCfg<KIND>::TILE;
   constexpr bool SEG = (KIND == K_SEGSCAN_F32);
   constexpr bool COMPACT = (KIND == K_FILTER || KIND == K_PARTITION);
-  constexpr int SB = SCAN_TILE * 4 + (SEG ? SCAN_TILE : 64);     // bytes of a tile buffer (compaction stages with up to 9 words of padding)
+  constexpr int SB = TILE * 4 + (SEG ? TILE : 64);     // bytes of a tile buffer (compaction stages with up to 9 words of padding)
   using Op = typename std::conditional<SEG, OpSegAddF32, OpAddU32>::type;
   extern __shared__ __align__(128) unsigned char s_buf[];   // two tile buffers
   __shared__ __align__(8) uint64_t s_bar[2];
@@ -264,7 +268,7 @@ stream_kernel(const LookbackArgs a) {
   const uint32_t workers = solo ? 1u : gridDim.x - 1;
   WorkMap wm;
   wm.nt = nt;
-  wm.lead = nt < (uint32_t)SCAN_LEAD ? nt : (uint32_t)SCAN_LEAD;
+  wm.lead = nt < (uint32_t)TileCfg<KIND>::LEAD ? nt : (uint32_t)TileCfg<KIND>::LEAD;
   // Every worker draws work items until it meets one past the end, so the counter ends at
   // total + workers; whoever draws that last value rewinds it for the next launch.
   const uint32_t last_value = wm.total() + workers - 1;
@@ -284,14 +288,14 @@ stream_kernel(const LookbackArgs a) {
     return (t << 1) | (ia ? 1u : 0u);
   };
   auto item_is_bulk = [&](uint32_t item) -> bool {
-    return item != ITEM_NONE && in_bulk && ((int64_t)((item >> 1) + 1) * SCAN_TILE <= a.n);
+    return item != ITEM_NONE && in_bulk && ((int64_t)((item >> 1) + 1) * TILE <= a.n);
   };
   auto arm = [&](int b, uint32_t tile) {   // thread 0: start the copies of a tile into buffer b
     unsigned char *dst = s_buf + b * SB;
-    const int64_t tb = (int64_t)tile * SCAN_TILE;
-    mbar_expect_tx(&s_bar[b], SCAN_TILE * 4 + (SEG ? SCAN_TILE : 0));
-    bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, SCAN_TILE * 4, &s_bar[b]);
-    if (SEG) bulk_g2s(dst + SCAN_TILE * 4, a.flags + tb, SCAN_TILE, &s_bar[b]);
+    const int64_t tb = (int64_t)tile * TILE;
+    mbar_expect_tx(&s_bar[b], TILE * 4 + (SEG ? TILE : 0));
+    bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, TILE * 4, &s_bar[b]);
+    if (SEG) bulk_g2s(dst + TILE * 4, a.flags + tb, TILE, &s_bar[b]);
   };
   auto draw = [&]() -> uint32_t {          // thread 0
     const uint32_t w = atomicAdd(&a.ticket[0], 1u);
@@ -330,9 +334,9 @@ stream_kernel(const LookbackArgs a) {
     // ---- the tile: in the buffer, by the bulk copy or (ragged / unaligned) copied in by the threads
     unsigned char *buf = s_buf + par * SB;
     uint32_t *s_tile = reinterpret_cast<uint32_t *>(buf);
-    const int64_t base = (int64_t)tile * SCAN_TILE;
-    const int count = (int)((a.n - base) < SCAN_TILE ? (a.n - base) : SCAN_TILE);
-    const bool full = (count == SCAN_TILE);
+    const int64_t base = (int64_t)tile * TILE;
+    const int count = (int)((a.n - base) < TILE ? (a.n - base) : TILE);
+    const bool full = (count == TILE);
     if (full && in_bulk) {
       if (!mbar_wait_bounded(&s_bar[par], (phases >> par) & 1u)) {
         atomicCAS(a.failure, FAIL_NONE, FAIL_BULK_COPY_TIMEOUT);
@@ -342,11 +346,11 @@ stream_kernel(const LookbackArgs a) {
       if (tid == 0) armed &= ~(1u << par);
     } else {
       const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
-      for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS)
+      for (int i = tid; i < TILE; i += SCAN_THREADS)
         s_tile[i] = (i < count) ? gin[i] : (COMPACT ? 0xffffffffu : 0u);     // padding: never selected / identity
       if (SEG) {
-        unsigned char *sfb = buf + SCAN_TILE * 4;
-        for (int i = tid; i < SCAN_TILE; i += SCAN_THREADS) sfb[i] = (i < count) ? a.flags[base + i] : (unsigned char)0;
+        unsigned char *sfb = buf + TILE * 4;
+        for (int i = tid; i < TILE; i += SCAN_THREADS) sfb[i] = (i < count) ? a.flags[base + i] : (unsigned char)0;
       }
       __syncthreads();
     }
@@ -364,7 +368,7 @@ stream_kernel(const LookbackArgs a) {
     uint32_t bits = 0;                   // segment starts (segmented scan) / selected keys (compaction)
     uint32_t tv_thread, tf_thread = 0;   // the thread's aggregate
     if (SEG) {
-      const uint32_t *sf = reinterpret_cast<const uint32_t *>(buf + SCAN_TILE * 4) + tid * V;
+      const uint32_t *sf = reinterpret_cast<const uint32_t *>(buf + TILE * 4) + tid * V;
       uint32_t fw[V];
 #pragma unroll
       for (int j = 0; j < V; j++) fw[j] = sf[j];
@@ -477,7 +481,7 @@ stream_kernel(const LookbackArgs a) {
       if (full && out_bulk) {
         fence_proxy_async_smem();        // the bulk store reads what the threads just wrote
         __syncthreads();
-        if (tid == 0) { bulk_s2g(gout, s_tile, SCAN_TILE * 4); bulk_commit(); }
+        if (tid == 0) { bulk_s2g(gout, s_tile, TILE * 4); bulk_commit(); }
       } else {
         __syncthreads();
         for (int i = tid; i < count; i += SCAN_THREADS) gout[i] = s_tile[i];
@@ -529,10 +533,11 @@ stream_kernel(const LookbackArgs a) {
 
 // ---- host launchers --------------------------------------------------------------------
 
-static inline uint32_t tiles_for(int64_t n) { return (uint32_t)((n + SCAN_TILE - 1) / SCAN_TILE); }
+template <int KIND>
+static inline uint32_t tiles_for(int64_t n) { return (uint32_t)((n + TileCfg<KIND>::TILE - 1) / TileCfg<KIND>::TILE); }
 
 size_t lookback_scratch_bytes(int64_t n) {
-  return 256 + (size_t)tiles_for(n) * sizeof(uint64_t);
+  return 256 + (size_t)((n + SCAN_TILE_MIN - 1) / SCAN_TILE_MIN) * sizeof(uint64_t);
 }
 
 static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **status) {
@@ -545,7 +550,7 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
 // cached per kind and device.
 template <int KIND>
 static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
-  constexpr size_t smem = 2 * (size_t)(SCAN_TILE * 4 + (KIND == K_SEGSCAN_F32 ? SCAN_TILE : 64));
+  constexpr size_t smem = 2 * (size_t)(TileCfg<KIND>::TILE * 4 + (KIND == K_SEGSCAN_F32 ? TileCfg<KIND>::TILE : 64));
   static int ctas_per_sm_dev[64], num_sms_dev[64];     // per device ordinal (function attributes are per device)
   int dev = 0;
   cudaGetDevice(&dev);
@@ -570,11 +575,12 @@ static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+template <int KIND>
 static LookbackArgs make_args(const void *in, const uint8_t *flags, void *out, uint32_t *out_false, int64_t n,
                               void *scratch, uint32_t epoch, int *failure) {
   LookbackArgs a;
   a.in = in; a.flags = flags; a.out = out; a.out_false = out_false; a.n = n;
-  a.num_tiles = tiles_for(n);
+  a.num_tiles = tiles_for<KIND>(n);
   split_scratch(scratch, &a.ticket, &a.status);
   a.epoch = epoch; a.failure = failure;
   a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr;
@@ -585,7 +591,7 @@ cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t 
                             const int32_t *carry_vals, int carry_n, void *scratch,
                             uint32_t epoch, int *failure, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  LookbackArgs a = make_args(in, nullptr, out, nullptr, n, scratch, epoch, failure);
+  LookbackArgs a = make_args<K_SCAN_I32>(in, nullptr, out, nullptr, n, scratch, epoch, failure);
   a.carry_in = (uint32_t)carry_in;
   a.carry_vals = reinterpret_cast<const uint32_t *>(carry_vals);
   a.carry_n = carry_n;
@@ -595,7 +601,7 @@ cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t 
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
                                void *scratch, uint32_t epoch, int *failure, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  LookbackArgs a = make_args(in, flags, out, nullptr, n, scratch, epoch, failure);
+  LookbackArgs a = make_args<K_SEGSCAN_F32>(in, flags, out, nullptr, n, scratch, epoch, failure);
   uint32_t bits;
   memcpy(&bits, &carry_in, 4);
   a.carry_in = bits;
@@ -651,7 +657,7 @@ cudaError_t launch_segscan_summary(void *scratch, int64_t n, uint32_t *dst, cuda
   if (n <= 0) return cudaMemsetAsync(dst, 0, 8, stream);   // (0, no flag): the identity
   uint32_t *ticket; uint64_t *status;
   split_scratch(scratch, &ticket, &status);
-  segscan_summary_kernel<<<1, 1, 0, stream>>>(status, tiles_for(n) - 1, dst);
+  segscan_summary_kernel<<<1, 1, 0, stream>>>(status, tiles_for<K_SEGSCAN_F32>(n) - 1, dst);
   return cudaGetLastError();
 }
 
@@ -673,7 +679,7 @@ cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out
                                int64_t n, int64_t *d_count, void *scratch, uint32_t epoch, int *failure,
                                cudaStream_t stream) {
   if (n <= 0) return cudaMemsetAsync(d_count, 0, sizeof(int64_t), stream);
-  LookbackArgs a = make_args(in, nullptr, out_true, out_false, n, scratch, epoch, failure);
+  LookbackArgs a = make_args<K_FILTER>(in, nullptr, out_true, out_false, n, scratch, epoch, failure);   // the two kinds share their geometry
   a.d_count = d_count;
   return partition ? launch_stream<K_PARTITION>(a, stream) : launch_stream<K_FILTER>(a, stream);
 }
@@ -709,7 +715,7 @@ cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls
 // fixed array below instead of in pooled memory.  The array is part of the loaded library
 // image: every GPU that loads the library holds these ~103 KiB until the process exits.
 constexpr int64_t NOALLOC_MAX_N = (int64_t)1 << 26;
-constexpr uint32_t NOALLOC_MAX_TILES = (uint32_t)((NOALLOC_MAX_N + SCAN_TILE - 1) / SCAN_TILE);
+constexpr uint32_t NOALLOC_MAX_TILES = (uint32_t)((NOALLOC_MAX_N + TileCfg<K_SCAN_I32>::TILE - 1) / TileCfg<K_SCAN_I32>::TILE);
 constexpr size_t NOALLOC_HEAD = 512;     // [0,4) ticket, [256,260) failure word
 constexpr size_t NOALLOC_BYTES = NOALLOC_HEAD + (size_t)NOALLOC_MAX_TILES * sizeof(uint64_t);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
@@ -764,7 +770,7 @@ extern "C" int futhark_b200_scan_i32_noalloc(const int32_t *in, int32_t *out, in
   if (n > 0) {
     LookbackArgs a;
     a.in = in; a.flags = nullptr; a.out = out; a.out_false = nullptr; a.n = n;
-    a.num_tiles = (uint32_t)((n + SCAN_TILE - 1) / SCAN_TILE);
+    a.num_tiles = tiles_for<K_SCAN_I32>(n);
     a.ticket = reinterpret_cast<uint32_t *>(base);
     a.status = reinterpret_cast<uint64_t *>(base + NOALLOC_HEAD);
     a.epoch = epoch; a.failure = failure;
