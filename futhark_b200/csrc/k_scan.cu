@@ -505,22 +505,27 @@ stream_kernel(const LookbackArgs a) {
         if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
         else if (KIND == K_PARTITION && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
       }
+      fence_proxy_async_smem();          // the bulk stores below read what the threads just staged
       __syncthreads();
-      auto copy_run = [&](uint32_t *g, uint32_t s0, uint32_t len) {
-        // g and s_tile + s0 are congruent modulo 16 bytes
-        uint32_t h = (4u - (s0 & 3u)) & 3u;
-        if (h > len) h = len;
-        const uint32_t nvec = (len - h) >> 2, tail0 = h + (nvec << 2);
-        if ((uint32_t)tid < h) g[tid] = s_tile[s0 + tid];
-        const int4 *sv = reinterpret_cast<const int4 *>(s_tile + s0 + h);
-        int4 *gv = reinterpret_cast<int4 *>(g + h);
-        for (uint32_t v = tid; v < nvec; v += SCAN_THREADS) gv[v] = sv[v];
-        if ((uint32_t)tid < len - tail0) g[tail0 + tid] = s_tile[s0 + tail0 + tid];
-      };
-      copy_run(dst, pad_t, tile_true);
-      if (KIND == K_PARTITION) copy_run(dstf, start_f, (uint32_t)count - tile_true);
+      // Each run leaves as one bulk store of its 16-byte aligned body, issued by thread 0, plus up
+      // to three keys in front and behind, stored by lanes of warp 0.
+      if (warp == 0) {
+        auto send_run = [&](uint32_t *g, uint32_t s0, uint32_t len, int lane0) {
+          // g and s_tile + s0 are congruent modulo 16 bytes
+          uint32_t h = (4u - (s0 & 3u)) & 3u;
+          if (h > len) h = len;
+          const uint32_t nvec = (len - h) >> 2, tail0 = h + (nvec << 2);
+          const uint32_t l = (uint32_t)(lane - lane0);               // lanes lane0 .. lane0+2 take the ends
+          if (l < h) g[l] = s_tile[s0 + l];
+          if (l < len - tail0) g[tail0 + l] = s_tile[s0 + tail0 + l];
+          if (lane == 0 && nvec > 0) bulk_s2g(g + h, s_tile + s0 + h, nvec << 4);
+        };
+        send_run(dst, pad_t, tile_true, 0);
+        if (KIND == K_PARTITION) send_run(dstf, start_f, (uint32_t)count - tile_true, 4);
+        if (lane == 0) bulk_commit();
+        __syncwarp();                    // thread 0 fills the buffer again only after these lanes have read their keys
+      }
       if (tile == nt - 1 && tid == 0) *a.d_count = true_before + (int64_t)tile_true;
-      __syncthreads();                   // the buffer is filled again at the top of the next iteration
     }
   }
   if (tid == 0) {
