@@ -59,19 +59,22 @@ constexpr int SCAN_WARPS = SCAN_THREADS / 32;
 enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3 };
 
 // Tile geometry per kind.  A thread owns V 16-byte vectors = 4V consecutive elements; V is odd
-// (see the kernel).  The scans take 5 (tiles of 5120 elements, 4 CTAs per SM); compaction,
-// whose second visit has three barriers, amortises them over 7 (7168 keys, 3 CTAs per SM).
-// LEAD = tiles by which visit A runs ahead of visit B: about 20 MiB of input either way (with
-// a quarter of it visit B waits; with twice as much the tile has left L2 before visit B).
+// (see the kernel).  The scans take 5 (tiles of 5120 elements, 4 CTAs per SM: larger tiles
+// were measured slower).  Compaction, whose second visit does much more per tile, takes 9
+// (9216 keys, 3 CTAs per SM, which just fit their 74 KB of buffers each; one bit per key of a
+// thread then needs a 64-bit mask): the filter is 11 % faster than with 7, partition the same.
+// LEAD = tiles by which visit A runs ahead of visit B: 20 MiB of input for the scans, 36 MiB
+// for compaction (with a quarter of it visit B waits; with twice as much the tile has left
+// L2 before visit B).
 template <int KIND> struct TileCfg {
   static constexpr bool kCompact = (KIND == K_FILTER || KIND == K_PARTITION);
-  static constexpr int V = kCompact ? 7 : 5;
+  static constexpr int V = kCompact ? 9 : 5;
   static constexpr int ITEMS = V * 4;
   static constexpr int TILE = SCAN_THREADS * ITEMS;
-  static constexpr int LEAD = kCompact ? 736 : 1024;
+  static constexpr int LEAD = 1024;
   static constexpr int CTAS = kCompact ? 3 : 4;
 };
-constexpr int SCAN_TILE_MIN = TileCfg<K_SCAN_I32>::TILE;     // the smallest tile: bounds the number of status words
+constexpr int SCAN_TILE_MIN = TileCfg<K_SCAN_I32>::TILE;     // the smallest tile: bounds the number of status words     // the smallest tile: bounds the number of status words
 constexpr int PROP_PER_LANE = 8;                          // status words per lane per round of the propagator
 constexpr int PROP_WINDOW = 32 * PROP_PER_LANE;
 constexpr uint32_t WAIT_MAX_ROUNDS = 1u << 22;            // idle polls before a wait gives up
@@ -365,7 +368,9 @@ stream_kernel(const LookbackArgs a) {
         x[4 * j + 0] = q.x; x[4 * j + 1] = q.y; x[4 * j + 2] = q.z; x[4 * j + 3] = q.w;
       }
     }
-    uint32_t bits = 0;                   // segment starts (segmented scan) / selected keys (compaction)
+    using mask_t = typename std::conditional<(ITEMS > 32), unsigned long long, uint32_t>::type;
+    static_assert(ITEMS <= 64 && (SEG ? ITEMS <= 32 : true), "one bit per element of the thread");
+    mask_t bits = 0;                     // segment starts (segmented scan) / selected keys (compaction)
     uint32_t tv_thread, tf_thread = 0;   // the thread's aggregate
     if (SEG) {
       const uint32_t *sf = reinterpret_cast<const uint32_t *>(buf + TILE * 4) + tid * V;
@@ -377,7 +382,7 @@ stream_kernel(const LookbackArgs a) {
       for (int q = 0; q < ITEMS; q++) {
         const bool fl = ((fw[q >> 2] >> (8 * (q & 3))) & 0xffu) != 0;
         const float v = __uint_as_float(x[q]);
-        if (fl) { acc = v; bits |= 1u << q; } else acc = acc + v;
+        if (fl) { acc = v; bits |= (mask_t)1 << q; } else acc = acc + v;
         x[q] = __float_as_uint(acc);
       }
       tv_thread = __float_as_uint(acc);
@@ -385,8 +390,8 @@ stream_kernel(const LookbackArgs a) {
     } else if (COMPACT) {
 #pragma unroll
       for (int q = 0; q < ITEMS; q++)
-        if ((x[q] & 7u) < 3u) bits |= 1u << q;
-      tv_thread = __popc(bits);
+        if ((x[q] & 7u) < 3u) bits |= (mask_t)1 << q;
+      tv_thread = (ITEMS > 32) ? (uint32_t)__popcll((unsigned long long)bits) : (uint32_t)__popc((uint32_t)bits);
     } else if (is_a) {
       uint32_t s = 0;
 #pragma unroll
@@ -462,7 +467,7 @@ stream_kernel(const LookbackArgs a) {
         // before the thread's first segment start its left neighbours count, and before the
         // tile's first segment start the incoming prefix as well
         const float left = lf ? __uint_as_float(lv) : __uint_as_float(ev) + __uint_as_float(lv);
-        const int first = bits ? (__ffs(bits) - 1) : ITEMS;
+        const int first = bits ? (__ffs((uint32_t)bits) - 1) : ITEMS;
 #pragma unroll
         for (int q = 0; q < ITEMS; q++)
           if (q < first) x[q] = __float_as_uint(left + __uint_as_float(x[q]));
