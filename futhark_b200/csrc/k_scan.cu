@@ -327,11 +327,13 @@ stream_kernel(const LookbackArgs a) {
     uint32_t drawn = ITEM_NONE;
     uint64_t pw = 0;                     // visit B: status word of the tile before
     if (tid == 0) {
-      bulk_wait_read0();                 // the bulk store of the previous iteration has read its buffer
       const uint32_t i1 = s_item[(it + 1) % 3];
+      uint32_t raw = 0xffffffffu;
+      if (i1 != ITEM_NONE) raw = draw();                           // the item after next; its round trip to L2 ...
+      if (!is_a && tile > 0) pw = ld_status(&a.status[tile - 1]);  // ... and this one overlap the wait below
+      bulk_wait_read0();                 // the bulk store of the previous iteration has read its buffer
       if (item_is_bulk(i1)) { arm(par ^ 1, i1 >> 1); armed |= 1u << (par ^ 1); }
-      if (i1 != ITEM_NONE) drawn = encode(draw());                // the item after next; stored before the barrier
-      if (!is_a && tile > 0) pw = ld_status(&a.status[tile - 1]);
+      if (i1 != ITEM_NONE) drawn = encode(raw);                    // stored before the barrier
     }
 
     // ---- the tile: in the buffer, by the bulk copy or (ragged / unaligned) copied in by the threads
