@@ -159,6 +159,7 @@ CASES = {
     "scan_i32": 1 << 26, "reduce_i32": 1 << 26, "segscan_f32": 1 << 27, "segreduce_f32": 1 << 27,
     "rowsum_f32": 1 << 27, "hist_add_i32": 1 << 28, "hist_max_f32": 1 << 28, "filter_u32": 1 << 28,
     "partition_u32": 1 << 28, "bmm_f16": 64, "transpose_f32": 1 << 27,
+    "exscan_i32": 1 << 26, "mss_i32": 1 << 26, "sum_i32_f32": 1 << 26,
 }
 
 
@@ -224,12 +225,12 @@ def run_case(args):
         if name.startswith("hist"):
             continue
         a = []
-        if name in ("scan_i32", "reduce_i32"):
+        if name in ("scan_i32", "reduce_i32", "exscan_i32", "mss_i32", "sum_i32_f32"):
             a = [ctx.new("i32_1d", datagen.workload_i32(n))]
-            if name == "scan_i32":
-                timed(name, lambda: ctx.entry_scan_i32(a[0]), 8 * n, n)
+            if name in ("scan_i32", "exscan_i32"):
+                timed(name, lambda: getattr(ctx, "entry_" + name)(a[0]), 8 * n, n)
             else:
-                timed(name, lambda: ctx.entry_reduce_i32(a[0]), 4 * n, n)
+                timed(name, lambda: getattr(ctx, "entry_" + name)(a[0]), 4 * n, n)
         elif name in ("segscan_f32", "segreduce_f32"):
             offsets, flags, xs = datagen.workload_seg_f32(n)
             a = [ctx.new("i64_1d", offsets), ctx.new("bool_1d", flags.view(np.bool_)), ctx.new("f32_1d", xs)]

@@ -124,6 +124,9 @@ def load():
     L.futhark_entry_bmm_f16.argtypes = [vp, pvp, vp, vp]
     L.futhark_entry_transpose_f32.argtypes = [vp, pvp, vp]
     L.futhark_entry_transpose_f32_3d.argtypes = [vp, pvp, vp]
+    L.futhark_entry_exscan_i32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_mss_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+    L.futhark_entry_sum_i32_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float), vp]
     _lib = L
     return L
 
@@ -363,6 +366,19 @@ class Context:
     def entry_transpose_f32_3d(self, xsss):
         return self._entry_arr("transpose_f32_3d", "f32_3d", xsss.ptr)
 
+    def entry_exscan_i32(self, xs):
+        return self._entry_arr("exscan_i32", "i32_1d", xs.ptr)
+
+    def entry_mss_i32(self, xs):
+        out = ctypes.c_int32()
+        self._check(self.lib.futhark_entry_mss_i32(self.ptr, ctypes.byref(out), xs.ptr))
+        return int(out.value)
+
+    def entry_sum_i32_f32(self, xs):
+        oi, of = ctypes.c_int32(), ctypes.c_float()
+        self._check(self.lib.futhark_entry_sum_i32_f32(self.ptr, ctypes.byref(oi), ctypes.byref(of), xs.ptr))
+        return int(oi.value), float(of.value)
+
 
 # ---- host-buffer conveniences: new -> entry -> values -> free, as a C caller would ----
 
@@ -389,6 +405,26 @@ def reduce_i32(ctx, xs):
         return ctx.entry_reduce_i32(a)
     finally:
         a.free()
+
+
+def exscan_i32(ctx, xs):
+    return _run(ctx, [("i32_1d", xs)], ctx.entry_exscan_i32)
+
+
+def _scalar(ctx, xs, fn):
+    a = ctx.new("i32_1d", xs)
+    try:
+        return fn(a)
+    finally:
+        a.free()
+
+
+def mss_i32(ctx, xs):
+    return _scalar(ctx, xs, ctx.entry_mss_i32)
+
+
+def sum_i32_f32(ctx, xs):
+    return _scalar(ctx, xs, ctx.entry_sum_i32_f32)
 
 
 def segscan_f32(ctx, flags, xs):

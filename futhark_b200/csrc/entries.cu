@@ -39,6 +39,21 @@ static int not_ready(futhark_context *ctx) {
   return 1;
 }
 
+// Launch a fused redomap whose result is `bytes` of scalars, read them back and wait
+// (scalar results are synchronous: Backends/GPU.hs:269-281).
+template <typename LAUNCH>
+static int scalar_redomap(futhark_context *ctx, const char *name, const char *prov, int64_t n, size_t bytes, LAUNCH launch) {
+  int rc;
+  {
+    LaunchScope ls(ctx, name, prov, "{" + kv("n", n) + "}");
+    rc = fb_cuda_check(ctx, launch(), name);
+  }
+  if (rc) return rc;
+  rc = fb_cuda_check(ctx, cudaMemcpyAsync(ctx->h_scalar, ctx->d_scalar, bytes, cudaMemcpyDeviceToHost, ctx->stream), "scalar read");
+  if (rc) return rc;
+  return fb_cuda_check(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+}
+
 extern "C" {
 
 int futhark_entry_scan_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_1d *in0) {
@@ -79,6 +94,57 @@ int futhark_entry_reduce_i32(struct futhark_context *ctx, int32_t *out0, const s
   rc = fb_cuda_check(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
   if (rc) return rc;
   *out0 = *reinterpret_cast<int32_t *>(ctx->h_scalar);
+  return FUTHARK_SUCCESS;
+}
+
+// exscan (+) 0 xs: the same single-pass kernel as scan_i32 with the write-back shifted by one
+// (the reference composes it from a scan and a scatter, prelude/soacs.fut:212-215).
+int futhark_entry_exscan_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  int rc;
+  futhark_i32_1d *out = make_1d<futhark_i32_1d>(ctx, n, 4, "exscan_i32.out", &rc);
+  if (out == nullptr) return rc;
+  if (n > 0) {
+    rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(n));
+    if (rc == 0) {
+      LaunchScope ls(ctx, "exscan_i32.segscan", PROV("exscan (+) 0 xs"), "{" + kv("n", n) + "}");
+      rc = fb_cuda_check(ctx, fb::launch_exscan_i32(dptr<int32_t>(in0->mem), dptr<int32_t>(out->mem), n, ctx->lookback_scratch,
+                                                    fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "exscan_i32");
+      ctx->failure_is_an_option = true;
+    }
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+// Maximum segment sum (tests/mss.fut): map body to 4-tuples, non-commutative tuple operator,
+// first component of the result.
+int futhark_entry_mss_i32(struct futhark_context *ctx, int32_t *out0, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  int rc = scalar_redomap(ctx, "mss_i32.segred_nonseg", PROV("(reduce redOp (0,0,0,0) (map mapOp xs)).0"), n, 16, [&] {
+    return fb::launch_mss_i32(dptr<int32_t>(in0->mem), n, reinterpret_cast<int32_t *>(ctx->d_scalar), ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+  });
+  if (rc) return rc;
+  *out0 = reinterpret_cast<int32_t *>(ctx->h_scalar)[0];
+  return FUTHARK_SUCCESS;
+}
+
+// Two reductions fused over one input (tests/fusion/red-red-fusion.fut): (i32.sum xs, f32.sum (map f32.i32 xs)).
+int futhark_entry_sum_i32_f32(struct futhark_context *ctx, int32_t *out0, float *out1, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  int rc = scalar_redomap(ctx, "sum_i32_f32.segred_nonseg", PROV("(i32.sum xs, f32.sum (map f32.i32 xs))"), n, 8, [&] {
+    return fb::launch_sum_i32_f32(dptr<int32_t>(in0->mem), n, ctx->d_scalar, ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+  });
+  if (rc) return rc;
+  *out0 = reinterpret_cast<int32_t *>(ctx->h_scalar)[0];
+  *out1 = reinterpret_cast<float *>(ctx->h_scalar)[1];
   return FUTHARK_SUCCESS;
 }
 

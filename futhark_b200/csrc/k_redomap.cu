@@ -1,0 +1,53 @@
+// Specifications for the fused-redomap kernel template (redomap.cuh) and their launchers.
+//
+//   mss_i32        maximum segment sum: a map body producing a 4-tuple and a NON-commutative
+//                  operator on 4-tuples of i32 (the program of tests/mss.fut:6-20)
+//   sum_i32_f32    two reductions fused horizontally over one input, the second behind a map
+//                  body: (i32.sum xs, f32.sum (map f32.i32 xs))
+//                  (the program of tests/fusion/red-red-fusion.fut:5)
+//
+// Integer arithmetic wraps like the reference's (rts/c/scalar.h:29: add32 is an unsigned add).
+#include "kernels.h"
+#include "redomap.cuh"
+
+namespace fb {
+
+__device__ __forceinline__ int32_t wadd(int32_t a, int32_t b) { return (int32_t)((uint32_t)a + (uint32_t)b); }
+
+struct SpecMss {
+  // x = best segment sum, y = best prefix sum, z = best suffix sum, w = total
+  using Acc = int4;
+  static constexpr bool commutative = false;
+  __device__ __forceinline__ static Acc neutral() { return make_int4(0, 0, 0, 0); }
+  __device__ __forceinline__ static Acc map(uint32_t bits) {
+    const int32_t x = (int32_t)bits, m = max(x, 0);
+    return make_int4(m, m, m, x);
+  }
+  __device__ __forceinline__ static Acc combine(const Acc &l, const Acc &r) {
+    Acc o;
+    o.x = max(l.x, max(r.x, wadd(l.z, r.y)));
+    o.y = max(l.y, wadd(l.w, r.y));
+    o.z = max(r.z, wadd(l.z, r.w));
+    o.w = wadd(l.w, r.w);
+    return o;
+  }
+};
+
+struct SumI32F32 { uint32_t s; float f; };
+struct SpecSumI32F32 {
+  using Acc = SumI32F32;
+  static constexpr bool commutative = true;
+  __device__ __forceinline__ static Acc neutral() { Acc a; a.s = 0u; a.f = 0.0f; return a; }
+  __device__ __forceinline__ static Acc map(uint32_t bits) { Acc a; a.s = bits; a.f = (float)(int32_t)bits; return a; }
+  __device__ __forceinline__ static Acc combine(const Acc &l, const Acc &r) { Acc a; a.s = l.s + r.s; a.f = l.f + r.f; return a; }
+};
+
+static_assert(RM_MAX_BLOCKS == 4096, "reduce_scratch_bytes() holds 4096 partials of 16 bytes");
+
+cudaError_t launch_mss_i32(const int32_t *in, int64_t n, int32_t *d_out4, void *scratch, int num_sms, cudaStream_t stream) {
+  return launch_redomap<SpecMss>(in, n, d_out4, scratch, num_sms, stream);
+}
+cudaError_t launch_sum_i32_f32(const int32_t *in, int64_t n, void *d_out2, void *scratch, int num_sms, cudaStream_t stream) {
+  return launch_redomap<SpecSumI32F32>(in, n, d_out2, scratch, num_sms, stream);
+}
+}  // namespace fb

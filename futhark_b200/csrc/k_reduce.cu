@@ -16,7 +16,9 @@ namespace fb {
 constexpr int RED_THREADS = 256;
 constexpr int RED_MAX_BLOCKS = 4096;
 
-size_t reduce_scratch_bytes() { return 256 + RED_MAX_BLOCKS * sizeof(uint32_t); }
+// a ticket word, then room for one partial per CTA; the fused-redomap template (redomap.cuh) shares
+// the area and keeps up to 16 bytes per CTA
+size_t reduce_scratch_bytes() { return 256 + RED_MAX_BLOCKS * 16; }
 
 // ---- reduce (+) 0 over i32 ----------------------------------------------------------
 // Stage one: grid-stride over 16-byte vectors, four loads in flight per thread.

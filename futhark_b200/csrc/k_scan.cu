@@ -56,7 +56,7 @@ namespace fb {
 
 constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_WARPS = SCAN_THREADS / 32;
-enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3 };
+enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3, K_EXSCAN_I32 = 4 };
 
 // Tile geometry per kind.  A thread owns V 16-byte vectors = 4V consecutive elements; V is odd
 // (see the kernel).  The scans take 5 (tiles of 5120 elements, 4 CTAs per SM: larger tiles
@@ -475,8 +475,15 @@ stream_kernel(const LookbackArgs a) {
           if (q < first) x[q] = __float_as_uint(left + __uint_as_float(x[q]));
       } else {
         const uint32_t left = ev + lv;
+        if (KIND == K_EXSCAN_I32) {
+          // exclusive: element q receives what precedes it (its left neighbour's inclusive value)
 #pragma unroll
-        for (int q = 0; q < ITEMS; q++) x[q] += left;
+          for (int q = ITEMS - 1; q > 0; q--) x[q] = x[q - 1] + left;
+          x[0] = left;
+        } else {
+#pragma unroll
+          for (int q = 0; q < ITEMS; q++) x[q] += left;
+        }
       }
       int4 *s4 = reinterpret_cast<int4 *>(s_tile) + tid * V;
 #pragma unroll
@@ -608,6 +615,13 @@ cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t 
   a.carry_vals = reinterpret_cast<const uint32_t *>(carry_vals);
   a.carry_n = carry_n;
   return launch_stream<K_SCAN_I32>(a, stream);
+}
+
+cudaError_t launch_exscan_i32(const int32_t *in, int32_t *out, int64_t n, void *scratch,
+                              uint32_t epoch, int *failure, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  LookbackArgs a = make_args<K_EXSCAN_I32>(in, nullptr, out, nullptr, n, scratch, epoch, failure);
+  return launch_stream<K_EXSCAN_I32>(a, stream);
 }
 
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,

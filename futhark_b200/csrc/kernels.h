@@ -16,6 +16,9 @@ size_t lookback_scratch_bytes(int64_t n);
 cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in,
                             const int32_t *carry_vals, int carry_n, void *scratch,
                             uint32_t epoch, int *failure, cudaStream_t stream);
+// Exclusive scan: out[0] = 0, out[i] = in[0] + ... + in[i-1] (prelude/soacs.fut:212-215).
+cudaError_t launch_exscan_i32(const int32_t *in, int32_t *out, int64_t n, void *scratch,
+                              uint32_t epoch, int *failure, cudaStream_t stream);
 // After launch_segscan_f32 on the same scratch: writes the shard summary {f32 bits, flag}.
 // A bounded wait on a status word that is never published: records FAIL_LOOKBACK_TIMEOUT.
 cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls, int *failure, cudaStream_t stream);
@@ -38,6 +41,12 @@ cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float
                               cudaStream_t stream);
 cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
                                  int num_sms, cudaStream_t stream);
+
+// ---- fused redomaps (k_redomap.cu; the kernel template is redomap.cuh) -----------------------
+// `scratch` as for the reductions.  mss: d_out4 receives the operator's 4-tuple (best segment
+// sum first).  sum_i32_f32: d_out2 receives {i32 sum, f32 sum of the converted elements}.
+cudaError_t launch_mss_i32(const int32_t *in, int64_t n, int32_t *d_out4, void *scratch, int num_sms, cudaStream_t stream);
+cudaError_t launch_sum_i32_f32(const int32_t *in, int64_t n, void *d_out2, void *scratch, int num_sms, cudaStream_t stream);
 
 // ---- histograms (k_hist.cu) -------------------------------------------------------------
 // op 0: (+) on i32 weights; op 1: max on f32 weights (result in f32 bits).  `out` holds

@@ -240,6 +240,25 @@ int futhark_entry_transpose_f32(struct futhark_context *ctx, struct futhark_f32_
 int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f32_3d **out0,
                                    const struct futhark_f32_3d *in0);
 
+/* Fused and multi-operator SegOps.  The reference generates ONE kernel for a map body fused
+ * with one or several reduction operators (src/Futhark/CodeGen/ImpGen/GPU/SegRed.hs:99-100,
+ * 129-145) and keeps operand order for non-commutative operators (:836-921); here one kernel
+ * template takes the body and the operators as a specification type.
+ *
+ * entry exscan_i32 (xs: []i32): []i32 = exscan (+) 0 xs          (prelude/soacs.fut:212-215;
+ *   tests/soacs/exscan0.fut, exscan1.fut): out[0] = 0, out[i] = xs[0] + ... + xs[i-1].
+ * entry mss_i32 (xs: []i32): i32 = (reduce redOp (0,0,0,0) (map mapOp xs)).0, the maximum
+ *   segment sum of tests/mss.fut:6-20: a 4-tuple-valued, non-commutative operator.
+ * entry sum_i32_f32 (xs: []i32): (i32, f32) = (i32.sum xs, f32.sum (map f32.i32 xs)), the
+ *   horizontally fused pair of tests/fusion/red-red-fusion.fut:5.
+ * The two with scalar results read them back, so they synchronise. */
+int futhark_entry_exscan_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                             const struct futhark_i32_1d *in0);
+int futhark_entry_mss_i32(struct futhark_context *ctx, int32_t *out0,
+                          const struct futhark_i32_1d *in0);
+int futhark_entry_sum_i32_f32(struct futhark_context *ctx, int32_t *out0, float *out1,
+                              const struct futhark_i32_1d *in0);
+
 /* ---- extensions (prefix futhark_b200_): not part of the reference's generated API ----
  * The reference keeps its one CUDA stream private (rts/c/backends/cuda.h:219); a host
  * program that shares a process with other CUDA code needs it to order its own work

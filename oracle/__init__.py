@@ -30,6 +30,10 @@ def lib():
         L.orc_reduce_i32.argtypes = [vp, i64, i32]
         L.orc_scan_i32.argtypes = [vp, i64, vp, i32]
         L.orc_segscan_f32.argtypes = [vp, vp, i64, vp, i32]
+        L.orc_exscan_i32.argtypes = [vp, i64, vp, i32]
+        L.orc_mss_i32.restype = ctypes.c_int32
+        L.orc_mss_i32.argtypes = [vp, i64, i32]
+        L.orc_sum_i32_f32.argtypes = [vp, i64, vp, vp, i32]
         L.orc_segscan_f32_seq64.argtypes = [vp, vp, i64, vp]
         L.orc_segreduce_f32.argtypes = [vp, i64, vp, vp, i32]
         L.orc_rowsum_f32.argtypes = [vp, i64, i64, vp, i32]
@@ -104,6 +108,25 @@ def scan_i32(xs, threads=0):
     out = np.empty_like(xs)
     lib().orc_scan_i32(_p(xs), xs.size, _p(out), threads)
     return out
+
+
+def exscan_i32(xs, threads=0):
+    xs = _c(xs, np.int32)
+    out = np.empty_like(xs)
+    lib().orc_exscan_i32(_p(xs), xs.size, _p(out), threads)
+    return out
+
+
+def mss_i32(xs, threads=0):
+    xs = _c(xs, np.int32)
+    return int(lib().orc_mss_i32(_p(xs), xs.size, threads))
+
+
+def sum_i32_f32(xs, threads=0):
+    xs = _c(xs, np.int32)
+    oi, of = ctypes.c_int32(), ctypes.c_float()
+    lib().orc_sum_i32_f32(_p(xs), xs.size, ctypes.byref(oi), ctypes.byref(of), threads)
+    return int(oi.value), float(of.value)
 
 
 def segscan_f32(flags, xs, threads=0):

@@ -1,15 +1,15 @@
 /* CPU oracle for the SegOp hot path.
  *
  * TEST INFRASTRUCTURE ONLY.  This file is a plain-C restatement of the algorithms
- * that the reference's `futhark multicore` backend generates for nine fixed entry
- * points.  It is used by the parity tests, by the smoke check and as the timed CPU
+ * that the reference's `futhark multicore` backend generates for the fixed entry
+ * points of the library.  It is used by the parity tests, by the smoke check and as the timed CPU
  * baseline; the shipped library never links, loads or calls it.
  *
  * Parity status: pinned against the known-answer vectors that the reference's own
  * tests carry for these paths (tests/soacs/scan0.fut, reduce0.fut, filter1.fut,
  * partition1.fut, tests/hist/simple.fut, max.fut, large.fut,
  * tests/segredomap/segsum-comm.fut, tests/soacs/segreduce-iota.fut,
- * tests/reg-tiling/mmm.fut).  The flagged f32 segmented scan and the f16-input
+ * tests/reg-tiling/mmm.fut, tests/mss.fut, tests/soacs/exscan0.fut, exscan1.fut).  The flagged f32 segmented scan and the f16-input
  * contraction have no pinned vectors in the reference ("auto output" only), so
  * for those two this oracle is "parity unpinned": it follows the reference's
  * operator definitions but cannot be checked against reference-produced values.
@@ -103,6 +103,82 @@ void orc_scan_i32(const int32_t *xs, int64_t n, int32_t *out, int nthreads) {
     for (int64_t i = lo; i < hi; i++) { acc += (uint32_t)xs[i]; out[i] = (int32_t)acc; }
   }
   free(agg);
+}
+
+/* ---- exclusive scan (+) 0 over i32 -----------------------------------------
+ * prelude/soacs.fut:212-215: the inclusive scan scattered one place to the right
+ * over an array of neutral elements; the last inclusive value falls off the end. */
+void orc_exscan_i32(const int32_t *xs, int64_t n, int32_t *out, int nthreads) {
+  if (n <= 0) return;
+  int32_t *incl = (int32_t *)malloc((size_t)n * sizeof(int32_t));
+  orc_scan_i32(xs, n, incl, nthreads);
+  out[0] = 0;
+  memcpy(out + 1, incl, (size_t)(n - 1) * sizeof(int32_t));
+  free(incl);
+}
+
+/* ---- maximum segment sum: redomap with a non-commutative 4-tuple operator ------
+ * The program of tests/mss.fut:6-20.  Multicore/SegRed.hs:297-320, 345-376: every
+ * subtask folds its contiguous chunk left to right from the neutral element, the
+ * per-subtask partials are folded in subtask order.  i32 additions wrap
+ * (rts/c/scalar.h:29), max is the signed maximum (smax32, :262). */
+typedef struct { int32_t mss, mis, mcs, ts; } orc_mss_t;
+static int32_t wadd32(int32_t a, int32_t b) { return (int32_t)((uint32_t)a + (uint32_t)b); }
+static int32_t smax32(int32_t a, int32_t b) { return a < b ? b : a; }
+static orc_mss_t mss_op(orc_mss_t x, orc_mss_t y) {
+  orc_mss_t r;
+  r.mss = smax32(x.mss, smax32(y.mss, wadd32(x.mcs, y.mis)));
+  r.mis = smax32(x.mis, wadd32(x.ts, y.mis));
+  r.mcs = smax32(y.mcs, wadd32(x.mcs, y.ts));
+  r.ts = wadd32(x.ts, y.ts);
+  return r;
+}
+int32_t orc_mss_i32(const int32_t *xs, int64_t n, int nthreads) {
+  int k = pick_threads(nthreads);
+  if (n < k) k = n > 0 ? (int)n : 1;
+  orc_mss_t *part = (orc_mss_t *)calloc((size_t)k, sizeof(orc_mss_t));
+#pragma omp parallel for num_threads(k) schedule(static, 1)
+  for (int t = 0; t < k; t++) {
+    int64_t lo, hi;
+    chunk_of(n, k, t, &lo, &hi);
+    orc_mss_t acc = {0, 0, 0, 0};
+    for (int64_t i = lo; i < hi; i++) {
+      int32_t m = smax32(xs[i], 0);
+      orc_mss_t e = {m, m, m, xs[i]};
+      acc = mss_op(acc, e);
+    }
+    part[t] = acc;
+  }
+  orc_mss_t r = {0, 0, 0, 0};
+  for (int t = 0; t < k; t++) r = mss_op(r, part[t]);
+  free(part);
+  return r.mss;
+}
+
+/* ---- two reductions fused over one input -------------------------------------
+ * The program of tests/fusion/red-red-fusion.fut:5: (i32.sum xs, f32.sum (map f32.i32 xs)),
+ * one SegRed with two operators; chunking as above.  f32.i32 is sitofp_i32_f32
+ * (rts/c/scalar.h: a C cast). */
+void orc_sum_i32_f32(const int32_t *xs, int64_t n, int32_t *out_i, float *out_f, int nthreads) {
+  int k = pick_threads(nthreads);
+  if (n < k) k = n > 0 ? (int)n : 1;
+  uint32_t *pi = (uint32_t *)calloc((size_t)k, sizeof(uint32_t));
+  float *pf = (float *)calloc((size_t)k, sizeof(float));
+#pragma omp parallel for num_threads(k) schedule(static, 1)
+  for (int t = 0; t < k; t++) {
+    int64_t lo, hi;
+    chunk_of(n, k, t, &lo, &hi);
+    uint32_t ai = 0;
+    float af = 0.0f;
+    for (int64_t i = lo; i < hi; i++) { ai += (uint32_t)xs[i]; af += (float)xs[i]; }
+    pi[t] = ai; pf[t] = af;
+  }
+  uint32_t ri = 0;
+  float rf = 0.0f;
+  for (int t = 0; t < k; t++) { ri += pi[t]; rf += pf[t]; }
+  free(pi); free(pf);
+  *out_i = (int32_t)ri;
+  *out_f = rf;
 }
 
 /* ---- flagged segmented inclusive scan (+) over f32 --------------------------

@@ -27,6 +27,9 @@ FILES = [
     "tests/hist/large.fut",
     "tests/segredomap/segsum-comm.fut",
     "tests/reg-tiling/mmm.fut",
+    "tests/mss.fut",
+    "tests/soacs/exscan0.fut",
+    "tests/soacs/exscan1.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f32\.nan|f32\.inf|-f32\.inf|true|false|"

@@ -1,0 +1,125 @@
+"""GPU parity of the fused / multi-operator SegOps -- exclusive scan, maximum segment sum (a map
+body plus a non-commutative 4-tuple operator) and two reductions fused over one input -- through
+the C ABI, against the CPU oracle and the reference's known answers."""
+import numpy as np
+import pytest
+import torch
+
+import futhark_b200 as fb
+import oracle
+from futhark_b200 import datagen
+from util import SIZES, TILE
+
+pytestmark = pytest.mark.gpu
+
+STEP = 32 * 5 * 4          # elements one warp takes per step in the redomap kernel
+MORE = [STEP - 1, STEP, STEP + 1, 8 * STEP + 3, 1 << 20, (1 << 22) + 3]
+
+
+@pytest.mark.parametrize("n", SIZES + [1 << 20, (1 << 22) + 3])
+def test_exscan_i32_bit_exact(ctx, n):
+    xs = datagen.workload_i32(n)
+    got = fb.exscan_i32(ctx, xs)
+    assert got.shape == (n,)
+    assert np.array_equal(got, oracle.exscan_i32(xs))
+
+
+def test_exscan_i32_reference_known_answers(ctx):
+    # tests/soacs/exscan0.fut:7-8, exscan1.fut:2-7 of the reference
+    for n, want in ((100, 4851), (1000000, 1782293665)):
+        assert int(fb.exscan_i32(ctx, np.arange(n, dtype=np.int32))[-1]) == want
+    assert fb.exscan_i32(ctx, np.arange(1, 10, dtype=np.int32)).tolist() == [0, 1, 3, 6, 10, 15, 21, 28, 36]
+
+
+def test_exscan_i32_unaligned_raw_pointer(ctx):
+    n = 4 * TILE + 123
+    xs = datagen.workload_i32(n + 1)
+    whole = ctx.new("i32_1d", xs)
+    view = ctx.new_raw("i32_1d", whole.raw + 4, n)
+    out = ctx.entry_exscan_i32(view)
+    got = out.values()
+    out.free(); view.free(); whole.free()
+    assert np.array_equal(got, oracle.exscan_i32(xs[1:]))
+
+
+def test_exscan_then_scan_share_status_words(ctx):
+    # both kinds use the same tile status words; epochs keep the launches apart
+    xs = datagen.uniform_i32(5, 0, 9 * TILE + 7, -50, 50)
+    for _ in range(3):
+        assert np.array_equal(fb.exscan_i32(ctx, xs), oracle.exscan_i32(xs))
+        assert np.array_equal(fb.scan_i32(ctx, xs), oracle.scan_i32(xs))
+
+
+def test_mss_reference_known_answer(ctx):
+    # tests/mss.fut:3-4 of the reference
+    assert fb.mss_i32(ctx, np.array([1, -2, 3, 4, -1, 5, -6, 1], np.int32)) == 11
+    assert fb.mss_i32(ctx, np.zeros(0, np.int32)) == 0
+    assert fb.mss_i32(ctx, np.full(1000, -3, np.int32)) == 0
+
+
+@pytest.mark.parametrize("n", SIZES + MORE)
+def test_mss_bit_exact(ctx, n):
+    xs = datagen.uniform_i32(11, 0, n, -1000, 1000)
+    assert fb.mss_i32(ctx, xs) == oracle.mss_i32(xs)
+
+
+def test_mss_operand_order_matters(ctx):
+    # one large positive run split by a large negative element: any reordering of the operands
+    # across lanes, warps or CTAs changes the answer
+    n = (1 << 21) + 77
+    xs = np.full(n, -1, np.int32)
+    xs[1000:200000] = 3
+    xs[200000] = -2000000000
+    xs[200001:1500000] = 2
+    want = oracle.mss_i32(xs, 1)
+    assert want == 2 * (1500000 - 200001)
+    assert fb.mss_i32(ctx, xs) == want
+    # and with wrapping totals
+    ys = datagen.uniform_i32(12, 0, 1 << 22, -2**31, 2**31 - 1)
+    assert fb.mss_i32(ctx, ys) == oracle.mss_i32(ys)
+
+
+def test_mss_unaligned_raw_pointer(ctx):
+    n = 100 * STEP + 17
+    xs = datagen.uniform_i32(13, 0, n + 1, -1000, 1000)
+    whole = ctx.new("i32_1d", xs)
+    view = ctx.new_raw("i32_1d", whole.raw + 4, n)
+    got = ctx.entry_mss_i32(view)
+    view.free(); whole.free()
+    assert got == oracle.mss_i32(xs[1:])
+
+
+@pytest.mark.parametrize("n", SIZES + MORE)
+def test_sum_i32_f32(ctx, n):
+    xs = datagen.uniform_i32(14, 0, n, -1000, 1000)
+    si, sf = fb.sum_i32_f32(ctx, xs)
+    oi, of = oracle.sum_i32_f32(xs)
+    assert si == oi                                                # the integer operator: bit-exact
+    l1 = float(np.abs(xs.astype(np.float64)).sum())
+    assert abs(sf - float(xs.astype(np.float64).sum())) <= 1e-5 * max(l1, 1e-6)   # the f32 operator: 1e-5 of the L1 norm
+    assert abs(sf - of) <= 2e-5 * max(l1, 1e-6)
+
+
+def test_fused_full_size_2p26(ctx):
+    dev = torch.device("cuda", 0)
+    n = 1 << 26
+    g = torch.Generator(device=dev)
+    g.manual_seed(21)
+    x = torch.randint(-1000, 1001, (n,), device=dev, dtype=torch.int32, generator=g)
+    torch.cuda.synchronize()
+    a = ctx.new_raw("i32_1d", x.data_ptr(), n)
+    out = ctx.entry_exscan_i32(a)
+    ctx.sync()
+    o = torch.as_tensor(out, device=dev).view(torch.int32)
+    assert int(o[0]) == 0
+    assert torch.equal(o[1:] - o[:-1], x[:-1])                      # differences of an exclusive scan give the input back
+    si, sf = ctx.entry_sum_i32_f32(a)
+    ref = int(x.to(torch.int64).sum().item())
+    assert si == ((ref + 2 ** 31) % 2 ** 32) - 2 ** 31
+    assert si == ((int(o[-1]) + int(x[-1]) + 2 ** 31) % 2 ** 32) - 2 ** 31
+    assert abs(sf - float(x.double().sum().item())) <= 1e-5 * float(x.double().abs().sum().item())
+    # maximum segment sum against a device-side evaluation: max over i of (P[i] - min_{j<=i} P[j]) on i64 prefix sums
+    p = torch.cat([torch.zeros(1, device=dev, dtype=torch.int64), torch.cumsum(x.to(torch.int64), 0)])
+    want = int((p - torch.cummin(p, 0).values).max().item())
+    assert ctx.entry_mss_i32(a) == want
+    out.free(); a.free()

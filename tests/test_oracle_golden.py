@@ -27,6 +27,54 @@ def test_scan0_last_element_of_prefix_sum_of_iota(c):
     assert np.array_equal(out, np.cumsum(xs.astype(np.int64)).astype(np.int32))
 
 
+@pytest.mark.parametrize("c", cases("tests/soacs/exscan0.fut"))
+def test_exscan0_last_element_of_exclusive_prefix_sum_of_iota(c):
+    n = c["input"][0]
+    xs = np.arange(n, dtype=np.int64).astype(np.int32)
+    for threads in (1, 3, 0):
+        out = oracle.exscan_i32(xs, threads)
+        assert int(out[n - 1]) == c["output"][0]
+        assert out[0] == 0 and np.array_equal(out[1:], np.cumsum(xs.astype(np.int64)).astype(np.int32)[:-1])
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/exscan1.fut"))
+def test_exscan1_small(c):
+    assert oracle.exscan_i32(np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+
+
+def _mss_by_definition(xs):
+    """Best sum over all contiguous segments, the empty one included (Kadane), in wrapping-free range."""
+    best = cur = 0
+    for x in xs.tolist():
+        cur = max(cur + x, 0)
+        best = max(best, cur)
+    return best
+
+
+@pytest.mark.parametrize("c", cases("tests/mss.fut"))
+def test_mss_known_answer_and_chunking(c):
+    xs = np.array(c["input"][0], np.int32)
+    for threads in (1, 2, 3, 8):
+        assert oracle.mss_i32(xs, threads) == c["output"][0]
+    # the operator is not commutative: every chunking must still give the sequential answer
+    rng = np.random.default_rng(7)
+    ys = rng.integers(-1000, 1001, 100003).astype(np.int32)
+    want = _mss_by_definition(ys)
+    for threads in (1, 5, 0):
+        assert oracle.mss_i32(ys, threads) == want
+    assert oracle.mss_i32(np.zeros(0, np.int32)) == 0
+    assert oracle.mss_i32(np.full(10, -5, np.int32)) == 0
+
+
+def test_sum_i32_f32_fused_pair():
+    rng = np.random.default_rng(8)
+    xs = rng.integers(-1000, 1001, 250001).astype(np.int32)
+    si, sf = oracle.sum_i32_f32(xs, 4)
+    assert si == int(xs.astype(np.int64).sum())
+    assert abs(sf - float(xs.astype(np.float64).sum())) <= 1e-5 * float(np.abs(xs.astype(np.float64)).sum())
+    assert oracle.sum_i32_f32(np.zeros(0, np.int32)) == (0, 0.0)
+
+
 @pytest.mark.parametrize("c", cases("tests/soacs/reduce0.fut"))
 def test_reduce0_sum_of_range_wraps(c):
     n = c["input"][0]
