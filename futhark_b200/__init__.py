@@ -125,6 +125,8 @@ def load():
     L.futhark_entry_transpose_f32.argtypes = [vp, pvp, vp]
     L.futhark_entry_transpose_f32_3d.argtypes = [vp, pvp, vp]
     L.futhark_entry_exscan_i32.argtypes = [vp, pvp, vp]
+    L.futhark_b200_lmad_copy.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.c_uint64, i64, vp, ctypes.c_uint64, i64, vp, vp]
+    L.futhark_b200_lmad_classify.argtypes = [ctypes.c_int, vp, vp, vp, vp]
     L.futhark_entry_mss_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
     L.futhark_entry_sum_i32_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float), vp]
     _lib = L
@@ -366,6 +368,14 @@ class Context:
     def entry_transpose_f32_3d(self, xsss):
         return self._entry_arr("transpose_f32_3d", "f32_3d", xsss.ptr)
 
+    def lmad_copy(self, elem_size, dst_ptr, dst_offset, dst_strides, src_ptr, src_offset, src_strides, shape):
+        """Strided device-to-device copy between two LMADs (offsets and strides in elements)."""
+        ds, ss, sh = (np.ascontiguousarray(x, np.int64) for x in (dst_strides, src_strides, shape))
+        assert ds.size == ss.size == sh.size
+        as_p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        self._check(self.lib.futhark_b200_lmad_copy(self.ptr, elem_size, sh.size, dst_ptr, dst_offset, as_p(ds),
+                                                    src_ptr, src_offset, as_p(ss), as_p(sh)))
+
     def entry_exscan_i32(self, xs):
         return self._entry_arr("exscan_i32", "i32_1d", xs.ptr)
 
@@ -405,6 +415,15 @@ def reduce_i32(ctx, xs):
         return ctx.entry_reduce_i32(a)
     finally:
         a.free()
+
+
+def lmad_classify(dst_strides, src_strides, shape):
+    """Host-only routing decision of `lmad_copy` for 4-byte elements: (kind, [arrays, rows, cols])."""
+    ds, ss, sh = (np.ascontiguousarray(x, np.int64) for x in (dst_strides, src_strides, shape))
+    knm = np.zeros(3, np.int64)
+    as_p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    kind = load().futhark_b200_lmad_classify(sh.size, as_p(ds), as_p(ss), as_p(sh), as_p(knm))
+    return kind, knm.tolist()
 
 
 def exscan_i32(ctx, xs):

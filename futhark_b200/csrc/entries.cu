@@ -389,6 +389,42 @@ int futhark_b200_debug_expire_wait(struct futhark_context *ctx, int max_polls) {
   return rc;
 }
 
+// ---- strided copies between device arrays (extension; the reference's lmad_copy_gpu2gpu) -------
+
+int futhark_b200_lmad_classify(int r, const int64_t *dst_strides, const int64_t *src_strides, const int64_t *shape, int64_t *knm) {
+  if (r < 0 || r > fb::LMAD_MAX_RANK) return -2;
+  int64_t ns[fb::LMAD_MAX_RANK], nd[fb::LMAD_MAX_RANK], nsrc[fb::LMAD_MAX_RANK];
+  const int m = fb::lmad_normalise(r, dst_strides, src_strides, shape, ns, nd, nsrc);
+  int64_t nb = 0, rows = 0, cols = 0;
+  const int kind = fb::lmad_classify(m, ns, nd, nsrc, &nb, &rows, &cols);
+  if (knm != nullptr) { knm[0] = nb; knm[1] = rows; knm[2] = cols; }
+  return kind;
+}
+
+int futhark_b200_lmad_copy(struct futhark_context *ctx, int elem_size, int r, CUdeviceptr dst, int64_t dst_offset,
+                           const int64_t *dst_strides, CUdeviceptr src, int64_t src_offset, const int64_t *src_strides,
+                           const int64_t *shape) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  if (r < 0 || r > fb::LMAD_MAX_RANK || (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8)) {
+    fb_set_error(ctx, "lmad_copy: the rank must be 0..8 and the element size 1, 2, 4 or 8 bytes.\n");
+    return 1;
+  }
+  int64_t total = 1;
+  for (int i = 0; i < r; i++) {
+    if (shape[i] < 0) return bad_sizes(ctx);
+    total *= shape[i];
+  }
+  if (total == 0) return FUTHARK_SUCCESS;
+  int kind = futhark_b200_lmad_classify(r, dst_strides, src_strides, shape, nullptr);
+  if (kind == fb::LMAD_TRANSPOSE && elem_size != 4) kind = fb::LMAD_GENERAL;
+  const char *name = kind == fb::LMAD_FLAT ? "copy_dev_to_dev" : kind == fb::LMAD_TRANSPOSE ? "lmad_copy.map_transpose_4b" : "lmad_copy.general";
+  LaunchScope ls(ctx, name, PROV("copy"), "{" + kv("elements", total) + "," + kv("elem_size", elem_size) + "}");
+  return fb_cuda_check(ctx, fb::launch_lmad_copy(elem_size, r, reinterpret_cast<void *>((uintptr_t)dst), dst_offset, dst_strides,
+                                                 reinterpret_cast<const void *>((uintptr_t)src), src_offset, src_strides, shape,
+                                                 ctx->num_sms, ctx->stream, nullptr), "lmad_copy");
+}
+
 // ---- shard-local pieces for arrays split across several contexts (extensions) -------------------
 
 int futhark_b200_reduce_i32_to_device(struct futhark_context *ctx, CUdeviceptr dst, const struct futhark_i32_1d *in0) {

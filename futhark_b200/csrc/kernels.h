@@ -59,6 +59,20 @@ cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weig
 cudaError_t launch_transpose_b32(const void *in, void *out, int64_t nb, int64_t rows, int64_t cols, int num_sms,
                                  cudaStream_t stream);
 
+// Strided copy between two device arrays given as LMADs (offset + one stride per dimension, in
+// elements) over a common shape of rank <= LMAD_MAX_RANK; elem_size 1, 2, 4 or 8.  *kind_out
+// (may be NULL) receives the route taken.  The two host-side steps are exported for tests:
+// lmad_normalise returns the rank of the normal form, lmad_classify the route for it.
+constexpr int LMAD_MAX_RANK = 8;
+enum LmadKind : int { LMAD_NOTHING = -1, LMAD_GENERAL = 0, LMAD_TRANSPOSE = 1, LMAD_FLAT = 2 };
+int lmad_normalise(int r, const int64_t *dst_strides, const int64_t *src_strides, const int64_t *shape,
+                   int64_t *n_shape, int64_t *n_dst, int64_t *n_src);
+int lmad_classify(int r, const int64_t *shape, const int64_t *dst, const int64_t *src, int64_t *nb, int64_t *rows,
+                  int64_t *cols);
+cudaError_t launch_lmad_copy(int elem_size, int r, void *dst, int64_t dst_offset, const int64_t *dst_strides,
+                             const void *src, int64_t src_offset, const int64_t *src_strides, const int64_t *shape,
+                             int num_sms, cudaStream_t stream, int *kind_out);
+
 // ---- batched f16 contraction (k_bmm.cu) ------------------------------------------------
 cudaError_t launch_bmm_f16(const uint16_t *A, const uint16_t *B, float *C, int64_t nb, int64_t m, int64_t k,
                            int64_t n, int *failure, cudaStream_t stream);

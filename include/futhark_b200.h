@@ -1,7 +1,7 @@
 /* futhark_b200.h -- C API of the B200-native SegOp core.
  *
  * The symbols below are the ones `futhark cuda --library` generates for a program
- * with the nine entry points listed at the end of this file; each declaration
+ * with the entry points listed at the end of this file; each declaration
  * cites the place in the reference (diku-dk/futhark v0.28.0) that defines the
  * interface it replaces.  A host program written against the generated header of
  * that program links against libfuthark_b200.so unchanged.
@@ -279,6 +279,28 @@ int64_t futhark_b200_context_get_launch_count(struct futhark_context *ctx);
  * clears the failure and resets the scan scratch, as after a real time-out
  * (the global_failure protocol of rts/c/backends/cuda.h:719-754); the context stays usable. */
 int futhark_b200_debug_expire_wait(struct futhark_context *ctx, int max_polls);
+
+/* Strided copy between two arrays in device memory, each described by an LMAD: an offset and
+ * one stride per dimension of the common `shape`, all counted in elements of elem_size (1, 2, 4
+ * or 8) bytes; rank 0..8.  For every index I below shape:
+ *     dst[dst_offset + sum_i I_i * dst_strides[i]] = src[src_offset + sum_i I_i * src_strides[i]]
+ * It stands where the reference's generated code calls lmad_copy_gpu2gpu_{1,2,4,8}b
+ * (rts/c/gpu.h:540-586; host-side twin rts/c/copy.h:60-268) for the layout changes the compiler
+ * inserts around SegOps, and routes the copy the same way: a batched transposition (of 4-byte
+ * elements) to the tiled transposition kernel, a copy between equal dense layouts to one
+ * device-to-device copy, the rest to a general strided kernel (rts/opencl/copy.cl:3-83).
+ * Strides may be zero or negative on the source; the destination index must be injective.
+ * Asynchronous, on the context's stream.
+ *
+ * futhark_b200_lmad_classify is the host-only routing decision for 4-byte elements
+ * (0 general, 1 batched transposition, 2 flat copy; -2 bad rank); for a transposition
+ * knm (may be NULL) receives {arrays, rows, columns of the source matrix}. */
+int futhark_b200_lmad_copy(struct futhark_context *ctx, int elem_size, int r,
+                           CUdeviceptr dst, int64_t dst_offset, const int64_t *dst_strides,
+                           CUdeviceptr src, int64_t src_offset, const int64_t *src_strides,
+                           const int64_t *shape);
+int futhark_b200_lmad_classify(int r, const int64_t *dst_strides, const int64_t *src_strides,
+                               const int64_t *shape, int64_t *knm);
 
 /* Shard-local pieces, for one logical array split into contiguous shards over several
  * contexts (one per GPU).  The reference is single-device (rts/c/backends/cuda.h:219) and has

@@ -86,6 +86,30 @@ def ref_scalar():
     return _ref
 
 
+_refcp = None
+
+
+def ref_copy():
+    """The reference's own host-side LMAD copy (oracle/_ref/libref_copy.so), or None if not built."""
+    global _refcp
+    if _refcp is None:
+        path = os.path.join(_HERE, "_ref", "libref_copy.so")
+        if not os.path.exists(path):
+            try:
+                _build.build()
+            except Exception:
+                pass
+        if not os.path.exists(path):
+            return None
+        R = ctypes.CDLL(path)
+        vp, i64 = ctypes.c_void_p, ctypes.c_int64
+        for nb in (1, 2, 4, 8):
+            getattr(R, "ref_lmad_copy_%db" % nb).argtypes = [ctypes.c_int, vp, i64, vp, vp, i64, vp, vp]
+        R.ref_lmad_classify.argtypes = [ctypes.c_int, vp, vp, vp, vp]
+        _refcp = R
+    return _refcp
+
+
 def _p(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 
@@ -223,3 +247,34 @@ def mm_f32(A, B):
     out = np.empty((m, n), dtype=np.float32)
     lib().orc_mm_f32(_p(A), _p(B), m, kk, n, _p(out))
     return out
+
+
+def lmad_copy(dst, dst_offset, dst_strides, src, src_offset, src_strides, shape):
+    """dst[dst_offset + I . dst_strides] = src[src_offset + I . src_strides] for every index I below
+    `shape`, on flat numpy arrays of one element type; offsets and strides count elements.  The
+    element-wise definition of rts/c/copy.h:35-56 (lmad_copy_elements), in index order."""
+    assert dst.ndim == 1 and src.ndim == 1 and dst.dtype == src.dtype
+    shape = [int(x) for x in shape]
+    if any(x == 0 for x in shape):
+        return
+    idx = np.indices(shape, dtype=np.int64).reshape(len(shape), -1) if shape else np.zeros((0, 1), np.int64)
+    d = int(dst_offset) + (idx * np.asarray(dst_strides, np.int64).reshape(-1, 1)).sum(axis=0)
+    s = int(src_offset) + (idx * np.asarray(src_strides, np.int64).reshape(-1, 1)).sum(axis=0)
+    dst[d] = src[s]
+
+
+def ref_lmad_copy(dst, dst_offset, dst_strides, src, src_offset, src_strides, shape):
+    """The same copy through the reference's own lmad_copy_{1,2,4,8}b (needs oracle/_ref)."""
+    R = ref_copy()
+    r = len(shape)
+    ds, ss, sh = (np.ascontiguousarray(x, np.int64) for x in (dst_strides, src_strides, shape))
+    getattr(R, "ref_lmad_copy_%db" % dst.dtype.itemsize)(r, _p(dst), int(dst_offset), _p(ds), _p(src), int(src_offset), _p(ss), _p(sh))
+
+
+def ref_lmad_classify(dst_strides, src_strides, shape):
+    """(kind, [k, n, m]) by the reference's lmad_map_tr / lmad_memcpyable: 0 general, 1 batched transposition, 2 flat."""
+    R = ref_copy()
+    ds, ss, sh = (np.ascontiguousarray(x, np.int64) for x in (dst_strides, src_strides, shape))
+    knm = np.zeros(3, np.int64)
+    kind = R.ref_lmad_classify(len(shape), _p(ds), _p(ss), _p(sh), _p(knm))
+    return kind, knm.tolist()

@@ -2,7 +2,8 @@
 
 `build()` compiles oracle/oracle.c into oracle/liboracle.so and, when a checkout of
 the reference is present, the scalar shim oracle/ref_scalar.c against the
-reference's own rts/c headers into oracle/_ref/libref_scalar.so.  Nothing from the
+reference's own rts/c headers into oracle/_ref/libref_scalar.so, and likewise
+oracle/ref_copy.c against rts/c/copy.h into oracle/_ref/libref_copy.so.  Nothing from the
 reference is copied: the headers are included from where they lie.
 """
 import os
@@ -37,6 +38,16 @@ def build(force=False, verbose=False):
             os.makedirs(ref_dir, exist_ok=True)
             cmd = ["gcc", "-O2", "-std=c99", "-w", "-shared", "-fPIC", "-I", REFERENCE_RTS,
                    ref_src, "-o", ref_lib, "-lm"]
+            if verbose:
+                print(" ".join(cmd))
+            subprocess.check_call(cmd)
+    # the reference's host-side LMAD copy (rts/c/copy.h), same recipe
+    cp_src = os.path.join(HERE, "ref_copy.c")
+    cp_lib = os.path.join(ref_dir, "libref_copy.so")
+    if os.path.isfile(os.path.join(REFERENCE_RTS, "copy.h")):
+        if force or _stale(cp_lib, [cp_src]):
+            os.makedirs(ref_dir, exist_ok=True)
+            cmd = ["gcc", "-O2", "-std=c99", "-w", "-shared", "-fPIC", "-I", REFERENCE_RTS, cp_src, "-o", cp_lib]
             if verbose:
                 print(" ".join(cmd))
             subprocess.check_call(cmd)

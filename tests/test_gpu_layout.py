@@ -1,5 +1,5 @@
-"""GPU parity of the layout operations (batched transposition of 4-byte elements) through
-the C ABI: bit-exact against numpy's transposition, which is what the reference's
+"""GPU parity of the layout operations (batched transposition of 4-byte elements, strided
+LMAD copies) through the C ABI: bit-exact against numpy's transposition, which is what the reference's
 map_transpose kernels compute (rts/opencl/transpose.cl)."""
 import numpy as np
 import pytest
@@ -39,3 +39,64 @@ def test_transpose_twice_is_the_identity_and_unaligned_base(ctx):
     got = tt.values()
     assert np.array_equal(got.view(np.uint32), x[1:].reshape(rows, cols).view(np.uint32))
     t.free(); tt.free(); view.free(); whole.free()
+
+
+# ---- strided (LMAD) copies -----------------------------------------------------------------------
+import oracle                                    # noqa: E402
+from lmad_cases import cases as lmad_cases       # noqa: E402
+
+LMAD_CASES = lmad_cases()
+
+
+def _upload(ctx, base):
+    """Any element type rides in a u32 array (the copy takes raw pointers and an element size)."""
+    raw = base.tobytes()
+    raw += b"\0" * (-len(raw) % 4)
+    return ctx.new("u32_1d", np.frombuffer(raw, np.uint32) if raw else np.zeros(0, np.uint32))
+
+
+def _download(arr, like):
+    return np.frombuffer(arr.values().tobytes()[:like.nbytes], like.dtype)
+
+
+@pytest.mark.parametrize("c", LMAD_CASES, ids=[c.name for c in LMAD_CASES])
+def test_lmad_copy_bit_exact(ctx, c):
+    src, dst = c.bases()
+    shape, doff, dstr, soff, sstr = c.lmads(src, dst)
+    want = dst.copy()
+    oracle.lmad_copy(want, doff, dstr, src, soff, sstr, shape)
+    assert np.array_equal(want, c.expected(src, dst))
+    sa, da = _upload(ctx, src), _upload(ctx, dst)
+    ctx.lmad_copy(c.dtype.itemsize, da.raw, doff, dstr, sa.raw, soff, sstr, shape)
+    ctx.sync()
+    got = _download(da, dst)
+    sa.free(); da.free()
+    assert np.array_equal(got, want)
+
+
+def test_lmad_copy_large_transposition_and_slice(ctx):
+    # a [64][1024][512] array: batched transposition through the LMAD entry equals the transposition entry,
+    # and a strided slice of it (every other row, a window of columns) equals numpy's
+    nb, rows, cols = 64, 1024, 512
+    x = datagen.normal_f32(44, 0, nb * rows * cols).reshape(nb, rows, cols)
+    xa = ctx.new("f32_3d", x)
+    out = ctx.new("f32_3d", np.zeros((nb, cols, rows), np.float32))
+    # destination row-major [nb][cols][rows]; source read as x[b][r][c] at index (b, c, r)
+    ctx.lmad_copy(4, out.raw, 0, [cols * rows, rows, 1], xa.raw, 0, [rows * cols, 1, cols], [nb, cols, rows])
+    ctx.sync()
+    assert np.array_equal(out.values().view(np.uint32), np.ascontiguousarray(x.transpose(0, 2, 1)).view(np.uint32))
+    sl = ctx.new("f32_3d", np.zeros((nb, rows // 2, 100), np.float32))
+    ctx.lmad_copy(4, sl.raw, 0, [rows // 2 * 100, 100, 1], xa.raw, 7, [rows * cols, 2 * cols, 1], [nb, rows // 2, 100])
+    ctx.sync()
+    assert np.array_equal(sl.values().view(np.uint32), np.ascontiguousarray(x[:, ::2, 7:107]).view(np.uint32))
+    xa.free(); out.free(); sl.free()
+
+
+def test_lmad_copy_rejects_bad_arguments(ctx):
+    a = ctx.new("u32_1d", np.arange(16, dtype=np.uint32))
+    with pytest.raises(fb.FutharkError):
+        ctx.lmad_copy(3, a.raw, 0, [1], a.raw, 0, [1], [4])
+    with pytest.raises(fb.FutharkError):
+        ctx.lmad_copy(4, a.raw, 0, [1] * 9, a.raw, 0, [1] * 9, [1] * 9)
+    a.free()
+    ctx.sync()
