@@ -136,6 +136,54 @@ def test_segreduce_empty_segments_and_no_segments(ctx):
     assert fb.segreduce_f32(ctx, np.zeros(0, dtype=np.int64), flags, xs).shape == (0,)
 
 
+def _check_segreduce(ctx, offsets, xs):
+    offsets = np.asarray(offsets, np.int64)
+    flags = np.zeros(xs.size, np.uint8)
+    got = fb.segreduce_f32(ctx, offsets, flags, xs)
+    assert got.shape == (offsets.size - 1,)
+    a = np.concatenate(([0.0], np.cumsum(np.abs(xs.astype(np.float64)))))
+    s = np.concatenate(([0.0], np.cumsum(xs.astype(np.float64))))
+    l1 = a[offsets[1:]] - a[offsets[:-1]]
+    assert_close_l1(got, s[offsets[1:]] - s[offsets[:-1]], np.maximum(l1, 1e-6), 1e-5, "segreduce vs f64")
+    assert np.array_equal(got[offsets[1:] == offsets[:-1]], np.zeros(int((offsets[1:] == offsets[:-1]).sum()), np.float32))
+    return got
+
+
+def test_segreduce_shapes_that_stress_the_element_ranges(ctx):
+    n = (1 << 21) + 13
+    xs = datagen.normal_f32(31, 0, n)
+    _check_segreduce(ctx, [0, n], xs)                                       # one segment over everything
+    _check_segreduce(ctx, [5, 5, 100, 70000, 70000, 200000], xs)            # neither starts at 0 nor ends at n
+    _check_segreduce(ctx, np.full(10001, n // 2), xs)                       # only empty segments, all at one place
+    _check_segreduce(ctx, np.full(5000, 0), xs)                             # ... at the very beginning
+    _check_segreduce(ctx, np.full(5000, n), xs)                             # ... and at the very end
+    _check_segreduce(ctx, np.arange(n + 1), xs)                             # every segment a single element
+    _check_segreduce(ctx, np.concatenate(([0], np.arange(1, n + 1, 127), [n])), xs)   # just under a step each
+    _check_segreduce(ctx, np.concatenate((np.arange(0, n, 128), [n])), xs)            # boundaries on step ends
+    # a few very long segments between runs of short and empty ones
+    rng = np.random.default_rng(3)
+    cuts = np.sort(np.concatenate((rng.integers(0, n, 3000), np.repeat(rng.integers(0, n, 50), 40), [0, 1000000, 1000001, n])))
+    _check_segreduce(ctx, cuts, xs)
+    got = _check_segreduce(ctx, [0, 3, 3, 10], np.arange(10, dtype=np.float32))
+    assert got.tolist() == [3.0, 0.0, 42.0]
+
+
+def test_segreduce_unaligned_values_pointer(ctx):
+    n = 300001
+    offsets, flags, xs = _seg_inputs(n + 1, 200, 5)
+    whole = ctx.new("f32_1d", xs)
+    off1 = np.clip(offsets - 1, 0, n)                  # the same cuts seen from element 1
+    view = ctx.new_raw("f32_1d", whole.raw + 4, n)
+    oa, fa = ctx.new("i64_1d", off1), ctx.new("bool_1d", np.zeros(n, np.bool_))
+    out = ctx.entry_segreduce_f32(oa, fa, view)
+    got = out.values()
+    for x in (out, oa, fa, view, whole):
+        x.free()
+    s = np.concatenate(([0.0], np.cumsum(xs[1:].astype(np.float64))))
+    a = np.concatenate(([0.0], np.cumsum(np.abs(xs[1:].astype(np.float64)))))
+    assert_close_l1(got, s[off1[1:]] - s[off1[:-1]], np.maximum(a[off1[1:]] - a[off1[:-1]], 1e-6), 1e-5, "unaligned")
+
+
 @pytest.mark.parametrize("rows,cols", [(0, 5), (3, 0), (2, 3), (1000, 1), (1000, 7), (513, 33), (257, 1024),
                                         (4096, 1024), (64, 4100), (3, 70000), (100000, 12)])
 def test_rowsum_f32_within_tolerance(ctx, rows, cols):
