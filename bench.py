@@ -159,7 +159,7 @@ CASES = {
     "scan_i32": 1 << 26, "reduce_i32": 1 << 26, "segscan_f32": 1 << 27, "segreduce_f32": 1 << 27,
     "rowsum_f32": 1 << 27, "hist_add_i32": 1 << 28, "hist_max_f32": 1 << 28, "filter_u32": 1 << 28,
     "partition_u32": 1 << 28, "bmm_f16": 64, "transpose_f32": 1 << 27,
-    "exscan_i32": 1 << 26, "mss_i32": 1 << 26, "sum_i32_f32": 1 << 26,
+    "exscan_i32": 1 << 26, "mss_i32": 1 << 26, "sum_i32_f32": 1 << 26, "lmad_permute_f32": 1 << 27,
 }
 
 
@@ -255,6 +255,14 @@ def run_case(args):
             rows = n // COLS
             a = [ctx.new("f32_2d", datagen.workload_rows_f32(rows, COLS))]
             timed(name, lambda: ctx.entry_transpose_f32(a[0]), 8 * rows * COLS, n)
+        elif name == "lmad_permute_f32":
+            # [b][r][1024] -> [r][b][1024] (neither a transposition of two groups nor flat): the general strided copy
+            nb, cols = 64, COLS
+            rows = n // (nb * cols)
+            a = [ctx.new("f32_3d", datagen.workload_rows_f32(nb * rows, cols).reshape(nb, rows, cols)),
+                 ctx.new("f32_3d", np.zeros((rows, nb, cols), np.float32))]
+            timed(name, lambda: ctx.lmad_copy(4, a[1].raw, 0, [nb * cols, cols, 1], a[0].raw, 0, [cols, rows * cols, 1], [rows, nb, cols]),
+                  8 * nb * rows * cols, n)
         elif name == "bmm_f16":
             m = args.bmm_dim
             A, Bm = datagen.workload_bmm(n, m, m, m)

@@ -37,6 +37,51 @@ PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 _lib = None
 
 
+class HostValue(ctypes.Structure):
+    """struct futhark_b200_value of the header."""
+    _fields_ = [("type", ctypes.c_char * 8), ("rank", ctypes.c_int32), ("shape", ctypes.c_int64 * 8), ("data", ctypes.c_void_p)]
+
+
+VALUE_DTYPES = {"i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64, "u8": np.uint8, "u16": np.uint16,
+                "u32": np.uint32, "u64": np.uint64, "f16": np.uint16, "f32": np.float32, "f64": np.float64, "bool": np.uint8}
+
+
+def value_from_bytes(data, tname, rank):
+    """Parse one value (text or binary data format) from `data`; returns (numpy array, bytes consumed).
+    f16 comes back as uint16 bits, bool as uint8."""
+    L = load()
+    v, used = HostValue(), ctypes.c_size_t()
+    buf = ctypes.create_string_buffer(data, len(data))
+    if L.futhark_b200_value_read_mem(buf, len(data), ctypes.byref(used), tname.encode(), rank, ctypes.byref(v)) != 0:
+        raise ValueError(L.futhark_b200_value_error().decode())
+    dims = tuple(int(v.shape[i]) for i in range(rank))
+    dt = np.dtype(VALUE_DTYPES[tname])
+    count = int(np.prod(dims)) if rank else 1
+    out = np.frombuffer(ctypes.string_at(v.data, count * dt.itemsize), dt).reshape(dims).copy()
+    L.futhark_b200_value_free(ctypes.byref(v))
+    return out, int(used.value)
+
+
+def value_to_bytes(arr, tname, binary):
+    """One value in the text or binary data format."""
+    L = load()
+    arr = np.asarray(arr, dtype=VALUE_DTYPES[tname])          # (ascontiguousarray would turn a scalar into a vector)
+    if not arr.flags.c_contiguous:
+        arr = arr.copy()
+    v = HostValue()
+    v.type = tname.encode()
+    v.rank = arr.ndim
+    for i, d in enumerate(arr.shape):
+        v.shape[i] = d
+    v.data = arr.ctypes.data
+    out, n = ctypes.c_void_p(), ctypes.c_size_t()
+    if L.futhark_b200_value_write_mem(ctypes.byref(v), int(binary), ctypes.byref(out), ctypes.byref(n)) != 0:
+        raise ValueError(L.futhark_b200_value_error().decode())
+    data = ctypes.string_at(out.value, n.value)
+    _libc.free(out)
+    return data
+
+
 class FutharkError(RuntimeError):
     def __init__(self, code, message):
         super().__init__("futhark error %d: %s" % (code, message))
@@ -125,6 +170,10 @@ def load():
     L.futhark_entry_transpose_f32.argtypes = [vp, pvp, vp]
     L.futhark_entry_transpose_f32_3d.argtypes = [vp, pvp, vp]
     L.futhark_entry_exscan_i32.argtypes = [vp, pvp, vp]
+    L.futhark_b200_value_error.restype = ctypes.c_char_p
+    L.futhark_b200_value_read_mem.argtypes = [vp, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t), ctypes.c_char_p, ci, ctypes.POINTER(HostValue)]
+    L.futhark_b200_value_write_mem.argtypes = [ctypes.POINTER(HostValue), ci, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
+    L.futhark_b200_value_free.argtypes = [ctypes.POINTER(HostValue)]
     L.futhark_b200_lmad_copy.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.c_uint64, i64, vp, ctypes.c_uint64, i64, vp, vp]
     L.futhark_b200_lmad_classify.argtypes = [ctypes.c_int, vp, vp, vp, vp]
     L.futhark_entry_mss_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]

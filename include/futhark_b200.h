@@ -302,6 +302,32 @@ int futhark_b200_lmad_copy(struct futhark_context *ctx, int elem_size, int r,
 int futhark_b200_lmad_classify(int r, const int64_t *dst_strides, const int64_t *src_strides,
                                const int64_t *shape, int64_t *knm);
 
+/* Host-side values in the two formats of the reference's compiled executables: the textual
+ * value syntax and the binary data format (docs/binary-data-format.rst; the behaviour of
+ * rts/c/values.h:18-845: read_array/read_scalar, write_array/write_scalar, end_of_input).
+ * Readers are typed like the reference's: the caller names the element type ("i8" ... "u64",
+ * "f16", "f32", "f64", "bool") and the rank its entry point expects; text or binary is detected
+ * per value (a leading 'b'), text elements may omit the type suffix, `--` comments are skipped.
+ * Unlike the reference, which ends the process, a malformed or mismatching value returns 1 and
+ * leaves a message for futhark_b200_value_error().  f16 data is binary16 bits. */
+struct futhark_b200_value {
+  char type[8];        /* element type name */
+  int32_t rank;        /* 0 for a scalar */
+  int64_t shape[8];
+  void *data;          /* row-major elements, malloc'd by the readers */
+};
+int futhark_b200_value_read(FILE *f, const char *type, int rank, struct futhark_b200_value *out);
+int futhark_b200_value_write(FILE *f, const struct futhark_b200_value *v, int binary);
+void futhark_b200_value_free(struct futhark_b200_value *v);
+/* 0 when nothing but blanks and comments remains (rts/c/values.h:713-722) */
+int futhark_b200_value_end_of_input(FILE *f);
+const char *futhark_b200_value_error(void);
+/* The same over memory: *consumed receives the bytes read; *buf is malloc'd. */
+int futhark_b200_value_read_mem(const void *buf, size_t len, size_t *consumed, const char *type,
+                                int rank, struct futhark_b200_value *out);
+int futhark_b200_value_write_mem(const struct futhark_b200_value *v, int binary, void **buf,
+                                 size_t *len);
+
 /* Shard-local pieces, for one logical array split into contiguous shards over several
  * contexts (one per GPU).  The reference is single-device (rts/c/backends/cuda.h:219) and has
  * no counterpart.  All are asynchronous; device pointers passed in must belong to the

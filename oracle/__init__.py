@@ -278,3 +278,58 @@ def ref_lmad_classify(dst_strides, src_strides, shape):
     knm = np.zeros(3, np.int64)
     kind = R.ref_lmad_classify(len(shape), _p(ds), _p(ss), _p(sh), _p(knm))
     return kind, knm.tolist()
+
+
+_refval = None
+
+
+def ref_values():
+    """The reference's own value reader/writer (oracle/_ref/libref_values.so), or None if not built."""
+    global _refval
+    if _refval is None:
+        path = os.path.join(_HERE, "_ref", "libref_values.so")
+        if not os.path.exists(path):
+            try:
+                _build.build()
+            except Exception:
+                pass
+        if not os.path.exists(path):
+            return None
+        R = ctypes.CDLL(path)
+        vp = ctypes.c_void_p
+        R.ref_write_value.argtypes = [ctypes.c_char_p, ctypes.c_int, vp, vp, ctypes.c_int, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
+        R.ref_read_value.argtypes = [ctypes.c_char_p, vp, ctypes.c_size_t, ctypes.POINTER(vp), vp, ctypes.c_int]
+        R.ref_free.argtypes = [vp]
+        _refval = R
+    return _refval
+
+
+def ref_write_value(tname, arr, binary):
+    """bytes of `arr` (numpy, any rank; f16 as uint16 bits, bool as uint8) written by the reference."""
+    R = ref_values()
+    arr = np.asarray(arr)
+    if not arr.flags.c_contiguous:
+        arr = arr.copy()
+    shape = np.asarray(arr.shape, np.int64)
+    out, n = ctypes.c_void_p(), ctypes.c_size_t()
+    rc = R.ref_write_value(tname.encode(), int(binary), _p(arr), _p(shape), arr.ndim, ctypes.byref(out), ctypes.byref(n))
+    assert rc == 0, rc
+    data = ctypes.string_at(out.value, n.value)
+    R.ref_free(out)
+    return data
+
+
+def ref_read_value(tname, data, rank, dtype):
+    """The value in `data` (bytes) as read by the reference: (status, numpy array or None)."""
+    R = ref_values()
+    buf = ctypes.create_string_buffer(data, len(data))
+    ptr = ctypes.c_void_p()
+    shape = np.zeros(max(rank, 1), np.int64)
+    rc = R.ref_read_value(tname.encode(), buf, len(data), ctypes.byref(ptr), _p(shape), rank)
+    if rc != 0:
+        return rc, None
+    dims = tuple(int(x) for x in shape[:rank])
+    count = int(np.prod(dims)) if rank else 1
+    out = np.frombuffer(ctypes.string_at(ptr.value, count * np.dtype(dtype).itemsize), dtype).reshape(dims).copy()
+    R.ref_free(ptr)
+    return 0, out

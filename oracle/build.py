@@ -3,7 +3,8 @@
 `build()` compiles oracle/oracle.c into oracle/liboracle.so and, when a checkout of
 the reference is present, the scalar shim oracle/ref_scalar.c against the
 reference's own rts/c headers into oracle/_ref/libref_scalar.so, and likewise
-oracle/ref_copy.c against rts/c/copy.h into oracle/_ref/libref_copy.so.  Nothing from the
+oracle/ref_copy.c against rts/c/copy.h into oracle/_ref/libref_copy.so and
+oracle/ref_values.c against rts/c/values.h into oracle/_ref/libref_values.so.  Nothing from the
 reference is copied: the headers are included from where they lie.
 """
 import os
@@ -48,6 +49,16 @@ def build(force=False, verbose=False):
         if force or _stale(cp_lib, [cp_src]):
             os.makedirs(ref_dir, exist_ok=True)
             cmd = ["gcc", "-O2", "-std=c99", "-w", "-shared", "-fPIC", "-I", REFERENCE_RTS, cp_src, "-o", cp_lib]
+            if verbose:
+                print(" ".join(cmd))
+            subprocess.check_call(cmd)
+    # the reference's value reader/writer (rts/c/values.h), same recipe
+    v_src = os.path.join(HERE, "ref_values.c")
+    v_lib = os.path.join(ref_dir, "libref_values.so")
+    if os.path.isfile(os.path.join(REFERENCE_RTS, "values.h")):
+        if force or _stale(v_lib, [v_src]):
+            os.makedirs(ref_dir, exist_ok=True)
+            cmd = ["gcc", "-O2", "-std=gnu99", "-w", "-shared", "-fPIC", "-I", REFERENCE_RTS, v_src, "-o", v_lib, "-lm"]
             if verbose:
                 print(" ".join(cmd))
             subprocess.check_call(cmd)
