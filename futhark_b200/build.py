@@ -62,7 +62,26 @@ def build(force=False, verbose=False, ptxas_v=False):
         subprocess.check_call(cmd)
     if ptxas_v and log:
         print(log)
+    build_cli(force, verbose)
     return LIB
+
+
+CLI_SRC = os.path.join(HERE, "cli", "futhark_b200_cli.cpp")
+CLI_BIN = os.path.join(HERE, "futhark_b200_cli")
+
+
+def build_cli(force=False, verbose=False):
+    """The executable front-end (plain C++ on the C ABI), linked against the library beside it."""
+    header = os.path.join(HERE, "..", "include", "futhark_b200.h")
+    newest = max(os.path.getmtime(p) for p in (CLI_SRC, header, LIB))
+    if not force and os.path.exists(CLI_BIN) and os.path.getmtime(CLI_BIN) >= newest:
+        return CLI_BIN
+    cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O2", "-Wall", CLI_SRC, "-L", HERE, "-lfuthark_b200",
+           "-Wl,-rpath,$ORIGIN", "-o", CLI_BIN]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+    return CLI_BIN
 
 
 if __name__ == "__main__":
