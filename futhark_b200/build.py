@@ -66,21 +66,25 @@ def build(force=False, verbose=False, ptxas_v=False):
     return LIB
 
 
-CLI_SRC = os.path.join(HERE, "cli", "futhark_b200_cli.cpp")
+CLI_DIR = os.path.join(HERE, "cli")
 CLI_BIN = os.path.join(HERE, "futhark_b200_cli")
+SERVER_BIN = os.path.join(HERE, "futhark_b200_server")
 
 
 def build_cli(force=False, verbose=False):
-    """The executable front-end (plain C++ on the C ABI), linked against the library beside it."""
+    """The executable and server front-ends (plain C++ on the C ABI), linked against the library beside them."""
     header = os.path.join(HERE, "..", "include", "futhark_b200.h")
-    newest = max(os.path.getmtime(p) for p in (CLI_SRC, header, LIB))
-    if not force and os.path.exists(CLI_BIN) and os.path.getmtime(CLI_BIN) >= newest:
-        return CLI_BIN
-    cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O2", "-Wall", CLI_SRC, "-L", HERE, "-lfuthark_b200",
-           "-Wl,-rpath,$ORIGIN", "-o", CLI_BIN]
-    if verbose:
-        print(" ".join(cmd), flush=True)
-    subprocess.check_call(cmd)
+    table = os.path.join(CLI_DIR, "entry_table.h")
+    for src, out in (("futhark_b200_cli.cpp", CLI_BIN), ("futhark_b200_server.cpp", SERVER_BIN)):
+        src = os.path.join(CLI_DIR, src)
+        newest = max(os.path.getmtime(p) for p in (src, table, header, LIB))
+        if not force and os.path.exists(out) and os.path.getmtime(out) >= newest:
+            continue
+        cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O2", "-Wall", src, "-L", HERE, "-lfuthark_b200",
+               "-Wl,-rpath,$ORIGIN", "-o", out]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
     return CLI_BIN
 
 

@@ -1,0 +1,207 @@
+// What the two front-ends (the executable and the server) know about the library: its array
+// types, its entry points with their parameter and result types, and a uniform representation
+// of the values they pass around.  It plays the part of the manifest-driven tables that the
+// reference generates into every program (src/Futhark/CodeGen/Backends/GenericC/Server.hs:
+// one `struct type` with restore/store/free functions per type and one `struct entry_point` per
+// entry; GenericC/CLI.hs for the executable).  Plain C++ on the library's C ABI.
+#pragma once
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <functional>
+#include <string>
+#include <vector>
+
+#define FUTHARK_B200_NO_CUDA_H
+#include "../../include/futhark_b200.h"
+
+namespace fe {
+
+struct PrimType { const char *name; size_t size; };
+static const PrimType PRIMS[] = {{"i8", 1}, {"i16", 2}, {"i32", 4}, {"i64", 8}, {"u8", 1}, {"u16", 2}, {"u32", 4},
+                                 {"u64", 8}, {"f16", 2}, {"f32", 4}, {"f64", 8}, {"bool", 1}};
+inline const PrimType *prim_type(const std::string &name) {
+  for (const PrimType &p : PRIMS)
+    if (name == p.name) return &p;
+  return nullptr;
+}
+
+// An array type of the C API behind type-erased functions.
+struct ArrayType {
+  const char *name;      // as the server protocol prints it: "[]i32", "[][][]f16"
+  const char *elem;
+  int rank;
+  size_t elem_size;
+  void *(*make)(futhark_context *, const void *, const int64_t *);
+  int (*values)(futhark_context *, void *, void *);
+  const int64_t *(*shape)(futhark_context *, void *);
+  int (*release)(futhark_context *, void *);
+};
+
+#define FE_DIMS_1 s[0]
+#define FE_DIMS_2 s[0], s[1]
+#define FE_DIMS_3 s[0], s[1], s[2]
+#define FE_ARRAY(T, CT, R, NAME, ELEM)                                                                              \
+  {NAME, ELEM, R, sizeof(CT),                                                                                       \
+   [](futhark_context *c, const void *d, const int64_t *s) -> void * { return futhark_new_##T##_##R##d(c, (const CT *)d, FE_DIMS_##R); }, \
+   [](futhark_context *c, void *a, void *d) { return futhark_values_##T##_##R##d(c, (futhark_##T##_##R##d *)a, (CT *)d); },              \
+   [](futhark_context *c, void *a) { return futhark_shape_##T##_##R##d(c, (futhark_##T##_##R##d *)a); },                                 \
+   [](futhark_context *c, void *a) { return futhark_free_##T##_##R##d(c, (futhark_##T##_##R##d *)a); }}
+
+static const ArrayType ARRAYS[] = {
+    FE_ARRAY(i32, int32_t, 1, "[]i32", "i32"),   FE_ARRAY(i64, int64_t, 1, "[]i64", "i64"), FE_ARRAY(u32, uint32_t, 1, "[]u32", "u32"),
+    FE_ARRAY(f32, float, 1, "[]f32", "f32"),     FE_ARRAY(bool, bool, 1, "[]bool", "bool"), FE_ARRAY(f32, float, 2, "[][]f32", "f32"),
+    FE_ARRAY(f32, float, 3, "[][][]f32", "f32"), FE_ARRAY(f16, uint16_t, 3, "[][][]f16", "f16"),
+};
+inline const ArrayType *array_type(const std::string &name) {
+  for (const ArrayType &a : ARRAYS)
+    if (name == a.name) return &a;
+  return nullptr;
+}
+
+// The record types entry points return (tuples: fields named 0, 1, ... as in the C API).
+struct RecordType { const char *name; std::vector<const char *> fields; };
+static const RecordType RECORDS[] = {{"([]u32, []u32)", {"[]u32", "[]u32"}}, {"(i32, f32)", {"i32", "f32"}}};
+inline const RecordType *record_type(const std::string &name) {
+  for (const RecordType &r : RECORDS)
+    if (name == r.name) return &r;
+  return nullptr;
+}
+
+// A value: a scalar held on the host, an array held on the device, or a record of values.
+struct Value {
+  std::string type;
+  const ArrayType *array = nullptr;
+  void *arr = nullptr;
+  unsigned char scalar[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  std::vector<Value> fields;
+};
+
+inline int release(futhark_context *ctx, Value &v) {
+  int rc = 0;
+  if (v.arr != nullptr) rc |= v.array->release(ctx, v.arr);
+  v.arr = nullptr;
+  for (Value &f : v.fields) rc |= release(ctx, f);
+  v.fields.clear();
+  return rc;
+}
+
+inline void set_array(Value &v, const char *type, void *arr) {
+  v.type = type;
+  v.array = array_type(type);
+  v.arr = arr;
+}
+template <typename T>
+inline void set_scalar(Value &v, const char *type, T x) {
+  v.type = type;
+  memcpy(v.scalar, &x, sizeof(T));
+}
+template <typename T>
+inline T scalar_of(const Value &v) {
+  T x;
+  memcpy(&x, v.scalar, sizeof(T));
+  return x;
+}
+
+// Host value (as read from a file) -> value; arrays are uploaded.  Returns 0, or 1 with the
+// context's error set / a type that is not transparent.
+inline int from_host(futhark_context *ctx, const std::string &type, const futhark_b200_value &h, Value &out) {
+  if (const ArrayType *a = array_type(type)) {
+    void *arr = a->make(ctx, h.data, h.shape);
+    if (arr == nullptr) return 1;
+    set_array(out, a->name, arr);
+    return 0;
+  }
+  if (const PrimType *p = prim_type(type)) {
+    out.type = p->name;
+    memcpy(out.scalar, h.data, p->size);
+    return 0;
+  }
+  return 1;
+}
+
+// Value -> host value (malloc'd data; arrays are downloaded, the caller synchronises before use).
+inline int to_host(futhark_context *ctx, const Value &v, futhark_b200_value &h) {
+  memset(&h, 0, sizeof(h));
+  if (v.array != nullptr) {
+    snprintf(h.type, sizeof(h.type), "%s", v.array->elem);
+    h.rank = v.array->rank;
+    const int64_t *shape = v.array->shape(ctx, v.arr);
+    size_t n = 1;
+    for (int d = 0; d < h.rank; d++) { h.shape[d] = shape[d]; n *= (size_t)shape[d]; }
+    h.data = calloc(n ? n : 1, v.array->elem_size);
+    return v.array->values(ctx, v.arr, h.data);
+  }
+  const PrimType *p = prim_type(v.type);
+  if (p == nullptr) return 1;
+  snprintf(h.type, sizeof(h.type), "%s", p->name);
+  h.rank = 0;
+  h.data = calloc(1, 8);
+  memcpy(h.data, v.scalar, p->size);
+  return 0;
+}
+
+// "[][]f32" -> ("f32", 2); a scalar type has rank 0
+inline void split_type(const std::string &type, std::string &elem, int &rank) {
+  size_t i = 0;
+  rank = 0;
+  while (type.compare(i, 2, "[]") == 0) { i += 2; rank++; }
+  elem = type.substr(i);
+}
+
+struct EntryPoint {
+  const char *name;
+  std::vector<const char *> ins;
+  const char *out;
+  std::function<int(futhark_context *, const std::vector<const Value *> &, Value &)> call;
+};
+
+#define FE_IN(i, T) ((const futhark_##T *)in[i]->arr)
+
+inline const std::vector<EntryPoint> &entry_points() {
+  typedef futhark_context C;
+  typedef const std::vector<const Value *> &In;
+  static const std::vector<EntryPoint> table = {
+      {"scan_i32", {"[]i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_scan_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_array(o, "[]i32", r); return rc; }},
+      {"exscan_i32", {"[]i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_exscan_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_array(o, "[]i32", r); return rc; }},
+      {"reduce_i32", {"[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_reduce_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
+      {"mss_i32", {"[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_mss_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
+      {"sum_i32_f32", {"[]i32"}, "(i32, f32)", [](C *c, In in, Value &o) {
+         int32_t a = 0; float b = 0;
+         int rc = futhark_entry_sum_i32_f32(c, &a, &b, FE_IN(0, i32_1d));
+         if (!rc) { o.type = "(i32, f32)"; o.fields.resize(2); set_scalar(o.fields[0], "i32", a); set_scalar(o.fields[1], "f32", b); }
+         return rc; }},
+      {"segscan_f32", {"[]bool", "[]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_segscan_f32(c, &r, FE_IN(0, bool_1d), FE_IN(1, f32_1d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
+      {"segreduce_f32", {"[]i64", "[]bool", "[]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_segreduce_f32(c, &r, FE_IN(0, i64_1d), FE_IN(1, bool_1d), FE_IN(2, f32_1d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
+      {"rowsum_f32", {"[][]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_rowsum_f32(c, &r, FE_IN(0, f32_2d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
+      {"hist_add_i32", {"i64", "[]i32", "[]i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_hist_add_i32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_1d), FE_IN(2, i32_1d)); if (!rc) set_array(o, "[]i32", r); return rc; }},
+      {"hist_max_f32", {"i64", "[]i32", "[]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_hist_max_f32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_1d), FE_IN(2, f32_1d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
+      {"filter_u32", {"[]u32"}, "[]u32", [](C *c, In in, Value &o) { futhark_u32_1d *r = nullptr; int rc = futhark_entry_filter_u32(c, &r, FE_IN(0, u32_1d)); if (!rc) set_array(o, "[]u32", r); return rc; }},
+      {"partition_u32", {"[]u32"}, "([]u32, []u32)", [](C *c, In in, Value &o) {
+         futhark_opaque_tup2_arr1d_u32_arr1d_u32 *r = nullptr;
+         int rc = futhark_entry_partition_u32(c, &r, FE_IN(0, u32_1d));
+         if (rc) return rc;
+         futhark_u32_1d *a = nullptr, *b = nullptr;
+         rc = futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_0(c, &a, r) | futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(c, &b, r);
+         rc |= futhark_free_opaque_tup2_arr1d_u32_arr1d_u32(c, r);
+         o.type = "([]u32, []u32)";
+         o.fields.resize(2);
+         set_array(o.fields[0], "[]u32", a);
+         set_array(o.fields[1], "[]u32", b);
+         return rc; }},
+      {"bmm_f16", {"[][][]f16", "[][][]f16"}, "[][][]f32", [](C *c, In in, Value &o) { futhark_f32_3d *r = nullptr; int rc = futhark_entry_bmm_f16(c, &r, FE_IN(0, f16_3d), FE_IN(1, f16_3d)); if (!rc) set_array(o, "[][][]f32", r); return rc; }},
+      {"transpose_f32", {"[][]f32"}, "[][]f32", [](C *c, In in, Value &o) { futhark_f32_2d *r = nullptr; int rc = futhark_entry_transpose_f32(c, &r, FE_IN(0, f32_2d)); if (!rc) set_array(o, "[][]f32", r); return rc; }},
+      {"transpose_f32_3d", {"[][][]f32"}, "[][][]f32", [](C *c, In in, Value &o) { futhark_f32_3d *r = nullptr; int rc = futhark_entry_transpose_f32_3d(c, &r, FE_IN(0, f32_3d)); if (!rc) set_array(o, "[][][]f32", r); return rc; }},
+  };
+  return table;
+}
+
+inline const EntryPoint *entry_point(const std::string &name) {
+  for (const EntryPoint &e : entry_points())
+    if (name == e.name) return &e;
+  return nullptr;
+}
+
+}  // namespace fe

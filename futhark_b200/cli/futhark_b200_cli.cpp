@@ -16,13 +16,10 @@
 #include <string.h>
 #include <sys/time.h>
 
-#include <functional>
-#include <memory>
 #include <string>
 #include <vector>
 
-#define FUTHARK_B200_NO_CUDA_H
-#include "../../include/futhark_b200.h"
+#include "entry_table.h"
 
 static void panic(int code, const char *fmt, ...) {
   va_list ap;
@@ -38,281 +35,11 @@ static int64_t wall_usec() {
   return (int64_t)t.tv_sec * 1000000 + t.tv_usec;
 }
 
-typedef futhark_b200_value Val;
-
-struct Param { const char *type; int rank; };
-
-// One entry point: its parameter and result types as the manifest would list them, and a
-// runner that packs host values into arrays, calls the entry and unpacks the results.
-struct Entry {
-  const char *name;
-  std::vector<Param> ins, outs;
-  // uploads happen in `pack`, outside the timed region, as in the generated code
-  std::function<void(futhark_context *, const std::vector<Val> &)> pack;
-  std::function<int(futhark_context *)> run;                       // the timed call
-  std::function<void(futhark_context *, std::vector<Val> &)> fetch;  // results to host values
-  std::function<void(futhark_context *)> free_outputs, free_inputs;
-};
-
 static void check(futhark_context *ctx, int rc) {
   if (rc != 0) {
     char *e = futhark_context_get_error(ctx);
     panic(1, "%s", e ? e : "unknown error\n");
   }
-}
-
-static Val host_val(const char *type, int rank, const int64_t *shape, size_t elem) {
-  Val v;
-  memset(&v, 0, sizeof(v));
-  snprintf(v.type, sizeof(v.type), "%s", type);
-  v.rank = rank;
-  size_t n = 1;
-  for (int d = 0; d < rank; d++) { v.shape[d] = shape[d]; n *= (size_t)shape[d]; }
-  v.data = calloc(n ? n : 1, elem);
-  return v;
-}
-
-// ---- array plumbing per array type of the API -----------------------------------------------------
-#define ARR1(T, CT, NAME)                                                                                          \
-  static futhark_##T##_1d *up_##T##_1d(futhark_context *c, const Val &v) {                                         \
-    futhark_##T##_1d *a = futhark_new_##T##_1d(c, (const CT *)v.data, v.shape[0]);                                  \
-    if (a == nullptr) check(c, 1);                                                                                 \
-    return a;                                                                                                      \
-  }                                                                                                                \
-  [[maybe_unused]] static Val down_##T##_1d(futhark_context *c, futhark_##T##_1d *a) {                                            \
-    Val v = host_val(NAME, 1, futhark_shape_##T##_1d(c, a), sizeof(CT));                                            \
-    check(c, futhark_values_##T##_1d(c, a, (CT *)v.data));                                                         \
-    return v;                                                                                                      \
-  }
-ARR1(i32, int32_t, "i32")
-ARR1(i64, int64_t, "i64")
-ARR1(u32, uint32_t, "u32")
-ARR1(f32, float, "f32")
-ARR1(bool, bool, "bool")
-
-static futhark_f32_2d *up_f32_2d(futhark_context *c, const Val &v) {
-  futhark_f32_2d *a = futhark_new_f32_2d(c, (const float *)v.data, v.shape[0], v.shape[1]);
-  if (a == nullptr) check(c, 1);
-  return a;
-}
-static Val down_f32_2d(futhark_context *c, futhark_f32_2d *a) {
-  Val v = host_val("f32", 2, futhark_shape_f32_2d(c, a), 4);
-  check(c, futhark_values_f32_2d(c, a, (float *)v.data));
-  return v;
-}
-static futhark_f32_3d *up_f32_3d(futhark_context *c, const Val &v) {
-  futhark_f32_3d *a = futhark_new_f32_3d(c, (const float *)v.data, v.shape[0], v.shape[1], v.shape[2]);
-  if (a == nullptr) check(c, 1);
-  return a;
-}
-static Val down_f32_3d(futhark_context *c, futhark_f32_3d *a) {
-  Val v = host_val("f32", 3, futhark_shape_f32_3d(c, a), 4);
-  check(c, futhark_values_f32_3d(c, a, (float *)v.data));
-  return v;
-}
-static futhark_f16_3d *up_f16_3d(futhark_context *c, const Val &v) {
-  futhark_f16_3d *a = futhark_new_f16_3d(c, (const uint16_t *)v.data, v.shape[0], v.shape[1], v.shape[2]);
-  if (a == nullptr) check(c, 1);
-  return a;
-}
-
-static Val scalar_val(const char *type, const void *src, size_t elem) {
-  Val v = host_val(type, 0, nullptr, 8);
-  memcpy(v.data, src, elem);
-  return v;
-}
-
-// ---- the entry points ------------------------------------------------------------------------------
-// array in -> array out, same element type and rank 1
-template <typename A, typename UP, typename DOWN, typename FREE, typename CALL>
-static Entry map1(const char *name, const char *t, UP up, DOWN down, FREE fr, CALL call) {
-  struct St { A *in = nullptr, *out = nullptr; };
-  auto st = std::make_shared<St>();
-  Entry e;
-  e.name = name;
-  e.ins = {{t, 1}};
-  e.outs = {{t, 1}};
-  e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->in = up(c, v[0]); };
-  e.run = [=](futhark_context *c) { return call(c, &st->out, st->in); };
-  e.fetch = [=](futhark_context *c, std::vector<Val> &o) { o.push_back(down(c, st->out)); };
-  e.free_outputs = [=](futhark_context *c) { if (st->out) { fr(c, st->out); st->out = nullptr; } };
-  e.free_inputs = [=](futhark_context *c) { if (st->in) { fr(c, st->in); st->in = nullptr; } };
-  return e;
-}
-
-static std::vector<Entry> make_entries() {
-  std::vector<Entry> es;
-  es.push_back(map1<futhark_i32_1d>("scan_i32", "i32", up_i32_1d, down_i32_1d, futhark_free_i32_1d, futhark_entry_scan_i32));
-  es.push_back(map1<futhark_i32_1d>("exscan_i32", "i32", up_i32_1d, down_i32_1d, futhark_free_i32_1d, futhark_entry_exscan_i32));
-  es.push_back(map1<futhark_u32_1d>("filter_u32", "u32", up_u32_1d, down_u32_1d, futhark_free_u32_1d, futhark_entry_filter_u32));
-
-  {  // i32 array -> i32 scalar
-    struct St { futhark_i32_1d *in = nullptr; int32_t out = 0; };
-    for (int which = 0; which < 2; which++) {
-      auto st = std::make_shared<St>();
-      Entry e;
-      e.name = which == 0 ? "reduce_i32" : "mss_i32";
-      e.ins = {{"i32", 1}};
-      e.outs = {{"i32", 0}};
-      e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->in = up_i32_1d(c, v[0]); };
-      e.run = [=](futhark_context *c) { return which == 0 ? futhark_entry_reduce_i32(c, &st->out, st->in) : futhark_entry_mss_i32(c, &st->out, st->in); };
-      e.fetch = [=](futhark_context *, std::vector<Val> &o) { o.push_back(scalar_val("i32", &st->out, 4)); };
-      e.free_outputs = [](futhark_context *) {};
-      e.free_inputs = [=](futhark_context *c) { if (st->in) { futhark_free_i32_1d(c, st->in); st->in = nullptr; } };
-      es.push_back(e);
-    }
-  }
-  {  // i32 array -> (i32, f32)
-    struct St { futhark_i32_1d *in = nullptr; int32_t o0 = 0; float o1 = 0; };
-    auto st = std::make_shared<St>();
-    Entry e;
-    e.name = "sum_i32_f32";
-    e.ins = {{"i32", 1}};
-    e.outs = {{"i32", 0}, {"f32", 0}};
-    e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->in = up_i32_1d(c, v[0]); };
-    e.run = [=](futhark_context *c) { return futhark_entry_sum_i32_f32(c, &st->o0, &st->o1, st->in); };
-    e.fetch = [=](futhark_context *, std::vector<Val> &o) { o.push_back(scalar_val("i32", &st->o0, 4)); o.push_back(scalar_val("f32", &st->o1, 4)); };
-    e.free_outputs = [](futhark_context *) {};
-    e.free_inputs = [=](futhark_context *c) { if (st->in) { futhark_free_i32_1d(c, st->in); st->in = nullptr; } };
-    es.push_back(e);
-  }
-  {  // (flags, xs) -> f32 array
-    struct St { futhark_bool_1d *f = nullptr; futhark_f32_1d *x = nullptr, *out = nullptr; };
-    auto st = std::make_shared<St>();
-    Entry e;
-    e.name = "segscan_f32";
-    e.ins = {{"bool", 1}, {"f32", 1}};
-    e.outs = {{"f32", 1}};
-    e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->f = up_bool_1d(c, v[0]); st->x = up_f32_1d(c, v[1]); };
-    e.run = [=](futhark_context *c) { return futhark_entry_segscan_f32(c, &st->out, st->f, st->x); };
-    e.fetch = [=](futhark_context *c, std::vector<Val> &o) { o.push_back(down_f32_1d(c, st->out)); };
-    e.free_outputs = [=](futhark_context *c) { if (st->out) { futhark_free_f32_1d(c, st->out); st->out = nullptr; } };
-    e.free_inputs = [=](futhark_context *c) {
-      if (st->f) { futhark_free_bool_1d(c, st->f); st->f = nullptr; }
-      if (st->x) { futhark_free_f32_1d(c, st->x); st->x = nullptr; }
-    };
-    es.push_back(e);
-  }
-  {  // (offsets, flags, xs) -> f32 array
-    struct St { futhark_i64_1d *o = nullptr; futhark_bool_1d *f = nullptr; futhark_f32_1d *x = nullptr, *out = nullptr; };
-    auto st = std::make_shared<St>();
-    Entry e;
-    e.name = "segreduce_f32";
-    e.ins = {{"i64", 1}, {"bool", 1}, {"f32", 1}};
-    e.outs = {{"f32", 1}};
-    e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->o = up_i64_1d(c, v[0]); st->f = up_bool_1d(c, v[1]); st->x = up_f32_1d(c, v[2]); };
-    e.run = [=](futhark_context *c) { return futhark_entry_segreduce_f32(c, &st->out, st->o, st->f, st->x); };
-    e.fetch = [=](futhark_context *c, std::vector<Val> &o) { o.push_back(down_f32_1d(c, st->out)); };
-    e.free_outputs = [=](futhark_context *c) { if (st->out) { futhark_free_f32_1d(c, st->out); st->out = nullptr; } };
-    e.free_inputs = [=](futhark_context *c) {
-      if (st->o) { futhark_free_i64_1d(c, st->o); st->o = nullptr; }
-      if (st->f) { futhark_free_bool_1d(c, st->f); st->f = nullptr; }
-      if (st->x) { futhark_free_f32_1d(c, st->x); st->x = nullptr; }
-    };
-    es.push_back(e);
-  }
-  {  // [][]f32 -> []f32 and [][]f32 -> [][]f32
-    struct St { futhark_f32_2d *in = nullptr, *out2 = nullptr; futhark_f32_1d *out1 = nullptr; };
-    for (int which = 0; which < 2; which++) {
-      auto st = std::make_shared<St>();
-      Entry e;
-      e.name = which == 0 ? "rowsum_f32" : "transpose_f32";
-      e.ins = {{"f32", 2}};
-      e.outs = {{"f32", which == 0 ? 1 : 2}};
-      e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->in = up_f32_2d(c, v[0]); };
-      e.run = [=](futhark_context *c) { return which == 0 ? futhark_entry_rowsum_f32(c, &st->out1, st->in) : futhark_entry_transpose_f32(c, &st->out2, st->in); };
-      e.fetch = [=](futhark_context *c, std::vector<Val> &o) { o.push_back(which == 0 ? down_f32_1d(c, st->out1) : down_f32_2d(c, st->out2)); };
-      e.free_outputs = [=](futhark_context *c) {
-        if (st->out1) { futhark_free_f32_1d(c, st->out1); st->out1 = nullptr; }
-        if (st->out2) { futhark_free_f32_2d(c, st->out2); st->out2 = nullptr; }
-      };
-      e.free_inputs = [=](futhark_context *c) { if (st->in) { futhark_free_f32_2d(c, st->in); st->in = nullptr; } };
-      es.push_back(e);
-    }
-  }
-  {  // [][][]f32 -> [][][]f32
-    struct St { futhark_f32_3d *in = nullptr, *out = nullptr; };
-    auto st = std::make_shared<St>();
-    Entry e;
-    e.name = "transpose_f32_3d";
-    e.ins = {{"f32", 3}};
-    e.outs = {{"f32", 3}};
-    e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->in = up_f32_3d(c, v[0]); };
-    e.run = [=](futhark_context *c) { return futhark_entry_transpose_f32_3d(c, &st->out, st->in); };
-    e.fetch = [=](futhark_context *c, std::vector<Val> &o) { o.push_back(down_f32_3d(c, st->out)); };
-    e.free_outputs = [=](futhark_context *c) { if (st->out) { futhark_free_f32_3d(c, st->out); st->out = nullptr; } };
-    e.free_inputs = [=](futhark_context *c) { if (st->in) { futhark_free_f32_3d(c, st->in); st->in = nullptr; } };
-    es.push_back(e);
-  }
-  {  // (B, is, ws) -> histogram
-    struct St { int64_t B = 0; futhark_i32_1d *is = nullptr, *wi = nullptr, *oi = nullptr; futhark_f32_1d *wf = nullptr, *of = nullptr; };
-    for (int which = 0; which < 2; which++) {
-      auto st = std::make_shared<St>();
-      Entry e;
-      e.name = which == 0 ? "hist_add_i32" : "hist_max_f32";
-      e.ins = {{"i64", 0}, {"i32", 1}, {which == 0 ? "i32" : "f32", 1}};
-      e.outs = {{which == 0 ? "i32" : "f32", 1}};
-      e.pack = [=](futhark_context *c, const std::vector<Val> &v) {
-        st->B = *(const int64_t *)v[0].data;
-        st->is = up_i32_1d(c, v[1]);
-        if (which == 0) st->wi = up_i32_1d(c, v[2]); else st->wf = up_f32_1d(c, v[2]);
-      };
-      e.run = [=](futhark_context *c) {
-        return which == 0 ? futhark_entry_hist_add_i32(c, &st->oi, st->B, st->is, st->wi) : futhark_entry_hist_max_f32(c, &st->of, st->B, st->is, st->wf);
-      };
-      e.fetch = [=](futhark_context *c, std::vector<Val> &o) { o.push_back(which == 0 ? down_i32_1d(c, st->oi) : down_f32_1d(c, st->of)); };
-      e.free_outputs = [=](futhark_context *c) {
-        if (st->oi) { futhark_free_i32_1d(c, st->oi); st->oi = nullptr; }
-        if (st->of) { futhark_free_f32_1d(c, st->of); st->of = nullptr; }
-      };
-      e.free_inputs = [=](futhark_context *c) {
-        if (st->is) { futhark_free_i32_1d(c, st->is); st->is = nullptr; }
-        if (st->wi) { futhark_free_i32_1d(c, st->wi); st->wi = nullptr; }
-        if (st->wf) { futhark_free_f32_1d(c, st->wf); st->wf = nullptr; }
-      };
-      es.push_back(e);
-    }
-  }
-  {  // []u32 -> ([]u32, []u32): the tuple's fields are printed one per line (CLI.hs:279-296)
-    struct St { futhark_u32_1d *in = nullptr; futhark_opaque_tup2_arr1d_u32_arr1d_u32 *out = nullptr; };
-    auto st = std::make_shared<St>();
-    Entry e;
-    e.name = "partition_u32";
-    e.ins = {{"u32", 1}};
-    e.outs = {{"u32", 1}, {"u32", 1}};
-    e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->in = up_u32_1d(c, v[0]); };
-    e.run = [=](futhark_context *c) { return futhark_entry_partition_u32(c, &st->out, st->in); };
-    e.fetch = [=](futhark_context *c, std::vector<Val> &o) {
-      futhark_u32_1d *a = nullptr, *b = nullptr;
-      check(c, futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_0(c, &a, st->out));
-      check(c, futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(c, &b, st->out));
-      o.push_back(down_u32_1d(c, a));
-      o.push_back(down_u32_1d(c, b));
-      futhark_free_u32_1d(c, a);
-      futhark_free_u32_1d(c, b);
-    };
-    e.free_outputs = [=](futhark_context *c) { if (st->out) { futhark_free_opaque_tup2_arr1d_u32_arr1d_u32(c, st->out); st->out = nullptr; } };
-    e.free_inputs = [=](futhark_context *c) { if (st->in) { futhark_free_u32_1d(c, st->in); st->in = nullptr; } };
-    es.push_back(e);
-  }
-  {  // ([b][m][k]f16, [b][k][n]f16) -> [b][m][n]f32
-    struct St { futhark_f16_3d *a = nullptr, *b = nullptr; futhark_f32_3d *out = nullptr; };
-    auto st = std::make_shared<St>();
-    Entry e;
-    e.name = "bmm_f16";
-    e.ins = {{"f16", 3}, {"f16", 3}};
-    e.outs = {{"f32", 3}};
-    e.pack = [=](futhark_context *c, const std::vector<Val> &v) { st->a = up_f16_3d(c, v[0]); st->b = up_f16_3d(c, v[1]); };
-    e.run = [=](futhark_context *c) { return futhark_entry_bmm_f16(c, &st->out, st->a, st->b); };
-    e.fetch = [=](futhark_context *c, std::vector<Val> &o) { o.push_back(down_f32_3d(c, st->out)); };
-    e.free_outputs = [=](futhark_context *c) { if (st->out) { futhark_free_f32_3d(c, st->out); st->out = nullptr; } };
-    e.free_inputs = [=](futhark_context *c) {
-      if (st->a) { futhark_free_f16_3d(c, st->a); st->a = nullptr; }
-      if (st->b) { futhark_free_f16_3d(c, st->b); st->b = nullptr; }
-    };
-    es.push_back(e);
-  }
-  return es;
 }
 
 static const char *USAGE =
@@ -333,7 +60,6 @@ static const char *USAGE =
     "  --list-entry-points        Print the entry points with their parameter and result types and exit.\n";
 
 int main(int argc, char **argv) {
-  std::vector<Entry> entries = make_entries();
   futhark_context_config *cfg = futhark_context_config_new();
   const char *entry_point = "main";
   const char *runtime_path = nullptr;
@@ -390,12 +116,10 @@ int main(int argc, char **argv) {
       }
       case 4: futhark_context_config_set_cache_file(cfg, optarg); break;
       case 5:
-        for (const Entry &e : entries) {
+        for (const fe::EntryPoint &e : fe::entry_points()) {
           printf("%s:", e.name);
-          for (const Param &p : e.ins) { printf(" "); for (int d = 0; d < p.rank; d++) printf("[]"); printf("%s", p.type); }
-          printf(" ->");
-          for (const Param &p : e.outs) { printf(" "); for (int d = 0; d < p.rank; d++) printf("[]"); printf("%s", p.type); }
-          printf("\n");
+          for (const char *t : e.ins) printf(" %s", t);
+          printf(" -> %s\n", e.out);
         }
         return 0;
       case ':': panic(-1, "Missing argument for option %s\n", argv[optind - 1]);
@@ -404,12 +128,10 @@ int main(int argc, char **argv) {
   }
   if (optind != argc) panic(1, "Excess non-option: %s\n", argv[optind]);
 
-  const Entry *entry = nullptr;
-  for (const Entry &e : entries)
-    if (strcmp(e.name, entry_point) == 0) entry = &e;
+  const fe::EntryPoint *entry = fe::entry_point(entry_point);
   if (entry == nullptr) {
     fprintf(stderr, "No entry point '%s'.  Select another with --entry-point.  Options are:\n", entry_point);
-    for (const Entry &e : entries) fprintf(stderr, "%s\n", e.name);
+    for (const fe::EntryPoint &e : fe::entry_points()) fprintf(stderr, "%s\n", e.name);
     return 1;
   }
 
@@ -427,23 +149,29 @@ int main(int argc, char **argv) {
   futhark_context_pause_profiling(ctx);       // initialisation is not profiled (CLI.hs:385-386)
 
   // read the arguments, then insist on the end of the input (CLI.hs:388-394)
-  std::vector<Val> inputs(entry->ins.size());
+  std::vector<futhark_b200_value> parsed(entry->ins.size());
   for (size_t i = 0; i < entry->ins.size(); i++) {
-    if (futhark_b200_value_read(stdin, entry->ins[i].type, entry->ins[i].rank, &inputs[i]) != 0) {
-      std::string t;
-      for (int d = 0; d < entry->ins[i].rank; d++) t += "[]";
-      panic(1, "Error when reading input #%d of type %s%s (errno: %s).\n%s\n", (int)i, t.c_str(), entry->ins[i].type, strerror(errno),
-            futhark_b200_value_error());
-    }
+    std::string elem;
+    int rank;
+    fe::split_type(entry->ins[i], elem, rank);
+    if (futhark_b200_value_read(stdin, elem.c_str(), rank, &parsed[i]) != 0)
+      panic(1, "Error when reading input #%d of type %s (errno: %s).\n%s\n", (int)i, entry->ins[i], strerror(errno), futhark_b200_value_error());
   }
   if (futhark_b200_value_end_of_input(stdin) != 0) panic(1, "Expected EOF on stdin after reading input for \"%s\".\n", entry->name);
 
+  fe::Value result;
   auto run_once = [&](bool timed, bool profiled) {
-    entry->pack(ctx, inputs);
+    // the arguments are packed into fresh arrays for every run, outside the timed region
+    std::vector<fe::Value> args(entry->ins.size());
+    std::vector<const fe::Value *> argp;
+    for (size_t i = 0; i < args.size(); i++) {
+      if (fe::from_host(ctx, entry->ins[i], parsed[i], args[i]) != 0) check(ctx, 1);
+      argp.push_back(&args[i]);
+    }
     check(ctx, futhark_context_sync(ctx));
     if (profiled) futhark_context_unpause_profiling(ctx);
     const int64_t t0 = wall_usec();
-    check(ctx, entry->run(ctx));
+    check(ctx, entry->call(ctx, argp, result));
     check(ctx, futhark_context_sync(ctx));
     if (profiled) futhark_context_pause_profiling(ctx);
     const int64_t t1 = wall_usec();
@@ -451,29 +179,33 @@ int main(int argc, char **argv) {
       fprintf(runtime_file, "%lld\n", (long long)(t1 - t0));
       fflush(runtime_file);
     }
-    entry->free_inputs(ctx);
+    for (fe::Value &a : args) check(ctx, fe::release(ctx, a));
   };
   if (perform_warmup) {
     run_once(false, false);
-    entry->free_outputs(ctx);
+    check(ctx, fe::release(ctx, result));
   }
   for (int run = 0; run < num_runs; run++) {
     run_once(true, run == num_runs - 1);       // only the last run is profiled
-    if (run < num_runs - 1) entry->free_outputs(ctx);
+    if (run < num_runs - 1) check(ctx, fe::release(ctx, result));
   }
-  for (Val &v : inputs) futhark_b200_value_free(&v);
+  for (futhark_b200_value &v : parsed) futhark_b200_value_free(&v);
 
   if (print_result) {
-    std::vector<Val> outs;
-    entry->fetch(ctx, outs);
-    check(ctx, futhark_context_sync(ctx));
-    for (Val &v : outs) {
-      futhark_b200_value_write(stdout, &v, binary_output);
+    // a tuple's fields are printed one per line (CLI.hs:279-296)
+    std::vector<const fe::Value *> outs;
+    if (result.fields.empty()) outs.push_back(&result);
+    else for (const fe::Value &f : result.fields) outs.push_back(&f);
+    for (const fe::Value *v : outs) {
+      futhark_b200_value h;
+      check(ctx, fe::to_host(ctx, *v, h));
+      check(ctx, futhark_context_sync(ctx));
+      futhark_b200_value_write(stdout, &h, binary_output);
       puts("");
-      futhark_b200_value_free(&v);
+      futhark_b200_value_free(&h);
     }
   }
-  entry->free_outputs(ctx);
+  check(ctx, fe::release(ctx, result));
   if (runtime_file != nullptr) fclose(runtime_file);
   if (profile) {
     char *report = futhark_context_report(ctx);

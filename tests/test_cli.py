@@ -28,7 +28,7 @@ def test_lists_entry_points_and_params_without_a_device(cli):
     assert r.returncode == 0
     lines = dict(l.split(": ") for l in r.stdout.decode().strip().split("\n"))
     assert lines["segscan_f32"] == "[]bool []f32 -> []f32"
-    assert lines["partition_u32"] == "[]u32 -> []u32 []u32"
+    assert lines["partition_u32"] == "[]u32 -> ([]u32, []u32)"
     assert lines["hist_add_i32"] == "i64 []i32 []i32 -> []i32"
     assert len(lines) == 15
     r = run(cli, ["--print-params"])
@@ -100,3 +100,124 @@ def test_input_errors_end_with_status_1(cli):
     assert r.returncode == 1 and b"Expected EOF on stdin" in r.stderr
     r = run(cli, ["-e", "segscan_f32"], b"[true] [1.0, 2.0]")
     assert r.returncode == 1 and b"invalid sizes" in r.stderr
+
+
+# ---- the server front-end (docs/server-protocol.rst of the reference) ---------------------------------
+
+class ServerProc:
+    def __init__(self, path, args=()):
+        self.p = subprocess.Popen([path] + list(args), stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE)
+        assert self._reply() == ([], False)                      # "%%% OK" once initialisation has finished
+
+    def _reply(self):
+        lines, failed = [], False
+        while True:
+            line = self.p.stdout.readline().decode()
+            assert line != "", self.p.stderr.read().decode()
+            line = line.rstrip("\n")
+            if line == "%%% OK":
+                return lines, failed
+            if line == "%%% FAILURE":
+                failed = True
+                continue
+            lines.append(line)
+
+    def cmd(self, text):
+        self.p.stdin.write((text + "\n").encode())
+        self.p.stdin.flush()
+        return self._reply()
+
+    def ok(self, text):
+        lines, failed = self.cmd(text)
+        assert not failed, (text, lines)
+        return lines
+
+    def close(self):
+        self.p.stdin.close()
+        assert self.p.wait(timeout=60) == 0
+
+
+def test_server_without_a_device_fails_loudly(cli):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    r = subprocess.run([build.SERVER_BIN], input=b"types\n", capture_output=True, timeout=120)
+    assert r.returncode == 1 and b"Error during context initialisation" in r.stderr and b"%%% OK" not in r.stdout
+
+
+@gpu
+def test_server_session_restore_call_store_free(cli, tmp_path):
+    s = ServerProc(build.SERVER_BIN)
+    assert "scan_i32" in s.ok("entry_points") and len(s.ok("entry_points")) == 15
+    assert s.ok("inputs segscan_f32") == ["[]bool", "[]f32"] and s.ok("output segscan_f32") == ["*[]f32"]
+    assert s.ok("output partition_u32") == ["*([]u32, []u32)"]
+    assert s.ok('kind "([]u32, []u32)"') == ["record"] and s.ok("kind []i32") == ["array"] and s.ok("kind i64") == ["primitive"]
+    assert s.ok('fields "([]u32, []u32)"') == ["0 []u32", "1 []u32"]
+    assert s.ok("rank [][][]f16") == ["3"] and s.ok("elemtype [][][]f16") == ["f16"]
+    # restore two values of different formats from one file, call, store, compare with the oracle
+    n = 200003
+    offsets, flags, xs = datagen.workload_seg_f32(n)
+    data = tmp_path / "in.dat"
+    data.write_bytes(fb.value_to_bytes(flags, "bool", True) + b"\n" + fb.value_to_bytes(xs, "f32", True))
+    s.ok("restore %s fl []bool xs []f32" % data)
+    assert s.ok("type xs") == ["[]f32"] and s.ok("shape xs") == [str(n)]
+    reply = s.ok("call segscan_f32 out fl xs")
+    assert len(reply) == 1 and reply[0].startswith("runtime: ") and int(reply[0].split()[1]) >= 0
+    outp = tmp_path / "out.dat"
+    s.ok("store %s out" % outp)
+    got, used = fb.value_from_bytes(outp.read_bytes(), "f32", 1)
+    ref = oracle.segscan_f32_seq64(flags, xs)
+    a = np.abs(xs.astype(np.float64))
+    assert float(np.max(np.abs(got - ref) / np.maximum(np.cumsum(a), 1e-6))) <= 1e-5
+    # records: project the fields of a partition, store both in one file
+    keys = datagen.workload_keys_u32(50000)
+    kf = tmp_path / "keys.dat"
+    kf.write_bytes(fb.value_to_bytes(keys, "u32", True))
+    s.ok("restore %s ks []u32" % kf)
+    s.ok("call partition_u32 pr ks")
+    assert s.ok("type pr") == ["([]u32, []u32)"]
+    s.ok("project sel pr 0")
+    s.ok("project rej pr 1")
+    pf = tmp_path / "parts.dat"
+    s.ok("store %s sel rej" % pf)
+    raw = pf.read_bytes()
+    sel, used = fb.value_from_bytes(raw, "u32", 1)
+    rej, _ = fb.value_from_bytes(raw[used:], "u32", 1)
+    mask = (keys & 7) < 3
+    assert np.array_equal(sel, keys[mask]) and np.array_equal(rej, keys[~mask])
+    s.ok("rename sel chosen")
+    s.ok("free chosen rej pr ks out fl xs")
+    # scalars travel as values too
+    hf = tmp_path / "hist.dat"
+    hf.write_bytes(b"4i64 [0, 1, 1, 9, -1] [1, 2, 3, 4, 5]")
+    s.ok("restore %s B i64 is []i32 ws []i32" % hf)
+    s.ok("call hist_add_i32 h B is ws")
+    s.ok("store %s h" % (tmp_path / "h.dat"))
+    assert fb.value_from_bytes((tmp_path / "h.dat").read_bytes(), "i32", 1)[0].tolist() == [1, 5, 0, 0]
+    s.ok("clear")
+    assert s.cmd("type h") == (["Unknown variable: h"], True)
+    s.close()
+
+
+@gpu
+def test_server_failures_keep_the_session_alive(cli, tmp_path):
+    s = ServerProc(build.SERVER_BIN)
+    assert s.cmd("call nonesuch o") == (["Unknown entry point: nonesuch"], True)
+    assert s.cmd("frobnicate") == (["Unknown command: frobnicate"], True)
+    assert s.cmd("restore /nonexistent/file v []i32")[1]
+    f = tmp_path / "v.dat"
+    f.write_bytes(b"[1, 2, 3]")
+    s.ok("restore %s v []i32" % f)
+    assert s.cmd("restore %s v []i32" % f) == (["Variable already exists: v"], True)
+    assert s.cmd("call segscan_f32 o v v") == (["Wrong input type.  Expected []bool, got []i32."], True)
+    assert s.cmd("call scan_i32 v v") == (["Variable already exists: v"], True)
+    f2 = tmp_path / "bad.dat"
+    f2.write_bytes(b"[1.5, 2.5]")
+    lines, failed = s.cmd("restore %s w []i32" % f2)
+    assert failed and lines[0] == "Failed to restore variable w."
+    assert s.cmd("zip a b c")[1]
+    # and the session still works
+    assert s.ok("call reduce_i32 r v")[0].startswith("runtime: ")
+    s.ok("store %s r" % (tmp_path / "r.dat"))
+    assert fb.value_from_bytes((tmp_path / "r.dat").read_bytes(), "i32", 0)[0] == 6
+    s.close()
