@@ -160,6 +160,7 @@ CASES = {
     "rowsum_f32": 1 << 27, "hist_add_i32": 1 << 28, "hist_max_f32": 1 << 28, "filter_u32": 1 << 28,
     "partition_u32": 1 << 28, "bmm_f16": 64, "transpose_f32": 1 << 27,
     "exscan_i32": 1 << 26, "mss_i32": 1 << 26, "sum_i32_f32": 1 << 26, "lmad_permute_f32": 1 << 27,
+    "dotprod_f32": 1 << 26,
 }
 
 
@@ -255,6 +256,10 @@ def run_case(args):
             rows = n // COLS
             a = [ctx.new("f32_2d", datagen.workload_rows_f32(rows, COLS))]
             timed(name, lambda: ctx.entry_transpose_f32(a[0]), 8 * rows * COLS, n)
+        elif name == "dotprod_f32":
+            a = [ctx.new("f32_1d", datagen.normal_f32(datagen.SEEDS["scan_reduce_i32"], 0, n, stream=7)),
+                 ctx.new("f32_1d", datagen.normal_f32(datagen.SEEDS["scan_reduce_i32"], 0, n, stream=8))]
+            timed(name, lambda: ctx.entry_dotprod_f32(a[0], a[1]), 8 * n, n)
         elif name == "lmad_permute_f32":
             # [b][r][1024] -> [r][b][1024] (neither a transposition of two groups nor flat): the general strided copy
             nb, cols = 64, COLS

@@ -170,6 +170,8 @@ def load():
     L.futhark_entry_transpose_f32.argtypes = [vp, pvp, vp]
     L.futhark_entry_transpose_f32_3d.argtypes = [vp, pvp, vp]
     L.futhark_entry_exscan_i32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_dotprod_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_float), vp, vp]
+    L.futhark_entry_prod_of_sums_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp, vp]
     L.futhark_b200_value_error.restype = ctypes.c_char_p
     L.futhark_b200_value_read_mem.argtypes = [vp, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t), ctypes.c_char_p, ci, ctypes.POINTER(HostValue)]
     L.futhark_b200_value_write_mem.argtypes = [ctypes.POINTER(HostValue), ci, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
@@ -433,6 +435,16 @@ class Context:
         self._check(self.lib.futhark_entry_mss_i32(self.ptr, ctypes.byref(out), xs.ptr))
         return int(out.value)
 
+    def entry_dotprod_f32(self, xs, ys):
+        out = ctypes.c_float()
+        self._check(self.lib.futhark_entry_dotprod_f32(self.ptr, ctypes.byref(out), xs.ptr, ys.ptr))
+        return float(out.value)
+
+    def entry_prod_of_sums_i32(self, xs, ys):
+        out = ctypes.c_int32()
+        self._check(self.lib.futhark_entry_prod_of_sums_i32(self.ptr, ctypes.byref(out), xs.ptr, ys.ptr))
+        return int(out.value)
+
     def entry_sum_i32_f32(self, xs):
         oi, of = ctypes.c_int32(), ctypes.c_float()
         self._check(self.lib.futhark_entry_sum_i32_f32(self.ptr, ctypes.byref(oi), ctypes.byref(of), xs.ptr))
@@ -493,6 +505,22 @@ def mss_i32(ctx, xs):
 
 def sum_i32_f32(ctx, xs):
     return _scalar(ctx, xs, ctx.entry_sum_i32_f32)
+
+
+def _scalar2(ctx, tname, xs, ys, fn):
+    a, b = ctx.new(tname, xs), ctx.new(tname, ys)
+    try:
+        return fn(a, b)
+    finally:
+        a.free(); b.free()
+
+
+def dotprod_f32(ctx, xs, ys):
+    return _scalar2(ctx, "f32_1d", xs, ys, ctx.entry_dotprod_f32)
+
+
+def prod_of_sums_i32(ctx, xs, ys):
+    return _scalar2(ctx, "i32_1d", xs, ys, ctx.entry_prod_of_sums_i32)
 
 
 def segscan_f32(ctx, flags, xs):

@@ -148,6 +148,34 @@ int futhark_entry_sum_i32_f32(struct futhark_context *ctx, int32_t *out0, float 
   return FUTHARK_SUCCESS;
 }
 
+// reduce (+) 0 (map2 (*) xs ys): a redomap whose map body takes two inputs.
+int futhark_entry_dotprod_f32(struct futhark_context *ctx, float *out0, const struct futhark_f32_1d *in0, const struct futhark_f32_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  if (in1->shape[0] != n) return bad_sizes(ctx);
+  int rc = scalar_redomap(ctx, "dotprod_f32.segred_nonseg", PROV("reduce (+) 0 (map2 (*) xs ys)"), n, 4, [&] {
+    return fb::launch_dotprod_f32(dptr<float>(in0->mem), dptr<float>(in1->mem), n, reinterpret_cast<float *>(ctx->d_scalar), ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+  });
+  if (rc) return rc;
+  *out0 = reinterpret_cast<float *>(ctx->h_scalar)[0];
+  return FUTHARK_SUCCESS;
+}
+
+// reduce (*) 1 (map2 (+) xs ys) (tests/modules/functor1.fut:30-33 at i32).
+int futhark_entry_prod_of_sums_i32(struct futhark_context *ctx, int32_t *out0, const struct futhark_i32_1d *in0, const struct futhark_i32_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  if (in1->shape[0] != n) return bad_sizes(ctx);
+  int rc = scalar_redomap(ctx, "prod_of_sums_i32.segred_nonseg", PROV("reduce (*) 1 (map2 (+) xs ys)"), n, 4, [&] {
+    return fb::launch_prod_of_sums_i32(dptr<int32_t>(in0->mem), dptr<int32_t>(in1->mem), n, reinterpret_cast<int32_t *>(ctx->d_scalar), ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+  });
+  if (rc) return rc;
+  *out0 = reinterpret_cast<int32_t *>(ctx->h_scalar)[0];
+  return FUTHARK_SUCCESS;
+}
+
 int futhark_entry_segscan_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
                               const struct futhark_f32_1d *in1) {
   if (!ctx->ready) return not_ready(ctx);

@@ -47,6 +47,9 @@ cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const flo
 // sum first).  sum_i32_f32: d_out2 receives {i32 sum, f32 sum of the converted elements}.
 cudaError_t launch_mss_i32(const int32_t *in, int64_t n, int32_t *d_out4, void *scratch, int num_sms, cudaStream_t stream);
 cudaError_t launch_sum_i32_f32(const int32_t *in, int64_t n, void *d_out2, void *scratch, int num_sms, cudaStream_t stream);
+// map2 bodies: the f32 dot product, and the product of the element-wise sums of two i32 arrays
+cudaError_t launch_dotprod_f32(const float *xs, const float *ys, int64_t n, float *d_out, void *scratch, int num_sms, cudaStream_t stream);
+cudaError_t launch_prod_of_sums_i32(const int32_t *xs, const int32_t *ys, int64_t n, int32_t *d_out, void *scratch, int num_sms, cudaStream_t stream);
 
 // ---- histograms (k_hist.cu) -------------------------------------------------------------
 // op 0: (+) on i32 weights; op 1: max on f32 weights (result in f32 bits).  `out` holds

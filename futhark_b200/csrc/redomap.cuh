@@ -9,13 +9,14 @@
 //   using Acc                      the accumulator: all operators' values side by side, a
 //                                  trivially copyable struct of 1..4 32-bit words
 //   static constexpr bool commutative
+//   static constexpr int NIN       1 or 2 input arrays of 4-byte elements (map or map2)
 //   static Acc neutral()           the neutral element(s)
-//   static Acc map(uint32_t bits)  the map body on one 4-byte input element
+//   static Acc map(uint32_t bits [, uint32_t bits2])   the map body on one element of each input
 //   static Acc combine(Acc l, Acc r)   l (+) r, associative
 //
-// Operand order.  Every warp owns a contiguous run of *steps* (a step = 32 * RM_K vectors of
-// 16 bytes, read coalesced).  A commutative specification folds each lane's vectors as they
-// come.  Otherwise a step goes through a warp-private shared-memory area that turns the
+// Operand order.  Every warp owns a contiguous run of *steps* (a step = 32 * K vectors of
+// 16 bytes per input, read coalesced; K = RM_K, or 2 with two inputs to bound the registers).
+// A commutative specification folds each lane's vectors as they come.  Otherwise a step goes through a warp-private shared-memory area that turns the
 // coalesced layout into a blocked one (lane l then holds vectors l*RM_K .. l*RM_K+RM_K-1; RM_K
 // is odd, which makes these 16-byte reads conflict-free), the lane folds its 4*RM_K consecutive
 // elements left to right and a shuffle tree that keeps lane order folds the 32 lanes.  Warp,
@@ -69,38 +70,58 @@ template <class Spec>
 __device__ __forceinline__ typename Spec::Acc fold_vec(typename Spec::Acc a, const uint32_t &v) {
   return Spec::combine(a, Spec::map(v));
 }
+template <class Spec>
+__device__ __forceinline__ typename Spec::Acc fold_vec(typename Spec::Acc a, const int4 &v, const int4 &w) {
+  a = Spec::combine(a, Spec::map((uint32_t)v.x, (uint32_t)w.x));
+  a = Spec::combine(a, Spec::map((uint32_t)v.y, (uint32_t)w.y));
+  a = Spec::combine(a, Spec::map((uint32_t)v.z, (uint32_t)w.z));
+  a = Spec::combine(a, Spec::map((uint32_t)v.w, (uint32_t)w.w));
+  return a;
+}
+template <class Spec>
+__device__ __forceinline__ typename Spec::Acc fold_vec(typename Spec::Acc a, const uint32_t &v, const uint32_t &w) {
+  return Spec::combine(a, Spec::map(v, w));
+}
 
-// VEC: the input is 16-byte aligned and read as int4; the n % 4 last elements are folded in by
+// VEC: the inputs are 16-byte aligned and read as int4; the n % 4 last elements are folded in by
 // the thread that writes the result.  Otherwise one element per load.
 template <class Spec, bool VEC>
 __global__ void __launch_bounds__(RM_THREADS)
-redomap_kernel(const uint32_t *__restrict__ in, int64_t n, typename Spec::Acc *__restrict__ d_out, uint32_t *ticket,
-               typename Spec::Acc *partials) {
+redomap_kernel(const uint32_t *__restrict__ in, const uint32_t *__restrict__ in2, int64_t n,
+               typename Spec::Acc *__restrict__ d_out, uint32_t *ticket, typename Spec::Acc *partials) {
   using Acc = typename Spec::Acc;
   using Vec = typename std::conditional<VEC, int4, uint32_t>::type;
   constexpr bool ORDERED = !Spec::commutative;
-  __shared__ Vec s_tr[ORDERED ? RM_WARPS * 32 * RM_K : 1];
+  constexpr int NIN = Spec::NIN;
+  static_assert(NIN == 1 || (NIN == 2 && !ORDERED), "two inputs are supported for commutative operators");
+  constexpr int K = NIN == 2 ? 2 : RM_K;
+  __shared__ Vec s_tr[ORDERED ? RM_WARPS * 32 * K : 1];
   __shared__ Acc s_warp[RM_WARPS];
   __shared__ uint32_t s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const Vec *vec = reinterpret_cast<const Vec *>(in);
+  const Vec *vec2 = reinterpret_cast<const Vec *>(in2);
   const int64_t nvec = VEC ? (n >> 2) : n;
-  constexpr int64_t STEP = 32 * RM_K;
+  constexpr int64_t STEP = 32 * K;
   const int64_t steps = (nvec + STEP - 1) / STEP;
   const int64_t nwarps = (int64_t)gridDim.x * RM_WARPS;
   const int64_t per = (steps + nwarps - 1) / nwarps;
   const int64_t s0 = ((int64_t)blockIdx.x * RM_WARPS + warp) * per;
   const int64_t s1 = s0 + per < steps ? s0 + per : steps;
 
+  auto ld = [&](const Vec *p) {
+    if constexpr (VEC) return ld_stream_v4(p);
+    else return *p;
+  };
   Acc acc = Spec::neutral();              // ORDERED: meaningful in lane 0 only
-  Vec cur[RM_K], nxt[RM_K];
-  auto load = [&](Vec (&v)[RM_K], int64_t s) {
+  Vec cur[NIN][K], nxt[NIN][K];
+  auto load = [&](Vec (&v)[NIN][K], int64_t s) {
     const int64_t base = s * STEP + lane;
     if (base - lane + STEP <= nvec) {
 #pragma unroll
-      for (int j = 0; j < RM_K; j++) {
-        if constexpr (VEC) v[j] = ld_stream_v4(vec + base + j * 32);
-        else v[j] = vec[base + j * 32];
+      for (int j = 0; j < K; j++) {
+        v[0][j] = ld(vec + base + j * 32);
+        if constexpr (NIN == 2) v[1][j] = ld(vec2 + base + j * 32);
       }
     }
   };
@@ -109,33 +130,42 @@ redomap_kernel(const uint32_t *__restrict__ in, int64_t n, typename Spec::Acc *_
     if (s + 1 < s1) load(nxt, s + 1);
     const int64_t base = s * STEP;
     if (base + STEP <= nvec) {
-      if (ORDERED) {
-        Vec *mine = s_tr + warp * (32 * RM_K);
+      if constexpr (ORDERED) {
+        Vec *mine = s_tr + warp * (32 * K);
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < RM_K; j++) mine[j * 32 + lane] = cur[j];
+        for (int j = 0; j < K; j++) mine[j * 32 + lane] = cur[0][j];
         __syncwarp();
         Acc a = Spec::neutral();
 #pragma unroll
-        for (int j = 0; j < RM_K; j++) a = fold_vec<Spec>(a, mine[lane * RM_K + j]);
+        for (int j = 0; j < K; j++) a = fold_vec<Spec>(a, mine[lane * K + j]);
         a = warp_fold_ordered<Spec>(a, lane);
         acc = Spec::combine(acc, a);
       } else {
 #pragma unroll
-        for (int j = 0; j < RM_K; j++) acc = fold_vec<Spec>(acc, cur[j]);
+        for (int j = 0; j < K; j++) {
+          if constexpr (NIN == 2) acc = fold_vec<Spec>(acc, cur[0][j], cur[1][j]);
+          else acc = fold_vec<Spec>(acc, cur[0][j]);
+        }
       }
     } else {
       // the one ragged step at the end of the input: row by row, absent vectors count as neutral
-      for (int j = 0; j < RM_K; j++) {
+      for (int j = 0; j < K; j++) {
         const int64_t idx = base + j * 32 + lane;
         Acc a = Spec::neutral();
-        if (idx < nvec) a = fold_vec<Spec>(a, vec[idx]);
+        if (idx < nvec) {
+          if constexpr (NIN == 2) a = fold_vec<Spec>(a, vec[idx], vec2[idx]);
+          else a = fold_vec<Spec>(a, vec[idx]);
+        }
         if (ORDERED) { a = warp_fold_ordered<Spec>(a, lane); acc = Spec::combine(acc, a); }
         else acc = Spec::combine(acc, a);
       }
     }
 #pragma unroll
-    for (int j = 0; j < RM_K; j++) cur[j] = nxt[j];
+    for (int j = 0; j < K; j++) {
+      cur[0][j] = nxt[0][j];
+      if constexpr (NIN == 2) cur[1][j] = nxt[1][j];
+    }
   }
   if (!ORDERED) acc = warp_fold_ordered<Spec>(acc, lane);
   if (lane == 0) s_warp[warp] = acc;
@@ -175,7 +205,10 @@ redomap_kernel(const uint32_t *__restrict__ in, int64_t n, typename Spec::Acc *_
     b = warp_fold_ordered<Spec>(b, lane);
     if (lane == 0) {
       if (VEC)
-        for (int64_t i = nvec << 2; i < n; i++) b = Spec::combine(b, Spec::map(in[i]));
+        for (int64_t i = nvec << 2; i < n; i++) {
+          if constexpr (NIN == 2) b = Spec::combine(b, Spec::map(in[i], in2[i]));
+          else b = Spec::combine(b, Spec::map(in[i]));
+        }
       *d_out = b;
       *ticket = 0u;
     }
@@ -185,11 +218,12 @@ redomap_kernel(const uint32_t *__restrict__ in, int64_t n, typename Spec::Acc *_
 // `scratch`: a ticket word (zero before the first launch; every launch leaves it zero) and,
 // 256 bytes further, room for RM_MAX_BLOCKS accumulators of 16 bytes.
 template <class Spec>
-cudaError_t launch_redomap(const void *in, int64_t n, void *d_out, void *scratch, int num_sms, cudaStream_t stream) {
+cudaError_t launch_redomap(const void *in, const void *in2, int64_t n, void *d_out, void *scratch, int num_sms, cudaStream_t stream) {
   using Acc = typename Spec::Acc;
+  constexpr int K = Spec::NIN == 2 ? 2 : RM_K;
   uint32_t *ticket = reinterpret_cast<uint32_t *>(scratch);
   Acc *partials = reinterpret_cast<Acc *>(reinterpret_cast<char *>(scratch) + 256);
-  const bool vec = (reinterpret_cast<uintptr_t>(in) & 15) == 0;
+  const bool vec = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(in2)) & 15) == 0;
   static int occ_v = 0, occ_s = 0;
   int &occ = vec ? occ_v : occ_s;
   if (occ == 0) {
@@ -199,15 +233,15 @@ cudaError_t launch_redomap(const void *in, int64_t n, void *d_out, void *scratch
     if (occ < 1) occ = 1;
   }
   const int64_t nvec = vec ? (n >> 2) : n;
-  const int64_t steps = (nvec + 32 * RM_K - 1) / (32 * RM_K);
+  const int64_t steps = (nvec + 32 * K - 1) / (32 * K);
   int64_t want = (steps + RM_WARPS - 1) / RM_WARPS;
   int blocks = num_sms * occ;
   if (blocks > RM_MAX_BLOCKS) blocks = RM_MAX_BLOCKS;
   if (want < blocks) blocks = want < 1 ? 1 : (int)want;
-  const uint32_t *p = reinterpret_cast<const uint32_t *>(in);
+  const uint32_t *p = reinterpret_cast<const uint32_t *>(in), *p2 = reinterpret_cast<const uint32_t *>(in2);
   Acc *out = reinterpret_cast<Acc *>(d_out);
-  if (vec) redomap_kernel<Spec, true><<<blocks, RM_THREADS, 0, stream>>>(p, n, out, ticket, partials);
-  else redomap_kernel<Spec, false><<<blocks, RM_THREADS, 0, stream>>>(p, n, out, ticket, partials);
+  if (vec) redomap_kernel<Spec, true><<<blocks, RM_THREADS, 0, stream>>>(p, p2, n, out, ticket, partials);
+  else redomap_kernel<Spec, false><<<blocks, RM_THREADS, 0, stream>>>(p, p2, n, out, ticket, partials);
   return cudaGetLastError();
 }
 

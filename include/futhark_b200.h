@@ -251,13 +251,21 @@ int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f
  *   segment sum of tests/mss.fut:6-20: a 4-tuple-valued, non-commutative operator.
  * entry sum_i32_f32 (xs: []i32): (i32, f32) = (i32.sum xs, f32.sum (map f32.i32 xs)), the
  *   horizontally fused pair of tests/fusion/red-red-fusion.fut:5.
- * The two with scalar results read them back, so they synchronise. */
+ * entry dotprod_f32 (xs: []f32) (ys: []f32): f32 = reduce (+) 0 (map2 (*) xs ys): a map body over two
+ *   inputs fused into the reduction (the shape of every dot product in the programs under tests/tiling).
+ * entry prod_of_sums_i32 (xs: []i32) (ys: []i32): i32 = reduce (*) 1 (map2 (+) xs ys), the DotProd
+ *   functor of tests/modules/functor1.fut:30-33 applied to i32 (known answer :3-4).
+ * Those with scalar results read them back, so they synchronise. */
 int futhark_entry_exscan_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
                              const struct futhark_i32_1d *in0);
 int futhark_entry_mss_i32(struct futhark_context *ctx, int32_t *out0,
                           const struct futhark_i32_1d *in0);
 int futhark_entry_sum_i32_f32(struct futhark_context *ctx, int32_t *out0, float *out1,
                               const struct futhark_i32_1d *in0);
+int futhark_entry_dotprod_f32(struct futhark_context *ctx, float *out0,
+                              const struct futhark_f32_1d *in0, const struct futhark_f32_1d *in1);
+int futhark_entry_prod_of_sums_i32(struct futhark_context *ctx, int32_t *out0,
+                                   const struct futhark_i32_1d *in0, const struct futhark_i32_1d *in1);
 
 /* ---- extensions (prefix futhark_b200_): not part of the reference's generated API ----
  * The reference keeps its one CUDA stream private (rts/c/backends/cuda.h:219); a host

@@ -31,6 +31,10 @@ def lib():
         L.orc_scan_i32.argtypes = [vp, i64, vp, i32]
         L.orc_segscan_f32.argtypes = [vp, vp, i64, vp, i32]
         L.orc_exscan_i32.argtypes = [vp, i64, vp, i32]
+        L.orc_dotprod_f32.restype = ctypes.c_float
+        L.orc_dotprod_f32.argtypes = [vp, vp, i64, i32]
+        L.orc_prod_of_sums_i32.restype = ctypes.c_int32
+        L.orc_prod_of_sums_i32.argtypes = [vp, vp, i64, i32]
         L.orc_mss_i32.restype = ctypes.c_int32
         L.orc_mss_i32.argtypes = [vp, i64, i32]
         L.orc_sum_i32_f32.argtypes = [vp, i64, vp, vp, i32]
@@ -139,6 +143,18 @@ def exscan_i32(xs, threads=0):
     out = np.empty_like(xs)
     lib().orc_exscan_i32(_p(xs), xs.size, _p(out), threads)
     return out
+
+
+def dotprod_f32(xs, ys, threads=0):
+    xs, ys = _c(xs, np.float32), _c(ys, np.float32)
+    assert xs.size == ys.size
+    return float(lib().orc_dotprod_f32(_p(xs), _p(ys), xs.size, threads))
+
+
+def prod_of_sums_i32(xs, ys, threads=0):
+    xs, ys = _c(xs, np.int32), _c(ys, np.int32)
+    assert xs.size == ys.size
+    return int(lib().orc_prod_of_sums_i32(_p(xs), _p(ys), xs.size, threads))
 
 
 def mss_i32(xs, threads=0):

@@ -9,7 +9,8 @@
  * tests carry for these paths (tests/soacs/scan0.fut, reduce0.fut, filter1.fut,
  * partition1.fut, tests/hist/simple.fut, max.fut, large.fut,
  * tests/segredomap/segsum-comm.fut, tests/soacs/segreduce-iota.fut,
- * tests/reg-tiling/mmm.fut, tests/mss.fut, tests/soacs/exscan0.fut, exscan1.fut).  The flagged f32 segmented scan and the f16-input
+ * tests/reg-tiling/mmm.fut, tests/mss.fut, tests/soacs/exscan0.fut, exscan1.fut,
+ * tests/modules/functor1.fut).  The flagged f32 segmented scan and the f16-input
  * contraction have no pinned vectors in the reference ("auto output" only), so
  * for those two this oracle is "parity unpinned": it follows the reference's
  * operator definitions but cannot be checked against reference-produced values.
@@ -179,6 +180,47 @@ void orc_sum_i32_f32(const int32_t *xs, int64_t n, int32_t *out_i, float *out_f,
   free(pi); free(pf);
   *out_i = (int32_t)ri;
   *out_f = rf;
+}
+
+/* ---- redomaps over two inputs ---------------------------------------------------
+ * reduce (+) 0 (map2 (*) xs ys) over f32, and reduce (*) 1 (map2 (+) xs ys) over i32 (the
+ * DotProd functor of tests/modules/functor1.fut:30-33); chunking as for the other
+ * reductions (Multicore/SegRed.hs:297-320, 345-376).  The product and the sum are separate
+ * roundings: the build forbids contraction into a fused multiply-add. */
+float orc_dotprod_f32(const float *xs, const float *ys, int64_t n, int nthreads) {
+  int k = pick_threads(nthreads);
+  if (n < k) k = n > 0 ? (int)n : 1;
+  float *part = (float *)calloc((size_t)k, sizeof(float));
+#pragma omp parallel for num_threads(k) schedule(static, 1)
+  for (int t = 0; t < k; t++) {
+    int64_t lo, hi;
+    chunk_of(n, k, t, &lo, &hi);
+    float acc = 0.0f;
+    for (int64_t i = lo; i < hi; i++) acc += xs[i] * ys[i];
+    part[t] = acc;
+  }
+  float r = 0.0f;
+  for (int t = 0; t < k; t++) r += part[t];
+  free(part);
+  return r;
+}
+
+int32_t orc_prod_of_sums_i32(const int32_t *xs, const int32_t *ys, int64_t n, int nthreads) {
+  int k = pick_threads(nthreads);
+  if (n < k) k = n > 0 ? (int)n : 1;
+  uint32_t *part = (uint32_t *)calloc((size_t)k, sizeof(uint32_t));
+#pragma omp parallel for num_threads(k) schedule(static, 1)
+  for (int t = 0; t < k; t++) {
+    int64_t lo, hi;
+    chunk_of(n, k, t, &lo, &hi);
+    uint32_t acc = 1;
+    for (int64_t i = lo; i < hi; i++) acc *= (uint32_t)xs[i] + (uint32_t)ys[i];
+    part[t] = acc;
+  }
+  uint32_t r = 1;
+  for (int t = 0; t < k; t++) r *= part[t];
+  free(part);
+  return (int32_t)r;
 }
 
 /* ---- flagged segmented inclusive scan (+) over f32 --------------------------

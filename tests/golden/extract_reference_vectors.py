@@ -30,6 +30,7 @@ FILES = [
     "tests/mss.fut",
     "tests/soacs/exscan0.fut",
     "tests/soacs/exscan1.fut",
+    "tests/modules/functor1.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f32\.nan|f32\.inf|-f32\.inf|true|false|"

@@ -30,7 +30,7 @@ def test_lists_entry_points_and_params_without_a_device(cli):
     assert lines["segscan_f32"] == "[]bool []f32 -> []f32"
     assert lines["partition_u32"] == "[]u32 -> ([]u32, []u32)"
     assert lines["hist_add_i32"] == "i64 []i32 []i32 -> []i32"
-    assert len(lines) == 15
+    assert len(lines) == 17
     r = run(cli, ["--print-params"])
     assert r.returncode == 0 and b"(thread_block_size)" in r.stdout
     assert run(cli, ["-h"]).stdout.startswith(b"Usage: ")
@@ -64,6 +64,8 @@ def test_text_in_text_out(cli):
     assert run(cli, ["-e", "mss_i32"], b"[1, -2, 3, 4, -1, 5, -6, 1]").stdout == b"11i32\n"       # tests/mss.fut
     assert run(cli, ["-e", "exscan_i32"], b"[1,2,3,4,5,6,7,8,9]").stdout == b"[0i32, 1i32, 3i32, 6i32, 10i32, 15i32, 21i32, 28i32, 36i32]\n"
     assert run(cli, ["-e", "sum_i32_f32"], b"[1,2,3]").stdout == b"6i32\n6f32\n"
+    assert run(cli, ["-e", "prod_of_sums_i32"], b"[1,2,3] [4,5,6]").stdout == b"315i32\n"           # tests/modules/functor1.fut
+    assert run(cli, ["-e", "dotprod_f32"], b"[1f32,2f32,3f32] [4f32,5f32,6f32]").stdout == b"32f32\n"
     assert run(cli, ["-e", "partition_u32"], b"[8u32, 3u32, 1u32, 7u32]").stdout == b"[8u32, 1u32]\n[3u32, 7u32]\n"
     assert run(cli, ["-e", "filter_u32"], b"[3u32, 7u32]").stdout == b"empty([0]u32)\n"
     assert run(cli, ["-e", "hist_add_i32"], b"4i64 [0, 1, 1, 9, -1] [1, 2, 3, 4, 5]").stdout == b"[1i32, 5i32, 0i32, 0i32]\n"
@@ -148,7 +150,7 @@ def test_server_without_a_device_fails_loudly(cli):
 @gpu
 def test_server_session_restore_call_store_free(cli, tmp_path):
     s = ServerProc(build.SERVER_BIN)
-    assert "scan_i32" in s.ok("entry_points") and len(s.ok("entry_points")) == 15
+    assert "scan_i32" in s.ok("entry_points") and len(s.ok("entry_points")) == 17
     assert s.ok("inputs segscan_f32") == ["[]bool", "[]f32"] and s.ok("output segscan_f32") == ["*[]f32"]
     assert s.ok("output partition_u32") == ["*([]u32, []u32)"]
     assert s.ok('kind "([]u32, []u32)"') == ["record"] and s.ok("kind []i32") == ["array"] and s.ok("kind i64") == ["primitive"]

@@ -100,6 +100,46 @@ def test_sum_i32_f32(ctx, n):
     assert abs(sf - of) <= 2e-5 * max(l1, 1e-6)
 
 
+def test_prod_of_sums_reference_known_answer(ctx):
+    # tests/modules/functor1.fut:3-4 of the reference
+    assert fb.prod_of_sums_i32(ctx, np.array([1, 2, 3], np.int32), np.array([4, 5, 6], np.int32)) == 315
+    assert fb.prod_of_sums_i32(ctx, np.zeros(0, np.int32), np.zeros(0, np.int32)) == 1
+
+
+@pytest.mark.parametrize("n", SIZES + MORE)
+def test_prod_of_sums_i32_bit_exact(ctx, n):
+    xs = datagen.uniform_i32(15, 0, n, -2**31, 2**31 - 1) | 1            # odd + even = odd: the product never collapses to 0
+    ys = datagen.uniform_i32(16, 0, n, -2**31, 2**31 - 1) & ~1
+    assert fb.prod_of_sums_i32(ctx, xs, ys) == oracle.prod_of_sums_i32(xs, ys)
+
+
+@pytest.mark.parametrize("n", SIZES + MORE)
+def test_dotprod_f32(ctx, n):
+    xs, ys = datagen.normal_f32(17, 0, n), datagen.normal_f32(18, 0, n)
+    got = fb.dotprod_f32(ctx, xs, ys)
+    p = xs.astype(np.float64) * ys.astype(np.float64)
+    l1 = max(float(np.abs(p).sum()), 1e-6)
+    assert abs(got - float(p.sum())) <= 1e-5 * l1                       # 1e-5 of the L1 norm of the products
+    assert abs(got - oracle.dotprod_f32(xs, ys)) <= 2e-5 * l1
+
+
+def test_two_input_redomaps_check_sizes_and_take_unaligned_pointers(ctx):
+    a, b = ctx.new("f32_1d", np.zeros(5, np.float32)), ctx.new("f32_1d", np.zeros(6, np.float32))
+    with pytest.raises(fb.FutharkError) as e:
+        ctx.entry_dotprod_f32(a, b)
+    assert "invalid sizes" in e.value.message
+    a.free(); b.free()
+    n = 77 * STEP + 5
+    xs, ys = datagen.normal_f32(19, 0, n + 1), datagen.normal_f32(20, 0, n + 1)
+    wx, wy = ctx.new("f32_1d", xs), ctx.new("f32_1d", ys)
+    vx, vy = ctx.new_raw("f32_1d", wx.raw + 4, n), ctx.new_raw("f32_1d", wy.raw, n)      # one side only 4-byte aligned
+    got = ctx.entry_dotprod_f32(vx, vy)
+    for x in (vx, vy, wx, wy):
+        x.free()
+    p = xs[1:].astype(np.float64) * ys[:n].astype(np.float64)
+    assert abs(got - float(p.sum())) <= 1e-5 * float(np.abs(p).sum())
+
+
 def test_fused_full_size_2p26(ctx):
     dev = torch.device("cuda", 0)
     n = 1 << 26
@@ -123,3 +163,11 @@ def test_fused_full_size_2p26(ctx):
     want = int((p - torch.cummin(p, 0).values).max().item())
     assert ctx.entry_mss_i32(a) == want
     out.free(); a.free()
+    del x, p, o
+    u, v = torch.randn(n, device=dev, generator=g), torch.randn(n, device=dev, generator=g)
+    torch.cuda.synchronize()
+    ua, va = ctx.new_raw("f32_1d", u.data_ptr(), n), ctx.new_raw("f32_1d", v.data_ptr(), n)
+    d = ctx.entry_dotprod_f32(ua, va)
+    prod = u.double() * v.double()
+    assert abs(d - float(prod.sum().item())) <= 1e-5 * float(prod.abs().sum().item())
+    ua.free(); va.free()

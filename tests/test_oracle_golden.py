@@ -66,6 +66,31 @@ def test_mss_known_answer_and_chunking(c):
     assert oracle.mss_i32(np.full(10, -5, np.int32)) == 0
 
 
+@pytest.mark.parametrize("c", cases("tests/modules/functor1.fut"))
+def test_functor1_product_of_sums(c):
+    xs, ys = np.array(c["input"][0], np.int32), np.array(c["input"][1], np.int32)
+    for threads in (1, 2, 0):
+        assert oracle.prod_of_sums_i32(xs, ys, threads) == c["output"][0]
+    rng = np.random.default_rng(9)
+    a, b = rng.integers(-2**31, 2**31 - 1, 10001).astype(np.int32), rng.integers(-2**31, 2**31 - 1, 10001).astype(np.int32)
+    want = 1
+    for u, v in zip(a.tolist(), b.tolist()):
+        want = (want * ((u + v) & 0xFFFFFFFF)) & 0xFFFFFFFF
+    want = want - 2**32 if want >= 2**31 else want
+    assert oracle.prod_of_sums_i32(a, b, 3) == want
+    assert oracle.prod_of_sums_i32(np.zeros(0, np.int32), np.zeros(0, np.int32)) == 1
+
+
+def test_dotprod_f32_against_f64():
+    rng = np.random.default_rng(10)
+    xs, ys = rng.standard_normal(300001).astype(np.float32), rng.standard_normal(300001).astype(np.float32)
+    ref = float(np.dot(xs.astype(np.float64), ys.astype(np.float64)))
+    l1 = float(np.abs(xs.astype(np.float64) * ys.astype(np.float64)).sum())
+    for threads in (1, 4, 0):
+        assert abs(oracle.dotprod_f32(xs, ys, threads) - ref) <= 1e-5 * l1
+    assert oracle.dotprod_f32(np.zeros(0, np.float32), np.zeros(0, np.float32)) == 0.0
+
+
 def test_sum_i32_f32_fused_pair():
     rng = np.random.default_rng(8)
     xs = rng.integers(-1000, 1001, 250001).astype(np.int32)
