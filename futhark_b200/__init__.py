@@ -179,7 +179,14 @@ def load():
     L.futhark_b200_lmad_copy.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.c_uint64, i64, vp, ctypes.c_uint64, i64, vp, vp]
     L.futhark_b200_lmad_classify.argtypes = [ctypes.c_int, vp, vp, vp, vp]
     L.futhark_entry_mss_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
-    L.futhark_entry_sum_i32_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float), vp]
+    L.futhark_entry_sum_i32_f32.argtypes = [vp, pvp, vp]
+    L.futhark_project_opaque_tup2_i32_f32_0.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+    L.futhark_project_opaque_tup2_i32_f32_1.argtypes = [vp, ctypes.POINTER(ctypes.c_float), vp]
+    L.futhark_free_opaque_tup2_i32_f32.argtypes = [vp, vp]
+    L.futhark_new_opaque_tup2_i32_f32.argtypes = [vp, pvp, ctypes.c_int32, ctypes.c_float]
+    L.futhark_store_opaque_tup2_i32_f32.argtypes = [vp, vp, pvp, ctypes.POINTER(ctypes.c_size_t)]
+    L.futhark_restore_opaque_tup2_i32_f32.restype = vp
+    L.futhark_restore_opaque_tup2_i32_f32.argtypes = [vp, vp]
     _lib = L
     return L
 
@@ -446,8 +453,13 @@ class Context:
         return int(out.value)
 
     def entry_sum_i32_f32(self, xs):
+        """The opaque (i32, f32) result, projected and freed: returns the two scalars."""
+        obj = ctypes.c_void_p()
+        self._check(self.lib.futhark_entry_sum_i32_f32(self.ptr, ctypes.byref(obj), xs.ptr))
         oi, of = ctypes.c_int32(), ctypes.c_float()
-        self._check(self.lib.futhark_entry_sum_i32_f32(self.ptr, ctypes.byref(oi), ctypes.byref(of), xs.ptr))
+        self._check(self.lib.futhark_project_opaque_tup2_i32_f32_0(self.ptr, ctypes.byref(oi), obj))
+        self._check(self.lib.futhark_project_opaque_tup2_i32_f32_1(self.ptr, ctypes.byref(of), obj))
+        self._check(self.lib.futhark_free_opaque_tup2_i32_f32(self.ptr, obj))
         return int(oi.value), float(of.value)
 
 

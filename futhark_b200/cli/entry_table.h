@@ -61,30 +61,31 @@ inline const ArrayType *array_type(const std::string &name) {
   return nullptr;
 }
 
-// The record types entry points return (tuples: fields named 0, 1, ... as in the C API).
-struct RecordType { const char *name; std::vector<const char *> fields; };
-static const RecordType RECORDS[] = {{"([]u32, []u32)", {"[]u32", "[]u32"}}, {"(i32, f32)", {"i32", "f32"}}};
-inline const RecordType *record_type(const std::string &name) {
-  for (const RecordType &r : RECORDS)
-    if (name == r.name) return &r;
-  return nullptr;
-}
+struct RecordType;
 
-// A value: a scalar held on the host, an array held on the device, or a record of values.
+// A value: a scalar held on the host, an array held on the device, or a record (an opaque object
+// of the C API whose fields are reached by projection).
 struct Value {
   std::string type;
   const ArrayType *array = nullptr;
-  void *arr = nullptr;
+  const RecordType *record = nullptr;
+  void *arr = nullptr;                       // the array or opaque object
   unsigned char scalar[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  std::vector<Value> fields;
+};
+
+// The record types entry points return (tuples: fields named 0, 1, ... as in the C API).
+struct RecordType {
+  const char *name;
+  std::vector<const char *> fields;
+  int (*release)(futhark_context *, void *);
+  int (*project)(futhark_context *, const void *obj, int field, Value &out);   // a new reference / the scalar
+  int (*make)(futhark_context *, const std::vector<const Value *> &fields, void **obj);
 };
 
 inline int release(futhark_context *ctx, Value &v) {
   int rc = 0;
-  if (v.arr != nullptr) rc |= v.array->release(ctx, v.arr);
+  if (v.arr != nullptr) rc = v.record != nullptr ? v.record->release(ctx, v.arr) : v.array->release(ctx, v.arr);
   v.arr = nullptr;
-  for (Value &f : v.fields) rc |= release(ctx, f);
-  v.fields.clear();
   return rc;
 }
 
@@ -103,6 +104,44 @@ inline T scalar_of(const Value &v) {
   T x;
   memcpy(&x, v.scalar, sizeof(T));
   return x;
+}
+
+static const RecordType RECORDS[] = {
+    {"([]u32, []u32)", {"[]u32", "[]u32"},
+     [](futhark_context *c, void *o) { return futhark_free_opaque_tup2_arr1d_u32_arr1d_u32(c, (futhark_opaque_tup2_arr1d_u32_arr1d_u32 *)o); },
+     [](futhark_context *c, const void *o, int k, Value &out) {
+       futhark_u32_1d *a = nullptr;
+       const auto *obj = (const futhark_opaque_tup2_arr1d_u32_arr1d_u32 *)o;
+       const int rc = k == 0 ? futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_0(c, &a, obj) : futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(c, &a, obj);
+       if (!rc) set_array(out, "[]u32", a);
+       return rc;
+     },
+     [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
+       return futhark_new_opaque_tup2_arr1d_u32_arr1d_u32(c, (futhark_opaque_tup2_arr1d_u32_arr1d_u32 **)obj, (const futhark_u32_1d *)f[0]->arr, (const futhark_u32_1d *)f[1]->arr);
+     }},
+    {"(i32, f32)", {"i32", "f32"},
+     [](futhark_context *c, void *o) { return futhark_free_opaque_tup2_i32_f32(c, (futhark_opaque_tup2_i32_f32 *)o); },
+     [](futhark_context *c, const void *o, int k, Value &out) {
+       const auto *obj = (const futhark_opaque_tup2_i32_f32 *)o;
+       int32_t a = 0;
+       float b = 0;
+       const int rc = k == 0 ? futhark_project_opaque_tup2_i32_f32_0(c, &a, obj) : futhark_project_opaque_tup2_i32_f32_1(c, &b, obj);
+       if (!rc) { if (k == 0) set_scalar(out, "i32", a); else set_scalar(out, "f32", b); }
+       return rc;
+     },
+     [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
+       return futhark_new_opaque_tup2_i32_f32(c, (futhark_opaque_tup2_i32_f32 **)obj, scalar_of<int32_t>(*f[0]), scalar_of<float>(*f[1]));
+     }},
+};
+inline const RecordType *record_type(const std::string &name) {
+  for (const RecordType &r : RECORDS)
+    if (name == r.name) return &r;
+  return nullptr;
+}
+inline void set_record(Value &v, const char *type, void *obj) {
+  v.type = type;
+  v.record = record_type(type);
+  v.arr = obj;
 }
 
 // Host value (as read from a file) -> value; arrays are uploaded.  Returns 0, or 1 with the
@@ -168,11 +207,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"exscan_i32", {"[]i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_exscan_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_array(o, "[]i32", r); return rc; }},
       {"reduce_i32", {"[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_reduce_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
       {"mss_i32", {"[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_mss_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
-      {"sum_i32_f32", {"[]i32"}, "(i32, f32)", [](C *c, In in, Value &o) {
-         int32_t a = 0; float b = 0;
-         int rc = futhark_entry_sum_i32_f32(c, &a, &b, FE_IN(0, i32_1d));
-         if (!rc) { o.type = "(i32, f32)"; o.fields.resize(2); set_scalar(o.fields[0], "i32", a); set_scalar(o.fields[1], "f32", b); }
-         return rc; }},
+      {"sum_i32_f32", {"[]i32"}, "(i32, f32)", [](C *c, In in, Value &o) { futhark_opaque_tup2_i32_f32 *r = nullptr; int rc = futhark_entry_sum_i32_f32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "(i32, f32)", r); return rc; }},
       {"dotprod_f32", {"[]f32", "[]f32"}, "f32", [](C *c, In in, Value &o) { float r = 0; int rc = futhark_entry_dotprod_f32(c, &r, FE_IN(0, f32_1d), FE_IN(1, f32_1d)); if (!rc) set_scalar(o, "f32", r); return rc; }},
       {"prod_of_sums_i32", {"[]i32", "[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_prod_of_sums_i32(c, &r, FE_IN(0, i32_1d), FE_IN(1, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
       {"segscan_f32", {"[]bool", "[]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_segscan_f32(c, &r, FE_IN(0, bool_1d), FE_IN(1, f32_1d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
@@ -181,18 +216,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"hist_add_i32", {"i64", "[]i32", "[]i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_hist_add_i32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_1d), FE_IN(2, i32_1d)); if (!rc) set_array(o, "[]i32", r); return rc; }},
       {"hist_max_f32", {"i64", "[]i32", "[]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_hist_max_f32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_1d), FE_IN(2, f32_1d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
       {"filter_u32", {"[]u32"}, "[]u32", [](C *c, In in, Value &o) { futhark_u32_1d *r = nullptr; int rc = futhark_entry_filter_u32(c, &r, FE_IN(0, u32_1d)); if (!rc) set_array(o, "[]u32", r); return rc; }},
-      {"partition_u32", {"[]u32"}, "([]u32, []u32)", [](C *c, In in, Value &o) {
-         futhark_opaque_tup2_arr1d_u32_arr1d_u32 *r = nullptr;
-         int rc = futhark_entry_partition_u32(c, &r, FE_IN(0, u32_1d));
-         if (rc) return rc;
-         futhark_u32_1d *a = nullptr, *b = nullptr;
-         rc = futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_0(c, &a, r) | futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(c, &b, r);
-         rc |= futhark_free_opaque_tup2_arr1d_u32_arr1d_u32(c, r);
-         o.type = "([]u32, []u32)";
-         o.fields.resize(2);
-         set_array(o.fields[0], "[]u32", a);
-         set_array(o.fields[1], "[]u32", b);
-         return rc; }},
+      {"partition_u32", {"[]u32"}, "([]u32, []u32)", [](C *c, In in, Value &o) { futhark_opaque_tup2_arr1d_u32_arr1d_u32 *r = nullptr; int rc = futhark_entry_partition_u32(c, &r, FE_IN(0, u32_1d)); if (!rc) set_record(o, "([]u32, []u32)", r); return rc; }},
       {"bmm_f16", {"[][][]f16", "[][][]f16"}, "[][][]f32", [](C *c, In in, Value &o) { futhark_f32_3d *r = nullptr; int rc = futhark_entry_bmm_f16(c, &r, FE_IN(0, f16_3d), FE_IN(1, f16_3d)); if (!rc) set_array(o, "[][][]f32", r); return rc; }},
       {"transpose_f32", {"[][]f32"}, "[][]f32", [](C *c, In in, Value &o) { futhark_f32_2d *r = nullptr; int rc = futhark_entry_transpose_f32(c, &r, FE_IN(0, f32_2d)); if (!rc) set_array(o, "[][]f32", r); return rc; }},
       {"transpose_f32_3d", {"[][][]f32"}, "[][][]f32", [](C *c, In in, Value &o) { futhark_f32_3d *r = nullptr; int rc = futhark_entry_transpose_f32_3d(c, &r, FE_IN(0, f32_3d)); if (!rc) set_array(o, "[][][]f32", r); return rc; }},

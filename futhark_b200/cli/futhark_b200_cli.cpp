@@ -192,17 +192,23 @@ int main(int argc, char **argv) {
   for (futhark_b200_value &v : parsed) futhark_b200_value_free(&v);
 
   if (print_result) {
-    // a tuple's fields are printed one per line (CLI.hs:279-296)
-    std::vector<const fe::Value *> outs;
-    if (result.fields.empty()) outs.push_back(&result);
-    else for (const fe::Value &f : result.fields) outs.push_back(&f);
-    for (const fe::Value *v : outs) {
+    // a tuple's fields are projected and printed one per line (CLI.hs:279-296)
+    std::vector<fe::Value> outs;
+    if (result.record == nullptr) outs.push_back(result);
+    else
+      for (size_t k = 0; k < result.record->fields.size(); k++) {
+        fe::Value f;
+        check(ctx, result.record->project(ctx, result.arr, (int)k, f));
+        outs.push_back(f);
+      }
+    for (fe::Value &v : outs) {
       futhark_b200_value h;
-      check(ctx, fe::to_host(ctx, *v, h));
+      check(ctx, fe::to_host(ctx, v, h));
       check(ctx, futhark_context_sync(ctx));
       futhark_b200_value_write(stdout, &h, binary_output);
       puts("");
       futhark_b200_value_free(&h);
+      if (result.record != nullptr) check(ctx, fe::release(ctx, v));
     }
   }
   check(ctx, fe::release(ctx, result));

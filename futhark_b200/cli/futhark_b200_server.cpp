@@ -146,7 +146,7 @@ static void cmd_store(Server &s, const std::vector<std::string> &a) {
   for (size_t i = 2; i < a.size(); i++) {
     fe::Value *v = s.var(a[i]);
     if (v == nullptr) break;
-    if (!v->fields.empty()) { s.failure("Cannot store a value of type %s; project its fields.\n", v->type.c_str()); break; }
+    if (v->record != nullptr) { s.failure("Cannot store a value of type %s; project its fields.\n", v->type.c_str()); break; }
     futhark_b200_value h;
     int rc = fe::to_host(s.ctx, *v, h);
     rc |= futhark_context_sync(s.ctx);
@@ -231,36 +231,35 @@ static void dispatch(Server &s, const std::vector<std::string> &a) {
     if (r == nullptr) { s.failure("Not a record type\n"); return; }
     for (size_t i = 0; i < r->fields.size(); i++) printf("%d %s\n", (int)i, r->fields[i]);
   } else if (c == "project") {
-    // project TO FROM FIELD: the field shares the device array with the record (as in the C API,
-    // where a projection is a new reference to the same memory); here it is moved out, and the
-    // record keeps its other fields
+    // project TO FROM FIELD: a new reference to the field (the record stays as it is)
     if (!need(3)) return;
     fe::Value *from = s.var(a[2]);
     if (from == nullptr) return;
-    if (from->fields.empty()) { s.failure("Not a record type\n"); return; }
+    if (from->record == nullptr) { s.failure("Not a record type\n"); return; }
     const size_t k = (size_t)atoi(a[3].c_str());
-    if (k >= from->fields.size() || a[3] != std::to_string(k)) { s.failure("No such field\n"); return; }
+    if (k >= from->record->fields.size() || a[3] != std::to_string(k)) { s.failure("No such field\n"); return; }
     if (!s.fresh(a[1])) return;
-    fe::Value &fld = from->fields[k];
-    if (fld.array != nullptr && fld.arr == nullptr) { s.failure("Field %s was already projected out\n", a[3].c_str()); return; }
+    fe::Value fld;
+    if (s.bad(from->record->project(s.ctx, from->arr, (int)k, fld))) return;
     s.vars[a[1]] = fld;
-    fld.arr = nullptr;
   } else if (c == "new") {
-    // new V0 TYPE V1 ... VN: a record from variables of the field types (the fields are moved in)
+    // new V0 TYPE V1 ... VN: a record from variables of the field types (which stay valid)
     if (!need(2)) return;
     const fe::RecordType *r = fe::record_type(a[2]);
     if (r == nullptr) { s.failure("Not a record type\n"); return; }
     if (a.size() != 3 + r->fields.size()) { s.failure("%d fields expected but %d values provided.\n", (int)r->fields.size(), (int)a.size() - 3); return; }
     if (!s.fresh(a[1])) return;
-    fe::Value rec;
-    rec.type = r->name;
+    std::vector<const fe::Value *> fields;
     for (size_t i = 0; i < r->fields.size(); i++) {
       fe::Value *v = s.var(a[3 + i]);
       if (v == nullptr) return;
       if (v->type != r->fields[i]) { s.failure("Field %d mismatch: expected type %s, got %s\n", (int)i, r->fields[i], v->type.c_str()); return; }
-      rec.fields.push_back(*v);
+      fields.push_back(v);
     }
-    for (size_t i = 0; i < r->fields.size(); i++) s.vars.erase(a[3 + i]);
+    void *obj = nullptr;
+    if (s.bad(r->make(s.ctx, fields, &obj))) return;
+    fe::Value rec;
+    fe::set_record(rec, r->name, obj);
     s.vars[a[1]] = rec;
   } else if (c == "set_tuning_param") {
     if (!need(2)) return;

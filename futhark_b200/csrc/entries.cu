@@ -135,17 +135,22 @@ int futhark_entry_mss_i32(struct futhark_context *ctx, int32_t *out0, const stru
 }
 
 // Two reductions fused over one input (tests/fusion/red-red-fusion.fut): (i32.sum xs, f32.sum (map f32.i32 xs)).
-int futhark_entry_sum_i32_f32(struct futhark_context *ctx, int32_t *out0, float *out1, const struct futhark_i32_1d *in0) {
+int futhark_entry_sum_i32_f32(struct futhark_context *ctx, struct futhark_opaque_tup2_i32_f32 **out0, const struct futhark_i32_1d *in0) {
   if (!ctx->ready) return not_ready(ctx);
-  CtxGuard g(ctx);
   const int64_t n = in0->shape[0];
-  int rc = scalar_redomap(ctx, "sum_i32_f32.segred_nonseg", PROV("(i32.sum xs, f32.sum (map f32.i32 xs))"), n, 8, [&] {
-    return fb::launch_sum_i32_f32(dptr<int32_t>(in0->mem), n, ctx->d_scalar, ctx->reduce_scratch, ctx->num_sms, ctx->stream);
-  });
+  int rc;
+  int32_t s_i = 0;
+  float s_f = 0.0f;
+  {
+    CtxGuard g(ctx);             // the staging words are read before the lock is given up
+    rc = scalar_redomap(ctx, "sum_i32_f32.segred_nonseg", PROV("(i32.sum xs, f32.sum (map f32.i32 xs))"), n, 8, [&] {
+      return fb::launch_sum_i32_f32(dptr<int32_t>(in0->mem), n, ctx->d_scalar, ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+    });
+    s_i = reinterpret_cast<int32_t *>(ctx->h_scalar)[0];
+    s_f = reinterpret_cast<float *>(ctx->h_scalar)[1];
+  }
   if (rc) return rc;
-  *out0 = reinterpret_cast<int32_t *>(ctx->h_scalar)[0];
-  *out1 = reinterpret_cast<float *>(ctx->h_scalar)[1];
-  return FUTHARK_SUCCESS;
+  return futhark_new_opaque_tup2_i32_f32(ctx, out0, s_i, s_f);
 }
 
 // reduce (+) 0 (map2 (*) xs ys): a redomap whose map body takes two inputs.

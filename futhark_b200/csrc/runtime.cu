@@ -698,4 +698,64 @@ pair_t *futhark_restore_opaque_tup2_arr1d_u32_arr1d_u32(struct futhark_context *
   return out;
 }
 
+// ---- the opaque pair of scalars returned by sum_i32_f32: same functions, host-side fields -----------
+typedef struct futhark_opaque_tup2_i32_f32 spair_t;
+
+int futhark_free_opaque_tup2_i32_f32(struct futhark_context *ctx, spair_t *obj) {
+  (void)ctx;
+  free(obj);
+  return 0;
+}
+
+int futhark_new_opaque_tup2_i32_f32(struct futhark_context *ctx, spair_t **out, const int32_t v0, const float v1) {
+  (void)ctx;
+  spair_t *p = (spair_t *)malloc(sizeof(spair_t));
+  if (p == nullptr) return 1;
+  p->v0 = v0;
+  p->v1 = v1;
+  *out = p;
+  return 0;
+}
+
+int futhark_project_opaque_tup2_i32_f32_0(struct futhark_context *ctx, int32_t *out, const spair_t *obj) {
+  (void)ctx;
+  *out = obj->v0;
+  return 0;
+}
+int futhark_project_opaque_tup2_i32_f32_1(struct futhark_context *ctx, float *out, const spair_t *obj) {
+  (void)ctx;
+  *out = obj->v1;
+  return 0;
+}
+
+// Serialised form: the two scalars in the binary data format ('b', version 2, rank 0, type, value).
+static const size_t kScalarHdr = 1 + 1 + 1 + 4;
+int futhark_store_opaque_tup2_i32_f32(struct futhark_context *ctx, const spair_t *obj, void **p, size_t *n) {
+  (void)ctx;
+  const size_t total = 2 * (kScalarHdr + 4);
+  *n = total;
+  if (p == nullptr) return 0;
+  if (*p == nullptr) *p = malloc(total);
+  if (*p == nullptr) return 1;
+  unsigned char *o = (unsigned char *)*p;
+  *o++ = 'b'; *o++ = 2; *o++ = 0; memcpy(o, " i32", 4); o += 4; memcpy(o, &obj->v0, 4); o += 4;
+  *o++ = 'b'; *o++ = 2; *o++ = 0; memcpy(o, " f32", 4); o += 4; memcpy(o, &obj->v1, 4);
+  return 0;
+}
+
+spair_t *futhark_restore_opaque_tup2_i32_f32(struct futhark_context *ctx, const void *p) {
+  const unsigned char *s = (const unsigned char *)p;
+  const unsigned char *t = s + kScalarHdr + 4;
+  if (s[0] != 'b' || s[1] != 2 || s[2] != 0 || memcmp(s + 3, " i32", 4) != 0 || t[0] != 'b' || t[1] != 2 || t[2] != 0 ||
+      memcmp(t + 3, " f32", 4) != 0) {
+    fb_set_error(ctx, "Cannot restore value: malformed header.");
+    return nullptr;
+  }
+  spair_t *out = (spair_t *)malloc(sizeof(spair_t));
+  if (out == nullptr) return nullptr;
+  memcpy(&out->v0, s + kScalarHdr, 4);
+  memcpy(&out->v1, t + kScalarHdr, 4);
+  return out;
+}
+
 }  // extern "C"

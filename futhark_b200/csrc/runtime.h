@@ -138,3 +138,8 @@ struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 {
   futhark_u32_1d *v0;
   futhark_u32_1d *v1;
 };
+
+struct futhark_opaque_tup2_i32_f32 {
+  int32_t v0;
+  float v1;
+};

@@ -159,8 +159,22 @@ int futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(struct futhark_context *ct
                                                       struct futhark_u32_1d **out,
                                                       const struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *obj);
 
+/* ---- opaque tuple (i32, f32) returned by sum_i32_f32: same naming and functions; its
+ *      fields are scalars, so `new` takes and the projections return them by value ---------- */
+struct futhark_opaque_tup2_i32_f32;
+int futhark_free_opaque_tup2_i32_f32(struct futhark_context *ctx, struct futhark_opaque_tup2_i32_f32 *obj);
+int futhark_store_opaque_tup2_i32_f32(struct futhark_context *ctx, const struct futhark_opaque_tup2_i32_f32 *obj,
+                                      void **p, size_t *n);
+struct futhark_opaque_tup2_i32_f32 *futhark_restore_opaque_tup2_i32_f32(struct futhark_context *ctx, const void *p);
+int futhark_new_opaque_tup2_i32_f32(struct futhark_context *ctx, struct futhark_opaque_tup2_i32_f32 **out,
+                                    const int32_t v0, const float v1);
+int futhark_project_opaque_tup2_i32_f32_0(struct futhark_context *ctx, int32_t *out,
+                                          const struct futhark_opaque_tup2_i32_f32 *obj);
+int futhark_project_opaque_tup2_i32_f32_1(struct futhark_context *ctx, float *out,
+                                          const struct futhark_opaque_tup2_i32_f32 *obj);
+
 /* ---- entry points: src/Futhark/CodeGen/Backends/GenericC/EntryPoints.hs:133-223.
- * One out-parameter each; array results are allocated by the callee and owned by
+ * One out-parameter each (a tuple result is one opaque value); array results are allocated by the callee and owned by
  * the caller; on error the out-parameter is untouched.  The Futhark source of each
  * entry is given; the kernels that implement them replace what
  * src/Futhark/CodeGen/ImpGen/GPU/{SegRed,SegScan/SinglePass,SegHist,SegMap}.hs
@@ -260,7 +274,7 @@ int futhark_entry_exscan_i32(struct futhark_context *ctx, struct futhark_i32_1d 
                              const struct futhark_i32_1d *in0);
 int futhark_entry_mss_i32(struct futhark_context *ctx, int32_t *out0,
                           const struct futhark_i32_1d *in0);
-int futhark_entry_sum_i32_f32(struct futhark_context *ctx, int32_t *out0, float *out1,
+int futhark_entry_sum_i32_f32(struct futhark_context *ctx, struct futhark_opaque_tup2_i32_f32 **out0,
                               const struct futhark_i32_1d *in0);
 int futhark_entry_dotprod_f32(struct futhark_context *ctx, float *out0,
                               const struct futhark_f32_1d *in0, const struct futhark_f32_1d *in1);

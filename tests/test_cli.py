@@ -187,6 +187,11 @@ def test_server_session_restore_call_store_free(cli, tmp_path):
     rej, _ = fb.value_from_bytes(raw[used:], "u32", 1)
     mask = (keys & 7) < 3
     assert np.array_equal(sel, keys[mask]) and np.array_equal(rej, keys[~mask])
+    # projecting leaves the record whole: it can be projected again, and rebuilt from its fields
+    s.ok("project sel2 pr 0")
+    s.ok('new pr2 "([]u32, []u32)" sel2 rej')
+    assert s.ok("type pr2") == ["([]u32, []u32)"]
+    s.ok("free sel2 pr2")
     s.ok("rename sel chosen")
     s.ok("free chosen rej pr ks out fl xs")
     # scalars travel as values too

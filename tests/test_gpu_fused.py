@@ -171,3 +171,29 @@ def test_fused_full_size_2p26(ctx):
     prod = u.double() * v.double()
     assert abs(d - float(prod.sum().item())) <= 1e-5 * float(prod.abs().sum().item())
     ua.free(); va.free()
+
+
+def test_sum_i32_f32_result_is_an_opaque_tuple_with_store_and_restore(ctx):
+    import ctypes
+    xs = ctx.new("i32_1d", np.array([1, 2, 3, -10], np.int32))
+    L, obj = ctx.lib, ctypes.c_void_p()
+    assert L.futhark_entry_sum_i32_f32(ctx.ptr, ctypes.byref(obj), xs.ptr) == 0
+    buf, n = ctypes.c_void_p(), ctypes.c_size_t()
+    assert L.futhark_store_opaque_tup2_i32_f32(ctx.ptr, obj, ctypes.byref(buf), ctypes.byref(n)) == 0
+    data = ctypes.string_at(buf.value, n.value)
+    # the serialised form is the two scalars in the binary data format
+    a, used = fb.value_from_bytes(data, "i32", 0)
+    b, _ = fb.value_from_bytes(data[used:], "f32", 0)
+    assert (int(a), float(b)) == (-4, -4.0)
+    back = L.futhark_restore_opaque_tup2_i32_f32(ctx.ptr, buf)
+    oi, of = ctypes.c_int32(), ctypes.c_float()
+    assert L.futhark_project_opaque_tup2_i32_f32_0(ctx.ptr, ctypes.byref(oi), back) == 0
+    assert L.futhark_project_opaque_tup2_i32_f32_1(ctx.ptr, ctypes.byref(of), back) == 0
+    assert (oi.value, of.value) == (-4, -4.0)
+    made = ctypes.c_void_p()
+    assert L.futhark_new_opaque_tup2_i32_f32(ctx.ptr, ctypes.byref(made), 7, 0.5) == 0
+    assert L.futhark_project_opaque_tup2_i32_f32_1(ctx.ptr, ctypes.byref(of), made) == 0 and of.value == 0.5
+    for o in (obj, back, made):
+        assert L.futhark_free_opaque_tup2_i32_f32(ctx.ptr, o) == 0
+    fb._libc.free(buf)
+    xs.free()
