@@ -208,3 +208,42 @@ def test_transpose_f32_131072x1024(ctx, dev):
     ctx.sync()
     assert torch.equal(view(back, dev, torch.float32), x)
     out.free(); back.free(); a.free()
+
+
+def test_beyond_2p31_elements(ctx, dev):
+    """More than 2^31 elements: every index on the path must be 64-bit."""
+    n = (1 << 31) + 4099
+    x = torch.randint(-1000, 1001, (n,), device=dev, dtype=torch.int32, generator=gen(dev, 8))
+    ready()
+    a = ctx.new_raw("i32_1d", x.data_ptr(), n)
+    out = ctx.entry_scan_i32(a)
+    ctx.sync()
+    o = view(out, dev, torch.int32)
+    assert int(o[0]) == int(x[0])
+    step = 1 << 28                                              # compare in slices to bound the temporaries
+    for lo in range(1, n, step):
+        hi = min(lo + step, n)
+        assert torch.equal(o[lo:hi] - o[lo - 1:hi - 1], x[lo:hi])
+    total = ctx.entry_reduce_i32(a)
+    assert total == int(o[-1])
+    ref = sum(int(x[lo:min(lo + step, n)].to(torch.int64).sum().item()) for lo in range(0, n, step))
+    assert total == ((ref + 2 ** 31) % 2 ** 32) - 2 ** 31
+    si, sf = ctx.entry_sum_i32_f32(a)
+    assert si == total
+    l1 = sum(float(x[lo:min(lo + step, n)].double().abs().sum().item()) for lo in range(0, n, step))
+    assert abs(sf - ref) <= 1e-5 * l1
+    out.free()
+    # compaction states its limit instead of overflowing a 32-bit count
+    ka = ctx.new_raw("u32_1d", x.data_ptr(), n)
+    with pytest.raises(fb.FutharkError) as e:
+        ctx.entry_filter_u32(ka)
+    assert "2^31-1" in e.value.message
+    ka.free(); a.free()
+    del o, x
+    u = torch.randn(n, device=dev, generator=gen(dev, 9))
+    ready()
+    ua = ctx.new_raw("f32_1d", u.data_ptr(), n)
+    d = ctx.entry_dotprod_f32(ua, ua)                            # sum of squares
+    ref2 = sum(float((u[lo:min(lo + step, n)].double() ** 2).sum().item()) for lo in range(0, n, step))
+    assert abs(d - ref2) <= 1e-5 * ref2
+    ua.free()
