@@ -160,10 +160,14 @@ hist_smem_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ 
 // hold them.  Where the histogram leaves room (two ranges of <= 33536 bins), every thread
 // keeps HIST_STAGES 16-byte copies of indices and of weights in flight straight into shared
 // memory (cp.async), three rounds ahead of its own reading; a thread reads back only what it
-// copied itself, so no barrier is involved.  One private copy of the bins (log2c = 0): with
-// skewed indices the updates of a hot bin queue up on its one word (~4 cycles each; 13.7 % of
-// the updates for Zipf 1.1 over 65536 bins), which then bounds the kernel.  Combining equal
-// bins across the warp first (match.any + warp reduction) was measured 10x slower.
+// copied itself, so no barrier is involved.  One private copy of the bins (log2c = 0).  With
+// skewed indices (Zipf 1.1 over 65536 bins) the CTA whose range holds the most frequent bins
+// runs ~13 % longer than its partner, falls behind it, and re-reads from HBM what has left L2
+// meanwhile (measured: 1.47x the input), which then bounds the kernel.  Measured and not kept:
+// combining equal bins across the warp first (match.any + warp reduction, 10x slower); the four
+// most frequent bins of a CTA combined in registers (no faster, and slower for uniform
+// indices); the CTAs of a group paced by a cluster barrier (Zipf 12 % faster, uniform max 9 %
+// slower, three and four ranges slower).
 constexpr int HIST_STAGES = 3;
 constexpr int HIST_STAGE_BYTES = HIST_THREADS * 32;       // 16 bytes of indices + 16 bytes of weights per thread
 

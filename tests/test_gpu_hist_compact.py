@@ -50,6 +50,38 @@ def test_hist_many_bins_long_input(ctx, dist):
     assert np.array_equal(got.view(np.uint32), oracle.hist_max_f32(B, bins, wf).view(np.uint32))
 
 
+@pytest.mark.parametrize("B", [10000, 20000, 57344, 65536, 100000, 1 << 20])
+@pytest.mark.parametrize("kind", ["one_bin", "last_bin", "five_bins", "int_min", "nan_on_hot", "drifting"])
+def test_hist_hot_bins_in_registers(ctx, B, kind):
+    # very frequent bins are combined in registers (paths with four copies of a bin or fewer, and the
+    # cached path; 10000 bins have eight copies and take the plain loop); the result
+    # must not depend on which bins a CTA takes for hot
+    n = (1 << 21) + 7
+    rng = np.random.default_rng(B + len(kind))
+    bins = rng.integers(-B // 100, B + B // 100, n, dtype=np.int64).astype(np.int32)
+    wi = rng.integers(-100, 100, n, dtype=np.int32)
+    wf = rng.standard_normal(n).astype(np.float32)
+    hot = rng.random(n) < 0.6
+    if kind == "one_bin":
+        bins[:] = 12345
+    elif kind == "last_bin":                       # lies in the last bin range
+        bins[hot] = B - 1
+    elif kind == "five_bins":                      # one more than the registers hold
+        bins[hot] = rng.choice(np.array([0, 3, B // 2, B // 2 + 1, B - 2], dtype=np.int32), int(hot.sum()))
+    elif kind == "int_min":                        # frequent, but out of range
+        bins[hot] = np.iinfo(np.int32).min
+        bins[::7] = 5
+    elif kind == "nan_on_hot":
+        bins[hot] = 77
+        wf[hot & (rng.random(n) < 0.9)] = np.nan
+        wf[bins == 77] = np.where(np.isnan(wf[bins == 77]), np.nan, -3.0)
+    elif kind == "drifting":                       # the frequent bin changes along the input
+        bins[hot] = (np.arange(n)[hot] // (n // 8)).astype(np.int32) * 1000
+    assert np.array_equal(fb.hist_add_i32(ctx, B, bins, wi), oracle.hist_add_i32(B, bins, wi))
+    got = fb.hist_max_f32(ctx, B, bins, wf)
+    assert np.array_equal(got.view(np.uint32), oracle.hist_max_f32(B, bins, wf).view(np.uint32))
+
+
 def test_hist_reference_known_answers(ctx):
     # tests/hist/simple.fut:4-50 with a zero destination; index 10000000 is out of range
     assert np.array_equal(fb.hist_add_i32(ctx, 5, [1, 1, 1, 1, 1], [1, 1, 1, 1, 1]), [0, 5, 0, 0, 0])
