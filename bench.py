@@ -15,6 +15,14 @@ every step starts from pinned host buffers and ends with the results in host mem
 (futhark_new_* / futhark_entry_* / futhark_values_* / futhark_context_sync).
 `--impl reference` times the CPU restatement of the reference's multicore algorithms
 (oracle/) on the host cores for the same metric.
+
+After the headline step the same run times every configuration of the baseline at full size
+(scan and reduce over 2^26 i32, the three parts of the step, the twelve histogram cases over
+2^28 indices, filter and partition of 2^28 keys, the 64 x 1024^3 f16 contraction) and reports
+them as the `per_soac` list of the one JSON line, with a clock record of their own.  With N
+GPUs the entries go through the sharded operations (one exchange each where the operation has
+one), every rank holding a full-size shard, except the contraction, whose 64 batches are
+divided among the ranks.
 """
 import argparse
 import json
@@ -45,6 +53,44 @@ def measured_peaks():
         d = json.load(open(path))
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def measured_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
+def bind_host_thread_near_gpu(index):
+    """Pin this process to the host cores of the GPU's NUMA node before any pinned host buffer
+    is allocated, so that with several ranks the buffers are spread over the host's memory
+    controllers instead of all landing on the node the launcher happened to run on.  Reads
+    sysfs only; returns what it did for the JSON line."""
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(index).pci_bus_id if hasattr(torch.cuda.get_device_properties(index), "pci_bus_id") else None
+        dom = getattr(torch.cuda.get_device_properties(index), "pci_domain_id", 0)
+        dev = getattr(torch.cuda.get_device_properties(index), "pci_device_id", 0)
+        if bus is None:
+            return {"bound": False, "why": "no PCI bus id"}
+        base = "/sys/bus/pci/devices/%04x:%02x:%02x.0" % (dom, bus, dev)
+        node = int(open(base + "/numa_node").read().strip())
+        cpus = open(base + "/local_cpulist").read().strip()
+        want = set()
+        for part in cpus.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                want.update(range(int(a), int(b) + 1))
+            elif part:
+                want.add(int(part))
+        allowed = set(os.sched_getaffinity(0)) & want
+        if node < 0 or not allowed:
+            return {"bound": False, "numa_node": node, "why": "no usable local cpu list"}
+        os.sched_setaffinity(0, allowed)
+        return {"bound": True, "numa_node": node, "cpus": len(allowed)}
+    except Exception as e:                                   # no sysfs, no permission: run unbound
+        return {"bound": False, "why": type(e).__name__}
 
 
 class ClockSampler:
@@ -175,6 +221,9 @@ def run_case(args):
     ctx = fb.Context(profiling=True)
 
     def timed(name, fn, nbytes, n, extra=None, flops=None):
+        sampler = ClockSampler(ctx.device)
+        sampler.start()
+        time.sleep(0.3)                  # nvidia-smi needs a moment before its first sample
         ctx.sync()
         ctx.pause_profiling()
         for _ in range(args.warmup):
@@ -193,7 +242,7 @@ def run_case(args):
         us = [e["duration"] for e in ev]
         avg = float(np.mean(us))
         line = {"case": name, "n": n, "launches": len(us), "avg_us": avg, "min_us": float(np.min(us)),
-                "kernel_event": ev[0]["name"], "algorithmic_bytes": int(nbytes)}
+                "kernel_event": ev[0]["name"], "algorithmic_bytes": int(nbytes), "clocks": sampler.stop()}
         line.update(extra or {})
         if flops:
             tf = flops / (avg * 1e-6) / 1e12
@@ -286,6 +335,228 @@ def run_case(args):
     ctx.close()
 
 
+# ---- every configuration of the baseline at full size, inside the default run --------------------
+
+def _device_inputs(torch, dev, rank):
+    """Seeded generators on the device with the workload's shapes and distributions (what
+    `futhark_b200.datagen` draws on the host for the parity tests, drawn here by torch so that
+    2^28-element inputs take milliseconds).  The library borrows the tensors' memory."""
+    def g(seed):
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed + 1000 * rank)
+        return gen
+
+    def i32(n, seed):
+        return torch.randint(-1000, 1001, (n,), device=dev, dtype=torch.int32, generator=g(seed))
+
+    def segments(n, seed):
+        gen = g(seed)
+        x = torch.randn(n, device=dev, generator=gen)
+        flags = (torch.rand(n, device=dev, generator=gen) < 1.0 / 256).to(torch.uint8)   # gaps 1 + Geometric(1/256)
+        flags[0] = 1
+        offsets = torch.cat([torch.nonzero(flags).flatten(), torch.tensor([n], device=dev)]).to(torch.int64)
+        return x, flags, offsets
+
+    def bins(n, B, dist_name, seed):
+        gen = g(seed)
+        if dist_name == "uniform":
+            b = torch.randint(0, B, (n,), device=dev, dtype=torch.int32, generator=gen)
+        else:                                                   # Zipf s = 1.1 over ranks, ranks scattered over the bins
+            w = torch.arange(1, B + 1, device=dev, dtype=torch.float64) ** -1.1
+            cdf = torch.cumsum(w, 0)
+            cdf /= cdf[-1].clone()
+            rnk = torch.searchsorted(cdf, torch.rand(n, device=dev, dtype=torch.float64, generator=gen)).clamp_(max=B - 1)
+            b = ((rnk * 0x9E3779B1 + 0x7F4A7C15) % B).to(torch.int32)
+            del w, cdf, rnk
+        oor = torch.rand(n, device=dev, generator=gen) < 0.01    # ~1 % out of range, half below and half above
+        b[oor] = torch.where(torch.rand(int(oor.sum()), device=dev, generator=gen) < 0.5, -7, B + 12345).to(torch.int32)
+        return b
+
+    return {"g": g, "i32": i32, "segments": segments, "bins": bins}
+
+
+def run_per_soac(ctx, group, torch, dist, dev, rank, world, reps, warmup):
+    """Times every configuration of the baseline at full size with the inputs resident.
+    One GPU: CUDA event pairs around each kernel (the library's profiling records).  Several
+    GPUs: the sharded operation, CUDA events on the library's stream around `reps` calls
+    between two barriers, the maximum over the ranks."""
+    import futhark_b200 as fb
+    peak, peak_kind = measured_peaks()
+    tpeak, _ = measured_tensor_peak()
+    mk = _device_inputs(torch, dev, rank)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+    out = []
+
+    def free(o):
+        for x in (o if isinstance(o, (tuple, list)) else (o,)):
+            if hasattr(x, "free"):
+                x.free()
+
+    def timed(name, fn, n, nbytes=None, flops=None, extra=None, scaling="weak"):
+        torch.cuda.synchronize()
+        ctx.sync()
+        for _ in range(warmup):
+            free(fn())
+        ctx.sync()
+        if world == 1:
+            ctx.unpause_profiling()
+            ctx.report()
+            for _ in range(reps):
+                free(fn())
+            ctx.sync()
+            ev = json.loads(ctx.report())["events"]
+            ctx.pause_profiling()
+            per_call = len(ev) // reps
+            us = [sum(e["duration"] for e in ev[i * per_call:(i + 1) * per_call]) for i in range(reps)]
+            avg, mn = float(np.mean(us)), float(np.min(us))
+        else:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                free(fn())
+            e1.record(stream)
+            ctx.sync()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            avg = mn = float(t[0])
+        total_n = n * world if scaling == "weak" else n
+        line = {"case": name, "n": int(total_n), "scaling": scaling, "avg_us": avg, "min_us": mn,
+                "elements_per_s": total_n / (avg * 1e-6)}
+        if flops is not None:
+            tf = flops / (avg * 1e-6) / 1e12
+            line.update({"tflops": tf, "peak_tflops": tpeak * world, "frac": tf / (tpeak * world)})
+        else:
+            total_b = nbytes * world if scaling == "weak" else nbytes
+            gbs = total_b / (avg * 1e-6) / 1e9
+            line.update({"algorithmic_bytes": int(total_b), "gbs": gbs, "peak_gbs": peak * world, "frac": gbs / (peak * world)})
+        line.update(extra or {})
+        out.append(line)
+
+    # configuration 1
+    n = 1 << 26
+    x = mk["i32"](n, 1)
+    torch.cuda.synchronize()
+    a = ctx.new_raw("i32_1d", x.data_ptr(), n)
+    timed("scan_i32", (lambda: ctx.entry_scan_i32(a)) if group is None else (lambda: group.scan_i32(a)), n, 8 * n)
+    timed("reduce_i32", (lambda: ctx.entry_reduce_i32(a)) if group is None else (lambda: group.reduce_i32_device(a)), n, 4 * n)
+    a.free(); del x
+    # configuration 2
+    n = N_SEG
+    x, flags, offsets = mk["segments"](n, 2)
+    nseg = offsets.numel() - 1
+    torch.cuda.synchronize()
+    xa, fa, oa = ctx.new_raw("f32_1d", x.data_ptr(), n), ctx.new_raw("bool_1d", flags.data_ptr(), n), ctx.new_raw("i64_1d", offsets.data_ptr(), nseg + 1)
+    timed("segscan_f32", (lambda: ctx.entry_segscan_f32(fa, xa)) if group is None else (lambda: group.segscan_f32(fa, xa)), n, 9 * n)
+    timed("segreduce_f32", lambda: ctx.entry_segreduce_f32(oa, fa, xa), n, 4 * n + 8 * (nseg + 1) + 4 * nseg, extra={"segments": int(nseg)})
+    for z in (xa, fa, oa):
+        z.free()
+    del flags, offsets
+    ra = ctx.new_raw("f32_2d", x.data_ptr(), ROWS, COLS)
+    timed("rowsum_f32", lambda: ctx.entry_rowsum_f32(ra), ROWS * COLS, 4 * ROWS * COLS + 4 * ROWS)
+    ra.free(); del x
+    # configuration 3
+    n = 1 << 28
+    gen = mk["g"](4)
+    wi = torch.randint(0, 101, (n,), device=dev, dtype=torch.int32, generator=gen)
+    wf = torch.randn(n, device=dev, generator=gen)
+    for B in (256, 65536, 1 << 20):
+        for dist_name in ("uniform", "zipf"):
+            b = mk["bins"](n, B, dist_name, 40 + (B % 97))
+            torch.cuda.synchronize()
+            ba, wia, wfa = ctx.new_raw("i32_1d", b.data_ptr(), n), ctx.new_raw("i32_1d", wi.data_ptr(), n), ctx.new_raw("f32_1d", wf.data_ptr(), n)
+            extra = {"bins": B, "dist": dist_name}
+            timed("hist_add_i32", (lambda: ctx.entry_hist_add_i32(B, ba, wia)) if group is None else (lambda: group.hist("add", B, ba, wia)),
+                  n, 8 * n + 4 * B, extra=extra)
+            timed("hist_max_f32", (lambda: ctx.entry_hist_max_f32(B, ba, wfa)) if group is None else (lambda: group.hist("max", B, ba, wfa)),
+                  n, 8 * n + 4 * B, extra=extra)
+            for z in (ba, wia, wfa):
+                z.free()
+            del b
+    del wi, wf
+    ctx.clear_caches()
+    # configuration 4
+    k = torch.randint(-2 ** 31, 2 ** 31 - 1, (n,), device=dev, dtype=torch.int32, generator=mk["g"](5))
+    sel = int(((k & 7) < 3).sum())
+    torch.cuda.synchronize()
+    ka = ctx.new_raw("u32_1d", k.data_ptr(), n)
+    timed("filter_u32", (lambda: ctx.entry_filter_u32(ka)) if group is None else (lambda: group.filter_u32(ka)[0]), n, 4 * n + 4 * sel)
+
+    def part():
+        if group is None:
+            return ctx.entry_partition_u32(ka)
+        r = group.partition_u32(ka)
+        return r[0], r[1]
+    timed("partition_u32", part, n, 8 * n)
+    ka.free(); del k
+    ctx.clear_caches()
+    # configuration 5: the 64 batches are divided among the ranks
+    nb, m = 64, 1024
+    from futhark_b200 import sharded
+    blo, bhi = sharded.shard_bounds(nb, world, rank)
+    gen = mk["g"](6)
+    A = (torch.rand(max(bhi - blo, 1), m, m, device=dev, generator=gen) * 2 - 1).half()
+    Bm = (torch.rand(max(bhi - blo, 1), m, m, device=dev, generator=gen) * 2 - 1).half()
+    torch.cuda.synchronize()
+    Aa, Ba = ctx.new_raw("f16_3d", A.data_ptr(), bhi - blo, m, m), ctx.new_raw("f16_3d", Bm.data_ptr(), bhi - blo, m, m)
+    timed("bmm_f16", (lambda: ctx.entry_bmm_f16(Aa, Ba)) if group is None else (lambda: group.bmm_f16(Aa, Ba)),
+          nb * m * m, flops=2 * nb * m * m * m, extra={"batches": nb, "dim": m}, scaling="strong")
+    Aa.free(); Ba.free(); del A, Bm
+    ctx.clear_caches()
+    return out
+
+
+def verify_sharded(ctx, group, torch, dist, rank, world):
+    """Once, outside every timed region, at a reduced size: each rank checks its shard of the
+    sharded scans against the CPU oracle run on its own shard plus the gathered exchange data,
+    and the exchange data it contributed against the oracle as well, so the whole chain
+    (shard-local kernels, collective, carry kernels) is compared on the GPUs that run the
+    bench.  Returns a dict of booleans (all ranks' results AND-ed)."""
+    import oracle
+    from futhark_b200 import datagen, sharded
+    n = (1 << 20) + 4099
+    res = {}
+    xs = datagen.uniform_i32(900 + rank, 0, n, -1000, 1000)
+    a = ctx.new("i32_1d", xs)
+    o = group.scan_i32(a)
+    got = o.values()
+    o.free()
+    mine = torch.tensor([oracle.reduce_i32(xs)], dtype=torch.int32, device="cuda")
+    totals = torch.empty(world, dtype=torch.int32, device="cuda")
+    dist.all_gather_into_tensor(totals, mine)
+    carry = int(totals[:rank].to(torch.int64).sum().item())
+    want = (oracle.scan_i32(xs).astype(np.int64) + carry).astype(np.int32)        # wraps like the i32 scan
+    res["scan_i32"] = bool(np.array_equal(got, want))
+    res["reduce_i32"] = group.reduce_i32(a) == (((int(totals.to(torch.int64).sum().item()) + 2 ** 31) % 2 ** 32) - 2 ** 31)
+    a.free()
+    for mean in (256, 10 ** 9):
+        _, flags = datagen.geometric_segments(910 + rank, n, mean)
+        if rank > 0 and mean > n:
+            flags[:] = 0                                                         # a shard without any segment start
+        vals = datagen.uniform_i32(920 + rank, 0, n, -8, 8).astype(np.float32)     # small integers: exact sums, bit-exact check
+        fa, xa = ctx.new("bool_1d", flags.view(np.bool_)), ctx.new("f32_1d", vals)
+        o = group.segscan_f32(fa, xa)
+        got = o.values()
+        o.free(); fa.free(); xa.free()
+        local = oracle.segscan_f32_seq64(flags, vals).astype(np.float32)
+        s_mine = torch.tensor([float(local[-1]), float(flags.any())], dtype=torch.float32, device="cuda")
+        s_all = torch.empty(2 * world, dtype=torch.float32, device="cuda")
+        dist.all_gather_into_tensor(s_all, s_mine)
+        s_all = s_all.cpu().numpy().reshape(world, 2)
+        carry, _ = sharded.fold_summaries([(v, int(f)) for v, f in s_all], rank)
+        nz = np.flatnonzero(flags)
+        first = int(nz[0]) if len(nz) else n
+        want = local.copy()
+        want[:first] = np.float32(carry) + want[:first]
+        res["segscan_f32_mean%d" % min(mean, 10 ** 9)] = bool(np.array_equal(got, want))
+    ok = torch.tensor([int(all(res.values()))] + [int(v) for v in res.values()], dtype=torch.int32, device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    flat = ok.cpu().tolist()
+    return {"all": bool(flat[0]), **{k: bool(v) for k, v in zip(res.keys(), flat[1:])}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default=None, help="run one entry point, 'all', or 'sweep' (every baseline configuration) instead of the step")
@@ -300,6 +571,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-per-soac", action="store_true", help="skip the per-configuration timings after the step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -320,6 +592,7 @@ def main():
     from futhark_b200 import sharded
 
     torch.cuda.set_device(local_rank)
+    binding = bind_host_thread_near_gpu(local_rank) if world > 1 else {"bound": False, "why": "single rank"}
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = fb.Context(device="#%d" % local_rank, profiling=True)
@@ -428,6 +701,20 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
 
+    verified = verify_sharded(ctx, group, torch, dist, rank, world) if world > 1 else None
+
+    per_soac, soac_clocks = None, None
+    if not args.no_per_soac:
+        for a in (d_off, d_flags, d_xs, d_rows):
+            a.free()
+        d_off = d_flags = d_xs = d_rows = None
+        ctx.clear_caches()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        per_soac = run_per_soac(ctx, group, torch, dist, torch.device("cuda", local_rank), rank, world, args.reps, args.warmup)
+        soac_clocks = sampler.stop()
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
@@ -447,10 +734,12 @@ def main():
         line = {
             "metric": "elements/s", "value": world * ELEMS_PER_STEP / (ms * 1e-3), "unit": "elements/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,       # no published number for this metric
+            "dtype": "f32", "data": "synthetic",
             "config": workload_config(),
             "roofline": {"bound": "hbm", "kernel": "stream_kernel<K_SEGSCAN_F32>", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_note": "the peak is a read+write copy; kernels that almost only read (reduce, rowsum, histograms) can exceed it",
                          "traffic": NCU_TRAFFIC_SEGSCAN_2P25 * (N_SEG / float(1 << 25)),
                          "traffic_note": "ncu capture of a 2^25-element launch scaled by elements; the write-back of the L2-resident tail of the output is not in it",
                          "algorithmic_bytes_per_launch": ALG_BYTES_SEGSCAN, "avg_launch_us": seg_us},
@@ -460,10 +749,17 @@ def main():
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            "per_soac": per_soac,
+            "per_soac_clocks": soac_clocks,
+            "sharded_results_verified": verified,
+            "host_binding": binding,
         }
+        if cpu is not None:
+            line["vs_cpu_baseline"] = {"resident": line["value"] / cpu["value"], "e2e": line["e2e"]["value"] / cpu["value"]}
         print(json.dumps(line), flush=True)
     for a in (d_off, d_flags, d_xs, d_rows):
-        a.free()
+        if a is not None:
+            a.free()
     ctx.close()
     if world > 1:
         dist.destroy_process_group()

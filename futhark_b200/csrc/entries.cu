@@ -181,27 +181,31 @@ int futhark_entry_prod_of_sums_i32(struct futhark_context *ctx, int32_t *out0, c
   return FUTHARK_SUCCESS;
 }
 
-int futhark_entry_segscan_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
-                              const struct futhark_f32_1d *in1) {
-  if (!ctx->ready) return not_ready(ctx);
-  CtxGuard g(ctx);
+// The caller holds the context's lock.  shard_out (device, 4 words, or NULL): see launch_segscan_f32.
+static int segscan_f32_locked(futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
+                              const struct futhark_f32_1d *in1, uint32_t *shard_out) {
   const int64_t n = in1->shape[0];
   if (in0->shape[0] != n) return bad_sizes(ctx);
   int rc;
   futhark_f32_1d *out = make_1d<futhark_f32_1d>(ctx, n, 4, "segscan_f32.out", &rc);
   if (out == nullptr) return rc;
-  if (n > 0) {
-    rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(n));
-    if (rc == 0) {
-      LaunchScope ls(ctx, "segscan_f32.segscan", PROV("scan lifted(+) (false,0) (zip flags xs)"), "{" + kv("n", n) + "}");
-      rc = fb_cuda_check(ctx, fb::launch_segscan_f32(dptr<uint8_t>(in0->mem), dptr<float>(in1->mem), dptr<float>(out->mem), n, 0.0f,
-                                                     ctx->lookback_scratch, fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "segscan_f32");
-      ctx->failure_is_an_option = true;
-    }
-    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  rc = n > 0 ? fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(n)) : 0;
+  if (rc == 0 && (n > 0 || shard_out != nullptr)) {
+    LaunchScope ls(ctx, "segscan_f32.segscan", PROV("scan lifted(+) (false,0) (zip flags xs)"), "{" + kv("n", n) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_segscan_f32(dptr<uint8_t>(in0->mem), dptr<float>(in1->mem), dptr<float>(out->mem), n, 0.0f, shard_out,
+                                                   ctx->lookback_scratch, fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "segscan_f32");
+    ctx->failure_is_an_option = true;
   }
+  if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
   *out0 = out;
   return FUTHARK_SUCCESS;
+}
+
+int futhark_entry_segscan_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
+                              const struct futhark_f32_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  return segscan_f32_locked(ctx, out0, in0, in1, nullptr);
 }
 
 int futhark_entry_segreduce_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_i64_1d *in0,
@@ -493,12 +497,10 @@ int futhark_b200_entry_scan_i32_carried(struct futhark_context *ctx, struct futh
 
 int futhark_b200_entry_segscan_f32_shard(struct futhark_context *ctx, struct futhark_f32_1d **out0, CUdeviceptr summary_dst,
                                          const struct futhark_bool_1d *in0, const struct futhark_f32_1d *in1) {
-  int rc = futhark_entry_segscan_f32(ctx, out0, in0, in1);
-  if (rc != 0) return rc;
+  if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
-  ctx->launch_count++;
-  return fb_cuda_check(ctx, fb::launch_segscan_summary(ctx->lookback_scratch, in1->shape[0], reinterpret_cast<uint32_t *>((uintptr_t)summary_dst),
-                                                       ctx->stream), "segscan summary");
+  // the scan kernel writes the summary itself: one launch, one critical section
+  return segscan_f32_locked(ctx, out0, in0, in1, reinterpret_cast<uint32_t *>((uintptr_t)summary_dst));
 }
 
 int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct futhark_f32_1d *out, const struct futhark_bool_1d *in0,
@@ -506,10 +508,11 @@ int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct f
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
   if (out->shape[0] != in0->shape[0]) return bad_sizes(ctx);
-  if (rank > 0 && out->shape[0] > 0) ctx->launch_count += 2;
+  if (rank <= 0 || out->shape[0] <= 0) return FUTHARK_SUCCESS;
+  LaunchScope ls(ctx, "segscan_f32.apply_carry", PROV("carry of the shards before this one"), "{" + kv("n", out->shape[0]) + "}");
   return fb_cuda_check(ctx, fb::launch_segscan_apply_carry(dptr<float>(out->mem), dptr<uint8_t>(in0->mem), out->shape[0],
                                                            reinterpret_cast<const uint32_t *>((uintptr_t)summaries), rank,
-                                                           reinterpret_cast<unsigned long long *>(ctx->d_scalar + 4), ctx->num_sms, ctx->stream),
+                                                           ctx->num_sms, ctx->stream),
                        "segscan carry");
 }
 

@@ -103,11 +103,16 @@ __device__ __forceinline__ bool aligned16(const void *p) { return (((uintptr_t)p
 // ---- the propagator (one warp in the whole grid) --------------------------------------------
 // Walks the status words in tile order.  For every contiguous run of published aggregates
 // it writes the inclusive prefixes back.  `seed` is the exclusive prefix of tile 0.
+// When `shard_out` is given, the warp leaves there what a scan split over several devices
+// needs of this shard: {value bits, flag} of the inclusive prefix of the last tile and the
+// index of the first tile that contains a segment start (all ones if none does).
 template <typename Op>
-__device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, uint32_t seed, int *failure) {
+__device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, uint32_t seed, int *failure,
+                               uint32_t *shard_out) {
   const int lane = threadIdx.x & 31;
   uint32_t run_v = seed, run_f = 0;     // inclusive prefix of tile pos-1
   uint32_t pos = 0, idle = 0;
+  uint32_t first_flagged = 0xffffffffu;
   while (pos < nt) {
     uint64_t w[PROP_PER_LANE];
     const uint32_t first = pos + PROP_PER_LANE * lane;
@@ -153,6 +158,13 @@ __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, ui
       }
       iv[q] = tv; iflag[q] = tf;
     }
+    if (Op::kHasFlag && shard_out != nullptr && first_flagged == 0xffffffffu) {
+      uint32_t cand = 0xffffffffu;
+#pragma unroll
+      for (int q = PROP_PER_LANE - 1; q >= 0; q--)
+        if (q < mine && status_flag(w[q])) cand = first + q;
+      first_flagged = __reduce_min_sync(kFull, cand);
+    }
     uint32_t sv = tv, sf = tf;          // inclusive scan of lane totals
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -176,6 +188,9 @@ __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, ui
     run_v = lastv; run_f = lastf;
     pos += run;
   }
+  if (shard_out != nullptr && lane == 0) {
+    shard_out[0] = run_v; shard_out[1] = run_f; shard_out[2] = first_flagged; shard_out[3] = 0u;
+  }
 }
 
 // ---- the persistent tile kernel ------------------------------------------------------------------
@@ -195,6 +210,7 @@ struct LookbackArgs {
   const uint32_t *carry_vals;
   int carry_n;
   int64_t *d_count;        // compaction: number of selected keys
+  uint32_t *shard_out;     // segmented scan of one shard of a split array: 4 words, see run_propagator (or NULL)
 };
 
 // Inclusive scan over the first SCAN_WARPS lanes of the warp totals held in shared memory;
@@ -265,7 +281,7 @@ stream_kernel(const LookbackArgs a) {
     for (int q = 0; q < a.carry_n; q++) seed += a.carry_vals[q];
   const bool solo = (gridDim.x == 1);    // a lone CTA turns its own aggregates into prefixes
   if (s_role == 0 && !solo) {
-    if (warp == 0) run_propagator<Op>(a.status, nt, a.epoch, seed, a.failure);
+    if (warp == 0) run_propagator<Op>(a.status, nt, a.epoch, seed, a.failure, a.shard_out);
     return;
   }
   const uint32_t workers = solo ? 1u : gridDim.x - 1;
@@ -278,6 +294,7 @@ stream_kernel(const LookbackArgs a) {
   const bool in_bulk = aligned16(a.in) && (!SEG || aligned16(a.flags));
   const bool out_bulk = !COMPACT && aligned16(a.out);
   uint32_t self_v = seed, self_f = 0;    // thread 0 of a lone CTA: running inclusive prefix
+  uint32_t self_first = 0xffffffffu;     // ... and the first tile with a segment start
 
   // The tile of the next iteration is fetched while this iteration computes: one bulk async
   // copy (TMA) per array into the buffer the iteration before last used, awaited on an
@@ -357,6 +374,7 @@ stream_kernel(const LookbackArgs a) {
         unsigned char *sfb = buf + TILE * 4;
         for (int i = tid; i < TILE; i += SCAN_THREADS) sfb[i] = (i < count) ? a.flags[base + i] : (unsigned char)0;
       }
+      fence_proxy_async_smem();          // a later bulk copy lands in this buffer: order it after these stores
       __syncthreads();
     }
     // A thread owns ITEMS consecutive elements = V 16-byte vectors; V is odd, so the 128-bit
@@ -453,6 +471,7 @@ stream_kernel(const LookbackArgs a) {
     if (is_a) {
       if (tid == 0) {
         if (solo) {
+          if (SEG && tf && self_first == 0xffffffffu) self_first = tile;
           Op::combine(self_v, self_f, tv, tf, self_v, self_f);
           st_status(&a.status[tile], pack_status(self_v, a.epoch, self_f, ST_PREFIX));
         } else {
@@ -497,6 +516,7 @@ stream_kernel(const LookbackArgs a) {
         __syncthreads();
         if (tid == 0) { bulk_s2g(gout, s_tile, TILE * 4); bulk_commit(); }
       } else {
+        fence_proxy_async_smem();        // the buffer is filled again by a bulk copy: order it after the stores above
         __syncthreads();
         for (int i = tid; i < count; i += SCAN_THREADS) gout[i] = s_tile[i];
         __syncthreads();                 // the buffer is filled again at the top of the next iteration
@@ -543,6 +563,9 @@ stream_kernel(const LookbackArgs a) {
     }
   }
   if (tid == 0) {
+    if (solo && a.shard_out != nullptr && !s_fail) {
+      a.shard_out[0] = self_v; a.shard_out[1] = self_f; a.shard_out[2] = self_first; a.shard_out[3] = 0u;
+    }
     bulk_wait_read0();                   // shared memory must outlive the last bulk store's reads
     // A failing grid leaves early: a copy still in flight must land before the CTA's shared memory goes.
     for (int b = 0; b < 2; b++)
@@ -602,7 +625,7 @@ static LookbackArgs make_args(const void *in, const uint8_t *flags, void *out, u
   a.num_tiles = tiles_for<KIND>(n);
   split_scratch(scratch, &a.ticket, &a.status);
   a.epoch = epoch; a.failure = failure;
-  a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr;
+  a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr; a.shard_out = nullptr;
   return a;
 }
 
@@ -624,80 +647,74 @@ cudaError_t launch_exscan_i32(const int32_t *in, int32_t *out, int64_t n, void *
   return launch_stream<K_EXSCAN_I32>(a, stream);
 }
 
+// ---- pieces of a segmented scan whose array is split across several devices ---------------
+// A shard's scan leaves a 4-word summary (see run_propagator): {value bits, flag} of its last
+// inclusive prefix, and the index of its first tile that holds a segment start.  An empty
+// shard has the identity (0, no flag, no such tile).
+__global__ void shard_identity_kernel(uint32_t *dst) {
+  dst[0] = 0u; dst[1] = 0u; dst[2] = 0xffffffffu; dst[3] = 0u;
+}
+
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
-                               void *scratch, uint32_t epoch, int *failure, cudaStream_t stream) {
-  if (n <= 0) return cudaSuccess;
+                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream) {
+  if (n <= 0) {
+    if (shard_out != nullptr) {
+      shard_identity_kernel<<<1, 1, 0, stream>>>(shard_out);
+      return cudaGetLastError();
+    }
+    return cudaSuccess;
+  }
   LookbackArgs a = make_args<K_SEGSCAN_F32>(in, flags, out, nullptr, n, scratch, epoch, failure);
   uint32_t bits;
   memcpy(&bits, &carry_in, 4);
   a.carry_in = bits;
+  a.shard_out = shard_out;
   return launch_stream<K_SEGSCAN_F32>(a, stream);
 }
 
-// ---- pieces of a segmented scan whose array is split across several devices ---------------
-// Summary of a shard = inclusive prefix of its last tile: (value, "a segment starts somewhere
-// in the shard").  Written as two 32-bit words {f32 bits, flag}.
-__global__ void segscan_summary_kernel(const uint64_t *status, uint32_t last_tile, uint32_t *dst) {
-  const uint64_t w = status[last_tile];
-  dst[0] = status_value(w);
-  dst[1] = status_flag(w);
-}
-
-// Position of the first segment start (all ones if none): CTAs take 16 KiB chunks in ascending
-// order and stop as soon as a start before their chunk is known.  A chunk is looked at in
-// rounds of 4 KiB, 16 independent byte loads per thread and round, and left at the first
-// round that contains a start: with segments of a few hundred elements that is one round trip.
+// out[i] = carry + out[i] for every i before the shard's first segment start, where carry is
+// the fold of the summaries of the shards before this one under the lifted operator.  The
+// summary of this shard names the first tile with a segment start: everything before that
+// tile takes the carry (grid-stride, 16-byte vectors where the array allows), and the last
+// CTA finds the start inside that one tile and finishes the elements in front of it.
 __global__ void __launch_bounds__(256)
-first_flag_kernel(const uint8_t *__restrict__ flags, int64_t n, unsigned long long *first) {
-  constexpr int64_t CHUNK = 16384, ROUND = 256 * 16;
-  for (int64_t c = blockIdx.x; c * CHUNK < n; c += gridDim.x) {
-    const int64_t lo = c * CHUNK;
-    if (*reinterpret_cast<volatile unsigned long long *>(first) < (unsigned long long)lo) return;
-    const int64_t hi = lo + CHUNK < n ? lo + CHUNK : n;
-    for (int64_t base = lo; base < hi; base += ROUND) {
-      const int64_t i0 = base + (int64_t)threadIdx.x * 16;
-      uint32_t mask = 0;
-#pragma unroll
-      for (int k = 0; k < 16; k++)
-        if (i0 + k < hi && flags[i0 + k]) mask |= 1u << k;
-      if (mask) atomicMin(first, (unsigned long long)(i0 + __ffs(mask) - 1));
-      if (__syncthreads_or(mask != 0)) break;       // later rounds and chunks only hold later positions
+apply_carry_kernel(float *__restrict__ out, const uint8_t *__restrict__ flags, int64_t n, const uint32_t *summaries, int rank) {
+  constexpr int64_t TILE = TileCfg<K_SEGSCAN_F32>::TILE;
+  __shared__ int s_first;
+  uint32_t cv = 0, cf = 0;
+  for (int q = 0; q < rank; q++) OpSegAddF32::combine(cv, cf, summaries[4 * q], summaries[4 * q + 1], cv, cf);
+  const float carry = __uint_as_float(cv);
+  const uint32_t ft = summaries[4 * rank + 2];
+  const int64_t tile_lo = (ft == 0xffffffffu || (int64_t)ft * TILE > n) ? n : (int64_t)ft * TILE;
+  const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x, stride = (int64_t)gridDim.x * 256;
+  if (aligned16(out)) {
+    float4 *o4 = reinterpret_cast<float4 *>(out);
+    const int64_t nv = tile_lo >> 2;
+    for (int64_t i = gtid; i < nv; i += stride) {
+      float4 v = o4[i];
+      v.x = carry + v.x; v.y = carry + v.y; v.z = carry + v.z; v.w = carry + v.w;
+      o4[i] = v;
     }
+    for (int64_t i = (nv << 2) + gtid; i < tile_lo; i += stride) out[i] = carry + out[i];
+  } else {
+    for (int64_t i = gtid; i < tile_lo; i += stride) out[i] = carry + out[i];
+  }
+  if (blockIdx.x == gridDim.x - 1 && tile_lo < n) {
+    const int count = (int)((n - tile_lo) < TILE ? (n - tile_lo) : TILE);
+    if (threadIdx.x == 0) s_first = count;
+    __syncthreads();
+    for (int i = threadIdx.x; i < count; i += 256)
+      if (flags[tile_lo + i]) { atomicMin(&s_first, i); break; }
+    __syncthreads();
+    const int first = s_first;
+    for (int i = threadIdx.x; i < first; i += 256) out[tile_lo + i] = carry + out[tile_lo + i];
   }
 }
 
-// out[i] += carry for i before the first segment start, where carry is the fold of the
-// summaries of the shards before this one under the lifted operator.
-__global__ void __launch_bounds__(256)
-apply_carry_kernel(float *__restrict__ out, int64_t n, const unsigned long long *first, const uint32_t *summaries, int rank) {
-  uint32_t cv = 0, cf = 0;
-  for (int q = 0; q < rank; q++) OpSegAddF32::combine(cv, cf, summaries[2 * q], summaries[2 * q + 1], cv, cf);
-  const float carry = __uint_as_float(cv);
-  const unsigned long long f = *first;
-  const int64_t end = f < (unsigned long long)n ? (int64_t)f : n;
-  const int64_t stride = (int64_t)gridDim.x * 256;
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < end; i += stride) out[i] = carry + out[i];
-}
-
-cudaError_t launch_segscan_summary(void *scratch, int64_t n, uint32_t *dst, cudaStream_t stream) {
-  if (n <= 0) return cudaMemsetAsync(dst, 0, 8, stream);   // (0, no flag): the identity
-  uint32_t *ticket; uint64_t *status;
-  split_scratch(scratch, &ticket, &status);
-  segscan_summary_kernel<<<1, 1, 0, stream>>>(status, tiles_for<K_SEGSCAN_F32>(n) - 1, dst);
-  return cudaGetLastError();
-}
-
 cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
-                                       int rank, unsigned long long *d_first, int num_sms, cudaStream_t stream) {
+                                       int rank, int num_sms, cudaStream_t stream) {
   if (n <= 0 || rank <= 0) return cudaSuccess;
-  // all ones = "no segment start found" (a memset, not a copy from pageable host memory, which
-  // would make the host wait for the stream)
-  cudaError_t err = cudaMemsetAsync(d_first, 0xff, sizeof(unsigned long long), stream);
-  if (err != cudaSuccess) return err;
-  int64_t chunks = (n + 16383) / 16384;
-  int grid = (int)(chunks < (int64_t)num_sms * 4 ? chunks : (int64_t)num_sms * 4);
-  first_flag_kernel<<<grid, 256, 0, stream>>>(flags, n, d_first);
-  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, n, d_first, summaries, rank);
+  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, flags, n, summaries, rank);
   return cudaGetLastError();
 }
 
@@ -768,6 +785,13 @@ extern "C" int futhark_b200_scan_i32_noalloc(const int32_t *in, int32_t *out, in
     snprintf(d, sizeof(d), "%lld elements requested, at most %lld fit the fixed scratch array", (long long)n, (long long)NOALLOC_MAX_N);
     return fail(1, "futhark_b200_scan_i32_noalloc: input too long", d);
   }
+  // Visit B of a tile stores while visit A of later tiles still reads: the scan is not safe in place.
+  if (n > 0) {
+    const uintptr_t ib = reinterpret_cast<uintptr_t>(in), ob = reinterpret_cast<uintptr_t>(out);
+    const uintptr_t bytes = (uintptr_t)n * sizeof(int32_t);
+    if (ib < ob + bytes && ob < ib + bytes)
+      return fail(1, "futhark_b200_scan_i32_noalloc: `in` and `out` overlap", "the scan cannot run in place; pass disjoint buffers");
+  }
   int dev = -1;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: cudaGetDevice", cudaGetErrorString(err));
@@ -800,7 +824,7 @@ extern "C" int futhark_b200_scan_i32_noalloc(const int32_t *in, int32_t *out, in
     a.ticket = reinterpret_cast<uint32_t *>(base);
     a.status = reinterpret_cast<uint64_t *>(base + NOALLOC_HEAD);
     a.epoch = epoch; a.failure = failure;
-    a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr;
+    a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr; a.shard_out = nullptr;
     err = launch_stream<K_SCAN_I32>(a, st);
     if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: kernel launch", cudaGetErrorString(err));
   }

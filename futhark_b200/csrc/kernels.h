@@ -19,15 +19,17 @@ cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t 
 // Exclusive scan: out[0] = 0, out[i] = in[0] + ... + in[i-1] (prelude/soacs.fut:212-215).
 cudaError_t launch_exscan_i32(const int32_t *in, int32_t *out, int64_t n, void *scratch,
                               uint32_t epoch, int *failure, cudaStream_t stream);
-// After launch_segscan_f32 on the same scratch: writes the shard summary {f32 bits, flag}.
 // A bounded wait on a status word that is never published: records FAIL_LOOKBACK_TIMEOUT.
 cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls, int *failure, cudaStream_t stream);
-cudaError_t launch_segscan_summary(void *scratch, int64_t n, uint32_t *dst, cudaStream_t stream);
-// Adds the fold of summaries[0..rank) to out[0 .. first segment start).
-cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
-                                       int rank, unsigned long long *d_first, int num_sms, cudaStream_t stream);
+// Flagged segmented scan.  With shard_out != NULL the kernel also leaves the 4-word summary of
+// the array seen as one shard of a longer one: {f32 bits, flag} of its last inclusive prefix, the
+// index of its first 5120-element tile that holds a segment start (all ones if none), 0.
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
-                               void *scratch, uint32_t epoch, int *failure, cudaStream_t stream);
+                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream);
+// Adds the fold of summaries[0..rank) (4 words per shard) to out[0 .. first segment start),
+// the first start being located through summaries[rank].
+cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
+                                       int rank, int num_sms, cudaStream_t stream);
 cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out_true, uint32_t *out_false,
                                int64_t n, int64_t *d_count, void *scratch, uint32_t epoch, int *failure,
                                cudaStream_t stream);

@@ -8,8 +8,9 @@ The reference is single-device; this layer is new.  Per operation:
   scan            local reduce -> all_gather of the shard totals -> local scan started from
                   the sum of the totals of the earlier shards (12 B/element instead of the
                   16 B/element of scan + carry-add)
-  segmented scan  local scan -> all_gather of one (value, has-segment-start) summary per
-                  shard -> the carry is added only to the elements before the shard's first
+  segmented scan  local scan, whose kernel also writes the shard's 16-byte summary (value,
+                  has-segment-start, first tile with a start) -> all_gather of the summaries
+                  -> one kernel adds the carry to the elements before the shard's first
                   segment start
   segmented / row reduce   sharded by whole segments / rows: no exchange
   histogram       local histogram -> all_reduce(SUM | MAX) over the B bins
@@ -65,6 +66,7 @@ class LibLocal:
     def __init__(self, ctx, stream):
         self.ctx, self.stream = ctx, stream
         self.device = torch.device("cuda", ctx.device)
+        self.side = torch.cuda.Stream(device=self.device)
         L = ctx.lib
         vp, pvp = ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)
         L.futhark_b200_reduce_i32_to_device.argtypes = [vp, ctypes.c_uint64, vp]
@@ -73,15 +75,20 @@ class LibLocal:
         L.futhark_b200_segscan_f32_apply_carries.argtypes = [vp, vp, vp, ctypes.c_uint64, ctypes.c_int]
 
     def empty(self, n, dtype):
-        return torch.empty(n, dtype=dtype, device=self.device)
+        """Exchange buffer.  Allocated with the kernels' stream current, so that torch's caching
+        allocator reuses the block only behind the work enqueued on that stream; the second
+        stream, where some collectives run, is recorded as a user as well."""
+        with torch.cuda.stream(self.stream):
+            t = torch.empty(n, dtype=dtype, device=self.device)
+        if getattr(self, "side", None) is not None:
+            t.record_stream(self.side)
+        return t
 
     def collective_stream(self):
         return torch.cuda.stream(self.stream)
 
     def exchange_stream(self):
         """A second stream, ordered after everything enqueued so far on the kernels' stream."""
-        if getattr(self, "side", None) is None:
-            self.side = torch.cuda.Stream(device=self.device)
         self.side.wait_stream(self.stream)
         return torch.cuda.stream(self.side)
 
@@ -127,6 +134,9 @@ class LibLocal:
         pair.free()
         return s, r, s.shape[0], r.shape[0]
 
+    def bmm_f16(self, A, B):
+        return self.ctx.entry_bmm_f16(A, B)
+
 
 class Group:
     """The sharded operations of one rank."""
@@ -138,19 +148,27 @@ class Group:
         self.world = dist.get_world_size(pg)
 
     # -- reduce (+) i32: one value per rank, summed (wrapping) by the collective
-    def reduce_i32(self, xs):
+    def reduce_i32_device(self, xs):
+        """The sum as a one-element tensor in the executor's memory: nothing waits on the host."""
         buf = self.local.empty(1, torch.int32)
         self.local.reduce_i32_into(xs, buf)
         with self.local.collective_stream():
             dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.pg)
+        return buf
+
+    def reduce_i32(self, xs):
+        """The sum as a host scalar (a scalar result is synchronous, as in the C API)."""
+        buf = self.reduce_i32_device(xs)
+        with self.local.collective_stream():
             return int(buf.item())
 
     # -- scan (+) i32: totals first, then one seeded pass
     def scan_i32(self, xs):
         totals = self.local.empty(self.world, torch.int32)
-        self.local.reduce_i32_into(xs, totals[self.rank:self.rank + 1])
+        mine = self.local.empty(1, torch.int32)
+        self.local.reduce_i32_into(xs, mine)
         with self.local.collective_stream():
-            dist.all_gather_into_tensor(totals, totals[self.rank:self.rank + 1].clone(), group=self.pg)
+            dist.all_gather_into_tensor(totals, mine, group=self.pg)
         return self.local.scan_i32_carried(xs, totals, self.rank)
 
     # -- flagged segmented scan (+) f32
@@ -163,25 +181,24 @@ class Group:
         kernels (where the executor has a second stream), so whatever the caller launches
         between the exchange and `segscan_f32_finish` overlaps it.  A collective's kernel takes
         a few CTA slots: a persistent kernel sized to fill the GPU should not be what overlaps it."""
-        summaries = self.local.empty(2 * self.world, torch.int32)
-        mine = summaries[2 * self.rank:2 * self.rank + 2]
+        summaries = self.local.empty(4 * self.world, torch.int32)
+        mine = self.local.empty(4, torch.int32)
         out = self.local.segscan_shard(flags, xs, mine)
-        pending = [out, flags, summaries, False]
+        pending = [out, flags, summaries, False, mine]
         if exchange:
             self.segscan_f32_exchange(pending)
         return pending
 
     def segscan_f32_exchange(self, pending):
-        summaries = pending[2]
-        mine = summaries[2 * self.rank:2 * self.rank + 2]
+        summaries, mine = pending[2], pending[4]
         with self.local.exchange_stream():
-            dist.all_gather_into_tensor(summaries, mine.clone(), group=self.pg)
+            dist.all_gather_into_tensor(summaries, mine, group=self.pg)
         pending[3] = True
 
     def segscan_f32_finish(self, pending):
         if not pending[3]:
             self.segscan_f32_exchange(pending)
-        out, flags, summaries, _ = pending
+        out, flags, summaries = pending[0], pending[1], pending[2]
         self.local.exchange_done()
         self.local.segscan_apply(out, flags, summaries, self.rank)
         return out
@@ -194,6 +211,10 @@ class Group:
             with self.local.collective_stream():
                 dist.all_reduce(t, op=dist.ReduceOp.SUM if op == "add" else dist.ReduceOp.MAX, group=self.pg)
         return out
+
+    # -- contraction: batch-sharded, every rank multiplies its own batches; no exchange
+    def bmm_f16(self, A, B):
+        return self.local.bmm_f16(A, B)
 
     # -- compaction: local result + where it sits in the logical concatenation
     def filter_u32(self, ks):

@@ -358,12 +358,15 @@ int futhark_b200_value_write_mem(const struct futhark_b200_value *v, int binary,
  *  reduce_i32_to_device    writes reduce (+) 0 of the shard to *dst (one i32 on the device)
  *  entry_scan_i32_carried  scan (+) of the shard started from the sum of the num_carries i32
  *                          values at `carries` (the totals of the shards before this one)
- *  entry_segscan_f32_shard the segmented scan of the shard alone, plus its 8-byte summary at
- *                          summary_dst: {f32 bits of the last element, 1 if any segment starts
- *                          in the shard else 0}
- *  segscan_f32_apply_carries  given the summaries of all shards (2 x u32 each, in rank order),
+ *  entry_segscan_f32_shard the segmented scan of the shard alone, plus its 16-byte summary at
+ *                          summary_dst, written by the scan kernel itself: {f32 bits of the last
+ *                          element, 1 if any segment starts in the shard else 0, index of the
+ *                          first 5120-element tile of the shard that holds a segment start (all
+ *                          ones if none), 0}
+ *  segscan_f32_apply_carries  given the summaries of all shards (4 x u32 each, in rank order),
  *                          adds the carry of shards 0..rank-1 to the elements of `out` that
- *                          precede the shard's first segment start */
+ *                          precede the shard's first segment start (one kernel; shard `rank`'s
+ *                          own summary tells it where to look for that start) */
 int futhark_b200_reduce_i32_to_device(struct futhark_context *ctx, CUdeviceptr dst,
                                       const struct futhark_i32_1d *in0);
 int futhark_b200_entry_scan_i32_carried(struct futhark_context *ctx, struct futhark_i32_1d **out0,
@@ -385,7 +388,8 @@ int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct f
  * host program (a latency-bound loop after start-up, say) where a device-wide
  * synchronisation or an out-of-memory failure from cudaMalloc cannot be tolerated.  The
  * caller supplies `in` and `out` (device pointers, 4-byte aligned; 16-byte alignment is
- * faster); the scan's temporaries (a tile counter and one 8-byte status word per tile of
+ * faster; the two ranges must not overlap -- the scan does not work in place, and an
+ * overlapping pair is refused with a non-zero return); the scan's temporaries (a tile counter and one 8-byte status word per tile of
  * 5120 elements) live in a fixed ~103 KiB array inside the library image, which every GPU
  * that loads the library keeps until the process exits.
  *

@@ -3,8 +3,9 @@ not depend on the size (differences of a scan give back its input, a histogram c
 sum of its weights, a partition is a stable permutation, ...) and against independent
 device-side evaluations by torch.  Inputs are made on the device with a seeded generator (the
 distributions of `futhark_b200.datagen`, not its values) and handed to the library as borrowed
-pointers, so each case takes seconds.  The small and medium sizes are compared with the CPU
-oracle element by element in the other test files."""
+pointers, so each case takes seconds.  The three `*_against_the_oracle` cases at the end
+additionally compare configurations 1, 2 and 4 at full size, element by element, with the
+CPU oracle on the workload generator's own inputs."""
 import numpy as np
 import pytest
 import torch
@@ -247,3 +248,46 @@ def test_beyond_2p31_elements(ctx, dev):
     ref2 = sum(float((u[lo:min(lo + step, n)].double() ** 2).sum().item()) for lo in range(0, n, step))
     assert abs(d - ref2) <= 1e-5 * ref2
     ua.free()
+
+
+# ---- full-size configurations against the CPU oracle, element by element ----------------------
+
+def test_config1_scan_reduce_i32_2p26_against_the_oracle(ctx):
+    import oracle
+    from futhark_b200 import datagen
+    xs = datagen.workload_i32(1 << 26)
+    assert np.array_equal(fb.scan_i32(ctx, xs), oracle.scan_i32(xs))
+    assert fb.reduce_i32(ctx, xs) == oracle.reduce_i32(xs)
+
+
+def test_config2_segscan_segreduce_rowsum_against_the_oracle(ctx):
+    import oracle
+    from futhark_b200 import datagen
+    from util import assert_close_l1, seg_abs_prefix
+    n = 1 << 27
+    offsets, flags, xs = datagen.workload_seg_f32(n)
+    got = fb.segscan_f32(ctx, flags, xs)
+    l1 = seg_abs_prefix(flags, xs)
+    assert_close_l1(got, oracle.segscan_f32_seq64(flags, xs), l1, 1e-5, "segscan vs f64, 2^27")
+    assert_close_l1(got, oracle.segscan_f32(flags, xs).astype(np.float64), l1, 2e-5, "segscan vs oracle, 2^27")
+    st = np.flatnonzero(flags)
+    assert np.array_equal(got[st], xs[st])
+    red = fb.segreduce_f32(ctx, offsets, flags, xs)
+    want = oracle.segreduce_f32(offsets, xs)
+    seg_l1 = np.maximum(l1[offsets[1:] - 1], 1e-6)                  # |x| summed over each (non-empty) segment
+    assert red.shape == want.shape
+    assert_close_l1(red, want.astype(np.float64), seg_l1, 2e-5, "segreduce vs oracle, 2^27")
+    del got, l1, red, want
+    rows = datagen.workload_rows_f32(131072, 1024)
+    assert_close_l1(fb.rowsum_f32(ctx, rows), oracle.rowsum_f32(rows).astype(np.float64),
+                    np.abs(rows.astype(np.float64)).sum(axis=1), 2e-5, "rowsum vs oracle")
+
+
+def test_config4_filter_partition_u32_2p28_against_the_oracle(ctx):
+    import oracle
+    from futhark_b200 import datagen
+    ks = datagen.workload_keys_u32(1 << 28)
+    sel, rej = oracle.partition_u32(ks)
+    assert np.array_equal(fb.filter_u32(ctx, ks), sel)
+    s, r = fb.partition_u32(ctx, ks)
+    assert np.array_equal(s, sel) and np.array_equal(r, rej)

@@ -93,6 +93,31 @@ def test_segscan_f32_within_tolerance(ctx, n, mean):
     assert np.array_equal(got[st], xs[st])
 
 
+@pytest.mark.parametrize("n,mean", [(3 * TILE + 17, 256), (1 << 20, 256), (1 << 20, 3), ((1 << 20) + 5, 40000), (1 << 22, 700)])
+def test_segscan_segreduce_bit_exact_on_small_integers(ctx, n, mean):
+    """The reference holds no output values for the flagged scan (`auto output`), so the
+    tolerance tests pin it only within 1e-5.  With small integer values every partial sum
+    is an integer below 2^24: exact in f32 whatever the association, so the definition of
+    the lifted operator alone fixes every output bit, and the kernels must reproduce them."""
+    offsets, flags = datagen.geometric_segments(41, n, mean)
+    xs = datagen.uniform_i32(41, 0, n, -8, 8).astype(np.float32)
+    want = oracle.segscan_f32_seq64(flags, xs)
+    assert np.abs(want).max() < 2 ** 24
+    assert np.array_equal(fb.segscan_f32(ctx, flags, xs), want.astype(np.float32))
+    assert np.array_equal(oracle.segscan_f32(flags, xs), want.astype(np.float32))        # the oracle port as well
+    red = fb.segreduce_f32(ctx, offsets, flags, xs)
+    assert np.array_equal(red, want[offsets[1:] - 1].astype(np.float32))                  # segments here are never empty
+    assert np.array_equal(red, oracle.segreduce_f32(offsets, xs))
+
+
+def test_rowsum_bit_exact_on_small_integers(ctx):
+    for rows, cols in ((1000, 1024), (300, 1000), (7, 40000), (50000, 9)):
+        xss = datagen.uniform_i32(42, 0, rows * cols, -8, 8).astype(np.float32).reshape(rows, cols)
+        want = xss.astype(np.float64).sum(axis=1).astype(np.float32)
+        assert np.array_equal(fb.rowsum_f32(ctx, xss), want)
+        assert np.array_equal(oracle.rowsum_f32(xss), want)
+
+
 def test_segscan_no_flags_is_plain_scan(ctx):
     n = 6 * TILE + 11
     xs = datagen.normal_f32(9, 0, n)

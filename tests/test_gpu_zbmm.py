@@ -53,6 +53,21 @@ def test_bmm_identity_is_exact(ctx):
     assert np.array_equal(got, A.view(np.float16).astype(np.float32))
 
 
+@pytest.mark.parametrize("nb,m,k,n", [(1, 128, 64, 256), (2, 256, 1024, 512), (3, 200, 72, 264), (4, 1024, 1024, 1024)])
+def test_bmm_bit_exact_on_small_integers(ctx, nb, m, k, n):
+    """The reference has no f16-input matmul test with values.  Small integer inputs
+    (|a|, |b| <= 4, k <= 1024) make every product and every partial sum an integer below 2^24,
+    exact in f32 in any summation order: the tensor-core result must equal the sequential
+    oracle bit for bit, not merely within the workload's 1e-2."""
+    rng = np.random.default_rng(nb * 1000 + k)
+    A = rng.integers(-4, 5, size=(nb, m, k)).astype(np.float16)
+    B = rng.integers(-4, 5, size=(nb, k, n)).astype(np.float16)
+    got = fb.bmm_f16(ctx, A, B)
+    want = oracle.bmm_f16(A, B)
+    assert np.array_equal(want, np.matmul(A.astype(np.float64), B.astype(np.float64)).astype(np.float32))
+    assert np.array_equal(got, want)
+
+
 def test_bmm_size_mismatch(ctx):
     a = ctx.new("f16_3d", np.zeros((2, 8, 8), np.uint16))
     b = ctx.new("f16_3d", np.zeros((2, 16, 8), np.uint16))

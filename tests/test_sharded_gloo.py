@@ -46,14 +46,22 @@ class NumpyLocal:
         last = out[-1] if len(out) else np.float32(0)
         slot[0] = int(np.float32(last).view(np.int32))
         slot[1] = int(flags.any())
+        nz = np.flatnonzero(flags)
+        slot[2] = int(nz[0]) // 5120 if len(nz) else -1      # first tile with a segment start (all ones if none)
+        slot[3] = 0
         return out
 
     def segscan_apply(self, out, flags, summaries, rank):
-        s = summaries.numpy().reshape(-1, 2)
-        pairs = [(np.int32(v).view(np.float32), int(f)) for v, f in s]
+        s = summaries.numpy().reshape(-1, 4)
+        pairs = [(np.int32(v).view(np.float32), int(f)) for v, f, _, _ in s]
         carry, _ = sharded.fold_summaries(pairs, rank)
-        nz = np.flatnonzero(flags)
-        first = int(nz[0]) if len(nz) else len(out)
+        # like the kernel: the shard's own summary names the tile, the flags of that tile the position
+        tile = int(s[rank][2])
+        if tile < 0:
+            first = len(out)
+        else:
+            nz = np.flatnonzero(flags[tile * 5120:(tile + 1) * 5120])
+            first = tile * 5120 + int(nz[0])
         out[:first] = carry + out[:first]
 
     def hist(self, op, B, bins, ws):
@@ -69,6 +77,9 @@ class NumpyLocal:
     def partition(self, ks):
         s, r = oracle.partition_u32(ks)
         return s, r, len(s), len(r)
+
+    def bmm_f16(self, A, B):
+        return oracle.bmm_f16(A, B)
 
 
 def _free_port():
@@ -108,6 +119,10 @@ def _worker(rank, world, port, q):
         # segment-aligned split for the reductions
         offsets, flags = datagen.geometric_segments(11, n, 256)
         res["segsplit"] = sharded.split_segments(offsets, world, rank)
+        # contraction: whole batches per shard
+        A, B = datagen.workload_bmm(5, 16, 8, 24)
+        blo, bhi = sharded.shard_bounds(5, world, rank)
+        res["bmm"] = g.bmm_f16(A[blo:bhi], B[blo:bhi])
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
@@ -153,6 +168,8 @@ def test_sharded_ops_match_single_array(world):
         out[ro:ro + len(rj)] = rj
     assert np.array_equal(fout, sel)
     assert np.array_equal(out, np.concatenate([sel, rej]))
+    A, B = datagen.workload_bmm(5, 16, 8, 24)
+    assert np.array_equal(np.concatenate([got[r]["bmm"] for r in range(world)]), oracle.bmm_f16(A, B))
     # the segment split covers every segment exactly once, in order
     offsets, _ = datagen.geometric_segments(11, n, 256)
     cuts = [got[r]["segsplit"] for r in range(world)]
