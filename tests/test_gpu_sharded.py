@@ -61,6 +61,10 @@ def _worker(rank, world, port, q):
         s, r, so, ro, tot = g.partition_u32(ka)
         res["partition"] = (s.values(), r.values(), so, ro, tot)
         s.free(); r.free(); ka.free()
+        A, B = datagen.workload_bmm(2 * world + 1, 128, 64, 256)
+        blo, bhi = sharded.shard_bounds(2 * world + 1, world, rank)
+        Aa, Ba = ctx.new("f16_3d", A[blo:bhi]), ctx.new("f16_3d", B[blo:bhi])
+        o = g.bmm_f16(Aa, Ba); res["bmm"] = o.values(); o.free(); Aa.free(); Ba.free()
         ctx.sync()
         ctx.close()
         q.put((rank, res))
@@ -99,6 +103,11 @@ def test_sharded_ops_on_gpus():
     for r in range(world):
         assert np.array_equal(got[r]["hist_add"], oracle.hist_add_i32(1000, bins, wi))
         assert np.array_equal(got[r]["hist_max"], oracle.hist_max_f32(1000, bins, wf))
+    A, B = datagen.workload_bmm(2 * world + 1, 128, 64, 256)
+    whole = np.concatenate([got[r]["bmm"] for r in range(world)])
+    want = oracle.bmm_f16(A, B)
+    l1 = np.matmul(np.abs(A.view(np.float16).astype(np.float32)), np.abs(B.view(np.float16).astype(np.float32)))
+    assert (np.abs(whole - want) <= 1e-4 * np.maximum(l1, 1e-6)).all()
     ks = datagen.workload_keys_u32(n)
     sel, rej = oracle.partition_u32(ks)
     out = np.zeros(n, dtype=np.uint32)
