@@ -221,7 +221,8 @@ int futhark_entry_segreduce_f32(struct futhark_context *ctx, struct futhark_f32_
   if (nseg > 0) {
     LaunchScope ls(ctx, "segreduce_f32.segred", PROV("map (reduce (+) 0) over offsets"), "{" + kv("n", n) + "," + kv("segments", nseg) + "}");
     rc = fb_cuda_check(ctx, fb::launch_segreduce_f32(dptr<int64_t>(in0->mem), nseg, dptr<float>(in2->mem), n, dptr<float>(out->mem),
-                                                     ctx->num_sms, ctx->stream), "segreduce_f32");
+                                                     ctx->reduce_scratch, ctx->d_failure, ctx->num_sms, ctx->stream), "segreduce_f32");
+    ctx->failure_is_an_option = true;
     if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
   }
   *out0 = out;

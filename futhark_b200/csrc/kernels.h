@@ -41,8 +41,9 @@ cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void
                               cudaStream_t stream);
 cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float *out, int num_sms,
                               cudaStream_t stream);
+// out[s] = sum of xs[offsets[s] .. offsets[s+1]) for s < nseg (offsets ascending, clamped to [0, n]); `scratch` as above.
 cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
-                                 int num_sms, cudaStream_t stream);
+                                 void *scratch, int *failure, int num_sms, cudaStream_t stream);
 
 // ---- fused redomaps (k_redomap.cu; the kernel template is redomap.cuh) -----------------------
 // `scratch` as for the reductions.  mss: d_out4 receives the operator's 4-tuple (best segment
