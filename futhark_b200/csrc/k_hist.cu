@@ -167,7 +167,16 @@ hist_smem_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ 
 // combining equal bins across the warp first (match.any + warp reduction, 10x slower); the four
 // most frequent bins of a CTA combined in registers (no faster, and slower for uniform
 // indices); the CTAs of a group paced by a cluster barrier (Zipf 12 % faster, uniform max 9 %
-// slower, three and four ranges slower).
+// slower, three and four ranges slower); the CTAs of a group paced through progress counters
+// in global memory, a CTA waiting only when it is more than 12-16 rounds ahead (uniform AND
+// Zipf 3.4x - 6.5x slower: in this kernel a global load or store queues behind the SM's
+// outstanding input requests for several microseconds, during which the grid streams ~50 MB,
+// so a counter is that stale when it is read, which is most of what L2 can keep for the slower
+// CTA; and a check that waits for its load drains the CTA's copy pipeline each time).  Cutting
+// the bins by residue (bin mod P) instead of into contiguous ranges does not change the
+// picture for this workload: the rank -> bin permutation already scatters the frequent bins
+// over both ranges, and what makes one CTA slower is the single most frequent bin (12 % of
+// all updates under Zipf 1.1), which lands in one CTA whatever the split.
 constexpr int HIST_STAGES = 3;
 constexpr int HIST_STAGE_BYTES = HIST_THREADS * 32;       // 16 bytes of indices + 16 bytes of weights per thread
 
