@@ -28,11 +28,15 @@ ARRAY_TYPES = {
     "f32_1d": (np.float32, 1, ctypes.c_float),
     "bool_1d": (np.bool_, 1, ctypes.c_bool),
     "f32_2d": (np.float32, 2, ctypes.c_float),
+    "i32_2d": (np.int32, 2, ctypes.c_int32),
+    "i64_2d": (np.int64, 2, ctypes.c_int64),
+    "f64_1d": (np.float64, 1, ctypes.c_double),
     "f32_3d": (np.float32, 3, ctypes.c_float),
     "f16_3d": (np.uint16, 3, ctypes.c_uint16),
 }
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
+TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
 
 _lib = None
 
@@ -172,6 +176,18 @@ def load():
     L.futhark_entry_exscan_i32.argtypes = [vp, pvp, vp]
     L.futhark_entry_dotprod_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_float), vp, vp]
     L.futhark_entry_prod_of_sums_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp, vp]
+    for name in ("scan_max_i32", "segscan_rows_i32", "scanomap_steps_i32", "filter_pos_i32", "partition2_i32"):
+        getattr(L, "futhark_entry_" + name).argtypes = [vp, pvp, vp]
+    L.futhark_entry_filter_by_flag_i32.argtypes = [vp, pvp, vp, vp]
+    for name in ("and_i32", "or_i32", "xor_i32", "mul_i32"):
+        getattr(L, "futhark_entry_hist_" + name).argtypes = [vp, pvp, i64, vp, vp]
+    for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32"):
+        getattr(L, "futhark_entry_reduce_by_index_" + name).argtypes = [vp, pvp, vp, vp, vp]
+    L.futhark_entry_hist_rows_add_i32.argtypes = [vp, pvp, i64, vp, vp]
+    L.futhark_entry_reduce_by_index_2d_add_i32.argtypes = [vp, pvp, vp, vp, vp, vp]
+    for i in range(3):
+        getattr(L, "futhark_project_%s_%d" % (TRIPLE, i)).argtypes = [vp, pvp, vp]
+    getattr(L, "futhark_free_" + TRIPLE).argtypes = [vp, vp]
     L.futhark_b200_value_error.restype = ctypes.c_char_p
     L.futhark_b200_value_read_mem.argtypes = [vp, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t), ctypes.c_char_p, ci, ctypes.POINTER(HostValue)]
     L.futhark_b200_value_write_mem.argtypes = [ctypes.POINTER(HostValue), ci, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
@@ -409,6 +425,20 @@ class Context:
     def entry_hist_max_f32(self, B, bins, ws):
         return self._entry_arr("hist_max_f32", "f32_1d", int(B), bins.ptr, ws.ptr)
 
+    def entry_hist_op(self, op, B, bins, ws):
+        """hist <op> <neutral> B (map i64.i32 bins) ws for op in and_i32, or_i32, xor_i32, mul_i32."""
+        return self._entry_arr("hist_" + op, "i32_1d", int(B), bins.ptr, ws.ptr)
+
+    def entry_reduce_by_index(self, op, dest, bins, ws):
+        """reduce_by_index dest <op> <neutral> (map i64.i32 bins) ws for op in min_i32, max_i32, min_u32, max_u32, add_f32."""
+        return self._entry_arr("reduce_by_index_" + op, op[-3:] + "_1d", dest.ptr, bins.ptr, ws.ptr)
+
+    def entry_hist_rows_add_i32(self, m, iss, vss):
+        return self._entry_arr("hist_rows_add_i32", "i32_2d", int(m), iss.ptr, vss.ptr)
+
+    def entry_reduce_by_index_2d_add_i32(self, dest, is_, js, vs):
+        return self._entry_arr("reduce_by_index_2d_add_i32", "i32_2d", dest.ptr, is_.ptr, js.ptr, vs.ptr)
+
     def entry_filter_u32(self, ks):
         return self._entry_arr("filter_u32", "u32_1d", ks.ptr)
 
@@ -436,6 +466,33 @@ class Context:
 
     def entry_exscan_i32(self, xs):
         return self._entry_arr("exscan_i32", "i32_1d", xs.ptr)
+
+    def entry_scan_max_i32(self, xs):
+        return self._entry_arr("scan_max_i32", "i32_1d", xs.ptr)
+
+    def entry_segscan_rows_i32(self, xss):
+        return self._entry_arr("segscan_rows_i32", "i32_2d", xss.ptr)
+
+    def entry_scanomap_steps_i32(self, xs):
+        return self._entry_arr("scanomap_steps_i32", "i32_1d", xs.ptr)
+
+    def entry_filter_pos_i32(self, xs):
+        return self._entry_arr("filter_pos_i32", "i32_1d", xs.ptr)
+
+    def entry_filter_by_flag_i32(self, xs, keep):
+        return self._entry_arr("filter_by_flag_i32", "i32_1d", xs.ptr, keep.ptr)
+
+    def entry_partition2_i32(self, xs):
+        """The three groups as arrays (the opaque triple is projected and freed)."""
+        obj = ctypes.c_void_p()
+        self._check(self.lib.futhark_entry_partition2_i32(self.ptr, ctypes.byref(obj), xs.ptr))
+        parts = []
+        for i in range(3):
+            out = ctypes.c_void_p()
+            self._check(getattr(self.lib, "futhark_project_%s_%d" % (TRIPLE, i))(self.ptr, ctypes.byref(out), obj))
+            parts.append(Array(self, "i32_1d", out.value))
+        self._check(getattr(self.lib, "futhark_free_" + TRIPLE)(self.ptr, obj))
+        return parts
 
     def entry_mss_i32(self, xs):
         out = ctypes.c_int32()
@@ -587,3 +644,53 @@ def transpose_f32(ctx, xs):
     if xs.ndim == 2:
         return _run(ctx, [("f32_2d", xs)], ctx.entry_transpose_f32)
     return _run(ctx, [("f32_3d", xs)], ctx.entry_transpose_f32_3d)
+
+
+def scan_max_i32(ctx, xs):
+    return _run(ctx, [("i32_1d", xs)], ctx.entry_scan_max_i32)
+
+
+def segscan_rows_i32(ctx, xss):
+    return _run(ctx, [("i32_2d", xss)], ctx.entry_segscan_rows_i32)
+
+
+def scanomap_steps_i32(ctx, xs):
+    return _run(ctx, [("i32_1d", xs)], ctx.entry_scanomap_steps_i32)
+
+
+def filter_pos_i32(ctx, xs):
+    return _run(ctx, [("i32_1d", xs)], ctx.entry_filter_pos_i32)
+
+
+def filter_by_flag_i32(ctx, xs, keep):
+    return _run(ctx, [("i32_1d", xs), ("bool_1d", keep)], ctx.entry_filter_by_flag_i32)
+
+
+def partition2_i32(ctx, xs):
+    a = ctx.new("i32_1d", xs)
+    try:
+        parts = ctx.entry_partition2_i32(a)
+        try:
+            return tuple(p.values() for p in parts)
+        finally:
+            for p in parts:
+                p.free()
+    finally:
+        a.free()
+
+
+def hist_op(ctx, op, B, bins, ws):
+    return _run(ctx, [("i32_1d", bins), ("i32_1d", ws)], lambda b, w: ctx.entry_hist_op(op, B, b, w))
+
+
+def reduce_by_index(ctx, op, dest, bins, ws):
+    t = op[-3:] + "_1d"
+    return _run(ctx, [(t, dest), ("i32_1d", bins), (t, ws)], lambda d, b, w: ctx.entry_reduce_by_index(op, d, b, w))
+
+
+def hist_rows_add_i32(ctx, m, iss, vss):
+    return _run(ctx, [("i32_2d", iss), ("i32_2d", vss)], lambda i, v: ctx.entry_hist_rows_add_i32(m, i, v))
+
+
+def reduce_by_index_2d_add_i32(ctx, dest, is_, js, vs):
+    return _run(ctx, [("i32_2d", dest), ("i64_1d", is_), ("i64_1d", js), ("i32_1d", vs)], ctx.entry_reduce_by_index_2d_add_i32)

@@ -245,9 +245,10 @@ int futhark_entry_rowsum_f32(struct futhark_context *ctx, struct futhark_f32_1d 
   return FUTHARK_SUCCESS;
 }
 
-static int hist_common(futhark_context *ctx, int op, void **out_arr, int64_t B, const futhark_i32_1d *is, const memblock_device &ws,
-                       int64_t ws_len, const char *name) {
-  const int64_t n = is->shape[0];
+// hist op ne B is ws (dest == NULL) or reduce_by_index dest op ne is ws: any operator of fb::HistOpKind
+// over 32-bit values.  `is_raw` are the bin indices as i32 on the device.
+static int hist_launch(futhark_context *ctx, int op, void **out_arr, int64_t B, const memblock_device *dest, const int32_t *is_raw,
+                       int64_t n, const memblock_device &ws, int64_t ws_len, const char *name) {
   if (ws_len != n) return bad_sizes(ctx);
   if (B < 0) {
     // a negative size is a program error in the reference (array construction with a negative length)
@@ -255,16 +256,22 @@ static int hist_common(futhark_context *ctx, int op, void **out_arr, int64_t B, 
     return FUTHARK_PROGRAM_ERROR;
   }
   int rc;
-  futhark_i32_1d *out = make_1d<futhark_i32_1d>(ctx, B, 4, name, &rc);   // same layout for the f32 result
+  futhark_i32_1d *out = make_1d<futhark_i32_1d>(ctx, B, 4, name, &rc);   // the same layout for every 4-byte element type
   if (out == nullptr) return rc;
   if (B > 0) {
     LaunchScope ls(ctx, name, PROV("hist op ne B (map i64.i32 is) ws"), "{" + kv("n", n) + "," + kv("bins", B) + "}");
-    ctx->launch_count += (op == 1 ? 2 : 1);   // the fill (and, for max, the key decode) besides the histogram kernel
-    rc = fb_cuda_check(ctx, fb::launch_hist(op, B, dptr<int32_t>(is->mem), dptr<void>(ws), n, dptr<void>(out->mem), ctx->num_sms, ctx->stream), name);
+    ctx->launch_count += (op == fb::HOP_MAX_F32 ? 2 : 1);   // the fill (and, for the f32 max, the key decode) besides the histogram kernel
+    rc = fb_cuda_check(ctx, fb::launch_hist(op, B, is_raw, dptr<void>(ws), n, dptr<void>(out->mem), dest ? dptr<void>(*dest) : nullptr,
+                                            ctx->num_sms, ctx->stream), name);
     if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
   }
   *out_arr = out;
   return FUTHARK_SUCCESS;
+}
+
+static int hist_common(futhark_context *ctx, int op, void **out_arr, int64_t B, const futhark_i32_1d *is, const memblock_device &ws,
+                       int64_t ws_len, const char *name) {
+  return hist_launch(ctx, op, out_arr, B, nullptr, dptr<int32_t>(is->mem), is->shape[0], ws, ws_len, name);
 }
 
 int futhark_entry_hist_add_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const int64_t in0, const struct futhark_i32_1d *in1,
@@ -272,7 +279,7 @@ int futhark_entry_hist_add_i32(struct futhark_context *ctx, struct futhark_i32_1
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
   void *o = nullptr;
-  int rc = hist_common(ctx, 0, &o, in0, in1, in2->mem, in2->shape[0], "hist_add_i32.seghist");
+  int rc = hist_common(ctx, fb::HOP_ADD_I32, &o, in0, in1, in2->mem, in2->shape[0], "hist_add_i32.seghist");
   if (rc == 0) *out0 = (futhark_i32_1d *)o;
   return rc;
 }
@@ -282,34 +289,134 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
   void *o = nullptr;
-  int rc = hist_common(ctx, 1, &o, in0, in1, in2->mem, in2->shape[0], "hist_max_f32.seghist");
+  int rc = hist_common(ctx, fb::HOP_MAX_F32, &o, in0, in1, in2->mem, in2->shape[0], "hist_max_f32.seghist");
   if (rc == 0) *out0 = (futhark_f32_1d *)o;   // futhark_i32_1d and futhark_f32_1d have the same layout
   return rc;
 }
 
-// Shared by filter and partition: one look-back pass, then the count is read back so the
-// result shapes can be filled in.
-static int compact_common(futhark_context *ctx, bool partition, const futhark_u32_1d *in, futhark_u32_1d **sel, futhark_u32_1d **rej) {
-  const int64_t n = in->shape[0];
-  if (n >= (1ll << 31)) {
-    fb_set_error(ctx, "filter/partition: %lld elements exceed the supported 2^31-1 per call.", (long long)n);
+// ---- the histogram kernels under other operators (tests/hist/{and,or,xor,min,max,f32}.fut) --------
+#define FB_HIST_ENTRY(NAME, OP, ARR)                                                                                          \
+  int futhark_entry_hist_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0, const int64_t in0,                   \
+                                const struct futhark_i32_1d *in1, const struct futhark_##ARR *in2) {                         \
+    if (!ctx->ready) return not_ready(ctx);                                                                                   \
+    CtxGuard g(ctx);                                                                                                          \
+    void *o = nullptr;                                                                                                        \
+    int rc = hist_common(ctx, OP, &o, in0, in1, in2->mem, in2->shape[0], "hist_" #NAME ".seghist");                           \
+    if (rc == 0) *out0 = (futhark_##ARR *)o;                                                                                  \
+    return rc;                                                                                                                \
+  }
+FB_HIST_ENTRY(and_i32, fb::HOP_AND_I32, i32_1d)
+FB_HIST_ENTRY(or_i32, fb::HOP_OR_I32, i32_1d)
+FB_HIST_ENTRY(xor_i32, fb::HOP_XOR_I32, i32_1d)
+FB_HIST_ENTRY(mul_i32, fb::HOP_MUL_I32, i32_1d)
+
+// reduce_by_index dest op ne (map i64.i32 is) vs: the result starts as a copy of dest
+#define FB_RBI_ENTRY(NAME, OP, ARR)                                                                                           \
+  int futhark_entry_reduce_by_index_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0,                          \
+                                           const struct futhark_##ARR *in0, const struct futhark_i32_1d *in1,                 \
+                                           const struct futhark_##ARR *in2) {                                                 \
+    if (!ctx->ready) return not_ready(ctx);                                                                                   \
+    CtxGuard g(ctx);                                                                                                          \
+    void *o = nullptr;                                                                                                        \
+    int rc = hist_launch(ctx, OP, &o, in0->shape[0], &in0->mem, dptr<int32_t>(in1->mem), in1->shape[0], in2->mem,              \
+                         in2->shape[0], "reduce_by_index_" #NAME ".seghist");                                                 \
+    if (rc == 0) *out0 = (futhark_##ARR *)o;                                                                                  \
+    return rc;                                                                                                                \
+  }
+FB_RBI_ENTRY(min_i32, fb::HOP_MIN_I32, i32_1d)
+FB_RBI_ENTRY(max_i32, fb::HOP_MAX_I32, i32_1d)
+FB_RBI_ENTRY(min_u32, fb::HOP_MIN_U32, u32_1d)
+FB_RBI_ENTRY(max_u32, fb::HOP_MAX_U32, u32_1d)
+FB_RBI_ENTRY(add_f32, fb::HOP_ADD_F32, f32_1d)
+
+// map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss (tests/hist/segmented.fut: a SegHist with a
+// segment dimension, SegHist.hs:97-148): one histogram over rows * m bins whose index carries the row.
+int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const int64_t in0,
+                                    const struct futhark_i32_2d *in1, const struct futhark_i32_2d *in2) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t rows = in1->shape[0], cols = in1->shape[1], m = in0;
+  if (in2->shape[0] != rows || in2->shape[1] != cols) return bad_sizes(ctx);
+  if (m < 0) { fb_set_error(ctx, "Error: negative histogram size %lld.\n", (long long)m); return FUTHARK_PROGRAM_ERROR; }
+  if (rows * m >= (1ll << 31)) { fb_set_error(ctx, "hist_rows_add_i32: %lld bins in all exceed 2^31-1.", (long long)(rows * m)); return 1; }
+  memblock_device flat;
+  int rc = fb_alloc(ctx, (size_t)(rows * cols) * 4, "hist_rows.flat_index", &flat);
+  if (rc != 0) return rc;
+  void *o = nullptr;
+  ctx->launch_count++;
+  rc = fb_cuda_check(ctx, fb::launch_flatten_rows_index(dptr<int32_t>(in1->mem), rows * cols, cols, m, dptr<int32_t>(flat), ctx->num_sms, ctx->stream),
+                     "flatten_rows_index");
+  if (rc == 0) rc = hist_launch(ctx, fb::HOP_ADD_I32, &o, rows * m, nullptr, dptr<int32_t>(flat), rows * cols, in2->mem, rows * cols,
+                                "hist_rows_add_i32.seghist");
+  fb_unref(ctx, &flat);
+  if (rc != 0) return rc;
+  futhark_i32_1d *h = (futhark_i32_1d *)o;
+  futhark_i32_2d *out = (futhark_i32_2d *)malloc(sizeof(futhark_i32_2d));
+  if (out == nullptr) { fb_unref(ctx, &h->mem); free(h); return 1; }
+  out->mem = h->mem; out->shape[0] = rows; out->shape[1] = m;
+  free(h);
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+// reduce_by_index_2d dest (+) 0 (zip is js) vs (prelude/soacs.fut:149-152; tests/hist/hist2d.fut).
+int futhark_entry_reduce_by_index_2d_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const struct futhark_i32_2d *in0,
+                                             const struct futhark_i64_1d *in1, const struct futhark_i64_1d *in2,
+                                             const struct futhark_i32_1d *in3) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t N = in0->shape[0], M = in0->shape[1], n = in1->shape[0];
+  if (in2->shape[0] != n || in3->shape[0] != n) return bad_sizes(ctx);
+  if (N * M >= (1ll << 31)) { fb_set_error(ctx, "reduce_by_index_2d_add_i32: %lld bins exceed 2^31-1.", (long long)(N * M)); return 1; }
+  memblock_device flat;
+  int rc = fb_alloc(ctx, (size_t)n * 4, "reduce_by_index_2d.flat_index", &flat);
+  if (rc != 0) return rc;
+  void *o = nullptr;
+  ctx->launch_count++;
+  rc = fb_cuda_check(ctx, fb::launch_flatten_2d_index(dptr<int64_t>(in1->mem), dptr<int64_t>(in2->mem), n, N, M, dptr<int32_t>(flat), ctx->num_sms,
+                                                      ctx->stream), "flatten_2d_index");
+  if (rc == 0) rc = hist_launch(ctx, fb::HOP_ADD_I32, &o, N * M, &in0->mem, dptr<int32_t>(flat), n, in3->mem, n, "reduce_by_index_2d_add_i32.seghist");
+  fb_unref(ctx, &flat);
+  if (rc != 0) return rc;
+  futhark_i32_1d *h = (futhark_i32_1d *)o;
+  futhark_i32_2d *out = (futhark_i32_2d *)malloc(sizeof(futhark_i32_2d));
+  if (out == nullptr) { fb_unref(ctx, &h->mem); free(h); return 1; }
+  out->mem = h->mem; out->shape[0] = N; out->shape[1] = M;
+  free(h);
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+// ---- compaction entry points -----------------------------------------------------------------------
+// Shared by every filter and partition: one look-back pass per 2^30 keys, then the count is read back
+// so the result shapes can be filled in.  ARR is any one-dimensional array struct of 4-byte elements.
+}  // extern "C"
+template <typename ARR>
+static int compact_common(futhark_context *ctx, int which, bool partition, const char *name, const memblock_device &in, int64_t n,
+                          const uint8_t *flags, ARR **sel, ARR **rej) {
+  const int pieces = fb::compact_pieces_needed(n);
+  if (pieces > 64) {
+    fb_set_error(ctx, "filter/partition: %lld elements exceed the supported 2^36 per call.", (long long)n);
     return 1;
   }
   int rc;
-  futhark_u32_1d *t = make_1d<futhark_u32_1d>(ctx, n, 4, partition ? "partition_u32.selected" : "filter_u32.out", &rc);
+  ARR *t = make_1d<ARR>(ctx, n, 4, name, &rc);
   if (t == nullptr) return rc;
-  futhark_u32_1d *f = nullptr;
+  ARR *f = nullptr;
   if (partition) {
-    f = make_1d<futhark_u32_1d>(ctx, n, 4, "partition_u32.rejected", &rc);
+    f = make_1d<ARR>(ctx, n, 4, name, &rc);
     if (f == nullptr) { fb_unref(ctx, &t->mem); free(t); return rc; }
   }
-  rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(n));
+  const int64_t piece_n = n < ((int64_t)1 << 30) ? n : ((int64_t)1 << 30);
+  rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(piece_n));
   if (rc == 0) {
-    LaunchScope ls(ctx, partition ? "partition_u32.segscan" : "filter_u32.segscan", PROV("scan (+) of predicate flags with scatter post-op"),
-                   "{" + kv("n", n) + "}");
-    rc = fb_cuda_check(ctx, fb::launch_compact_u32(partition, dptr<uint32_t>(in->mem), dptr<uint32_t>(t->mem), f ? dptr<uint32_t>(f->mem) : nullptr,
-                                                   n, ctx->d_scalar, ctx->lookback_scratch, fb_next_epoch(ctx), ctx->d_failure, ctx->stream),
-                       "compact_u32");
+    LaunchScope ls(ctx, name, PROV("scan (+) of predicate flags with scatter post-op"), "{" + kv("n", n) + "}");
+    uint32_t epochs[64];
+    for (int i = 0; i < pieces; i++) epochs[i] = fb_next_epoch(ctx);
+    ctx->launch_count += pieces - 1;
+    rc = fb_cuda_check(ctx, fb::launch_compact(which, dptr<void>(in), flags, dptr<void>(t->mem), f ? dptr<void>(f->mem) : nullptr,
+                                               n, ctx->d_scalar, ctx->lookback_scratch, epochs, ctx->d_failure, ctx->stream),
+                       "compact");
     ctx->failure_is_an_option = true;
   }
   if (rc == 0) rc = fb_cuda_check(ctx, cudaMemcpyAsync(ctx->h_scalar, ctx->d_scalar, sizeof(int64_t), cudaMemcpyDeviceToHost, ctx->stream), "count read");
@@ -331,12 +438,13 @@ static int compact_common(futhark_context *ctx, bool partition, const futhark_u3
   if (partition) { f->shape[0] = n - count; *rej = f; }
   return FUTHARK_SUCCESS;
 }
+extern "C" {
 
 int futhark_entry_filter_u32(struct futhark_context *ctx, struct futhark_u32_1d **out0, const struct futhark_u32_1d *in0) {
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
   futhark_u32_1d *sel = nullptr;
-  int rc = compact_common(ctx, false, in0, &sel, nullptr);
+  int rc = compact_common<futhark_u32_1d>(ctx, fb::COMPACT_FILTER_LOW3_U32, false, "filter_u32.segscan", in0->mem, in0->shape[0], nullptr, &sel, nullptr);
   if (rc == 0) *out0 = sel;
   return rc;
 }
@@ -346,7 +454,7 @@ int futhark_entry_partition_u32(struct futhark_context *ctx, struct futhark_opaq
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
   futhark_u32_1d *sel = nullptr, *rej = nullptr;
-  int rc = compact_common(ctx, true, in0, &sel, &rej);
+  int rc = compact_common<futhark_u32_1d>(ctx, fb::COMPACT_PARTITION_LOW3_U32, true, "partition_u32.segscan", in0->mem, in0->shape[0], nullptr, &sel, &rej);
   if (rc != 0) return rc;
   auto *p = (futhark_opaque_tup2_arr1d_u32_arr1d_u32 *)malloc(sizeof(futhark_opaque_tup2_arr1d_u32_arr1d_u32));
   if (p == nullptr) return 1;
@@ -354,6 +462,141 @@ int futhark_entry_partition_u32(struct futhark_context *ctx, struct futhark_opaq
   p->v1 = rej;
   *out0 = p;
   return FUTHARK_SUCCESS;
+}
+
+// filter (0 <) xs (tests/soacs/filter1.fut): the compaction kernel under another predicate.
+int futhark_entry_filter_pos_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  futhark_i32_1d *sel = nullptr;
+  int rc = compact_common<futhark_i32_1d>(ctx, fb::COMPACT_FILTER_POS_I32, false, "filter_pos_i32.segscan", in0->mem, in0->shape[0], nullptr, &sel, nullptr);
+  if (rc == 0) *out0 = sel;
+  return rc;
+}
+
+// (filter (.1) (zip xs keep)).0 (tests/soacs/filter3.fut): the predicate reads a second array.
+int futhark_entry_filter_by_flag_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_1d *in0,
+                                     const struct futhark_bool_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  if (in1->shape[0] != in0->shape[0]) return bad_sizes(ctx);
+  futhark_i32_1d *sel = nullptr;
+  int rc = compact_common<futhark_i32_1d>(ctx, fb::COMPACT_FILTER_BY_FLAG_I32, false, "filter_by_flag_i32.segscan", in0->mem, in0->shape[0],
+                                          dptr<uint8_t>(in1->mem), &sel, nullptr);
+  if (rc == 0) *out0 = sel;
+  return rc;
+}
+
+// partition2 (\x -> x % 2 == 0) (\x -> x % 3 == 0) xs (tests/soacs/partition1.fut; prelude/soacs.fut:293-323):
+// a partition by the first predicate, then a partition of what it rejected by the second.  All
+// three groups keep the original order.
+int futhark_entry_partition2_i32(struct futhark_context *ctx, struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **out0,
+                                 const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  futhark_i32_1d *c0 = nullptr, *rest = nullptr, *c1 = nullptr, *c2 = nullptr;
+  int rc = compact_common<futhark_i32_1d>(ctx, fb::COMPACT_PARTITION_EVEN_I32, true, "partition2_i32.segscan", in0->mem, in0->shape[0], nullptr, &c0, &rest);
+  if (rc != 0) return rc;
+  rc = compact_common<futhark_i32_1d>(ctx, fb::COMPACT_PARTITION_DIV3_I32, true, "partition2_i32.segscan", rest->mem, rest->shape[0], nullptr, &c1, &c2);
+  fb_unref(ctx, &rest->mem); free(rest);
+  if (rc != 0) { fb_unref(ctx, &c0->mem); free(c0); return rc; }
+  auto *p = (futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *)malloc(sizeof(futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32));
+  if (p == nullptr) return 1;
+  p->v[0] = c0; p->v[1] = c1; p->v[2] = c2;
+  *out0 = p;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_free_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(struct futhark_context *ctx, struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj) {
+  if (obj == nullptr) return 0;
+  for (int i = 0; i < 3; i++) futhark_free_i32_1d(ctx, obj->v[i]);
+  free(obj);
+  return 0;
+}
+
+static int project_tup3(futhark_context *ctx, futhark_i32_1d **out, const futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj, int i) {
+  CtxGuard g(ctx);
+  futhark_i32_1d *a = (futhark_i32_1d *)malloc(sizeof(futhark_i32_1d));
+  if (a == nullptr) return 1;
+  *a = *obj->v[i];
+  fb_ref(&a->mem);          // the projection shares the block (docs/c-api.rst:383-391)
+  *out = a;
+  return 0;
+}
+int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_0(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                                const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj) { return project_tup3(ctx, out, obj, 0); }
+int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                                const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj) { return project_tup3(ctx, out, obj, 1); }
+int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_2(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                                const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj) { return project_tup3(ctx, out, obj, 2); }
+
+// ---- scans under other specifications of the single-pass kernel -------------------------------------
+}  // extern "C"
+template <typename ARR>
+static int scan_like(futhark_context *ctx, ARR **out0, const ARR *in0, int64_t n, const char *name, const char *prov,
+                     cudaError_t (*launch)(futhark_context *, const ARR *, ARR *, int64_t)) {
+  ARR *out = (ARR *)malloc(sizeof(ARR));
+  if (out == nullptr) return 1;
+  *out = *in0;                                   // same shape
+  int rc = fb_alloc(ctx, (size_t)n * 4, name, &out->mem);
+  if (rc != 0) { free(out); return rc; }
+  if (n > 0) {
+    rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(n));
+    if (rc == 0) {
+      LaunchScope ls(ctx, name, prov, "{" + kv("n", n) + "}");
+      rc = fb_cuda_check(ctx, launch(ctx, in0, out, n), name);
+      ctx->failure_is_an_option = true;
+    }
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+extern "C" {
+
+// scan i32.max i32.lowest xs
+int futhark_entry_scan_max_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  return scan_like<futhark_i32_1d>(ctx, out0, in0, in0->shape[0], "scan_max_i32.segscan", PROV("scan i32.max i32.lowest xs"),
+                                   [](futhark_context *c, const futhark_i32_1d *in, futhark_i32_1d *out, int64_t n) {
+                                     return fb::launch_scan_variant_i32(1, dptr<int32_t>(in->mem), dptr<int32_t>(out->mem), n, 0, nullptr, c->lookback_scratch,
+                                                                        fb_next_epoch(c), c->d_failure, c->stream);
+                                   });
+}
+
+// map (scan (+) 0) xss (tests/intrablock/segscan0.fut): a regular segmented scan, one launch over all rows.
+int futhark_entry_segscan_rows_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const struct futhark_i32_2d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  return scan_like<futhark_i32_2d>(ctx, out0, in0, in0->shape[0] * in0->shape[1], "segscan_rows_i32.segscan", PROV("map (scan (+) 0) xss"),
+                                   [](futhark_context *c, const futhark_i32_2d *in, futhark_i32_2d *out, int64_t) {
+                                     return fb::launch_segscan_rows_i32(dptr<int32_t>(in->mem), dptr<int32_t>(out->mem), in->shape[0], in->shape[1],
+                                                                        c->lookback_scratch, fb_next_epoch(c), c->d_failure, c->stream);
+                                   });
+}
+
+// tests/soacs/scan4.fut: two rounds of  xs' = map2 (+) (map (+ sum) (scan (+) 0 (map (+1) xs))) xs  with
+// sum = reduce (+) 0 (map (+1) xs).  Per round one reduction (sum of xs; the n ones are added on the
+// host side of the seed) and one scan kernel with the map body and the post-operation fused in.
+int futhark_entry_scanomap_steps_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  futhark_i32_1d *mid = nullptr;
+  auto round = [](futhark_context *c, const futhark_i32_1d *in, futhark_i32_1d *out, int64_t n) -> cudaError_t {
+    int32_t *sum = reinterpret_cast<int32_t *>(c->d_scalar + 2);
+    cudaError_t err = fb::launch_reduce_i32(dptr<int32_t>(in->mem), n, sum, c->reduce_scratch, c->num_sms, c->stream);
+    if (err != cudaSuccess) return err;
+    c->launch_count++;
+    return fb::launch_scan_variant_i32(2, dptr<int32_t>(in->mem), dptr<int32_t>(out->mem), n, (int32_t)(uint32_t)n, sum, c->lookback_scratch,
+                                       fb_next_epoch(c), c->d_failure, c->stream);
+  };
+  int rc = scan_like<futhark_i32_1d>(ctx, &mid, in0, n, "scanomap_steps_i32.segscan", PROV("scan (+) 0 (map (+1) xs), post-op (+ sum + x)"), round);
+  if (rc != 0) return rc;
+  rc = scan_like<futhark_i32_1d>(ctx, out0, mid, n, "scanomap_steps_i32.segscan", PROV("scan (+) 0 (map (+1) xs), post-op (+ sum + x)"), round);
+  fb_unref(ctx, &mid->mem); free(mid);
+  return rc;
 }
 
 int futhark_entry_bmm_f16(struct futhark_context *ctx, struct futhark_f32_3d **out0, const struct futhark_f16_3d *in0,

@@ -1,12 +1,15 @@
-// Generalised histogram (reduce_by_index) for two operators: (+) on i32 weights and
-// max on f32 weights.  Replaces the generated seghist_local / seghist_global kernels
-// of the reference (src/Futhark/CodeGen/ImpGen/GPU/SegHist.hs:377-1188).
+// Generalised histogram (reduce_by_index) over 32-bit values.  Replaces the generated
+// seghist_local / seghist_global kernels of the reference
+// (src/Futhark/CodeGen/ImpGen/GPU/SegHist.hs:377-1188).
 //
-// Both operators become a 32-bit integer atomic: add, or unsigned max on an
-// order-preserving key of the float (so no compare-and-swap loop as in
-// ImpGen/GPU/Base.hs:844-905).  Indices outside [0,B) are skipped
-// (SegHist.hs:450-455); NaN weights are skipped by max, as fmaxf drops them
-// (rts/c/scalar.h:932).
+// The kernels are templated on the operator (HistOpKind, kernels.h).  What an operator
+// supplies is what the reference's atomic-update choice supplies (ImpGen/GPU/Base.hs:720-905,
+// the table of ImpGen/GPU.hs:46-90): its neutral element, how a value is combined into a bin
+// atomically (a native 32-bit atomic where there is one: add, min, max, and, or, xor, f32 add;
+// f32 max as unsigned max on an order-preserving key of the float; a compare-and-swap loop
+// for what has none, here the integer product), and how two partial bins are folded.
+// Indices outside [0,B) are skipped (SegHist.hs:450-455); NaN weights are skipped by the
+// f32 max, as fmaxf drops them (rts/c/scalar.h:932).
 //
 // Strategies, by number of bins B (CAP = 57344 bins = 224 KiB of shared memory):
 //   B <= CAP      one CTA per SM holds C = 2^k <= 32 private copies of the histogram in
@@ -46,23 +49,58 @@ __device__ __forceinline__ uint32_t key_f32(uint32_t key) {
 __device__ __forceinline__ bool is_nan_bits(uint32_t bits) { return (bits & 0x7FFFFFFFu) > 0x7F800000u; }
 
 template <int OP>
-__device__ __forceinline__ uint32_t neutral() { return OP == 0 ? 0u : KEY_NEG_INF; }
+__device__ __host__ __forceinline__ constexpr uint32_t neutral() {
+  return OP == HOP_MAX_F32 ? KEY_NEG_INF
+       : OP == HOP_MIN_I32 ? 0x7FFFFFFFu
+       : OP == HOP_MAX_I32 ? 0x80000000u
+       : OP == HOP_MIN_U32 ? 0xFFFFFFFFu
+       : OP == HOP_AND_I32 ? 0xFFFFFFFFu
+       : OP == HOP_MUL_I32 ? 1u
+       : 0u;                       // add (i32, f32: +0.0), u32 max, or, xor
+}
 
-// update of a shared-memory bin
+// update of a bin, in shared or in global memory (generic address)
 template <int OP>
-__device__ __forceinline__ void upd_shared(uint32_t *p, uint32_t w) {
-  if (OP == 0) atomicAdd(p, w);
-  else atomicMax(p, w);
+__device__ __forceinline__ void upd_bin(uint32_t *p, uint32_t w) {
+  if (OP == HOP_ADD_I32) atomicAdd(p, w);              // result unused: compiles to a reduction
+  else if (OP == HOP_MAX_F32 || OP == HOP_MAX_U32) atomicMax(p, w);
+  else if (OP == HOP_MIN_U32) atomicMin(p, w);
+  else if (OP == HOP_MIN_I32) atomicMin(reinterpret_cast<int *>(p), (int)w);
+  else if (OP == HOP_MAX_I32) atomicMax(reinterpret_cast<int *>(p), (int)w);
+  else if (OP == HOP_AND_I32) atomicAnd(p, w);
+  else if (OP == HOP_OR_I32) atomicOr(p, w);
+  else if (OP == HOP_XOR_I32) atomicXor(p, w);
+  else if (OP == HOP_ADD_F32) atomicAdd(reinterpret_cast<float *>(p), __uint_as_float(w));
+  else {                                               // no native atomic: compare-and-swap until nobody interfered (Base.hs:844-905)
+    uint32_t old = *reinterpret_cast<volatile uint32_t *>(p), assumed;
+    do {
+      assumed = old;
+      old = atomicCAS(p, assumed, assumed * w);
+    } while (old != assumed);
+  }
 }
 template <int OP>
-__device__ __forceinline__ void upd_global(uint32_t *p, uint32_t w) {
-  if (OP == 0) atomicAdd(p, w);    // result unused: compiles to a reduction
-  else atomicMax(p, w);
+__device__ __forceinline__ void upd_shared(uint32_t *p, uint32_t w) { upd_bin<OP>(p, w); }
+template <int OP>
+__device__ __forceinline__ void upd_global(uint32_t *p, uint32_t w) { upd_bin<OP>(p, w); }
+// two partial bins folded (the private copies of a CTA)
+template <int OP>
+__device__ __forceinline__ uint32_t fold_bins(uint32_t a, uint32_t b) {
+  if (OP == HOP_ADD_I32) return a + b;
+  if (OP == HOP_MAX_F32 || OP == HOP_MAX_U32) return a > b ? a : b;
+  if (OP == HOP_MIN_U32) return a < b ? a : b;
+  if (OP == HOP_MIN_I32) return (uint32_t)min((int)a, (int)b);
+  if (OP == HOP_MAX_I32) return (uint32_t)max((int)a, (int)b);
+  if (OP == HOP_AND_I32) return a & b;
+  if (OP == HOP_OR_I32) return a | b;
+  if (OP == HOP_XOR_I32) return a ^ b;
+  if (OP == HOP_ADD_F32) return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
+  return a * b;
 }
-// weight as stored in the accumulator; `skip` set for a NaN under max
+// weight as stored in the accumulator; `skip` set for a NaN under the f32 max
 template <int OP>
 __device__ __forceinline__ uint32_t prep(uint32_t wbits, bool &skip) {
-  if (OP == 0) { skip = false; return wbits; }
+  if (OP != HOP_MAX_F32) { skip = false; return wbits; }
   skip = is_nan_bits(wbits);
   return f32_key(wbits);
 }
@@ -148,7 +186,7 @@ hist_smem_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ 
     for (uint32_t c = 0; c < C; c++) {
       // rotate the starting copy per bin so the lanes of a warp hit different banks
       const uint32_t v = s_hist[(b << log2c) + ((c + b) & (C - 1))];
-      acc = (OP == 0) ? acc + v : (v > acc ? v : acc);
+      acc = fold_bins<OP>(acc, v);
     }
     if (acc != neutral<OP>()) upd_global<OP>(&out[bin_lo + b], acc);
   }
@@ -340,10 +378,16 @@ static int grid_for(int64_t n, int threads, int cap) {
 
 template <int OP>
 static cudaError_t launch_hist_op(int64_t B, const int32_t *bins, const uint32_t *ws, int64_t n, uint32_t *out,
-                                  int num_sms, cudaStream_t stream) {
-  // the result starts at the neutral element (prelude/soacs.fut:132-133)
-  fill_u32_kernel<<<grid_for(B, 256, num_sms * 8), 256, 0, stream>>>(out, B, OP == 0 ? 0u : KEY_NEG_INF);
-  cudaError_t err = cudaGetLastError();
+                                  const uint32_t *dest, int num_sms, cudaStream_t stream) {
+  // the result starts at the neutral element (hist, prelude/soacs.fut:132-133) or as a copy of the
+  // destination (reduce_by_index, :117-130)
+  cudaError_t err;
+  if (dest != nullptr) {
+    err = cudaMemcpyAsync(out, dest, (size_t)B * 4, cudaMemcpyDeviceToDevice, stream);
+  } else {
+    fill_u32_kernel<<<grid_for(B, 256, num_sms * 8), 256, 0, stream>>>(out, B, neutral<OP>());
+    err = cudaGetLastError();
+  }
   if (err != cudaSuccess) return err;
   if (n > 0) {
     const int64_t P64 = (B + HIST_CAP_BINS - 1) / HIST_CAP_BINS;
@@ -385,7 +429,7 @@ static cudaError_t launch_hist_op(int64_t B, const int32_t *bins, const uint32_t
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
   }
-  if (OP == 1) {
+  if (OP == HOP_MAX_F32) {
     decode_keys_kernel<<<grid_for(B, 256, num_sms * 8), 256, 0, stream>>>(out, B);
     err = cudaGetLastError();
   }
@@ -393,13 +437,58 @@ static cudaError_t launch_hist_op(int64_t B, const int32_t *bins, const uint32_t
 }
 
 cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
-                        int num_sms, cudaStream_t stream) {
+                        const void *dest, int num_sms, cudaStream_t stream) {
   if (B <= 0) return cudaSuccess;
-  if (op == 0)
-    return launch_hist_op<0>(B, bins, reinterpret_cast<const uint32_t *>(weights), n,
-                             reinterpret_cast<uint32_t *>(out), num_sms, stream);
-  return launch_hist_op<1>(B, bins, reinterpret_cast<const uint32_t *>(weights), n,
-                           reinterpret_cast<uint32_t *>(out), num_sms, stream);
+  const uint32_t *w = reinterpret_cast<const uint32_t *>(weights), *d = reinterpret_cast<const uint32_t *>(dest);
+  uint32_t *o = reinterpret_cast<uint32_t *>(out);
+  switch (op) {
+    case HOP_ADD_I32: return launch_hist_op<HOP_ADD_I32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_MAX_F32: return dest != nullptr ? cudaErrorInvalidValue : launch_hist_op<HOP_MAX_F32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_MIN_I32: return launch_hist_op<HOP_MIN_I32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_MAX_I32: return launch_hist_op<HOP_MAX_I32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_MIN_U32: return launch_hist_op<HOP_MIN_U32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_MAX_U32: return launch_hist_op<HOP_MAX_U32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_AND_I32: return launch_hist_op<HOP_AND_I32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_OR_I32: return launch_hist_op<HOP_OR_I32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_XOR_I32: return launch_hist_op<HOP_XOR_I32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_ADD_F32: return launch_hist_op<HOP_ADD_F32>(B, bins, w, n, o, d, num_sms, stream);
+    case HOP_MUL_I32: return launch_hist_op<HOP_MUL_I32>(B, bins, w, n, o, d, num_sms, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+// ---- index spaces with more than one dimension -----------------------------------------------------
+// A histogram per row of [rows][cols] (segment dimension of the SegHist, SegHist.hs:97-148) is one
+// histogram over rows * B bins whose index carries the row; reduce_by_index_2d
+// (prelude/soacs.fut:149-152) is one over n * m bins.  These kernels write that flat index, -1 for
+// what is out of range in any dimension.
+__global__ void __launch_bounds__(256)
+flatten_rows_index_kernel(const int32_t *__restrict__ is, int64_t n, int64_t cols, int64_t B, int32_t *__restrict__ flat) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+    const int32_t b = is[i];
+    flat[i] = (b >= 0 && (int64_t)b < B) ? (int32_t)((i / cols) * B + b) : -1;
+  }
+}
+__global__ void __launch_bounds__(256)
+flatten_2d_index_kernel(const int64_t *__restrict__ is, const int64_t *__restrict__ js, int64_t n, int64_t N, int64_t M,
+                        int32_t *__restrict__ flat) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+    const int64_t a = is[i], b = js[i];
+    flat[i] = (a >= 0 && a < N && b >= 0 && b < M) ? (int32_t)(a * M + b) : -1;
+  }
+}
+cudaError_t launch_flatten_rows_index(const int32_t *is, int64_t n, int64_t cols, int64_t B, int32_t *flat, int num_sms, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  flatten_rows_index_kernel<<<grid_for(n, 256, num_sms * 8), 256, 0, stream>>>(is, n, cols, B, flat);
+  return cudaGetLastError();
+}
+cudaError_t launch_flatten_2d_index(const int64_t *is, const int64_t *js, int64_t n, int64_t N, int64_t M, int32_t *flat, int num_sms,
+                                    cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  flatten_2d_index_kernel<<<grid_for(n, 256, num_sms * 8), 256, 0, stream>>>(is, js, n, N, M, flat);
+  return cudaGetLastError();
 }
 
 }  // namespace fb

@@ -1,10 +1,11 @@
-// Single-pass scan kernels: inclusive scan (+) over i32, flagged segmented inclusive scan
-// (+) over f32, and filter / partition compaction of u32 keys.  They replace the generated
+// Single-pass scan kernels: scans, flagged and regular segmented scans, scans with a fused
+// map body and post-operation, and filter / partition compaction.  They replace the generated
 // `segscan` kernel of the reference
 // (src/Futhark/CodeGen/ImpGen/GPU/SegScan/SinglePass.hs:327-879) and, for compaction, the
-// scan + scatter that prelude/soacs.fut:241-286 expands into.
+// scan + scatter that prelude/soacs.fut:241-323 expands into.
 //
-// One persistent kernel, templated on what a tile computes; 256 threads per CTA, 4 CTAs
+// One persistent kernel, templated on a specification type (scan_specs.cuh) that supplies
+// operator, map body, post-operation, flag source and predicate; 256 threads per CTA, 4 CTAs
 // per SM.  A tile holds 256 x 20 = 5120 elements.  Like the reference's kernel it hands
 // prefixes between tiles through one status word per tile (value and state in one 64-bit
 // word, :628-660 there) and numbers its work by a global counter, so that what a tile
@@ -51,50 +52,20 @@
 #include "../../include/futhark_b200.h"
 #include "common.cuh"
 #include "kernels.h"
+#include "scan_specs.cuh"
 
 namespace fb {
 
 constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_WARPS = SCAN_THREADS / 32;
-enum ScanKind : int { K_SCAN_I32 = 0, K_SEGSCAN_F32 = 1, K_FILTER = 2, K_PARTITION = 3, K_EXSCAN_I32 = 4 };
-
-// Tile geometry per kind.  A thread owns V 16-byte vectors = 4V consecutive elements; V is odd
-// (see the kernel).  The scans take 5 (tiles of 5120 elements, 4 CTAs per SM: larger tiles
-// were measured slower).  Compaction, whose second visit does much more per tile, takes 9
-// (9216 keys, 3 CTAs per SM, which just fit their 74 KB of buffers each; one bit per key of a
-// thread then needs a 64-bit mask): the filter is 11 % faster than with 7, partition the same.
-// LEAD = tiles by which visit A runs ahead of visit B: 20 MiB of input for the scans, 36 MiB
-// for compaction (with a quarter of it visit B waits; with twice as much the tile has left
-// L2 before visit B).
-template <int KIND> struct TileCfg {
-  static constexpr bool kCompact = (KIND == K_FILTER || KIND == K_PARTITION);
-  static constexpr int V = kCompact ? 9 : 5;
-  static constexpr int ITEMS = V * 4;
-  static constexpr int TILE = SCAN_THREADS * ITEMS;
-  static constexpr int LEAD = 1024;
-  static constexpr int CTAS = kCompact ? 3 : 4;
-};
-constexpr int SCAN_TILE_MIN = TileCfg<K_SCAN_I32>::TILE;     // the smallest tile: bounds the number of status words     // the smallest tile: bounds the number of status words
+constexpr int SCAN_TILE_MIN = SCAN_THREADS * 20;          // the smallest tile (V = 5): bounds the number of status words
 constexpr int PROP_PER_LANE = 8;                          // status words per lane per round of the propagator
 constexpr int PROP_WINDOW = 32 * PROP_PER_LANE;
 constexpr uint32_t WAIT_MAX_ROUNDS = 1u << 22;            // idle polls before a wait gives up
 
-// ---- operators on (value bits, flag) pairs -----------------------------------------
-struct OpAddU32 {  // wrapping integer add; the flag is unused (always 0)
-  static __device__ __forceinline__ void combine(uint32_t lv, uint32_t lf, uint32_t rv, uint32_t rf,
-                                                 uint32_t &ov, uint32_t &of) {
-    ov = lv + rv; of = 0; (void)lf; (void)rf;
-  }
-  static constexpr bool kHasFlag = false;
-};
-struct OpSegAddF32 {  // (f1,v1) (+) (f2,v2) = (f1|f2, f2 ? v2 : v1+v2) on f32 bit patterns
-  static __device__ __forceinline__ void combine(uint32_t lv, uint32_t lf, uint32_t rv, uint32_t rf,
-                                                 uint32_t &ov, uint32_t &of) {
-    float s = __uint_as_float(lv) + __uint_as_float(rv);
-    ov = rf ? rv : __float_as_uint(s);
-    of = lf | rf;
-  }
-  static constexpr bool kHasFlag = true;
+template <typename S> struct TileOf {
+  static constexpr int ITEMS = S::V * 4;
+  static constexpr int TILE = SCAN_THREADS * ITEMS;
 };
 
 __device__ __forceinline__ bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
@@ -149,7 +120,7 @@ __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, ui
     const int mine = (lane < stop_lane) ? PROP_PER_LANE : (lane == stop_lane ? stop_ready : 0);
     // in-lane inclusive fold of the aggregates, then exclusive scan across lanes
     uint32_t iv[PROP_PER_LANE], iflag[PROP_PER_LANE];
-    uint32_t tv = 0, tf = 0;            // lane total (identity if the lane has nothing)
+    uint32_t tv = Op::kIdentity, tf = 0;    // lane total (identity if the lane has nothing)
 #pragma unroll
     for (int q = 0; q < PROP_PER_LANE; q++) {
       if (q < mine) {
@@ -210,6 +181,9 @@ struct LookbackArgs {
   const uint32_t *carry_vals;
   int carry_n;
   int64_t *d_count;        // compaction: number of selected keys
+  const int64_t *d_base;   // compaction of one piece of a longer array: selected keys in the pieces before (device word, or NULL)
+  int64_t index_base;      // ... and the index of this piece's first key in the whole array
+  int64_t seg_len;         // regular segmented scan: the length of every segment
   uint32_t *shard_out;     // segmented scan of one shard of a split array: 4 words, see run_propagator (or NULL)
 };
 
@@ -219,7 +193,7 @@ struct LookbackArgs {
 template <typename Op>
 __device__ __forceinline__ void fold_warp_totals(const uint32_t *s_wv, const uint32_t *s_wf, int lane, int warp,
                                                  uint32_t &tv, uint32_t &tf, uint32_t &bv, uint32_t &bf) {
-  uint32_t wv = (lane < SCAN_WARPS) ? s_wv[lane] : 0u;
+  uint32_t wv = (lane < SCAN_WARPS) ? s_wv[lane] : Op::kIdentity;
   uint32_t wf = (Op::kHasFlag && lane < SCAN_WARPS) ? s_wf[lane] : 0u;
 #pragma unroll
   for (int o = 1; o < SCAN_WARPS; o <<= 1) {
@@ -230,7 +204,7 @@ __device__ __forceinline__ void fold_warp_totals(const uint32_t *s_wv, const uin
   tf = __shfl_sync(kFull, wf, SCAN_WARPS - 1);
   bv = __shfl_sync(kFull, wv, warp > 0 ? warp - 1 : 0);
   bf = __shfl_sync(kFull, wf, warp > 0 ? warp - 1 : 0);
-  if (warp == 0) { bv = 0; bf = 0; }
+  if (warp == 0) { bv = Op::kIdentity; bf = 0; }
 }
 
 // Work item w of a launch -> (visit, tile).  The first `lead` items are visit A of tiles
@@ -248,14 +222,21 @@ struct WorkMap {
   }
 };
 
-template <int KIND>
-__global__ void __launch_bounds__(SCAN_THREADS, TileCfg<KIND>::CTAS)
+template <typename S>
+__global__ void __launch_bounds__(SCAN_THREADS, S::CTAS)
 stream_kernel(const LookbackArgs a) {
-  constexpr int V = TileCfg<KIND>::V, ITEMS = TileCfg<KIND>::ITEMS, TILE = TileCfg<KIND>::TILE;
-  constexpr bool SEG = (KIND == K_SEGSCAN_F32);
-  constexpr bool COMPACT = (KIND == K_FILTER || KIND == K_PARTITION);
-  constexpr int SB = TILE * 4 + (SEG ? TILE : 64);     // bytes of a tile buffer (compaction stages with up to 9 words of padding)
-  using Op = typename std::conditional<SEG, OpSegAddF32, OpAddU32>::type;
+  constexpr int V = S::V, ITEMS = TileOf<S>::ITEMS, TILE = TileOf<S>::TILE;
+  using Op = typename S::Op;
+  constexpr bool SEG = Op::kHasFlag;                   // the operator works on (flag, value) pairs
+  constexpr bool HASF = S::kFlagArray;                 // a byte array is loaded with the values
+  constexpr bool COMPACT = S::kCompact, PART = S::kPartition;
+  constexpr bool ADD = std::is_same<Op, OpAddU32>::value;            // the operator is the wrapping add (counts included)
+  constexpr bool REDO = !COMPACT && !SEG && (S::kHasPost || S::kExclusive);   // the second visit folds again from the prefix
+  // bytes of a tile buffer; compaction stages with up to 9 words of padding, the flag bytes lie behind
+  constexpr int FO = COMPACT ? TILE * 4 + 64 : TILE * 4;
+  constexpr int SB = COMPACT ? TILE * 4 + 64 + (HASF ? TILE : 0) : TILE * 4 + (HASF ? TILE : 64);
+  static_assert(!SEG || HASF || S::kSegRegular, "a flagged operator needs a flag source");
+  static_assert(!COMPACT || ADD, "compaction counts with the wrapping add");
   extern __shared__ __align__(128) unsigned char s_buf[];   // two tile buffers
   __shared__ __align__(8) uint64_t s_bar[2];
   __shared__ uint32_t s_item[3];         // decoded work items of iterations it, it+1, it+2: tile << 1 | visit A, or ITEM_NONE
@@ -277,8 +258,9 @@ stream_kernel(const LookbackArgs a) {
   }
   __syncthreads();
   uint32_t seed = a.carry_in;
-  if (KIND == K_SCAN_I32 && a.carry_vals != nullptr)
+  if (ADD && !COMPACT && a.carry_vals != nullptr)
     for (int q = 0; q < a.carry_n; q++) seed += a.carry_vals[q];
+  const int64_t sel_base = (COMPACT && a.d_base != nullptr) ? *a.d_base : 0;   // selected keys in the pieces before this one
   const bool solo = (gridDim.x == 1);    // a lone CTA turns its own aggregates into prefixes
   if (s_role == 0 && !solo) {
     if (warp == 0) run_propagator<Op>(a.status, nt, a.epoch, seed, a.failure, a.shard_out);
@@ -287,11 +269,11 @@ stream_kernel(const LookbackArgs a) {
   const uint32_t workers = solo ? 1u : gridDim.x - 1;
   WorkMap wm;
   wm.nt = nt;
-  wm.lead = nt < (uint32_t)TileCfg<KIND>::LEAD ? nt : (uint32_t)TileCfg<KIND>::LEAD;
+  wm.lead = nt < (uint32_t)S::LEAD ? nt : (uint32_t)S::LEAD;
   // Every worker draws work items until it meets one past the end, so the counter ends at
   // total + workers; whoever draws that last value rewinds it for the next launch.
   const uint32_t last_value = wm.total() + workers - 1;
-  const bool in_bulk = aligned16(a.in) && (!SEG || aligned16(a.flags));
+  const bool in_bulk = aligned16(a.in) && (!HASF || aligned16(a.flags));
   const bool out_bulk = !COMPACT && aligned16(a.out);
   uint32_t self_v = seed, self_f = 0;    // thread 0 of a lone CTA: running inclusive prefix
   uint32_t self_first = 0xffffffffu;     // ... and the first tile with a segment start
@@ -313,9 +295,9 @@ stream_kernel(const LookbackArgs a) {
   auto arm = [&](int b, uint32_t tile) {   // thread 0: start the copies of a tile into buffer b
     unsigned char *dst = s_buf + b * SB;
     const int64_t tb = (int64_t)tile * TILE;
-    mbar_expect_tx(&s_bar[b], TILE * 4 + (SEG ? TILE : 0));
+    mbar_expect_tx(&s_bar[b], TILE * 4 + (HASF ? TILE : 0));
     bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, TILE * 4, &s_bar[b]);
-    if (SEG) bulk_g2s(dst + TILE * 4, a.flags + tb, TILE, &s_bar[b]);
+    if (HASF) bulk_g2s(dst + FO, a.flags + tb, TILE, &s_bar[b]);
   };
   auto draw = [&]() -> uint32_t {          // thread 0
     const uint32_t w = atomicAdd(&a.ticket[0], 1u);
@@ -368,10 +350,9 @@ stream_kernel(const LookbackArgs a) {
       if (tid == 0) armed &= ~(1u << par);
     } else {
       const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
-      for (int i = tid; i < TILE; i += SCAN_THREADS)
-        s_tile[i] = (i < count) ? gin[i] : (COMPACT ? 0xffffffffu : 0u);     // padding: never selected / identity
-      if (SEG) {
-        unsigned char *sfb = buf + TILE * 4;
+      for (int i = tid; i < TILE; i += SCAN_THREADS) s_tile[i] = (i < count) ? gin[i] : 0u;     // (what lies past `count` is masked below)
+      if (HASF) {
+        unsigned char *sfb = buf + FO;
         for (int i = tid; i < TILE; i += SCAN_THREADS) sfb[i] = (i < count) ? a.flags[base + i] : (unsigned char)0;
       }
       fence_proxy_async_smem();          // a later bulk copy lands in this buffer: order it after these stores
@@ -390,41 +371,67 @@ stream_kernel(const LookbackArgs a) {
     }
     using mask_t = typename std::conditional<(ITEMS > 32), unsigned long long, uint32_t>::type;
     static_assert(ITEMS <= 64 && (SEG ? ITEMS <= 32 : true), "one bit per element of the thread");
+    // elements of this thread that exist (the last tile may be ragged)
+    const int valid = full ? ITEMS : (count - tid * ITEMS < 0 ? 0 : (count - tid * ITEMS > ITEMS ? ITEMS : count - tid * ITEMS));
     mask_t bits = 0;                     // segment starts (segmented scan) / selected keys (compaction)
     uint32_t tv_thread, tf_thread = 0;   // the thread's aggregate
-    if (SEG) {
-      const uint32_t *sf = reinterpret_cast<const uint32_t *>(buf + TILE * 4) + tid * V;
-      uint32_t fw[V];
+    uint32_t fw[HASF ? V : 1];           // the thread's flag bytes
+    if (HASF) {
+      const uint32_t *sf = reinterpret_cast<const uint32_t *>(buf + FO) + tid * V;
 #pragma unroll
       for (int j = 0; j < V; j++) fw[j] = sf[j];
-      float acc = 0.0f;
+    }
+    if (COMPACT) {
 #pragma unroll
       for (int q = 0; q < ITEMS; q++) {
-        const bool fl = ((fw[q >> 2] >> (8 * (q & 3))) & 0xffu) != 0;
-        const float v = __uint_as_float(x[q]);
-        if (fl) { acc = v; bits |= (mask_t)1 << q; } else acc = acc + v;
-        x[q] = __float_as_uint(acc);
+        const uint32_t fl = HASF ? (fw[q >> 2] >> (8 * (q & 3))) & 0xffu : 0u;
+        if (S::pred(x[q], fl)) bits |= (mask_t)1 << q;
       }
-      tv_thread = __float_as_uint(acc);
-      tf_thread = bits ? 1u : 0u;
-    } else if (COMPACT) {
-#pragma unroll
-      for (int q = 0; q < ITEMS; q++)
-        if ((x[q] & 7u) < 3u) bits |= (mask_t)1 << q;
+      if (!full) bits &= (valid >= ITEMS) ? ~(mask_t)0 : (((mask_t)1 << valid) - 1);
       tv_thread = (ITEMS > 32) ? (uint32_t)__popcll((unsigned long long)bits) : (uint32_t)__popc((uint32_t)bits);
-    } else if (is_a) {
-      uint32_t s = 0;
-#pragma unroll
-      for (int q = 0; q < ITEMS; q++) s += x[q];
-      tv_thread = s;
     } else {
+      // the map body, and the neutral element behind the end of a ragged tile
 #pragma unroll
-      for (int q = 1; q < ITEMS; q++) x[q] += x[q - 1];
-      tv_thread = x[ITEMS - 1];
+      for (int q = 0; q < ITEMS; q++) {
+        if (!REDO) x[q] = S::map(x[q]);              // (REDO keeps the elements for the post-operation and maps on the fly)
+        if (!full && q >= valid) x[q] = Op::kIdentity;
+      }
+      if (SEG) {
+        // head flags: from the byte array, or computed from the position inside the regular segment
+        int64_t pos = 0;
+        if (S::kSegRegular) pos = (base + (int64_t)tid * ITEMS) % a.seg_len;
+        uint32_t acc = Op::kIdentity, accf = 0;
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) {
+          bool fl;
+          if (S::kSegRegular) { fl = (pos == 0); pos = (pos + 1 == a.seg_len) ? 0 : pos + 1; }
+          else fl = ((fw[q >> 2] >> (8 * (q & 3))) & 0xffu) != 0;
+          if (fl) bits |= (mask_t)1 << q;
+          Op::combine(acc, accf, x[q], fl ? 1u : 0u, acc, accf);
+          x[q] = acc;
+        }
+        tv_thread = acc;
+        tf_thread = bits ? 1u : 0u;
+      } else if (is_a || REDO) {
+        uint32_t s = REDO ? S::map(x[0]) : x[0], sf = 0;
+        if (REDO && !full && valid < 1) s = Op::kIdentity;
+#pragma unroll
+        for (int q = 1; q < ITEMS; q++) {
+          uint32_t y = REDO ? S::map(x[q]) : x[q];
+          if (REDO && !full && q >= valid) y = Op::kIdentity;
+          Op::combine(s, sf, y, 0u, s, sf);
+        }
+        tv_thread = s;
+      } else {
+        uint32_t sf = 0;
+#pragma unroll
+        for (int q = 1; q < ITEMS; q++) Op::combine(x[q - 1], 0u, x[q], 0u, x[q], sf);
+        tv_thread = x[ITEMS - 1];
+      }
     }
-    uint32_t xv = 0, xf = 0;             // what precedes this thread inside its warp
-    if (!SEG && is_a) {
-      // only the tile's aggregate is wanted
+    uint32_t xv = Op::kIdentity, xf = 0; // what precedes this thread inside its warp
+    if (ADD && is_a) {
+      // only the tile's aggregate is wanted, and the order does not matter
       const uint32_t t = warp_sum(tv_thread);
       if (lane == 31) s_wv[par][warp] = t;
     } else {
@@ -437,7 +444,7 @@ stream_kernel(const LookbackArgs a) {
         if (lane >= o) Op::combine(lv, lf, iv, ifl, iv, ifl);
       }
       xv = __shfl_up_sync(kFull, iv, 1); xf = SEG ? __shfl_up_sync(kFull, ifl, 1) : 0u;
-      if (lane == 0) { xv = 0; xf = 0; }
+      if (lane == 0) { xv = Op::kIdentity; xf = 0; }
       if (lane == 31) { s_wv[par][warp] = iv; if (SEG) s_wf[par][warp] = ifl; }
     }
 
@@ -484,25 +491,32 @@ stream_kernel(const LookbackArgs a) {
     uint32_t lv, lf;
     Op::combine(bv, bf, xv, xf, lv, lf);                           // what precedes this thread inside the tile
     if (!COMPACT) {
+      // what precedes this thread: the tile's incoming prefix, then its left neighbours
+      uint32_t pv, pf;
+      Op::combine(ev, 0u, lv, lf, pv, pf);
       if (SEG) {
-        // before the thread's first segment start its left neighbours count, and before the
-        // tile's first segment start the incoming prefix as well
-        const float left = lf ? __uint_as_float(lv) : __uint_as_float(ev) + __uint_as_float(lv);
+        // only the elements in front of the thread's first segment start take it
         const int first = bits ? (__ffs((uint32_t)bits) - 1) : ITEMS;
 #pragma unroll
-        for (int q = 0; q < ITEMS; q++)
-          if (q < first) x[q] = __float_as_uint(left + __uint_as_float(x[q]));
-      } else {
-        const uint32_t left = ev + lv;
-        if (KIND == K_EXSCAN_I32) {
-          // exclusive: element q receives what precedes it (its left neighbour's inclusive value)
-#pragma unroll
-          for (int q = ITEMS - 1; q > 0; q--) x[q] = x[q - 1] + left;
-          x[0] = left;
-        } else {
-#pragma unroll
-          for (int q = 0; q < ITEMS; q++) x[q] += left;
+        for (int q = 0; q < ITEMS; q++) {
+          uint32_t ov, of;
+          Op::combine(pv, pf, x[q], 0u, ov, of);
+          if (q < first) x[q] = ov;
         }
+      } else if (REDO) {
+        // fold once more, from the prefix: element q receives post(scan up to q, element q); for
+        // an exclusive scan, the scan up to q - 1
+        uint32_t sv = pv, sf = 0;
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) {
+          uint32_t y = S::map(x[q]);
+          if (!full && q >= valid) y = Op::kIdentity;
+          if (S::kExclusive) { const uint32_t o = S::post(sv, x[q]); Op::combine(sv, sf, y, 0u, sv, sf); x[q] = o; }
+          else { Op::combine(sv, sf, y, 0u, sv, sf); x[q] = S::post(sv, x[q]); }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) { uint32_t of; Op::combine(pv, 0u, x[q], 0u, x[q], of); }
       }
       int4 *s4 = reinterpret_cast<int4 *>(s_tile) + tid * V;
 #pragma unroll
@@ -526,18 +540,18 @@ stream_kernel(const LookbackArgs a) {
       // group is staged at the same offset modulo 4 as its destination, so that the body of a
       // run moves as aligned 16-byte vectors on both sides.
       const uint32_t tile_true = tv;
-      const int64_t true_before = (int64_t)ev;                    // selected keys in earlier tiles (n < 2^31)
+      const int64_t true_before = sel_base + (int64_t)ev;         // selected keys in earlier tiles (and pieces); a piece has < 2^31 keys
       uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
-      uint32_t *dstf = (KIND == K_PARTITION) ? a.out_false + (base - true_before) : nullptr;
+      uint32_t *dstf = PART ? a.out_false + (a.index_base + base - true_before) : nullptr;
       const uint32_t pad_t = (uint32_t)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3u);
-      const uint32_t pad_f = (KIND == K_PARTITION) ? (uint32_t)((reinterpret_cast<uintptr_t>(dstf) >> 2) & 3u) : 0u;
+      const uint32_t pad_f = PART ? (uint32_t)((reinterpret_cast<uintptr_t>(dstf) >> 2) & 3u) : 0u;
       const uint32_t start_f = ((pad_t + tile_true + 3u) & ~3u) + pad_f;     // first rejected key in the buffer
       uint32_t rank = lv;
       const uint32_t first_ord = (uint32_t)tid * ITEMS;
 #pragma unroll
       for (int q = 0; q < ITEMS; q++) {
         if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
-        else if (KIND == K_PARTITION && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
+        else if (PART && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
       }
       fence_proxy_async_smem();          // the bulk stores below read what the threads just staged
       __syncthreads();
@@ -555,7 +569,7 @@ stream_kernel(const LookbackArgs a) {
           if (lane == 0 && nvec > 0) bulk_s2g(g + h, s_tile + s0 + h, nvec << 4);
         };
         send_run(dst, pad_t, tile_true, 0);
-        if (KIND == K_PARTITION) send_run(dstf, start_f, (uint32_t)count - tile_true, 4);
+        if (PART) send_run(dstf, start_f, (uint32_t)count - tile_true, 4);
         if (lane == 0) bulk_commit();
         __syncwarp();                    // thread 0 fills the buffer again only after these lanes have read their keys
       }
@@ -575,8 +589,8 @@ stream_kernel(const LookbackArgs a) {
 
 // ---- host launchers --------------------------------------------------------------------
 
-template <int KIND>
-static inline uint32_t tiles_for(int64_t n) { return (uint32_t)((n + TileCfg<KIND>::TILE - 1) / TileCfg<KIND>::TILE); }
+template <typename S>
+static inline uint32_t tiles_for(int64_t n) { return (uint32_t)((n + TileOf<S>::TILE - 1) / TileOf<S>::TILE); }
 
 size_t lookback_scratch_bytes(int64_t n) {
   return 256 + (size_t)((n + SCAN_TILE_MIN - 1) / SCAN_TILE_MIN) * sizeof(uint64_t);
@@ -589,22 +603,23 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
 
 // Grid of the persistent kernel: what is resident at once (occupancy x SMs) and at most one
 // worker per tile, plus the propagator.  The occupancy query allocates nothing and is
-// cached per kind and device.
-template <int KIND>
+// cached per specification and device.
+template <typename S>
 static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
-  constexpr size_t smem = 2 * (size_t)(TileCfg<KIND>::TILE * 4 + (KIND == K_SEGSCAN_F32 ? TileCfg<KIND>::TILE : 64));
+  constexpr int TILE = TileOf<S>::TILE;
+  constexpr size_t smem = 2 * (size_t)(S::kCompact ? TILE * 4 + 64 + (S::kFlagArray ? TILE : 0) : TILE * 4 + (S::kFlagArray ? TILE : 64));
   static int ctas_per_sm_dev[64], num_sms_dev[64];     // per device ordinal (function attributes are per device)
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
   int &ctas_per_sm = ctas_per_sm_dev[dev], &num_sms = num_sms_dev[dev];
   if (ctas_per_sm == 0) {
-    cudaError_t err = cudaFuncSetAttribute(stream_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(stream_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
     int occ = 0, sms = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, stream_kernel<KIND>, SCAN_THREADS, smem);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, stream_kernel<S>, SCAN_THREADS, smem);
     if (err != cudaSuccess) return err;
     if (occ < 1) return cudaErrorLaunchOutOfResources;
     num_sms = sms;
@@ -613,19 +628,20 @@ static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
   const uint32_t resident = (uint32_t)(ctas_per_sm * num_sms);
   uint32_t grid = 2 * a.num_tiles + 1 < resident ? 2 * a.num_tiles + 1 : resident;
   if (a.num_tiles <= 1 || grid < 2) grid = 1;          // a single tile: one CTA that propagates for itself
-  stream_kernel<KIND><<<grid, SCAN_THREADS, smem, stream>>>(a);
+  stream_kernel<S><<<grid, SCAN_THREADS, smem, stream>>>(a);
   return cudaGetLastError();
 }
 
-template <int KIND>
+template <typename S>
 static LookbackArgs make_args(const void *in, const uint8_t *flags, void *out, uint32_t *out_false, int64_t n,
                               void *scratch, uint32_t epoch, int *failure) {
   LookbackArgs a;
   a.in = in; a.flags = flags; a.out = out; a.out_false = out_false; a.n = n;
-  a.num_tiles = tiles_for<KIND>(n);
+  a.num_tiles = tiles_for<S>(n);
   split_scratch(scratch, &a.ticket, &a.status);
   a.epoch = epoch; a.failure = failure;
-  a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr; a.shard_out = nullptr;
+  a.carry_in = S::kCompact ? 0u : S::Op::kIdentity; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr; a.shard_out = nullptr;
+  a.d_base = nullptr; a.index_base = 0; a.seg_len = 1;
   return a;
 }
 
@@ -633,18 +649,45 @@ cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t 
                             const int32_t *carry_vals, int carry_n, void *scratch,
                             uint32_t epoch, int *failure, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  LookbackArgs a = make_args<K_SCAN_I32>(in, nullptr, out, nullptr, n, scratch, epoch, failure);
+  LookbackArgs a = make_args<SpecScanAddI32>(in, nullptr, out, nullptr, n, scratch, epoch, failure);
   a.carry_in = (uint32_t)carry_in;
   a.carry_vals = reinterpret_cast<const uint32_t *>(carry_vals);
   a.carry_n = carry_n;
-  return launch_stream<K_SCAN_I32>(a, stream);
+  return launch_stream<SpecScanAddI32>(a, stream);
+}
+
+// Scans that differ from the above only in their specification: 0 exclusive (+), 1 inclusive max,
+// 2 the scanomap step of tests/soacs/scan4.fut, seeded with seed_host plus the device value at `seed` (may be NULL).
+cudaError_t launch_scan_variant_i32(int variant, const int32_t *in, int32_t *out, int64_t n, int32_t seed_host, const int32_t *seed,
+                                    void *scratch, uint32_t epoch, int *failure, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  switch (variant) {
+    case 0: return launch_stream<SpecExscanAddI32>(make_args<SpecExscanAddI32>(in, nullptr, out, nullptr, n, scratch, epoch, failure), stream);
+    case 1: return launch_stream<SpecScanMaxI32>(make_args<SpecScanMaxI32>(in, nullptr, out, nullptr, n, scratch, epoch, failure), stream);
+    case 2: {
+      LookbackArgs a = make_args<SpecScanomapStepI32>(in, nullptr, out, nullptr, n, scratch, epoch, failure);
+      a.carry_in = (uint32_t)seed_host;
+      a.carry_vals = reinterpret_cast<const uint32_t *>(seed);
+      a.carry_n = seed != nullptr ? 1 : 0;
+      return launch_stream<SpecScanomapStepI32>(a, stream);
+    }
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 cudaError_t launch_exscan_i32(const int32_t *in, int32_t *out, int64_t n, void *scratch,
                               uint32_t epoch, int *failure, cudaStream_t stream) {
-  if (n <= 0) return cudaSuccess;
-  LookbackArgs a = make_args<K_EXSCAN_I32>(in, nullptr, out, nullptr, n, scratch, epoch, failure);
-  return launch_stream<K_EXSCAN_I32>(a, stream);
+  return launch_scan_variant_i32(0, in, out, n, 0, nullptr, scratch, epoch, failure, stream);
+}
+
+// map (scan (+) 0) over [rows][cols] i32: one scan over rows * cols elements whose head flags are
+// computed from the index (SegScan/SinglePass.hs:471-482, 594-599).
+cudaError_t launch_segscan_rows_i32(const int32_t *in, int32_t *out, int64_t rows, int64_t cols, void *scratch,
+                                    uint32_t epoch, int *failure, cudaStream_t stream) {
+  if (rows * cols <= 0) return cudaSuccess;
+  LookbackArgs a = make_args<SpecSegRowsAddI32>(in, nullptr, out, nullptr, rows * cols, scratch, epoch, failure);
+  a.seg_len = cols;
+  return launch_stream<SpecSegRowsAddI32>(a, stream);
 }
 
 // ---- pieces of a segmented scan whose array is split across several devices ---------------
@@ -664,12 +707,12 @@ cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out
     }
     return cudaSuccess;
   }
-  LookbackArgs a = make_args<K_SEGSCAN_F32>(in, flags, out, nullptr, n, scratch, epoch, failure);
+  LookbackArgs a = make_args<SpecSegScanAddF32>(in, flags, out, nullptr, n, scratch, epoch, failure);
   uint32_t bits;
   memcpy(&bits, &carry_in, 4);
   a.carry_in = bits;
   a.shard_out = shard_out;
-  return launch_stream<K_SEGSCAN_F32>(a, stream);
+  return launch_stream<SpecSegScanAddF32>(a, stream);
 }
 
 // out[i] = carry + out[i] for every i before the shard's first segment start, where carry is
@@ -679,7 +722,7 @@ cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out
 // CTA finds the start inside that one tile and finishes the elements in front of it.
 __global__ void __launch_bounds__(256)
 apply_carry_kernel(float *__restrict__ out, const uint8_t *__restrict__ flags, int64_t n, const uint32_t *summaries, int rank) {
-  constexpr int64_t TILE = TileCfg<K_SEGSCAN_F32>::TILE;
+  constexpr int64_t TILE = TileOf<SpecSegScanAddF32>::TILE;
   __shared__ int s_first;
   uint32_t cv = 0, cf = 0;
   for (int q = 0; q < rank; q++) OpSegAddF32::combine(cv, cf, summaries[4 * q], summaries[4 * q + 1], cv, cf);
@@ -718,13 +761,43 @@ cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t
   return cudaGetLastError();
 }
 
-cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out_true, uint32_t *out_false,
-                               int64_t n, int64_t *d_count, void *scratch, uint32_t epoch, int *failure,
-                               cudaStream_t stream) {
+// Compaction of n 4-byte keys under the predicate `which` (COMPACT_* of kernels.h).  Pieces of
+// at most 2^30 keys are launched one behind the other: inside a piece ranks are 32-bit, across
+// pieces the number of keys selected so far travels in *d_count (a 64-bit device word), so the
+// count is 64-bit like the reference's (prelude/soacs.fut:241-253).  `epochs` holds one fresh
+// epoch per piece (compact_pieces_needed(n) of them).
+template <typename S>
+static cudaError_t compact_pieces(const uint32_t *in, const uint8_t *flags, uint32_t *out_true, uint32_t *out_false, int64_t n,
+                                  int64_t *d_count, void *scratch, const uint32_t *epochs, int *failure, cudaStream_t stream) {
+  constexpr int64_t PIECE = (int64_t)1 << 30;
+  cudaError_t err = cudaSuccess;
+  for (int64_t lo = 0; lo < n && err == cudaSuccess; lo += PIECE) {
+    const int64_t len = n - lo < PIECE ? n - lo : PIECE;
+    LookbackArgs a = make_args<S>(in + lo, flags != nullptr ? flags + lo : nullptr, out_true, out_false, len, scratch, epochs[lo >> 30], failure);
+    a.d_count = d_count;
+    a.d_base = lo > 0 ? d_count : nullptr;
+    a.index_base = lo;
+    err = launch_stream<S>(a, stream);
+  }
+  return err;
+}
+
+int compact_pieces_needed(int64_t n) { return n <= 0 ? 1 : (int)((n + ((int64_t)1 << 30) - 1) >> 30); }
+
+cudaError_t launch_compact(int which, const void *in, const uint8_t *flags, void *out_true, void *out_false,
+                           int64_t n, int64_t *d_count, void *scratch, const uint32_t *epochs, int *failure, cudaStream_t stream) {
   if (n <= 0) return cudaMemsetAsync(d_count, 0, sizeof(int64_t), stream);
-  LookbackArgs a = make_args<K_FILTER>(in, nullptr, out_true, out_false, n, scratch, epoch, failure);   // the two kinds share their geometry
-  a.d_count = d_count;
-  return partition ? launch_stream<K_PARTITION>(a, stream) : launch_stream<K_FILTER>(a, stream);
+  const uint32_t *k = reinterpret_cast<const uint32_t *>(in);
+  uint32_t *t = reinterpret_cast<uint32_t *>(out_true), *f = reinterpret_cast<uint32_t *>(out_false);
+  switch (which) {
+    case COMPACT_FILTER_LOW3_U32: return compact_pieces<SpecFilterLow3U32>(k, nullptr, t, f, n, d_count, scratch, epochs, failure, stream);
+    case COMPACT_PARTITION_LOW3_U32: return compact_pieces<SpecPartitionLow3U32>(k, nullptr, t, f, n, d_count, scratch, epochs, failure, stream);
+    case COMPACT_FILTER_POS_I32: return compact_pieces<SpecFilterPosI32>(k, nullptr, t, f, n, d_count, scratch, epochs, failure, stream);
+    case COMPACT_PARTITION_EVEN_I32: return compact_pieces<SpecPartitionEvenI32>(k, nullptr, t, f, n, d_count, scratch, epochs, failure, stream);
+    case COMPACT_PARTITION_DIV3_I32: return compact_pieces<SpecPartitionDiv3I32>(k, nullptr, t, f, n, d_count, scratch, epochs, failure, stream);
+    case COMPACT_FILTER_BY_FLAG_I32: return compact_pieces<SpecFilterByFlagI32>(k, flags, t, f, n, d_count, scratch, epochs, failure, stream);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 // ---- a wait that runs out, on purpose -------------------------------------------------------------
@@ -758,7 +831,7 @@ cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls
 // fixed array below instead of in pooled memory.  The array is part of the loaded library
 // image: every GPU that loads the library holds these ~103 KiB until the process exits.
 constexpr int64_t NOALLOC_MAX_N = (int64_t)1 << 26;
-constexpr uint32_t NOALLOC_MAX_TILES = (uint32_t)((NOALLOC_MAX_N + TileCfg<K_SCAN_I32>::TILE - 1) / TileCfg<K_SCAN_I32>::TILE);
+constexpr uint32_t NOALLOC_MAX_TILES = (uint32_t)((NOALLOC_MAX_N + TileOf<SpecScanAddI32>::TILE - 1) / TileOf<SpecScanAddI32>::TILE);
 constexpr size_t NOALLOC_HEAD = 512;     // [0,4) ticket, [256,260) failure word
 constexpr size_t NOALLOC_BYTES = NOALLOC_HEAD + (size_t)NOALLOC_MAX_TILES * sizeof(uint64_t);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
@@ -820,12 +893,13 @@ extern "C" int futhark_b200_scan_i32_noalloc(const int32_t *in, int32_t *out, in
   if (n > 0) {
     LookbackArgs a;
     a.in = in; a.flags = nullptr; a.out = out; a.out_false = nullptr; a.n = n;
-    a.num_tiles = tiles_for<K_SCAN_I32>(n);
+    a.num_tiles = tiles_for<SpecScanAddI32>(n);
     a.ticket = reinterpret_cast<uint32_t *>(base);
     a.status = reinterpret_cast<uint64_t *>(base + NOALLOC_HEAD);
     a.epoch = epoch; a.failure = failure;
     a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr; a.shard_out = nullptr;
-    err = launch_stream<K_SCAN_I32>(a, st);
+    a.d_base = nullptr; a.index_base = 0; a.seg_len = 1;
+    err = launch_stream<SpecScanAddI32>(a, st);
     if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: kernel launch", cudaGetErrorString(err));
   }
   if (status_dev != nullptr) {

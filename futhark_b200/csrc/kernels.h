@@ -30,9 +30,24 @@ cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out
 // the first start being located through summaries[rank].
 cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
                                        int rank, int num_sms, cudaStream_t stream);
-cudaError_t launch_compact_u32(bool partition, const uint32_t *in, uint32_t *out_true, uint32_t *out_false,
-                               int64_t n, int64_t *d_count, void *scratch, uint32_t epoch, int *failure,
-                               cudaStream_t stream);
+// Scans given by another specification of the same kernel (scan_specs.cuh): variant 0 exclusive
+// (+), 1 inclusive i32.max, 2 the scanomap step of tests/soacs/scan4.fut seeded with seed_host + *seed.
+cudaError_t launch_scan_variant_i32(int variant, const int32_t *in, int32_t *out, int64_t n, int32_t seed_host, const int32_t *seed,
+                                    void *scratch, uint32_t epoch, int *failure, cudaStream_t stream);
+// map (scan (+) 0) xss over [rows][cols] i32 (regular segments, head flags from the index).
+cudaError_t launch_segscan_rows_i32(const int32_t *in, int32_t *out, int64_t rows, int64_t cols, void *scratch,
+                                    uint32_t epoch, int *failure, cudaStream_t stream);
+// Compaction of 4-byte keys.  `which` names the predicate and whether the rejected keys are
+// kept (out_false); COMPACT_FILTER_BY_FLAG_I32 keeps in[i] where flags[i] != 0.  *d_count
+// receives the number of selected keys.  The keys are worked off in pieces of 2^30; `epochs`
+// holds one fresh epoch for each of the compact_pieces_needed(n) pieces.
+enum CompactKind : int {
+  COMPACT_FILTER_LOW3_U32 = 0, COMPACT_PARTITION_LOW3_U32 = 1, COMPACT_FILTER_POS_I32 = 2,
+  COMPACT_PARTITION_EVEN_I32 = 3, COMPACT_PARTITION_DIV3_I32 = 4, COMPACT_FILTER_BY_FLAG_I32 = 5,
+};
+int compact_pieces_needed(int64_t n);
+cudaError_t launch_compact(int which, const void *in, const uint8_t *flags, void *out_true, void *out_false,
+                           int64_t n, int64_t *d_count, void *scratch, const uint32_t *epochs, int *failure, cudaStream_t stream);
 
 // ---- reductions (k_reduce.cu) ---------------------------------------------------------
 // `scratch` must hold reduce_scratch_bytes() bytes, zeroed once when allocated.
@@ -55,10 +70,20 @@ cudaError_t launch_dotprod_f32(const float *xs, const float *ys, int64_t n, floa
 cudaError_t launch_prod_of_sums_i32(const int32_t *xs, const int32_t *ys, int64_t n, int32_t *d_out, void *scratch, int num_sms, cudaStream_t stream);
 
 // ---- histograms (k_hist.cu) -------------------------------------------------------------
-// op 0: (+) on i32 weights; op 1: max on f32 weights (result in f32 bits).  `out` holds
-// B 4-byte bins and is fully overwritten.
+// out[b] = fold of the weights whose index is b, over 32-bit values; `out` holds B 4-byte bins.
+// dest == NULL: the bins start at the operator's neutral element (hist); otherwise `out`
+// starts as a copy of the B values at dest (reduce_by_index; not offered for HOP_MAX_F32).
+enum HistOpKind : int {
+  HOP_ADD_I32 = 0, HOP_MAX_F32 = 1, HOP_MIN_I32 = 2, HOP_MAX_I32 = 3, HOP_MIN_U32 = 4, HOP_MAX_U32 = 5,
+  HOP_AND_I32 = 6, HOP_OR_I32 = 7, HOP_XOR_I32 = 8, HOP_ADD_F32 = 9, HOP_MUL_I32 = 10,
+};
 cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
-                        int num_sms, cudaStream_t stream);
+                        const void *dest, int num_sms, cudaStream_t stream);
+// flat[i] = (i / cols) * B + is[i], or -1 if is[i] is outside [0, B): a histogram per row
+cudaError_t launch_flatten_rows_index(const int32_t *is, int64_t n, int64_t cols, int64_t B, int32_t *flat, int num_sms, cudaStream_t stream);
+// flat[i] = is[i] * M + js[i], or -1 if either index is out of range: reduce_by_index_2d
+cudaError_t launch_flatten_2d_index(const int64_t *is, const int64_t *js, int64_t n, int64_t N, int64_t M, int32_t *flat, int num_sms,
+                                    cudaStream_t stream);
 
 // ---- layout operations (k_layout.cu) ----------------------------------------------------------
 // out[b][c][r] = in[b][r][c] for 4-byte elements.

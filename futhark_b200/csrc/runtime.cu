@@ -606,6 +606,9 @@ FB_ARRAY_1D(u32_1d, uint32_t)
 FB_ARRAY_1D(f32_1d, float)
 FB_ARRAY_1D(bool_1d, bool)
 FB_ARRAY_2D(f32_2d, float)
+FB_ARRAY_2D(i32_2d, int32_t)
+FB_ARRAY_2D(i64_2d, int64_t)
+FB_ARRAY_1D(f64_1d, double)
 FB_ARRAY_3D(f32_3d, float)
 FB_ARRAY_3D(f16_3d, uint16_t)
 

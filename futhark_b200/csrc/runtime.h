@@ -131,12 +131,19 @@ FB_DEFINE_ARRAY_STRUCT(u32_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(bool_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_2d, 2)
+FB_DEFINE_ARRAY_STRUCT(i32_2d, 2)
+FB_DEFINE_ARRAY_STRUCT(i64_2d, 2)
+FB_DEFINE_ARRAY_STRUCT(f64_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_3d, 3)
 FB_DEFINE_ARRAY_STRUCT(f16_3d, 3)
 
 struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 {
   futhark_u32_1d *v0;
   futhark_u32_1d *v1;
+};
+
+struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 {
+  futhark_i32_1d *v[3];
 };
 
 struct futhark_opaque_tup2_i32_f32 {

@@ -134,6 +134,9 @@ FUTHARK_B200_ARRAY_1D(u32_1d, uint32_t)
 FUTHARK_B200_ARRAY_1D(f32_1d, float)
 FUTHARK_B200_ARRAY_1D(bool_1d, bool)
 FUTHARK_B200_ARRAY_2D(f32_2d, float)
+FUTHARK_B200_ARRAY_2D(i32_2d, int32_t)
+FUTHARK_B200_ARRAY_2D(i64_2d, int64_t)
+FUTHARK_B200_ARRAY_1D(f64_1d, double)
 FUTHARK_B200_ARRAY_3D(f32_3d, float)
 FUTHARK_B200_ARRAY_3D(f16_3d, uint16_t)
 
@@ -158,6 +161,18 @@ int futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_0(struct futhark_context *ct
 int futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(struct futhark_context *ctx,
                                                       struct futhark_u32_1d **out,
                                                       const struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *obj);
+
+/* ---- opaque triple of i32 arrays returned by partition2_i32 (same naming rule); `free`
+ *      releases the three arrays, the projections share them (docs/c-api.rst:383-391) ---------- */
+struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32;
+int futhark_free_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(struct futhark_context *ctx,
+                                                           struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_0(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                                const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                                const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_2(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                                const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
 
 /* ---- opaque tuple (i32, f32) returned by sum_i32_f32: same naming and functions; its
  *      fields are scalars, so `new` takes and the projections return them by value ---------- */
@@ -225,10 +240,59 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
                                const int64_t in0, const struct futhark_i32_1d *in1,
                                const struct futhark_f32_1d *in2);
 
+/* The histogram kernels under other operators and index spaces.  The reference chooses per
+ * operator between a native atomic, a compare-and-swap loop and a lock
+ * (src/Futhark/CodeGen/ImpGen/GPU/Base.hs:720-905, table ImpGen/GPU.hs:46-90); here the operator is
+ * a template parameter of the same three kernels.  Indices are i32, widened to i64 as in
+ * `map i64.i32 is`; out-of-range indices are ignored.
+ *
+ * entry hist_and_i32 (n: i64) (is: []i32) (vs: []i32): [n]i32 = hist (i32.&) (-1) n (map i64.i32 is) vs   (tests/hist/and.fut)
+ * entry hist_or_i32  ... = hist (i32.|) 0 n ...                                                  (tests/hist/or.fut)
+ * entry hist_xor_i32 ... = hist (i32.^) 0 n ...                                                  (tests/hist/xor.fut)
+ * entry hist_mul_i32 ... = hist (i32.*) 1 n ...      (no native atomic: a compare-and-swap loop, Base.hs:844-905)
+ * entry reduce_by_index_min_i32 (dest: *[n]i32) (is: []i32) (vs: []i32): [n]i32 =
+ *   reduce_by_index dest i32.min i32.highest (map i64.i32 is) vs        (tests/hist/min.fut, first result)
+ * entry reduce_by_index_min_u32 ... u32.min u32.highest ...            (tests/hist/min.fut, second result)
+ * entry reduce_by_index_max_i32, reduce_by_index_max_u32 ... max / lowest (tests/hist/max.fut)
+ * entry reduce_by_index_add_f32 (dest: *[n]f32) (is: []i32) (vs: []f32): [n]f32 =
+ *   reduce_by_index dest (+) 0f32 (map i64.i32 is) vs                   (tests/hist/f32.fut; NaN propagates)
+ * entry hist_rows_add_i32 (m: i64) (iss: [][]i32) (vss: [][]i32): [][m]i32 =
+ *   map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss           (tests/hist/segmented.fut: the segment
+ *   dimension of a SegHist, SegHist.hs:97-148)
+ * entry reduce_by_index_2d_add_i32 (dest: *[n][m]i32) (is: []i64) (js: []i64) (vs: []i32): [n][m]i32 =
+ *   reduce_by_index_2d dest (+) 0 (zip is js) vs                        (prelude/soacs.fut:149-152; tests/hist/hist2d.fut) */
+#define FUTHARK_B200_HIST_ENTRY(NAME, ARR)                                                          \
+  int futhark_entry_hist_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0,           \
+                                const int64_t in0, const struct futhark_i32_1d *in1,               \
+                                const struct futhark_##ARR *in2);
+FUTHARK_B200_HIST_ENTRY(and_i32, i32_1d)
+FUTHARK_B200_HIST_ENTRY(or_i32, i32_1d)
+FUTHARK_B200_HIST_ENTRY(xor_i32, i32_1d)
+FUTHARK_B200_HIST_ENTRY(mul_i32, i32_1d)
+#define FUTHARK_B200_RBI_ENTRY(NAME, ARR)                                                           \
+  int futhark_entry_reduce_by_index_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0,\
+                                           const struct futhark_##ARR *in0,                        \
+                                           const struct futhark_i32_1d *in1,                       \
+                                           const struct futhark_##ARR *in2);
+FUTHARK_B200_RBI_ENTRY(min_i32, i32_1d)
+FUTHARK_B200_RBI_ENTRY(max_i32, i32_1d)
+FUTHARK_B200_RBI_ENTRY(min_u32, u32_1d)
+FUTHARK_B200_RBI_ENTRY(max_u32, u32_1d)
+FUTHARK_B200_RBI_ENTRY(add_f32, f32_1d)
+int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
+                                    const int64_t in0, const struct futhark_i32_2d *in1,
+                                    const struct futhark_i32_2d *in2);
+int futhark_entry_reduce_by_index_2d_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
+                                             const struct futhark_i32_2d *in0,
+                                             const struct futhark_i64_1d *in1,
+                                             const struct futhark_i64_1d *in2,
+                                             const struct futhark_i32_1d *in3);
+
 /* entry filter_u32 (ks: []u32): []u32 = filter (\k -> (k & 7) < 3) ks
  * entry partition_u32 (ks: []u32): ([]u32, []u32) = partition (\k -> (k & 7) < 3) ks
  * (prelude/soacs.fut:241-286: stable; the split count is shape[0] of field 0).
- * Both read the result size back, so they synchronise. */
+ * Both read the result size back, so they synchronise.  Counts are 64-bit as in the
+ * reference: more than 2^31 keys are worked off in pieces of 2^30 inside one call. */
 int futhark_entry_filter_u32(struct futhark_context *ctx, struct futhark_u32_1d **out0,
                              const struct futhark_u32_1d *in0);
 int futhark_entry_partition_u32(struct futhark_context *ctx,
@@ -253,6 +317,36 @@ int futhark_entry_transpose_f32(struct futhark_context *ctx, struct futhark_f32_
                                 const struct futhark_f32_2d *in0);
 int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f32_3d **out0,
                                    const struct futhark_f32_3d *in0);
+
+/* Other scans, segmented scans, filters and partitions: the same single-pass kernel under other
+ * specifications (operator, fused map body, post-operation, flag source, predicate), where the
+ * reference generates a kernel per program from the same pieces (src/Futhark/CodeGen/ImpGen/GPU/
+ * SegScan.hs:17-90, SegScan/SinglePass.hs:327-879; prelude/soacs.fut:241-323).
+ *
+ * entry scan_max_i32 (xs: []i32): []i32 = scan i32.max i32.lowest xs
+ * entry segscan_rows_i32 (xss: [][]i32): [][]i32 = map (scan (+) 0) xss   (tests/intrablock/segscan0.fut;
+ *   a regular segmented scan: the innermost dimension is the segment, SegScan/SinglePass.hs:471-482,594-599)
+ * entry scanomap_steps_i32 (xs: []i32): []i32 = main of tests/soacs/scan4.fut:20-22: two rounds of
+ *   xs' = map2 (+) (map (+ sum) (scan (+) 0 (map (+1) xs))) xs, sum = reduce (+) 0 (map (+1) xs):
+ *   the map body in front of the scan and the post-operation behind it run inside the scan kernel
+ * entry filter_pos_i32 (xs: []i32): []i32 = filter (0 <) xs                (tests/soacs/filter1.fut)
+ * entry filter_by_flag_i32 (xs: []i32) (keep: []bool): []i32 = (unzip (filter (.1) (zip xs keep))).0
+ *   (tests/soacs/filter3.fut: the predicate reads a second array)
+ * entry partition2_i32 (xs: []i32): ([]i32, []i32, []i32) =
+ *   partition2 (\x -> x % 2 == 0) (\x -> x % 3 == 0) xs   (tests/soacs/partition1.fut; prelude/soacs.fut:293-323) */
+int futhark_entry_scan_max_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                               const struct futhark_i32_1d *in0);
+int futhark_entry_segscan_rows_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
+                                   const struct futhark_i32_2d *in0);
+int futhark_entry_scanomap_steps_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                                     const struct futhark_i32_1d *in0);
+int futhark_entry_filter_pos_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                                 const struct futhark_i32_1d *in0);
+int futhark_entry_filter_by_flag_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                                     const struct futhark_i32_1d *in0, const struct futhark_bool_1d *in1);
+int futhark_entry_partition2_i32(struct futhark_context *ctx,
+                                 struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **out0,
+                                 const struct futhark_i32_1d *in0);
 
 /* Fused and multi-operator SegOps.  The reference generates ONE kernel for a map body fused
  * with one or several reduction operators (src/Futhark/CodeGen/ImpGen/GPU/SegRed.hs:99-100,

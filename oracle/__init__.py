@@ -21,7 +21,7 @@ def lib():
     global _lib
     if _lib is None:
         path = os.path.join(_HERE, "liboracle.so")
-        if not os.path.exists(path) or os.path.getmtime(path) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
+        if not os.path.exists(path) or os.path.getmtime(path) < max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("oracle.c", "oracle_ext.c")):
             _build.build()
         L = ctypes.CDLL(path)
         i64, i32, vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
@@ -50,6 +50,17 @@ def lib():
         L.orc_partition_u32.argtypes = [vp, i64, vp, i32]
         L.orc_bmm_f16.argtypes = [vp, vp, i64, i64, i64, i64, vp, i32]
         L.orc_mm_f32.argtypes = [vp, vp, i64, i64, i64, vp]
+        L.orc_scan_max_i32.argtypes = [vp, i64, vp]
+        L.orc_segscan_rows_i32.argtypes = [vp, i64, i64, vp]
+        L.orc_scanomap_steps_i32.argtypes = [vp, i64, vp]
+        L.orc_filter_pos_i32.restype = i64
+        L.orc_filter_pos_i32.argtypes = [vp, i64, vp]
+        L.orc_filter_by_flag_i32.restype = i64
+        L.orc_filter_by_flag_i32.argtypes = [vp, vp, i64, vp]
+        L.orc_partition2_i32.argtypes = [vp, i64, vp, vp]
+        L.orc_reduce_by_index_32.argtypes = [i32, vp, i64, vp, vp, i64]
+        L.orc_hist_rows_add_i32.argtypes = [i64, vp, vp, i64, i64, vp]
+        L.orc_reduce_by_index_2d_add_i32.argtypes = [vp, i64, i64, vp, vp, vp, i64]
         L.orc_half_to_float.restype = ctypes.c_float
         L.orc_half_to_float.argtypes = [ctypes.c_uint16]
         L.orc_add32.restype = ctypes.c_uint32
@@ -349,3 +360,83 @@ def ref_read_value(tname, data, rank, dtype):
     out = np.frombuffer(ctypes.string_at(ptr.value, count * np.dtype(dtype).itemsize), dtype).reshape(dims).copy()
     R.ref_free(ptr)
     return 0, out
+
+
+# ---- the entry points of oracle_ext.c ---------------------------------------------------------
+
+def scan_max_i32(xs):
+    xs = _c(xs, np.int32)
+    out = np.empty_like(xs)
+    lib().orc_scan_max_i32(_p(xs), xs.size, _p(out))
+    return out
+
+
+def segscan_rows_i32(xss):
+    xss = _c(xss, np.int32)
+    out = np.empty_like(xss)
+    lib().orc_segscan_rows_i32(_p(xss), xss.shape[0], xss.shape[1], _p(out))
+    return out
+
+
+def scanomap_steps_i32(xs):
+    xs = _c(xs, np.int32)
+    out = np.empty_like(xs)
+    lib().orc_scanomap_steps_i32(_p(xs), xs.size, _p(out))
+    return out
+
+
+def filter_pos_i32(xs):
+    xs = _c(xs, np.int32)
+    out = np.empty_like(xs)
+    k = lib().orc_filter_pos_i32(_p(xs), xs.size, _p(out))
+    return out[:k].copy()
+
+
+def filter_by_flag_i32(xs, keep):
+    xs, keep = _c(xs, np.int32), _c(np.asarray(keep).astype(np.uint8), np.uint8)
+    out = np.empty_like(xs)
+    k = lib().orc_filter_by_flag_i32(_p(xs), _p(keep), xs.size, _p(out))
+    return out[:k].copy()
+
+
+def partition2_i32(xs):
+    xs = _c(xs, np.int32)
+    out = np.empty_like(xs)
+    counts = np.zeros(3, np.int64)
+    lib().orc_partition2_i32(_p(xs), xs.size, _p(out), _p(counts))
+    a, b = int(counts[0]), int(counts[0] + counts[1])
+    return out[:a].copy(), out[a:b].copy(), out[b:].copy()
+
+
+HIST_OPS = {"add_i32": (0, np.int32, 0), "min_i32": (2, np.int32, 2 ** 31 - 1), "max_i32": (3, np.int32, -2 ** 31),
+            "min_u32": (4, np.uint32, 2 ** 32 - 1), "max_u32": (5, np.uint32, 0), "and_i32": (6, np.int32, -1),
+            "or_i32": (7, np.int32, 0), "xor_i32": (8, np.int32, 0), "add_f32": (9, np.float32, 0.0), "mul_i32": (10, np.int32, 1)}
+
+
+def reduce_by_index(op, dest, is_, vs):
+    """reduce_by_index dest op ne (map i64.i32 is) vs for an operator name of HIST_OPS."""
+    code, dt, _ = HIST_OPS[op]
+    dest = _c(dest, dt).copy()
+    is_, vs = _c(is_, np.int32), _c(vs, dt)
+    lib().orc_reduce_by_index_32(code, _p(dest), dest.size, _p(is_), _p(vs), is_.size)
+    return dest
+
+
+def hist(op, B, is_, vs):
+    """hist op ne B (map i64.i32 is) vs."""
+    _, dt, ne = HIST_OPS[op]
+    return reduce_by_index(op, np.full(B, ne, dtype=dt), is_, vs)
+
+
+def hist_rows_add_i32(m, iss, vss):
+    iss, vss = _c(iss, np.int32), _c(vss, np.int32)
+    out = np.empty((iss.shape[0], m), np.int32)
+    lib().orc_hist_rows_add_i32(m, _p(iss), _p(vss), iss.shape[0], iss.shape[1], _p(out))
+    return out
+
+
+def reduce_by_index_2d_add_i32(dest, is_, js, vs):
+    dest = _c(dest, np.int32).copy()
+    is_, js, vs = _c(is_, np.int64), _c(js, np.int64), _c(vs, np.int32)
+    lib().orc_reduce_by_index_2d_add_i32(_p(dest), dest.shape[0], dest.shape[1], _p(is_), _p(js), _p(vs), is_.size)
+    return dest

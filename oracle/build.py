@@ -1,7 +1,8 @@
 """Build recipe for the CPU oracle (test infrastructure, not product code).
 
-`build()` compiles oracle/oracle.c into oracle/liboracle.so and, when a checkout of
-the reference is present, the scalar shim oracle/ref_scalar.c against the
+`build()` compiles oracle/oracle.c and oracle/oracle_ext.c into oracle/liboracle.so and, when a
+checkout of the reference is found (environment variable FUTHARK_REFERENCE, else a directory
+`reference` beside the repository), the scalar shim oracle/ref_scalar.c against the
 reference's own rts/c headers into oracle/_ref/libref_scalar.so, and likewise
 oracle/ref_copy.c against rts/c/copy.h into oracle/_ref/libref_copy.so and
 oracle/ref_values.c against rts/c/values.h into oracle/_ref/libref_values.so.  Nothing from the
@@ -12,7 +13,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_RTS = os.environ.get("FUTHARK_REFERENCE_RTS", "/root/reference/rts/c")
+REFERENCE = os.environ.get("FUTHARK_REFERENCE", os.path.join(HERE, "..", "..", "reference"))
+REFERENCE_RTS = os.path.join(REFERENCE, "rts", "c")
 
 
 def _stale(target, sources):
@@ -23,11 +25,10 @@ def _stale(target, sources):
 
 
 def build(force=False, verbose=False):
-    src = os.path.join(HERE, "oracle.c")
+    srcs = [os.path.join(HERE, "oracle.c"), os.path.join(HERE, "oracle_ext.c")]
     lib = os.path.join(HERE, "liboracle.so")
-    if force or _stale(lib, [src]):
-        cmd = ["gcc", "-O3", "-std=c99", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC",
-               src, "-o", lib, "-lm"]
+    if force or _stale(lib, srcs):
+        cmd = ["gcc", "-O3", "-std=c99", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC"] + srcs + ["-o", lib, "-lm"]
         if verbose:
             print(" ".join(cmd))
         subprocess.check_call(cmd)

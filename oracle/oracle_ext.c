@@ -1,0 +1,119 @@
+/* CPU oracle, second part: the entry points that put the scan, compaction and histogram
+ * kernels under other operators, predicates and index spaces.
+ *
+ * TEST INFRASTRUCTURE ONLY, like oracle.c: used by the parity tests, never by the shipped
+ * library.  Every function restates the Futhark definition of its entry point literally
+ * (sequential loops; these entry points are not part of the timed baseline).
+ *
+ * Parity status: pinned against the reference's own known-answer tests
+ * tests/soacs/filter1.fut, filter3.fut, partition1.fut, scan4.fut,
+ * tests/hist/and.fut, or.fut, xor.fut, min.fut, max.fut, f32.fut, segmented.fut, hist2d.fut.
+ * tests/intrablock/segscan0.fut carries no values ("auto output"); the regular segmented scan
+ * of i32 is fixed by its definition alone (integer arithmetic), as is scan i32.max.
+ *
+ * Scalar semantics follow rts/c/scalar.h: add32 / mul32 wrap (:29, :41), smin/smax/umin/umax
+ * (:96-167), and/or/xor (:199-229), fadd32 (:865).  Futhark's x % m is the floored modulus
+ * (smod32, scalar.h:352-361): it is 0 exactly when the C remainder is 0.
+ */
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+static int32_t wadd(int32_t a, int32_t b) { return (int32_t)((uint32_t)a + (uint32_t)b); }
+
+/* scan i32.max i32.lowest xs (prelude/soacs.fut:176-178 with the operator of scalar.h:146) */
+void orc_scan_max_i32(const int32_t *xs, int64_t n, int32_t *out) {
+  int32_t acc = INT32_MIN;
+  for (int64_t i = 0; i < n; i++) { acc = xs[i] > acc ? xs[i] : acc; out[i] = acc; }
+}
+
+/* map (scan (+) 0) xss (tests/intrablock/segscan0.fut:8-10) */
+void orc_segscan_rows_i32(const int32_t *xss, int64_t rows, int64_t cols, int32_t *out) {
+  for (int64_t r = 0; r < rows; r++) {
+    int32_t acc = 0;
+    for (int64_t c = 0; c < cols; c++) { acc = wadd(acc, xss[r * cols + c]); out[r * cols + c] = acc; }
+  }
+}
+
+/* tests/soacs/scan4.fut:11-22, statement by statement */
+static void scan4_step(const int32_t *xs, int64_t n, int32_t *out) {
+  int32_t bits_sum = 0;
+  for (int64_t i = 0; i < n; i++) bits_sum = wadd(bits_sum, wadd(xs[i], 1));   /* reduce (+) 0 (map (+1) xs) */
+  int32_t ps = 0;
+  for (int64_t i = 0; i < n; i++) {
+    ps = wadd(ps, wadd(xs[i], 1));                    /* ps1 = scan (+) 0 bits */
+    out[i] = wadd(wadd(ps, bits_sum), xs[i]);         /* map2 (+) (map (+ bits_sum) ps1) xs */
+  }
+}
+void orc_scanomap_steps_i32(const int32_t *xs, int64_t n, int32_t *out) {
+  int32_t *tmp = (int32_t *)malloc((size_t)(n > 0 ? n : 1) * sizeof(int32_t));
+  scan4_step(xs, n, tmp);
+  scan4_step(tmp, n, out);
+  free(tmp);
+}
+
+/* filter (0 <) xs (tests/soacs/filter1.fut:14; prelude/soacs.fut:241-253) */
+int64_t orc_filter_pos_i32(const int32_t *xs, int64_t n, int32_t *out) {
+  int64_t k = 0;
+  for (int64_t i = 0; i < n; i++) if (0 < xs[i]) out[k++] = xs[i];
+  return k;
+}
+
+/* (unzip (filter (.1) (zip xs keep))).0 (tests/soacs/filter3.fut:11-19) */
+int64_t orc_filter_by_flag_i32(const int32_t *xs, const uint8_t *keep, int64_t n, int32_t *out) {
+  int64_t k = 0;
+  for (int64_t i = 0; i < n; i++) if (keep[i]) out[k++] = xs[i];
+  return k;
+}
+
+/* partition2 (x % 2 == 0) (x % 3 == 0) xs (tests/soacs/partition1.fut:13-18; prelude/soacs.fut:293-323):
+ * out = group 0 ++ group 1 ++ group 2, each in original order; counts[0..2] their sizes. */
+void orc_partition2_i32(const int32_t *xs, int64_t n, int32_t *out, int64_t *counts) {
+  int64_t c[3] = {0, 0, 0};
+  for (int64_t i = 0; i < n; i++) c[xs[i] % 2 == 0 ? 0 : (xs[i] % 3 == 0 ? 1 : 2)]++;
+  int64_t o[3] = {0, c[0], c[0] + c[1]};
+  for (int64_t i = 0; i < n; i++) out[o[xs[i] % 2 == 0 ? 0 : (xs[i] % 3 == 0 ? 1 : 2)]++] = xs[i];
+  memcpy(counts, c, sizeof(c));
+}
+
+/* reduce_by_index dest op ne is vs over 32-bit values (prelude/soacs.fut:117-130): dest is updated
+ * in place; indices outside [0, B) are ignored.  op: 0 add i32, 2 min i32, 3 max i32, 4 min u32,
+ * 5 max u32, 6 and, 7 or, 8 xor, 9 add f32 (sequential order), 10 mul i32 (numbering of the
+ * library's operator list; 1, the f32 max, is orc_hist_max_f32 in oracle.c). */
+void orc_reduce_by_index_32(int op, uint32_t *dest, int64_t B, const int32_t *is, const uint32_t *vs, int64_t n) {
+  for (int64_t i = 0; i < n; i++) {
+    const int64_t b = (int64_t)is[i];
+    if (b < 0 || b >= B) continue;
+    const uint32_t a = dest[b], v = vs[i];
+    uint32_t r;
+    switch (op) {
+      case 0: r = a + v; break;
+      case 2: r = (uint32_t)((int32_t)a < (int32_t)v ? (int32_t)a : (int32_t)v); break;
+      case 3: r = (uint32_t)((int32_t)a > (int32_t)v ? (int32_t)a : (int32_t)v); break;
+      case 4: r = a < v ? a : v; break;
+      case 5: r = a > v ? a : v; break;
+      case 6: r = a & v; break;
+      case 7: r = a | v; break;
+      case 8: r = a ^ v; break;
+      case 9: { float fa, fv; memcpy(&fa, &a, 4); memcpy(&fv, &v, 4); fa = fa + fv; memcpy(&r, &fa, 4); break; }
+      default: r = a * v; break;
+    }
+    dest[b] = r;
+  }
+}
+
+/* map2 (\is vs -> hist (+) 0 m is vs) iss vss (tests/hist/segmented.fut:9-10) */
+void orc_hist_rows_add_i32(int64_t m, const int32_t *iss, const int32_t *vss, int64_t rows, int64_t cols, int32_t *out) {
+  memset(out, 0, (size_t)(rows * m) * sizeof(int32_t));
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t c = 0; c < cols; c++) {
+      const int64_t b = (int64_t)iss[r * cols + c];
+      if (b >= 0 && b < m) out[r * m + b] = wadd(out[r * m + b], vss[r * cols + c]);
+    }
+}
+
+/* reduce_by_index_2d dest (+) 0 (zip is js) vs (prelude/soacs.fut:149-152): dest [N][M] updated in place */
+void orc_reduce_by_index_2d_add_i32(int32_t *dest, int64_t N, int64_t M, const int64_t *is, const int64_t *js, const int32_t *vs, int64_t n) {
+  for (int64_t i = 0; i < n; i++)
+    if (is[i] >= 0 && is[i] < N && js[i] >= 0 && js[i] < M) dest[is[i] * M + js[i]] = wadd(dest[is[i] * M + js[i]], vs[i]);
+}

@@ -2,7 +2,7 @@
 test programs and writes them to reference_vectors.json (committed beside this script).
 
 Run in a container that has the reference checkout:
-    python tests/golden/extract_reference_vectors.py [/path/to/reference]
+    python tests/golden/extract_reference_vectors.py /path/to/reference
 
 Each `.fut` test file carries `-- ==` blocks with `input { ... } output { ... }` pairs
 (format: docs/man/futhark-test.rst:20-120 of the reference).  Only blocks with literal
@@ -31,6 +31,14 @@ FILES = [
     "tests/soacs/exscan0.fut",
     "tests/soacs/exscan1.fut",
     "tests/modules/functor1.fut",
+    "tests/soacs/filter3.fut",
+    "tests/soacs/scan4.fut",
+    "tests/hist/and.fut",
+    "tests/hist/or.fut",
+    "tests/hist/xor.fut",
+    "tests/hist/min.fut",
+    "tests/hist/segmented.fut",
+    "tests/hist/hist2d.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f32\.nan|f32\.inf|-f32\.inf|true|false|"
@@ -111,7 +119,9 @@ def blocks(path):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: extract_reference_vectors.py /path/to/reference")
+    ref = sys.argv[1]
     out = {}
     for f in FILES:
         cases = []

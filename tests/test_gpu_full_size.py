@@ -234,11 +234,32 @@ def test_beyond_2p31_elements(ctx, dev):
     l1 = sum(float(x[lo:min(lo + step, n)].double().abs().sum().item()) for lo in range(0, n, step))
     assert abs(sf - ref) <= 1e-5 * l1
     out.free()
-    # compaction states its limit instead of overflowing a 32-bit count
+    # compaction counts in 64 bits: the keys are worked off in pieces of 2^30 inside one call
     ka = ctx.new_raw("u32_1d", x.data_ptr(), n)
-    with pytest.raises(fb.FutharkError) as e:
-        ctx.entry_filter_u32(ka)
-    assert "2^31-1" in e.value.message
+    sel = ctx.entry_filter_u32(ka)
+    mask = (x & 7) < 3
+    cnt = int(mask.sum())
+    assert sel.shape == (cnt,)
+    sv = view(sel, dev, torch.int32)
+    for lo in range(0, n, step):                                # compare piecewise to bound the temporaries
+        hi = min(lo + step, n)
+        before = int(mask[:lo].sum())
+        part = x[lo:hi][mask[lo:hi]]
+        assert torch.equal(sv[before:before + part.numel()], part)
+    sel.free()
+    pair = ctx.entry_partition_u32(ka)
+    ps, pr = pair.project(0), pair.project(1)
+    pair.free()
+    assert ps.shape == (cnt,) and pr.shape == (n - cnt,)
+    rv = view(pr, dev, torch.int32)
+    for lo in range(0, n, step):
+        hi = min(lo + step, n)
+        before = lo - int(mask[:lo].sum())
+        part = x[lo:hi][~mask[lo:hi]]
+        assert torch.equal(rv[before:before + part.numel()], part)
+    assert torch.equal(view(ps, dev, torch.int32)[-1000:], x[mask][-1000:])
+    ps.free(); pr.free()
+    del mask
     ka.free(); a.free()
     del o, x
     u = torch.randn(n, device=dev, generator=gen(dev, 9))

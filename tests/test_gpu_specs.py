@@ -1,0 +1,169 @@
+"""GPU parity of the entry points that put the scan, compaction and histogram kernels under
+other operators, map bodies, predicates and index spaces: against the reference's own
+known-answer vectors (tests/golden/reference_vectors.json) and, on seeded inputs of many
+sizes, bit for bit against the CPU oracle (everything here is integer, index or compaction
+work except the f32 histogram sum, which is compared within 1e-5 of the L1 norm)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import futhark_b200 as fb
+import oracle
+from futhark_b200 import datagen
+from util import SIZES, TILE
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_vectors.json")))
+BIG = [1 << 20, (1 << 21) + 77]
+
+
+def _f(v):
+    return [float("nan") if x == "nan" else float(x) for x in v]
+
+
+# ---- the reference's vectors, through the C ABI on the GPU ----------------------------------
+
+def test_reference_vectors_scans_and_compaction(ctx):
+    for c in GOLDEN["tests/soacs/filter1.fut"]:
+        assert fb.filter_pos_i32(ctx, np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+    for c in GOLDEN["tests/soacs/filter3.fut"]:
+        assert fb.filter_by_flag_i32(ctx, np.array(c["input"][0], np.int32), np.array(c["input"][1], np.bool_)).tolist() == c["output"][1]
+    for c in GOLDEN["tests/soacs/partition1.fut"]:
+        assert [g.tolist() for g in fb.partition2_i32(ctx, np.array(c["input"][0], np.int32))] == c["output"]
+    for c in GOLDEN["tests/soacs/scan4.fut"]:
+        assert fb.scanomap_steps_i32(ctx, np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+
+
+def test_reference_vectors_histograms(ctx):
+    for name, op in (("tests/hist/and.fut", "and_i32"), ("tests/hist/or.fut", "or_i32"), ("tests/hist/xor.fut", "xor_i32")):
+        for c in GOLDEN[name]:
+            n, is_, image = c["input"]
+            assert fb.hist_op(ctx, op, n, np.array(is_, np.int32), np.array(image, np.int32)).tolist() == c["output"][0]
+    for name, sop, uop in (("tests/hist/min.fut", "min_i32", "min_u32"), ("tests/hist/max.fut", "max_i32", "max_u32")):
+        for c in GOLDEN[name]:
+            n, is_, image = c["input"]
+            is_ = np.array(is_, np.int32)
+            assert fb.reduce_by_index(ctx, sop, np.zeros(n, np.int32), is_, np.array(image, np.int32)).tolist() == c["output"][0]
+            got = fb.reduce_by_index(ctx, uop, np.zeros(n, np.uint32), is_, np.array(image, np.int32).view(np.uint32))
+            assert got.view(np.int32).tolist() == c["output"][1]
+    for c in GOLDEN["tests/hist/f32.fut"]:
+        dest, is_, image = c["input"]
+        got = fb.reduce_by_index(ctx, "add_f32", np.array(_f(dest), np.float32), np.array(is_, np.int32), np.array(_f(image), np.float32))
+        assert np.allclose(got, np.array(_f(c["output"][0]), np.float32), rtol=1e-6, equal_nan=True)
+    for c in GOLDEN["tests/hist/segmented.fut"]:
+        m, xss = c["input"]
+        xss = np.array(xss, np.int32)
+        assert fb.hist_rows_add_i32(ctx, m, xss, np.ones_like(xss)).tolist() == c["output"][0]
+    for c in GOLDEN["tests/hist/hist2d.fut"]:
+        xss, is_, js, vs = c["input"]
+        got = fb.reduce_by_index_2d_add_i32(ctx, np.array(xss, np.int32), np.array(is_, np.int64), np.array(js, np.int64), np.array(vs, np.int32))
+        assert got.tolist() == c["output"][0]
+
+
+# ---- against the oracle on seeded inputs ---------------------------------------------------------
+
+@pytest.mark.parametrize("n", SIZES + BIG)
+def test_scan_max_and_scanomap_steps(ctx, n):
+    xs = datagen.uniform_i32(61, 0, n, -100000, 100000)
+    assert np.array_equal(fb.scan_max_i32(ctx, xs), oracle.scan_max_i32(xs))
+    assert np.array_equal(fb.scanomap_steps_i32(ctx, xs), oracle.scanomap_steps_i32(xs))
+
+
+@pytest.mark.parametrize("rows,cols", [(0, 5), (5, 0), (1, 1), (1, 256), (16, 16), (256, 1), (3, 100003), (1000, 1000), (100003, 3),
+                                        (7, TILE), (9, TILE + 1), (2, 4 * TILE - 1), (50000, 41)])
+def test_segscan_rows_i32(ctx, rows, cols):
+    xss = datagen.uniform_i32(62, 0, rows * cols, -1000, 1000).reshape(rows, cols)
+    got = fb.segscan_rows_i32(ctx, xss)
+    assert got.shape == (rows, cols)
+    assert np.array_equal(got, oracle.segscan_rows_i32(xss))
+
+
+@pytest.mark.parametrize("n", SIZES + BIG)
+def test_filters_and_partition2(ctx, n):
+    xs = datagen.uniform_i32(63, 0, n, -50, 50)
+    assert np.array_equal(fb.filter_pos_i32(ctx, xs), oracle.filter_pos_i32(xs))
+    keep = (datagen.uniform_i32(64, 0, n, 0, 99) < 30)
+    assert np.array_equal(fb.filter_by_flag_i32(ctx, xs, keep), oracle.filter_by_flag_i32(xs, keep))
+    got, want = fb.partition2_i32(ctx, xs), oracle.partition2_i32(xs)
+    assert all(np.array_equal(g, w) for g, w in zip(got, want))
+    assert sum(len(g) for g in got) == n
+
+
+def test_compaction_extremes(ctx):
+    n = 3 * 9216 + 5
+    for xs in (np.full(n, 6, np.int32), np.full(n, 1, np.int32), np.full(n, -3, np.int32), np.full(n, 9, np.int32)):
+        assert np.array_equal(fb.filter_pos_i32(ctx, xs), oracle.filter_pos_i32(xs))
+        got, want = fb.partition2_i32(ctx, xs), oracle.partition2_i32(xs)
+        assert all(np.array_equal(g, w) for g, w in zip(got, want))
+    for keep in (np.zeros(n, np.bool_), np.ones(n, np.bool_)):
+        assert np.array_equal(fb.filter_by_flag_i32(ctx, np.arange(n, dtype=np.int32), keep), oracle.filter_by_flag_i32(np.arange(n, dtype=np.int32), keep))
+
+
+@pytest.mark.parametrize("B", [1, 7, 256, 5000, 57344, 65536, 200000, 300000])
+@pytest.mark.parametrize("op", ["and_i32", "or_i32", "xor_i32", "mul_i32"])
+def test_hist_other_operators(ctx, op, B):
+    n = 200003
+    bins = datagen.hist_bins(71, 0, n, B, "zipf" if B >= 256 and (B & (B - 1)) == 0 else "uniform")
+    ws = datagen.uniform_i32(72, 0, n, -3, 3) if op == "mul_i32" else datagen.uniform_i32(72, 0, n, -2 ** 31, 2 ** 31 - 1)
+    assert np.array_equal(fb.hist_op(ctx, op, B, bins, ws), oracle.hist(op, B, bins, ws))
+
+
+@pytest.mark.parametrize("B", [1, 256, 5000, 65536, 300000])
+@pytest.mark.parametrize("op", ["min_i32", "max_i32", "min_u32", "max_u32"])
+def test_reduce_by_index_min_max(ctx, op, B):
+    n = 200003
+    dt = np.uint32 if op.endswith("u32") else np.int32
+    bins = datagen.hist_bins(73, 0, n, B, "uniform")
+    ws = datagen.uniform_i32(74, 0, n, -2 ** 31, 2 ** 31 - 1).view(dt)
+    dest = datagen.uniform_i32(75, 0, B, -2 ** 31, 2 ** 31 - 1).view(dt)
+    assert np.array_equal(fb.reduce_by_index(ctx, op, dest, bins, ws), oracle.reduce_by_index(op, dest, bins, ws))
+
+
+@pytest.mark.parametrize("B", [3, 256, 65536, 300000])
+def test_reduce_by_index_add_f32(ctx, B):
+    n = 200003
+    bins = datagen.hist_bins(76, 0, n, B, "uniform")
+    ws = datagen.normal_f32(77, 0, n)
+    dest = datagen.normal_f32(78, 0, B)
+    got = fb.reduce_by_index(ctx, "add_f32", dest, bins, ws)
+    ok = (bins >= 0) & (bins < B)
+    ref = dest.astype(np.float64)
+    np.add.at(ref, bins[ok], ws[ok].astype(np.float64))
+    l1 = np.abs(dest.astype(np.float64))
+    np.add.at(l1, bins[ok], np.abs(ws[ok].astype(np.float64)))
+    assert (np.abs(got - ref) <= 1e-5 * np.maximum(l1, 1e-6)).all()
+    # small integers: exact in any order
+    wi = datagen.uniform_i32(79, 0, n, -8, 8).astype(np.float32)
+    di = datagen.uniform_i32(80, 0, B, -8, 8).astype(np.float32)
+    assert np.array_equal(fb.reduce_by_index(ctx, "add_f32", di, bins, wi), oracle.reduce_by_index("add_f32", di, bins, wi))
+
+
+@pytest.mark.parametrize("rows,cols,m", [(1, 1, 1), (3, 3, 10), (100, 1000, 17), (1000, 37, 300), (5, 100003, 70000), (0, 4, 3), (4, 0, 3)])
+def test_hist_rows(ctx, rows, cols, m):
+    iss = datagen.uniform_i32(81, 0, rows * cols, -2, m + 1).reshape(rows, cols)
+    vss = datagen.uniform_i32(82, 0, rows * cols, 0, 100).reshape(rows, cols)
+    got = fb.hist_rows_add_i32(ctx, m, iss, vss)
+    assert got.shape == (rows, m)
+    assert np.array_equal(got, oracle.hist_rows_add_i32(m, iss, vss))
+
+
+@pytest.mark.parametrize("N,M,n", [(3, 3, 10), (100, 200, 100003), (1, 70000, 50000), (700, 1, 5000)])
+def test_reduce_by_index_2d(ctx, N, M, n):
+    dest = datagen.uniform_i32(83, 0, N * M, -1000, 1000).reshape(N, M)
+    is_ = datagen.uniform_i32(84, 0, n, -1, N).astype(np.int64)
+    js = datagen.uniform_i32(85, 0, n, -1, M).astype(np.int64)
+    vs = datagen.uniform_i32(86, 0, n, -1000, 1000)
+    assert np.array_equal(fb.reduce_by_index_2d_add_i32(ctx, dest, is_, js, vs), oracle.reduce_by_index_2d_add_i32(dest, is_, js, vs))
+
+
+def test_size_mismatches_are_errors(ctx):
+    a, k = ctx.new("i32_1d", np.zeros(5, np.int32)), ctx.new("bool_1d", np.zeros(6, np.bool_))
+    with pytest.raises(fb.FutharkError) as e:
+        ctx.entry_filter_by_flag_i32(a, k)
+    assert "invalid sizes" in e.value.message
+    with pytest.raises(fb.FutharkError):
+        ctx.entry_hist_op("and_i32", -1, a, a)
+    a.free(); k.free()

@@ -1,0 +1,95 @@
+"""The second part of the CPU oracle (oracle/oracle_ext.c: other operators, predicates and
+index spaces) against the reference's own known-answer vectors, extracted into
+tests/golden/reference_vectors.json by tests/golden/extract_reference_vectors.py."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_vectors.json")))
+
+
+def cases(name):
+    return GOLDEN[name]
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/filter1.fut"))
+def test_filter1_positive(c):
+    assert oracle.filter_pos_i32(np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/filter3.fut"))
+def test_filter3_by_second_component(c):
+    xs, keep = c["input"]
+    got = oracle.filter_by_flag_i32(np.array(xs, np.int32), np.array(keep, np.bool_))
+    assert got.tolist() == c["output"][1]
+    assert c["output"][0] == [True] * len(got)
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/partition1.fut"))
+def test_partition1_three_groups(c):
+    got = oracle.partition2_i32(np.array(c["input"][0], np.int32))
+    assert [g.tolist() for g in got] == c["output"]
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/scan4.fut"))
+def test_scan4_two_rounds(c):
+    assert oracle.scanomap_steps_i32(np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("name,op", [("tests/hist/and.fut", "and_i32"), ("tests/hist/or.fut", "or_i32"), ("tests/hist/xor.fut", "xor_i32")])
+def test_hist_bit_operators(name, op):
+    for c in cases(name):
+        n, is_, image = c["input"]
+        assert oracle.hist(op, n, is_, image).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("name,sop,uop", [("tests/hist/min.fut", "min_i32", "min_u32"), ("tests/hist/max.fut", "max_i32", "max_u32")])
+def test_reduce_by_index_min_max_signed_and_unsigned(name, sop, uop):
+    for c in cases(name):
+        n, is_, image = c["input"]
+        assert oracle.reduce_by_index(sop, np.zeros(n, np.int32), is_, image).tolist() == c["output"][0]
+        got_u = oracle.reduce_by_index(uop, np.zeros(n, np.uint32), is_, np.array(image, np.int32).view(np.uint32))
+        assert got_u.view(np.int32).tolist() == c["output"][1]
+
+
+def _f(v):
+    return [float("nan") if x == "nan" else float(x) for x in v]
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/f32.fut"))
+def test_reduce_by_index_add_f32_with_nan(c):
+    dest, is_, image = c["input"]
+    got = oracle.reduce_by_index("add_f32", np.array(_f(dest), np.float32), is_, np.array(_f(image), np.float32))
+    assert np.array_equal(got, np.array(_f(c["output"][0]), np.float32), equal_nan=True)
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/segmented.fut"))
+def test_hist_per_row(c):
+    m, xss = c["input"]
+    xss = np.array(xss, np.int32)
+    assert oracle.hist_rows_add_i32(m, xss, np.ones_like(xss)).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/hist2d.fut"))
+def test_reduce_by_index_2d(c):
+    xss, is_, js, vs = c["input"]
+    assert oracle.reduce_by_index_2d_add_i32(np.array(xss, np.int32), is_, js, vs).tolist() == c["output"][0]
+
+
+def test_definitions_without_reference_values():
+    rng = np.random.default_rng(0)
+    xs = rng.integers(-1000, 1000, 1000).astype(np.int32)
+    assert np.array_equal(oracle.scan_max_i32(xs), np.maximum.accumulate(xs))
+    xss = rng.integers(-1000, 1000, (37, 29)).astype(np.int32)
+    assert np.array_equal(oracle.segscan_rows_i32(xss), np.cumsum(xss, axis=1, dtype=np.int32))
+    is_ = rng.integers(-2, 12, 500).astype(np.int32)
+    vs = rng.integers(-3, 4, 500).astype(np.int32)
+    want = np.ones(10, np.int64)
+    for b, v in zip(is_, vs):
+        if 0 <= b < 10:
+            want[b] = ((want[b] * int(v) + 2 ** 31) % 2 ** 32) - 2 ** 31
+    assert oracle.hist("mul_i32", 10, is_, vs).tolist() == want.tolist()
