@@ -179,6 +179,8 @@ def load():
     for name in ("scan_max_i32", "segscan_rows_i32", "scanomap_steps_i32", "filter_pos_i32", "partition2_i32"):
         getattr(L, "futhark_entry_" + name).argtypes = [vp, pvp, vp]
     L.futhark_entry_filter_by_flag_i32.argtypes = [vp, pvp, vp, vp]
+    L.futhark_entry_scan_i64.argtypes = [vp, pvp, vp]
+    L.futhark_entry_linrec_f32.argtypes = [vp, pvp, vp, vp]
     for name in ("and_i32", "or_i32", "xor_i32", "mul_i32"):
         getattr(L, "futhark_entry_hist_" + name).argtypes = [vp, pvp, i64, vp, vp]
     for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32"):
@@ -467,6 +469,12 @@ class Context:
     def entry_exscan_i32(self, xs):
         return self._entry_arr("exscan_i32", "i32_1d", xs.ptr)
 
+    def entry_scan_i64(self, xs):
+        return self._entry_arr("scan_i64", "i64_1d", xs.ptr)
+
+    def entry_linrec_f32(self, as_, bs):
+        return self._entry_arr("linrec_f32", "f32_1d", as_.ptr, bs.ptr)
+
     def entry_scan_max_i32(self, xs):
         return self._entry_arr("scan_max_i32", "i32_1d", xs.ptr)
 
@@ -694,3 +702,11 @@ def hist_rows_add_i32(ctx, m, iss, vss):
 
 def reduce_by_index_2d_add_i32(ctx, dest, is_, js, vs):
     return _run(ctx, [("i32_2d", dest), ("i64_1d", is_), ("i64_1d", js), ("i32_1d", vs)], ctx.entry_reduce_by_index_2d_add_i32)
+
+
+def scan_i64(ctx, xs):
+    return _run(ctx, [("i64_1d", xs)], ctx.entry_scan_i64)
+
+
+def linrec_f32(ctx, as_, bs):
+    return _run(ctx, [("f32_1d", as_), ("f32_1d", bs)], ctx.entry_linrec_f32)

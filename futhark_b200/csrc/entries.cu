@@ -599,6 +599,45 @@ int futhark_entry_scanomap_steps_i32(struct futhark_context *ctx, struct futhark
   return rc;
 }
 
+// scan (+) 0 over i64, and a scan over pairs: operators the single-pass kernel's 32-bit status
+// word cannot carry go through the two-pass route (SegScan/TwoPass.hs:621-682).
+int futhark_entry_scan_i64(struct futhark_context *ctx, struct futhark_i64_1d **out0, const struct futhark_i64_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  int rc;
+  futhark_i64_1d *out = make_1d<futhark_i64_1d>(ctx, n, 8, "scan_i64.out", &rc);
+  if (out == nullptr) return rc;
+  if (n > 0) {
+    LaunchScope ls(ctx, "scan_i64.scan_stage1-3", PROV("scan (+) 0 xs"), "{" + kv("n", n) + "}");
+    ctx->launch_count += 2;
+    rc = fb_cuda_check(ctx, fb::launch_scan_i64(dptr<int64_t>(in0->mem), dptr<int64_t>(out->mem), n, ctx->reduce_scratch, ctx->num_sms, ctx->stream), "scan_i64");
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_entry_linrec_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_f32_1d *in0,
+                             const struct futhark_f32_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  if (in1->shape[0] != n) return bad_sizes(ctx);
+  int rc;
+  futhark_f32_1d *out = make_1d<futhark_f32_1d>(ctx, n, 4, "linrec_f32.out", &rc);
+  if (out == nullptr) return rc;
+  if (n > 0) {
+    LaunchScope ls(ctx, "linrec_f32.scan_stage1-3", PROV("map (.1) (scan compose (1,0) (zip as bs))"), "{" + kv("n", n) + "}");
+    ctx->launch_count += 2;
+    rc = fb_cuda_check(ctx, fb::launch_linrec_f32(dptr<float>(in0->mem), dptr<float>(in1->mem), dptr<float>(out->mem), n, ctx->reduce_scratch,
+                                                  ctx->num_sms, ctx->stream), "linrec_f32");
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
 int futhark_entry_bmm_f16(struct futhark_context *ctx, struct futhark_f32_3d **out0, const struct futhark_f16_3d *in0,
                           const struct futhark_f16_3d *in1) {
   if (!ctx->ready) return not_ready(ctx);

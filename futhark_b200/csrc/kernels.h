@@ -49,6 +49,14 @@ int compact_pieces_needed(int64_t n);
 cudaError_t launch_compact(int which, const void *in, const uint8_t *flags, void *out_true, void *out_false,
                            int64_t n, int64_t *d_count, void *scratch, const uint32_t *epochs, int *failure, cudaStream_t stream);
 
+// ---- two-pass scans for 8-byte and tuple operators (k_twopass.cu) ---------------------------
+// `scratch`: the reduce scratch (at least twopass_scratch_bytes()).
+size_t twopass_scratch_bytes();
+cudaError_t launch_scan_i64(const int64_t *in, int64_t *out, int64_t n, void *scratch, int num_sms, cudaStream_t stream);
+// out[i] = x_i of the recurrence x_i = as[i] * x_{i-1} + bs[i], x_{-1} = 0: the second component of the
+// scan of the pairs (as[i], bs[i]) under composition of affine maps
+cudaError_t launch_linrec_f32(const float *as, const float *bs, float *out, int64_t n, void *scratch, int num_sms, cudaStream_t stream);
+
 // ---- reductions (k_reduce.cu) ---------------------------------------------------------
 // `scratch` must hold reduce_scratch_bytes() bytes, zeroed once when allocated.
 size_t reduce_scratch_bytes();

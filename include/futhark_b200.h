@@ -348,6 +348,20 @@ int futhark_entry_partition2_i32(struct futhark_context *ctx,
                                  struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **out0,
                                  const struct futhark_i32_1d *in0);
 
+/* Scans whose operator works on 8-byte values or on tuples take the two-pass route (three
+ * launches: per-block scan, scan of the block carries, carry distribution), as the reference's do
+ * when its single-pass kernel does not apply (src/Futhark/CodeGen/ImpGen/GPU/SegScan.hs:51-90,
+ * SegScan/TwoPass.hs:146-682).
+ *
+ * entry scan_i64 (xs: []i64): []i64 = scan (+) 0 xs
+ * entry linrec_f32 (as: []f32) (bs: []f32): []f32 =
+ *   map (.1) (scan (\(a1,b1) (a2,b2) -> (a1*a2, b1*a2+b2)) (1,0) (zip as bs))
+ *   (a non-commutative operator on pairs: out[i] = as[i] * out[i-1] + bs[i], out[-1] = 0) */
+int futhark_entry_scan_i64(struct futhark_context *ctx, struct futhark_i64_1d **out0,
+                           const struct futhark_i64_1d *in0);
+int futhark_entry_linrec_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0,
+                             const struct futhark_f32_1d *in0, const struct futhark_f32_1d *in1);
+
 /* Fused and multi-operator SegOps.  The reference generates ONE kernel for a map body fused
  * with one or several reduction operators (src/Futhark/CodeGen/ImpGen/GPU/SegRed.hs:99-100,
  * 129-145) and keeps operand order for non-commutative operators (:836-921); here one kernel

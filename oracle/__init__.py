@@ -61,6 +61,9 @@ def lib():
         L.orc_reduce_by_index_32.argtypes = [i32, vp, i64, vp, vp, i64]
         L.orc_hist_rows_add_i32.argtypes = [i64, vp, vp, i64, i64, vp]
         L.orc_reduce_by_index_2d_add_i32.argtypes = [vp, i64, i64, vp, vp, vp, i64]
+        L.orc_scan_i64.argtypes = [vp, i64, vp]
+        L.orc_linrec_f32.argtypes = [vp, vp, i64, vp]
+        L.orc_linrec_f64.argtypes = [vp, vp, i64, vp, vp]
         L.orc_half_to_float.restype = ctypes.c_float
         L.orc_half_to_float.argtypes = [ctypes.c_uint16]
         L.orc_add32.restype = ctypes.c_uint32
@@ -440,3 +443,25 @@ def reduce_by_index_2d_add_i32(dest, is_, js, vs):
     is_, js, vs = _c(is_, np.int64), _c(js, np.int64), _c(vs, np.int32)
     lib().orc_reduce_by_index_2d_add_i32(_p(dest), dest.shape[0], dest.shape[1], _p(is_), _p(js), _p(vs), is_.size)
     return dest
+
+
+def scan_i64(xs):
+    xs = _c(xs, np.int64)
+    out = np.empty_like(xs)
+    lib().orc_scan_i64(_p(xs), xs.size, _p(out))
+    return out
+
+
+def linrec_f32(as_, bs):
+    as_, bs = _c(as_, np.float32), _c(bs, np.float32)
+    out = np.empty_like(as_)
+    lib().orc_linrec_f32(_p(as_), _p(bs), as_.size, _p(out))
+    return out
+
+
+def linrec_f64(as_, bs):
+    """(f64 evaluation of the recurrence, the same recurrence over absolute values)."""
+    as_, bs = _c(as_, np.float32), _c(bs, np.float32)
+    out, cond = np.empty(as_.size, np.float64), np.empty(as_.size, np.float64)
+    lib().orc_linrec_f64(_p(as_), _p(bs), as_.size, _p(out), _p(cond))
+    return out, cond

@@ -117,3 +117,30 @@ void orc_reduce_by_index_2d_add_i32(int32_t *dest, int64_t N, int64_t M, const i
   for (int64_t i = 0; i < n; i++)
     if (is[i] >= 0 && is[i] < N && js[i] >= 0 && js[i] < M) dest[is[i] * M + js[i]] = wadd(dest[is[i] * M + js[i]], vs[i]);
 }
+
+/* scan (+) 0 over i64 (add64 wraps, scalar.h:33) */
+void orc_scan_i64(const int64_t *xs, int64_t n, int64_t *out) {
+  uint64_t acc = 0;
+  for (int64_t i = 0; i < n; i++) { acc += (uint64_t)xs[i]; out[i] = (int64_t)acc; }
+}
+
+/* map (.1) (scan (\(a1,b1) (a2,b2) -> (a1*a2, b1*a2+b2)) (1,0) (zip as bs)), evaluated left to right in
+ * f32 (products and sums rounded separately: no contraction), and in f64 for the tolerance check */
+void orc_linrec_f32(const float *as, const float *bs, int64_t n, float *out) {
+  float a = 1.0f, b = 0.0f;
+  for (int64_t i = 0; i < n; i++) {
+    const float na = a * as[i], t = b * as[i];
+    b = t + bs[i];
+    a = na;
+    out[i] = b;
+  }
+}
+void orc_linrec_f64(const float *as, const float *bs, int64_t n, double *out, double *cond) {
+  double x = 0.0, c = 0.0;          /* c: the same recurrence on absolute values bounds the rounding error */
+  for (int64_t i = 0; i < n; i++) {
+    x = (double)as[i] * x + (double)bs[i];
+    c = (as[i] < 0 ? -(double)as[i] : (double)as[i]) * c + (bs[i] < 0 ? -(double)bs[i] : (double)bs[i]);
+    out[i] = x;
+    cond[i] = c;
+  }
+}

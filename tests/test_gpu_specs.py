@@ -159,6 +159,34 @@ def test_reduce_by_index_2d(ctx, N, M, n):
     assert np.array_equal(fb.reduce_by_index_2d_add_i32(ctx, dest, is_, js, vs), oracle.reduce_by_index_2d_add_i32(dest, is_, js, vs))
 
 
+# ---- the two-pass scan: 8-byte values and a non-commutative operator on pairs ---------------------
+
+@pytest.mark.parametrize("n", SIZES + [2047, 2048, 2049, 5 * 2048 + 1] + BIG)
+def test_scan_i64_two_pass(ctx, n):
+    xs = (datagen.uniform_i32(91, 0, n, -2 ** 31, 2 ** 31 - 1).astype(np.int64) << 20) + datagen.uniform_i32(92, 0, n, 0, 1000)
+    assert np.array_equal(fb.scan_i64(ctx, xs), oracle.scan_i64(xs))
+
+
+def test_scan_i64_wraps(ctx):
+    xs = np.full(100003, 2 ** 62, np.int64)
+    assert np.array_equal(fb.scan_i64(ctx, xs), oracle.scan_i64(xs))
+
+
+@pytest.mark.parametrize("n", [n for n in SIZES if n > 0] + [2048, 2049] + BIG)
+def test_linrec_f32_two_pass(ctx, n):
+    as_ = (0.5 + 0.5 * datagen.uniform01(93, 0, n, 1)).astype(np.float32) * np.where(datagen.uniform_i32(94, 0, n, 0, 9) == 0, -1, 1).astype(np.float32)
+    bs = datagen.normal_f32(95, 0, n)
+    got = fb.linrec_f32(ctx, as_, bs)
+    ref, cond = oracle.linrec_f64(as_, bs)
+    # forward error of a recurrence evaluated in any association: a few ulps of the same recurrence over absolute values
+    assert (np.abs(got - ref) <= 1e-5 * np.maximum(cond, 1e-6)).all()
+    assert (np.abs(oracle.linrec_f32(as_, bs) - ref) <= 1e-5 * np.maximum(cond, 1e-6)).all()
+    # powers of two and small integers: every product and sum is exact, so the definition fixes every bit
+    a2 = np.where(datagen.uniform_i32(96, 0, n, 0, 3) == 0, 0.0, 1.0).astype(np.float32)       # a in {0, 1}: restarts
+    b2 = datagen.uniform_i32(97, 0, n, -8, 8).astype(np.float32)
+    assert np.array_equal(fb.linrec_f32(ctx, a2, b2), oracle.linrec_f32(a2, b2))
+
+
 def test_size_mismatches_are_errors(ctx):
     a, k = ctx.new("i32_1d", np.zeros(5, np.int32)), ctx.new("bool_1d", np.zeros(6, np.bool_))
     with pytest.raises(fb.FutharkError) as e:
