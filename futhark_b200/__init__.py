@@ -29,6 +29,7 @@ ARRAY_TYPES = {
     "bool_1d": (np.bool_, 1, ctypes.c_bool),
     "f32_2d": (np.float32, 2, ctypes.c_float),
     "i32_2d": (np.int32, 2, ctypes.c_int32),
+    "bool_2d": (np.bool_, 2, ctypes.c_bool),
     "i64_2d": (np.int64, 2, ctypes.c_int64),
     "f64_1d": (np.float64, 1, ctypes.c_double),
     "f32_3d": (np.float32, 3, ctypes.c_float),
@@ -180,6 +181,10 @@ def load():
         getattr(L, "futhark_entry_" + name).argtypes = [vp, pvp, vp]
     L.futhark_entry_filter_by_flag_i32.argtypes = [vp, pvp, vp, vp]
     L.futhark_entry_scan_i64.argtypes = [vp, pvp, vp]
+    for name in ("transpose_f16_3d", "transpose_i64", "transpose_bool"):
+        getattr(L, "futhark_entry_" + name).argtypes = [vp, pvp, vp]
+    L.futhark_entry_replicate_i32.argtypes = [vp, pvp, i64, ctypes.c_int32]
+    L.futhark_entry_iota_i64.argtypes = [vp, pvp, i64]
     L.futhark_entry_linrec_f32.argtypes = [vp, pvp, vp, vp]
     for name in ("and_i32", "or_i32", "xor_i32", "mul_i32"):
         getattr(L, "futhark_entry_hist_" + name).argtypes = [vp, pvp, i64, vp, vp]
@@ -468,6 +473,21 @@ class Context:
 
     def entry_exscan_i32(self, xs):
         return self._entry_arr("exscan_i32", "i32_1d", xs.ptr)
+
+    def entry_transpose_f16_3d(self, xsss):
+        return self._entry_arr("transpose_f16_3d", "f16_3d", xsss.ptr)
+
+    def entry_transpose_i64(self, xss):
+        return self._entry_arr("transpose_i64", "i64_2d", xss.ptr)
+
+    def entry_transpose_bool(self, xss):
+        return self._entry_arr("transpose_bool", "bool_2d", xss.ptr)
+
+    def entry_replicate_i32(self, n, v):
+        return self._entry_arr("replicate_i32", "i32_1d", int(n), int(v))
+
+    def entry_iota_i64(self, n):
+        return self._entry_arr("iota_i64", "i64_1d", int(n))
 
     def entry_scan_i64(self, xs):
         return self._entry_arr("scan_i64", "i64_1d", xs.ptr)

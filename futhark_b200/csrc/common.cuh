@@ -32,9 +32,6 @@ __device__ __forceinline__ int ld_stream_b32(const void *p) {
   asm volatile("ld.global.nc.L1::no_allocate.s32 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
-// Loads of data that will be read once more soon (from L2): same path, default L2 priority.
-__device__ __forceinline__ int4 ld_keep_v4(const void *p) { return ld_stream_v4(p); }
-__device__ __forceinline__ int ld_keep_b32(const void *p) { return ld_stream_b32(p); }
 __device__ __forceinline__ void st_stream_v4(void *p, int4 v) {
   asm volatile("st.global.cs.v4.s32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");

@@ -68,7 +68,8 @@ int futhark_entry_scan_i32(struct futhark_context *ctx, struct futhark_i32_1d **
     if (rc == 0) {
       LaunchScope ls(ctx, "scan_i32.segscan", PROV("scan (+) 0 xs"), "{" + kv("n", n) + "}");
       rc = fb_cuda_check(ctx, fb::launch_scan_i32(dptr<int32_t>(in0->mem), dptr<int32_t>(out->mem), n, 0, nullptr, 0, ctx->lookback_scratch,
-                                                  fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "scan_i32");
+                                                  fb_next_epoch(ctx), ctx->d_failure, ctx->stream,
+                                                  (int)fb_tuning(ctx, "scan_i32.segscan_num_tblocks")), "scan_i32");
       ctx->failure_is_an_option = true;
     }
     if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
@@ -85,7 +86,8 @@ int futhark_entry_reduce_i32(struct futhark_context *ctx, int32_t *out0, const s
   {
     LaunchScope ls(ctx, "reduce_i32.segred_nonseg", PROV("reduce (+) 0 xs"), "{" + kv("n", n) + "}");
     rc = fb_cuda_check(ctx, fb::launch_reduce_i32(dptr<int32_t>(in0->mem), n, reinterpret_cast<int32_t *>(ctx->d_scalar),
-                                                  ctx->reduce_scratch, ctx->num_sms, ctx->stream), "reduce_i32");
+                                                  ctx->reduce_scratch, ctx->num_sms, ctx->stream,
+                                                  (int)fb_tuning(ctx, "reduce_i32.segred_num_tblocks")), "reduce_i32");
   }
   if (rc) return rc;
   // scalar result: read back and wait (Backends/GPU.hs:269-281)
@@ -193,7 +195,8 @@ static int segscan_f32_locked(futhark_context *ctx, struct futhark_f32_1d **out0
   if (rc == 0 && (n > 0 || shard_out != nullptr)) {
     LaunchScope ls(ctx, "segscan_f32.segscan", PROV("scan lifted(+) (false,0) (zip flags xs)"), "{" + kv("n", n) + "}");
     rc = fb_cuda_check(ctx, fb::launch_segscan_f32(dptr<uint8_t>(in0->mem), dptr<float>(in1->mem), dptr<float>(out->mem), n, 0.0f, shard_out,
-                                                   ctx->lookback_scratch, fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "segscan_f32");
+                                                   ctx->lookback_scratch, fb_next_epoch(ctx), ctx->d_failure, ctx->stream,
+                                                   (int)fb_tuning(ctx, "segscan_f32.segscan_num_tblocks")), "segscan_f32");
     ctx->failure_is_an_option = true;
   }
   if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
@@ -238,7 +241,8 @@ int futhark_entry_rowsum_f32(struct futhark_context *ctx, struct futhark_f32_1d 
   if (out == nullptr) return rc;
   if (rows > 0) {
     LaunchScope ls(ctx, "rowsum_f32.segred", PROV("map (reduce (+) 0) xss"), "{" + kv("rows", rows) + "," + kv("cols", cols) + "}");
-    rc = fb_cuda_check(ctx, fb::launch_rowsum_f32(dptr<float>(in0->mem), rows, cols, dptr<float>(out->mem), ctx->num_sms, ctx->stream), "rowsum_f32");
+    rc = fb_cuda_check(ctx, fb::launch_rowsum_f32(dptr<float>(in0->mem), rows, cols, dptr<float>(out->mem), ctx->num_sms, ctx->stream,
+                                                  fb_tuning(ctx, "rowsum_f32.suff_outer_par")), "rowsum_f32");
     if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
   }
   *out0 = out;
@@ -697,6 +701,89 @@ int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f
   return FUTHARK_SUCCESS;
 }
 
+// map transpose over f16 (the `transpose b` of the matrix product, tests/reg-tiling/mmm.fut:17-21), and
+// transposition of 8-byte and 1-byte elements: rts/opencl/transpose.cl:3-277 at the other widths.
+static int transpose_sized(futhark_context *ctx, int es, int64_t nb, int64_t rows, int64_t cols, const memblock_device &in, memblock_device *out,
+                           const char *name) {
+  int rc = fb_alloc(ctx, (size_t)(nb * rows * cols) * es, name, out);
+  if (rc != 0) return rc;
+  if (nb * rows * cols > 0) {
+    LaunchScope ls(ctx, name, PROV("map transpose xsss"), "{" + kv("batch", nb) + "," + kv("rows", rows) + "," + kv("cols", cols) + "," + kv("elem_size", es) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_transpose(es, dptr<void>(in), dptr<void>(*out), nb, rows, cols, ctx->num_sms, ctx->stream), name);
+    if (rc != 0) fb_unref(ctx, out);
+  }
+  return rc;
+}
+
+int futhark_entry_transpose_f16_3d(struct futhark_context *ctx, struct futhark_f16_3d **out0, const struct futhark_f16_3d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  futhark_f16_3d *out = (futhark_f16_3d *)malloc(sizeof(futhark_f16_3d));
+  if (out == nullptr) return 1;
+  out->shape[0] = in0->shape[0]; out->shape[1] = in0->shape[2]; out->shape[2] = in0->shape[1];
+  int rc = transpose_sized(ctx, 2, in0->shape[0], in0->shape[1], in0->shape[2], in0->mem, &out->mem, "transpose_f16_3d.map_transpose_2b");
+  if (rc != 0) { free(out); return rc; }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_entry_transpose_i64(struct futhark_context *ctx, struct futhark_i64_2d **out0, const struct futhark_i64_2d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  futhark_i64_2d *out = (futhark_i64_2d *)malloc(sizeof(futhark_i64_2d));
+  if (out == nullptr) return 1;
+  out->shape[0] = in0->shape[1]; out->shape[1] = in0->shape[0];
+  int rc = transpose_sized(ctx, 8, 1, in0->shape[0], in0->shape[1], in0->mem, &out->mem, "transpose_i64.map_transpose_8b");
+  if (rc != 0) { free(out); return rc; }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_entry_transpose_bool(struct futhark_context *ctx, struct futhark_bool_2d **out0, const struct futhark_bool_2d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  futhark_bool_2d *out = (futhark_bool_2d *)malloc(sizeof(futhark_bool_2d));
+  if (out == nullptr) return 1;
+  out->shape[0] = in0->shape[1]; out->shape[1] = in0->shape[0];
+  int rc = transpose_sized(ctx, 1, 1, in0->shape[0], in0->shape[1], in0->mem, &out->mem, "transpose_bool.map_transpose_1b");
+  if (rc != 0) { free(out); return rc; }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+// replicate n v and iota n: the fills the compiler puts around SegOps (ImpGen/GPU/Base.hs:1342-1436)
+int futhark_entry_replicate_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const int64_t in0, const int32_t in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  if (in0 < 0) { fb_set_error(ctx, "Error: negative array size %lld.\n", (long long)in0); return FUTHARK_PROGRAM_ERROR; }
+  int rc;
+  futhark_i32_1d *out = make_1d<futhark_i32_1d>(ctx, in0, 4, "replicate_i32.out", &rc);
+  if (out == nullptr) return rc;
+  if (in0 > 0) {
+    LaunchScope ls(ctx, "replicate_i32.replicate", PROV("replicate n v"), "{" + kv("n", in0) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_replicate(4, dptr<void>(out->mem), in0, (uint32_t)in1, ctx->num_sms, ctx->stream), "replicate_i32");
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_entry_iota_i64(struct futhark_context *ctx, struct futhark_i64_1d **out0, const int64_t in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  if (in0 < 0) { fb_set_error(ctx, "Error: negative array size %lld.\n", (long long)in0); return FUTHARK_PROGRAM_ERROR; }
+  int rc;
+  futhark_i64_1d *out = make_1d<futhark_i64_1d>(ctx, in0, 8, "iota_i64.out", &rc);
+  if (out == nullptr) return rc;
+  if (in0 > 0) {
+    LaunchScope ls(ctx, "iota_i64.iota", PROV("iota n"), "{" + kv("n", in0) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_iota(8, dptr<void>(out->mem), in0, 0, 1, ctx->num_sms, ctx->stream), "iota_i64");
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
 int futhark_b200_debug_expire_wait(struct futhark_context *ctx, int max_polls) {
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
@@ -737,8 +824,7 @@ int futhark_b200_lmad_copy(struct futhark_context *ctx, int elem_size, int r, CU
   }
   if (total == 0) return FUTHARK_SUCCESS;
   int kind = futhark_b200_lmad_classify(r, dst_strides, src_strides, shape, nullptr);
-  if (kind == fb::LMAD_TRANSPOSE && elem_size != 4) kind = fb::LMAD_GENERAL;
-  const char *name = kind == fb::LMAD_FLAT ? "copy_dev_to_dev" : kind == fb::LMAD_TRANSPOSE ? "lmad_copy.map_transpose_4b" : "lmad_copy.general";
+  const char *name = kind == fb::LMAD_FLAT ? "copy_dev_to_dev" : kind == fb::LMAD_TRANSPOSE ? "lmad_copy.map_transpose" : "lmad_copy.general";
   LaunchScope ls(ctx, name, PROV("copy"), "{" + kv("elements", total) + "," + kv("elem_size", elem_size) + "}");
   return fb_cuda_check(ctx, fb::launch_lmad_copy(elem_size, r, reinterpret_cast<void *>((uintptr_t)dst), dst_offset, dst_strides,
                                                  reinterpret_cast<const void *>((uintptr_t)src), src_offset, src_strides, shape,

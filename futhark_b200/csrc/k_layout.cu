@@ -1,7 +1,9 @@
 // Layout operations that the reference's compiler inserts on either side of a SegOp:
-// batched transposition of 4-byte elements, and strided (LMAD) copies (second half of the file).  Replaces the map_transpose_4b kernels of the
-// reference's runtime (rts/opencl/transpose.cl:3-275: the tiled kernel and its low-width,
-// low-height, small and large variants; rts/c/gpu.h:144-168).
+// batched transposition of 1-, 2-, 4- and 8-byte elements, strided (LMAD) copies (second half
+// of the file), and the replicate / iota fills.  Replaces the map_transpose_{1,2,4,8}b kernels
+// of the reference's runtime (rts/opencl/transpose.cl:3-277: the tiled kernel and its
+// low-width, low-height, small and large variants; rts/c/gpu.h:144-168, 333-461) and the fill
+// kernels its compiler generates (src/Futhark/CodeGen/ImpGen/GPU/Base.hs:1274-1436).
 //
 // One kernel.  A CTA of 256 threads moves 64 x 64 tiles through shared memory: rows of the
 // input are read as 16-byte vectors (a warp covers two rows of 256 bytes), the tile is held
@@ -82,6 +84,99 @@ cudaError_t launch_transpose_b32(const void *in, void *out, int64_t nb, int64_t 
   const int grid = (int)(total < resident ? total : resident);
   transpose_b32_kernel<<<grid, TR_THREADS, 0, stream>>>(reinterpret_cast<const uint32_t *>(in),
                                                        reinterpret_cast<uint32_t *>(out), nb, rows, cols, tiles_r, tiles_c);
+  return cudaGetLastError();
+}
+
+// ---- the other element widths ------------------------------------------------------------------
+// The same 64 x 64 tile through shared memory for 1-, 2- and 8-byte elements: a row of the tile
+// is read by 64 consecutive threads, a row of the output written by 64 consecutive threads, the
+// tile pitch is 65 elements.  (The 4-byte kernel above additionally moves 16-byte vectors.)
+template <typename T>
+__global__ void __launch_bounds__(TR_THREADS)
+transpose_any_kernel(const T *__restrict__ in, T *__restrict__ out, int64_t nb, int64_t rows, int64_t cols,
+                     int64_t tiles_r, int64_t tiles_c) {
+  __shared__ T s_t[TR_TILE * TR_PITCH];
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;      // 64 across, 4 down
+  const int64_t per_batch = tiles_r * tiles_c, total = per_batch * nb;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const int64_t b = t / per_batch, rem = t - b * per_batch;
+    const int64_t tc = rem / tiles_r, tr = rem - tc * tiles_r;
+    const int64_t r0 = tr * TR_TILE, c0 = tc * TR_TILE;
+    const T *src = in + b * rows * cols;
+    T *dst = out + b * rows * cols;
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
+      const int r = ty + 4 * k;
+      if (r0 + r < rows && c0 + tx < cols) s_t[r * TR_PITCH + tx] = src[(r0 + r) * cols + c0 + tx];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
+      const int c = ty + 4 * k;                     // input column = output row
+      if (c0 + c < cols && r0 + tx < rows) dst[(c0 + c) * rows + r0 + tx] = s_t[tx * TR_PITCH + c];
+    }
+    __syncthreads();
+  }
+}
+
+cudaError_t launch_transpose(int elem_size, const void *in, void *out, int64_t nb, int64_t rows, int64_t cols, int num_sms,
+                             cudaStream_t stream) {
+  if (nb <= 0 || rows <= 0 || cols <= 0) return cudaSuccess;
+  if (elem_size == 4) return launch_transpose_b32(in, out, nb, rows, cols, num_sms, stream);
+  const int64_t tiles_r = (rows + TR_TILE - 1) / TR_TILE, tiles_c = (cols + TR_TILE - 1) / TR_TILE;
+  const int64_t total = tiles_r * tiles_c * nb;
+  const int64_t resident = (int64_t)num_sms * (elem_size == 8 ? 4 : 8);
+  const int grid = (int)(total < resident ? total : resident);
+  if (elem_size == 1)
+    transpose_any_kernel<uint8_t><<<grid, TR_THREADS, 0, stream>>>(reinterpret_cast<const uint8_t *>(in), reinterpret_cast<uint8_t *>(out), nb, rows, cols, tiles_r, tiles_c);
+  else if (elem_size == 2)
+    transpose_any_kernel<uint16_t><<<grid, TR_THREADS, 0, stream>>>(reinterpret_cast<const uint16_t *>(in), reinterpret_cast<uint16_t *>(out), nb, rows, cols, tiles_r, tiles_c);
+  else if (elem_size == 8)
+    transpose_any_kernel<uint64_t><<<grid, TR_THREADS, 0, stream>>>(reinterpret_cast<const uint64_t *>(in), reinterpret_cast<uint64_t *>(out), nb, rows, cols, tiles_r, tiles_c);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// ---- replicate and iota (ImpGen/GPU/Base.hs:1342-1436: sReplicate, sIota) ---------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) replicate_kernel(T *__restrict__ dst, int64_t n, T v) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) dst[i] = v;
+}
+// dst[i] = start + i * step in the integer type T (wrapping, as the reference's iota over a sized type)
+template <typename T>
+__global__ void __launch_bounds__(256) iota_kernel(T *__restrict__ dst, int64_t n, int64_t start, int64_t step) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride)
+    dst[i] = (T)((uint64_t)start + (uint64_t)i * (uint64_t)step);
+}
+static int fill_grid(int64_t n, int num_sms) {
+  const int64_t want = (n + 255) / 256, cap = (int64_t)num_sms * 8;
+  return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+cudaError_t launch_replicate(int elem_size, void *dst, int64_t n, uint64_t value_bits, int num_sms, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  const int grid = fill_grid(n, num_sms);
+  switch (elem_size) {
+    case 1: replicate_kernel<uint8_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint8_t *>(dst), n, (uint8_t)value_bits); break;
+    case 2: replicate_kernel<uint16_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint16_t *>(dst), n, (uint16_t)value_bits); break;
+    case 4: replicate_kernel<uint32_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint32_t *>(dst), n, (uint32_t)value_bits); break;
+    case 8: replicate_kernel<uint64_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint64_t *>(dst), n, value_bits); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+cudaError_t launch_iota(int elem_size, void *dst, int64_t n, int64_t start, int64_t step, int num_sms, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  const int grid = fill_grid(n, num_sms);
+  switch (elem_size) {
+    case 1: iota_kernel<uint8_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint8_t *>(dst), n, start, step); break;
+    case 2: iota_kernel<uint16_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint16_t *>(dst), n, start, step); break;
+    case 4: iota_kernel<uint32_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint32_t *>(dst), n, start, step); break;
+    case 8: iota_kernel<uint64_t><<<grid, 256, 0, stream>>>(reinterpret_cast<uint64_t *>(dst), n, start, step); break;
+    default: return cudaErrorInvalidValue;
+  }
   return cudaGetLastError();
 }
 
@@ -199,10 +294,9 @@ cudaError_t launch_lmad_copy(int elem_size, int r, void *dst, int64_t dst_offset
   // (named d/s: the char pointers already include the offsets)
   int64_t nb = 0, rows = 0, cols = 0;
   int kind = lmad_classify(a.r, a.shape, a.dst, a.src, &nb, &rows, &cols);
-  if (kind == LMAD_TRANSPOSE && elem_size != 4) kind = LMAD_GENERAL;   // the tiled kernel moves 4-byte elements
   if (kind_out) *kind_out = kind;
   if (kind == LMAD_FLAT) return cudaMemcpyAsync(d, s, (size_t)total * elem_size, cudaMemcpyDeviceToDevice, stream);
-  if (kind == LMAD_TRANSPOSE) return launch_transpose_b32(s, d, nb, rows, cols, num_sms, stream);
+  if (kind == LMAD_TRANSPOSE) return launch_transpose(elem_size, s, d, nb, rows, cols, num_sms, stream);
   if (a.r == 0) { a.r = 1; a.shape[0] = 1; a.dst[0] = 0; a.src[0] = 0; }
   // Widen the element while the innermost dimension is contiguous on both sides and everything
   // else (extent, the other strides, both addresses) stays a multiple of the doubled size: rows

@@ -98,7 +98,7 @@ reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict
 }
 
 cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void *scratch, int num_sms,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, int block_cap) {
   if (n <= 0) return cudaMemsetAsync(d_out, 0, sizeof(int32_t), stream);   // the neutral element
   uint32_t *ticket = reinterpret_cast<uint32_t *>(scratch);
   uint32_t *partials = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(scratch) + 256);
@@ -106,6 +106,7 @@ cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void
   int blocks = num_sms * 8;
   if (blocks > RED_MAX_BLOCKS) blocks = RED_MAX_BLOCKS;
   if (want < blocks) blocks = want < 1 ? 1 : (int)want;
+  if (block_cap > 0 && block_cap < blocks) blocks = block_cap;       // reduce_i32.segred_num_tblocks
   reduce_i32_kernel<<<blocks, RED_THREADS, 0, stream>>>(in, n, d_out, ticket, partials);
   return cudaGetLastError();
 }
@@ -183,14 +184,14 @@ rowsum_thread_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, f
 }
 
 cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float *out, int num_sms,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, int64_t suff_outer_par) {
   if (rows <= 0) return cudaSuccess;
   if (cols <= 0) return cudaMemsetAsync(out, 0, (size_t)rows * sizeof(float), stream);
   if (cols < 16) {
     int64_t want = (rows + RED_THREADS - 1) / RED_THREADS;
     int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
     rowsum_thread_kernel<<<blocks, RED_THREADS, 0, stream>>>(in, rows, cols, out);
-  } else if (cols <= 16384) {
+  } else if (cols <= 16384 || rows >= suff_outer_par) {
     int64_t want = (rows * 32 + RED_THREADS - 1) / RED_THREADS;
     int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
     const bool vec = (cols % 4 == 0) && ((((uintptr_t)in) & 15) == 0);

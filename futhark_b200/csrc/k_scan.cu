@@ -605,7 +605,7 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
 // worker per tile, plus the propagator.  The occupancy query allocates nothing and is
 // cached per specification and device.
 template <typename S>
-static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
+static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream, int grid_cap = 0) {
   constexpr int TILE = TileOf<S>::TILE;
   constexpr size_t smem = 2 * (size_t)(S::kCompact ? TILE * 4 + 64 + (S::kFlagArray ? TILE : 0) : TILE * 4 + (S::kFlagArray ? TILE : 64));
   static int ctas_per_sm_dev[64], num_sms_dev[64];     // per device ordinal (function attributes are per device)
@@ -627,6 +627,7 @@ static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream) {
   }
   const uint32_t resident = (uint32_t)(ctas_per_sm * num_sms);
   uint32_t grid = 2 * a.num_tiles + 1 < resident ? 2 * a.num_tiles + 1 : resident;
+  if (grid_cap >= 2 && (uint32_t)grid_cap < grid) grid = (uint32_t)grid_cap;   // the <entry>.segscan_num_tblocks tuning parameter
   if (a.num_tiles <= 1 || grid < 2) grid = 1;          // a single tile: one CTA that propagates for itself
   stream_kernel<S><<<grid, SCAN_THREADS, smem, stream>>>(a);
   return cudaGetLastError();
@@ -647,13 +648,13 @@ static LookbackArgs make_args(const void *in, const uint8_t *flags, void *out, u
 
 cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in,
                             const int32_t *carry_vals, int carry_n, void *scratch,
-                            uint32_t epoch, int *failure, cudaStream_t stream) {
+                            uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap) {
   if (n <= 0) return cudaSuccess;
   LookbackArgs a = make_args<SpecScanAddI32>(in, nullptr, out, nullptr, n, scratch, epoch, failure);
   a.carry_in = (uint32_t)carry_in;
   a.carry_vals = reinterpret_cast<const uint32_t *>(carry_vals);
   a.carry_n = carry_n;
-  return launch_stream<SpecScanAddI32>(a, stream);
+  return launch_stream<SpecScanAddI32>(a, stream, grid_cap);
 }
 
 // Scans that differ from the above only in their specification: 0 exclusive (+), 1 inclusive max,
@@ -699,7 +700,7 @@ __global__ void shard_identity_kernel(uint32_t *dst) {
 }
 
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
-                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream) {
+                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap) {
   if (n <= 0) {
     if (shard_out != nullptr) {
       shard_identity_kernel<<<1, 1, 0, stream>>>(shard_out);
@@ -712,7 +713,7 @@ cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out
   memcpy(&bits, &carry_in, 4);
   a.carry_in = bits;
   a.shard_out = shard_out;
-  return launch_stream<SpecSegScanAddF32>(a, stream);
+  return launch_stream<SpecSegScanAddF32>(a, stream, grid_cap);
 }
 
 // out[i] = carry + out[i] for every i before the shard's first segment start, where carry is

@@ -15,7 +15,7 @@ size_t lookback_scratch_bytes(int64_t n);
 // device values it points to.
 cudaError_t launch_scan_i32(const int32_t *in, int32_t *out, int64_t n, int32_t carry_in,
                             const int32_t *carry_vals, int carry_n, void *scratch,
-                            uint32_t epoch, int *failure, cudaStream_t stream);
+                            uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap = 0);
 // Exclusive scan: out[0] = 0, out[i] = in[0] + ... + in[i-1] (prelude/soacs.fut:212-215).
 cudaError_t launch_exscan_i32(const int32_t *in, int32_t *out, int64_t n, void *scratch,
                               uint32_t epoch, int *failure, cudaStream_t stream);
@@ -25,7 +25,7 @@ cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls
 // the array seen as one shard of a longer one: {f32 bits, flag} of its last inclusive prefix, the
 // index of its first 5120-element tile that holds a segment start (all ones if none), 0.
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
-                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream);
+                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap = 0);
 // Adds the fold of summaries[0..rank) (4 words per shard) to out[0 .. first segment start),
 // the first start being located through summaries[rank].
 cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
@@ -60,10 +60,13 @@ cudaError_t launch_linrec_f32(const float *as, const float *bs, float *out, int6
 // ---- reductions (k_reduce.cu) ---------------------------------------------------------
 // `scratch` must hold reduce_scratch_bytes() bytes, zeroed once when allocated.
 size_t reduce_scratch_bytes();
+// grid_cap (> 0) bounds the number of CTAs; suff_outer_par: with at least that many rows one warp takes a
+// row whatever its length (the outer parallelism suffices), with fewer a long row is shared by a CTA.
+// grid_cap / block_cap: 0 = the launcher's own choice (the *_num_tblocks tuning parameters).
 cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void *scratch, int num_sms,
-                              cudaStream_t stream);
+                              cudaStream_t stream, int block_cap = 0);
 cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float *out, int num_sms,
-                              cudaStream_t stream);
+                              cudaStream_t stream, int64_t suff_outer_par = 32768);
 // out[s] = sum of xs[offsets[s] .. offsets[s+1]) for s < nseg (offsets ascending, clamped to [0, n]); `scratch` as above.
 cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
                                  void *scratch, int *failure, int num_sms, cudaStream_t stream);
@@ -97,6 +100,12 @@ cudaError_t launch_flatten_2d_index(const int64_t *is, const int64_t *js, int64_
 // out[b][c][r] = in[b][r][c] for 4-byte elements.
 cudaError_t launch_transpose_b32(const void *in, void *out, int64_t nb, int64_t rows, int64_t cols, int num_sms,
                                  cudaStream_t stream);
+// The same for elements of 1, 2, 4 or 8 bytes.
+cudaError_t launch_transpose(int elem_size, const void *in, void *out, int64_t nb, int64_t rows, int64_t cols, int num_sms,
+                             cudaStream_t stream);
+// dst[i] = value (elements of 1, 2, 4 or 8 bytes, given as bits); dst[i] = start + i * step in that integer width.
+cudaError_t launch_replicate(int elem_size, void *dst, int64_t n, uint64_t value_bits, int num_sms, cudaStream_t stream);
+cudaError_t launch_iota(int elem_size, void *dst, int64_t n, int64_t start, int64_t step, int num_sms, cudaStream_t stream);
 
 // Strided copy between two device arrays given as LMADs (offset + one stride per dimension, in
 // elements) over a common shape of rank <= LMAD_MAX_RANK; elem_size 1, 2, 4 or 8.  *kind_out

@@ -16,9 +16,13 @@
 
 // ---- tuning parameters ---------------------------------------------------------------------
 // Names follow the reference's "<entry>.<kernel>_<what>" scheme and its size classes
-// (rts/c/backends/cuda.h:552-596).  The kernels of this library have fixed launch shapes
-// chosen for 148 SMs; the parameters are accepted, stored and reported so that tuning
-// files written for the reference load without error.
+// (rts/c/backends/cuda.h:552-596).  Four of them act: the three *_num_tblocks of the persistent
+// scan / reduce grids cap the number of CTAs (0 = as many as are resident at once), and
+// rowsum_f32.suff_outer_par is the threshold at which the outer parallelism of a row
+// reduction is taken to suffice (one warp per row whatever the row length; below it a long
+// row is shared by a CTA): the version choice of src/Futhark/CodeGen/Backends/GPU.hs:147-156.
+// The others (block sizes, tile sizes) name shapes that are fixed in these kernels; they are
+// accepted, stored and reported so that tuning files written for the reference load without error.
 const TuningParam kTuningParams[] = {
     {"builtin#replicate_i32.tblock_size", "thread_block_size", 256},
     {"scan_i32.segscan_tblock_size", "thread_block_size", 256},
@@ -26,6 +30,7 @@ const TuningParam kTuningParams[] = {
     {"reduce_i32.segred_tblock_size", "thread_block_size", 256},
     {"reduce_i32.segred_num_tblocks", "grid_size", 0},
     {"segscan_f32.segscan_tblock_size", "thread_block_size", 256},
+    {"segscan_f32.segscan_num_tblocks", "grid_size", 0},
     {"segreduce_f32.segred_tblock_size", "thread_block_size", 256},
     {"rowsum_f32.segred_tblock_size", "thread_block_size", 256},
     {"rowsum_f32.suff_outer_par", "threshold(def, )", 32768},
@@ -195,6 +200,13 @@ int fb_ensure_lookback_scratch(futhark_context *ctx, size_t bytes) {
   ctx->lookback_scratch = p;
   ctx->lookback_scratch_bytes = want;
   return FUTHARK_SUCCESS;
+}
+
+int64_t fb_tuning(futhark_context *ctx, const char *name) {
+  for (int i = 0; i < kNumTuningParams; i++)
+    if (strcmp(name, kTuningParams[i].name) == 0)
+      return (ctx->cfg != nullptr && (int)ctx->cfg->tuning.size() > i) ? ctx->cfg->tuning[i] : kTuningParams[i].def;
+  return 0;
 }
 
 uint32_t fb_next_epoch(futhark_context *ctx) {
@@ -607,6 +619,7 @@ FB_ARRAY_1D(f32_1d, float)
 FB_ARRAY_1D(bool_1d, bool)
 FB_ARRAY_2D(f32_2d, float)
 FB_ARRAY_2D(i32_2d, int32_t)
+FB_ARRAY_2D(bool_2d, bool)
 FB_ARRAY_2D(i64_2d, int64_t)
 FB_ARRAY_1D(f64_1d, double)
 FB_ARRAY_3D(f32_3d, float)

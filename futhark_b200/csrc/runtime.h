@@ -101,6 +101,7 @@ void fb_unref(futhark_context *ctx, memblock_device *mb);
 void fb_ref(memblock_device *mb);
 int fb_ensure_lookback_scratch(futhark_context *ctx, size_t bytes);
 uint32_t fb_next_epoch(futhark_context *ctx);
+int64_t fb_tuning(futhark_context *ctx, const char *name);   // value of a tuning parameter (its default if never set)
 
 // RAII guard: lock + make the context's device current
 struct CtxGuard {
@@ -132,6 +133,7 @@ FB_DEFINE_ARRAY_STRUCT(f32_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(bool_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(i32_2d, 2)
+FB_DEFINE_ARRAY_STRUCT(bool_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(i64_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(f64_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_3d, 3)

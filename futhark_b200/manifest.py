@@ -1,0 +1,121 @@
+"""The manifest of libfuthark_b200.so: the machine-readable description of its C API that the
+reference's compiler writes beside every compiled library (`<prog>.json`; format:
+docs/manifest.schema.json and docs/c-api.rst:792-871 of the reference).  `futhark bench`,
+`futhark test` and bindings generators read it to learn the entry points and their types.
+
+The entry points of this library are fixed, so the manifest is built from the table below.
+    python -m futhark_b200.manifest          writes futhark_b200/futhark_b200.json
+"""
+import json
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PATH = os.path.join(HERE, "futhark_b200.json")
+
+ELEM = {"i32": "int32_t", "i64": "int64_t", "u32": "uint32_t", "f32": "float", "f64": "double", "bool": "bool", "f16": "uint16_t"}
+ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "bool_1d", "f32_2d", "i32_2d", "i64_2d", "bool_2d", "f32_3d", "f16_3d"]
+
+PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
+TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
+I32F32 = "opaque_tup2_i32_f32"
+
+
+def tname(arr):
+    """Futhark spelling of an array type name: i32_2d -> [][]i32."""
+    elem, rank = arr.rsplit("_", 1)
+    return "[]" * int(rank[0]) + elem
+
+
+# name: (inputs as (name, type), output type, tuning parameters)
+ENTRIES = {
+    "scan_i32": ([("xs", "[]i32")], "[]i32", ["scan_i32.segscan_tblock_size", "scan_i32.segscan_num_tblocks"]),
+    "reduce_i32": ([("xs", "[]i32")], "i32", ["reduce_i32.segred_tblock_size", "reduce_i32.segred_num_tblocks"]),
+    "exscan_i32": ([("xs", "[]i32")], "[]i32", []),
+    "scan_max_i32": ([("xs", "[]i32")], "[]i32", []),
+    "scan_i64": ([("xs", "[]i64")], "[]i64", []),
+    "linrec_f32": ([("as", "[]f32"), ("bs", "[]f32")], "[]f32", []),
+    "scanomap_steps_i32": ([("xs", "[]i32")], "[]i32", []),
+    "segscan_f32": ([("flags", "[]bool"), ("xs", "[]f32")], "[]f32", ["segscan_f32.segscan_tblock_size", "segscan_f32.segscan_num_tblocks"]),
+    "segscan_rows_i32": ([("xss", "[][]i32")], "[][]i32", []),
+    "segreduce_f32": ([("offsets", "[]i64"), ("flags", "[]bool"), ("xs", "[]f32")], "[]f32", ["segreduce_f32.segred_tblock_size"]),
+    "rowsum_f32": ([("xss", "[][]f32")], "[]f32", ["rowsum_f32.segred_tblock_size", "rowsum_f32.suff_outer_par"]),
+    "hist_add_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", ["hist_add_i32.seghist_tblock_size", "hist_add_i32.seghist_num_tblocks"]),
+    "hist_max_f32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]f32")], "[]f32", ["hist_max_f32.seghist_tblock_size"]),
+    "hist_and_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", []),
+    "hist_or_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", []),
+    "hist_xor_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", []),
+    "hist_mul_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", []),
+    "reduce_by_index_min_i32": ([("dest", "[]i32"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", []),
+    "reduce_by_index_max_i32": ([("dest", "[]i32"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", []),
+    "reduce_by_index_min_u32": ([("dest", "[]u32"), ("is", "[]i32"), ("vs", "[]u32")], "[]u32", []),
+    "reduce_by_index_max_u32": ([("dest", "[]u32"), ("is", "[]i32"), ("vs", "[]u32")], "[]u32", []),
+    "reduce_by_index_add_f32": ([("dest", "[]f32"), ("is", "[]i32"), ("vs", "[]f32")], "[]f32", []),
+    "hist_rows_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vss", "[][]i32")], "[][]i32", []),
+    "reduce_by_index_2d_add_i32": ([("dest", "[][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("vs", "[]i32")], "[][]i32", []),
+    "filter_u32": ([("ks", "[]u32")], "[]u32", ["filter_u32.segscan_tblock_size"]),
+    "partition_u32": ([("ks", "[]u32")], "([]u32, []u32)", ["partition_u32.segscan_tblock_size"]),
+    "filter_pos_i32": ([("xs", "[]i32")], "[]i32", []),
+    "filter_by_flag_i32": ([("xs", "[]i32"), ("keep", "[]bool")], "[]i32", []),
+    "partition2_i32": ([("xs", "[]i32")], "([]i32, []i32, []i32)", []),
+    "bmm_f16": ([("A", "[][][]f16"), ("B", "[][][]f16")], "[][][]f32", ["bmm_f16.tile_size", "bmm_f16.reg_tile_size"]),
+    "transpose_f32": ([("xss", "[][]f32")], "[][]f32", []),
+    "transpose_f32_3d": ([("xsss", "[][][]f32")], "[][][]f32", []),
+    "transpose_f16_3d": ([("xsss", "[][][]f16")], "[][][]f16", []),
+    "transpose_i64": ([("xss", "[][]i64")], "[][]i64", []),
+    "transpose_bool": ([("xss", "[][]bool")], "[][]bool", []),
+    "replicate_i32": ([("n", "i64"), ("v", "i32")], "[]i32", ["builtin#replicate_i32.tblock_size"]),
+    "iota_i64": ([("n", "i64")], "[]i64", []),
+    "mss_i32": ([("xs", "[]i32")], "i32", []),
+    "sum_i32_f32": ([("xs", "[]i32")], "(i32, f32)", []),
+    "dotprod_f32": ([("xs", "[]f32"), ("ys", "[]f32")], "f32", []),
+    "prod_of_sums_i32": ([("xs", "[]i32"), ("ys", "[]i32")], "i32", []),
+}
+
+
+def build():
+    types = {}
+    for arr in ARRAYS:
+        elem, rank = arr.rsplit("_", 1)
+        types[tname(arr)] = {
+            "kind": "array", "ctype": "struct futhark_%s *" % arr, "rank": int(rank[0]), "elemtype": elem,
+            "ops": {k: "futhark_%s_%s" % (k, arr) for k in ("free", "shape", "values", "values_raw", "new", "new_raw", "index")},
+        }
+    types["([]u32, []u32)"] = {
+        "kind": "opaque", "ctype": "struct futhark_%s *" % PAIR,
+        "ops": {"free": "futhark_free_" + PAIR, "store": "futhark_store_" + PAIR, "restore": "futhark_restore_" + PAIR},
+        "record": {"new": "futhark_new_" + PAIR,
+                   "fields": [{"name": str(i), "type": "[]u32", "project": "futhark_project_%s_%d" % (PAIR, i)} for i in range(2)]},
+    }
+    types["(i32, f32)"] = {
+        "kind": "opaque", "ctype": "struct futhark_%s *" % I32F32,
+        "ops": {"free": "futhark_free_" + I32F32, "store": "futhark_store_" + I32F32, "restore": "futhark_restore_" + I32F32},
+        "record": {"new": "futhark_new_" + I32F32,
+                   "fields": [{"name": "0", "type": "i32", "project": "futhark_project_%s_0" % I32F32},
+                              {"name": "1", "type": "f32", "project": "futhark_project_%s_1" % I32F32}]},
+    }
+    types["([]i32, []i32, []i32)"] = {
+        "kind": "opaque", "ctype": "struct futhark_%s *" % TRIPLE,
+        "ops": {"free": "futhark_free_" + TRIPLE},
+        "record": {"fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (TRIPLE, i)} for i in range(3)]},
+    }
+    entries = {}
+    for name, (ins, out, tuning) in ENTRIES.items():
+        entries[name] = {
+            "cfun": "futhark_entry_" + name,
+            "tuning_params": tuning,
+            "attributes": [],
+            "output": {"type": out, "unique": out.startswith("[") or out.startswith("(")},
+            "inputs": [{"name": n, "type": t, "unique": False} for n, t in ins],
+        }
+    return {"backend": "cuda", "version": "futhark_b200 0.2 (sm_100a)", "entry_points": entries, "types": types}
+
+
+def write(path=PATH):
+    with open(path, "w") as fh:
+        json.dump(build(), fh, indent=1, sort_keys=True)
+        fh.write("\n")
+    return path
+
+
+if __name__ == "__main__":
+    print("wrote", write())

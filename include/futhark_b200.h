@@ -135,6 +135,7 @@ FUTHARK_B200_ARRAY_1D(f32_1d, float)
 FUTHARK_B200_ARRAY_1D(bool_1d, bool)
 FUTHARK_B200_ARRAY_2D(f32_2d, float)
 FUTHARK_B200_ARRAY_2D(i32_2d, int32_t)
+FUTHARK_B200_ARRAY_2D(bool_2d, bool)
 FUTHARK_B200_ARRAY_2D(i64_2d, int64_t)
 FUTHARK_B200_ARRAY_1D(f64_1d, double)
 FUTHARK_B200_ARRAY_3D(f32_3d, float)
@@ -317,6 +318,20 @@ int futhark_entry_transpose_f32(struct futhark_context *ctx, struct futhark_f32_
                                 const struct futhark_f32_2d *in0);
 int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f32_3d **out0,
                                    const struct futhark_f32_3d *in0);
+/* The other element widths of the reference's transposition kernels (rts/opencl/transpose.cl:3-277,
+ * instantiated for 1, 2, 4 and 8 bytes at rts/c/gpu.h:145-168): `map transpose` over f16 (the
+ * `transpose b` of the f16 matrix product), `transpose` over i64 and over bool. */
+int futhark_entry_transpose_f16_3d(struct futhark_context *ctx, struct futhark_f16_3d **out0,
+                                   const struct futhark_f16_3d *in0);
+int futhark_entry_transpose_i64(struct futhark_context *ctx, struct futhark_i64_2d **out0,
+                                const struct futhark_i64_2d *in0);
+int futhark_entry_transpose_bool(struct futhark_context *ctx, struct futhark_bool_2d **out0,
+                                 const struct futhark_bool_2d *in0);
+/* entry replicate_i32 (n: i64) (v: i32): [n]i32 = replicate n v;  entry iota_i64 (n: i64): [n]i64 = iota n:
+ * the fills the reference's compiler emits around SegOps (src/Futhark/CodeGen/ImpGen/GPU/Base.hs:1342-1436). */
+int futhark_entry_replicate_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                                const int64_t in0, const int32_t in1);
+int futhark_entry_iota_i64(struct futhark_context *ctx, struct futhark_i64_1d **out0, const int64_t in0);
 
 /* Other scans, segmented scans, filters and partitions: the same single-pass kernel under other
  * specifications (operator, fused map body, post-operation, flag source, predicate), where the

@@ -100,3 +100,64 @@ def test_lmad_copy_rejects_bad_arguments(ctx):
         ctx.lmad_copy(4, a.raw, 0, [1] * 9, a.raw, 0, [1] * 9, [1] * 9)
     a.free()
     ctx.sync()
+
+
+# ---- the other element widths, replicate and iota -------------------------------------------------
+
+@pytest.mark.parametrize("nb,rows,cols", [(1, 1, 1), (1, 64, 64), (3, 65, 130), (2, 1000, 3), (1, 3, 1000), (4, 257, 511), (1, 2048, 1024)])
+def test_transpose_f16_3d(ctx, nb, rows, cols):
+    x = (np.arange(nb * rows * cols, dtype=np.int64) * 2654435761 % 65521).astype(np.uint16).reshape(nb, rows, cols)
+    a = ctx.new("f16_3d", x)
+    out = ctx.entry_transpose_f16_3d(a)
+    got = out.values()
+    out.free(); a.free()
+    assert np.array_equal(got, np.transpose(x, (0, 2, 1)))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (64, 64), (65, 130), (1000, 3), (3, 1000), (1500, 700)])
+def test_transpose_i64_and_bool(ctx, rows, cols):
+    x = (np.arange(rows * cols, dtype=np.int64) * 6364136223846793005).reshape(rows, cols)
+    a = ctx.new("i64_2d", x)
+    out = ctx.entry_transpose_i64(a)
+    assert np.array_equal(out.values(), x.T)
+    out.free(); a.free()
+    b = (x >> 17) % 3 == 0
+    a = ctx.new("bool_2d", b)
+    out = ctx.entry_transpose_bool(a)
+    assert np.array_equal(out.values(), b.T)
+    out.free(); a.free()
+
+
+@pytest.mark.parametrize("es", [1, 2, 8])
+def test_lmad_copy_routes_transpositions_of_every_width(ctx, es):
+    """A batched transposition given as an LMAD goes to the tiled kernel for 1-, 2- and 8-byte elements
+    as well (the reference instantiates lmad_copy_gpu2gpu for the four widths, rts/c/gpu.h:540-586)."""
+    dt = {1: np.uint8, 2: np.uint16, 8: np.uint64}[es]
+    nb, rows, cols = 3, 130, 70
+    src = (np.arange(nb * rows * cols, dtype=np.uint64) * 11400714819323198485 >> 7).astype(dt).reshape(nb, rows, cols)
+    tname = {1: "bool_2d", 2: "f16_3d", 8: "i64_2d"}[es]
+    shape3 = (nb, rows, cols)
+    if es == 2:
+        s, d = ctx.new(tname, src), ctx.new(tname, np.zeros((nb, cols, rows), dt))
+    elif es == 8:
+        s, d = ctx.new(tname, src.view(np.int64).reshape(nb * rows, cols)), ctx.new(tname, np.zeros((nb * cols, rows), np.int64))
+    else:
+        s, d = ctx.new(tname, src.view(np.bool_).reshape(nb * rows, cols)), ctx.new(tname, np.zeros((nb * cols, rows), np.bool_))
+    # dst[b][c][r] = src[b][r][c]
+    ctx.lmad_copy(es, d.raw, 0, [rows * cols, 1, rows], s.raw, 0, [rows * cols, cols, 1], list(shape3))
+    got = d.values().view(dt).reshape(nb, cols, rows)
+    s.free(); d.free()
+    assert np.array_equal(got, np.transpose(src, (0, 2, 1)))
+
+
+def test_replicate_and_iota(ctx):
+    for n in (0, 1, 255, 100003):
+        r = ctx.entry_replicate_i32(n, -7)
+        assert np.array_equal(r.values(), np.full(n, -7, np.int32))
+        r.free()
+        i = ctx.entry_iota_i64(n)
+        assert np.array_equal(i.values(), np.arange(n, dtype=np.int64))
+        i.free()
+    import futhark_b200 as fb
+    with pytest.raises(fb.FutharkError):
+        ctx.entry_iota_i64(-1)

@@ -150,3 +150,36 @@ def test_a_wait_that_runs_out_is_reported_at_sync_and_the_context_stays_usable(c
     got = out.values()
     assert np.array_equal(got, oracle.scan_i32(xs))
     out.free(); a.free()
+
+
+def test_tuning_parameters_that_act():
+    """The *_num_tblocks parameters cap the persistent grids and rowsum_f32.suff_outer_par moves the
+    version threshold: results stay exact under every setting, and a scan capped to two CTAs (one
+    propagates, one works) is several times slower than the uncapped one."""
+    import json
+    import time
+
+    import oracle
+    from futhark_b200 import datagen
+    n = 1 << 22
+    xs = datagen.workload_i32(n)
+    _, flags, vals = datagen.workload_seg_f32(200003)
+    vals = np.round(vals * 4).astype(np.float32)                       # small integers: exact sums
+    rows = np.round(datagen.workload_rows_f32(3, 70000)).astype(np.float32)
+    times = {}
+    for cap in (0, 2, 7):
+        with fb.Context(profiling=True, tuning={"scan_i32.segscan_num_tblocks": cap, "reduce_i32.segred_num_tblocks": cap,
+                                                "segscan_f32.segscan_num_tblocks": cap,
+                                                "rowsum_f32.suff_outer_par": 1 if cap else 32768}) as c:
+            a = c.new("i32_1d", xs)
+            c.entry_scan_i32(a).free()                                   # warm-up
+            c.sync(); c.report()
+            out = c.entry_scan_i32(a)
+            got = out.values()
+            times[cap] = json.loads(c.report())["events"][0]["duration"]
+            assert np.array_equal(got, oracle.scan_i32(xs))
+            assert c.entry_reduce_i32(a) == oracle.reduce_i32(xs)
+            out.free(); a.free()
+            assert np.array_equal(fb.segscan_f32(c, flags, vals), oracle.segscan_f32_seq64(flags, vals).astype(np.float32))
+            assert np.array_equal(fb.rowsum_f32(c, rows), rows.astype(np.float64).sum(axis=1).astype(np.float32))
+    assert times[2] > 3 * times[0], times
