@@ -18,8 +18,15 @@ The reference is single-device; this layer is new.  Per operation:
                   result stays sharded (shard r holds out[offset_r : offset_r + count_r])
   contraction     batch-sharded: no exchange
 
-`Group` takes a *local executor*: `LibLocal` drives libfuthark_b200.so; the CPU tests pass
-their own executor with the same methods, so the exchange logic is tested without a GPU.
+Two implementations of the same operations:
+
+  * `NativeGroup` binds the library's own `futhark_b200_group_*` functions (group.cu): the
+    exchange runs inside the library, through NCCL, on the context's stream.  This is what a C
+    host program uses; Python only hands the 128-byte NCCL id from rank 0 to the others.
+  * `Group` does the exchange in Python over `torch.distributed`, on top of a *local executor*:
+    `LibLocal` drives the shard-local entry points of libfuthark_b200.so; the CPU tests pass
+    their own executor with the same methods, so the exchange logic is tested without a GPU
+    (gloo).  It can also overlap an exchange with other kernels on a second stream.
 """
 import ctypes
 
@@ -241,3 +248,93 @@ class Group:
             dist.all_gather_into_tensor(allc, mine, group=self.pg)
             host = allc.cpu()
         return host.numpy().reshape(self.world, len(vals))
+
+
+class NativeGroup:
+    """The sharded operations of one rank through the library's C ABI (`futhark_b200_group_*`).
+    `id_bytes`: the 128 bytes `NativeGroup.unique_id()` returned on one rank."""
+
+    @staticmethod
+    def _lib(ctx):
+        L = ctx.lib
+        if getattr(L, "_group_bound", False):
+            return L
+        vp, pvp, i64, ci = ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64, ctypes.c_int
+        pi64 = ctypes.POINTER(ctypes.c_int64)
+        L.futhark_b200_group_unique_id.argtypes = [vp, ctypes.c_size_t]
+        L.futhark_b200_group_unavailable.restype = ctypes.c_char_p
+        L.futhark_b200_group_new.restype = vp
+        L.futhark_b200_group_new.argtypes = [vp, vp, ci, ci]
+        L.futhark_b200_group_free.argtypes = [vp]
+        L.futhark_b200_group_free.restype = None
+        L.futhark_b200_group_reduce_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+        L.futhark_b200_group_scan_i32.argtypes = [vp, pvp, vp]
+        L.futhark_b200_group_segscan_f32.argtypes = [vp, pvp, vp, vp]
+        L.futhark_b200_group_hist_add_i32.argtypes = [vp, pvp, i64, vp, vp]
+        L.futhark_b200_group_hist_max_f32.argtypes = [vp, pvp, i64, vp, vp]
+        L.futhark_b200_group_filter_u32.argtypes = [vp, pvp, pi64, pi64, vp]
+        L.futhark_b200_group_partition_u32.argtypes = [vp, pvp, pi64, pi64, pi64, vp]
+        L.futhark_b200_group_bmm_f16.argtypes = [vp, pvp, vp, vp]
+        L._group_bound = True
+        return L
+
+    @staticmethod
+    def unique_id(ctx):
+        L = NativeGroup._lib(ctx)
+        buf = ctypes.create_string_buffer(128)
+        if L.futhark_b200_group_unique_id(buf, 128) != 0:
+            raise RuntimeError("NCCL unavailable: %s" % (L.futhark_b200_group_unavailable() or b"?").decode())
+        return buf.raw
+
+    def __init__(self, ctx, id_bytes, rank, world):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.lib = NativeGroup._lib(ctx)
+        self._id = ctypes.create_string_buffer(id_bytes, 128)
+        self.ptr = self.lib.futhark_b200_group_new(ctx.ptr, self._id, rank, world)
+        if not self.ptr:
+            raise RuntimeError(ctx.get_error() or "futhark_b200_group_new failed")
+
+    def close(self):
+        if self.ptr:
+            self.lib.futhark_b200_group_free(self.ptr)
+            self.ptr = None
+
+    def _arr(self, fn, tname, *args):
+        from . import Array
+        out = ctypes.c_void_p()
+        self.ctx._check(fn(self.ptr, ctypes.byref(out), *args))
+        return Array(self.ctx, tname, out.value)
+
+    def reduce_i32(self, xs):
+        out = ctypes.c_int32()
+        self.ctx._check(self.lib.futhark_b200_group_reduce_i32(self.ptr, ctypes.byref(out), xs.ptr))
+        return int(out.value)
+
+    def scan_i32(self, xs):
+        return self._arr(self.lib.futhark_b200_group_scan_i32, "i32_1d", xs.ptr)
+
+    def segscan_f32(self, flags, xs):
+        return self._arr(self.lib.futhark_b200_group_segscan_f32, "f32_1d", flags.ptr, xs.ptr)
+
+    def hist(self, op, B, bins, ws):
+        if op == "add":
+            return self._arr(self.lib.futhark_b200_group_hist_add_i32, "i32_1d", int(B), bins.ptr, ws.ptr)
+        return self._arr(self.lib.futhark_b200_group_hist_max_f32, "f32_1d", int(B), bins.ptr, ws.ptr)
+
+    def filter_u32(self, ks):
+        from . import Array
+        out, off, tot = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_int64()
+        self.ctx._check(self.lib.futhark_b200_group_filter_u32(self.ptr, ctypes.byref(out), ctypes.byref(off), ctypes.byref(tot), ks.ptr))
+        return Array(self.ctx, "u32_1d", out.value), int(off.value), int(tot.value)
+
+    def partition_u32(self, ks):
+        from . import Pair
+        out, so, ro, ts = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        self.ctx._check(self.lib.futhark_b200_group_partition_u32(self.ptr, ctypes.byref(out), ctypes.byref(so), ctypes.byref(ro), ctypes.byref(ts), ks.ptr))
+        pair = Pair(self.ctx, out.value)
+        s, r = pair.project(0), pair.project(1)
+        pair.free()
+        return s, r, int(so.value), int(ro.value), int(ts.value)
+
+    def bmm_f16(self, A, B):
+        return self._arr(self.lib.futhark_b200_group_bmm_f16, "f32_3d", A.ptr, B.ptr)

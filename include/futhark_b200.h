@@ -502,6 +502,54 @@ int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct f
                                            const struct futhark_bool_1d *in0, CUdeviceptr summaries,
                                            int rank);
 
+/* The sharded operations through the C ABI: a group is one rank of a set of contexts (one per
+ * GPU, in one process or several) that hold contiguous shards of one logical array.  Each
+ * operation runs the shard-local entry points above plus, where it has an exchange step, one
+ * NCCL collective on the context's own stream (NCCL is looked up at run time in the libnccl.so.2
+ * of the process; the library does not link it).  No counterpart in the reference, which is
+ * single-device (rts/c/backends/cuda.h:219).
+ *
+ *  group_unique_id   fills 128 bytes (an ncclUniqueId) on ONE rank; the host program hands them
+ *                    to the others (MPI, a file, a socket, torch.distributed ...)
+ *  group_new         joins the group: ncclCommInitRank on the context's device; collective
+ *  group_from_comm   or: borrows a communicator (ncclComm_t) the host already has
+ *  group_unavailable NULL, or why NCCL could not be loaded
+ *  group_reduce_i32  the sum over all shards, on every rank (synchronous, like every scalar result)
+ *  group_scan_i32    this rank's shard of the scan of the whole array
+ *  group_segscan_f32 this rank's shard of the flagged segmented scan of the whole array
+ *  group_hist_*      the histogram of the whole array, on every rank
+ *  group_filter_u32 / group_partition_u32   this rank's part of the result, with the offsets at
+ *                    which it lies in the logical result (selected keys of all ranks first, then
+ *                    the rejected ones) and the total number of selected keys
+ *  group_bmm_f16     whole batches per rank: the local contraction */
+struct futhark_b200_group;
+int futhark_b200_group_unique_id(void *id_out, size_t len);
+const char *futhark_b200_group_unavailable(void);
+struct futhark_b200_group *futhark_b200_group_new(struct futhark_context *ctx, const void *unique_id,
+                                                  int rank, int world);
+struct futhark_b200_group *futhark_b200_group_from_comm(struct futhark_context *ctx, void *nccl_comm,
+                                                        int rank, int world);
+void futhark_b200_group_free(struct futhark_b200_group *g);
+int futhark_b200_group_rank(const struct futhark_b200_group *g);
+int futhark_b200_group_size(const struct futhark_b200_group *g);
+int futhark_b200_group_reduce_i32(struct futhark_b200_group *g, int32_t *out0, const struct futhark_i32_1d *in0);
+int futhark_b200_group_scan_i32(struct futhark_b200_group *g, struct futhark_i32_1d **out0,
+                                const struct futhark_i32_1d *in0);
+int futhark_b200_group_segscan_f32(struct futhark_b200_group *g, struct futhark_f32_1d **out0,
+                                   const struct futhark_bool_1d *in0, const struct futhark_f32_1d *in1);
+int futhark_b200_group_hist_add_i32(struct futhark_b200_group *g, struct futhark_i32_1d **out0, const int64_t in0,
+                                    const struct futhark_i32_1d *in1, const struct futhark_i32_1d *in2);
+int futhark_b200_group_hist_max_f32(struct futhark_b200_group *g, struct futhark_f32_1d **out0, const int64_t in0,
+                                    const struct futhark_i32_1d *in1, const struct futhark_f32_1d *in2);
+int futhark_b200_group_filter_u32(struct futhark_b200_group *g, struct futhark_u32_1d **out0, int64_t *offset,
+                                  int64_t *total, const struct futhark_u32_1d *in0);
+int futhark_b200_group_partition_u32(struct futhark_b200_group *g,
+                                     struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 **out0,
+                                     int64_t *sel_offset, int64_t *rej_offset, int64_t *total_selected,
+                                     const struct futhark_u32_1d *in0);
+int futhark_b200_group_bmm_f16(struct futhark_b200_group *g, struct futhark_f32_3d **out0,
+                               const struct futhark_f16_3d *in0, const struct futhark_f16_3d *in1);
+
 /* Inclusive scan (+) over n i32 values in device memory, in -> out, with no allocation of
  * any kind.  It has no counterpart in the reference, whose entry points always allocate
  * their results and temporaries from the context's pool (rts/c/gpu.h:240-316).

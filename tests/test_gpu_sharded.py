@@ -66,6 +66,32 @@ def _worker(rank, world, port, q):
         Aa, Ba = ctx.new("f16_3d", A[blo:bhi]), ctx.new("f16_3d", B[blo:bhi])
         o = g.bmm_f16(Aa, Ba); res["bmm"] = o.values(); o.free(); Aa.free(); Ba.free()
         ctx.sync()
+        # the same operations through the library's own group layer (futhark_b200_group_*, NCCL inside the library)
+        ids = [sharded.NativeGroup.unique_id(ctx) if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        ng = sharded.NativeGroup(ctx, ids[0], rank, world)
+        nat = {}
+        a = ctx.new("i32_1d", xs[lo:hi])
+        nat["reduce"] = ng.reduce_i32(a)
+        o = ng.scan_i32(a); nat["scan"] = o.values(); o.free(); a.free()
+        for mean in (3, 256, 10 ** 9):
+            offsets, flags = datagen.geometric_segments(11, n, mean)
+            vals = datagen.normal_f32(11, 0, n)
+            fa, xa = ctx.new("bool_1d", flags[lo:hi].view(np.bool_)), ctx.new("f32_1d", vals[lo:hi])
+            o = ng.segscan_f32(fa, xa); nat["segscan%d" % mean] = o.values(); o.free(); fa.free(); xa.free()
+        ba, wia, wfa = ctx.new("i32_1d", bins[lo:hi]), ctx.new("i32_1d", wi[lo:hi]), ctx.new("f32_1d", wf[lo:hi])
+        o = ng.hist("add", 1000, ba, wia); nat["hist_add"] = o.values(); o.free()
+        o = ng.hist("max", 1000, ba, wfa); nat["hist_max"] = o.values(); o.free()
+        ba.free(); wia.free(); wfa.free()
+        ka = ctx.new("u32_1d", ks[lo:hi])
+        out, off, total = ng.filter_u32(ka)
+        nat["filter"] = (out.values(), off, total); out.free()
+        s, r, so, ro, tot = ng.partition_u32(ka)
+        nat["partition"] = (s.values(), r.values(), so, ro, tot)
+        s.free(); r.free(); ka.free()
+        nat["bmm"] = res["bmm"]
+        ng.close()
+        res["native"] = nat
         ctx.close()
         q.put((rank, res))
     finally:
@@ -89,6 +115,13 @@ def test_sharded_ops_on_gpus():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
+    _check_results(got, world)
+    _check_results({r: got[r]["native"] for r in range(world)}, world)
+
+
+def _check_results(got, world):
+    import oracle
+    from futhark_b200 import datagen
     n = 3 * 10240 * world + 12345
     xs = datagen.workload_i32(n)
     assert all(got[r]["reduce"] == oracle.reduce_i32(xs) for r in range(world))
