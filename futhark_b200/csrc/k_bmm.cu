@@ -1,5 +1,8 @@
 // Batched dense contraction C[b] = A[b] x B[b], f16 inputs, f32 accumulation, on the
-// 5th-generation tensor cores (tcgen05.mma with the accumulator in tensor memory).
+// 5th-generation tensor cores (tcgen05.mma with the accumulator in tensor memory).  Two
+// kernels: the one described first works with one CTA per 128 x 256 tile and takes any shape
+// the bulk tensor copies can address; where M and N are multiples of 256 the second one, further
+// down, puts a pair of CTAs on a 256 x 256 tile (tcgen05.mma.cta_group::2).
 // Replaces the block/register-tiled SIMT kernel the reference generates for a
 // map-map-reduce nest (src/Futhark/Optimise/BlkRegTiling.hs:68-140,727-743;
 // src/Futhark/CodeGen/ImpGen/GPU/Block.hs:687-722).
@@ -305,6 +308,224 @@ bmm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
+// ---- the same contraction with CTA pairs: tcgen05.mma.cta_group::2 ---------------------------------
+// Two CTAs of a cluster work on one 256 x 256 tile.  CTA r of the pair loads rows r*128 .. +128 of
+// the A tile and columns r*128 .. +128 of the B tile into its own shared memory (its own,
+// non-multicast bulk tensor copies), and holds rows r*128 .. +128 of the accumulator in its own
+// tensor memory; one thread of the pair's first CTA issues M256 N256 K16 instructions that read
+// both CTAs' shared memory.  Per instruction a CTA therefore brings 128 x 64 + 64 x 128 operand
+// elements from L2 for 128 x 256 x 64 multiply-adds of its own, against 128 x 64 + 64 x 256 in the
+// one-CTA kernel above: the L2 -> SM traffic, which bounds that kernel, drops by a third.
+//
+// Barriers: full[s] lives in the first CTA and collects the bytes of both CTAs' copies (the second
+// CTA's copies name it by its cluster address); empty[s] and tmem_full[a] exist in both CTAs and
+// are signalled in both by one tcgen05.commit with a CTA mask; tmem_empty[a] lives in the first
+// CTA and counts the epilogue threads of both.  Every wait is bounded.  The pair meets at a
+// cluster barrier after setting its barriers up and again before anything is torn down, so that
+// no CTA signals into a partner that has left.
+constexpr int P_STAGES = 6;                            // (5 stages measured the same: 133 us on 64 x 1024^3)
+constexpr int P_A_BYTES = BM * BK * 2;                 // 128 x 64 f16: 16 KiB
+constexpr int P_B_BYTES = BK * 128 * 2;                // 64 x 128 f16 as two 64-wide slabs: 16 KiB
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int BMM2_SMEM = P_STAGES * P_STAGE_BYTES + 1024 + 1024 + EPI_BYTES;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// bulk tensor copy into this CTA's shared memory whose completion is counted by a barrier given by
+// its cluster address (it may be the partner's)
+__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorMap *tm, int x, int y, int z, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc2_commit_both(uint64_t *bar) {     // arrives on `bar` in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc2_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor of the pair: D = f32, A = B = f16, A K-major, B MN-major, N = 256, M = 256.
+constexpr uint32_t BMM2_IDESC = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (1u << 16) |
+                                ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+struct Bmm2Barriers {
+  uint64_t full[P_STAGES];        // used in the first CTA only
+  uint64_t empty[P_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];         // used in the first CTA only
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(BMM_THREADS, 1)
+bmm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmC, int nb, int M, int N, int K, int *failure) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Bmm2Barriers *bars = reinterpret_cast<Bmm2Barriers *>(smem + P_STAGES * P_STAGE_BYTES);
+  float *epi = reinterpret_cast<float *>(smem + P_STAGES * P_STAGE_BYTES + 1024);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();             // 0: issues the instructions of the pair
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int tiles_m = M / 256, tiles_n = N / 256;      // the launcher takes this kernel only for multiples of 256
+  const int tiles_per_batch = tiles_m * tiles_n;
+  const int64_t num_tiles = (int64_t)tiles_per_batch * nb;
+  const int kblocks = (K + BK - 1) / BK;
+
+  if (tid == 0) {
+    for (int s = 0; s < P_STAGES; s++) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&bars->tmem_full[a], 1); mbar_init(&bars->tmem_empty[a], 256); }
+    bars->failed = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                  // both CTAs' barriers exist before either signals the other's
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const bool poisoned = ld_failure(failure) != FAIL_NONE;
+
+  if (!poisoned && kblocks > 0) {
+    if (warp == 0) {
+      // ---------------- producer: this CTA's half of A and of B ----------------
+      if (lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = pair; t < num_tiles && ok; t += npairs) {
+          const int batch = (int)(t / tiles_per_batch);
+          const int r = (int)(t % tiles_per_batch);
+          const int m0 = (r / tiles_n) * 256 + (int)rank * 128, n0 = (r % tiles_n) * 256 + (int)rank * 128;
+          for (int kb = 0; kb < kblocks; kb++, it++) {
+            const int s = it % P_STAGES;
+            const uint32_t ph = (it / P_STAGES) & 1;
+            if (!mbar_wait_bounded(&bars->empty[s], ph ^ 1)) { ok = false; break; }
+            uint8_t *sa = smem + s * P_STAGE_BYTES;
+            uint8_t *sb = sa + P_A_BYTES;
+            const uint32_t full0 = map_to_cta(smem_u32(&bars->full[s]), 0);      // the first CTA's barrier
+            if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * P_STAGE_BYTES);     // both CTAs' bytes
+            tma_load_3d_pair(sa, &tmA, kb * BK, m0, batch, full0);
+            tma_load_3d_pair(sb, &tmB, n0, kb * BK, batch, full0);
+            tma_load_3d_pair(sb + B_NBLOCK_BYTES, &tmB, n0 + 64, kb * BK, batch, full0);
+          }
+        }
+        if (!ok) { atomicCAS(failure, FAIL_NONE, FAIL_MMA_TIMEOUT); bars->failed = 1; }
+      }
+    } else if (warp == 1) {
+      // ---------------- MMA issuer: one thread of the first CTA ----------------
+      if (lane == 0 && rank == 0) {
+        uint32_t it = 0, tile_it = 0;
+        bool ok = true;
+        for (int64_t t = pair; t < num_tiles && ok; t += npairs, tile_it++) {
+          const uint32_t acc = tile_it & 1, acc_ph = (tile_it >> 1) & 1;
+          if (!mbar_wait_bounded(&bars->tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * 256;
+          for (int kb = 0; kb < kblocks; kb++, it++) {
+            const int s = it % P_STAGES;
+            const uint32_t ph = (it / P_STAGES) & 1;
+            if (!mbar_wait_bounded(&bars->full[s], ph)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * P_STAGE_BYTES);
+            const uint32_t sb = sa + P_A_BYTES;
+            const uint64_t adesc = make_smem_desc(sa, 16, 1024);
+            const uint64_t bdesc = make_smem_desc(sb, B_NBLOCK_BYTES, 1024);
+#pragma unroll
+            for (int k = 0; k < BK / 16; k++)
+              tc2_mma_f16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), BMM2_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            tc2_commit_both(&bars->empty[s]);          // the stage is free in both CTAs once these instructions have read it
+          }
+          if (ok) tc2_commit_both(&bars->tmem_full[acc]);
+        }
+        if (!ok) { atomicCAS(failure, FAIL_NONE, FAIL_MMA_TIMEOUT); bars->failed = 1; }
+      }
+    } else {
+      // ---------------- epilogue (warps 2..5): this CTA's 128 rows of the tile ----------------
+      const int quarter = warp & 3;
+      uint32_t tile_it = 0;
+      bool ok = true;
+      float *stg = epi + (warp - 2) * (2 * EPI_CHUNK_BYTES / 4);
+      for (int64_t t = pair; t < num_tiles && ok; t += npairs, tile_it++) {
+        const int batch = (int)(t / tiles_per_batch);
+        const int r = (int)(t % tiles_per_batch);
+        const int m0 = (r / tiles_n) * 256 + (int)rank * 128, n0 = (r % tiles_n) * 256;
+        const uint32_t acc = tile_it & 1, acc_ph = (tile_it >> 1) & 1;
+        if (!__all_sync(kFull, mbar_wait_bounded(&bars->tmem_full[acc], acc_ph))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
+        auto emit_tma = [&](const uint32_t (&v)[32], int c) {
+          float *buf = stg + (c & 1) * (EPI_CHUNK_BYTES / 4);
+          if (lane == 0) bulk_wait_read1();
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * q]); o.y = __uint_as_float(v[4 * q + 1]);
+            o.z = __uint_as_float(v[4 * q + 2]); o.w = __uint_as_float(v[4 * q + 3]);
+            *reinterpret_cast<float4 *>(buf + lane * 32 + ((q ^ (lane & 7)) << 2)) = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmC, buf, n0 + c * 32, m0 + quarter * 32, batch);
+            bulk_commit();
+          }
+        };
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(taddr0, va);
+#pragma unroll 1
+        for (int c = 0; c < 256 / 32; c += 2) {
+          tmem_ld_wait();
+          tmem_ld_32x32(taddr0 + (c + 1) * 32, vb);
+          emit_tma(va, c);
+          tmem_ld_wait();
+          if (c + 2 < 256 / 32) tmem_ld_32x32(taddr0 + (c + 2) * 32, va);
+          emit_tma(vb, c + 1);
+        }
+        tc_fence_before();
+        mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (!ok) { atomicCAS(failure, FAIL_NONE, FAIL_MMA_TIMEOUT); bars->failed = 1; }
+    }
+  }
+  // ---------------- teardown: every thread of both CTAs arrives here, whatever happened ----------------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                  // nobody signals into a partner that has left
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ---- plain kernel for shapes the TMA path cannot take -----------------------------------------
 __global__ void __launch_bounds__(256)
 bmm_f16_simple_kernel(const __half *__restrict__ A, const __half *__restrict__ B, float *__restrict__ C,
@@ -377,6 +598,16 @@ cudaError_t launch_bmm_f16(const uint16_t *A, const uint16_t *B, float *C, int64
       CUtensorMap tmC = tmA;
       const int c_by_tma = ((n % 4 == 0) && ((((uintptr_t)C) & 15) == 0) &&
                             make_map_3d(&tmC, C, (uint64_t)n, (uint64_t)m, (uint64_t)nb, 32, 32, true)) ? 1 : 0;
+      // tiles of 256 x 256 on CTA pairs where the shape is made of them
+      if (c_by_tma && m % 256 == 0 && n % 256 == 0 && sms >= 2) {
+        err = cudaFuncSetAttribute(bmm_f16_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BMM2_SMEM);
+        if (err != cudaSuccess) return err;
+        const int64_t tiles2 = (m / 256) * (n / 256) * nb;
+        int pairs = sms / 2;
+        if (tiles2 < pairs) pairs = (int)tiles2;
+        bmm_f16_tc2_kernel<<<2 * pairs, BMM_THREADS, BMM2_SMEM, stream>>>(tmA, tmB, tmC, (int)nb, (int)m, (int)n, (int)k, failure);
+        return cudaGetLastError();
+      }
       bmm_f16_tc_kernel<<<grid, BMM_THREADS, BMM_SMEM, stream>>>(tmA, tmB, tmC, c_by_tma, C, (int)nb, (int)m, (int)n, (int)k, failure);
       return cudaGetLastError();
     }
