@@ -54,6 +54,8 @@ static const ArrayType ARRAYS[] = {
     FE_ARRAY(i32, int32_t, 1, "[]i32", "i32"),   FE_ARRAY(i64, int64_t, 1, "[]i64", "i64"), FE_ARRAY(u32, uint32_t, 1, "[]u32", "u32"),
     FE_ARRAY(f32, float, 1, "[]f32", "f32"),     FE_ARRAY(bool, bool, 1, "[]bool", "bool"), FE_ARRAY(f32, float, 2, "[][]f32", "f32"),
     FE_ARRAY(f32, float, 3, "[][][]f32", "f32"), FE_ARRAY(f16, uint16_t, 3, "[][][]f16", "f16"),
+    FE_ARRAY(f64, double, 1, "[]f64", "f64"),    FE_ARRAY(i32, int32_t, 2, "[][]i32", "i32"), FE_ARRAY(i64, int64_t, 2, "[][]i64", "i64"),
+    FE_ARRAY(bool, bool, 2, "[][]bool", "bool"),
 };
 inline const ArrayType *array_type(const std::string &name) {
   for (const ArrayType &a : ARRAYS)
@@ -118,6 +120,21 @@ static const RecordType RECORDS[] = {
      },
      [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
        return futhark_new_opaque_tup2_arr1d_u32_arr1d_u32(c, (futhark_opaque_tup2_arr1d_u32_arr1d_u32 **)obj, (const futhark_u32_1d *)f[0]->arr, (const futhark_u32_1d *)f[1]->arr);
+     }},
+    {"([]i32, []i32, []i32)", {"[]i32", "[]i32", "[]i32"},
+     [](futhark_context *c, void *o) { return futhark_free_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *)o); },
+     [](futhark_context *c, const void *o, int k, Value &out) {
+       futhark_i32_1d *a = nullptr;
+       const auto *obj = (const futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *)o;
+       const int rc = k == 0   ? futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_0(c, &a, obj)
+                      : k == 1 ? futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(c, &a, obj)
+                               : futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_2(c, &a, obj);
+       if (!rc) set_array(out, "[]i32", a);
+       return rc;
+     },
+     [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
+       return futhark_new_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **)obj, (const futhark_i32_1d *)f[0]->arr,
+                                                                    (const futhark_i32_1d *)f[1]->arr, (const futhark_i32_1d *)f[2]->arr);
      }},
     {"(i32, f32)", {"i32", "f32"},
      [](futhark_context *c, void *o) { return futhark_free_opaque_tup2_i32_f32(c, (futhark_opaque_tup2_i32_f32 *)o); },
@@ -198,6 +215,15 @@ struct EntryPoint {
 };
 
 #define FE_IN(i, T) ((const futhark_##T *)in[i]->arr)
+// entry points of the shapes array -> array, (i64, array, array) -> array and (array, array[, array]) -> array
+#define FE_E1(NAME, TI, SI, TO, SO) \
+  {#NAME, {SI}, SO, [](C *c, In in, Value &o) { futhark_##TO *r = nullptr; int rc = futhark_entry_##NAME(c, &r, FE_IN(0, TI)); if (!rc) set_array(o, SO, r); return rc; }}
+#define FE_E2(NAME, T0, S0, T1, S1, TO, SO) \
+  {#NAME, {S0, S1}, SO, [](C *c, In in, Value &o) { futhark_##TO *r = nullptr; int rc = futhark_entry_##NAME(c, &r, FE_IN(0, T0), FE_IN(1, T1)); if (!rc) set_array(o, SO, r); return rc; }}
+#define FE_E3(NAME, T0, S0, T1, S1, T2, S2, TO, SO) \
+  {#NAME, {S0, S1, S2}, SO, [](C *c, In in, Value &o) { futhark_##TO *r = nullptr; int rc = futhark_entry_##NAME(c, &r, FE_IN(0, T0), FE_IN(1, T1), FE_IN(2, T2)); if (!rc) set_array(o, SO, r); return rc; }}
+#define FE_EH(NAME, T1, S1, T2, S2, TO, SO) \
+  {#NAME, {"i64", S1, S2}, SO, [](C *c, In in, Value &o) { futhark_##TO *r = nullptr; int rc = futhark_entry_##NAME(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, T1), FE_IN(2, T2)); if (!rc) set_array(o, SO, r); return rc; }}
 
 inline const std::vector<EntryPoint> &entry_points() {
   typedef futhark_context C;
@@ -220,6 +246,30 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"bmm_f16", {"[][][]f16", "[][][]f16"}, "[][][]f32", [](C *c, In in, Value &o) { futhark_f32_3d *r = nullptr; int rc = futhark_entry_bmm_f16(c, &r, FE_IN(0, f16_3d), FE_IN(1, f16_3d)); if (!rc) set_array(o, "[][][]f32", r); return rc; }},
       {"transpose_f32", {"[][]f32"}, "[][]f32", [](C *c, In in, Value &o) { futhark_f32_2d *r = nullptr; int rc = futhark_entry_transpose_f32(c, &r, FE_IN(0, f32_2d)); if (!rc) set_array(o, "[][]f32", r); return rc; }},
       {"transpose_f32_3d", {"[][][]f32"}, "[][][]f32", [](C *c, In in, Value &o) { futhark_f32_3d *r = nullptr; int rc = futhark_entry_transpose_f32_3d(c, &r, FE_IN(0, f32_3d)); if (!rc) set_array(o, "[][][]f32", r); return rc; }},
+      FE_E1(scan_max_i32, i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_E1(scan_i64, i64_1d, "[]i64", i64_1d, "[]i64"),
+      FE_E1(scanomap_steps_i32, i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_E1(segscan_rows_i32, i32_2d, "[][]i32", i32_2d, "[][]i32"),
+      FE_E1(filter_pos_i32, i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_E1(transpose_f16_3d, f16_3d, "[][][]f16", f16_3d, "[][][]f16"),
+      FE_E1(transpose_i64, i64_2d, "[][]i64", i64_2d, "[][]i64"),
+      FE_E1(transpose_bool, bool_2d, "[][]bool", bool_2d, "[][]bool"),
+      FE_E2(linrec_f32, f32_1d, "[]f32", f32_1d, "[]f32", f32_1d, "[]f32"),
+      FE_E2(filter_by_flag_i32, i32_1d, "[]i32", bool_1d, "[]bool", i32_1d, "[]i32"),
+      FE_EH(hist_and_i32, i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_EH(hist_or_i32, i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_EH(hist_xor_i32, i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_EH(hist_mul_i32, i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_EH(hist_rows_add_i32, i32_2d, "[][]i32", i32_2d, "[][]i32", i32_2d, "[][]i32"),
+      FE_E3(reduce_by_index_min_i32, i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_E3(reduce_by_index_max_i32, i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32", i32_1d, "[]i32"),
+      FE_E3(reduce_by_index_min_u32, u32_1d, "[]u32", i32_1d, "[]i32", u32_1d, "[]u32", u32_1d, "[]u32"),
+      FE_E3(reduce_by_index_max_u32, u32_1d, "[]u32", i32_1d, "[]i32", u32_1d, "[]u32", u32_1d, "[]u32"),
+      FE_E3(reduce_by_index_add_f32, f32_1d, "[]f32", i32_1d, "[]i32", f32_1d, "[]f32", f32_1d, "[]f32"),
+      {"reduce_by_index_2d_add_i32", {"[][]i32", "[]i64", "[]i64", "[]i32"}, "[][]i32", [](C *c, In in, Value &o) { futhark_i32_2d *r = nullptr; int rc = futhark_entry_reduce_by_index_2d_add_i32(c, &r, FE_IN(0, i32_2d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i32_1d)); if (!rc) set_array(o, "[][]i32", r); return rc; }},
+      {"partition2_i32", {"[]i32"}, "([]i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32)", r); return rc; }},
+      {"replicate_i32", {"i64", "i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_replicate_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int32_t>(*in[1])); if (!rc) set_array(o, "[]i32", r); return rc; }},
+      {"iota_i64", {"i64"}, "[]i64", [](C *c, In in, Value &o) { futhark_i64_1d *r = nullptr; int rc = futhark_entry_iota_i64(c, &r, scalar_of<int64_t>(*in[0])); if (!rc) set_array(o, "[]i64", r); return rc; }},
   };
   return table;
 }

@@ -518,6 +518,22 @@ int futhark_free_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(struct futhark_contex
   return 0;
 }
 
+int futhark_new_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(struct futhark_context *ctx, struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **out,
+                                                          const struct futhark_i32_1d *v0, const struct futhark_i32_1d *v1, const struct futhark_i32_1d *v2) {
+  CtxGuard g(ctx);
+  auto *p = (futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *)malloc(sizeof(futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32));
+  if (p == nullptr) return 1;
+  const futhark_i32_1d *src[3] = {v0, v1, v2};
+  for (int i = 0; i < 3; i++) {
+    p->v[i] = (futhark_i32_1d *)malloc(sizeof(futhark_i32_1d));
+    if (p->v[i] == nullptr) return 1;
+    *p->v[i] = *src[i];
+    fb_ref(&p->v[i]->mem);         // the record shares the blocks of its fields (docs/c-api.rst:366-381)
+  }
+  *out = p;
+  return 0;
+}
+
 static int project_tup3(futhark_context *ctx, futhark_i32_1d **out, const futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj, int i) {
   CtxGuard g(ctx);
   futhark_i32_1d *a = (futhark_i32_1d *)malloc(sizeof(futhark_i32_1d));

@@ -96,7 +96,8 @@ def build():
     types["([]i32, []i32, []i32)"] = {
         "kind": "opaque", "ctype": "struct futhark_%s *" % TRIPLE,
         "ops": {"free": "futhark_free_" + TRIPLE},
-        "record": {"fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (TRIPLE, i)} for i in range(3)]},
+        "record": {"new": "futhark_new_" + TRIPLE,
+                   "fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (TRIPLE, i)} for i in range(3)]},
     }
     entries = {}
     for name, (ins, out, tuning) in ENTRIES.items():

@@ -164,10 +164,14 @@ int futhark_project_opaque_tup2_arr1d_u32_arr1d_u32_1(struct futhark_context *ct
                                                       const struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 *obj);
 
 /* ---- opaque triple of i32 arrays returned by partition2_i32 (same naming rule); `free`
- *      releases the three arrays, the projections share them (docs/c-api.rst:383-391) ---------- */
+ *      releases the three arrays, `new` and the projections share them (docs/c-api.rst:366-391) ---------- */
 struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32;
 int futhark_free_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(struct futhark_context *ctx,
                                                            struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_new_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(struct futhark_context *ctx,
+                                                          struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **out,
+                                                          const struct futhark_i32_1d *v0, const struct futhark_i32_1d *v1,
+                                                          const struct futhark_i32_1d *v2);
 int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_0(struct futhark_context *ctx, struct futhark_i32_1d **out,
                                                                 const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
 int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(struct futhark_context *ctx, struct futhark_i32_1d **out,

@@ -30,7 +30,14 @@ def test_lists_entry_points_and_params_without_a_device(cli):
     assert lines["segscan_f32"] == "[]bool []f32 -> []f32"
     assert lines["partition_u32"] == "[]u32 -> ([]u32, []u32)"
     assert lines["hist_add_i32"] == "i64 []i32 []i32 -> []i32"
-    assert len(lines) == 17
+    assert lines["partition2_i32"] == "[]i32 -> ([]i32, []i32, []i32)"
+    assert lines["reduce_by_index_2d_add_i32"] == "[][]i32 []i64 []i64 []i32 -> [][]i32"
+    # the front-ends know every entry point of the manifest, with the same types
+    from futhark_b200 import manifest
+    m = manifest.build()["entry_points"]
+    assert set(lines) == set(m)
+    for name, e in m.items():
+        assert lines[name] == " ".join(i["type"] for i in e["inputs"]) + " -> " + e["output"]["type"], name
     r = run(cli, ["--print-params"])
     assert r.returncode == 0 and b"(thread_block_size)" in r.stdout
     assert run(cli, ["-h"]).stdout.startswith(b"Usage: ")
@@ -72,6 +79,20 @@ def test_text_in_text_out(cli):
     assert run(cli, ["-e", "rowsum_f32"], b"[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]]").stdout == b"[6f32, 15f32]\n"
     assert run(cli, ["-e", "transpose_f32"], b"[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]]").stdout == b"[[1f32, 4f32], [2f32, 5f32], [3f32, 6f32]]\n"
     assert run(cli, ["-e", "segscan_f32"], b"[true, false, true, false] [1.0, 2.0, 3.0, 4.5]").stdout == b"[1f32, 3f32, 3f32, 7.5f32]\n"
+    # the entry points under other specifications, on the reference's own test vectors
+    assert run(cli, ["-e", "partition2_i32"], b"[0,1,2,3,4,5,6,7,8,9]").stdout == b"[0i32, 2i32, 4i32, 6i32, 8i32]\n[3i32, 9i32]\n[1i32, 5i32, 7i32]\n"   # tests/soacs/partition1.fut
+    assert run(cli, ["-e", "filter_pos_i32"], b"[1,0,2,-5,3,-1]").stdout == b"[1i32, 2i32, 3i32]\n"                                                          # tests/soacs/filter1.fut
+    assert run(cli, ["-e", "filter_by_flag_i32"], b"[0, 1, -2, 5, 42] [false, true, true, false, true]").stdout == b"[1i32, -2i32, 42i32]\n"                   # tests/soacs/filter3.fut
+    assert run(cli, ["-e", "scanomap_steps_i32"], b"[83, 1, 4, 99, 33, 0, 6, 5]").stdout == b"[4339i32, 4586i32, 4929i32, 5654i32, 6120i32, 6554i32, 7046i32, 7535i32]\n"   # tests/soacs/scan4.fut
+    assert run(cli, ["-e", "hist_xor_i32"], b"5i64 [0, 0, 0, 0, 0] [6, 1, 4, 5, -1]").stdout == b"[-7i32, 0i32, 0i32, 0i32, 0i32]\n"                          # tests/hist/xor.fut
+    assert run(cli, ["-e", "reduce_by_index_min_i32"], b"[0,0,0,0,0] [0, 1, 2, 3, 4] [1, -1, 1, 1, 1]").stdout == b"[0i32, -1i32, 0i32, 0i32, 0i32]\n"        # tests/hist/min.fut
+    assert run(cli, ["-e", "hist_rows_add_i32"], b"4i64 [[1,2,3],[2,3,3]] [[1,1,1],[1,1,1]]").stdout == b"[[0i32, 1i32, 1i32, 1i32], [0i32, 0i32, 1i32, 2i32]]\n"
+    assert run(cli, ["-e", "segscan_rows_i32"], b"[[1,2,3],[4,5,6]]").stdout == b"[[1i32, 3i32, 6i32], [4i32, 9i32, 15i32]]\n"
+    assert run(cli, ["-e", "scan_i64"], b"[1i64, 2i64, 3i64]").stdout == b"[1i64, 3i64, 6i64]\n"
+    assert run(cli, ["-e", "linrec_f32"], b"[2f32, 2f32, 2f32] [1f32, 1f32, 1f32]").stdout == b"[1f32, 3f32, 7f32]\n"
+    assert run(cli, ["-e", "iota_i64"], b"4i64").stdout == b"[0i64, 1i64, 2i64, 3i64]\n"
+    assert run(cli, ["-e", "replicate_i32"], b"3i64 7i32").stdout == b"[7i32, 7i32, 7i32]\n"
+    assert run(cli, ["-e", "transpose_i64"], b"[[1i64, 2i64, 3i64], [4i64, 5i64, 6i64]]").stdout == b"[[1i64, 4i64], [2i64, 5i64], [3i64, 6i64]]\n"
 
 
 @gpu
@@ -150,7 +171,9 @@ def test_server_without_a_device_fails_loudly(cli):
 @gpu
 def test_server_session_restore_call_store_free(cli, tmp_path):
     s = ServerProc(build.SERVER_BIN)
-    assert "scan_i32" in s.ok("entry_points") and len(s.ok("entry_points")) == 17
+    from futhark_b200 import manifest
+    assert set(s.ok("entry_points")) == set(manifest.build()["entry_points"])
+    assert s.ok('fields "([]i32, []i32, []i32)"') == ["0 []i32", "1 []i32", "2 []i32"]
     assert s.ok("inputs segscan_f32") == ["[]bool", "[]f32"] and s.ok("output segscan_f32") == ["*[]f32"]
     assert s.ok("output partition_u32") == ["*([]u32, []u32)"]
     assert s.ok('kind "([]u32, []u32)"') == ["record"] and s.ok("kind []i32") == ["array"] and s.ok("kind i64") == ["primitive"]
