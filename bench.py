@@ -102,12 +102,17 @@ class ClockSampler:
         self.index, self.proc, self.lines = index, None, []
 
     def start(self):
+        """Starts nvidia-smi and waits (at most 10 s) for its first sample: with eight ranks starting
+        one each, the tool can take seconds to come up, longer than a short timed region lasts."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 10.0 and self.proc.poll() is None:
+                time.sleep(0.05)
         except OSError:
             self.proc = None
 
@@ -612,13 +617,11 @@ def main():
     ctx.sync()
 
     def step_resident():
-        # with several GPUs the exchange of the scan's shard summaries runs beside the row reduction
-        # (not beside the segmented reduction: its persistent grid fills every CTA slot)
-        pending = group.segscan_f32_begin(d_flags, d_xs, exchange=False) if group is not None else None
+        # with several GPUs the exchange of the scan's shard summaries runs on a second stream beside the
+        # segmented reduction (whose 4 CTAs per SM leave room for the collective's kernel) and the row reduction
+        pending = group.segscan_f32_begin(d_flags, d_xs, exchange=True) if group is not None else None
         o1 = ctx.entry_segscan_f32(d_flags, d_xs) if group is None else None
         o2 = ctx.entry_segreduce_f32(d_off, d_flags, d_xs)
-        if group is not None:
-            group.segscan_f32_exchange(pending)
         o3 = ctx.entry_rowsum_f32(d_rows)
         if group is not None:
             o1 = group.segscan_f32_finish(pending)
@@ -646,7 +649,6 @@ def main():
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
     launches = ctx.launch_count - launches0
-    clocks = sampler.stop()
 
     # per-kernel durations, measured live with CUDA event pairs on the library's stream
     ctx.unpause_profiling()
@@ -656,6 +658,7 @@ def main():
     ctx.sync()
     events = json.loads(ctx.report())["events"]
     ctx.pause_profiling()
+    clocks = sampler.stop()              # sampled over the timed steps and the per-kernel pass (the same work)
     per_kernel = {}
     for e in events:
         per_kernel.setdefault(e["name"], []).append(e["duration"])
