@@ -15,6 +15,7 @@ enum FailureCode : int {
   FAIL_LOOKBACK_TIMEOUT = 1,   // a tile waited too long for its predecessors
   FAIL_BULK_COPY_TIMEOUT = 2,  // an mbarrier wait on a bulk copy ran out
   FAIL_MMA_TIMEOUT = 3,        // an mbarrier wait in the tensor-core pipeline ran out
+  FAIL_PEER_TIMEOUT = 4,       // a wait for the summary of another GPU's shard ran out
 };
 
 constexpr int kWarp = 32;

@@ -184,8 +184,8 @@ int futhark_entry_prod_of_sums_i32(struct futhark_context *ctx, int32_t *out0, c
 }
 
 // The caller holds the context's lock.  shard_out (device, 4 words, or NULL): see launch_segscan_f32.
-static int segscan_f32_locked(futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
-                              const struct futhark_f32_1d *in1, uint32_t *shard_out) {
+int segscan_f32_locked(futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
+                       const struct futhark_f32_1d *in1, uint32_t *shard_out, const fb::PeerPush *peer) {
   const int64_t n = in1->shape[0];
   if (in0->shape[0] != n) return bad_sizes(ctx);
   int rc;
@@ -196,7 +196,7 @@ static int segscan_f32_locked(futhark_context *ctx, struct futhark_f32_1d **out0
     LaunchScope ls(ctx, "segscan_f32.segscan", PROV("scan lifted(+) (false,0) (zip flags xs)"), "{" + kv("n", n) + "}");
     rc = fb_cuda_check(ctx, fb::launch_segscan_f32(dptr<uint8_t>(in0->mem), dptr<float>(in1->mem), dptr<float>(out->mem), n, 0.0f, shard_out,
                                                    ctx->lookback_scratch, fb_next_epoch(ctx), ctx->d_failure, ctx->stream,
-                                                   (int)fb_tuning(ctx, "segscan_f32.segscan_num_tblocks")), "segscan_f32");
+                                                   (int)fb_tuning(ctx, "segscan_f32.segscan_num_tblocks"), peer), "segscan_f32");
     ctx->failure_is_an_option = true;
   }
   if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
@@ -208,7 +208,7 @@ int futhark_entry_segscan_f32(struct futhark_context *ctx, struct futhark_f32_1d
                               const struct futhark_f32_1d *in1) {
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
-  return segscan_f32_locked(ctx, out0, in0, in1, nullptr);
+  return segscan_f32_locked(ctx, out0, in0, in1, nullptr, nullptr);
 }
 
 int futhark_entry_segreduce_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_i64_1d *in0,
@@ -242,7 +242,7 @@ int futhark_entry_rowsum_f32(struct futhark_context *ctx, struct futhark_f32_1d 
   if (rows > 0) {
     LaunchScope ls(ctx, "rowsum_f32.segred", PROV("map (reduce (+) 0) xss"), "{" + kv("rows", rows) + "," + kv("cols", cols) + "}");
     rc = fb_cuda_check(ctx, fb::launch_rowsum_f32(dptr<float>(in0->mem), rows, cols, dptr<float>(out->mem), ctx->num_sms, ctx->stream,
-                                                  fb_tuning(ctx, "rowsum_f32.suff_outer_par")), "rowsum_f32");
+                                                  fb_tuning(ctx, "rowsum_f32.suff_outer_par"), (int)fb_tuning(ctx, "rowsum_f32.segred_num_tblocks")), "rowsum_f32");
     if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
   }
   *out0 = out;
@@ -885,7 +885,7 @@ int futhark_b200_entry_segscan_f32_shard(struct futhark_context *ctx, struct fut
   if (!ctx->ready) return not_ready(ctx);
   CtxGuard g(ctx);
   // the scan kernel writes the summary itself: one launch, one critical section
-  return segscan_f32_locked(ctx, out0, in0, in1, reinterpret_cast<uint32_t *>((uintptr_t)summary_dst));
+  return segscan_f32_locked(ctx, out0, in0, in1, reinterpret_cast<uint32_t *>((uintptr_t)summary_dst), nullptr);
 }
 
 int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct futhark_f32_1d *out, const struct futhark_bool_1d *in0,

@@ -21,6 +21,7 @@
 #include <dlfcn.h>
 #include <stdlib.h>
 #include <string.h>
+#include <unistd.h>
 
 #include <mutex>
 #include <string>
@@ -82,6 +83,12 @@ struct futhark_b200_group {
   bool owns_comm;
   int rank, world;
   int32_t *d_xchg;          // exchange area on the device: 4 words per rank, then 4 of this rank
+  // exchange by peer stores (futhark_b200_group_enable_peer_exchange)
+  uint32_t *peer_buf = nullptr;        // this rank's buffer, written by the ranks in front
+  uint32_t **d_peer_bufs = nullptr;    // device array: every rank's buffer as this GPU addresses it
+  void *opened[64] = {nullptr};        // IPC mappings to close
+  uint32_t seq = 0;                    // sequence number of the last segmented scan
+  struct Pending { futhark_f32_1d *out; uint32_t seq; } pending = {nullptr, 0};
 };
 
 static int group_check(futhark_b200_group *g, int rc, const char *what) {
@@ -143,6 +150,10 @@ void futhark_b200_group_free(struct futhark_b200_group *g) {
   {
     CtxGuard guard(g->ctx);
     cudaStreamSynchronize(g->ctx->stream);
+    for (int r = 0; r < 64; r++)
+      if (g->opened[r] != nullptr) cudaIpcCloseMemHandle(g->opened[r]);
+    if (g->d_peer_bufs != nullptr) cudaFree(g->d_peer_bufs);
+    if (g->peer_buf != nullptr) cudaFree(g->peer_buf);
     cudaFree(g->d_xchg);
     if (g->owns_comm) nccl().CommDestroy(g->comm);
   }
@@ -178,21 +189,118 @@ int futhark_b200_group_scan_i32(struct futhark_b200_group *g, struct futhark_i32
   return futhark_b200_entry_scan_i32_carried(ctx, out0, in0, (CUdeviceptr)(uintptr_t)g->d_xchg, g->rank);
 }
 
-int futhark_b200_group_segscan_f32(struct futhark_b200_group *g, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
-                                   const struct futhark_f32_1d *in1) {
+// ---- the summaries of the segmented scan exchanged by peer stores instead of a collective ------------
+// Collective over the group, once: every rank allocates an exchange buffer, the ranks swap the
+// buffers' IPC handles (one all-gather), and each maps the others' buffers.  From then on the
+// scan kernel of a rank writes its shard's summary straight into the buffers of the ranks
+// behind it, and a rank's carry kernel waits for the summaries of the ranks in front: no
+// collective, no second stream, nothing between the kernels of a step.  The buffers hold 16
+// generations; every eighth call the ranks meet in a one-word all-reduce on their streams, so no
+// rank runs more than eight calls ahead of another and a generation is never overwritten before
+// it was read.  Needs one process per GPU, or peer access between the GPUs of one process.
+int futhark_b200_group_enable_peer_exchange(struct futhark_b200_group *g) {
   futhark_context *ctx = g->ctx;
-  int32_t *mine = g->d_xchg + 4 * g->world;
-  futhark_f32_1d *out = nullptr;
-  int rc = futhark_b200_entry_segscan_f32_shard(ctx, &out, (CUdeviceptr)(uintptr_t)mine, in0, in1);
+  if (g->d_peer_bufs != nullptr) return 0;
+  if (g->world > 64) { fb_set_error(ctx, "group: peer exchange supports at most 64 ranks"); return 1; }
+  CtxGuard guard(ctx);
+  struct Card { cudaIpcMemHandle_t handle; long long pid; unsigned long long ptr; int device; int pad; };
+  const size_t bytes = fb::peer_exchange_bytes(g->world);
+  int rc = fb_cuda_check(ctx, cudaMalloc((void **)&g->peer_buf, bytes), "peer exchange buffer");
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaMemset(g->peer_buf, 0, bytes), "peer exchange buffer");
+  Card mine;
+  memset(&mine, 0, sizeof(mine));
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaIpcGetMemHandle(&mine.handle, g->peer_buf), "cudaIpcGetMemHandle");
   if (rc != 0) return rc;
-  {
-    CtxGuard guard(ctx);
-    rc = group_check(g, nccl().AllGather(mine, g->d_xchg, 4, NCCL_INT32, g->comm, ctx->stream), "all-gather of the shard summaries");
+  mine.pid = (long long)getpid();
+  mine.ptr = (unsigned long long)(uintptr_t)g->peer_buf;
+  mine.device = ctx->device;
+  Card *d_cards = nullptr, *h_cards = (Card *)malloc(sizeof(Card) * (size_t)g->world);
+  rc = fb_cuda_check(ctx, cudaMalloc((void **)&d_cards, sizeof(Card) * (size_t)(g->world + 1)), "handle exchange");
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaMemcpyAsync(d_cards + g->world, &mine, sizeof(Card), cudaMemcpyHostToDevice, ctx->stream), "handle exchange");
+  if (rc == 0) rc = group_check(g, nccl().AllGather(d_cards + g->world, d_cards, sizeof(Card), 0 /* ncclInt8 */, g->comm, ctx->stream), "all-gather of the buffer handles");
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaMemcpyAsync(h_cards, d_cards, sizeof(Card) * (size_t)g->world, cudaMemcpyDeviceToHost, ctx->stream), "handle exchange");
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaStreamSynchronize(ctx->stream), "handle exchange");
+  uint32_t *bufs[64];
+  for (int r = 0; r < g->world && rc == 0; r++) {
+    if (r == g->rank) { bufs[r] = g->peer_buf; continue; }
+    if (h_cards[r].pid == mine.pid) {                 // a rank in this process: its pointer is valid here once peer access is on
+      int can = 0;
+      cudaDeviceCanAccessPeer(&can, ctx->device, h_cards[r].device);
+      if (!can) { fb_set_error(ctx, "group: GPU %d cannot address the memory of GPU %d", ctx->device, h_cards[r].device); rc = 1; break; }
+      cudaError_t e = cudaDeviceEnablePeerAccess(h_cards[r].device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+      rc = fb_cuda_check(ctx, e, "cudaDeviceEnablePeerAccess");
+      bufs[r] = reinterpret_cast<uint32_t *>((uintptr_t)h_cards[r].ptr);
+    } else {
+      void *p = nullptr;
+      rc = fb_cuda_check(ctx, cudaIpcOpenMemHandle(&p, h_cards[r].handle, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+      g->opened[r] = p;
+      bufs[r] = reinterpret_cast<uint32_t *>(p);
+    }
   }
-  if (rc == 0) rc = futhark_b200_segscan_f32_apply_carries(ctx, out, in0, (CUdeviceptr)(uintptr_t)g->d_xchg, g->rank);
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaMalloc((void **)&g->d_peer_bufs, sizeof(uint32_t *) * (size_t)g->world), "peer table");
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaMemcpy(g->d_peer_bufs, bufs, sizeof(uint32_t *) * (size_t)g->world, cudaMemcpyHostToDevice), "peer table");
+  // nobody writes into a buffer before every rank has mapped everything: one more collective
+  if (rc == 0) rc = group_check(g, nccl().AllReduce(g->d_xchg, g->d_xchg, 1, NCCL_INT32, NCCL_SUM, g->comm, ctx->stream), "barrier");
+  if (rc == 0) rc = fb_cuda_check(ctx, cudaStreamSynchronize(ctx->stream), "barrier");
+  cudaFree(d_cards);
+  free(h_cards);
+  if (rc != 0 && g->d_peer_bufs != nullptr) { cudaFree(g->d_peer_bufs); g->d_peer_bufs = nullptr; }
+  return rc;
+}
+
+// The segmented scan in two halves, so that the host can put other work of the step between the
+// shard's scan (which sends the summary off) and the carry (which needs the others' summaries).
+int futhark_b200_group_segscan_f32_begin(struct futhark_b200_group *g, const struct futhark_bool_1d *in0, const struct futhark_f32_1d *in1) {
+  futhark_context *ctx = g->ctx;
+  if (g->pending.out != nullptr) { fb_set_error(ctx, "group: a segmented scan is already in progress"); return 1; }
+  CtxGuard guard(ctx);
+  int32_t *mine = g->d_xchg + 4 * g->world;
+  g->seq = g->seq == 0xfffffffeu ? 1u : g->seq + 1u;
+  int rc = 0;
+  futhark_f32_1d *out = nullptr;
+  if (g->d_peer_bufs != nullptr) {
+    if ((g->seq & 7u) == 0u)       // keep the ranks within eight calls of each other (see enable_peer_exchange)
+      rc = group_check(g, nccl().AllReduce(g->d_xchg, g->d_xchg, 1, NCCL_INT32, NCCL_SUM, g->comm, ctx->stream), "pacing all-reduce");
+    fb::PeerPush peer = {g->d_peer_bufs, g->rank, g->world, g->seq};
+    if (rc == 0) rc = segscan_f32_locked(ctx, &out, in0, in1, reinterpret_cast<uint32_t *>(mine), &peer);
+  } else {
+    rc = segscan_f32_locked(ctx, &out, in0, in1, reinterpret_cast<uint32_t *>(mine), nullptr);
+    if (rc == 0) rc = group_check(g, nccl().AllGather(mine, g->d_xchg, 4, NCCL_INT32, g->comm, ctx->stream), "all-gather of the shard summaries");
+    if (rc != 0 && out != nullptr) { fb_unref(ctx, &out->mem); free(out); out = nullptr; }
+  }
+  if (rc != 0) return rc;
+  g->pending.out = out;
+  g->pending.seq = g->seq;
+  return 0;
+}
+
+int futhark_b200_group_segscan_f32_finish(struct futhark_b200_group *g, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0) {
+  futhark_context *ctx = g->ctx;
+  futhark_f32_1d *out = g->pending.out;
+  if (out == nullptr) { fb_set_error(ctx, "group: no segmented scan in progress"); return 1; }
+  g->pending.out = nullptr;
+  int rc;
+  if (g->d_peer_bufs != nullptr) {
+    CtxGuard guard(ctx);
+    if (g->rank > 0 && out->shape[0] > 0) ctx->launch_count++;
+    rc = fb_cuda_check(ctx, fb::launch_segscan_apply_carry_peer(gdptr<float>(out->mem), gdptr<uint8_t>(in0->mem), out->shape[0], g->peer_buf,
+                                                                reinterpret_cast<const uint32_t *>(g->d_xchg + 4 * g->world), g->rank, g->world,
+                                                                g->pending.seq, ctx->d_failure, ctx->num_sms, ctx->stream), "segscan carry");
+    ctx->failure_is_an_option = true;
+  } else {
+    rc = futhark_b200_segscan_f32_apply_carries(ctx, out, in0, (CUdeviceptr)(uintptr_t)g->d_xchg, g->rank);
+  }
   if (rc != 0) { futhark_free_f32_1d(ctx, out); return rc; }
   *out0 = out;
   return 0;
+}
+
+int futhark_b200_group_segscan_f32(struct futhark_b200_group *g, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
+                                   const struct futhark_f32_1d *in1) {
+  int rc = futhark_b200_group_segscan_f32_begin(g, in0, in1);
+  if (rc != 0) return rc;
+  return futhark_b200_group_segscan_f32_finish(g, out0, in0);
 }
 
 int futhark_b200_group_hist_add_i32(struct futhark_b200_group *g, struct futhark_i32_1d **out0, const int64_t in0,

@@ -184,7 +184,7 @@ rowsum_thread_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, f
 }
 
 cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float *out, int num_sms,
-                              cudaStream_t stream, int64_t suff_outer_par) {
+                              cudaStream_t stream, int64_t suff_outer_par, int block_cap) {
   if (rows <= 0) return cudaSuccess;
   if (cols <= 0) return cudaMemsetAsync(out, 0, (size_t)rows * sizeof(float), stream);
   if (cols < 16) {
@@ -194,6 +194,7 @@ cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float
   } else if (cols <= 16384 || rows >= suff_outer_par) {
     int64_t want = (rows * 32 + RED_THREADS - 1) / RED_THREADS;
     int blocks = (int)(want < (int64_t)num_sms * 8 ? want : (int64_t)num_sms * 8);
+    if (block_cap > 0 && block_cap < blocks) blocks = block_cap;       // rowsum_f32.segred_num_tblocks
     const bool vec = (cols % 4 == 0) && ((((uintptr_t)in) & 15) == 0);
     if (vec) rowsum_warp_kernel<true><<<blocks, RED_THREADS, 0, stream>>>(in, rows, cols, out);
     else rowsum_warp_kernel<false><<<blocks, RED_THREADS, 0, stream>>>(in, rows, cols, out);

@@ -71,6 +71,21 @@ template <typename S> struct TileOf {
 __device__ __forceinline__ bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
 
 
+// ---- a shard's summary written into the other GPUs' memory ---------------------------------------
+// Exchange buffer of a rank: PEER_RING generations of `world` slots of 4 words {value, flag,
+// sequence number, -}; generation = sequence number mod PEER_RING.  Rank q writes slot q of the
+// ranks behind it with ordinary peer stores, the sequence number last and with release
+// semantics at system scope; the reader (apply_carry_peer_kernel) acquires it.
+constexpr uint32_t PEER_RING = 16;
+__device__ __forceinline__ void push_summary(uint32_t *const *bufs, int rank, int world, uint32_t seq, uint32_t v, uint32_t f) {
+  for (int r = rank + 1; r < world; r++) {
+    uint32_t *slot = bufs[r] + ((size_t)(seq % PEER_RING) * world + rank) * 4;
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(slot), "r"(v) : "memory");
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(slot + 1), "r"(f) : "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(slot + 2), "r"(seq) : "memory");
+  }
+}
+
 // ---- the propagator (one warp in the whole grid) --------------------------------------------
 // Walks the status words in tile order.  For every contiguous run of published aggregates
 // it writes the inclusive prefixes back.  `seed` is the exclusive prefix of tile 0.
@@ -79,7 +94,7 @@ __device__ __forceinline__ bool aligned16(const void *p) { return (((uintptr_t)p
 // index of the first tile that contains a segment start (all ones if none does).
 template <typename Op>
 __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, uint32_t seed, int *failure,
-                               uint32_t *shard_out) {
+                               uint32_t *shard_out, uint32_t *const *peer_bufs, int peer_rank, int peer_world, uint32_t peer_seq) {
   const int lane = threadIdx.x & 31;
   uint32_t run_v = seed, run_f = 0;     // inclusive prefix of tile pos-1
   uint32_t pos = 0, idle = 0;
@@ -161,6 +176,7 @@ __device__ void run_propagator(uint64_t *status, uint32_t nt, uint32_t epoch, ui
   }
   if (shard_out != nullptr && lane == 0) {
     shard_out[0] = run_v; shard_out[1] = run_f; shard_out[2] = first_flagged; shard_out[3] = 0u;
+    if (peer_bufs != nullptr) push_summary(peer_bufs, peer_rank, peer_world, peer_seq, run_v, run_f);
   }
 }
 
@@ -184,6 +200,10 @@ struct LookbackArgs {
   const int64_t *d_base;   // compaction of one piece of a longer array: selected keys in the pieces before (device word, or NULL)
   int64_t index_base;      // ... and the index of this piece's first key in the whole array
   int64_t seg_len;         // regular segmented scan: the length of every segment
+  // a shard's summary pushed straight into the exchange buffers of the GPUs behind it (or peer_bufs == NULL)
+  uint32_t *const *peer_bufs;   // device array [peer_world]: every rank's exchange buffer, peer-mapped
+  int peer_rank, peer_world;
+  uint32_t peer_seq;            // the call's sequence number (never 0)
   uint32_t *shard_out;     // segmented scan of one shard of a split array: 4 words, see run_propagator (or NULL)
 };
 
@@ -263,7 +283,7 @@ stream_kernel(const LookbackArgs a) {
   const int64_t sel_base = (COMPACT && a.d_base != nullptr) ? *a.d_base : 0;   // selected keys in the pieces before this one
   const bool solo = (gridDim.x == 1);    // a lone CTA turns its own aggregates into prefixes
   if (s_role == 0 && !solo) {
-    if (warp == 0) run_propagator<Op>(a.status, nt, a.epoch, seed, a.failure, a.shard_out);
+    if (warp == 0) run_propagator<Op>(a.status, nt, a.epoch, seed, a.failure, a.shard_out, a.peer_bufs, a.peer_rank, a.peer_world, a.peer_seq);
     return;
   }
   const uint32_t workers = solo ? 1u : gridDim.x - 1;
@@ -579,6 +599,7 @@ stream_kernel(const LookbackArgs a) {
   if (tid == 0) {
     if (solo && a.shard_out != nullptr && !s_fail) {
       a.shard_out[0] = self_v; a.shard_out[1] = self_f; a.shard_out[2] = self_first; a.shard_out[3] = 0u;
+      if (a.peer_bufs != nullptr) push_summary(a.peer_bufs, a.peer_rank, a.peer_world, a.peer_seq, self_v, self_f);
     }
     bulk_wait_read0();                   // shared memory must outlive the last bulk store's reads
     // A failing grid leaves early: a copy still in flight must land before the CTA's shared memory goes.
@@ -643,6 +664,7 @@ static LookbackArgs make_args(const void *in, const uint8_t *flags, void *out, u
   a.epoch = epoch; a.failure = failure;
   a.carry_in = S::kCompact ? 0u : S::Op::kIdentity; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr; a.shard_out = nullptr;
   a.d_base = nullptr; a.index_base = 0; a.seg_len = 1;
+  a.peer_bufs = nullptr; a.peer_rank = 0; a.peer_world = 0; a.peer_seq = 0;
   return a;
 }
 
@@ -695,15 +717,18 @@ cudaError_t launch_segscan_rows_i32(const int32_t *in, int32_t *out, int64_t row
 // A shard's scan leaves a 4-word summary (see run_propagator): {value bits, flag} of its last
 // inclusive prefix, and the index of its first tile that holds a segment start.  An empty
 // shard has the identity (0, no flag, no such tile).
-__global__ void shard_identity_kernel(uint32_t *dst) {
+__global__ void shard_identity_kernel(uint32_t *dst, uint32_t *const *peer_bufs, int rank, int world, uint32_t seq) {
   dst[0] = 0u; dst[1] = 0u; dst[2] = 0xffffffffu; dst[3] = 0u;
+  if (peer_bufs != nullptr) push_summary(peer_bufs, rank, world, seq, 0u, 0u);
 }
 
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
-                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap) {
+                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap,
+                               const PeerPush *peer) {
   if (n <= 0) {
     if (shard_out != nullptr) {
-      shard_identity_kernel<<<1, 1, 0, stream>>>(shard_out);
+      shard_identity_kernel<<<1, 1, 0, stream>>>(shard_out, peer ? peer->bufs : nullptr, peer ? peer->rank : 0, peer ? peer->world : 0,
+                                                 peer ? peer->seq : 0u);
       return cudaGetLastError();
     }
     return cudaSuccess;
@@ -713,6 +738,7 @@ cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out
   memcpy(&bits, &carry_in, 4);
   a.carry_in = bits;
   a.shard_out = shard_out;
+  if (peer != nullptr && shard_out != nullptr) { a.peer_bufs = peer->bufs; a.peer_rank = peer->rank; a.peer_world = peer->world; a.peer_seq = peer->seq; }
   return launch_stream<SpecSegScanAddF32>(a, stream, grid_cap);
 }
 
@@ -721,14 +747,47 @@ cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out
 // summary of this shard names the first tile with a segment start: everything before that
 // tile takes the carry (grid-stride, 16-byte vectors where the array allows), and the last
 // CTA finds the start inside that one tile and finishes the elements in front of it.
+// With peer_seq != 0 the summaries of the shards in front are not gathered by a collective: the
+// GPUs that hold them write them into this GPU's exchange buffer (push_summary), and thread 0 of
+// every CTA waits, bounded, until the sequence number of each has arrived.  `summaries` then is the
+// generation of the ring this call uses, `own` the shard's own 4-word summary.
 __global__ void __launch_bounds__(256)
-apply_carry_kernel(float *__restrict__ out, const uint8_t *__restrict__ flags, int64_t n, const uint32_t *summaries, int rank) {
+apply_carry_kernel(float *__restrict__ out, const uint8_t *__restrict__ flags, int64_t n, const uint32_t *summaries, const uint32_t *own,
+                   int rank, uint32_t peer_seq, int *failure) {
   constexpr int64_t TILE = TileOf<SpecSegScanAddF32>::TILE;
   __shared__ int s_first;
-  uint32_t cv = 0, cf = 0;
-  for (int q = 0; q < rank; q++) OpSegAddF32::combine(cv, cf, summaries[4 * q], summaries[4 * q + 1], cv, cf);
-  const float carry = __uint_as_float(cv);
-  const uint32_t ft = summaries[4 * rank + 2];
+  __shared__ uint32_t s_cv, s_ok;
+  if (peer_seq != 0u) {
+    if (threadIdx.x == 0) {
+      uint32_t cv = 0, cf = 0, ok = 1;
+      for (int q = 0; q < rank && ok; q++) {
+        const uint32_t *slot = summaries + 4 * q;
+        uint32_t polls = 0, got = 0;
+        while (true) {
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(slot + 2) : "memory");
+          if (got == peer_seq) break;
+          polls++;
+          if ((polls & 255u) == 0 && (ld_failure(failure) != FAIL_NONE || polls >= (1u << 21))) {
+            atomicCAS(failure, FAIL_NONE, FAIL_PEER_TIMEOUT);
+            ok = 0;
+            break;
+          }
+          __nanosleep(polls > 32 ? 500 : 50);
+        }
+        if (ok) OpSegAddF32::combine(cv, cf, slot[0], slot[1], cv, cf);
+      }
+      s_cv = cv; s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+  } else if (threadIdx.x == 0) {
+    uint32_t cv = 0, cf = 0;
+    for (int q = 0; q < rank; q++) OpSegAddF32::combine(cv, cf, summaries[4 * q], summaries[4 * q + 1], cv, cf);
+    s_cv = cv;
+  }
+  __syncthreads();
+  const float carry = __uint_as_float(s_cv);
+  const uint32_t ft = own[2];
   const int64_t tile_lo = (ft == 0xffffffffu || (int64_t)ft * TILE > n) ? n : (int64_t)ft * TILE;
   const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x, stride = (int64_t)gridDim.x * 256;
   if (aligned16(out)) {
@@ -758,9 +817,19 @@ apply_carry_kernel(float *__restrict__ out, const uint8_t *__restrict__ flags, i
 cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
                                        int rank, int num_sms, cudaStream_t stream) {
   if (n <= 0 || rank <= 0) return cudaSuccess;
-  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, flags, n, summaries, rank);
+  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, flags, n, summaries, summaries + 4 * rank, rank, 0u, nullptr);
   return cudaGetLastError();
 }
+
+cudaError_t launch_segscan_apply_carry_peer(float *out, const uint8_t *flags, int64_t n, const uint32_t *my_buf, const uint32_t *own, int rank,
+                                            int world, uint32_t seq, int *failure, int num_sms, cudaStream_t stream) {
+  if (n <= 0 || rank <= 0) return cudaSuccess;
+  const uint32_t *generation = my_buf + (size_t)(seq % PEER_RING) * world * 4;
+  apply_carry_kernel<<<num_sms * 4, 256, 0, stream>>>(out, flags, n, generation, own, rank, seq, failure);
+  return cudaGetLastError();
+}
+
+size_t peer_exchange_bytes(int world) { return (size_t)PEER_RING * world * 16; }
 
 // Compaction of n 4-byte keys under the predicate `which` (COMPACT_* of kernels.h).  Pieces of
 // at most 2^30 keys are launched one behind the other: inside a piece ranks are 32-bit, across
@@ -900,6 +969,7 @@ extern "C" int futhark_b200_scan_i32_noalloc(const int32_t *in, int32_t *out, in
     a.epoch = epoch; a.failure = failure;
     a.carry_in = 0; a.carry_vals = nullptr; a.carry_n = 0; a.d_count = nullptr; a.shard_out = nullptr;
     a.d_base = nullptr; a.index_base = 0; a.seg_len = 1;
+    a.peer_bufs = nullptr; a.peer_rank = 0; a.peer_world = 0; a.peer_seq = 0;
     err = launch_stream<SpecScanAddI32>(a, st);
     if (err != cudaSuccess) return fail(1, "futhark_b200_scan_i32_noalloc: kernel launch", cudaGetErrorString(err));
   }

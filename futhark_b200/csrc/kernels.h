@@ -24,8 +24,21 @@ cudaError_t launch_expire_wait(void *scratch, uint32_t epoch, uint32_t max_polls
 // Flagged segmented scan.  With shard_out != NULL the kernel also leaves the 4-word summary of
 // the array seen as one shard of a longer one: {f32 bits, flag} of its last inclusive prefix, the
 // index of its first 5120-element tile that holds a segment start (all ones if none), 0.
+// With `peer` the scan kernel also writes {f32 bits, flag, seq} of the summary into the exchange buffers
+// (peer-mapped, peer_exchange_bytes(world) each) of the ranks behind this one.
+struct PeerPush {
+  uint32_t *const *bufs;   // device array [world] of every rank's exchange buffer as this GPU addresses it
+  int rank, world;
+  uint32_t seq;            // sequence number of the call, the same on every rank, never 0
+};
+size_t peer_exchange_bytes(int world);
 cudaError_t launch_segscan_f32(const uint8_t *flags, const float *in, float *out, int64_t n, float carry_in,
-                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap = 0);
+                               uint32_t *shard_out, void *scratch, uint32_t epoch, int *failure, cudaStream_t stream, int grid_cap = 0,
+                               const PeerPush *peer = nullptr);
+// The carry kernel fed by peer stores instead of a gathered array: it waits (bounded; FAIL_PEER_TIMEOUT) for
+// the summaries of ranks 0..rank-1 of call `seq` in this rank's own exchange buffer; `own` is this shard's summary.
+cudaError_t launch_segscan_apply_carry_peer(float *out, const uint8_t *flags, int64_t n, const uint32_t *my_buf, const uint32_t *own, int rank,
+                                            int world, uint32_t seq, int *failure, int num_sms, cudaStream_t stream);
 // Adds the fold of summaries[0..rank) (4 words per shard) to out[0 .. first segment start),
 // the first start being located through summaries[rank].
 cudaError_t launch_segscan_apply_carry(float *out, const uint8_t *flags, int64_t n, const uint32_t *summaries,
@@ -66,7 +79,7 @@ size_t reduce_scratch_bytes();
 cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void *scratch, int num_sms,
                               cudaStream_t stream, int block_cap = 0);
 cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float *out, int num_sms,
-                              cudaStream_t stream, int64_t suff_outer_par = 32768);
+                              cudaStream_t stream, int64_t suff_outer_par = 32768, int block_cap = 0);
 // out[s] = sum of xs[offsets[s] .. offsets[s+1]) for s < nseg (offsets ascending, clamped to [0, n]); `scratch` as above.
 cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
                                  void *scratch, int *failure, int num_sms, cudaStream_t stream);

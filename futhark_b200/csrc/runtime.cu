@@ -16,7 +16,7 @@
 
 // ---- tuning parameters ---------------------------------------------------------------------
 // Names follow the reference's "<entry>.<kernel>_<what>" scheme and its size classes
-// (rts/c/backends/cuda.h:552-596).  Four of them act: the three *_num_tblocks of the persistent
+// (rts/c/backends/cuda.h:552-596).  Five of them act: the four *_num_tblocks of the persistent
 // scan / reduce grids cap the number of CTAs (0 = as many as are resident at once), and
 // rowsum_f32.suff_outer_par is the threshold at which the outer parallelism of a row
 // reduction is taken to suffice (one warp per row whatever the row length; below it a long
@@ -33,6 +33,7 @@ const TuningParam kTuningParams[] = {
     {"segscan_f32.segscan_num_tblocks", "grid_size", 0},
     {"segreduce_f32.segred_tblock_size", "thread_block_size", 256},
     {"rowsum_f32.segred_tblock_size", "thread_block_size", 256},
+    {"rowsum_f32.segred_num_tblocks", "grid_size", 0},
     {"rowsum_f32.suff_outer_par", "threshold(def, )", 32768},
     {"hist_add_i32.seghist_tblock_size", "thread_block_size", 1024},
     {"hist_add_i32.seghist_num_tblocks", "grid_size", 0},
@@ -391,6 +392,7 @@ static const char *failure_text(int code) {
     case fb::FAIL_LOOKBACK_TIMEOUT: return "a scan tile waited too long for its predecessors (look-back wait limit reached)";
     case fb::FAIL_BULK_COPY_TIMEOUT: return "a bulk shared-memory copy did not complete within its wait limit";
     case fb::FAIL_MMA_TIMEOUT: return "the tensor-core pipeline did not make progress within its wait limit";
+    case fb::FAIL_PEER_TIMEOUT: return "the summary of another GPU's shard did not arrive within the wait limit";
     default: return "unknown device failure code";
   }
 }

@@ -103,6 +103,13 @@ int fb_ensure_lookback_scratch(futhark_context *ctx, size_t bytes);
 uint32_t fb_next_epoch(futhark_context *ctx);
 int64_t fb_tuning(futhark_context *ctx, const char *name);   // value of a tuning parameter (its default if never set)
 
+// The flagged segmented scan with the context's lock held (entries.cu); shard_out / peer: see kernels.h.
+namespace fb { struct PeerPush; }
+struct futhark_f32_1d;
+struct futhark_bool_1d;
+extern "C" int segscan_f32_locked(futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
+                                  const struct futhark_f32_1d *in1, uint32_t *shard_out, const fb::PeerPush *peer);
+
 // RAII guard: lock + make the context's device current
 struct CtxGuard {
   futhark_context *ctx;

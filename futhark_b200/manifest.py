@@ -38,7 +38,7 @@ ENTRIES = {
     "segscan_f32": ([("flags", "[]bool"), ("xs", "[]f32")], "[]f32", ["segscan_f32.segscan_tblock_size", "segscan_f32.segscan_num_tblocks"]),
     "segscan_rows_i32": ([("xss", "[][]i32")], "[][]i32", []),
     "segreduce_f32": ([("offsets", "[]i64"), ("flags", "[]bool"), ("xs", "[]f32")], "[]f32", ["segreduce_f32.segred_tblock_size"]),
-    "rowsum_f32": ([("xss", "[][]f32")], "[]f32", ["rowsum_f32.segred_tblock_size", "rowsum_f32.suff_outer_par"]),
+    "rowsum_f32": ([("xss", "[][]f32")], "[]f32", ["rowsum_f32.segred_tblock_size", "rowsum_f32.segred_num_tblocks", "rowsum_f32.suff_outer_par"]),
     "hist_add_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", ["hist_add_i32.seghist_tblock_size", "hist_add_i32.seghist_num_tblocks"]),
     "hist_max_f32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]f32")], "[]f32", ["hist_max_f32.seghist_tblock_size"]),
     "hist_and_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", []),

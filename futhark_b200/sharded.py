@@ -270,6 +270,9 @@ class NativeGroup:
         L.futhark_b200_group_reduce_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
         L.futhark_b200_group_scan_i32.argtypes = [vp, pvp, vp]
         L.futhark_b200_group_segscan_f32.argtypes = [vp, pvp, vp, vp]
+        L.futhark_b200_group_segscan_f32_begin.argtypes = [vp, vp, vp]
+        L.futhark_b200_group_segscan_f32_finish.argtypes = [vp, pvp, vp]
+        L.futhark_b200_group_enable_peer_exchange.argtypes = [vp]
         L.futhark_b200_group_hist_add_i32.argtypes = [vp, pvp, i64, vp, vp]
         L.futhark_b200_group_hist_max_f32.argtypes = [vp, pvp, i64, vp, vp]
         L.futhark_b200_group_filter_u32.argtypes = [vp, pvp, pi64, pi64, vp]
@@ -315,6 +318,17 @@ class NativeGroup:
 
     def segscan_f32(self, flags, xs):
         return self._arr(self.lib.futhark_b200_group_segscan_f32, "f32_1d", flags.ptr, xs.ptr)
+
+    def enable_peer_exchange(self):
+        """Collective, once: from now on the scan kernels write their shard summaries straight into the
+        other GPUs' memory and the carry kernels wait for them; no collective in a segmented scan."""
+        self.ctx._check(self.lib.futhark_b200_group_enable_peer_exchange(self.ptr))
+
+    def segscan_f32_begin(self, flags, xs):
+        self.ctx._check(self.lib.futhark_b200_group_segscan_f32_begin(self.ptr, flags.ptr, xs.ptr))
+
+    def segscan_f32_finish(self, flags):
+        return self._arr(self.lib.futhark_b200_group_segscan_f32_finish, "f32_1d", flags.ptr)
 
     def hist(self, op, B, bins, ws):
         if op == "add":

@@ -521,6 +521,12 @@ int futhark_b200_segscan_f32_apply_carries(struct futhark_context *ctx, struct f
  *  group_reduce_i32  the sum over all shards, on every rank (synchronous, like every scalar result)
  *  group_scan_i32    this rank's shard of the scan of the whole array
  *  group_segscan_f32 this rank's shard of the flagged segmented scan of the whole array
+ *  group_segscan_f32_begin / _finish   the same in two halves: the shard's scan, and the carry; what
+ *                    the host enqueues between them runs while the summaries travel
+ *  group_enable_peer_exchange   collective, once: from then on the summaries of the segmented scan
+ *                    are written by the scan kernels straight into the other GPUs' memory (peer
+ *                    stores over NVLink, buffers swapped as CUDA IPC handles) and awaited by the
+ *                    carry kernels with a bounded wait, instead of gathered by a collective
  *  group_hist_*      the histogram of the whole array, on every rank
  *  group_filter_u32 / group_partition_u32   this rank's part of the result, with the offsets at
  *                    which it lies in the logical result (selected keys of all ranks first, then
@@ -541,6 +547,11 @@ int futhark_b200_group_scan_i32(struct futhark_b200_group *g, struct futhark_i32
                                 const struct futhark_i32_1d *in0);
 int futhark_b200_group_segscan_f32(struct futhark_b200_group *g, struct futhark_f32_1d **out0,
                                    const struct futhark_bool_1d *in0, const struct futhark_f32_1d *in1);
+int futhark_b200_group_segscan_f32_begin(struct futhark_b200_group *g, const struct futhark_bool_1d *in0,
+                                         const struct futhark_f32_1d *in1);
+int futhark_b200_group_segscan_f32_finish(struct futhark_b200_group *g, struct futhark_f32_1d **out0,
+                                          const struct futhark_bool_1d *in0);
+int futhark_b200_group_enable_peer_exchange(struct futhark_b200_group *g);
 int futhark_b200_group_hist_add_i32(struct futhark_b200_group *g, struct futhark_i32_1d **out0, const int64_t in0,
                                     const struct futhark_i32_1d *in1, const struct futhark_i32_1d *in2);
 int futhark_b200_group_hist_max_f32(struct futhark_b200_group *g, struct futhark_f32_1d **out0, const int64_t in0,

@@ -8,6 +8,9 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
+from futhark_b200 import datagen
+
 pytestmark = pytest.mark.gpu
 
 
@@ -90,6 +93,25 @@ def _worker(rank, world, port, q):
         nat["partition"] = (s.values(), r.values(), so, ro, tot)
         s.free(); r.free(); ka.free()
         nat["bmm"] = res["bmm"]
+        # the segmented scan with its summaries exchanged by peer stores: many calls in a row (the exchange
+        # buffers hold 16 generations and the ranks are paced every eighth call), with the ranks out of step
+        ng.enable_peer_exchange()
+        import time
+        peer = []
+        for it in range(40):
+            mean = (3, 256, 10 ** 9)[it % 3]
+            offsets, flags = datagen.geometric_segments(100 + it, n, mean)
+            vals = datagen.uniform_i32(200 + it, 0, n, -8, 8).astype(np.float32)
+            fa, xa = ctx.new("bool_1d", flags[lo:hi].view(np.bool_)), ctx.new("f32_1d", vals[lo:hi])
+            if it % 5 == rank:
+                time.sleep(0.02)
+            ng.segscan_f32_begin(fa, xa)
+            o = ng.segscan_f32_finish(fa)
+            if it % 3 == 2 or it > 30:
+                peer.append((it, o.values()))
+            o.free(); fa.free(); xa.free()
+        ctx.sync()
+        nat["peer"] = peer
         ng.close()
         res["native"] = nat
         ctx.close()
@@ -117,11 +139,17 @@ def test_sharded_ops_on_gpus():
         assert p.exitcode == 0
     _check_results(got, world)
     _check_results({r: got[r]["native"] for r in range(world)}, world)
+    # the peer-store exchange: small integers, so every bit is fixed by the definition
+    n = 3 * 10240 * world + 12345
+    for k, (it, _) in enumerate(got[0]["native"]["peer"]):
+        mean = (3, 256, 10 ** 9)[it % 3]
+        offsets, flags = datagen.geometric_segments(100 + it, n, mean)
+        vals = datagen.uniform_i32(200 + it, 0, n, -8, 8).astype(np.float32)
+        whole = np.concatenate([got[r]["native"]["peer"][k][1] for r in range(world)])
+        assert np.array_equal(whole, oracle.segscan_f32_seq64(flags, vals).astype(np.float32)), it
 
 
 def _check_results(got, world):
-    import oracle
-    from futhark_b200 import datagen
     n = 3 * 10240 * world + 12345
     xs = datagen.workload_i32(n)
     assert all(got[r]["reduce"] == oracle.reduce_i32(xs) for r in range(world))
