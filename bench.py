@@ -200,7 +200,7 @@ def workload_config():
     return {"workload": "segmented inclusive scan (+) and segmented reduce (+) over 2^27 f32 in irregular segments "
                         "(geometric lengths, mean 256) + [131072][1024] f32 row reduce",
             "elements_per_step_per_gpu": ELEMS_PER_STEP, "l2": "inputs (1.16 GB per step) are larger than L2",
-            "parallelism": "contiguous shards, one carry exchange for the scan"}
+            "parallelism": "contiguous shards; the scan's shard summaries travel by peer stores, the reductions need no exchange"}
 
 
 # ---- single-SOAC cases: every configuration of the baseline, inputs resident ---------------------
@@ -513,7 +513,7 @@ def run_per_soac(ctx, group, torch, dist, dev, rank, world, reps, warmup):
     return out
 
 
-def verify_sharded(ctx, group, torch, dist, rank, world):
+def verify_sharded(ctx, group, torch, dist, rank, world, native=None):
     """Once, outside every timed region, at a reduced size: each rank checks its shard of the
     sharded scans against the CPU oracle run on its own shard plus the gathered exchange data,
     and the exchange data it contributed against the oracle as well, so the whole chain
@@ -544,7 +544,14 @@ def verify_sharded(ctx, group, torch, dist, rank, world):
         fa, xa = ctx.new("bool_1d", flags.view(np.bool_)), ctx.new("f32_1d", vals)
         o = group.segscan_f32(fa, xa)
         got = o.values()
-        o.free(); fa.free(); xa.free()
+        o.free()
+        got_native = None
+        if native is not None:                 # the path the timed step takes (the library's group layer)
+            native.segscan_f32_begin(fa, xa)
+            o = native.segscan_f32_finish(fa)
+            got_native = o.values()
+            o.free()
+        fa.free(); xa.free()
         local = oracle.segscan_f32_seq64(flags, vals).astype(np.float32)
         s_mine = torch.tensor([float(local[-1]), float(flags.any())], dtype=torch.float32, device="cuda")
         s_all = torch.empty(2 * world, dtype=torch.float32, device="cuda")
@@ -556,6 +563,8 @@ def verify_sharded(ctx, group, torch, dist, rank, world):
         want = local.copy()
         want[:first] = np.float32(carry) + want[:first]
         res["segscan_f32_mean%d" % min(mean, 10 ** 9)] = bool(np.array_equal(got, want))
+        if got_native is not None:
+            res["segscan_f32_native_mean%d" % min(mean, 10 ** 9)] = bool(np.array_equal(got_native, want))
     ok = torch.tensor([int(all(res.values()))] + [int(v) for v in res.values()], dtype=torch.int32, device="cuda")
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     flat = ok.cpu().tolist()
@@ -600,15 +609,19 @@ def main():
     binding = bind_host_thread_near_gpu(local_rank) if world > 1 else {"bound": False, "why": "single rank"}
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    # With several GPUs the row reduction leaves a few CTA slots per SM free, so that the kernel of the
-    # collective that exchanges the scan's summaries can run beside it (measured: 82.7 us with all 8
-    # CTAs per SM, 85.1 us with 6, 87.5 us with 5).
-    cap = int(os.environ.get("FB_BENCH_ROWSUM_CTAS", "6"))
-    tuning = {"rowsum_f32.segred_num_tblocks": torch.cuda.get_device_properties(local_rank).multi_processor_count * cap} if world > 1 and cap > 0 else None
-    ctx = fb.Context(device="#%d" % local_rank, profiling=True, tuning=tuning)
+    ctx = fb.Context(device="#%d" % local_rank, profiling=True)
     ctx.pause_profiling()
     stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
     group = sharded.Group(ctx, stream) if world > 1 else None
+    # the step itself goes through the library's own group layer, with the scan's shard summaries
+    # written by the scan kernels straight into the other GPUs' memory (no collective inside a step)
+    native = None
+    if world > 1:
+        ids = [sharded.NativeGroup.unique_id(ctx) if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        native = sharded.NativeGroup(ctx, ids[0], rank, world)
+        if os.environ.get("FB_BENCH_EXCHANGE", "peer") == "peer":
+            native.enable_peer_exchange()
 
     offsets, flags, xs, rows = make_inputs(rank)
     nseg = offsets.size - 1
@@ -622,15 +635,15 @@ def main():
     ctx.sync()
 
     def step_resident():
-        # with several GPUs the exchange of the scan's shard summaries runs on a second stream beside the row reduction
-        pending = group.segscan_f32_begin(d_flags, d_xs, exchange=False) if group is not None else None
-        o1 = ctx.entry_segscan_f32(d_flags, d_xs) if group is None else None
+        # with several GPUs: the shard's scan (which sends its summary off), the two reductions, then the
+        # carry kernel (which needs the summaries of the shards in front)
+        if native is not None:
+            native.segscan_f32_begin(d_flags, d_xs)
+        o1 = ctx.entry_segscan_f32(d_flags, d_xs) if native is None else None
         o2 = ctx.entry_segreduce_f32(d_off, d_flags, d_xs)
-        if group is not None:
-            group.segscan_f32_exchange(pending)
         o3 = ctx.entry_rowsum_f32(d_rows)
-        if group is not None:
-            o1 = group.segscan_f32_finish(pending)
+        if native is not None:
+            o1 = native.segscan_f32_finish(d_flags)
         o1.free(); o2.free(); o3.free()
 
     def barrier():
@@ -682,7 +695,11 @@ def main():
         a_off = ctx.new("i64_1d", h["offsets"].numpy())
         a_fl = ctx.new("bool_1d", h["flags"].numpy().view(np.bool_))
         a_xs = ctx.new("f32_1d", h["xs"].numpy())
-        o1 = group.segscan_f32(a_fl, a_xs) if group is not None else ctx.entry_segscan_f32(a_fl, a_xs)
+        if native is not None:
+            native.segscan_f32_begin(a_fl, a_xs)
+            o1 = native.segscan_f32_finish(a_fl)
+        else:
+            o1 = ctx.entry_segscan_f32(a_fl, a_xs)
         o1.values_into(out_scan.numpy())
         o2 = ctx.entry_segreduce_f32(a_off, a_fl, a_xs)
         o2.values_into(out_seg.numpy())
@@ -710,7 +727,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
 
-    verified = verify_sharded(ctx, group, torch, dist, rank, world) if world > 1 else None
+    verified = verify_sharded(ctx, group, torch, dist, rank, world, native) if world > 1 else None
 
     per_soac, soac_clocks = None, None
     if not args.no_per_soac:
@@ -769,6 +786,8 @@ def main():
     for a in (d_off, d_flags, d_xs, d_rows):
         if a is not None:
             a.free()
+    if native is not None:
+        native.close()
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
