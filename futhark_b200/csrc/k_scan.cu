@@ -5,8 +5,9 @@
 // scan + scatter that prelude/soacs.fut:241-323 expands into.
 //
 // One persistent kernel, templated on a specification type (scan_specs.cuh) that supplies
-// operator, map body, post-operation, flag source and predicate; 256 threads per CTA, 4 CTAs
-// per SM.  A tile holds 256 x 20 = 5120 elements.  Like the reference's kernel it hands
+// operator, map body, post-operation, flag source and predicate; 8 worker warps and one
+// scheduler warp per CTA, 4 CTAs per SM.  A tile holds 256 x 20 = 5120 elements.  Like the
+// reference's kernel it hands
 // prefixes between tiles through one status word per tile (value and state in one 64-bit
 // word, :628-660 there) and numbers its work by a global counter, so that what a tile
 // depends on has always been claimed by a running CTA before it (:444-461).  Where it
@@ -26,15 +27,23 @@
 //     round trip, turning published aggregates into inclusive prefixes.  Visit B reads one
 //     word, its predecessor's prefix.
 //
-//   * Loads run ahead of the threads.  Thread 0 draws work items two iterations ahead and
+//   * Loads run ahead of the threads.  The scheduler warp draws work items ahead and
 //     starts a bulk async copy (TMA) per array of the next item's tile into the other of
-//     two shared-memory buffers; an mbarrier tells the threads when it has landed.  A
-//     thread owns 20 CONSECUTIVE elements = 5 x 16 bytes, an odd stride in 16-byte units,
-//     so the 128-bit shared-memory accesses are conflict-free without padding: sequential
-//     scan in the thread, one shuffle scan of the thread totals, 8 warp totals through
-//     shared memory.  Visit B writes its results back into the buffer and thread 0 sends
-//     it off with one bulk store; compaction ranks the keys, stages them in the buffer at
-//     the 16-byte phase of their destination and copies the runs out as aligned vectors.
+//     two shared-memory buffers; an mbarrier hands the buffer to the workers when it has
+//     landed.  A worker thread owns 20 CONSECUTIVE elements = 5 x 16 bytes, an odd stride in
+//     16-byte units, so the 128-bit shared-memory accesses are conflict-free without
+//     padding: sequential scan in the thread, one shuffle scan of the thread totals, 8 warp
+//     totals through shared memory.  Visit B writes its results back into the buffer and
+//     the scheduler sends it off with one bulk store; compaction ranks the keys, stages
+//     them in the buffer at the 16-byte phase of their destination and the scheduler warp
+//     copies the runs out as aligned vectors.
+//
+//   * The workers wait for little.  In a visit A they leave their warp totals in shared
+//     memory, arrive at a named barrier and go on to the next tile; the scheduler warp waits
+//     there, folds the totals and publishes the aggregate.  In a visit B they meet once (warp
+//     totals and incoming prefix, which the scheduler fetched meanwhile), write their results
+//     and arrive; drawing work, status polls, the store and the wait for the store to have
+//     read its buffer are all the scheduler's.
 //
 // Progress: the propagator exists as soon as any CTA runs and needs the aggregates in
 // tile order.  Visit A waits for nothing, and visit B of tile t is drawn after visit A of
@@ -56,16 +65,49 @@
 
 namespace fb {
 
-constexpr int SCAN_THREADS = 256;
-constexpr int SCAN_WARPS = SCAN_THREADS / 32;
-constexpr int SCAN_TILE_MIN = SCAN_THREADS * 20;          // the smallest tile (V = 5): bounds the number of status words
+constexpr int SCAN_WORKERS = 256;                         // threads that work on the tiles
+constexpr int SCAN_WARPS = SCAN_WORKERS / 32;
+constexpr int SCAN_THREADS = SCAN_WORKERS + 32;           // ... and the scheduler warp
+constexpr int SCAN_TILE_MIN = SCAN_WORKERS * 12;          // the smallest tile a specification may choose (V = 3): bounds the number of status words
+// Named barriers of the tile kernel (0 is __syncthreads); the first two exist once per slot r of a ring of iterations.
+constexpr int BAR_MID = 1;       // +r: visit B: the warp totals and the tile's incoming prefix are written (workers wait, the scheduler arrives)
+constexpr int BAR_DONE = 5;      // +r: the workers are through with the iteration's buffer (workers arrive, the scheduler waits)
+constexpr int BAR_WORKERS = 9;   // the workers among themselves (a tile copied in or out by the threads)
+template <int ID, int COUNT>
+__device__ __forceinline__ void bar_sync() { asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory"); }
+template <int ID, int COUNT>
+__device__ __forceinline__ void bar_arrive() { asm volatile("bar.arrive %0, %1;" ::"n"(ID), "n"(COUNT) : "memory"); }
+// barrier ID + r, r < 4 (the slot of the iteration in a small ring)
+template <int ID, int COUNT>
+__device__ __forceinline__ void bar_sync(int r) {
+  switch (r) {
+    case 0: bar_sync<ID, COUNT>(); break;
+    case 1: bar_sync<ID + 1, COUNT>(); break;
+    case 2: bar_sync<ID + 2, COUNT>(); break;
+    default: bar_sync<ID + 3, COUNT>(); break;
+  }
+}
+template <int ID, int COUNT>
+__device__ __forceinline__ void bar_arrive(int r) {
+  switch (r) {
+    case 0: bar_arrive<ID, COUNT>(); break;
+    case 1: bar_arrive<ID + 1, COUNT>(); break;
+    case 2: bar_arrive<ID + 2, COUNT>(); break;
+    default: bar_arrive<ID + 3, COUNT>(); break;
+  }
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 constexpr int PROP_PER_LANE = 8;                          // status words per lane per round of the propagator
 constexpr int PROP_WINDOW = 32 * PROP_PER_LANE;
 constexpr uint32_t WAIT_MAX_ROUNDS = 1u << 22;            // idle polls before a wait gives up
 
 template <typename S> struct TileOf {
   static constexpr int ITEMS = S::V * 4;
-  static constexpr int TILE = SCAN_THREADS * ITEMS;
+  static constexpr int TILE = SCAN_WORKERS * ITEMS;
+  // bytes of a tile buffer; compaction stages with up to 9 words of padding, the flag bytes lie behind the values
+  static constexpr int FO = S::kCompact ? TILE * 4 + 64 : TILE * 4;
+  static constexpr int SB = S::kCompact ? TILE * 4 + 64 + (S::kFlagArray ? TILE : 0) : TILE * 4 + (S::kFlagArray ? TILE : 64);
 };
 
 __device__ __forceinline__ bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
@@ -252,18 +294,21 @@ stream_kernel(const LookbackArgs a) {
   constexpr bool COMPACT = S::kCompact, PART = S::kPartition;
   constexpr bool ADD = std::is_same<Op, OpAddU32>::value;            // the operator is the wrapping add (counts included)
   constexpr bool REDO = !COMPACT && !SEG && (S::kHasPost || S::kExclusive);   // the second visit folds again from the prefix
-  // bytes of a tile buffer; compaction stages with up to 9 words of padding, the flag bytes lie behind
-  constexpr int FO = COMPACT ? TILE * 4 + 64 : TILE * 4;
-  constexpr int SB = COMPACT ? TILE * 4 + 64 + (HASF ? TILE : 0) : TILE * 4 + (HASF ? TILE : 64);
+  constexpr int FO = TileOf<S>::FO, SB = TileOf<S>::SB;
+  // NBUF tile buffers; the tile of iteration it + DIST is fetched while iteration it computes.  What
+  // belongs to one iteration (warp totals, prefix, named barriers) lives in slot it % RING: the
+  // workers are never more than DIST iterations apart.
+  constexpr int NBUF = S::NBUF, DIST = S::DIST, RING = DIST + 1, IR = DIST + 2;
+  static_assert(DIST >= 1 && DIST < NBUF && RING <= 4, "ring sizes");
   static_assert(!SEG || HASF || S::kSegRegular, "a flagged operator needs a flag source");
   static_assert(!COMPACT || ADD, "compaction counts with the wrapping add");
-  extern __shared__ __align__(128) unsigned char s_buf[];   // two tile buffers
-  __shared__ __align__(8) uint64_t s_bar[2];
-  __shared__ uint32_t s_item[3];         // decoded work items of iterations it, it+1, it+2: tile << 1 | visit A, or ITEM_NONE
-  __shared__ uint32_t s_wv[2][SCAN_WARPS], s_wf[2][SCAN_WARPS];
+  extern __shared__ __align__(128) unsigned char s_buf[];   // the tile buffers
+  __shared__ __align__(8) uint64_t s_bar[NBUF];
+  __shared__ uint32_t s_item[IR];        // work items of iterations it .. it+DIST+1: tile << 1 | visit A, or ITEM_NONE
+  __shared__ uint32_t s_wv[RING][SCAN_WARPS], s_wf[RING][SCAN_WARPS];
   __shared__ uint32_t s_role;
-  __shared__ volatile uint32_t s_fail;
-  __shared__ uint32_t s_ev[2], s_ok[2];
+  __shared__ volatile uint32_t s_fail;      // a worker's wait for a tile ran out
+  __shared__ uint32_t s_ev[RING], s_ok[RING];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (ld_failure(a.failure) != FAIL_NONE) return;
@@ -290,19 +335,14 @@ stream_kernel(const LookbackArgs a) {
   WorkMap wm;
   wm.nt = nt;
   wm.lead = nt < (uint32_t)S::LEAD ? nt : (uint32_t)S::LEAD;
-  // Every worker draws work items until it meets one past the end, so the counter ends at
+  // Every CTA draws work items until it meets one past the end, so the counter ends at
   // total + workers; whoever draws that last value rewinds it for the next launch.
   const uint32_t last_value = wm.total() + workers - 1;
   const bool in_bulk = aligned16(a.in) && (!HASF || aligned16(a.flags));
   const bool out_bulk = !COMPACT && aligned16(a.out);
-  uint32_t self_v = seed, self_f = 0;    // thread 0 of a lone CTA: running inclusive prefix
-  uint32_t self_first = 0xffffffffu;     // ... and the first tile with a segment start
-
-  // The tile of the next iteration is fetched while this iteration computes: one bulk async
-  // copy (TMA) per array into the buffer the iteration before last used, awaited on an
-  // mbarrier.  Work items are therefore drawn two iterations ahead.
   constexpr uint32_t ITEM_NONE = 0xffffffffu;
-  auto encode = [&](uint32_t w) -> uint32_t {     // thread 0: work item -> what the threads need of it
+
+  auto encode = [&](uint32_t w) -> uint32_t {     // work item -> what the threads need of it
     if (w >= wm.total()) return ITEM_NONE;
     bool ia;
     uint32_t t;
@@ -312,71 +352,188 @@ stream_kernel(const LookbackArgs a) {
   auto item_is_bulk = [&](uint32_t item) -> bool {
     return item != ITEM_NONE && in_bulk && ((int64_t)((item >> 1) + 1) * TILE <= a.n);
   };
-  auto arm = [&](int b, uint32_t tile) {   // thread 0: start the copies of a tile into buffer b
-    unsigned char *dst = s_buf + b * SB;
-    const int64_t tb = (int64_t)tile * TILE;
-    mbar_expect_tx(&s_bar[b], TILE * 4 + (HASF ? TILE : 0));
-    bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, TILE * 4, &s_bar[b]);
-    if (HASF) bulk_g2s(dst + FO, a.flags + tb, TILE, &s_bar[b]);
+  // Hands buffer b to the workers for `item`: by the copies' completion, or (no item, a ragged
+  // tile, unaligned arrays: the workers copy the tile in themselves) at once.
+  auto hand_over = [&](int b, uint32_t item) {
+    if (item_is_bulk(item)) {
+      unsigned char *dst = s_buf + b * SB;
+      const int64_t tb = (int64_t)(item >> 1) * TILE;
+      mbar_expect_tx(&s_bar[b], TILE * 4 + (HASF ? TILE : 0));
+      bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, TILE * 4, &s_bar[b]);
+      if (HASF) bulk_g2s(dst + FO, a.flags + tb, TILE, &s_bar[b]);
+    } else {
+      mbar_arrive(&s_bar[b]);
+    }
   };
-  auto draw = [&]() -> uint32_t {          // thread 0
+  auto draw = [&]() -> uint32_t {
     const uint32_t w = atomicAdd(&a.ticket[0], 1u);
     if (w == last_value) atomicExch(&a.ticket[0], 0u);
     return w;
   };
-  uint32_t armed = 0;                    // thread 0: buffers with a copy that has not been consumed
-  if (tid == 0) {
-    mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1);
+  // set-up by the scheduler's lane 0: the buffers' mbarriers, the first work items and copies
+  if (warp == SCAN_WARPS && lane == 0) {
+    for (int b = 0; b < NBUF; b++) mbar_init(&s_bar[b], 1);
     fence_mbar_init();
-    const uint32_t w0 = draw();
-    const uint32_t w1 = (w0 < wm.total()) ? draw() : 0xffffffffu;   // a worker stops at its first item past the end
-    const uint32_t i0 = encode(w0);
-    s_item[0] = i0; s_item[1] = encode(w1);
-    if (item_is_bulk(i0)) { arm(0, i0 >> 1); armed |= 1u; }
+    uint32_t prev = 0;
+    for (int k = 0; k <= DIST; k++) {      // a CTA stops drawing at its first item past the end
+      prev = (prev != ITEM_NONE) ? encode(draw()) : ITEM_NONE;
+      s_item[k] = prev;
+    }
+    __threadfence_block();
+    for (int k = 0; k < DIST; k++) hand_over(k % NBUF, s_item[k]);
   }
   __syncthreads();
-  uint32_t phases = 0;                   // bit b: parity the next completion of buffer b's barrier will have
 
+  // ================= the scheduler warp =================================================
+  // Lane 0 draws the work items (two iterations ahead), starts the bulk async copy (TMA) of the
+  // next iteration's tile into the buffer the previous iteration used, fetches the incoming
+  // prefix of a visit B, and when the workers are through with the tile publishes its
+  // aggregate (visit A) or sends the buffer off (visit B).  The workers never wait for any of
+  // that except through the buffer's mbarrier and, in a visit B, for the prefix.
+  if (warp == SCAN_WARPS) {
+    uint32_t self_v = seed, self_f = 0;    // a lone CTA: running inclusive prefix
+    uint32_t self_first = 0xffffffffu;     // ... and the first tile with a segment start
+    bool failed = false;                   // lane 0: a wait ran out; draw nothing more
+    volatile uint32_t *v_item = s_item;
+    for (uint32_t it = 0;; it++) {
+      const int r = (int)(it % RING);
+      const uint32_t item = __shfl_sync(kFull, v_item[it % IR], 0);
+      if (item == ITEM_NONE) break;
+      const bool is_a = (item & 1u) != 0;
+      const uint32_t tile = item >> 1;
+      const int64_t base = (int64_t)tile * TILE;
+      const int count = (int)((a.n - base) < TILE ? (a.n - base) : TILE);
+      const bool full = (count == TILE);
+      uint32_t ahead = ITEM_NONE;          // lane 0: the item DIST iterations on, the newest known
+      uint32_t raw = 0xffffffffu, ev = seed, ok = 1;
+      if (lane == 0) {
+        uint64_t pw = 0;
+        ahead = v_item[(it + DIST) % IR];
+        if (ahead != ITEM_NONE && !failed) raw = draw();              // the item after that; its round trip to L2 ...
+        if (!is_a && tile > 0) pw = ld_status(&a.status[tile - 1]);  // ... and this one overlap the wait below
+        // The buffer of iteration it + DIST was last used NBUF iterations earlier: the workers left it
+        // before that iteration's last barrier, and the bulk stores since then may still be reading.
+        bulk_wait_read<NBUF - 1 - DIST>();
+        hand_over((int)((it + DIST) % NBUF), ahead);
+        if (!is_a) {
+          // the exclusive prefix of the tile (normally there long ago: visit A runs `lead` tiles ahead)
+          if (tile > 0) {
+            uint32_t polls = 0;
+            while (true) {
+              const uint32_t st = status_state(pw, a.epoch);
+              if (st == ST_PREFIX || (SEG && st == ST_AGG && status_flag(pw))) break;
+              polls++;
+              if ((polls & 63u) == 0 && (ld_failure(a.failure) != FAIL_NONE || polls >= WAIT_MAX_ROUNDS)) {
+                atomicCAS(a.failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT);
+                ok = 0;
+                break;
+              }
+              if (polls > 4) __nanosleep(polls > 64 ? 200 : 40);
+              pw = ld_status(&a.status[tile - 1]);
+            }
+            ev = status_value(pw);
+          }
+          s_ev[r] = ev; s_ok[r] = ok;
+          __threadfence_block();
+        }
+      }
+      __syncwarp();
+      if (!is_a) bar_arrive<BAR_MID, SCAN_THREADS>(r);     // the prefix is there
+      bar_sync<BAR_DONE, SCAN_THREADS>(r);                 // the workers are through with the buffer
+      ok = __shfl_sync(kFull, ok, 0);
+      if (s_fail) ok = 0;
+      uint32_t tv, tf, bv, bf;
+      fold_warp_totals<Op>(s_wv[r], s_wf[r], lane, 0, tv, tf, bv, bf);
+      uint32_t *s_tile = reinterpret_cast<uint32_t *>(s_buf + (it % NBUF) * SB);
+      if (is_a) {
+        if (lane == 0) {
+          if (solo) {
+            if (SEG && tf && self_first == 0xffffffffu) self_first = tile;
+            Op::combine(self_v, self_f, tv, tf, self_v, self_f);
+            st_status(&a.status[tile], pack_status(self_v, a.epoch, self_f, ST_PREFIX));
+          } else {
+            st_status(&a.status[tile], pack_status(tv, a.epoch, tf, ST_AGG));
+          }
+        }
+      } else if (!COMPACT) {
+        if (ok && full && out_bulk && lane == 0) {
+          bulk_s2g(reinterpret_cast<uint32_t *>(a.out) + base, s_tile, TILE * 4);
+          bulk_commit();
+        }
+      } else if (ok) {
+        // Each run leaves as one bulk store of its 16-byte aligned body, issued by lane 0, plus up
+        // to three keys in front and behind, stored by the other lanes.  (Same arithmetic as the
+        // workers' staging below.)
+        ev = __shfl_sync(kFull, ev, 0);
+        const uint32_t tile_true = tv;
+        const int64_t true_before = sel_base + (int64_t)ev;
+        uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
+        uint32_t *dstf = PART ? a.out_false + (a.index_base + base - true_before) : nullptr;
+        const uint32_t pad_t = (uint32_t)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3u);
+        const uint32_t pad_f = PART ? (uint32_t)((reinterpret_cast<uintptr_t>(dstf) >> 2) & 3u) : 0u;
+        const uint32_t start_f = ((pad_t + tile_true + 3u) & ~3u) + pad_f;
+        auto send_run = [&](uint32_t *g, uint32_t s0, uint32_t len, int lane0) {
+          // g and s_tile + s0 are congruent modulo 16 bytes
+          uint32_t h = (4u - (s0 & 3u)) & 3u;
+          if (h > len) h = len;
+          const uint32_t nvec = (len - h) >> 2, tail0 = h + (nvec << 2);
+          const uint32_t l = (uint32_t)(lane - lane0);               // lanes lane0 .. lane0+2 take the ends
+          if (l < h) g[l] = s_tile[s0 + l];
+          if (l < len - tail0) g[tail0 + l] = s_tile[s0 + tail0 + l];
+          if (lane == 0 && nvec > 0) bulk_s2g(g + h, s_tile + s0 + h, nvec << 4);
+        };
+        send_run(dst, pad_t, tile_true, 0);
+        if (PART) send_run(dstf, start_f, (uint32_t)count - tile_true, 4);
+        if (lane == 0) bulk_commit();
+        __syncwarp();                      // lane 0 fills the buffer again only after these lanes have read their keys
+        if (tile == nt - 1 && lane == 0) *a.d_count = true_before + (int64_t)tile_true;
+      }
+      if (lane == 0) {
+        if (!ok) failed = true;
+        const uint32_t drawn = (ahead != ITEM_NONE && !failed) ? encode(raw) : ITEM_NONE;
+        v_item[(it + DIST + 1) % IR] = drawn;      // (the slot of the previous iteration's item)
+        __threadfence_block();
+      }
+    }
+    if (lane == 0) {
+      if (solo && a.shard_out != nullptr && !failed) {
+        a.shard_out[0] = self_v; a.shard_out[1] = self_f; a.shard_out[2] = self_first; a.shard_out[3] = 0u;
+        if (a.peer_bufs != nullptr) push_summary(a.peer_bufs, a.peer_rank, a.peer_world, a.peer_seq, self_v, self_f);
+      }
+      bulk_wait_read0();                   // shared memory must outlive the last bulk store's reads
+    }
+    return;
+  }
+
+  // ================= the worker warps =====================================================
   for (uint32_t it = 0;; it++) {
-    const int par = (int)(it & 1u);
-    const uint32_t item = s_item[it % 3];
+    const int nb = (int)(it % NBUF), r = (int)(it % RING);
+    // the buffer is ours once its mbarrier completes (once every NBUF iterations); the iteration's
+    // item was written before that
+    if (!mbar_wait_bounded(&s_bar[nb], (it / NBUF) & 1u)) {
+      atomicCAS(a.failure, FAIL_NONE, FAIL_BULK_COPY_TIMEOUT);
+      s_fail = 1;
+    }
+    const uint32_t item = reinterpret_cast<volatile uint32_t *>(s_item)[it % IR];
     if (item == ITEM_NONE) break;
     const bool is_a = (item & 1u) != 0;
     const uint32_t tile = item >> 1;
-    uint32_t drawn = ITEM_NONE;
-    uint64_t pw = 0;                     // visit B: status word of the tile before
-    if (tid == 0) {
-      const uint32_t i1 = s_item[(it + 1) % 3];
-      uint32_t raw = 0xffffffffu;
-      if (i1 != ITEM_NONE) raw = draw();                           // the item after next; its round trip to L2 ...
-      if (!is_a && tile > 0) pw = ld_status(&a.status[tile - 1]);  // ... and this one overlap the wait below
-      bulk_wait_read0();                 // the bulk store of the previous iteration has read its buffer
-      if (item_is_bulk(i1)) { arm(par ^ 1, i1 >> 1); armed |= 1u << (par ^ 1); }
-      if (i1 != ITEM_NONE) drawn = encode(raw);                    // stored before the barrier
-    }
 
     // ---- the tile: in the buffer, by the bulk copy or (ragged / unaligned) copied in by the threads
-    unsigned char *buf = s_buf + par * SB;
+    unsigned char *buf = s_buf + nb * SB;
     uint32_t *s_tile = reinterpret_cast<uint32_t *>(buf);
     const int64_t base = (int64_t)tile * TILE;
     const int count = (int)((a.n - base) < TILE ? (a.n - base) : TILE);
     const bool full = (count == TILE);
-    if (full && in_bulk) {
-      if (!mbar_wait_bounded(&s_bar[par], (phases >> par) & 1u)) {
-        atomicCAS(a.failure, FAIL_NONE, FAIL_BULK_COPY_TIMEOUT);
-        s_fail = 1;
-      }
-      phases ^= 1u << par;
-      if (tid == 0) armed &= ~(1u << par);
-    } else {
+    if (!(full && in_bulk)) {
       const uint32_t *gin = reinterpret_cast<const uint32_t *>(a.in) + base;
-      for (int i = tid; i < TILE; i += SCAN_THREADS) s_tile[i] = (i < count) ? gin[i] : 0u;     // (what lies past `count` is masked below)
+      for (int i = tid; i < TILE; i += SCAN_WORKERS) s_tile[i] = (i < count) ? gin[i] : 0u;     // (what lies past `count` is masked below)
       if (HASF) {
         unsigned char *sfb = buf + FO;
-        for (int i = tid; i < TILE; i += SCAN_THREADS) sfb[i] = (i < count) ? a.flags[base + i] : (unsigned char)0;
+        for (int i = tid; i < TILE; i += SCAN_WORKERS) sfb[i] = (i < count) ? a.flags[base + i] : (unsigned char)0;
       }
       fence_proxy_async_smem();          // a later bulk copy lands in this buffer: order it after these stores
-      __syncthreads();
+      bar_sync<BAR_WORKERS, SCAN_WORKERS>();
     }
     // A thread owns ITEMS consecutive elements = V 16-byte vectors; V is odd, so the 128-bit
     // shared-memory accesses of a warp are conflict-free.
@@ -453,7 +610,7 @@ stream_kernel(const LookbackArgs a) {
     if (ADD && is_a) {
       // only the tile's aggregate is wanted, and the order does not matter
       const uint32_t t = warp_sum(tv_thread);
-      if (lane == 31) s_wv[par][warp] = t;
+      if (lane == 31) s_wv[r][warp] = t;
     } else {
       // scan of the thread aggregates across the warp
       uint32_t iv = tv_thread, ifl = tf_thread;
@@ -465,146 +622,85 @@ stream_kernel(const LookbackArgs a) {
       }
       xv = __shfl_up_sync(kFull, iv, 1); xf = SEG ? __shfl_up_sync(kFull, ifl, 1) : 0u;
       if (lane == 0) { xv = Op::kIdentity; xf = 0; }
-      if (lane == 31) { s_wv[par][warp] = iv; if (SEG) s_wf[par][warp] = ifl; }
+      if (lane == 31) { s_wv[r][warp] = iv; if (SEG) s_wf[r][warp] = ifl; }
     }
-
-    if (tid == 0) {
-      // visit B: the exclusive prefix of the tile (normally there long ago: visit A runs `lead` tiles ahead)
-      uint32_t ev = seed, ok = 1;
-      if (!is_a && tile > 0) {
-        uint32_t polls = 0;
-        while (true) {
-          const uint32_t st = status_state(pw, a.epoch);
-          if (st == ST_PREFIX || (SEG && st == ST_AGG && status_flag(pw))) break;
-          polls++;
-          if ((polls & 63u) == 0 && (ld_failure(a.failure) != FAIL_NONE || polls >= WAIT_MAX_ROUNDS)) {
-            atomicCAS(a.failure, FAIL_NONE, FAIL_LOOKBACK_TIMEOUT);
-            ok = 0;
-            break;
-          }
-          if (polls > 4) __nanosleep(polls > 64 ? 200 : 40);
-          pw = ld_status(&a.status[tile - 1]);
-        }
-        ev = status_value(pw);
-      }
-      s_ev[par] = ev; s_ok[par] = ok;
-      s_item[(it + 2) % 3] = drawn;
-    }
-    __syncthreads();
-    if (!s_ok[par] || s_fail) break;
-
-    uint32_t tv, tf, bv, bf;
-    fold_warp_totals<Op>(s_wv[par], s_wf[par], lane, warp, tv, tf, bv, bf);
     if (is_a) {
-      if (tid == 0) {
-        if (solo) {
-          if (SEG && tf && self_first == 0xffffffffu) self_first = tile;
-          Op::combine(self_v, self_f, tv, tf, self_v, self_f);
-          st_status(&a.status[tile], pack_status(self_v, a.epoch, self_f, ST_PREFIX));
-        } else {
-          st_status(&a.status[tile], pack_status(tv, a.epoch, tf, ST_AGG));
-        }
-      }
+      // the scheduler folds the warp totals and publishes the aggregate; nobody waits here
+      __threadfence_block();
+      bar_arrive<BAR_DONE, SCAN_THREADS>(r);
       continue;
     }
-    const uint32_t ev = s_ev[par];
-    uint32_t lv, lf;
-    Op::combine(bv, bf, xv, xf, lv, lf);                           // what precedes this thread inside the tile
-    if (!COMPACT) {
-      // what precedes this thread: the tile's incoming prefix, then its left neighbours
-      uint32_t pv, pf;
-      Op::combine(ev, 0u, lv, lf, pv, pf);
-      if (SEG) {
-        // only the elements in front of the thread's first segment start take it
-        const int first = bits ? (__ffs((uint32_t)bits) - 1) : ITEMS;
+    bar_sync<BAR_MID, SCAN_THREADS>(r);         // all warp totals and the tile's incoming prefix are there
+    if (s_ok[r]) {         // (set by the scheduler before the barrier: the same for every worker)
+      uint32_t tv, tf, bv, bf;
+      fold_warp_totals<Op>(s_wv[r], s_wf[r], lane, warp, tv, tf, bv, bf);
+      const uint32_t ev = s_ev[r];
+      uint32_t lv, lf;
+      Op::combine(bv, bf, xv, xf, lv, lf);                           // what precedes this thread inside the tile
+      if (!COMPACT) {
+        // what precedes this thread: the tile's incoming prefix, then its left neighbours
+        uint32_t pv, pf;
+        Op::combine(ev, 0u, lv, lf, pv, pf);
+        if (SEG) {
+          // only the elements in front of the thread's first segment start take it
+          const int first = bits ? (__ffs((uint32_t)bits) - 1) : ITEMS;
 #pragma unroll
-        for (int q = 0; q < ITEMS; q++) {
-          uint32_t ov, of;
-          Op::combine(pv, pf, x[q], 0u, ov, of);
-          if (q < first) x[q] = ov;
+          for (int q = 0; q < ITEMS; q++) {
+            uint32_t ov, of;
+            Op::combine(pv, pf, x[q], 0u, ov, of);
+            if (q < first) x[q] = ov;
+          }
+        } else if (REDO) {
+          // fold once more, from the prefix: element q receives post(scan up to q, element q); for
+          // an exclusive scan, the scan up to q - 1
+          uint32_t sv = pv, sf = 0;
+#pragma unroll
+          for (int q = 0; q < ITEMS; q++) {
+            uint32_t y = S::map(x[q]);
+            if (!full && q >= valid) y = Op::kIdentity;
+            if (S::kExclusive) { const uint32_t o = S::post(sv, x[q]); Op::combine(sv, sf, y, 0u, sv, sf); x[q] = o; }
+            else { Op::combine(sv, sf, y, 0u, sv, sf); x[q] = S::post(sv, x[q]); }
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < ITEMS; q++) { uint32_t of; Op::combine(pv, 0u, x[q], 0u, x[q], of); }
         }
-      } else if (REDO) {
-        // fold once more, from the prefix: element q receives post(scan up to q, element q); for
-        // an exclusive scan, the scan up to q - 1
-        uint32_t sv = pv, sf = 0;
+        int4 *s4 = reinterpret_cast<int4 *>(s_tile) + tid * V;
 #pragma unroll
-        for (int q = 0; q < ITEMS; q++) {
-          uint32_t y = S::map(x[q]);
-          if (!full && q >= valid) y = Op::kIdentity;
-          if (S::kExclusive) { const uint32_t o = S::post(sv, x[q]); Op::combine(sv, sf, y, 0u, sv, sf); x[q] = o; }
-          else { Op::combine(sv, sf, y, 0u, sv, sf); x[q] = S::post(sv, x[q]); }
+        for (int j = 0; j < V; j++) {
+          int4 q; q.x = x[4 * j + 0]; q.y = x[4 * j + 1]; q.z = x[4 * j + 2]; q.w = x[4 * j + 3];
+          s4[j] = q;
+        }
+        if (!(full && out_bulk)) {
+          // ragged tile or unaligned result: the threads copy it out themselves
+          uint32_t *gout = reinterpret_cast<uint32_t *>(a.out) + base;
+          bar_sync<BAR_WORKERS, SCAN_WORKERS>();
+          for (int i = tid; i < count; i += SCAN_WORKERS) gout[i] = s_tile[i];
         }
       } else {
+        // Keys back into the buffer, selected first, each group in order; the scheduler sends the
+        // runs.  Each group is staged at the same offset modulo 4 as its destination, so that the
+        // body of a run moves as aligned 16-byte vectors on both sides.
+        const uint32_t tile_true = tv;
+        const int64_t true_before = sel_base + (int64_t)ev;         // selected keys in earlier tiles (and pieces); a piece has < 2^31 keys
+        uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
+        uint32_t *dstf = PART ? a.out_false + (a.index_base + base - true_before) : nullptr;
+        const uint32_t pad_t = (uint32_t)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3u);
+        const uint32_t pad_f = PART ? (uint32_t)((reinterpret_cast<uintptr_t>(dstf) >> 2) & 3u) : 0u;
+        const uint32_t start_f = ((pad_t + tile_true + 3u) & ~3u) + pad_f;     // first rejected key in the buffer
+        uint32_t rank = lv;
+        const uint32_t first_ord = (uint32_t)tid * ITEMS;
 #pragma unroll
-        for (int q = 0; q < ITEMS; q++) { uint32_t of; Op::combine(pv, 0u, x[q], 0u, x[q], of); }
+        for (int q = 0; q < ITEMS; q++) {
+          if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
+          else if (PART && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
+        }
       }
-      int4 *s4 = reinterpret_cast<int4 *>(s_tile) + tid * V;
-#pragma unroll
-      for (int j = 0; j < V; j++) {
-        int4 q; q.x = x[4 * j + 0]; q.y = x[4 * j + 1]; q.z = x[4 * j + 2]; q.w = x[4 * j + 3];
-        s4[j] = q;
-      }
-      uint32_t *gout = reinterpret_cast<uint32_t *>(a.out) + base;
-      if (full && out_bulk) {
-        fence_proxy_async_smem();        // the bulk store reads what the threads just wrote
-        __syncthreads();
-        if (tid == 0) { bulk_s2g(gout, s_tile, TILE * 4); bulk_commit(); }
-      } else {
-        fence_proxy_async_smem();        // the buffer is filled again by a bulk copy: order it after the stores above
-        __syncthreads();
-        for (int i = tid; i < count; i += SCAN_THREADS) gout[i] = s_tile[i];
-        __syncthreads();                 // the buffer is filled again at the top of the next iteration
-      }
-    } else {
-      // Keys back into the buffer, selected first, each group in order; then out as runs.  Each
-      // group is staged at the same offset modulo 4 as its destination, so that the body of a
-      // run moves as aligned 16-byte vectors on both sides.
-      const uint32_t tile_true = tv;
-      const int64_t true_before = sel_base + (int64_t)ev;         // selected keys in earlier tiles (and pieces); a piece has < 2^31 keys
-      uint32_t *dst = reinterpret_cast<uint32_t *>(a.out) + true_before;
-      uint32_t *dstf = PART ? a.out_false + (a.index_base + base - true_before) : nullptr;
-      const uint32_t pad_t = (uint32_t)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3u);
-      const uint32_t pad_f = PART ? (uint32_t)((reinterpret_cast<uintptr_t>(dstf) >> 2) & 3u) : 0u;
-      const uint32_t start_f = ((pad_t + tile_true + 3u) & ~3u) + pad_f;     // first rejected key in the buffer
-      uint32_t rank = lv;
-      const uint32_t first_ord = (uint32_t)tid * ITEMS;
-#pragma unroll
-      for (int q = 0; q < ITEMS; q++) {
-        if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
-        else if (PART && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
-      }
-      fence_proxy_async_smem();          // the bulk stores below read what the threads just staged
-      __syncthreads();
-      // Each run leaves as one bulk store of its 16-byte aligned body, issued by thread 0, plus up
-      // to three keys in front and behind, stored by lanes of warp 0.
-      if (warp == 0) {
-        auto send_run = [&](uint32_t *g, uint32_t s0, uint32_t len, int lane0) {
-          // g and s_tile + s0 are congruent modulo 16 bytes
-          uint32_t h = (4u - (s0 & 3u)) & 3u;
-          if (h > len) h = len;
-          const uint32_t nvec = (len - h) >> 2, tail0 = h + (nvec << 2);
-          const uint32_t l = (uint32_t)(lane - lane0);               // lanes lane0 .. lane0+2 take the ends
-          if (l < h) g[l] = s_tile[s0 + l];
-          if (l < len - tail0) g[tail0 + l] = s_tile[s0 + tail0 + l];
-          if (lane == 0 && nvec > 0) bulk_s2g(g + h, s_tile + s0 + h, nvec << 4);
-        };
-        send_run(dst, pad_t, tile_true, 0);
-        if (PART) send_run(dstf, start_f, (uint32_t)count - tile_true, 4);
-        if (lane == 0) bulk_commit();
-        __syncwarp();                    // thread 0 fills the buffer again only after these lanes have read their keys
-      }
-      if (tile == nt - 1 && tid == 0) *a.d_count = true_before + (int64_t)tile_true;
     }
-  }
-  if (tid == 0) {
-    if (solo && a.shard_out != nullptr && !s_fail) {
-      a.shard_out[0] = self_v; a.shard_out[1] = self_f; a.shard_out[2] = self_first; a.shard_out[3] = 0u;
-      if (a.peer_bufs != nullptr) push_summary(a.peer_bufs, a.peer_rank, a.peer_world, a.peer_seq, self_v, self_f);
-    }
-    bulk_wait_read0();                   // shared memory must outlive the last bulk store's reads
-    // A failing grid leaves early: a copy still in flight must land before the CTA's shared memory goes.
-    for (int b = 0; b < 2; b++)
-      if (armed & (1u << b)) (void)mbar_wait_bounded(&s_bar[b], (phases >> b) & 1u, 1u << 16);
+    // what the threads wrote is read by the scheduler's bulk store, and the buffer is filled again by a bulk copy
+    fence_proxy_async_smem();
+    __threadfence_block();
+    bar_arrive<BAR_DONE, SCAN_THREADS>(r);
   }
 }
 
@@ -628,7 +724,7 @@ static inline void split_scratch(void *scratch, uint32_t **ticket, uint64_t **st
 template <typename S>
 static cudaError_t launch_stream(LookbackArgs a, cudaStream_t stream, int grid_cap = 0) {
   constexpr int TILE = TileOf<S>::TILE;
-  constexpr size_t smem = 2 * (size_t)(S::kCompact ? TILE * 4 + 64 + (S::kFlagArray ? TILE : 0) : TILE * 4 + (S::kFlagArray ? TILE : 64));
+  constexpr size_t smem = (size_t)S::NBUF * TileOf<S>::SB;
   static int ctas_per_sm_dev[64], num_sms_dev[64];     // per device ordinal (function attributes are per device)
   int dev = 0;
   cudaGetDevice(&dev);

@@ -20,6 +20,7 @@
 //                 pred, in order; a partition also keeps the others, behind them
 //   V, CTAS, LEAD tile geometry: a thread owns V 16-byte vectors (V odd), CTAS CTAs per SM,
 //                 aggregates run LEAD tiles ahead of the scans
+//   NBUF, DIST    tile buffers per CTA, and how many iterations ahead a tile is fetched (DIST < NBUF)
 #pragma once
 #include <stdint.h>
 
@@ -69,7 +70,11 @@ struct SpecDefaults {
   using Op = OpAddU32;
   static constexpr bool kHasPost = false, kExclusive = false, kFlagArray = false, kSegRegular = false;
   static constexpr bool kCompact = false, kPartition = false;
+  // Measured on 2^26 i32 (scan) / 2^27 f32 with flags (segmented scan), V x CTAS x NBUF x DIST:
+  // 5x4x2x1 97 / 213 us; 5x5x2x1 102 / 219 us; 5x3x3x2 102 / 274 us; 5x3x3x1 105 / 295 us;
+  // 3x4x4x2 120 / 318 us; 3x4x3x2 119 / 279 us; 3x5x3x2 123 / 285 us.
   static constexpr int V = 5, CTAS = 4, LEAD = 1024;
+  static constexpr int NBUF = 2, DIST = 1;
   static __device__ __forceinline__ uint32_t map(uint32_t x) { return x; }
   static __device__ __forceinline__ uint32_t post(uint32_t scanned, uint32_t x) { (void)x; return scanned; }
   static __device__ __forceinline__ bool pred(uint32_t key, uint32_t flag) { (void)key; (void)flag; return false; }
@@ -104,7 +109,7 @@ struct SpecScanomapStepI32 : SpecDefaults {
 // per SM 393 / 492 us (no better with a lead of 1536 or 2048 tiles); 7168 keys 368 / 481 us.
 struct SpecCompact : SpecDefaults {
   static constexpr bool kCompact = true;
-  static constexpr int V = 9, CTAS = 3;
+  static constexpr int V = 9, CTAS = 3, NBUF = 2, DIST = 1;
 };
 struct SpecFilterLow3U32 : SpecCompact {                                         // filter (\k -> (k & 7) < 3) ks
   static __device__ __forceinline__ bool pred(uint32_t key, uint32_t) { return (key & 7u) < 3u; }
@@ -128,6 +133,7 @@ struct SpecPartitionDiv3I32 : SpecCompact {
 // travel with the keys, so the tile is smaller (5120 keys, 4 CTAs per SM)
 struct SpecFilterByFlagI32 : SpecDefaults {
   static constexpr bool kCompact = true, kFlagArray = true;
+  static constexpr int V = 5, CTAS = 4, NBUF = 2, DIST = 1;
   static __device__ __forceinline__ bool pred(uint32_t, uint32_t flag) { return flag != 0u; }
 };
 
