@@ -177,7 +177,7 @@ def load():
     L.futhark_entry_exscan_i32.argtypes = [vp, pvp, vp]
     L.futhark_entry_dotprod_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_float), vp, vp]
     L.futhark_entry_prod_of_sums_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp, vp]
-    for name in ("scan_max_i32", "segscan_rows_i32", "scanomap_steps_i32", "filter_pos_i32", "partition2_i32"):
+    for name in ("scan_max_i32", "segscan_rows_i32", "scan_map2_add_i32", "scanomap_steps_i32", "filter_pos_i32", "partition2_i32"):
         getattr(L, "futhark_entry_" + name).argtypes = [vp, pvp, vp]
     L.futhark_entry_filter_by_flag_i32.argtypes = [vp, pvp, vp, vp]
     L.futhark_entry_scan_i64.argtypes = [vp, pvp, vp]
@@ -188,7 +188,7 @@ def load():
     L.futhark_entry_linrec_f32.argtypes = [vp, pvp, vp, vp]
     for name in ("and_i32", "or_i32", "xor_i32", "mul_i32"):
         getattr(L, "futhark_entry_hist_" + name).argtypes = [vp, pvp, i64, vp, vp]
-    for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32"):
+    for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32", "add_f64"):
         getattr(L, "futhark_entry_reduce_by_index_" + name).argtypes = [vp, pvp, vp, vp, vp]
     L.futhark_entry_hist_rows_add_i32.argtypes = [vp, pvp, i64, vp, vp]
     L.futhark_entry_reduce_by_index_2d_add_i32.argtypes = [vp, pvp, vp, vp, vp, vp]
@@ -437,7 +437,7 @@ class Context:
         return self._entry_arr("hist_" + op, "i32_1d", int(B), bins.ptr, ws.ptr)
 
     def entry_reduce_by_index(self, op, dest, bins, ws):
-        """reduce_by_index dest <op> <neutral> (map i64.i32 bins) ws for op in min_i32, max_i32, min_u32, max_u32, add_f32."""
+        """reduce_by_index dest <op> <neutral> (map i64.i32 bins) ws for op in min_i32, max_i32, min_u32, max_u32, add_f32, add_f64."""
         return self._entry_arr("reduce_by_index_" + op, op[-3:] + "_1d", dest.ptr, bins.ptr, ws.ptr)
 
     def entry_hist_rows_add_i32(self, m, iss, vss):
@@ -500,6 +500,9 @@ class Context:
 
     def entry_segscan_rows_i32(self, xss):
         return self._entry_arr("segscan_rows_i32", "i32_2d", xss.ptr)
+
+    def entry_scan_map2_add_i32(self, xss):
+        return self._entry_arr("scan_map2_add_i32", "i32_2d", xss.ptr)
 
     def entry_scanomap_steps_i32(self, xs):
         return self._entry_arr("scanomap_steps_i32", "i32_1d", xs.ptr)
@@ -680,6 +683,10 @@ def scan_max_i32(ctx, xs):
 
 def segscan_rows_i32(ctx, xss):
     return _run(ctx, [("i32_2d", xss)], ctx.entry_segscan_rows_i32)
+
+
+def scan_map2_add_i32(ctx, xss):
+    return _run(ctx, [("i32_2d", xss)], ctx.entry_scan_map2_add_i32)
 
 
 def scanomap_steps_i32(ctx, xs):

@@ -250,6 +250,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       FE_E1(scan_i64, i64_1d, "[]i64", i64_1d, "[]i64"),
       FE_E1(scanomap_steps_i32, i32_1d, "[]i32", i32_1d, "[]i32"),
       FE_E1(segscan_rows_i32, i32_2d, "[][]i32", i32_2d, "[][]i32"),
+      FE_E1(scan_map2_add_i32, i32_2d, "[][]i32", i32_2d, "[][]i32"),
       FE_E1(filter_pos_i32, i32_1d, "[]i32", i32_1d, "[]i32"),
       FE_E1(transpose_f16_3d, f16_3d, "[][][]f16", f16_3d, "[][][]f16"),
       FE_E1(transpose_i64, i64_2d, "[][]i64", i64_2d, "[][]i64"),
@@ -266,6 +267,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       FE_E3(reduce_by_index_min_u32, u32_1d, "[]u32", i32_1d, "[]i32", u32_1d, "[]u32", u32_1d, "[]u32"),
       FE_E3(reduce_by_index_max_u32, u32_1d, "[]u32", i32_1d, "[]i32", u32_1d, "[]u32", u32_1d, "[]u32"),
       FE_E3(reduce_by_index_add_f32, f32_1d, "[]f32", i32_1d, "[]i32", f32_1d, "[]f32", f32_1d, "[]f32"),
+      FE_E3(reduce_by_index_add_f64, f64_1d, "[]f64", i32_1d, "[]i32", f64_1d, "[]f64", f64_1d, "[]f64"),
       {"reduce_by_index_2d_add_i32", {"[][]i32", "[]i64", "[]i64", "[]i32"}, "[][]i32", [](C *c, In in, Value &o) { futhark_i32_2d *r = nullptr; int rc = futhark_entry_reduce_by_index_2d_add_i32(c, &r, FE_IN(0, i32_2d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i32_1d)); if (!rc) set_array(o, "[][]i32", r); return rc; }},
       {"partition2_i32", {"[]i32"}, "([]i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32)", r); return rc; }},
       {"replicate_i32", {"i64", "i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_replicate_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int32_t>(*in[1])); if (!rc) set_array(o, "[]i32", r); return rc; }},

@@ -333,6 +333,27 @@ FB_RBI_ENTRY(min_u32, fb::HOP_MIN_U32, u32_1d)
 FB_RBI_ENTRY(max_u32, fb::HOP_MAX_U32, u32_1d)
 FB_RBI_ENTRY(add_f32, fb::HOP_ADD_F32, f32_1d)
 
+// reduce_by_index dest (+) 0f64 (map i64.i32 is) vs (tests/hist/f64.fut): 8-byte values take the route of
+// atomics on the result in global memory (SegHist.hs:377-560)
+int futhark_entry_reduce_by_index_add_f64(struct futhark_context *ctx, struct futhark_f64_1d **out0, const struct futhark_f64_1d *in0,
+                                          const struct futhark_i32_1d *in1, const struct futhark_f64_1d *in2) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t B = in0->shape[0], n = in1->shape[0];
+  if (in2->shape[0] != n) return bad_sizes(ctx);
+  int rc;
+  futhark_f64_1d *out = make_1d<futhark_f64_1d>(ctx, B, 8, "reduce_by_index_add_f64.out", &rc);
+  if (out == nullptr) return rc;
+  if (B > 0) {
+    LaunchScope ls(ctx, "reduce_by_index_add_f64.seghist", PROV("reduce_by_index dest (+) 0f64 (map i64.i32 is) vs"), "{" + kv("n", n) + "," + kv("bins", B) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_hist_add_f64(B, dptr<int32_t>(in1->mem), dptr<double>(in2->mem), n, dptr<double>(out->mem), dptr<double>(in0->mem),
+                                                    ctx->num_sms, ctx->stream), "reduce_by_index_add_f64");
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
 // map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss (tests/hist/segmented.fut: a SegHist with a
 // segment dimension, SegHist.hs:97-148): one histogram over rows * m bins whose index carries the row.
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const int64_t in0,
@@ -712,6 +733,39 @@ int futhark_entry_transpose_f32_3d(struct futhark_context *ctx, struct futhark_f
   if (out == nullptr) return 1;
   out->shape[0] = in0->shape[0]; out->shape[1] = in0->shape[2]; out->shape[2] = in0->shape[1];
   int rc = transpose_common(ctx, in0->shape[0], in0->shape[1], in0->shape[2], in0->mem, &out->mem);
+  if (rc != 0) { free(out); return rc; }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+// scan (map2 (+)) (replicate k 0) xss over xss: [m][k]i32 (tests/soacs/scan-with-map.fut, scan5.fut): a scan
+// whose operator works on whole rows.  The rows' elements never meet, so the scan is interchanged with
+// the inner map, as the reference does before it extracts kernels (src/Futhark/Transform/ISRWIM.hs):
+// transpose, one regular segmented scan over the k columns laid out as rows, transpose back.
+int futhark_entry_scan_map2_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const struct futhark_i32_2d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t m = in0->shape[0], k = in0->shape[1];
+  futhark_i32_2d *out = (futhark_i32_2d *)malloc(sizeof(futhark_i32_2d));
+  if (out == nullptr) return 1;
+  out->shape[0] = m; out->shape[1] = k;
+  memblock_device cols, scanned;
+  int rc = transpose_common(ctx, 1, m, k, in0->mem, &cols);                    // [k][m]
+  if (rc != 0) { free(out); return rc; }
+  rc = fb_alloc(ctx, (size_t)(m * k) * 4, "scan_map2_add_i32.scanned", &scanned);
+  if (rc != 0) { fb_unref(ctx, &cols); free(out); return rc; }
+  if (m * k > 0) {
+    rc = fb_ensure_lookback_scratch(ctx, fb::lookback_scratch_bytes(m * k));
+    if (rc == 0) {
+      LaunchScope ls(ctx, "scan_map2_add_i32.segscan", PROV("scan (map2 (+)) (replicate k 0) xss"), "{" + kv("m", m) + "," + kv("k", k) + "}");
+      rc = fb_cuda_check(ctx, fb::launch_segscan_rows_i32(dptr<int32_t>(cols), dptr<int32_t>(scanned), k, m, ctx->lookback_scratch,
+                                                          fb_next_epoch(ctx), ctx->d_failure, ctx->stream), "scan_map2_add_i32");
+      ctx->failure_is_an_option = true;
+    }
+  }
+  fb_unref(ctx, &cols);
+  if (rc == 0) rc = transpose_common(ctx, 1, k, m, scanned, &out->mem);        // [m][k]
+  fb_unref(ctx, &scanned);
   if (rc != 0) { free(out); return rc; }
   *out0 = out;
   return FUTHARK_SUCCESS;

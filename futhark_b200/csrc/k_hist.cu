@@ -491,4 +491,27 @@ cudaError_t launch_flatten_2d_index(const int64_t *is, const int64_t *js, int64_
   return cudaGetLastError();
 }
 
+// ---- 8-byte values: atomics straight to the result in global memory --------------------------------
+// The reference's histKernelGlobal (SegHist.hs:377-560) with one sub-histogram: every update is an
+// atomic on the result array, a native one where the hardware has it for the operator and type
+// (Base.hs:720-760 picks; f64 addition is native here).  The result starts as a copy of dest.
+__global__ void __launch_bounds__(256) hist_global_add_f64_kernel(const int32_t *__restrict__ bins, const double *__restrict__ vs, int64_t n,
+                                                                 int64_t B, double *out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int32_t b = bins[i];
+    if (b >= 0 && (int64_t)b < B) atomicAdd(&out[b], vs[i]);
+  }
+}
+cudaError_t launch_hist_add_f64(int64_t B, const int32_t *bins, const double *vs, int64_t n, double *out, const double *dest, int num_sms,
+                                cudaStream_t stream) {
+  if (B <= 0) return cudaSuccess;
+  cudaError_t err = cudaMemcpyAsync(out, dest, (size_t)B * sizeof(double), cudaMemcpyDeviceToDevice, stream);
+  if (err != cudaSuccess || n <= 0) return err;
+  int64_t grid = (n + 255) / 256;
+  if (grid > (int64_t)num_sms * 8) grid = (int64_t)num_sms * 8;
+  hist_global_add_f64_kernel<<<(int)grid, 256, 0, stream>>>(bins, vs, n, B, out);
+  return cudaGetLastError();
+}
+
 }  // namespace fb

@@ -37,6 +37,7 @@ ENTRIES = {
     "scanomap_steps_i32": ([("xs", "[]i32")], "[]i32", []),
     "segscan_f32": ([("flags", "[]bool"), ("xs", "[]f32")], "[]f32", ["segscan_f32.segscan_tblock_size", "segscan_f32.segscan_num_tblocks"]),
     "segscan_rows_i32": ([("xss", "[][]i32")], "[][]i32", []),
+    "scan_map2_add_i32": ([("xss", "[][]i32")], "[][]i32", []),
     "segreduce_f32": ([("offsets", "[]i64"), ("flags", "[]bool"), ("xs", "[]f32")], "[]f32", ["segreduce_f32.segred_tblock_size"]),
     "rowsum_f32": ([("xss", "[][]f32")], "[]f32", ["rowsum_f32.segred_tblock_size", "rowsum_f32.segred_num_tblocks", "rowsum_f32.suff_outer_par"]),
     "hist_add_i32": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i32", ["hist_add_i32.seghist_tblock_size", "hist_add_i32.seghist_num_tblocks"]),
@@ -50,6 +51,7 @@ ENTRIES = {
     "reduce_by_index_min_u32": ([("dest", "[]u32"), ("is", "[]i32"), ("vs", "[]u32")], "[]u32", []),
     "reduce_by_index_max_u32": ([("dest", "[]u32"), ("is", "[]i32"), ("vs", "[]u32")], "[]u32", []),
     "reduce_by_index_add_f32": ([("dest", "[]f32"), ("is", "[]i32"), ("vs", "[]f32")], "[]f32", []),
+    "reduce_by_index_add_f64": ([("dest", "[]f64"), ("is", "[]i32"), ("vs", "[]f64")], "[]f64", []),
     "hist_rows_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vss", "[][]i32")], "[][]i32", []),
     "reduce_by_index_2d_add_i32": ([("dest", "[][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("vs", "[]i32")], "[][]i32", []),
     "filter_u32": ([("ks", "[]u32")], "[]u32", ["filter_u32.segscan_tblock_size"]),

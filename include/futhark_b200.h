@@ -261,6 +261,9 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
  * entry reduce_by_index_max_i32, reduce_by_index_max_u32 ... max / lowest (tests/hist/max.fut)
  * entry reduce_by_index_add_f32 (dest: *[n]f32) (is: []i32) (vs: []f32): [n]f32 =
  *   reduce_by_index dest (+) 0f32 (map i64.i32 is) vs                   (tests/hist/f32.fut; NaN propagates)
+ * entry reduce_by_index_add_f64 (dest: *[n]f64) (is: []i32) (vs: []f64): [n]f64 =
+ *   reduce_by_index dest (+) 0f64 (map i64.i32 is) vs                   (tests/hist/f64.fut; 8-byte values go
+ *   the route of atomics on the result in global memory, SegHist.hs:377-560)
  * entry hist_rows_add_i32 (m: i64) (iss: [][]i32) (vss: [][]i32): [][m]i32 =
  *   map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss           (tests/hist/segmented.fut: the segment
  *   dimension of a SegHist, SegHist.hs:97-148)
@@ -284,6 +287,7 @@ FUTHARK_B200_RBI_ENTRY(max_i32, i32_1d)
 FUTHARK_B200_RBI_ENTRY(min_u32, u32_1d)
 FUTHARK_B200_RBI_ENTRY(max_u32, u32_1d)
 FUTHARK_B200_RBI_ENTRY(add_f32, f32_1d)
+FUTHARK_B200_RBI_ENTRY(add_f64, f64_1d)
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
                                     const int64_t in0, const struct futhark_i32_2d *in1,
                                     const struct futhark_i32_2d *in2);
@@ -352,11 +356,16 @@ int futhark_entry_iota_i64(struct futhark_context *ctx, struct futhark_i64_1d **
  * entry filter_by_flag_i32 (xs: []i32) (keep: []bool): []i32 = (unzip (filter (.1) (zip xs keep))).0
  *   (tests/soacs/filter3.fut: the predicate reads a second array)
  * entry partition2_i32 (xs: []i32): ([]i32, []i32, []i32) =
- *   partition2 (\x -> x % 2 == 0) (\x -> x % 3 == 0) xs   (tests/soacs/partition1.fut; prelude/soacs.fut:293-323) */
+ *   partition2 (\x -> x % 2 == 0) (\x -> x % 3 == 0) xs   (tests/soacs/partition1.fut; prelude/soacs.fut:293-323)
+ * entry scan_map2_add_i32 [m][k] (xss: [m][k]i32): [m][k]i32 = scan (map2 (+)) (replicate k 0) xss
+ *   (tests/soacs/scan-with-map.fut, scan5.fut: an operator on whole rows; the scan is interchanged with the
+ *   inner map and runs as a regular segmented scan over the transposed array) */
 int futhark_entry_scan_max_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
                                const struct futhark_i32_1d *in0);
 int futhark_entry_segscan_rows_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
                                    const struct futhark_i32_2d *in0);
+int futhark_entry_scan_map2_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
+                                    const struct futhark_i32_2d *in0);
 int futhark_entry_scanomap_steps_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
                                      const struct futhark_i32_1d *in0);
 int futhark_entry_filter_pos_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,

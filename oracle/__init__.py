@@ -52,6 +52,8 @@ def lib():
         L.orc_mm_f32.argtypes = [vp, vp, i64, i64, i64, vp]
         L.orc_scan_max_i32.argtypes = [vp, i64, vp]
         L.orc_segscan_rows_i32.argtypes = [vp, i64, i64, vp]
+        L.orc_scan_map2_add_i32.argtypes = [vp, i64, i64, vp]
+        L.orc_reduce_by_index_add_f64.argtypes = [vp, i64, vp, vp, i64]
         L.orc_scanomap_steps_i32.argtypes = [vp, i64, vp]
         L.orc_filter_pos_i32.restype = i64
         L.orc_filter_pos_i32.argtypes = [vp, i64, vp]
@@ -381,6 +383,14 @@ def segscan_rows_i32(xss):
     return out
 
 
+def scan_map2_add_i32(xss):
+    """scan (map2 (+)) (replicate k 0) xss."""
+    xss = _c(xss, np.int32)
+    out = np.empty_like(xss)
+    lib().orc_scan_map2_add_i32(_p(xss), xss.shape[0], xss.shape[1], _p(out))
+    return out
+
+
 def scanomap_steps_i32(xs):
     xs = _c(xs, np.int32)
     out = np.empty_like(xs)
@@ -422,6 +432,14 @@ def reduce_by_index(op, dest, is_, vs):
     dest = _c(dest, dt).copy()
     is_, vs = _c(is_, np.int32), _c(vs, dt)
     lib().orc_reduce_by_index_32(code, _p(dest), dest.size, _p(is_), _p(vs), is_.size)
+    return dest
+
+
+def reduce_by_index_add_f64(dest, is_, vs):
+    """reduce_by_index dest (+) 0f64 (map i64.i32 is) vs, updates applied in input order."""
+    dest = _c(dest, np.float64).copy()
+    is_, vs = _c(is_, np.int32), _c(vs, np.float64)
+    lib().orc_reduce_by_index_add_f64(_p(dest), dest.size, _p(is_), _p(vs), is_.size)
     return dest
 
 

@@ -35,6 +35,20 @@ void orc_segscan_rows_i32(const int32_t *xss, int64_t rows, int64_t cols, int32_
   }
 }
 
+/* scan (map2 (+)) (replicate k 0) xss for xss: [m][k]i32 (tests/soacs/scan-with-map.fut:13-16 with a all
+ * zeros, tests/soacs/scan5.fut:8): the accumulator is a whole row, rows are combined element by element */
+void orc_scan_map2_add_i32(const int32_t *xss, int64_t m, int64_t k, int32_t *out) {
+  for (int64_t i = 0; i < m; i++)
+    for (int64_t j = 0; j < k; j++)
+      out[i * k + j] = wadd(i > 0 ? out[(i - 1) * k + j] : 0, xss[i * k + j]);
+}
+
+/* reduce_by_index dest (+) 0f64 (map i64.i32 is) vs (tests/hist/f64.fut:40-41), in input order */
+void orc_reduce_by_index_add_f64(double *dest, int64_t n, const int32_t *is, const double *vs, int64_t m) {
+  for (int64_t i = 0; i < m; i++)
+    if (is[i] >= 0 && (int64_t)is[i] < n) dest[is[i]] = dest[is[i]] + vs[i];
+}
+
 /* tests/soacs/scan4.fut:11-22, statement by statement */
 static void scan4_step(const int32_t *xs, int64_t n, int32_t *out) {
   int32_t bits_sum = 0;

@@ -8,7 +8,7 @@ Each `.fut` test file carries `-- ==` blocks with `input { ... } output { ... }`
 (format: docs/man/futhark-test.rst:20-120 of the reference).  Only blocks with literal
 outputs are taken (`auto output` pins nothing).  Values are parsed from the Futhark
 value syntax subset these files use: integer and float literals with optional type
-suffixes, `true`/`false`, nested arrays, `empty([0]t)`, and `f32.nan`/`f32.inf`.
+suffixes, `true`/`false`, nested arrays, `empty([0]t)`, and `f32.nan`/`f64.nan`/`f32.inf`.
 """
 import json
 import os
@@ -39,9 +39,15 @@ FILES = [
     "tests/hist/min.fut",
     "tests/hist/segmented.fut",
     "tests/hist/hist2d.fut",
+    "tests/hist/max64.fut",
+    "tests/hist/f64.fut",
+    "tests/soacs/scan1.fut",
+    "tests/soacs/scan3.fut",
+    "tests/soacs/mapscan.fut",
+    "tests/soacs/scan-with-map.fut",
 ]
 
-TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f32\.nan|f32\.inf|-f32\.inf|true|false|"
+TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f(?:16|32|64)\.nan|f32\.inf|-f32\.inf|true|false|"
                    r"-?\d+\.\d*(?:[eE][-+]?\d+)?(?:f16|f32|f64)?|-?\d+(?:[eE][-+]?\d+)?(?:f16|f32|f64)|"
                    r"-?\d+(?:i8|i16|i32|i64|u8|u16|u32|u64)?|\[|\]|,)")
 
@@ -63,7 +69,7 @@ def parse_scalar(tok):
         return True
     if tok == "false":
         return False
-    if tok == "f32.nan":
+    if tok in ("f16.nan", "f32.nan", "f64.nan"):
         return "nan"
     if tok == "f32.inf":
         return "inf"

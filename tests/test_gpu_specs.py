@@ -63,6 +63,31 @@ def test_reference_vectors_histograms(ctx):
         assert got.tolist() == c["output"][0]
 
 
+def test_reference_vectors_more_types_and_index_spaces(ctx):
+    for c in GOLDEN["tests/hist/max64.fut"]:
+        n, is_, image = c["input"]
+        is_ = np.array(is_, np.int32)
+        assert fb.reduce_by_index(ctx, "max_i32", np.zeros(n, np.int32), is_, np.array(image, np.int32)).tolist() == c["output"][0]
+        got = fb.reduce_by_index(ctx, "max_u32", np.zeros(n, np.uint32), is_, np.array(image, np.int32).view(np.uint32))
+        assert got.view(np.int32).tolist() == c["output"][1]
+    for c in GOLDEN["tests/hist/f64.fut"]:
+        dest, is_, image = c["input"]
+        got = fb.reduce_by_index(ctx, "add_f64", np.array(_f(dest), np.float64), np.array(is_, np.int32), np.array(_f(image), np.float64))
+        assert np.allclose(got, np.array(_f(c["output"][0]), np.float64), rtol=1e-15, atol=0, equal_nan=True)
+    for c in GOLDEN["tests/soacs/mapscan.fut"]:
+        n, m = c["input"]
+        a = (np.arange(n, dtype=np.int64)[:, None] + np.arange(m, dtype=np.int64)[None, :]).astype(np.int32)
+        assert int(np.bitwise_xor.reduce(fb.segscan_rows_i32(ctx, a).reshape(-1))) == c["output"][0]
+    for c in GOLDEN["tests/soacs/scan-with-map.fut"]:
+        a, b, m = c["input"]
+        res = fb.scan_map2_add_i32(ctx, np.tile(np.array(b, np.int32), (m, 1)))
+        assert int(np.bitwise_xor.reduce(res.reshape(-1))) == c["output"][0]
+    c = GOLDEN["tests/soacs/scan1.fut"][0]
+    assert fb.scan_i32(ctx, np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+    i, a = GOLDEN["tests/soacs/scan3.fut"][0]["input"]
+    assert int(fb.scan_i32(ctx, np.array(a, np.int32))[i]) == GOLDEN["tests/soacs/scan3.fut"][0]["output"][1]
+
+
 # ---- against the oracle on seeded inputs ---------------------------------------------------------
 
 @pytest.mark.parametrize("n", SIZES + BIG)
@@ -139,6 +164,30 @@ def test_reduce_by_index_add_f32(ctx, B):
     wi = datagen.uniform_i32(79, 0, n, -8, 8).astype(np.float32)
     di = datagen.uniform_i32(80, 0, B, -8, 8).astype(np.float32)
     assert np.array_equal(fb.reduce_by_index(ctx, "add_f32", di, bins, wi), oracle.reduce_by_index("add_f32", di, bins, wi))
+
+
+@pytest.mark.parametrize("B", [1, 300, 100000])
+def test_reduce_by_index_add_f64(ctx, B):
+    n = 150001
+    bins = datagen.hist_bins(81, 0, n, B, "zipf")
+    ws = datagen.normal_f32(82, 0, n).astype(np.float64) * 1.000000123
+    dest = datagen.normal_f32(83, 0, B).astype(np.float64)
+    got = fb.reduce_by_index(ctx, "add_f64", dest, bins, ws)
+    ref = oracle.reduce_by_index_add_f64(dest, bins, ws)
+    ok = (bins >= 0) & (bins < B)
+    l1 = np.abs(dest)
+    np.add.at(l1, bins[ok], np.abs(ws[ok]))
+    assert (np.abs(got - ref) <= 1e-13 * np.maximum(l1, 1e-300)).all()      # the order of the atomics is free
+    wi = datagen.uniform_i32(84, 0, n, -1000, 1000).astype(np.float64)
+    assert np.array_equal(fb.reduce_by_index(ctx, "add_f64", dest * 0, bins, wi), oracle.reduce_by_index_add_f64(dest * 0, bins, wi))
+
+
+@pytest.mark.parametrize("m,k", [(1, 1), (1, 100), (100, 1), (100, 100), (100001, 3), (3, 100001), (777, 1025), (0, 5), (5, 0)])
+def test_scan_map2_add_i32(ctx, m, k):
+    xss = datagen.uniform_i32(85, 0, m * k, -2 ** 31, 2 ** 31 - 1).reshape(m, k)
+    got = fb.scan_map2_add_i32(ctx, xss)
+    assert got.shape == (m, k)
+    assert np.array_equal(got, oracle.scan_map2_add_i32(xss))
 
 
 @pytest.mark.parametrize("rows,cols,m", [(1, 1, 1), (3, 3, 10), (100, 1000, 17), (1000, 37, 300), (5, 100003, 70000), (0, 4, 3), (4, 0, 3)])

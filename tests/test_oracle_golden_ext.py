@@ -80,12 +80,57 @@ def test_reduce_by_index_2d(c):
     assert oracle.reduce_by_index_2d_add_i32(np.array(xss, np.int32), is_, js, vs).tolist() == c["output"][0]
 
 
+@pytest.mark.parametrize("c", cases("tests/hist/max64.fut"))
+def test_max64_signed_and_unsigned_max(c):
+    n, is_, image = c["input"]
+    assert oracle.reduce_by_index("max_i32", np.zeros(n, np.int32), is_, image).tolist() == c["output"][0]
+    got_u = oracle.reduce_by_index("max_u32", np.zeros(n, np.uint32), is_, np.array(image, np.int32).view(np.uint32))
+    assert got_u.view(np.int32).tolist() == c["output"][1]
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/f64.fut"))
+def test_reduce_by_index_add_f64_with_nan(c):
+    dest, is_, image = c["input"]
+    got = oracle.reduce_by_index_add_f64(np.array(_f(dest), np.float64), is_, np.array(_f(image), np.float64))
+    assert np.allclose(got, np.array(_f(c["output"][0]), np.float64), rtol=1e-15, atol=0, equal_nan=True)
+
+
+def mapscan_input(n, m):
+    """tests/soacs/mapscan.fut:8-12: a[i][j] = i32 (i + j)."""
+    return (np.arange(n, dtype=np.int64)[:, None] + np.arange(m, dtype=np.int64)[None, :]).astype(np.int32)
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/mapscan.fut"))
+def test_mapscan_row_scans_folded_with_xor(c):
+    n, m = c["input"]
+    b = oracle.segscan_rows_i32(mapscan_input(n, m))
+    assert int(np.bitwise_xor.reduce(b.reshape(-1))) == c["output"][0]
+
+
+@pytest.mark.parametrize("c", cases("tests/soacs/scan-with-map.fut"))
+def test_scan_with_an_operator_on_rows(c):
+    a, b, m = c["input"]
+    assert a == [0] * len(b)          # the neutral element of map2 (+)
+    res = oracle.scan_map2_add_i32(np.tile(np.array(b, np.int32), (m, 1)))
+    assert int(np.bitwise_xor.reduce(res.reshape(-1))) == c["output"][0]
+
+
+def test_scan1_and_scan3_prefix_sums():
+    c = cases("tests/soacs/scan1.fut")[0]
+    assert oracle.scan_i32(np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+    c = cases("tests/soacs/scan3.fut")[0]
+    i, a = c["input"]
+    a = np.array(a, np.int32)
+    assert [int(a[i] + 2), int(oracle.scan_i32(a)[i])] == c["output"]
+
+
 def test_definitions_without_reference_values():
     rng = np.random.default_rng(0)
     xs = rng.integers(-1000, 1000, 1000).astype(np.int32)
     assert np.array_equal(oracle.scan_max_i32(xs), np.maximum.accumulate(xs))
     xss = rng.integers(-1000, 1000, (37, 29)).astype(np.int32)
     assert np.array_equal(oracle.segscan_rows_i32(xss), np.cumsum(xss, axis=1, dtype=np.int32))
+    assert np.array_equal(oracle.scan_map2_add_i32(xss), np.cumsum(xss, axis=0, dtype=np.int32))
     is_ = rng.integers(-2, 12, 500).astype(np.int32)
     vs = rng.integers(-3, 4, 500).astype(np.int32)
     want = np.ones(10, np.int64)
