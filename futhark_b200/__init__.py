@@ -177,6 +177,9 @@ def load():
     L.futhark_entry_exscan_i32.argtypes = [vp, pvp, vp]
     L.futhark_entry_dotprod_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_float), vp, vp]
     L.futhark_entry_prod_of_sums_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp, vp]
+    L.futhark_entry_dotprod_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp, vp]
+    L.futhark_entry_product_i32.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+    L.futhark_entry_linrec_last_f32.argtypes = [vp, ctypes.POINTER(ctypes.c_float), vp, vp]
     for name in ("scan_max_i32", "segscan_rows_i32", "scan_map2_add_i32", "scanomap_steps_i32", "filter_pos_i32", "partition2_i32"):
         getattr(L, "futhark_entry_" + name).argtypes = [vp, pvp, vp]
     L.futhark_entry_filter_by_flag_i32.argtypes = [vp, pvp, vp, vp]
@@ -540,6 +543,21 @@ class Context:
         self._check(self.lib.futhark_entry_prod_of_sums_i32(self.ptr, ctypes.byref(out), xs.ptr, ys.ptr))
         return int(out.value)
 
+    def entry_dotprod_i32(self, xs, ys):
+        out = ctypes.c_int32()
+        self._check(self.lib.futhark_entry_dotprod_i32(self.ptr, ctypes.byref(out), xs.ptr, ys.ptr))
+        return int(out.value)
+
+    def entry_product_i32(self, xs):
+        out = ctypes.c_int32()
+        self._check(self.lib.futhark_entry_product_i32(self.ptr, ctypes.byref(out), xs.ptr))
+        return int(out.value)
+
+    def entry_linrec_last_f32(self, as_, bs):
+        out = ctypes.c_float()
+        self._check(self.lib.futhark_entry_linrec_last_f32(self.ptr, ctypes.byref(out), as_.ptr, bs.ptr))
+        return float(out.value)
+
     def entry_sum_i32_f32(self, xs):
         """The opaque (i32, f32) result, projected and freed: returns the two scalars."""
         obj = ctypes.c_void_p()
@@ -621,6 +639,18 @@ def dotprod_f32(ctx, xs, ys):
 
 def prod_of_sums_i32(ctx, xs, ys):
     return _scalar2(ctx, "i32_1d", xs, ys, ctx.entry_prod_of_sums_i32)
+
+
+def dotprod_i32(ctx, xs, ys):
+    return _scalar2(ctx, "i32_1d", xs, ys, ctx.entry_dotprod_i32)
+
+
+def product_i32(ctx, xs):
+    return _scalar(ctx, xs, ctx.entry_product_i32)
+
+
+def linrec_last_f32(ctx, as_, bs):
+    return _scalar2(ctx, "f32_1d", as_, bs, ctx.entry_linrec_last_f32)
 
 
 def segscan_f32(ctx, flags, xs):

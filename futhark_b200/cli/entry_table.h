@@ -236,6 +236,9 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"sum_i32_f32", {"[]i32"}, "(i32, f32)", [](C *c, In in, Value &o) { futhark_opaque_tup2_i32_f32 *r = nullptr; int rc = futhark_entry_sum_i32_f32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "(i32, f32)", r); return rc; }},
       {"dotprod_f32", {"[]f32", "[]f32"}, "f32", [](C *c, In in, Value &o) { float r = 0; int rc = futhark_entry_dotprod_f32(c, &r, FE_IN(0, f32_1d), FE_IN(1, f32_1d)); if (!rc) set_scalar(o, "f32", r); return rc; }},
       {"prod_of_sums_i32", {"[]i32", "[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_prod_of_sums_i32(c, &r, FE_IN(0, i32_1d), FE_IN(1, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
+      {"dotprod_i32", {"[]i32", "[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_dotprod_i32(c, &r, FE_IN(0, i32_1d), FE_IN(1, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
+      {"product_i32", {"[]i32"}, "i32", [](C *c, In in, Value &o) { int32_t r = 0; int rc = futhark_entry_product_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_scalar(o, "i32", r); return rc; }},
+      {"linrec_last_f32", {"[]f32", "[]f32"}, "f32", [](C *c, In in, Value &o) { float r = 0; int rc = futhark_entry_linrec_last_f32(c, &r, FE_IN(0, f32_1d), FE_IN(1, f32_1d)); if (!rc) set_scalar(o, "f32", r); return rc; }},
       {"segscan_f32", {"[]bool", "[]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_segscan_f32(c, &r, FE_IN(0, bool_1d), FE_IN(1, f32_1d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
       {"segreduce_f32", {"[]i64", "[]bool", "[]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_segreduce_f32(c, &r, FE_IN(0, i64_1d), FE_IN(1, bool_1d), FE_IN(2, f32_1d)); if (!rc) set_array(o, "[]f32", r); return rc; }},
       {"rowsum_f32", {"[][]f32"}, "[]f32", [](C *c, In in, Value &o) { futhark_f32_1d *r = nullptr; int rc = futhark_entry_rowsum_f32(c, &r, FE_IN(0, f32_2d)); if (!rc) set_array(o, "[]f32", r); return rc; }},

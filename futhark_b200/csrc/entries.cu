@@ -183,6 +183,46 @@ int futhark_entry_prod_of_sums_i32(struct futhark_context *ctx, int32_t *out0, c
   return FUTHARK_SUCCESS;
 }
 
+// reduce (+) 0 (map2 (*) xs ys) over i32 (tests/soacs/reduce2.fut) and reduce (*) 1 xs (tests/soacs/reduce1.fut)
+int futhark_entry_dotprod_i32(struct futhark_context *ctx, int32_t *out0, const struct futhark_i32_1d *in0, const struct futhark_i32_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  if (in1->shape[0] != n) return bad_sizes(ctx);
+  int rc = scalar_redomap(ctx, "dotprod_i32.segred_nonseg", PROV("reduce (+) 0 (map2 (*) xs ys)"), n, 4, [&] {
+    return fb::launch_dotprod_i32(dptr<int32_t>(in0->mem), dptr<int32_t>(in1->mem), n, reinterpret_cast<int32_t *>(ctx->d_scalar), ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+  });
+  if (rc) return rc;
+  *out0 = reinterpret_cast<int32_t *>(ctx->h_scalar)[0];
+  return FUTHARK_SUCCESS;
+}
+int futhark_entry_product_i32(struct futhark_context *ctx, int32_t *out0, const struct futhark_i32_1d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  int rc = scalar_redomap(ctx, "product_i32.segred_nonseg", PROV("reduce (*) 1 xs"), n, 4, [&] {
+    return fb::launch_product_i32(dptr<int32_t>(in0->mem), n, reinterpret_cast<int32_t *>(ctx->d_scalar), ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+  });
+  if (rc) return rc;
+  *out0 = reinterpret_cast<int32_t *>(ctx->h_scalar)[0];
+  return FUTHARK_SUCCESS;
+}
+
+// (reduce (\(a1,b1) (a2,b2) -> (a1*a2, b1*a2+b2)) (1,0) (zip as bs)).1: a non-commutative operator on pairs
+// over two inputs; the last value of the recurrence that linrec_f32 scans.
+int futhark_entry_linrec_last_f32(struct futhark_context *ctx, float *out0, const struct futhark_f32_1d *in0, const struct futhark_f32_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  if (in1->shape[0] != n) return bad_sizes(ctx);
+  int rc = scalar_redomap(ctx, "linrec_last_f32.segred_nonseg", PROV("(reduce compose (1,0) (zip as bs)).1"), n, 8, [&] {
+    return fb::launch_affine_f32(dptr<float>(in0->mem), dptr<float>(in1->mem), n, reinterpret_cast<float *>(ctx->d_scalar), ctx->reduce_scratch, ctx->num_sms, ctx->stream);
+  });
+  if (rc) return rc;
+  *out0 = reinterpret_cast<float *>(ctx->h_scalar)[1];
+  return FUTHARK_SUCCESS;
+}
+
 // The caller holds the context's lock.  shard_out (device, 4 words, or NULL): see launch_segscan_f32.
 int segscan_f32_locked(futhark_context *ctx, struct futhark_f32_1d **out0, const struct futhark_bool_1d *in0,
                        const struct futhark_f32_1d *in1, uint32_t *shard_out, const fb::PeerPush *peer) {

@@ -92,6 +92,10 @@ cudaError_t launch_sum_i32_f32(const int32_t *in, int64_t n, void *d_out2, void 
 // map2 bodies: the f32 dot product, and the product of the element-wise sums of two i32 arrays
 cudaError_t launch_dotprod_f32(const float *xs, const float *ys, int64_t n, float *d_out, void *scratch, int num_sms, cudaStream_t stream);
 cudaError_t launch_prod_of_sums_i32(const int32_t *xs, const int32_t *ys, int64_t n, int32_t *d_out, void *scratch, int num_sms, cudaStream_t stream);
+cudaError_t launch_dotprod_i32(const int32_t *xs, const int32_t *ys, int64_t n, int32_t *d_out, void *scratch, int num_sms, cudaStream_t stream);
+cudaError_t launch_product_i32(const int32_t *xs, int64_t n, int32_t *d_out, void *scratch, int num_sms, cudaStream_t stream);
+// d_out2: the pair (a, b) of the composed affine map
+cudaError_t launch_affine_f32(const float *as, const float *bs, int64_t n, float *d_out2, void *scratch, int num_sms, cudaStream_t stream);
 
 // ---- histograms (k_hist.cu) -------------------------------------------------------------
 // out[b] = fold of the weights whose index is b, over 32-bit values; `out` holds B 4-byte bins.

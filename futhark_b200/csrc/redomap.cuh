@@ -15,10 +15,10 @@
 //   static Acc combine(Acc l, Acc r)   l (+) r, associative
 //
 // Operand order.  Every warp owns a contiguous run of *steps* (a step = 32 * K vectors of
-// 16 bytes per input, read coalesced; K = RM_K, or 2 with two inputs to bound the registers).
+// 16 bytes per input, read coalesced; K = RM_K, or 2 or 3 with two inputs to bound the registers).
 // A commutative specification folds each lane's vectors as they come.  Otherwise a step goes through a warp-private shared-memory area that turns the
-// coalesced layout into a blocked one (lane l then holds vectors l*RM_K .. l*RM_K+RM_K-1; RM_K
-// is odd, which makes these 16-byte reads conflict-free), the lane folds its 4*RM_K consecutive
+// coalesced layout into a blocked one (lane l then holds vectors l*K .. l*K+K-1 of each input; K
+// is odd, which makes these 16-byte reads conflict-free), the lane folds its 4*K consecutive
 // elements left to right and a shuffle tree that keeps lane order folds the 32 lanes.  Warp,
 // CTA and grid partials are folded in index order as well.
 #pragma once
@@ -33,6 +33,9 @@ constexpr int RM_THREADS = 256;
 constexpr int RM_WARPS = RM_THREADS / 32;
 constexpr int RM_K = 5;
 constexpr int RM_MAX_BLOCKS = 4096;
+// vectors per lane, input and step: 2 with two inputs to bound the registers, 3 when their operand
+// order matters as well (odd: the blocked 16-byte reads of the transposition are conflict-free)
+template <class Spec> struct RedomapK { static constexpr int K = Spec::NIN == 2 ? (Spec::commutative ? 2 : 3) : RM_K; };
 
 template <class Acc>
 __device__ __forceinline__ Acc shfl_down_acc(const Acc &a, int d) {
@@ -93,9 +96,9 @@ redomap_kernel(const uint32_t *__restrict__ in, const uint32_t *__restrict__ in2
   using Vec = typename std::conditional<VEC, int4, uint32_t>::type;
   constexpr bool ORDERED = !Spec::commutative;
   constexpr int NIN = Spec::NIN;
-  static_assert(NIN == 1 || (NIN == 2 && !ORDERED), "two inputs are supported for commutative operators");
-  constexpr int K = NIN == 2 ? 2 : RM_K;
-  __shared__ Vec s_tr[ORDERED ? RM_WARPS * 32 * K : 1];
+  static_assert(NIN == 1 || NIN == 2, "one or two input arrays");
+  constexpr int K = RedomapK<Spec>::K;
+  __shared__ Vec s_tr[ORDERED ? RM_WARPS * 32 * K * NIN : 1];
   __shared__ Acc s_warp[RM_WARPS];
   __shared__ uint32_t s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -131,14 +134,20 @@ redomap_kernel(const uint32_t *__restrict__ in, const uint32_t *__restrict__ in2
     const int64_t base = s * STEP;
     if (base + STEP <= nvec) {
       if constexpr (ORDERED) {
-        Vec *mine = s_tr + warp * (32 * K);
+        Vec *mine = s_tr + warp * (32 * K * NIN);
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < K; j++) mine[j * 32 + lane] = cur[0][j];
+        for (int j = 0; j < K; j++) {
+          mine[j * 32 + lane] = cur[0][j];
+          if constexpr (NIN == 2) mine[32 * K + j * 32 + lane] = cur[1][j];
+        }
         __syncwarp();
         Acc a = Spec::neutral();
 #pragma unroll
-        for (int j = 0; j < K; j++) a = fold_vec<Spec>(a, mine[lane * K + j]);
+        for (int j = 0; j < K; j++) {
+          if constexpr (NIN == 2) a = fold_vec<Spec>(a, mine[lane * K + j], mine[32 * K + lane * K + j]);
+          else a = fold_vec<Spec>(a, mine[lane * K + j]);
+        }
         a = warp_fold_ordered<Spec>(a, lane);
         acc = Spec::combine(acc, a);
       } else {
@@ -220,7 +229,7 @@ redomap_kernel(const uint32_t *__restrict__ in, const uint32_t *__restrict__ in2
 template <class Spec>
 cudaError_t launch_redomap(const void *in, const void *in2, int64_t n, void *d_out, void *scratch, int num_sms, cudaStream_t stream) {
   using Acc = typename Spec::Acc;
-  constexpr int K = Spec::NIN == 2 ? 2 : RM_K;
+  constexpr int K = RedomapK<Spec>::K;
   uint32_t *ticket = reinterpret_cast<uint32_t *>(scratch);
   Acc *partials = reinterpret_cast<Acc *>(reinterpret_cast<char *>(scratch) + 256);
   const bool vec = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(in2)) & 15) == 0;

@@ -71,6 +71,9 @@ ENTRIES = {
     "sum_i32_f32": ([("xs", "[]i32")], "(i32, f32)", []),
     "dotprod_f32": ([("xs", "[]f32"), ("ys", "[]f32")], "f32", []),
     "prod_of_sums_i32": ([("xs", "[]i32"), ("ys", "[]i32")], "i32", []),
+    "dotprod_i32": ([("xs", "[]i32"), ("ys", "[]i32")], "i32", []),
+    "product_i32": ([("xs", "[]i32")], "i32", []),
+    "linrec_last_f32": ([("as", "[]f32"), ("bs", "[]f32")], "f32", []),
 }
 
 

@@ -405,6 +405,11 @@ int futhark_entry_linrec_f32(struct futhark_context *ctx, struct futhark_f32_1d 
  *   inputs fused into the reduction (the shape of every dot product in the programs under tests/tiling).
  * entry prod_of_sums_i32 (xs: []i32) (ys: []i32): i32 = reduce (*) 1 (map2 (+) xs ys), the DotProd
  *   functor of tests/modules/functor1.fut:30-33 applied to i32 (known answer :3-4).
+ * entry dotprod_i32 (xs: []i32) (ys: []i32): i32 = reduce (+) 0 (map2 (*) xs ys)   (tests/soacs/reduce2.fut)
+ * entry product_i32 (xs: []i32): i32 = reduce (*) 1 xs                             (tests/soacs/reduce1.fut)
+ * entry linrec_last_f32 (as: []f32) (bs: []f32): f32 =
+ *   (reduce (\(a1,b1) (a2,b2) -> (a1*a2, b1*a2+b2)) (1,0) (zip as bs)).1: a non-commutative operator on
+ *   pairs over two inputs (operand order kept as in SegRed.hs:836-921); equals last (linrec_f32 as bs).
  * Those with scalar results read them back, so they synchronise. */
 int futhark_entry_exscan_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
                              const struct futhark_i32_1d *in0);
@@ -416,6 +421,12 @@ int futhark_entry_dotprod_f32(struct futhark_context *ctx, float *out0,
                               const struct futhark_f32_1d *in0, const struct futhark_f32_1d *in1);
 int futhark_entry_prod_of_sums_i32(struct futhark_context *ctx, int32_t *out0,
                                    const struct futhark_i32_1d *in0, const struct futhark_i32_1d *in1);
+int futhark_entry_dotprod_i32(struct futhark_context *ctx, int32_t *out0,
+                              const struct futhark_i32_1d *in0, const struct futhark_i32_1d *in1);
+int futhark_entry_product_i32(struct futhark_context *ctx, int32_t *out0,
+                              const struct futhark_i32_1d *in0);
+int futhark_entry_linrec_last_f32(struct futhark_context *ctx, float *out0,
+                                  const struct futhark_f32_1d *in0, const struct futhark_f32_1d *in1);
 
 /* ---- extensions (prefix futhark_b200_): not part of the reference's generated API ----
  * The reference keeps its one CUDA stream private (rts/c/backends/cuda.h:219); a host

@@ -53,6 +53,12 @@ def lib():
         L.orc_scan_max_i32.argtypes = [vp, i64, vp]
         L.orc_segscan_rows_i32.argtypes = [vp, i64, i64, vp]
         L.orc_scan_map2_add_i32.argtypes = [vp, i64, i64, vp]
+        L.orc_dotprod_i32.restype = ctypes.c_int32
+        L.orc_dotprod_i32.argtypes = [vp, vp, i64]
+        L.orc_product_i32.restype = ctypes.c_int32
+        L.orc_product_i32.argtypes = [vp, i64]
+        L.orc_linrec_last_f32.restype = ctypes.c_float
+        L.orc_linrec_last_f32.argtypes = [vp, vp, i64]
         L.orc_reduce_by_index_add_f64.argtypes = [vp, i64, vp, vp, i64]
         L.orc_scanomap_steps_i32.argtypes = [vp, i64, vp]
         L.orc_filter_pos_i32.restype = i64
@@ -381,6 +387,23 @@ def segscan_rows_i32(xss):
     out = np.empty_like(xss)
     lib().orc_segscan_rows_i32(_p(xss), xss.shape[0], xss.shape[1], _p(out))
     return out
+
+
+def dotprod_i32(xs, ys):
+    xs, ys = _c(xs, np.int32), _c(ys, np.int32)
+    assert xs.size == ys.size
+    return int(lib().orc_dotprod_i32(_p(xs), _p(ys), xs.size))
+
+
+def product_i32(xs):
+    xs = _c(xs, np.int32)
+    return int(lib().orc_product_i32(_p(xs), xs.size))
+
+
+def linrec_last_f32(as_, bs):
+    as_, bs = _c(as_, np.float32), _c(bs, np.float32)
+    assert as_.size == bs.size
+    return float(lib().orc_linrec_last_f32(_p(as_), _p(bs), as_.size))
 
 
 def scan_map2_add_i32(xss):

@@ -49,6 +49,26 @@ void orc_reduce_by_index_add_f64(double *dest, int64_t n, const int32_t *is, con
     if (is[i] >= 0 && (int64_t)is[i] < n) dest[is[i]] = dest[is[i]] + vs[i];
 }
 
+/* reduce (+) 0 (map2 (*) a b) (tests/soacs/reduce2.fut:11-12) and reduce (*) 1 a (tests/soacs/reduce1.fut:8):
+ * mul32 and add32 wrap (rts/c/scalar.h:29-60) */
+int32_t orc_dotprod_i32(const int32_t *xs, const int32_t *ys, int64_t n) {
+  uint32_t acc = 0;
+  for (int64_t i = 0; i < n; i++) acc += (uint32_t)xs[i] * (uint32_t)ys[i];
+  return (int32_t)acc;
+}
+int32_t orc_product_i32(const int32_t *xs, int64_t n) {
+  uint32_t acc = 1;
+  for (int64_t i = 0; i < n; i++) acc *= (uint32_t)xs[i];
+  return (int32_t)acc;
+}
+
+/* (reduce (\(a1,b1) (a2,b2) -> (a1*a2, b1*a2+b2)) (1,0) (zip as bs)).1, folded from the left */
+float orc_linrec_last_f32(const float *as, const float *bs, int64_t n) {
+  float a = 1.0f, b = 0.0f;
+  for (int64_t i = 0; i < n; i++) { b = b * as[i] + bs[i]; a = a * as[i]; }
+  return b;
+}
+
 /* tests/soacs/scan4.fut:11-22, statement by statement */
 static void scan4_step(const int32_t *xs, int64_t n, int32_t *out) {
   int32_t bits_sum = 0;

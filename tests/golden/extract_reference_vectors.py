@@ -45,6 +45,8 @@ FILES = [
     "tests/soacs/scan3.fut",
     "tests/soacs/mapscan.fut",
     "tests/soacs/scan-with-map.fut",
+    "tests/soacs/reduce1.fut",
+    "tests/soacs/reduce2.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f(?:16|32|64)\.nan|f32\.inf|-f32\.inf|true|false|"

@@ -113,6 +113,36 @@ def test_prod_of_sums_i32_bit_exact(ctx, n):
     assert fb.prod_of_sums_i32(ctx, xs, ys) == oracle.prod_of_sums_i32(xs, ys)
 
 
+def test_reduce1_and_reduce2_reference_known_answers(ctx):
+    # tests/soacs/reduce1.fut:2-7 and reduce2.fut:2-9 of the reference
+    nine = np.arange(1, 10, dtype=np.int32)
+    assert fb.product_i32(ctx, nine) == 362880
+    assert fb.dotprod_i32(ctx, nine, nine) == 285
+    assert fb.product_i32(ctx, nine[:0]) == 1 and fb.dotprod_i32(ctx, nine[:0], nine[:0]) == 0
+
+
+@pytest.mark.parametrize("n", SIZES + MORE)
+def test_dotprod_and_product_i32_bit_exact(ctx, n):
+    xs = datagen.uniform_i32(21, 0, n, -2**31, 2**31 - 1)
+    ys = datagen.uniform_i32(22, 0, n, -2**31, 2**31 - 1)
+    assert fb.dotprod_i32(ctx, xs, ys) == oracle.dotprod_i32(xs, ys)
+    assert fb.product_i32(ctx, xs | 1) == oracle.product_i32(xs | 1)       # odd factors: the product never collapses to 0
+
+
+@pytest.mark.parametrize("n", SIZES + MORE)
+def test_linrec_last_f32_two_inputs_non_commutative(ctx, n):
+    # factors in {-1, 0, 1} and small integer terms: every value is exact in f32, so operand ORDER is all that can go wrong
+    as_ = datagen.uniform_i32(23, 0, n, -1, 1).astype(np.float32)
+    as_[datagen.uniform_i32(24, 0, n, 0, 15) != 0] = 1.0                    # a zero now and then, not everywhere
+    bs = datagen.uniform_i32(25, 0, n, -3, 3).astype(np.float32)
+    assert fb.linrec_last_f32(ctx, as_, bs) == oracle.linrec_last_f32(as_, bs)
+    # real factors: within 1e-5 of the scale of the terms
+    ar = (0.5 + 0.4 * np.tanh(datagen.normal_f32(26, 0, n))).astype(np.float32)
+    br = datagen.normal_f32(27, 0, n)
+    got, want = fb.linrec_last_f32(ctx, ar, br), oracle.linrec_last_f32(ar, br)
+    assert abs(got - want) <= 1e-5 * 10.0 * max(1.0, float(np.abs(br[-64:]).max()) if n else 1.0)
+
+
 @pytest.mark.parametrize("n", SIZES + MORE)
 def test_dotprod_f32(ctx, n):
     xs, ys = datagen.normal_f32(17, 0, n), datagen.normal_f32(18, 0, n)

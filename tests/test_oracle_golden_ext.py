@@ -124,6 +124,21 @@ def test_scan1_and_scan3_prefix_sums():
     assert [int(a[i] + 2), int(oracle.scan_i32(a)[i])] == c["output"]
 
 
+def test_reduce1_product_and_reduce2_dot_product():
+    c = cases("tests/soacs/reduce1.fut")[0]
+    assert oracle.product_i32(np.array(c["input"][0], np.int32)) == c["output"][0]
+    c = cases("tests/soacs/reduce2.fut")[0]
+    assert oracle.dotprod_i32(np.array(c["input"][0], np.int32), np.array(c["input"][1], np.int32)) == c["output"][0]
+
+
+def test_linrec_last_is_the_last_of_the_scan():
+    rng = np.random.default_rng(3)
+    as_ = rng.integers(-1, 2, 5000).astype(np.float32)
+    bs = rng.integers(-3, 4, 5000).astype(np.float32)
+    assert oracle.linrec_last_f32(as_, bs) == float(oracle.linrec_f32(as_, bs)[-1])
+    assert oracle.linrec_last_f32(as_[:0], bs[:0]) == 0.0
+
+
 def test_definitions_without_reference_values():
     rng = np.random.default_rng(0)
     xs = rng.integers(-1000, 1000, 1000).astype(np.int32)
