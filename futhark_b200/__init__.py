@@ -32,6 +32,9 @@ ARRAY_TYPES = {
     "bool_2d": (np.bool_, 2, ctypes.c_bool),
     "i64_2d": (np.int64, 2, ctypes.c_int64),
     "f64_1d": (np.float64, 1, ctypes.c_double),
+    "i8_1d": (np.int8, 1, ctypes.c_int8),
+    "i16_1d": (np.int16, 1, ctypes.c_int16),
+    "f16_1d": (np.uint16, 1, ctypes.c_uint16),
     "f32_3d": (np.float32, 3, ctypes.c_float),
     "f16_3d": (np.uint16, 3, ctypes.c_uint16),
 }
@@ -192,6 +195,8 @@ def load():
     for name in ("and_i32", "or_i32", "xor_i32", "mul_i32"):
         getattr(L, "futhark_entry_hist_" + name).argtypes = [vp, pvp, i64, vp, vp]
     for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32", "add_f64"):
+        getattr(L, "futhark_entry_reduce_by_index_" + name).argtypes = [vp, pvp, vp, vp, vp]
+    for name in ("add_i8", "add_i16", "add_f16"):
         getattr(L, "futhark_entry_reduce_by_index_" + name).argtypes = [vp, pvp, vp, vp, vp]
     L.futhark_entry_hist_rows_add_i32.argtypes = [vp, pvp, i64, vp, vp]
     L.futhark_entry_reduce_by_index_2d_add_i32.argtypes = [vp, pvp, vp, vp, vp, vp]
@@ -442,6 +447,10 @@ class Context:
     def entry_reduce_by_index(self, op, dest, bins, ws):
         """reduce_by_index dest <op> <neutral> (map i64.i32 bins) ws for op in min_i32, max_i32, min_u32, max_u32, add_f32, add_f64."""
         return self._entry_arr("reduce_by_index_" + op, op[-3:] + "_1d", dest.ptr, bins.ptr, ws.ptr)
+
+    def entry_reduce_by_index_subword(self, t, dest, bins, ws):
+        """reduce_by_index dest (+) 0 (map i64.iN bins) ws for t in i8, i16 (indices of the same type) and f16 (i16 indices)."""
+        return self._entry_arr("reduce_by_index_add_" + t, t + "_1d", dest.ptr, bins.ptr, ws.ptr)
 
     def entry_hist_rows_add_i32(self, m, iss, vss):
         return self._entry_arr("hist_rows_add_i32", "i32_2d", int(m), iss.ptr, vss.ptr)
@@ -751,6 +760,12 @@ def hist_op(ctx, op, B, bins, ws):
 def reduce_by_index(ctx, op, dest, bins, ws):
     t = op[-3:] + "_1d"
     return _run(ctx, [(t, dest), ("i32_1d", bins), (t, ws)], lambda d, b, w: ctx.entry_reduce_by_index(op, d, b, w))
+
+
+def reduce_by_index_subword(ctx, t, dest, bins, ws):
+    """t: "i8", "i16" or "f16" (binary16 bit patterns as uint16; the indices are i16)."""
+    it = "i8_1d" if t == "i8" else "i16_1d"
+    return _run(ctx, [(t + "_1d", dest), (it, bins), (t + "_1d", ws)], lambda d, b, w: ctx.entry_reduce_by_index_subword(t, d, b, w))
 
 
 def hist_rows_add_i32(ctx, m, iss, vss):

@@ -394,6 +394,34 @@ int futhark_entry_reduce_by_index_add_f64(struct futhark_context *ctx, struct fu
   return FUTHARK_SUCCESS;
 }
 
+// reduce_by_index dest (+) 0 (map i64.iN is) vs over i8, i16 and f16 (tests/hist/i8.fut, i16.fut, f16.fut): element
+// types without an atomic of their own take a compare-and-swap loop on the containing word (Base.hs:844-905)
+#define FB_RBI_SUBWORD_ENTRY(NAME, KIND, ARR, IARR, ES)                                                                        \
+  int futhark_entry_reduce_by_index_add_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0,                      \
+                                               const struct futhark_##ARR *in0, const struct futhark_##IARR *in1,              \
+                                               const struct futhark_##ARR *in2) {                                             \
+    if (!ctx->ready) return not_ready(ctx);                                                                                   \
+    CtxGuard g(ctx);                                                                                                          \
+    const int64_t B = in0->shape[0], n = in1->shape[0];                                                                       \
+    if (in2->shape[0] != n) return bad_sizes(ctx);                                                                            \
+    int rc;                                                                                                                   \
+    futhark_##ARR *out = make_1d<futhark_##ARR>(ctx, B, ES, "reduce_by_index_add_" #NAME ".out", &rc);                        \
+    if (out == nullptr) return rc;                                                                                            \
+    if (B > 0) {                                                                                                              \
+      LaunchScope ls(ctx, "reduce_by_index_add_" #NAME ".seghist", PROV("reduce_by_index dest (+) 0 is vs"),                  \
+                     "{" + kv("n", n) + "," + kv("bins", B) + "}");                                                           \
+      rc = fb_cuda_check(ctx, fb::launch_hist_add_subword(KIND, B, dptr<void>(in1->mem), dptr<void>(in2->mem), n, dptr<void>(out->mem), \
+                                                          dptr<void>(in0->mem), ctx->num_sms, ctx->stream),                   \
+                         "reduce_by_index_add_" #NAME);                                                                       \
+      if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }                                                        \
+    }                                                                                                                         \
+    *out0 = out;                                                                                                              \
+    return FUTHARK_SUCCESS;                                                                                                   \
+  }
+FB_RBI_SUBWORD_ENTRY(i8, 0, i8_1d, i8_1d, 1)
+FB_RBI_SUBWORD_ENTRY(i16, 1, i16_1d, i16_1d, 2)
+FB_RBI_SUBWORD_ENTRY(f16, 2, f16_1d, i16_1d, 2)
+
 // map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss (tests/hist/segmented.fut: a SegHist with a
 // segment dimension, SegHist.hs:97-148): one histogram over rows * m bins whose index carries the row.
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const int64_t in0,

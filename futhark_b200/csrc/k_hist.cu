@@ -31,6 +31,8 @@
 //                 and are accumulated on chip; their updates would otherwise queue up on
 //                 single L2 addresses.  A CTA that sees few hits (uniform indices over many
 //                 more bins than slots) stops looking into the cache.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -512,6 +514,77 @@ cudaError_t launch_hist_add_f64(int64_t B, const int32_t *bins, const double *vs
   if (grid > (int64_t)num_sms * 8) grid = (int64_t)num_sms * 8;
   hist_global_add_f64_kernel<<<(int)grid, 256, 0, stream>>>(bins, vs, n, B, out);
   return cudaGetLastError();
+}
+
+// ---- 1- and 2-byte values: compare-and-swap on the 32-bit word that holds the element ---------------
+// What the reference generates for element types without an atomic of their own (Base.hs:844-905): read
+// the word, combine inside it, try to swap it in, repeat while somebody else got there first.
+struct SwAddI8 {
+  using V = uint8_t; using I = int8_t;
+  static __device__ __forceinline__ uint32_t combine(uint32_t cur, uint32_t v) { return (cur + v) & 0xffu; }
+};
+struct SwAddI16 {
+  using V = uint16_t; using I = int16_t;
+  static __device__ __forceinline__ uint32_t combine(uint32_t cur, uint32_t v) { return (cur + v) & 0xffffu; }
+};
+// f32 -> binary16 bits by truncation (round toward zero), NaN payloads cut to their top ten bits: the
+// arithmetic of the reference's table-driven float2halfbits (rts/c/half.h:220-228)
+__device__ __forceinline__ uint32_t float_to_half_trunc(float f) {
+  const uint32_t bits = __float_as_uint(f), sign = (bits >> 16) & 0x8000u, e = (bits >> 23) & 0xffu, m = bits & 0x7fffffu;
+  if (e == 255u) return sign | 0x7c00u | (m >> 13);
+  if (e > 142u) return sign | 0x7c00u;                               // 2^16 and beyond: infinity
+  if (e >= 113u) return sign | ((e - 112u) << 10) | (m >> 13);      // normal numbers
+  if (e >= 103u) return sign | ((0x0400u >> (113u - e)) + (m >> (126u - e)));   // subnormal numbers
+  return sign;
+}
+struct SwAddF16 {
+  using V = uint16_t; using I = int16_t;
+  static __device__ __forceinline__ uint32_t combine(uint32_t cur, uint32_t v) {
+    const float s = __half2float(__ushort_as_half((unsigned short)cur)) + __half2float(__ushort_as_half((unsigned short)v));
+    return float_to_half_trunc(s);
+  }
+};
+template <class S>
+__global__ void __launch_bounds__(256) hist_global_cas_kernel(const typename S::I *__restrict__ bins, const typename S::V *__restrict__ vs,
+                                                             int64_t n, int64_t B, typename S::V *out) {
+  using V = typename S::V;
+  constexpr uint32_t BITS = 8 * sizeof(V), MASK = (1u << BITS) - 1u;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int64_t b = (int64_t)bins[i];                             // sign-extended, as i64.i8 / i64.i16
+    if (b < 0 || b >= B) continue;
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(out + b);
+    uint32_t *word = reinterpret_cast<uint32_t *>(addr & ~(uintptr_t)3);
+    const uint32_t shift = (uint32_t)(addr & 3u) * 8u;
+    const uint32_t v = (uint32_t)vs[i];
+    uint32_t old = *reinterpret_cast<volatile uint32_t *>(word), assumed;
+    do {
+      assumed = old;
+      const uint32_t nv = S::combine((assumed >> shift) & MASK, v);
+      old = atomicCAS(word, assumed, (assumed & ~(MASK << shift)) | (nv << shift));
+    } while (old != assumed);
+  }
+}
+template <class S>
+static cudaError_t launch_hist_cas(int64_t B, const void *bins, const void *vs, int64_t n, void *out, const void *dest, int num_sms, cudaStream_t stream) {
+  using V = typename S::V;
+  if (B <= 0) return cudaSuccess;
+  cudaError_t err = cudaMemcpyAsync(out, dest, (size_t)B * sizeof(V), cudaMemcpyDeviceToDevice, stream);
+  if (err != cudaSuccess || n <= 0) return err;
+  int64_t grid = (n + 255) / 256;
+  if (grid > (int64_t)num_sms * 8) grid = (int64_t)num_sms * 8;
+  hist_global_cas_kernel<S><<<(int)grid, 256, 0, stream>>>(reinterpret_cast<const typename S::I *>(bins), reinterpret_cast<const V *>(vs), n, B,
+                                                          reinterpret_cast<V *>(out));
+  return cudaGetLastError();
+}
+// `out` must be readable and writable up to the next multiple of 4 bytes (pooled blocks are)
+cudaError_t launch_hist_add_subword(int kind, int64_t B, const void *bins, const void *vs, int64_t n, void *out, const void *dest, int num_sms,
+                                    cudaStream_t stream) {
+  switch (kind) {
+    case 0: return launch_hist_cas<SwAddI8>(B, bins, vs, n, out, dest, num_sms, stream);
+    case 1: return launch_hist_cas<SwAddI16>(B, bins, vs, n, out, dest, num_sms, stream);
+    default: return launch_hist_cas<SwAddF16>(B, bins, vs, n, out, dest, num_sms, stream);
+  }
 }
 
 }  // namespace fb

@@ -110,6 +110,10 @@ cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weig
 // reduce_by_index dest (+) 0 is vs over f64: atomics on the result in global memory
 cudaError_t launch_hist_add_f64(int64_t B, const int32_t *bins, const double *vs, int64_t n, double *out, const double *dest, int num_sms,
                                 cudaStream_t stream);
+// reduce_by_index dest (+) 0 is vs over 1- and 2-byte values (kind 0: i8 with i8 indices, 1: i16 with i16 indices,
+// 2: f16 with i16 indices): a compare-and-swap loop on the containing 32-bit word
+cudaError_t launch_hist_add_subword(int kind, int64_t B, const void *bins, const void *vs, int64_t n, void *out, const void *dest, int num_sms,
+                                    cudaStream_t stream);
 // flat[i] = (i / cols) * B + is[i], or -1 if is[i] is outside [0, B): a histogram per row
 cudaError_t launch_flatten_rows_index(const int32_t *is, int64_t n, int64_t cols, int64_t B, int32_t *flat, int num_sms, cudaStream_t stream);
 // flat[i] = is[i] * M + js[i], or -1 if either index is out of range: reduce_by_index_2d

@@ -624,6 +624,9 @@ FB_ARRAY_2D(i32_2d, int32_t)
 FB_ARRAY_2D(bool_2d, bool)
 FB_ARRAY_2D(i64_2d, int64_t)
 FB_ARRAY_1D(f64_1d, double)
+FB_ARRAY_1D(i8_1d, int8_t)
+FB_ARRAY_1D(i16_1d, int16_t)
+FB_ARRAY_1D(f16_1d, uint16_t)
 FB_ARRAY_3D(f32_3d, float)
 FB_ARRAY_3D(f16_3d, uint16_t)
 

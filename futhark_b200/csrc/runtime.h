@@ -143,6 +143,9 @@ FB_DEFINE_ARRAY_STRUCT(i32_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(bool_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(i64_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(f64_1d, 1)
+FB_DEFINE_ARRAY_STRUCT(i8_1d, 1)
+FB_DEFINE_ARRAY_STRUCT(i16_1d, 1)
+FB_DEFINE_ARRAY_STRUCT(f16_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_3d, 3)
 FB_DEFINE_ARRAY_STRUCT(f16_3d, 3)
 

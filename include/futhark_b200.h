@@ -138,6 +138,9 @@ FUTHARK_B200_ARRAY_2D(i32_2d, int32_t)
 FUTHARK_B200_ARRAY_2D(bool_2d, bool)
 FUTHARK_B200_ARRAY_2D(i64_2d, int64_t)
 FUTHARK_B200_ARRAY_1D(f64_1d, double)
+FUTHARK_B200_ARRAY_1D(i8_1d, int8_t)
+FUTHARK_B200_ARRAY_1D(i16_1d, int16_t)
+FUTHARK_B200_ARRAY_1D(f16_1d, uint16_t)   /* binary16 bit patterns, as for f16_3d */
 FUTHARK_B200_ARRAY_3D(f32_3d, float)
 FUTHARK_B200_ARRAY_3D(f16_3d, uint16_t)
 
@@ -264,6 +267,13 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
  * entry reduce_by_index_add_f64 (dest: *[n]f64) (is: []i32) (vs: []f64): [n]f64 =
  *   reduce_by_index dest (+) 0f64 (map i64.i32 is) vs                   (tests/hist/f64.fut; 8-byte values go
  *   the route of atomics on the result in global memory, SegHist.hs:377-560)
+ * entry reduce_by_index_add_i8 (dest: *[n]i8) (is: []i8) (vs: []i8): [n]i8 =
+ *   reduce_by_index dest (+) 0i8 (map i64.i8 is) vs                     (tests/hist/i8.fut)
+ * entry reduce_by_index_add_i16 (dest: *[n]i16) (is: []i16) (vs: []i16): [n]i16   (tests/hist/i16.fut)
+ * entry reduce_by_index_add_f16 (dest: *[n]f16) (is: []i16) (vs: []f16): [n]f16   (tests/hist/f16.fut)
+ *   1- and 2-byte values have no atomic of their own: a compare-and-swap loop on the 32-bit word that
+ *   holds the element (Base.hs:844-905).  f16 values are added as f32 and narrowed by truncation, as
+ *   the reference's C code does it (rts/c/scalar_f16.h:16-46, rts/c/half.h:220-228).
  * entry hist_rows_add_i32 (m: i64) (iss: [][]i32) (vss: [][]i32): [][m]i32 =
  *   map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss           (tests/hist/segmented.fut: the segment
  *   dimension of a SegHist, SegHist.hs:97-148)
@@ -288,6 +298,15 @@ FUTHARK_B200_RBI_ENTRY(min_u32, u32_1d)
 FUTHARK_B200_RBI_ENTRY(max_u32, u32_1d)
 FUTHARK_B200_RBI_ENTRY(add_f32, f32_1d)
 FUTHARK_B200_RBI_ENTRY(add_f64, f64_1d)
+int futhark_entry_reduce_by_index_add_i8(struct futhark_context *ctx, struct futhark_i8_1d **out0,
+                                         const struct futhark_i8_1d *in0, const struct futhark_i8_1d *in1,
+                                         const struct futhark_i8_1d *in2);
+int futhark_entry_reduce_by_index_add_i16(struct futhark_context *ctx, struct futhark_i16_1d **out0,
+                                          const struct futhark_i16_1d *in0, const struct futhark_i16_1d *in1,
+                                          const struct futhark_i16_1d *in2);
+int futhark_entry_reduce_by_index_add_f16(struct futhark_context *ctx, struct futhark_f16_1d **out0,
+                                          const struct futhark_f16_1d *in0, const struct futhark_i16_1d *in1,
+                                          const struct futhark_f16_1d *in2);
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
                                     const int64_t in0, const struct futhark_i32_2d *in1,
                                     const struct futhark_i32_2d *in2);

@@ -60,6 +60,10 @@ def lib():
         L.orc_linrec_last_f32.restype = ctypes.c_float
         L.orc_linrec_last_f32.argtypes = [vp, vp, i64]
         L.orc_reduce_by_index_add_f64.argtypes = [vp, i64, vp, vp, i64]
+        for t in ("i8", "i16", "f16"):
+            getattr(L, "orc_reduce_by_index_add_" + t).argtypes = [vp, i64, vp, vp, i64]
+        L.orc_float_to_half_trunc.restype = ctypes.c_uint16
+        L.orc_float_to_half_trunc.argtypes = [ctypes.c_float]
         L.orc_scanomap_steps_i32.argtypes = [vp, i64, vp]
         L.orc_filter_pos_i32.restype = i64
         L.orc_filter_pos_i32.argtypes = [vp, i64, vp]
@@ -464,6 +468,20 @@ def reduce_by_index_add_f64(dest, is_, vs):
     is_, vs = _c(is_, np.int32), _c(vs, np.float64)
     lib().orc_reduce_by_index_add_f64(_p(dest), dest.size, _p(is_), _p(vs), is_.size)
     return dest
+
+
+def reduce_by_index_subword(t, dest, is_, vs):
+    """reduce_by_index dest (+) 0 (map i64.iN is) vs for t in i8, i16 (indices of the same type) and f16
+    (binary16 bit patterns as uint16, i16 indices, the C code's widen-add-truncate arithmetic)."""
+    vt, it = {"i8": (np.int8, np.int8), "i16": (np.int16, np.int16), "f16": (np.uint16, np.int16)}[t]
+    dest = _c(dest, vt).copy()
+    is_, vs = _c(is_, it), _c(vs, vt)
+    getattr(lib(), "orc_reduce_by_index_add_" + t)(_p(dest), dest.size, _p(is_), _p(vs), is_.size)
+    return dest
+
+
+def float_to_half_trunc(f):
+    return int(lib().orc_float_to_half_trunc(float(f)))
 
 
 def hist(op, B, is_, vs):

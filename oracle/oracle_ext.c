@@ -69,6 +69,38 @@ float orc_linrec_last_f32(const float *as, const float *bs, int64_t n) {
   return b;
 }
 
+/* reduce_by_index dest (+) 0 (map i64.iN is) vs over i8 and i16 (tests/hist/i8.fut:49-50, i16.fut): add8 / add16 wrap
+ * (rts/c/scalar.h:21-27) */
+void orc_reduce_by_index_add_i8(int8_t *dest, int64_t n, const int8_t *is, const int8_t *vs, int64_t m) {
+  for (int64_t i = 0; i < m; i++)
+    if (is[i] >= 0 && (int64_t)is[i] < n) dest[is[i]] = (int8_t)((uint8_t)dest[is[i]] + (uint8_t)vs[i]);
+}
+void orc_reduce_by_index_add_i16(int16_t *dest, int64_t n, const int16_t *is, const int16_t *vs, int64_t m) {
+  for (int64_t i = 0; i < m; i++)
+    if (is[i] >= 0 && (int64_t)is[i] < n) dest[is[i]] = (int16_t)((uint16_t)dest[is[i]] + (uint16_t)vs[i]);
+}
+
+/* f32 -> binary16 bits the way the reference's C code narrows (rts/c/half.h:220-228: a table lookup whose
+ * arithmetic this is): truncation, NaN payloads cut to their top ten bits */
+uint16_t orc_float_to_half_trunc(float f) {
+  union { float x; uint32_t y; } u;
+  u.x = f;
+  const uint32_t bits = u.y, sign = (bits >> 16) & 0x8000u, e = (bits >> 23) & 0xffu, m = bits & 0x7fffffu;
+  if (e == 255u) return (uint16_t)(sign | 0x7c00u | (m >> 13));
+  if (e > 142u) return (uint16_t)(sign | 0x7c00u);
+  if (e >= 113u) return (uint16_t)(sign | ((e - 112u) << 10) | (m >> 13));
+  if (e >= 103u) return (uint16_t)(sign | ((0x0400u >> (113u - e)) + (m >> (126u - e))));
+  return (uint16_t)sign;
+}
+float orc_half_to_float(uint16_t h);     /* oracle.c */
+/* tests/hist/f16.fut:40-41 under the C code's f16: values are widened to f32, added there and narrowed back
+ * when they are stored (rts/c/scalar_f16.h:16-46) */
+void orc_reduce_by_index_add_f16(uint16_t *dest, int64_t n, const int16_t *is, const uint16_t *vs, int64_t m) {
+  for (int64_t i = 0; i < m; i++)
+    if (is[i] >= 0 && (int64_t)is[i] < n)
+      dest[is[i]] = orc_float_to_half_trunc(orc_half_to_float(dest[is[i]]) + orc_half_to_float(vs[i]));
+}
+
 /* tests/soacs/scan4.fut:11-22, statement by statement */
 static void scan4_step(const int32_t *xs, int64_t n, int32_t *out) {
   int32_t bits_sum = 0;

@@ -47,6 +47,9 @@ FILES = [
     "tests/soacs/scan-with-map.fut",
     "tests/soacs/reduce1.fut",
     "tests/soacs/reduce2.fut",
+    "tests/hist/i8.fut",
+    "tests/hist/i16.fut",
+    "tests/hist/f16.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f(?:16|32|64)\.nan|f32\.inf|-f32\.inf|true|false|"

@@ -182,6 +182,40 @@ def test_reduce_by_index_add_f64(ctx, B):
     assert np.array_equal(fb.reduce_by_index(ctx, "add_f64", dest * 0, bins, wi), oracle.reduce_by_index_add_f64(dest * 0, bins, wi))
 
 
+def test_reference_vectors_one_and_two_byte_values(ctx):
+    for t, dt in (("i8", np.int8), ("i16", np.int16)):
+        for c in GOLDEN["tests/hist/%s.fut" % t]:
+            dest, is_, image = c["input"]
+            assert fb.reduce_by_index_subword(ctx, t, np.array(dest, dt), np.array(is_, dt), np.array(image, dt)).tolist() == c["output"][0]
+    h = lambda v: np.array(_f(v), np.float32).astype(np.float16).view(np.uint16)
+    for c in GOLDEN["tests/hist/f16.fut"]:
+        dest, is_, image = c["input"]
+        got = fb.reduce_by_index_subword(ctx, "f16", h(dest), np.array(is_, np.int16), h(image))
+        # relative 0.002, the reference's own tolerance for floats in tests (src/Futhark/Test.hs:528)
+        assert np.allclose(got.view(np.float16).astype(np.float64), np.array(_f(c["output"][0]), np.float64), rtol=0.002, atol=0, equal_nan=True)
+
+
+@pytest.mark.parametrize("t,B", [("i8", 1), ("i8", 100), ("i16", 7), ("i16", 30000), ("f16", 5), ("f16", 1001)])
+def test_reduce_by_index_subword(ctx, t, B):
+    n = 100003
+    it = np.int8 if t == "i8" else np.int16
+    lim = 127 if t == "i8" else 32767
+    bins = datagen.uniform_i32(86, 0, n, -3, min(B + 3, lim)).astype(it)                 # some outside [0, B)
+    dest_i = datagen.uniform_i32(88, 0, B, -100, 100)
+    if t == "f16":
+        # integers up to 2048 are exact in f16 and the sums stay below that: the order of the updates does not show
+        ws = datagen.uniform_i32(87, 0, n, -1, 1).astype(np.float16).view(np.uint16)
+        dest = dest_i.astype(np.float16).view(np.uint16)
+    else:
+        ws = datagen.uniform_i32(87, 0, n, -2 ** 31, 2 ** 31 - 1).astype(it)             # wraps
+        dest = dest_i.astype(it)
+    got = fb.reduce_by_index_subword(ctx, t, dest, bins, ws)
+    want = oracle.reduce_by_index_subword(t, dest, bins, ws)
+    if t == "f16":
+        assert np.abs(want.view(np.float16).astype(np.float32)).max() < 2048
+    assert np.array_equal(got, want)
+
+
 @pytest.mark.parametrize("m,k", [(1, 1), (1, 100), (100, 1), (100, 100), (100001, 3), (3, 100001), (777, 1025), (0, 5), (5, 0)])
 def test_scan_map2_add_i32(ctx, m, k):
     xss = datagen.uniform_i32(85, 0, m * k, -2 ** 31, 2 ** 31 - 1).reshape(m, k)

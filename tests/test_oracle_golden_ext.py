@@ -139,6 +139,39 @@ def test_linrec_last_is_the_last_of_the_scan():
     assert oracle.linrec_last_f32(as_[:0], bs[:0]) == 0.0
 
 
+@pytest.mark.parametrize("t,dt", [("i8", np.int8), ("i16", np.int16)])
+def test_reduce_by_index_on_one_and_two_byte_integers(t, dt):
+    for c in cases("tests/hist/%s.fut" % t):
+        dest, is_, image = c["input"]
+        assert oracle.reduce_by_index_subword(t, np.array(dest, dt), np.array(is_, dt), np.array(image, dt)).tolist() == c["output"][0]
+
+
+def _h(v):
+    """f16 literals -> binary16 bit patterns (nearest)."""
+    return np.array(_f(v), np.float32).astype(np.float16).view(np.uint16)
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/f16.fut"))
+def test_reduce_by_index_add_f16(c):
+    dest, is_, image = c["input"]
+    got = oracle.reduce_by_index_subword("f16", _h(dest), np.array(is_, np.int16), _h(image)).view(np.float16).astype(np.float64)
+    want = np.array(_f(c["output"][0]), np.float64)
+    # the reference's own test tolerance for floats (src/Futhark/Test.hs:528): relative 0.002; one case sits exactly
+    # between two f16 values (0.4 + 0.4 + 0.4), where truncation and the literal's rounding differ by one unit
+    assert np.allclose(got, want, rtol=0.002, atol=0, equal_nan=True)
+
+
+def test_f32_to_f16_narrowing_is_the_reference_table():
+    R = oracle.ref_scalar()
+    if R is None:
+        pytest.skip("reference checkout not present: oracle/_ref not built")
+    rng = np.random.default_rng(5)
+    bits = np.concatenate([rng.integers(0, 2 ** 32, 200000, dtype=np.uint64).astype(np.uint32),
+                           (np.arange(512, dtype=np.uint32) << 23)[:, None].repeat(3, 1).reshape(-1) | np.tile(np.array([0, 1, 0x7fffff], np.uint32), 512)])
+    for f in bits.view(np.float32):
+        assert oracle.float_to_half_trunc(f) == R.ref_float2halfbits(float(f)), float(f).hex()
+
+
 def test_definitions_without_reference_values():
     rng = np.random.default_rng(0)
     xs = rng.integers(-1000, 1000, 1000).astype(np.int32)
