@@ -763,7 +763,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,       # no published number for this metric
             "dtype": "f32", "data": "synthetic",
             "config": workload_config(),
-            "roofline": {"bound": "hbm", "kernel": "stream_kernel<K_SEGSCAN_F32>", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "stream_kernel<SpecSegScanAddF32>", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                          "peak_note": "the peak is a read+write copy; kernels that almost only read (reduce, rowsum, histograms) can exceed it",
                          "traffic": NCU_TRAFFIC_SEGSCAN_2P25 * (N_SEG / float(1 << 25)),

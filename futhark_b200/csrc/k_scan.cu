@@ -354,13 +354,26 @@ stream_kernel(const LookbackArgs a) {
   };
   // Hands buffer b to the workers for `item`: by the copies' completion, or (no item, a ragged
   // tile, unaligned arrays: the workers copy the tile in themselves) at once.
+  // L2 eviction priority (S::kStreamHints): a tile is dead in L2 once its visit B has read it, and the
+  // results are written once; marking both "evict first" leaves the room to the tiles that wait between
+  // their two visits.  Measured on 2^28 keys: filter 318 -> 308 us, partition 458 -> 431 us (DRAM reads of
+  // the partition were 1.67 x the input without it); no effect on the scans, whose window fits anyway.
+  const uint64_t pol_first = l2_policy_evict_first();
+  auto load_hinted = [&](void *dst, const void *src, uint32_t bytes, uint64_t *bar, bool visit_a) {
+    if (S::kStreamHints && !visit_a) bulk_g2s_hint(dst, src, bytes, bar, pol_first);
+    else bulk_g2s(dst, src, bytes, bar);
+  };
+  auto store_hinted = [&](void *gdst, const void *src, uint32_t bytes) {
+    if (S::kStreamHints) bulk_s2g_hint(gdst, src, bytes, pol_first);
+    else bulk_s2g(gdst, src, bytes);
+  };
   auto hand_over = [&](int b, uint32_t item) {
     if (item_is_bulk(item)) {
       unsigned char *dst = s_buf + b * SB;
       const int64_t tb = (int64_t)(item >> 1) * TILE;
       mbar_expect_tx(&s_bar[b], TILE * 4 + (HASF ? TILE : 0));
-      bulk_g2s(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, TILE * 4, &s_bar[b]);
-      if (HASF) bulk_g2s(dst + FO, a.flags + tb, TILE, &s_bar[b]);
+      load_hinted(dst, reinterpret_cast<const uint32_t *>(a.in) + tb, TILE * 4, &s_bar[b], (item & 1u) != 0);
+      if (HASF) load_hinted(dst + FO, a.flags + tb, TILE, &s_bar[b], (item & 1u) != 0);
     } else {
       mbar_arrive(&s_bar[b]);
     }
@@ -457,7 +470,7 @@ stream_kernel(const LookbackArgs a) {
         }
       } else if (!COMPACT) {
         if (ok && full && out_bulk && lane == 0) {
-          bulk_s2g(reinterpret_cast<uint32_t *>(a.out) + base, s_tile, TILE * 4);
+          store_hinted(reinterpret_cast<uint32_t *>(a.out) + base, s_tile, TILE * 4);
           bulk_commit();
         }
       } else if (ok) {
@@ -480,7 +493,7 @@ stream_kernel(const LookbackArgs a) {
           const uint32_t l = (uint32_t)(lane - lane0);               // lanes lane0 .. lane0+2 take the ends
           if (l < h) g[l] = s_tile[s0 + l];
           if (l < len - tail0) g[tail0 + l] = s_tile[s0 + tail0 + l];
-          if (lane == 0 && nvec > 0) bulk_s2g(g + h, s_tile + s0 + h, nvec << 4);
+          if (lane == 0 && nvec > 0) store_hinted(g + h, s_tile + s0 + h, nvec << 4);
         };
         send_run(dst, pad_t, tile_true, 0);
         if (PART) send_run(dstf, start_f, (uint32_t)count - tile_true, 4);

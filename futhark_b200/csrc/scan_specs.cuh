@@ -20,6 +20,7 @@
 //                 pred, in order; a partition also keeps the others, behind them
 //   V, CTAS, LEAD tile geometry: a thread owns V 16-byte vectors (V odd), CTAS CTAs per SM,
 //                 aggregates run LEAD tiles ahead of the scans
+//   kStreamHints  L2 eviction priority "first" for what visit B reads and for what is stored
 //   NBUF, DIST    tile buffers per CTA, and how many iterations ahead a tile is fetched (DIST < NBUF)
 #pragma once
 #include <stdint.h>
@@ -70,6 +71,7 @@ struct SpecDefaults {
   using Op = OpAddU32;
   static constexpr bool kHasPost = false, kExclusive = false, kFlagArray = false, kSegRegular = false;
   static constexpr bool kCompact = false, kPartition = false;
+  static constexpr bool kStreamHints = false;   // visit B's loads and the stores ask L2 to evict their lines first
   // Measured on 2^26 i32 (scan) / 2^27 f32 with flags (segmented scan), V x CTAS x NBUF x DIST:
   // 5x4x2x1 97 / 213 us; 5x5x2x1 102 / 219 us; 5x3x3x2 102 / 274 us; 5x3x3x1 105 / 295 us;
   // 3x4x4x2 120 / 318 us; 3x4x3x2 119 / 279 us; 3x5x3x2 123 / 285 us.
@@ -106,10 +108,12 @@ struct SpecScanomapStepI32 : SpecDefaults {
 // ---- compaction -----------------------------------------------------------------------------
 // Tiles of 9216 keys (V = 9), 3 CTAs per SM: the second visit does much more per tile than a
 // scan's.  Measured on 2^28 keys (filter / partition): 323 / 461 us; tiles of 5120 keys with 4 CTAs
-// per SM 393 / 492 us (no better with a lead of 1536 or 2048 tiles); 7168 keys 368 / 481 us.
+// per SM 393 / 492 us (no better with a lead of 1536 or 2048 tiles); 7168 keys 368 / 481 us.  With the eviction
+// hints (308 / 431 us) a lead of 704 / 768 / 896 / 1280 tiles gives 311 / 308 / 308 / 309 and 438 / 432 / 429 / 440 us.
 struct SpecCompact : SpecDefaults {
   static constexpr bool kCompact = true;
   static constexpr int V = 9, CTAS = 3, NBUF = 2, DIST = 1;
+  static constexpr bool kStreamHints = true;
 };
 struct SpecFilterLow3U32 : SpecCompact {                                         // filter (\k -> (k & 7) < 3) ks
   static __device__ __forceinline__ bool pred(uint32_t key, uint32_t) { return (key & 7u) < 3u; }
@@ -132,7 +136,7 @@ struct SpecPartitionDiv3I32 : SpecCompact {
 // filter over zip xs keep by the second component (tests/soacs/filter3.fut): the keep-flags
 // travel with the keys, so the tile is smaller (5120 keys, 4 CTAs per SM)
 struct SpecFilterByFlagI32 : SpecDefaults {
-  static constexpr bool kCompact = true, kFlagArray = true;
+  static constexpr bool kCompact = true, kFlagArray = true, kStreamHints = true;
   static constexpr int V = 5, CTAS = 4, NBUF = 2, DIST = 1;
   static __device__ __forceinline__ bool pred(uint32_t, uint32_t flag) { return flag != 0u; }
 };
