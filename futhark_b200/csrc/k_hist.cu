@@ -207,7 +207,9 @@ hist_smem_kernel(const int32_t *__restrict__ bins, const uint32_t *__restrict__ 
 // combining equal bins across the warp first (match.any + warp reduction, 10x slower); the four
 // most frequent bins of a CTA combined in registers (no faster, and slower for uniform
 // indices); the CTAs of a group paced by a cluster barrier (Zipf 12 % faster, uniform max 9 %
-// slower, three and four ranges slower); the CTAs of a group paced through progress counters
+// slower, three and four ranges slower; the same with the pair meeting only every 8th round and
+// arriving 4 rounds before it waits: add 405 / 502 us, max 502 / 527 us for uniform / Zipf indices against
+// 354 / 548 and 412 / 506 unpaced, so it is the cluster launch that costs); the CTAs of a group paced through progress counters
 // in global memory, a CTA waiting only when it is more than 12-16 rounds ahead (uniform AND
 // Zipf 3.4x - 6.5x slower: in this kernel a global load or store queues behind the SM's
 // outstanding input requests for several microseconds, during which the grid streams ~50 MB,
