@@ -110,6 +110,7 @@ struct SpecScanomapStepI32 : SpecDefaults {
 // scan's.  Measured on 2^28 keys (filter / partition): 323 / 461 us; tiles of 5120 keys with 4 CTAs
 // per SM 393 / 492 us (no better with a lead of 1536 or 2048 tiles); 7168 keys 368 / 481 us.  With the eviction
 // hints (308 / 431 us) a lead of 704 / 768 / 896 / 1280 tiles gives 311 / 308 / 308 / 309 and 438 / 432 / 429 / 440 us.
+// Tile sizes again with the hints: 5120 keys x 4 CTAs 369 / 478 us, 7168 x 3 349 / 468 us, 11264 x 2 348 / 510 us.
 struct SpecCompact : SpecDefaults {
   static constexpr bool kCompact = true;
   static constexpr int V = 9, CTAS = 3, NBUF = 2, DIST = 1;
