@@ -50,6 +50,7 @@ FILES = [
     "tests/hist/i8.fut",
     "tests/hist/i16.fut",
     "tests/hist/f16.fut",
+    "tests/tokens.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f(?:16|32|64)\.nan|f32\.inf|-f32\.inf|true|false|"

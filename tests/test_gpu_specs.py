@@ -88,6 +88,19 @@ def test_reference_vectors_more_types_and_index_spaces(ctx):
     assert int(fb.scan_i32(ctx, np.array(a, np.int32))[i]) == GOLDEN["tests/soacs/scan3.fut"][0]["output"][1]
 
 
+def test_reference_vector_through_the_flagged_segmented_scan(ctx):
+    # tests/tokens.fut: the words of a byte string, found with a flagged segmented scan of 0/1 values
+    from util import tokens_of
+    for c in GOLDEN["tests/tokens.fut"]:
+        s, i = c["input"]
+        start, length = tokens_of(lambda f, v: fb.segscan_f32(ctx, f, v), s)[i]
+        assert s[start:start + length] == c["output"][0]
+    # the same on a long text: 3 tiles of words, against the oracle's scan
+    rng = np.random.default_rng(11)
+    text = rng.choice(np.array([32, 97, 98, 99, 100], np.uint8), 3 * 5120 + 77)
+    assert tokens_of(lambda f, v: fb.segscan_f32(ctx, f, v), text) == tokens_of(oracle.segscan_f32, text)
+
+
 # ---- against the oracle on seeded inputs ---------------------------------------------------------
 
 @pytest.mark.parametrize("n", SIZES + BIG)

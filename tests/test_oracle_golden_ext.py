@@ -172,6 +172,16 @@ def test_f32_to_f16_narrowing_is_the_reference_table():
         assert oracle.float_to_half_trunc(f) == R.ref_float2halfbits(float(f)), float(f).hex()
 
 
+@pytest.mark.parametrize("c", cases("tests/tokens.fut"))
+def test_tokens_flagged_segmented_scan_known_answer(c):
+    # the reference's one known answer that goes through a flagged segmented scan (its operator is the lifted one
+    # of the bench's f32 scan; the values are 0 and 1, exact in f32)
+    from util import tokens_of
+    s, i = c["input"]
+    start, length = tokens_of(oracle.segscan_f32, s)[i]
+    assert s[start:start + length] == c["output"][0]
+
+
 def test_definitions_without_reference_values():
     rng = np.random.default_rng(0)
     xs = rng.integers(-1000, 1000, 1000).astype(np.int32)

@@ -27,3 +27,15 @@ def assert_close_l1(got, ref64, l1, rtol, what=""):
     bad = np.flatnonzero(err > bound)
     assert bad.size == 0, "%s: %d elements off, worst ratio %.3g at %d" % (
         what, bad.size, float((err / np.maximum(l1, 1e-30)).max()), int(bad[0]))
+
+
+def tokens_of(segscan, s):
+    """tests/tokens.fut:24-35 of the reference with the flagged segmented scan passed in: the words of the byte
+    string `s` as (start, length) pairs.  The scan runs over 0/1 values, exact in any element type."""
+    import numpy as np
+    s = np.asarray(s, np.uint8)
+    is_space = s == 32
+    x = np.asarray(segscan(is_space, (~is_space).astype(np.float32))).astype(np.int64)
+    y = np.roll(x, -1)                                  # rotate 1
+    keep = x > y
+    return [(int(i - x[i] + 1), int(x[i])) for i in np.nonzero(keep)[0]]
