@@ -10,10 +10,13 @@
  * partition1.fut, tests/hist/simple.fut, max.fut, large.fut,
  * tests/segredomap/segsum-comm.fut, tests/soacs/segreduce-iota.fut,
  * tests/reg-tiling/mmm.fut, tests/mss.fut, tests/soacs/exscan0.fut, exscan1.fut,
- * tests/modules/functor1.fut).  The flagged f32 segmented scan and the f16-input
- * contraction have no pinned vectors in the reference ("auto output" only), so
- * for those two this oracle is "parity unpinned": it follows the reference's
- * operator definitions but cannot be checked against reference-produced values.
+ * tests/modules/functor1.fut, tests/tokens.fut).  For the flagged f32 segmented
+ * scan and the f16-input contraction the reference holds one known answer each on
+ * exactly representable values (tests/tokens.fut: a flagged segmented scan of 0/1
+ * values; tests/reg-tiling/mmm.fut: a product of small integers) and otherwise
+ * "auto output" only, so for their rounding on general data this oracle is
+ * "parity unpinned": it follows the reference's operator definitions but cannot
+ * be checked against reference-produced values there.
  *
  * Scalar semantics follow rts/c/scalar.h: add32 is an unsigned add (:29), fmax32
  * is fmaxf (:932), f16 values are widened exactly to f32 before arithmetic
