@@ -36,6 +36,7 @@ ARRAY_TYPES = {
     "i16_1d": (np.int16, 1, ctypes.c_int16),
     "f16_1d": (np.uint16, 1, ctypes.c_uint16),
     "f32_3d": (np.float32, 3, ctypes.c_float),
+    "i32_3d": (np.int32, 3, ctypes.c_int32),
     "f16_3d": (np.uint16, 3, ctypes.c_uint16),
 }
 
@@ -200,6 +201,8 @@ def load():
         getattr(L, "futhark_entry_reduce_by_index_" + name).argtypes = [vp, pvp, vp, vp, vp]
     L.futhark_entry_hist_rows_add_i32.argtypes = [vp, pvp, i64, vp, vp]
     L.futhark_entry_reduce_by_index_2d_add_i32.argtypes = [vp, pvp, vp, vp, vp, vp]
+    L.futhark_entry_reduce_by_index_3d_add_i32.argtypes = [vp, pvp, vp, vp, vp, vp, vp]
+    L.futhark_entry_hist_rows_2d_add_i32.argtypes = [vp, pvp, i64, i64, vp, vp]
     for i in range(3):
         getattr(L, "futhark_project_%s_%d" % (TRIPLE, i)).argtypes = [vp, pvp, vp]
     getattr(L, "futhark_free_" + TRIPLE).argtypes = [vp, vp]
@@ -457,6 +460,12 @@ class Context:
 
     def entry_reduce_by_index_2d_add_i32(self, dest, is_, js, vs):
         return self._entry_arr("reduce_by_index_2d_add_i32", "i32_2d", dest.ptr, is_.ptr, js.ptr, vs.ptr)
+
+    def entry_reduce_by_index_3d_add_i32(self, dest, is_, js, ks, vs):
+        return self._entry_arr("reduce_by_index_3d_add_i32", "i32_3d", dest.ptr, is_.ptr, js.ptr, ks.ptr, vs.ptr)
+
+    def entry_hist_rows_2d_add_i32(self, n, m, xss, yss):
+        return self._entry_arr("hist_rows_2d_add_i32", "i32_3d", int(n), int(m), xss.ptr, yss.ptr)
 
     def entry_filter_u32(self, ks):
         return self._entry_arr("filter_u32", "u32_1d", ks.ptr)
@@ -770,6 +779,14 @@ def reduce_by_index_subword(ctx, t, dest, bins, ws):
 
 def hist_rows_add_i32(ctx, m, iss, vss):
     return _run(ctx, [("i32_2d", iss), ("i32_2d", vss)], lambda i, v: ctx.entry_hist_rows_add_i32(m, i, v))
+
+
+def reduce_by_index_3d_add_i32(ctx, dest, is_, js, ks, vs):
+    return _run(ctx, [("i32_3d", dest), ("i64_1d", is_), ("i64_1d", js), ("i64_1d", ks), ("i32_1d", vs)], ctx.entry_reduce_by_index_3d_add_i32)
+
+
+def hist_rows_2d_add_i32(ctx, n, m, xss, yss):
+    return _run(ctx, [("i32_2d", xss), ("i32_2d", yss)], lambda x, y: ctx.entry_hist_rows_2d_add_i32(n, m, x, y))
 
 
 def reduce_by_index_2d_add_i32(ctx, dest, is_, js, vs):

@@ -56,7 +56,7 @@ static const ArrayType ARRAYS[] = {
     FE_ARRAY(f32, float, 3, "[][][]f32", "f32"), FE_ARRAY(f16, uint16_t, 3, "[][][]f16", "f16"),
     FE_ARRAY(f64, double, 1, "[]f64", "f64"),    FE_ARRAY(i32, int32_t, 2, "[][]i32", "i32"), FE_ARRAY(i64, int64_t, 2, "[][]i64", "i64"),
     FE_ARRAY(bool, bool, 2, "[][]bool", "bool"), FE_ARRAY(i8, int8_t, 1, "[]i8", "i8"), FE_ARRAY(i16, int16_t, 1, "[]i16", "i16"),
-    FE_ARRAY(f16, uint16_t, 1, "[]f16", "f16"),
+    FE_ARRAY(f16, uint16_t, 1, "[]f16", "f16"), FE_ARRAY(i32, int32_t, 3, "[][][]i32", "i32"),
 };
 inline const ArrayType *array_type(const std::string &name) {
   for (const ArrayType &a : ARRAYS)
@@ -276,6 +276,8 @@ inline const std::vector<EntryPoint> &entry_points() {
       FE_E3(reduce_by_index_add_i16, i16_1d, "[]i16", i16_1d, "[]i16", i16_1d, "[]i16", i16_1d, "[]i16"),
       FE_E3(reduce_by_index_add_f16, f16_1d, "[]f16", i16_1d, "[]i16", f16_1d, "[]f16", f16_1d, "[]f16"),
       {"reduce_by_index_2d_add_i32", {"[][]i32", "[]i64", "[]i64", "[]i32"}, "[][]i32", [](C *c, In in, Value &o) { futhark_i32_2d *r = nullptr; int rc = futhark_entry_reduce_by_index_2d_add_i32(c, &r, FE_IN(0, i32_2d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i32_1d)); if (!rc) set_array(o, "[][]i32", r); return rc; }},
+      {"reduce_by_index_3d_add_i32", {"[][][]i32", "[]i64", "[]i64", "[]i64", "[]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_reduce_by_index_3d_add_i32(c, &r, FE_IN(0, i32_3d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i64_1d), FE_IN(4, i32_1d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
+      {"hist_rows_2d_add_i32", {"i64", "i64", "[][]i32", "[][]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_hist_rows_2d_add_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int64_t>(*in[1]), FE_IN(2, i32_2d), FE_IN(3, i32_2d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"partition2_i32", {"[]i32"}, "([]i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32)", r); return rc; }},
       {"replicate_i32", {"i64", "i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_replicate_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int32_t>(*in[1])); if (!rc) set_array(o, "[]i32", r); return rc; }},
       {"iota_i64", {"i64"}, "[]i64", [](C *c, In in, Value &o) { futhark_i64_1d *r = nullptr; int rc = futhark_entry_iota_i64(c, &r, scalar_of<int64_t>(*in[0])); if (!rc) set_array(o, "[]i64", r); return rc; }},

@@ -480,6 +480,69 @@ int futhark_entry_reduce_by_index_2d_add_i32(struct futhark_context *ctx, struct
   return FUTHARK_SUCCESS;
 }
 
+// reduce_by_index_3d dest (+) 0 (zip3 is js ks) vs (prelude/soacs.fut:153-154, tests/hist/hist3d.fut): one histogram
+// over k * m * l bins behind a kernel that flattens the index triples
+int futhark_entry_reduce_by_index_3d_add_i32(struct futhark_context *ctx, struct futhark_i32_3d **out0, const struct futhark_i32_3d *in0,
+                                             const struct futhark_i64_1d *in1, const struct futhark_i64_1d *in2,
+                                             const struct futhark_i64_1d *in3, const struct futhark_i32_1d *in4) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t K = in0->shape[0], M = in0->shape[1], L = in0->shape[2], n = in1->shape[0];
+  if (in2->shape[0] != n || in3->shape[0] != n || in4->shape[0] != n) return bad_sizes(ctx);
+  if (K * M * L >= (1ll << 31)) { fb_set_error(ctx, "reduce_by_index_3d_add_i32: %lld bins exceed 2^31-1.", (long long)(K * M * L)); return 1; }
+  memblock_device flat;
+  int rc = fb_alloc(ctx, (size_t)n * 4, "reduce_by_index_3d.flat_index", &flat);
+  if (rc != 0) return rc;
+  void *o = nullptr;
+  ctx->launch_count++;
+  rc = fb_cuda_check(ctx, fb::launch_flatten_3d_index(dptr<int64_t>(in1->mem), dptr<int64_t>(in2->mem), dptr<int64_t>(in3->mem), n, K, M, L,
+                                                      dptr<int32_t>(flat), ctx->num_sms, ctx->stream), "flatten_3d_index");
+  if (rc == 0) rc = hist_launch(ctx, fb::HOP_ADD_I32, &o, K * M * L, &in0->mem, dptr<int32_t>(flat), n, in4->mem, n, "reduce_by_index_3d_add_i32.seghist");
+  fb_unref(ctx, &flat);
+  if (rc != 0) return rc;
+  futhark_i32_1d *h = (futhark_i32_1d *)o;
+  futhark_i32_3d *out = (futhark_i32_3d *)malloc(sizeof(futhark_i32_3d));
+  if (out == nullptr) { fb_unref(ctx, &h->mem); free(h); return 1; }
+  out->mem = h->mem; out->shape[0] = K; out->shape[1] = M; out->shape[2] = L;
+  free(h);
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+// tests/hist/segmented_2d.fut: a 2-D histogram of ones per row of index pairs (a segment dimension over
+// reduce_by_index_2d, SegHist.hs:97-148): one histogram over rows * n * m bins
+int futhark_entry_hist_rows_2d_add_i32(struct futhark_context *ctx, struct futhark_i32_3d **out0, const int64_t in0, const int64_t in1,
+                                       const struct futhark_i32_2d *in2, const struct futhark_i32_2d *in3) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t N = in0, M = in1, rows = in2->shape[0], cols = in2->shape[1], n = rows * cols;
+  if (in3->shape[0] != rows || in3->shape[1] != cols) return bad_sizes(ctx);
+  if (N < 0 || M < 0) { fb_set_error(ctx, "Error: negative histogram size %lld x %lld.\n", (long long)N, (long long)M); return FUTHARK_PROGRAM_ERROR; }
+  if (rows * N * M >= (1ll << 31)) { fb_set_error(ctx, "hist_rows_2d_add_i32: %lld bins in all exceed 2^31-1.", (long long)(rows * N * M)); return 1; }
+  memblock_device flat, ones;
+  int rc = fb_alloc(ctx, (size_t)n * 4, "hist_rows_2d.flat_index", &flat);
+  if (rc != 0) return rc;
+  rc = fb_alloc(ctx, (size_t)n * 4, "hist_rows_2d.ones", &ones);
+  if (rc != 0) { fb_unref(ctx, &flat); return rc; }
+  void *o = nullptr;
+  ctx->launch_count += 2;
+  rc = fb_cuda_check(ctx, fb::launch_replicate(4, dptr<void>(ones), n, 1ull, ctx->num_sms, ctx->stream), "replicate");
+  if (rc == 0)
+    rc = fb_cuda_check(ctx, fb::launch_flatten_rows_2d_index(dptr<int32_t>(in2->mem), dptr<int32_t>(in3->mem), n, cols, N, M, dptr<int32_t>(flat),
+                                                             ctx->num_sms, ctx->stream), "flatten_rows_2d_index");
+  if (rc == 0) rc = hist_launch(ctx, fb::HOP_ADD_I32, &o, rows * N * M, nullptr, dptr<int32_t>(flat), n, ones, n, "hist_rows_2d_add_i32.seghist");
+  fb_unref(ctx, &flat);
+  fb_unref(ctx, &ones);
+  if (rc != 0) return rc;
+  futhark_i32_1d *h = (futhark_i32_1d *)o;
+  futhark_i32_3d *out = (futhark_i32_3d *)malloc(sizeof(futhark_i32_3d));
+  if (out == nullptr) { fb_unref(ctx, &h->mem); free(h); return 1; }
+  out->mem = h->mem; out->shape[0] = rows; out->shape[1] = N; out->shape[2] = M;
+  free(h);
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
 // ---- compaction entry points -----------------------------------------------------------------------
 // Shared by every filter and partition: one look-back pass per 2^30 keys, then the count is read back
 // so the result shapes can be filled in.  ARR is any one-dimensional array struct of 4-byte elements.

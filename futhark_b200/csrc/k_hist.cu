@@ -483,6 +483,37 @@ flatten_2d_index_kernel(const int64_t *__restrict__ is, const int64_t *__restric
     flat[i] = (a >= 0 && a < N && b >= 0 && b < M) ? (int32_t)(a * M + b) : -1;
   }
 }
+__global__ void __launch_bounds__(256)
+flatten_3d_index_kernel(const int64_t *__restrict__ is, const int64_t *__restrict__ js, const int64_t *__restrict__ ks, int64_t n, int64_t K,
+                        int64_t M, int64_t L, int32_t *__restrict__ flat) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+    const int64_t a = is[i], b = js[i], c = ks[i];
+    flat[i] = (a >= 0 && a < K && b >= 0 && b < M && c >= 0 && c < L) ? (int32_t)((a * M + b) * L + c) : -1;
+  }
+}
+// a 2-D histogram per row of [rows][cols] index pairs: flat = (row * N + x) * M + y
+__global__ void __launch_bounds__(256)
+flatten_rows_2d_index_kernel(const int32_t *__restrict__ xs, const int32_t *__restrict__ ys, int64_t n, int64_t cols, int64_t N, int64_t M,
+                             int32_t *__restrict__ flat) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+    const int64_t x = xs[i], y = ys[i];
+    flat[i] = (x >= 0 && x < N && y >= 0 && y < M) ? (int32_t)(((i / cols) * N + x) * M + y) : -1;
+  }
+}
+cudaError_t launch_flatten_3d_index(const int64_t *is, const int64_t *js, const int64_t *ks, int64_t n, int64_t K, int64_t M, int64_t L,
+                                    int32_t *flat, int num_sms, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  flatten_3d_index_kernel<<<grid_for(n, 256, num_sms * 8), 256, 0, stream>>>(is, js, ks, n, K, M, L, flat);
+  return cudaGetLastError();
+}
+cudaError_t launch_flatten_rows_2d_index(const int32_t *xs, const int32_t *ys, int64_t n, int64_t cols, int64_t N, int64_t M, int32_t *flat,
+                                         int num_sms, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  flatten_rows_2d_index_kernel<<<grid_for(n, 256, num_sms * 8), 256, 0, stream>>>(xs, ys, n, cols, N, M, flat);
+  return cudaGetLastError();
+}
 cudaError_t launch_flatten_rows_index(const int32_t *is, int64_t n, int64_t cols, int64_t B, int32_t *flat, int num_sms, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
   flatten_rows_index_kernel<<<grid_for(n, 256, num_sms * 8), 256, 0, stream>>>(is, n, cols, B, flat);

@@ -107,6 +107,12 @@ enum HistOpKind : int {
 };
 cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
                         const void *dest, int num_sms, cudaStream_t stream);
+// flat[i] = (is[i] * M + js[i]) * L + ks[i], or -1 out of range: reduce_by_index_3d
+cudaError_t launch_flatten_3d_index(const int64_t *is, const int64_t *js, const int64_t *ks, int64_t n, int64_t K, int64_t M, int64_t L,
+                                    int32_t *flat, int num_sms, cudaStream_t stream);
+// flat[i] = ((i / cols) * N + xs[i]) * M + ys[i], or -1 out of range: a 2-D histogram per row
+cudaError_t launch_flatten_rows_2d_index(const int32_t *xs, const int32_t *ys, int64_t n, int64_t cols, int64_t N, int64_t M, int32_t *flat,
+                                         int num_sms, cudaStream_t stream);
 // reduce_by_index dest (+) 0 is vs over f64: atomics on the result in global memory
 cudaError_t launch_hist_add_f64(int64_t B, const int32_t *bins, const double *vs, int64_t n, double *out, const double *dest, int num_sms,
                                 cudaStream_t stream);

@@ -147,6 +147,7 @@ FB_DEFINE_ARRAY_STRUCT(i8_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(i16_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f16_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_3d, 3)
+FB_DEFINE_ARRAY_STRUCT(i32_3d, 3)
 FB_DEFINE_ARRAY_STRUCT(f16_3d, 3)
 
 struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 {

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PATH = os.path.join(HERE, "futhark_b200.json")
 
 ELEM = {"i32": "int32_t", "i64": "int64_t", "u32": "uint32_t", "f32": "float", "f64": "double", "bool": "bool", "f16": "uint16_t"}
-ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "f16_1d", "bool_1d", "f32_2d", "i32_2d", "i64_2d", "bool_2d", "f32_3d", "f16_3d"]
+ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "f16_1d", "bool_1d", "f32_2d", "i32_2d", "i64_2d", "bool_2d", "f32_3d", "i32_3d", "f16_3d"]
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
@@ -57,6 +57,8 @@ ENTRIES = {
     "reduce_by_index_add_f16": ([("dest", "[]f16"), ("is", "[]i16"), ("vs", "[]f16")], "[]f16", []),
     "hist_rows_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vss", "[][]i32")], "[][]i32", []),
     "reduce_by_index_2d_add_i32": ([("dest", "[][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("vs", "[]i32")], "[][]i32", []),
+    "reduce_by_index_3d_add_i32": ([("dest", "[][][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("ks", "[]i64"), ("vs", "[]i32")], "[][][]i32", []),
+    "hist_rows_2d_add_i32": ([("n", "i64"), ("m", "i64"), ("xss", "[][]i32"), ("yss", "[][]i32")], "[][][]i32", []),
     "filter_u32": ([("ks", "[]u32")], "[]u32", ["filter_u32.segscan_tblock_size"]),
     "partition_u32": ([("ks", "[]u32")], "([]u32, []u32)", ["partition_u32.segscan_tblock_size"]),
     "filter_pos_i32": ([("xs", "[]i32")], "[]i32", []),

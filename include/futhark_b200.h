@@ -142,6 +142,7 @@ FUTHARK_B200_ARRAY_1D(i8_1d, int8_t)
 FUTHARK_B200_ARRAY_1D(i16_1d, int16_t)
 FUTHARK_B200_ARRAY_1D(f16_1d, uint16_t)   /* binary16 bit patterns, as for f16_3d */
 FUTHARK_B200_ARRAY_3D(f32_3d, float)
+FUTHARK_B200_ARRAY_3D(i32_3d, int32_t)
 FUTHARK_B200_ARRAY_3D(f16_3d, uint16_t)
 
 /* ---- opaque tuple returned by partition: naming per
@@ -278,7 +279,13 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
  *   map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss           (tests/hist/segmented.fut: the segment
  *   dimension of a SegHist, SegHist.hs:97-148)
  * entry reduce_by_index_2d_add_i32 (dest: *[n][m]i32) (is: []i64) (js: []i64) (vs: []i32): [n][m]i32 =
- *   reduce_by_index_2d dest (+) 0 (zip is js) vs                        (prelude/soacs.fut:149-152; tests/hist/hist2d.fut) */
+ *   reduce_by_index_2d dest (+) 0 (zip is js) vs                        (prelude/soacs.fut:149-152; tests/hist/hist2d.fut)
+ * entry reduce_by_index_3d_add_i32 (dest: *[k][m][l]i32) (is: []i64) (js: []i64) (ks: []i64) (vs: []i32): [k][m][l]i32 =
+ *   reduce_by_index_3d dest (+) 0 (zip3 is js ks) vs                    (prelude/soacs.fut:153-154; tests/hist/hist3d.fut)
+ * entry hist_rows_2d_add_i32 (n: i64) (m: i64) (xss: [][]i32) (yss: [][]i32): [][n][m]i32 =
+ *   map2 (\xs ys -> reduce_by_index_2d (replicate n (replicate m 0)) (+) 0 (zip (map i64.i32 xs) (map i64.i32 ys))
+ *                                      (map (const 1) xs)) xss yss      (tests/hist/segmented_2d.fut: a segment
+ *   dimension over a 2-D histogram) */
 #define FUTHARK_B200_HIST_ENTRY(NAME, ARR)                                                          \
   int futhark_entry_hist_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0,           \
                                 const int64_t in0, const struct futhark_i32_1d *in1,               \
@@ -315,6 +322,15 @@ int futhark_entry_reduce_by_index_2d_add_i32(struct futhark_context *ctx, struct
                                              const struct futhark_i64_1d *in1,
                                              const struct futhark_i64_1d *in2,
                                              const struct futhark_i32_1d *in3);
+int futhark_entry_reduce_by_index_3d_add_i32(struct futhark_context *ctx, struct futhark_i32_3d **out0,
+                                             const struct futhark_i32_3d *in0,
+                                             const struct futhark_i64_1d *in1,
+                                             const struct futhark_i64_1d *in2,
+                                             const struct futhark_i64_1d *in3,
+                                             const struct futhark_i32_1d *in4);
+int futhark_entry_hist_rows_2d_add_i32(struct futhark_context *ctx, struct futhark_i32_3d **out0,
+                                       const int64_t in0, const int64_t in1,
+                                       const struct futhark_i32_2d *in2, const struct futhark_i32_2d *in3);
 
 /* entry filter_u32 (ks: []u32): []u32 = filter (\k -> (k & 7) < 3) ks
  * entry partition_u32 (ks: []u32): ([]u32, []u32) = partition (\k -> (k & 7) < 3) ks

@@ -73,6 +73,8 @@ def lib():
         L.orc_reduce_by_index_32.argtypes = [i32, vp, i64, vp, vp, i64]
         L.orc_hist_rows_add_i32.argtypes = [i64, vp, vp, i64, i64, vp]
         L.orc_reduce_by_index_2d_add_i32.argtypes = [vp, i64, i64, vp, vp, vp, i64]
+        L.orc_reduce_by_index_3d_add_i32.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, i64]
+        L.orc_hist_rows_2d_add_i32.argtypes = [i64, i64, vp, vp, i64, i64, vp]
         L.orc_scan_i64.argtypes = [vp, i64, vp]
         L.orc_linrec_f32.argtypes = [vp, vp, i64, vp]
         L.orc_linrec_f64.argtypes = [vp, vp, i64, vp, vp]
@@ -494,6 +496,20 @@ def hist_rows_add_i32(m, iss, vss):
     iss, vss = _c(iss, np.int32), _c(vss, np.int32)
     out = np.empty((iss.shape[0], m), np.int32)
     lib().orc_hist_rows_add_i32(m, _p(iss), _p(vss), iss.shape[0], iss.shape[1], _p(out))
+    return out
+
+
+def reduce_by_index_3d_add_i32(dest, is_, js, ks, vs):
+    dest = _c(dest, np.int32).copy()
+    is_, js, ks, vs = _c(is_, np.int64), _c(js, np.int64), _c(ks, np.int64), _c(vs, np.int32)
+    lib().orc_reduce_by_index_3d_add_i32(_p(dest), dest.shape[0], dest.shape[1], dest.shape[2], _p(is_), _p(js), _p(ks), _p(vs), is_.size)
+    return dest
+
+
+def hist_rows_2d_add_i32(n, m, xss, yss):
+    xss, yss = _c(xss, np.int32), _c(yss, np.int32)
+    out = np.empty((xss.shape[0], n, m), np.int32)
+    lib().orc_hist_rows_2d_add_i32(n, m, _p(xss), _p(yss), xss.shape[0], xss.shape[1], _p(out))
     return out
 
 

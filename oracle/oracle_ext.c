@@ -101,6 +101,26 @@ void orc_reduce_by_index_add_f16(uint16_t *dest, int64_t n, const int16_t *is, c
       dest[is[i]] = orc_float_to_half_trunc(orc_half_to_float(dest[is[i]]) + orc_half_to_float(vs[i]));
 }
 
+/* reduce_by_index_3d dest (+) 0 (zip3 is js ks) vs (prelude/soacs.fut:153-154; tests/hist/hist3d.fut:8-9) */
+void orc_reduce_by_index_3d_add_i32(int32_t *dest, int64_t K, int64_t M, int64_t L, const int64_t *is, const int64_t *js, const int64_t *ks,
+                                    const int32_t *vs, int64_t n) {
+  for (int64_t i = 0; i < n; i++)
+    if (is[i] >= 0 && is[i] < K && js[i] >= 0 && js[i] < M && ks[i] >= 0 && ks[i] < L) {
+      int32_t *d = &dest[(is[i] * M + js[i]) * L + ks[i]];
+      *d = wadd(*d, vs[i]);
+    }
+}
+
+/* tests/hist/segmented_2d.fut:18-24: per row, reduce_by_index_2d of ones over (x, y) pairs into [n][m] zeros */
+void orc_hist_rows_2d_add_i32(int64_t N, int64_t M, const int32_t *xss, const int32_t *yss, int64_t rows, int64_t cols, int32_t *out) {
+  for (int64_t i = 0; i < rows * N * M; i++) out[i] = 0;
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t c = 0; c < cols; c++) {
+      const int64_t x = xss[r * cols + c], y = yss[r * cols + c];
+      if (x >= 0 && x < N && y >= 0 && y < M) out[(r * N + x) * M + y] = wadd(out[(r * N + x) * M + y], 1);
+    }
+}
+
 /* tests/soacs/scan4.fut:11-22, statement by statement */
 static void scan4_step(const int32_t *xs, int64_t n, int32_t *out) {
   int32_t bits_sum = 0;

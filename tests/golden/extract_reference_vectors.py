@@ -51,6 +51,8 @@ FILES = [
     "tests/hist/i16.fut",
     "tests/hist/f16.fut",
     "tests/tokens.fut",
+    "tests/hist/hist3d.fut",
+    "tests/hist/segmented_2d.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f(?:16|32|64)\.nan|f32\.inf|-f32\.inf|true|false|"

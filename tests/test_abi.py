@@ -45,7 +45,7 @@ def test_entry_points_present(lib):
               "hist_max_f32", "filter_u32", "partition_u32", "bmm_f16", "transpose_f32", "transpose_f32_3d",
               "exscan_i32", "mss_i32", "sum_i32_f32", "dotprod_f32", "prod_of_sums_i32", "dotprod_i32", "product_i32",
               "linrec_last_f32", "scan_map2_add_i32", "reduce_by_index_add_f64", "reduce_by_index_add_i8", "reduce_by_index_add_i16",
-              "reduce_by_index_add_f16"):
+              "reduce_by_index_add_f16", "reduce_by_index_3d_add_i32", "hist_rows_2d_add_i32"):
         assert hasattr(lib, "futhark_entry_" + e)
 
 

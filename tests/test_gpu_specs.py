@@ -101,6 +101,16 @@ def test_reference_vector_through_the_flagged_segmented_scan(ctx):
     assert tokens_of(lambda f, v: fb.segscan_f32(ctx, f, v), text) == tokens_of(oracle.segscan_f32, text)
 
 
+def test_reference_vectors_3d_and_per_row_2d_histograms(ctx):
+    c = GOLDEN["tests/hist/hist3d.fut"][0]
+    got = fb.reduce_by_index_3d_add_i32(ctx, np.array(c["input"][0], np.int32), np.array([1, 1], np.int64), np.array([1, -1], np.int64),
+                                        np.array([1, 1], np.int64), np.array([1337, 0], np.int32))
+    assert got.tolist() == c["output"][0]
+    c = GOLDEN["tests/hist/segmented_2d.fut"][0]
+    n, m, xss, yss = c["input"]
+    assert fb.hist_rows_2d_add_i32(ctx, n, m, np.array(xss, np.int32), np.array(yss, np.int32)).tolist() == c["output"][0]
+
+
 # ---- against the oracle on seeded inputs ---------------------------------------------------------
 
 @pytest.mark.parametrize("n", SIZES + BIG)
@@ -227,6 +237,25 @@ def test_reduce_by_index_subword(ctx, t, B):
     if t == "f16":
         assert np.abs(want.view(np.float16).astype(np.float32)).max() < 2048
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("K,M,L,n", [(1, 1, 1, 10), (3, 4, 5, 1000), (17, 33, 65, 200003), (64, 64, 64, 500000)])
+def test_reduce_by_index_3d(ctx, K, M, L, n):
+    is_ = datagen.uniform_i32(91, 0, n, -1, K).astype(np.int64)             # some outside on either side
+    js = datagen.uniform_i32(92, 0, n, -1, M).astype(np.int64)
+    ks = datagen.uniform_i32(93, 0, n, -1, L).astype(np.int64)
+    vs = datagen.uniform_i32(94, 0, n, -2 ** 31, 2 ** 31 - 1)
+    dest = datagen.uniform_i32(95, 0, K * M * L, -2 ** 31, 2 ** 31 - 1).reshape(K, M, L)
+    assert np.array_equal(fb.reduce_by_index_3d_add_i32(ctx, dest, is_, js, ks, vs), oracle.reduce_by_index_3d_add_i32(dest, is_, js, ks, vs))
+
+
+@pytest.mark.parametrize("rows,cols,N,M", [(1, 1, 1, 1), (3, 3, 4, 5), (100, 1000, 7, 9), (7, 100003, 300, 200), (0, 4, 3, 3), (4, 0, 3, 3)])
+def test_hist_rows_2d(ctx, rows, cols, N, M):
+    xss = datagen.uniform_i32(96, 0, rows * cols, -1, N).reshape(rows, cols)
+    yss = datagen.uniform_i32(97, 0, rows * cols, -1, M).reshape(rows, cols)
+    got = fb.hist_rows_2d_add_i32(ctx, N, M, xss, yss)
+    assert got.shape == (rows, N, M)
+    assert np.array_equal(got, oracle.hist_rows_2d_add_i32(N, M, xss, yss))
 
 
 @pytest.mark.parametrize("m,k", [(1, 1), (1, 100), (100, 1), (100, 100), (100001, 3), (3, 100001), (777, 1025), (0, 5), (5, 0)])

@@ -182,6 +182,16 @@ def test_tokens_flagged_segmented_scan_known_answer(c):
     assert s[start:start + length] == c["output"][0]
 
 
+def test_hist3d_and_segmented_2d():
+    c = cases("tests/hist/hist3d.fut")[0]
+    # main of hist3d.fut:8-9: the updates are constants of the program
+    got = oracle.reduce_by_index_3d_add_i32(np.array(c["input"][0], np.int32), [1, 1], [1, -1], [1, 1], [1337, 0])
+    assert got.tolist() == c["output"][0]
+    c = cases("tests/hist/segmented_2d.fut")[0]
+    n, m, xss, yss = c["input"]
+    assert oracle.hist_rows_2d_add_i32(n, m, np.array(xss, np.int32), np.array(yss, np.int32)).tolist() == c["output"][0]
+
+
 def test_definitions_without_reference_values():
     rng = np.random.default_rng(0)
     xs = rng.integers(-1000, 1000, 1000).astype(np.int32)
