@@ -43,12 +43,15 @@ constexpr int64_t HIST_CAP_BINS = 57344;        // 224 KiB / 4
 constexpr uint32_t KEY_NEG_INF = 0x007FFFFFu;   // key of -inf
 
 __device__ __forceinline__ uint32_t f32_key(uint32_t bits) {
-  return bits ^ ((bits >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+  return bits ^ ((uint32_t)((int32_t)bits >> 31) | 0x80000000u);     // a shift and one three-input logic operation
 }
+// Seen through the key, a NaN with the sign bit set lies below -inf (it can never win a maximum) and one
+// without lies above +inf: one comparison on the key finds the only NaNs that matter.
+constexpr uint32_t KEY_POS_INF = 0xFF800000u;
+__device__ __forceinline__ bool key_is_winning_nan(uint32_t key) { return key > KEY_POS_INF; }
 __device__ __forceinline__ uint32_t key_f32(uint32_t key) {
   return (key & 0x80000000u) ? (key ^ 0x80000000u) : ~key;
 }
-__device__ __forceinline__ bool is_nan_bits(uint32_t bits) { return (bits & 0x7FFFFFFFu) > 0x7F800000u; }
 
 template <int OP>
 __device__ __host__ __forceinline__ constexpr uint32_t neutral() {
@@ -103,8 +106,9 @@ __device__ __forceinline__ uint32_t fold_bins(uint32_t a, uint32_t b) {
 template <int OP>
 __device__ __forceinline__ uint32_t prep(uint32_t wbits, bool &skip) {
   if (OP != HOP_MAX_F32) { skip = false; return wbits; }
-  skip = is_nan_bits(wbits);
-  return f32_key(wbits);
+  const uint32_t key = f32_key(wbits);
+  skip = key_is_winning_nan(key);
+  return key;
 }
 
 // One update of a bin range [lo, lo + nb) held in shared memory (nb <= 57344, lo < 2^31).  A
