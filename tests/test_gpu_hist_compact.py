@@ -95,6 +95,28 @@ def test_hist_reference_known_answers(ctx):
     assert int(h.astype(np.int64).sum()) == 499500
 
 
+@pytest.mark.parametrize("B", [7, 65536, 1 << 20])
+def test_hist_max_nans_of_either_sign_and_infinities(ctx, B):
+    # quiet NaNs with and without the sign bit, with payloads, and both infinities: a NaN never wins (fmax drops
+    # it), -inf only where nothing else arrives, +inf always.  (Signalling NaNs are left out: fmaxf answers one
+    # with a quiet NaN, which the next value replaces, so the reference's own result depends on the order.)
+    n = 300007
+    rng = np.random.default_rng(B)
+    bins = rng.integers(0, B, n, dtype=np.int64).astype(np.int32)
+    wf = rng.standard_normal(n).astype(np.float32)
+    bits = wf.view(np.uint32)
+    special = np.array([0x7FC00000, 0xFFC00000, 0x7FC00001, 0xFFC12345, 0x7FFFFFFF, 0xFFFFFFFF, 0x7F800000, 0xFF800000], np.uint32)
+    where = rng.random(n) < 0.3
+    bits[where] = rng.choice(special, int(where.sum()))
+    bins[:8] = 3                                        # a bin that sees nothing but the special values
+    bits[:8] = special
+    got = fb.hist_max_f32(ctx, B, bins, wf)
+    assert np.array_equal(got.view(np.uint32), oracle.hist_max_f32(B, bins, wf).view(np.uint32))
+    only_nans = np.full(100, np.float32(np.nan)); only_nans.view(np.uint32)[::2] = 0xFFC00000
+    got = fb.hist_max_f32(ctx, 4, np.zeros(100, np.int32), only_nans)
+    assert np.array_equal(got, oracle.hist_max_f32(4, np.zeros(100, np.int32), only_nans)) and np.isneginf(got).all()
+
+
 def test_hist_max_nan_negative_indices_and_empty_bins(ctx):
     bins = np.array([0, 0, 1, -1, 7, 2, 2], dtype=np.int32)
     ws = np.array([np.nan, 2.0, np.nan, 9.0, 9.0, -3.5, -1e30], dtype=np.float32)
