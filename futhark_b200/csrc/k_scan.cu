@@ -581,27 +581,44 @@ stream_kernel(const LookbackArgs a) {
       tv_thread = (ITEMS > 32) ? (uint32_t)__popcll((unsigned long long)bits) : (uint32_t)__popc((uint32_t)bits);
     } else {
       // the map body, and the neutral element behind the end of a ragged tile
+      if (!REDO) {                                   // (REDO keeps the elements for the post-operation and maps on the fly)
 #pragma unroll
-      for (int q = 0; q < ITEMS; q++) {
-        if (!REDO) x[q] = S::map(x[q]);              // (REDO keeps the elements for the post-operation and maps on the fly)
-        if (!full && q >= valid) x[q] = Op::kIdentity;
+        for (int q = 0; q < ITEMS; q++) x[q] = S::map(x[q]);
+      }
+      if (!full) {                                   // only the last tile: nothing of this on the common path
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++)
+          if (q >= valid) x[q] = Op::kIdentity;
       }
       if (SEG) {
         // head flags: from the byte array, or computed from the position inside the regular segment
         int64_t pos = 0;
         if (S::kSegRegular) pos = (base + (int64_t)tid * ITEMS) % a.seg_len;
         uint32_t acc = Op::kIdentity, accf = 0;
+        if (is_a) {
+          // only the thread's aggregate is wanted: no record of where the segments start, nothing kept per element
 #pragma unroll
-        for (int q = 0; q < ITEMS; q++) {
-          bool fl;
-          if (S::kSegRegular) { fl = (pos == 0); pos = (pos + 1 == a.seg_len) ? 0 : pos + 1; }
-          else fl = ((fw[q >> 2] >> (8 * (q & 3))) & 0xffu) != 0;
-          if (fl) bits |= (mask_t)1 << q;
-          Op::combine(acc, accf, x[q], fl ? 1u : 0u, acc, accf);
-          x[q] = acc;
+          for (int q = 0; q < ITEMS; q++) {
+            bool fl;
+            if (S::kSegRegular) { fl = (pos == 0); pos = (pos + 1 == a.seg_len) ? 0 : pos + 1; }
+            else fl = ((fw[q >> 2] >> (8 * (q & 3))) & 0xffu) != 0;
+            Op::combine(acc, accf, x[q], fl ? 1u : 0u, acc, accf);
+          }
+          tv_thread = acc;
+          tf_thread = accf;
+        } else {
+#pragma unroll
+          for (int q = 0; q < ITEMS; q++) {
+            bool fl;
+            if (S::kSegRegular) { fl = (pos == 0); pos = (pos + 1 == a.seg_len) ? 0 : pos + 1; }
+            else fl = ((fw[q >> 2] >> (8 * (q & 3))) & 0xffu) != 0;
+            if (fl) bits |= (mask_t)1 << q;
+            Op::combine(acc, accf, x[q], fl ? 1u : 0u, acc, accf);
+            x[q] = acc;
+          }
+          tv_thread = acc;
+          tf_thread = bits ? 1u : 0u;
         }
-        tv_thread = acc;
-        tf_thread = bits ? 1u : 0u;
       } else if (is_a || REDO) {
         uint32_t s = REDO ? S::map(x[0]) : x[0], sf = 0;
         if (REDO && !full && valid < 1) s = Op::kIdentity;
@@ -703,10 +720,18 @@ stream_kernel(const LookbackArgs a) {
         const uint32_t start_f = ((pad_t + tile_true + 3u) & ~3u) + pad_f;     // first rejected key in the buffer
         uint32_t rank = lv;
         const uint32_t first_ord = (uint32_t)tid * ITEMS;
+        if (full) {
 #pragma unroll
-        for (int q = 0; q < ITEMS; q++) {
-          if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
-          else if (PART && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
+          for (int q = 0; q < ITEMS; q++) {
+            if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
+            else if (PART) s_tile[start_f + first_ord + q - rank] = x[q];
+          }
+        } else {                                     // the last tile: keys past the end are not staged
+#pragma unroll
+          for (int q = 0; q < ITEMS; q++) {
+            if ((bits >> q) & 1u) s_tile[pad_t + rank++] = x[q];
+            else if (PART && first_ord + q < (uint32_t)count) s_tile[start_f + first_ord + q - rank] = x[q];
+          }
         }
       }
     }
