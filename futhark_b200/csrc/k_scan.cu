@@ -672,13 +672,14 @@ stream_kernel(const LookbackArgs a) {
         uint32_t pv, pf;
         Op::combine(ev, 0u, lv, lf, pv, pf);
         if (SEG) {
-          // only the elements in front of the thread's first segment start take it
-          const int first = bits ? (__ffs((uint32_t)bits) - 1) : ITEMS;
+          // only the elements in front of the thread's first segment start take it: element q does if no
+          // start lies at or before it (one test of the start bits against a constant mask)
 #pragma unroll
           for (int q = 0; q < ITEMS; q++) {
-            uint32_t ov, of;
-            Op::combine(pv, pf, x[q], 0u, ov, of);
-            if (q < first) x[q] = ov;
+            if (((uint32_t)bits & ((2u << q) - 1u)) == 0u) {
+              uint32_t of;
+              Op::combine(pv, pf, x[q], 0u, x[q], of);
+            }
           }
         } else if (REDO) {
           // fold once more, from the prefix: element q receives post(scan up to q, element q); for
