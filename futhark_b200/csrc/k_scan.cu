@@ -620,15 +620,19 @@ stream_kernel(const LookbackArgs a) {
           tf_thread = bits ? 1u : 0u;
         }
       } else if (is_a || REDO) {
-        uint32_t s = REDO ? S::map(x[0]) : x[0], sf = 0;
-        if (REDO && !full && valid < 1) s = Op::kIdentity;
+        // (a ragged tile is the last one: its test of every element is kept off the common path)
+        auto fold = [&](auto ragged) {
+          uint32_t s = REDO ? S::map(x[0]) : x[0], sf = 0;
+          if (REDO && decltype(ragged)::value && valid < 1) s = Op::kIdentity;
 #pragma unroll
-        for (int q = 1; q < ITEMS; q++) {
-          uint32_t y = REDO ? S::map(x[q]) : x[q];
-          if (REDO && !full && q >= valid) y = Op::kIdentity;
-          Op::combine(s, sf, y, 0u, s, sf);
-        }
-        tv_thread = s;
+          for (int q = 1; q < ITEMS; q++) {
+            uint32_t y = REDO ? S::map(x[q]) : x[q];
+            if (REDO && decltype(ragged)::value && q >= valid) y = Op::kIdentity;
+            Op::combine(s, sf, y, 0u, s, sf);
+          }
+          return s;
+        };
+        tv_thread = (REDO && !full) ? fold(std::true_type{}) : fold(std::false_type{});
       } else {
         uint32_t sf = 0;
 #pragma unroll
@@ -684,14 +688,17 @@ stream_kernel(const LookbackArgs a) {
         } else if (REDO) {
           // fold once more, from the prefix: element q receives post(scan up to q, element q); for
           // an exclusive scan, the scan up to q - 1
-          uint32_t sv = pv, sf = 0;
+          auto refold = [&](auto ragged) {
+            uint32_t sv = pv, sf = 0;
 #pragma unroll
-          for (int q = 0; q < ITEMS; q++) {
-            uint32_t y = S::map(x[q]);
-            if (!full && q >= valid) y = Op::kIdentity;
-            if (S::kExclusive) { const uint32_t o = S::post(sv, x[q]); Op::combine(sv, sf, y, 0u, sv, sf); x[q] = o; }
-            else { Op::combine(sv, sf, y, 0u, sv, sf); x[q] = S::post(sv, x[q]); }
-          }
+            for (int q = 0; q < ITEMS; q++) {
+              uint32_t y = S::map(x[q]);
+              if (decltype(ragged)::value && q >= valid) y = Op::kIdentity;
+              if (S::kExclusive) { const uint32_t o = S::post(sv, x[q]); Op::combine(sv, sf, y, 0u, sv, sf); x[q] = o; }
+              else { Op::combine(sv, sf, y, 0u, sv, sf); x[q] = S::post(sv, x[q]); }
+            }
+          };
+          if (full) refold(std::false_type{}); else refold(std::true_type{});
         } else {
 #pragma unroll
           for (int q = 0; q < ITEMS; q++) { uint32_t of; Op::combine(pv, 0u, x[q], 0u, x[q], of); }
