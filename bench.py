@@ -42,9 +42,9 @@ ROWS, COLS = 131072, 1024
 ELEMS_PER_STEP = 2 * N_SEG + ROWS * COLS          # scan + segmented reduce + row reduce
 ALG_BYTES_SEGSCAN = 9 * N_SEG                      # read 4n + 1n, write 4n
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the segmented-scan kernel, from the
-# ncu capture of a 2^25-element case (profiles/stream_kernel_segscan_f32_2p25.md: 181.9 MB read,
-# 92.5 MB written), scaled by the number of elements; traffic grows in proportion to them.
-NCU_TRAFFIC_SEGSCAN_2P25 = 184.0e6 + 92.2e6
+# ncu capture of a 2^25-element case (profiles/stream_kernel_segscan_f32_2p25.md: 183.9 MB read,
+# 92.8 MB written), scaled by the number of elements; traffic grows in proportion to them.
+NCU_TRAFFIC_SEGSCAN_2P25 = 183.9e6 + 92.8e6
 
 
 def measured_peaks():
