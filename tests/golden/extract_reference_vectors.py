@@ -53,6 +53,7 @@ FILES = [
     "tests/tokens.fut",
     "tests/hist/hist3d.fut",
     "tests/hist/segmented_2d.fut",
+    "tests/segredomap/segsum-nocomm.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f(?:16|32|64)\.nan|f32\.inf|-f32\.inf|true|false|"

@@ -150,6 +150,13 @@ def test_segsum_rows(c):
     assert np.array_equal(oracle.rowsum_f32(xss), np.array(c["output"][0], dtype=np.float32))
 
 
+@pytest.mark.parametrize("c", cases("tests/segredomap/segsum-nocomm.fut"))
+def test_segsum_rows_written_as_a_non_commutative_operator(c):
+    b, xss = c["input"]
+    assert b is True                                                   # add b = (+) for b = true
+    assert np.array_equal(oracle.rowsum_f32(np.array(xss, dtype=np.float32)), np.array(c["output"][0], dtype=np.float32))
+
+
 @pytest.mark.parametrize("c", cases("tests/hist/simple.fut"))
 def test_hist_simple_add_with_out_of_range_and_empties(c):
     dest, image = c["input"]
