@@ -42,6 +42,7 @@ ARRAY_TYPES = {
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
+SEXTUPLE = "opaque_tup6" + "_arr1d_i32" * 6
 
 _lib = None
 
@@ -206,6 +207,11 @@ def load():
     for i in range(3):
         getattr(L, "futhark_project_%s_%d" % (TRIPLE, i)).argtypes = [vp, pvp, vp]
     getattr(L, "futhark_free_" + TRIPLE).argtypes = [vp, vp]
+    L.futhark_entry_partition2_pairs_i32.argtypes = [vp, pvp, vp, vp]
+    for i in range(6):
+        getattr(L, "futhark_project_%s_%d" % (SEXTUPLE, i)).argtypes = [vp, pvp, vp]
+    getattr(L, "futhark_free_" + SEXTUPLE).argtypes = [vp, vp]
+    getattr(L, "futhark_new_" + SEXTUPLE).argtypes = [vp, pvp] + [vp] * 6
     L.futhark_b200_value_error.restype = ctypes.c_char_p
     L.futhark_b200_value_read_mem.argtypes = [vp, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t), ctypes.c_char_p, ci, ctypes.POINTER(HostValue)]
     L.futhark_b200_value_write_mem.argtypes = [ctypes.POINTER(HostValue), ci, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
@@ -546,6 +552,18 @@ class Context:
         self._check(getattr(self.lib, "futhark_free_" + TRIPLE)(self.ptr, obj))
         return parts
 
+    def entry_partition2_pairs_i32(self, xs, ys):
+        """The six arrays (x1, x2, y1, y2, z1, z2) of the three groups (the opaque 6-tuple is projected and freed)."""
+        obj = ctypes.c_void_p()
+        self._check(self.lib.futhark_entry_partition2_pairs_i32(self.ptr, ctypes.byref(obj), xs.ptr, ys.ptr))
+        parts = []
+        for i in range(6):
+            out = ctypes.c_void_p()
+            self._check(getattr(self.lib, "futhark_project_%s_%d" % (SEXTUPLE, i))(self.ptr, ctypes.byref(out), obj))
+            parts.append(Array(self, "i32_1d", out.value))
+        self._check(getattr(self.lib, "futhark_free_" + SEXTUPLE)(self.ptr, obj))
+        return parts
+
     def entry_mss_i32(self, xs):
         out = ctypes.c_int32()
         self._check(self.lib.futhark_entry_mss_i32(self.ptr, ctypes.byref(out), xs.ptr))
@@ -760,6 +778,20 @@ def partition2_i32(ctx, xs):
                 p.free()
     finally:
         a.free()
+
+
+def partition2_pairs_i32(ctx, xs, ys):
+    a, b = ctx.new("i32_1d", xs), ctx.new("i32_1d", ys)
+    try:
+        parts = ctx.entry_partition2_pairs_i32(a, b)
+        try:
+            return tuple(p.values() for p in parts)
+        finally:
+            for p in parts:
+                p.free()
+    finally:
+        a.free()
+        b.free()
 
 
 def hist_op(ctx, op, B, bins, ws):

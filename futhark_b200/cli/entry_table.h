@@ -137,6 +137,22 @@ static const RecordType RECORDS[] = {
        return futhark_new_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **)obj, (const futhark_i32_1d *)f[0]->arr,
                                                                     (const futhark_i32_1d *)f[1]->arr, (const futhark_i32_1d *)f[2]->arr);
      }},
+    {"([]i32, []i32, []i32, []i32, []i32, []i32)", {"[]i32", "[]i32", "[]i32", "[]i32", "[]i32", "[]i32"},
+     [](futhark_context *c, void *o) { return futhark_free_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *)o); },
+     [](futhark_context *c, const void *o, int k, Value &out) {
+       using Project = int (*)(futhark_context *, futhark_i32_1d **, const futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *);
+       static const Project project[6] = {futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_0, futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_1, futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_2,
+                                          futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_3, futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_4, futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_5};
+       futhark_i32_1d *a = nullptr;
+       const int rc = project[k](c, &a, (const futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *)o);
+       if (!rc) set_array(out, "[]i32", a);
+       return rc;
+     },
+     [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
+       return futhark_new_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 **)obj, (const futhark_i32_1d *)f[0]->arr, (const futhark_i32_1d *)f[1]->arr,
+                                (const futhark_i32_1d *)f[2]->arr, (const futhark_i32_1d *)f[3]->arr, (const futhark_i32_1d *)f[4]->arr,
+                                (const futhark_i32_1d *)f[5]->arr);
+     }},
     {"(i32, f32)", {"i32", "f32"},
      [](futhark_context *c, void *o) { return futhark_free_opaque_tup2_i32_f32(c, (futhark_opaque_tup2_i32_f32 *)o); },
      [](futhark_context *c, const void *o, int k, Value &out) {
@@ -279,6 +295,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"reduce_by_index_3d_add_i32", {"[][][]i32", "[]i64", "[]i64", "[]i64", "[]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_reduce_by_index_3d_add_i32(c, &r, FE_IN(0, i32_3d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i64_1d), FE_IN(4, i32_1d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"hist_rows_2d_add_i32", {"i64", "i64", "[][]i32", "[][]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_hist_rows_2d_add_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int64_t>(*in[1]), FE_IN(2, i32_2d), FE_IN(3, i32_2d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"partition2_i32", {"[]i32"}, "([]i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32)", r); return rc; }},
+      {"partition2_pairs_i32", {"[]i32", "[]i32"}, "([]i32, []i32, []i32, []i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_pairs_i32(c, &r, FE_IN(0, i32_1d), FE_IN(1, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32, []i32, []i32, []i32)", r); return rc; }},
       {"replicate_i32", {"i64", "i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_replicate_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int32_t>(*in[1])); if (!rc) set_array(o, "[]i32", r); return rc; }},
       {"iota_i64", {"i64"}, "[]i64", [](C *c, In in, Value &o) { futhark_i64_1d *r = nullptr; int rc = futhark_entry_iota_i64(c, &r, scalar_of<int64_t>(*in[0])); if (!rc) set_array(o, "[]i64", r); return rc; }},
   };

@@ -702,6 +702,87 @@ int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(struct futhark_c
 int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_2(struct futhark_context *ctx, struct futhark_i32_1d **out,
                                                                 const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj) { return project_tup3(ctx, out, obj, 2); }
 
+// partition2 (\(x, y) -> x < y) (\(x, y) -> x == y) (zip xs ys), unzipped (tests/soacs/partition2.fut;
+// prelude/soacs.fut:293-323): one kernel writes the class of every pair as three arrays of keep-flags,
+// and each component of each group is a filter by its flags, so all six arrays keep the original order.
+#define FB_TUP6 futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32
+int futhark_entry_partition2_pairs_i32(struct futhark_context *ctx, struct FB_TUP6 **out0, const struct futhark_i32_1d *in0,
+                                       const struct futhark_i32_1d *in1) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t n = in0->shape[0];
+  if (in1->shape[0] != n) return bad_sizes(ctx);
+  const int64_t pitch = (n + 255) & ~(int64_t)255;          // every flag array starts on a 256-byte boundary
+  memblock_device keep;
+  int rc = fb_alloc(ctx, (size_t)(3 * pitch > 0 ? 3 * pitch : 1), "partition2_pairs_i32.keep", &keep);
+  if (rc != 0) return rc;
+  ctx->launch_count++;
+  rc = fb_cuda_check(ctx, fb::launch_classify_pairs_lt_eq(dptr<int32_t>(in0->mem), dptr<int32_t>(in1->mem), n, pitch, dptr<uint8_t>(keep),
+                                                          ctx->num_sms, ctx->stream), "classify_pairs");
+  futhark_i32_1d *part[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  for (int k = 0; k < 6 && rc == 0; k++) {
+    const futhark_i32_1d *src = (k & 1) ? in1 : in0;
+    rc = compact_common<futhark_i32_1d>(ctx, fb::COMPACT_FILTER_BY_FLAG_I32, false, "partition2_pairs_i32.segscan", src->mem, n,
+                                        dptr<uint8_t>(keep) + (k >> 1) * pitch, &part[k], nullptr);
+  }
+  fb_unref(ctx, &keep);
+  FB_TUP6 *p = rc == 0 ? (FB_TUP6 *)malloc(sizeof(FB_TUP6)) : nullptr;
+  if (p == nullptr) {
+    for (int k = 0; k < 6; k++) if (part[k] != nullptr) { fb_unref(ctx, &part[k]->mem); free(part[k]); }
+    return rc != 0 ? rc : 1;
+  }
+  for (int k = 0; k < 6; k++) p->v[k] = part[k];
+  *out0 = p;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_free_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32(struct futhark_context *ctx, struct FB_TUP6 *obj) {
+  if (obj == nullptr) return 0;
+  for (int i = 0; i < 6; i++) futhark_free_i32_1d(ctx, obj->v[i]);
+  free(obj);
+  return 0;
+}
+
+int futhark_new_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32(
+    struct futhark_context *ctx, struct FB_TUP6 **out, const struct futhark_i32_1d *v0, const struct futhark_i32_1d *v1,
+    const struct futhark_i32_1d *v2, const struct futhark_i32_1d *v3, const struct futhark_i32_1d *v4, const struct futhark_i32_1d *v5) {
+  CtxGuard g(ctx);
+  FB_TUP6 *p = (FB_TUP6 *)malloc(sizeof(FB_TUP6));
+  if (p == nullptr) return 1;
+  const futhark_i32_1d *src[6] = {v0, v1, v2, v3, v4, v5};
+  for (int i = 0; i < 6; i++) {
+    p->v[i] = (futhark_i32_1d *)malloc(sizeof(futhark_i32_1d));
+    if (p->v[i] == nullptr) return 1;
+    *p->v[i] = *src[i];
+    fb_ref(&p->v[i]->mem);         // the record shares the blocks of its fields (docs/c-api.rst:366-381)
+  }
+  *out = p;
+  return 0;
+}
+
+static int project_tup6(futhark_context *ctx, futhark_i32_1d **out, const FB_TUP6 *obj, int i) {
+  CtxGuard g(ctx);
+  futhark_i32_1d *a = (futhark_i32_1d *)malloc(sizeof(futhark_i32_1d));
+  if (a == nullptr) return 1;
+  *a = *obj->v[i];
+  fb_ref(&a->mem);          // the projection shares the block (docs/c-api.rst:383-391)
+  *out = a;
+  return 0;
+}
+#define FB_TUP6_PROJECT(I)                                                                                             \
+  int futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_##I(                     \
+      struct futhark_context *ctx, struct futhark_i32_1d **out, const struct FB_TUP6 *obj) {                           \
+    return project_tup6(ctx, out, obj, I);                                                                             \
+  }
+FB_TUP6_PROJECT(0)
+FB_TUP6_PROJECT(1)
+FB_TUP6_PROJECT(2)
+FB_TUP6_PROJECT(3)
+FB_TUP6_PROJECT(4)
+FB_TUP6_PROJECT(5)
+#undef FB_TUP6_PROJECT
+#undef FB_TUP6
+
 // ---- scans under other specifications of the single-pass kernel -------------------------------------
 }  // extern "C"
 template <typename ARR>

@@ -1034,6 +1034,32 @@ cudaError_t launch_compact(int which, const void *in, const uint8_t *flags, void
   }
 }
 
+// ---- classes of a three-way partition of pairs ----------------------------------------------------
+// partition2 (\(x, y) -> x < y) (\(x, y) -> x == y) (zip xs ys) (tests/soacs/partition2.fut;
+// prelude/soacs.fut:293-323): the class of a pair is written as three keep-flag arrays, `pitch`
+// bytes apart, and each component of each group is then one filter by flags.
+__global__ void __launch_bounds__(256)
+classify_pairs_lt_eq_kernel(const int32_t *__restrict__ xs, const int32_t *__restrict__ ys, int64_t n, int64_t pitch,
+                            uint8_t *__restrict__ keep) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int32_t x = xs[i], y = ys[i];
+    const int cls = x < y ? 0 : (x == y ? 1 : 2);
+    keep[i] = cls == 0;
+    keep[pitch + i] = cls == 1;
+    keep[2 * pitch + i] = cls == 2;
+  }
+}
+
+cudaError_t launch_classify_pairs_lt_eq(const int32_t *xs, const int32_t *ys, int64_t n, int64_t pitch, uint8_t *keep, int num_sms,
+                                        cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  int64_t want = (n + 255) / 256;
+  const int64_t cap = (int64_t)num_sms * 8;
+  classify_pairs_lt_eq_kernel<<<(int)(want < cap ? want : cap), 256, 0, stream>>>(xs, ys, n, pitch, keep);
+  return cudaGetLastError();
+}
+
 // ---- a wait that runs out, on purpose -------------------------------------------------------------
 // One warp waits, as visit B of a tile does, for a status word that nothing will publish
 // under this epoch, with a small poll limit; when the limit is reached it records

@@ -62,6 +62,10 @@ int compact_pieces_needed(int64_t n);
 cudaError_t launch_compact(int which, const void *in, const uint8_t *flags, void *out_true, void *out_false,
                            int64_t n, int64_t *d_count, void *scratch, const uint32_t *epochs, int *failure, cudaStream_t stream);
 
+// keep[c * pitch + i] = 1 if the pair (xs[i], ys[i]) is of class c (0: x < y, 1: x == y, 2: neither), else 0
+cudaError_t launch_classify_pairs_lt_eq(const int32_t *xs, const int32_t *ys, int64_t n, int64_t pitch, uint8_t *keep, int num_sms,
+                                        cudaStream_t stream);
+
 // ---- two-pass scans for 8-byte and tuple operators (k_twopass.cu) ---------------------------
 // `scratch`: the reduce scratch (at least twopass_scratch_bytes()).
 size_t twopass_scratch_bytes();

@@ -159,6 +159,10 @@ struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 {
   futhark_i32_1d *v[3];
 };
 
+struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 {
+  futhark_i32_1d *v[6];
+};
+
 struct futhark_opaque_tup2_i32_f32 {
   int32_t v0;
   float v1;

@@ -17,6 +17,7 @@ ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
+SEXTUPLE = "opaque_tup6" + "_arr1d_i32" * 6
 I32F32 = "opaque_tup2_i32_f32"
 
 
@@ -64,6 +65,7 @@ ENTRIES = {
     "filter_pos_i32": ([("xs", "[]i32")], "[]i32", []),
     "filter_by_flag_i32": ([("xs", "[]i32"), ("keep", "[]bool")], "[]i32", []),
     "partition2_i32": ([("xs", "[]i32")], "([]i32, []i32, []i32)", []),
+    "partition2_pairs_i32": ([("xs", "[]i32"), ("ys", "[]i32")], "([]i32, []i32, []i32, []i32, []i32, []i32)", []),
     "bmm_f16": ([("A", "[][][]f16"), ("B", "[][][]f16")], "[][][]f32", ["bmm_f16.tile_size", "bmm_f16.reg_tile_size"]),
     "transpose_f32": ([("xss", "[][]f32")], "[][]f32", []),
     "transpose_f32_3d": ([("xsss", "[][][]f32")], "[][][]f32", []),
@@ -108,6 +110,12 @@ def build():
         "ops": {"free": "futhark_free_" + TRIPLE},
         "record": {"new": "futhark_new_" + TRIPLE,
                    "fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (TRIPLE, i)} for i in range(3)]},
+    }
+    types["([]i32, []i32, []i32, []i32, []i32, []i32)"] = {
+        "kind": "opaque", "ctype": "struct futhark_%s *" % SEXTUPLE,
+        "ops": {"free": "futhark_free_" + SEXTUPLE},
+        "record": {"new": "futhark_new_" + SEXTUPLE,
+                   "fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (SEXTUPLE, i)} for i in range(6)]},
     }
     entries = {}
     for name, (ins, out, tuning) in ENTRIES.items():

@@ -183,6 +183,29 @@ int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(struct futhark_c
 int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_2(struct futhark_context *ctx, struct futhark_i32_1d **out,
                                                                 const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
 
+/* ---- opaque 6-tuple of i32 arrays returned by partition2_pairs_i32 (same naming rule, the name
+ *      findPrettyName of src/Futhark/CodeGen/Backends/SimpleRep.hs:145-175 gives the type
+ *      ([]i32, []i32, []i32, []i32, []i32, []i32)); same functions as the triple ---------- */
+struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32;
+int futhark_free_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32(
+    struct futhark_context *ctx, struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_new_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32(
+    struct futhark_context *ctx, struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 **out,
+    const struct futhark_i32_1d *v0, const struct futhark_i32_1d *v1, const struct futhark_i32_1d *v2,
+    const struct futhark_i32_1d *v3, const struct futhark_i32_1d *v4, const struct futhark_i32_1d *v5);
+int futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_0(
+    struct futhark_context *ctx, struct futhark_i32_1d **out, const struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_1(
+    struct futhark_context *ctx, struct futhark_i32_1d **out, const struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_2(
+    struct futhark_context *ctx, struct futhark_i32_1d **out, const struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_3(
+    struct futhark_context *ctx, struct futhark_i32_1d **out, const struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_4(
+    struct futhark_context *ctx, struct futhark_i32_1d **out, const struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_5(
+    struct futhark_context *ctx, struct futhark_i32_1d **out, const struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+
 /* ---- opaque tuple (i32, f32) returned by sum_i32_f32: same naming and functions; its
  *      fields are scalars, so `new` takes and the projections return them by value ---------- */
 struct futhark_opaque_tup2_i32_f32;
@@ -392,6 +415,9 @@ int futhark_entry_iota_i64(struct futhark_context *ctx, struct futhark_i64_1d **
  *   (tests/soacs/filter3.fut: the predicate reads a second array)
  * entry partition2_i32 (xs: []i32): ([]i32, []i32, []i32) =
  *   partition2 (\x -> x % 2 == 0) (\x -> x % 3 == 0) xs   (tests/soacs/partition1.fut; prelude/soacs.fut:293-323)
+ * entry partition2_pairs_i32 [n] (xs: [n]i32) (ys: [n]i32): ([]i32, []i32, []i32, []i32, []i32, []i32) =
+ *   main of tests/soacs/partition2.fut:16-21: partition2 (\(x, y) -> x < y) (\(x, y) -> x == y) (zip xs ys),
+ *   each of the three groups unzipped (a three-way partition of an array of tuples)
  * entry scan_map2_add_i32 [m][k] (xss: [m][k]i32): [m][k]i32 = scan (map2 (+)) (replicate k 0) xss
  *   (tests/soacs/scan-with-map.fut, scan5.fut: an operator on whole rows; the scan is interchanged with the
  *   inner map and runs as a regular segmented scan over the transposed array) */
@@ -410,6 +436,9 @@ int futhark_entry_filter_by_flag_i32(struct futhark_context *ctx, struct futhark
 int futhark_entry_partition2_i32(struct futhark_context *ctx,
                                  struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 **out0,
                                  const struct futhark_i32_1d *in0);
+int futhark_entry_partition2_pairs_i32(
+    struct futhark_context *ctx, struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 **out0,
+    const struct futhark_i32_1d *in0, const struct futhark_i32_1d *in1);
 
 /* Scans whose operator works on 8-byte values or on tuples take the two-pass route (three
  * launches: per-block scan, scan of the block carries, carry distribution), as the reference's do

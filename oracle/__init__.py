@@ -70,6 +70,7 @@ def lib():
         L.orc_filter_by_flag_i32.restype = i64
         L.orc_filter_by_flag_i32.argtypes = [vp, vp, i64, vp]
         L.orc_partition2_i32.argtypes = [vp, i64, vp, vp]
+        L.orc_partition2_pairs_i32.argtypes = [vp, vp, i64, vp, vp, vp]
         L.orc_reduce_by_index_32.argtypes = [i32, vp, i64, vp, vp, i64]
         L.orc_hist_rows_add_i32.argtypes = [i64, vp, vp, i64, i64, vp]
         L.orc_reduce_by_index_2d_add_i32.argtypes = [vp, i64, i64, vp, vp, vp, i64]
@@ -448,6 +449,16 @@ def partition2_i32(xs):
     lib().orc_partition2_i32(_p(xs), xs.size, _p(out), _p(counts))
     a, b = int(counts[0]), int(counts[0] + counts[1])
     return out[:a].copy(), out[a:b].copy(), out[b:].copy()
+
+
+def partition2_pairs_i32(xs, ys):
+    """The six arrays of tests/soacs/partition2.fut: (x1, x2, y1, y2, z1, z2)."""
+    xs, ys = _c(xs, np.int32), _c(ys, np.int32)
+    ox, oy = np.empty_like(xs), np.empty_like(ys)
+    counts = np.zeros(3, np.int64)
+    lib().orc_partition2_pairs_i32(_p(xs), _p(ys), xs.size, _p(ox), _p(oy), _p(counts))
+    a, b = int(counts[0]), int(counts[0] + counts[1])
+    return ox[:a].copy(), oy[:a].copy(), ox[a:b].copy(), oy[a:b].copy(), ox[b:].copy(), oy[b:].copy()
 
 
 HIST_OPS = {"add_i32": (0, np.int32, 0), "min_i32": (2, np.int32, 2 ** 31 - 1), "max_i32": (3, np.int32, -2 ** 31),

@@ -162,6 +162,22 @@ void orc_partition2_i32(const int32_t *xs, int64_t n, int32_t *out, int64_t *cou
   memcpy(counts, c, sizeof(c));
 }
 
+/* main of tests/soacs/partition2.fut:16-21: partition2 (x < y) (x == y) over zip xs ys, the three groups
+ * unzipped (prelude/soacs.fut:293-323: a pair goes to the first group whose predicate holds, else to the
+ * third; every group keeps the original order).  outx / outy = the first / second components of
+ * group 0 ++ group 1 ++ group 2; counts[0..2] the group sizes. */
+void orc_partition2_pairs_i32(const int32_t *xs, const int32_t *ys, int64_t n, int32_t *outx, int32_t *outy, int64_t *counts) {
+  int64_t c[3] = {0, 0, 0};
+  for (int64_t i = 0; i < n; i++) c[xs[i] < ys[i] ? 0 : (xs[i] == ys[i] ? 1 : 2)]++;
+  int64_t o[3] = {0, c[0], c[0] + c[1]};
+  for (int64_t i = 0; i < n; i++) {
+    const int64_t at = o[xs[i] < ys[i] ? 0 : (xs[i] == ys[i] ? 1 : 2)]++;
+    outx[at] = xs[i];
+    outy[at] = ys[i];
+  }
+  memcpy(counts, c, sizeof(c));
+}
+
 /* reduce_by_index dest op ne is vs over 32-bit values (prelude/soacs.fut:117-130): dest is updated
  * in place; indices outside [0, B) are ignored.  op: 0 add i32, 2 min i32, 3 max i32, 4 min u32,
  * 5 max u32, 6 and, 7 or, 8 xor, 9 add f32 (sequential order), 10 mul i32 (numbering of the

@@ -20,6 +20,7 @@ FILES = [
     "tests/soacs/reduce0.fut",
     "tests/soacs/filter1.fut",
     "tests/soacs/partition1.fut",
+    "tests/soacs/partition2.fut",
     "tests/soacs/segreduce-iota.fut",
     "tests/hist/simple.fut",
     "tests/hist/max.fut",

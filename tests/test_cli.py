@@ -81,6 +81,7 @@ def test_text_in_text_out(cli):
     assert run(cli, ["-e", "segscan_f32"], b"[true, false, true, false] [1.0, 2.0, 3.0, 4.5]").stdout == b"[1f32, 3f32, 3f32, 7.5f32]\n"
     # the entry points under other specifications, on the reference's own test vectors
     assert run(cli, ["-e", "partition2_i32"], b"[0,1,2,3,4,5,6,7,8,9]").stdout == b"[0i32, 2i32, 4i32, 6i32, 8i32]\n[3i32, 9i32]\n[1i32, 5i32, 7i32]\n"   # tests/soacs/partition1.fut
+    assert run(cli, ["-e", "partition2_pairs_i32"], b"[2,7,1,2,8,9,1,5,0,2] [6,1,0,9,8,7,9,4,2,1]").stdout == b"[2i32, 2i32, 1i32, 0i32]\n[6i32, 9i32, 9i32, 2i32]\n[8i32]\n[8i32]\n[7i32, 1i32, 9i32, 5i32, 2i32]\n[1i32, 0i32, 7i32, 4i32, 1i32]\n"   # tests/soacs/partition2.fut
     assert run(cli, ["-e", "filter_pos_i32"], b"[1,0,2,-5,3,-1]").stdout == b"[1i32, 2i32, 3i32]\n"                                                          # tests/soacs/filter1.fut
     assert run(cli, ["-e", "filter_by_flag_i32"], b"[0, 1, -2, 5, 42] [false, true, true, false, true]").stdout == b"[1i32, -2i32, 42i32]\n"                   # tests/soacs/filter3.fut
     assert run(cli, ["-e", "scanomap_steps_i32"], b"[83, 1, 4, 99, 33, 0, 6, 5]").stdout == b"[4339i32, 4586i32, 4929i32, 5654i32, 6120i32, 6554i32, 7046i32, 7535i32]\n"   # tests/soacs/scan4.fut

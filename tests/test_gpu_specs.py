@@ -35,6 +35,9 @@ def test_reference_vectors_scans_and_compaction(ctx):
         assert [g.tolist() for g in fb.partition2_i32(ctx, np.array(c["input"][0], np.int32))] == c["output"]
     for c in GOLDEN["tests/soacs/scan4.fut"]:
         assert fb.scanomap_steps_i32(ctx, np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+    for c in GOLDEN["tests/soacs/partition2.fut"]:
+        got = fb.partition2_pairs_i32(ctx, np.array(c["input"][0], np.int32), np.array(c["input"][1], np.int32))
+        assert [g.tolist() for g in got] == c["output"]
 
 
 def test_reference_vectors_histograms(ctx):
@@ -138,6 +141,17 @@ def test_filters_and_partition2(ctx, n):
     got, want = fb.partition2_i32(ctx, xs), oracle.partition2_i32(xs)
     assert all(np.array_equal(g, w) for g, w in zip(got, want))
     assert sum(len(g) for g in got) == n
+
+
+@pytest.mark.parametrize("n", [0, 1, 255, 256, 5121, 3 * 5120 + 17] + BIG)
+def test_partition2_of_pairs(ctx, n):
+    xs, ys = datagen.uniform_i32(65, 0, n, -4, 4), datagen.uniform_i32(66, 0, n, -4, 4)
+    got, want = fb.partition2_pairs_i32(ctx, xs, ys), oracle.partition2_pairs_i32(xs, ys)
+    assert len(got) == 6 and all(np.array_equal(g, w) for g, w in zip(got, want))
+    assert len(got[0]) + len(got[2]) + len(got[4]) == n
+    # one class only: the other groups come back empty
+    got = fb.partition2_pairs_i32(ctx, xs, xs)
+    assert np.array_equal(got[2], xs) and np.array_equal(got[3], xs) and all(len(got[k]) == 0 for k in (0, 1, 4, 5))
 
 
 def test_compaction_extremes(ctx):

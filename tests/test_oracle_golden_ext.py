@@ -35,6 +35,12 @@ def test_partition1_three_groups(c):
     assert [g.tolist() for g in got] == c["output"]
 
 
+@pytest.mark.parametrize("c", cases("tests/soacs/partition2.fut"))
+def test_partition2_of_pairs(c):
+    got = oracle.partition2_pairs_i32(np.array(c["input"][0], np.int32), np.array(c["input"][1], np.int32))
+    assert [g.tolist() for g in got] == c["output"]
+
+
 @pytest.mark.parametrize("c", cases("tests/soacs/scan4.fut"))
 def test_scan4_two_rounds(c):
     assert oracle.scanomap_steps_i32(np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
