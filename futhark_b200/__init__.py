@@ -35,6 +35,8 @@ ARRAY_TYPES = {
     "i8_1d": (np.int8, 1, ctypes.c_int8),
     "i16_1d": (np.int16, 1, ctypes.c_int16),
     "f16_1d": (np.uint16, 1, ctypes.c_uint16),
+    "u8_1d": (np.uint8, 1, ctypes.c_uint8),
+    "u16_1d": (np.uint16, 1, ctypes.c_uint16),
     "f32_3d": (np.float32, 3, ctypes.c_float),
     "i32_3d": (np.int32, 3, ctypes.c_int32),
     "f16_3d": (np.uint16, 3, ctypes.c_uint16),
@@ -194,9 +196,10 @@ def load():
     L.futhark_entry_replicate_i32.argtypes = [vp, pvp, i64, ctypes.c_int32]
     L.futhark_entry_iota_i64.argtypes = [vp, pvp, i64]
     L.futhark_entry_linrec_f32.argtypes = [vp, pvp, vp, vp]
-    for name in ("and_i32", "or_i32", "xor_i32", "mul_i32"):
+    for name in ("and_i32", "or_i32", "xor_i32", "mul_i32") + tuple(o + t for o in ("and", "or", "xor") for t in ("_i8", "_i16", "_i64")):
         getattr(L, "futhark_entry_hist_" + name).argtypes = [vp, pvp, i64, vp, vp]
-    for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32", "add_f64"):
+    for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32", "add_f64") + tuple(
+            o + t for o in ("min", "max") for t in ("_i8", "_u8", "_i16", "_u16")):
         getattr(L, "futhark_entry_reduce_by_index_" + name).argtypes = [vp, pvp, vp, vp, vp]
     for name in ("add_i8", "add_i16", "add_f16"):
         getattr(L, "futhark_entry_reduce_by_index_" + name).argtypes = [vp, pvp, vp, vp, vp]
@@ -450,12 +453,13 @@ class Context:
         return self._entry_arr("hist_max_f32", "f32_1d", int(B), bins.ptr, ws.ptr)
 
     def entry_hist_op(self, op, B, bins, ws):
-        """hist <op> <neutral> B (map i64.i32 bins) ws for op in and_i32, or_i32, xor_i32, mul_i32."""
-        return self._entry_arr("hist_" + op, "i32_1d", int(B), bins.ptr, ws.ptr)
+        """hist <op> <neutral> B (map i64.i32 bins) ws for op in and_i32, or_i32, xor_i32, mul_i32, {and,or,xor}_{i8,i16} and
+        {and,or,xor}_i64 (whose values are i32, widened in the kernel)."""
+        return self._entry_arr("hist_" + op, op.split("_")[-1] + "_1d", int(B), bins.ptr, ws.ptr)
 
     def entry_reduce_by_index(self, op, dest, bins, ws):
-        """reduce_by_index dest <op> <neutral> (map i64.i32 bins) ws for op in min_i32, max_i32, min_u32, max_u32, add_f32, add_f64."""
-        return self._entry_arr("reduce_by_index_" + op, op[-3:] + "_1d", dest.ptr, bins.ptr, ws.ptr)
+        """reduce_by_index dest <op> <neutral> (map i64.i32 bins) ws for op in {min,max}_{i32,u32,i8,u8,i16,u16}, add_f32, add_f64."""
+        return self._entry_arr("reduce_by_index_" + op, op.split("_")[-1] + "_1d", dest.ptr, bins.ptr, ws.ptr)
 
     def entry_reduce_by_index_subword(self, t, dest, bins, ws):
         """reduce_by_index dest (+) 0 (map i64.iN bins) ws for t in i8, i16 (indices of the same type) and f16 (i16 indices)."""
@@ -795,11 +799,12 @@ def partition2_pairs_i32(ctx, xs, ys):
 
 
 def hist_op(ctx, op, B, bins, ws):
-    return _run(ctx, [("i32_1d", bins), ("i32_1d", ws)], lambda b, w: ctx.entry_hist_op(op, B, b, w))
+    t = op.split("_")[-1]
+    return _run(ctx, [("i32_1d", bins), (("i32" if t == "i64" else t) + "_1d", ws)], lambda b, w: ctx.entry_hist_op(op, B, b, w))
 
 
 def reduce_by_index(ctx, op, dest, bins, ws):
-    t = op[-3:] + "_1d"
+    t = op.split("_")[-1] + "_1d"
     return _run(ctx, [(t, dest), ("i32_1d", bins), (t, ws)], lambda d, b, w: ctx.entry_reduce_by_index(op, d, b, w))
 
 

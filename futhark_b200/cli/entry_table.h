@@ -57,6 +57,7 @@ static const ArrayType ARRAYS[] = {
     FE_ARRAY(f64, double, 1, "[]f64", "f64"),    FE_ARRAY(i32, int32_t, 2, "[][]i32", "i32"), FE_ARRAY(i64, int64_t, 2, "[][]i64", "i64"),
     FE_ARRAY(bool, bool, 2, "[][]bool", "bool"), FE_ARRAY(i8, int8_t, 1, "[]i8", "i8"), FE_ARRAY(i16, int16_t, 1, "[]i16", "i16"),
     FE_ARRAY(f16, uint16_t, 1, "[]f16", "f16"), FE_ARRAY(i32, int32_t, 3, "[][][]i32", "i32"),
+    FE_ARRAY(u8, uint8_t, 1, "[]u8", "u8"), FE_ARRAY(u16, uint16_t, 1, "[]u16", "u16"),
 };
 inline const ArrayType *array_type(const std::string &name) {
   for (const ArrayType &a : ARRAYS)
@@ -289,6 +290,23 @@ inline const std::vector<EntryPoint> &entry_points() {
       FE_E3(reduce_by_index_add_f32, f32_1d, "[]f32", i32_1d, "[]i32", f32_1d, "[]f32", f32_1d, "[]f32"),
       FE_E3(reduce_by_index_add_f64, f64_1d, "[]f64", i32_1d, "[]i32", f64_1d, "[]f64", f64_1d, "[]f64"),
       FE_E3(reduce_by_index_add_i8, i8_1d, "[]i8", i8_1d, "[]i8", i8_1d, "[]i8", i8_1d, "[]i8"),
+      FE_EH(hist_and_i8, i32_1d, "[]i32", i8_1d, "[]i8", i8_1d, "[]i8"),
+      FE_EH(hist_and_i16, i32_1d, "[]i32", i16_1d, "[]i16", i16_1d, "[]i16"),
+      FE_EH(hist_and_i64, i32_1d, "[]i32", i32_1d, "[]i32", i64_1d, "[]i64"),
+      FE_EH(hist_or_i8, i32_1d, "[]i32", i8_1d, "[]i8", i8_1d, "[]i8"),
+      FE_EH(hist_or_i16, i32_1d, "[]i32", i16_1d, "[]i16", i16_1d, "[]i16"),
+      FE_EH(hist_or_i64, i32_1d, "[]i32", i32_1d, "[]i32", i64_1d, "[]i64"),
+      FE_EH(hist_xor_i8, i32_1d, "[]i32", i8_1d, "[]i8", i8_1d, "[]i8"),
+      FE_EH(hist_xor_i16, i32_1d, "[]i32", i16_1d, "[]i16", i16_1d, "[]i16"),
+      FE_EH(hist_xor_i64, i32_1d, "[]i32", i32_1d, "[]i32", i64_1d, "[]i64"),
+      FE_E3(reduce_by_index_min_i8, i8_1d, "[]i8", i32_1d, "[]i32", i8_1d, "[]i8", i8_1d, "[]i8"),
+      FE_E3(reduce_by_index_min_u8, u8_1d, "[]u8", i32_1d, "[]i32", u8_1d, "[]u8", u8_1d, "[]u8"),
+      FE_E3(reduce_by_index_min_i16, i16_1d, "[]i16", i32_1d, "[]i32", i16_1d, "[]i16", i16_1d, "[]i16"),
+      FE_E3(reduce_by_index_min_u16, u16_1d, "[]u16", i32_1d, "[]i32", u16_1d, "[]u16", u16_1d, "[]u16"),
+      FE_E3(reduce_by_index_max_i8, i8_1d, "[]i8", i32_1d, "[]i32", i8_1d, "[]i8", i8_1d, "[]i8"),
+      FE_E3(reduce_by_index_max_u8, u8_1d, "[]u8", i32_1d, "[]i32", u8_1d, "[]u8", u8_1d, "[]u8"),
+      FE_E3(reduce_by_index_max_i16, i16_1d, "[]i16", i32_1d, "[]i32", i16_1d, "[]i16", i16_1d, "[]i16"),
+      FE_E3(reduce_by_index_max_u16, u16_1d, "[]u16", i32_1d, "[]i32", u16_1d, "[]u16", u16_1d, "[]u16"),
       FE_E3(reduce_by_index_add_i16, i16_1d, "[]i16", i16_1d, "[]i16", i16_1d, "[]i16", i16_1d, "[]i16"),
       FE_E3(reduce_by_index_add_f16, f16_1d, "[]f16", i16_1d, "[]i16", f16_1d, "[]f16", f16_1d, "[]f16"),
       {"reduce_by_index_2d_add_i32", {"[][]i32", "[]i64", "[]i64", "[]i32"}, "[][]i32", [](C *c, In in, Value &o) { futhark_i32_2d *r = nullptr; int rc = futhark_entry_reduce_by_index_2d_add_i32(c, &r, FE_IN(0, i32_2d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i32_1d)); if (!rc) set_array(o, "[][]i32", r); return rc; }},

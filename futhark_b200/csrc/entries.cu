@@ -422,6 +422,92 @@ FB_RBI_SUBWORD_ENTRY(i8, 0, i8_1d, i8_1d, 1)
 FB_RBI_SUBWORD_ENTRY(i16, 1, i16_1d, i16_1d, 2)
 FB_RBI_SUBWORD_ENTRY(f16, 2, f16_1d, i16_1d, 2)
 
+// ---- histograms over 1-, 2- and 8-byte integers with i32 indices ---------------------------------------
+// tests/hist/{and,or,xor}{8,16}.fut, {min,max}{8,16}.fut: compare-and-swap on the containing word
+// (Base.hs:844-905); tests/hist/{and,xor}64.fut: native 64-bit atomics, the i32 values widened in the kernel.
+// dest == NULL: hist op ne B is vs; otherwise reduce_by_index dest op ne is vs.
+static int hist_narrow(futhark_context *ctx, int op, int es, void **out_arr, int64_t B, const memblock_device *dest, const futhark_i32_1d *is,
+                       const memblock_device &vs, int64_t vs_len, const char *name) {
+  const int64_t n = is->shape[0];
+  if (vs_len != n) return bad_sizes(ctx);
+  if (B < 0) {
+    fb_set_error(ctx, "Error: negative histogram size %lld.\n", (long long)B);
+    return FUTHARK_PROGRAM_ERROR;
+  }
+  int rc;
+  futhark_i8_1d *out = make_1d<futhark_i8_1d>(ctx, B, (size_t)es, name, &rc);     // the same layout for every one-dimensional array
+  if (out == nullptr) return rc;
+  if (B > 0) {
+    LaunchScope ls(ctx, name, PROV("hist / reduce_by_index over sub-word integers"), "{" + kv("n", n) + "," + kv("bins", B) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_hist_narrow(op, es, B, dptr<int32_t>(is->mem), dptr<void>(vs), n, dptr<void>(out->mem),
+                                                   dest ? dptr<void>(*dest) : nullptr, ctx->num_sms, ctx->stream), name);
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out_arr = out;
+  return FUTHARK_SUCCESS;
+}
+#define FB_HIST_NARROW_ENTRY(NAME, OP, ARR, ES)                                                                               \
+  int futhark_entry_hist_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0, const int64_t in0,                   \
+                                const struct futhark_i32_1d *in1, const struct futhark_##ARR *in2) {                         \
+    if (!ctx->ready) return not_ready(ctx);                                                                                   \
+    CtxGuard g(ctx);                                                                                                          \
+    void *o = nullptr;                                                                                                        \
+    int rc = hist_narrow(ctx, OP, ES, &o, in0, nullptr, in1, in2->mem, in2->shape[0], "hist_" #NAME ".seghist");              \
+    if (rc == 0) *out0 = (futhark_##ARR *)o;                                                                                  \
+    return rc;                                                                                                                \
+  }
+FB_HIST_NARROW_ENTRY(and_i8, fb::NOP_AND, i8_1d, 1)
+FB_HIST_NARROW_ENTRY(or_i8, fb::NOP_OR, i8_1d, 1)
+FB_HIST_NARROW_ENTRY(xor_i8, fb::NOP_XOR, i8_1d, 1)
+FB_HIST_NARROW_ENTRY(and_i16, fb::NOP_AND, i16_1d, 2)
+FB_HIST_NARROW_ENTRY(or_i16, fb::NOP_OR, i16_1d, 2)
+FB_HIST_NARROW_ENTRY(xor_i16, fb::NOP_XOR, i16_1d, 2)
+#define FB_RBI_NARROW_ENTRY(NAME, OP, ARR, ES)                                                                                \
+  int futhark_entry_reduce_by_index_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0,                          \
+                                           const struct futhark_##ARR *in0, const struct futhark_i32_1d *in1,                 \
+                                           const struct futhark_##ARR *in2) {                                                 \
+    if (!ctx->ready) return not_ready(ctx);                                                                                   \
+    CtxGuard g(ctx);                                                                                                          \
+    void *o = nullptr;                                                                                                        \
+    int rc = hist_narrow(ctx, OP, ES, &o, in0->shape[0], &in0->mem, in1, in2->mem, in2->shape[0],                             \
+                         "reduce_by_index_" #NAME ".seghist");                                                                \
+    if (rc == 0) *out0 = (futhark_##ARR *)o;                                                                                  \
+    return rc;                                                                                                                \
+  }
+FB_RBI_NARROW_ENTRY(min_i8, fb::NOP_MIN_S, i8_1d, 1)
+FB_RBI_NARROW_ENTRY(max_i8, fb::NOP_MAX_S, i8_1d, 1)
+FB_RBI_NARROW_ENTRY(min_u8, fb::NOP_MIN_U, u8_1d, 1)
+FB_RBI_NARROW_ENTRY(max_u8, fb::NOP_MAX_U, u8_1d, 1)
+FB_RBI_NARROW_ENTRY(min_i16, fb::NOP_MIN_S, i16_1d, 2)
+FB_RBI_NARROW_ENTRY(max_i16, fb::NOP_MAX_S, i16_1d, 2)
+FB_RBI_NARROW_ENTRY(min_u16, fb::NOP_MIN_U, u16_1d, 2)
+FB_RBI_NARROW_ENTRY(max_u16, fb::NOP_MAX_U, u16_1d, 2)
+
+#define FB_HIST_I64_ENTRY(NAME, OP)                                                                                           \
+  int futhark_entry_hist_##NAME(struct futhark_context *ctx, struct futhark_i64_1d **out0, const int64_t in0,                  \
+                                const struct futhark_i32_1d *in1, const struct futhark_i32_1d *in2) {                        \
+    if (!ctx->ready) return not_ready(ctx);                                                                                   \
+    CtxGuard g(ctx);                                                                                                          \
+    const int64_t n = in1->shape[0];                                                                                          \
+    if (in2->shape[0] != n) return bad_sizes(ctx);                                                                            \
+    if (in0 < 0) { fb_set_error(ctx, "Error: negative histogram size %lld.\n", (long long)in0); return FUTHARK_PROGRAM_ERROR; } \
+    int rc;                                                                                                                   \
+    futhark_i64_1d *out = make_1d<futhark_i64_1d>(ctx, in0, 8, "hist_" #NAME ".out", &rc);                                    \
+    if (out == nullptr) return rc;                                                                                            \
+    if (in0 > 0) {                                                                                                            \
+      LaunchScope ls(ctx, "hist_" #NAME ".seghist", PROV("hist op ne B (map i64.i32 is) (map i64.i32 vs)"),                   \
+                     "{" + kv("n", n) + "," + kv("bins", (int64_t)in0) + "}");                                                \
+      rc = fb_cuda_check(ctx, fb::launch_hist_bitop_i64(OP, in0, dptr<int32_t>(in1->mem), dptr<int32_t>(in2->mem), n,          \
+                                                        dptr<int64_t>(out->mem), ctx->num_sms, ctx->stream), "hist_" #NAME);   \
+      if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }                                                        \
+    }                                                                                                                         \
+    *out0 = out;                                                                                                              \
+    return FUTHARK_SUCCESS;                                                                                                   \
+  }
+FB_HIST_I64_ENTRY(and_i64, fb::NOP_AND)
+FB_HIST_I64_ENTRY(or_i64, fb::NOP_OR)
+FB_HIST_I64_ENTRY(xor_i64, fb::NOP_XOR)
+
 // map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss (tests/hist/segmented.fut: a SegHist with a
 // segment dimension, SegHist.hs:97-148): one histogram over rows * m bins whose index carries the row.
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const int64_t in0,

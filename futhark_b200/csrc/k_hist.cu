@@ -603,10 +603,12 @@ __global__ void __launch_bounds__(256) hist_global_cas_kernel(const typename S::
   }
 }
 template <class S>
-static cudaError_t launch_hist_cas(int64_t B, const void *bins, const void *vs, int64_t n, void *out, const void *dest, int num_sms, cudaStream_t stream) {
+static cudaError_t launch_hist_cas(int64_t B, const void *bins, const void *vs, int64_t n, void *out, const void *dest, int num_sms, cudaStream_t stream,
+                                   int fill_byte = 0) {      // dest == NULL: every byte of the result starts as fill_byte
   using V = typename S::V;
   if (B <= 0) return cudaSuccess;
-  cudaError_t err = cudaMemcpyAsync(out, dest, (size_t)B * sizeof(V), cudaMemcpyDeviceToDevice, stream);
+  cudaError_t err = dest != nullptr ? cudaMemcpyAsync(out, dest, (size_t)B * sizeof(V), cudaMemcpyDeviceToDevice, stream)
+                                    : cudaMemsetAsync(out, fill_byte, (size_t)B * sizeof(V), stream);
   if (err != cudaSuccess || n <= 0) return err;
   int64_t grid = (n + 255) / 256;
   if (grid > (int64_t)num_sms * 8) grid = (int64_t)num_sms * 8;
@@ -622,6 +624,78 @@ cudaError_t launch_hist_add_subword(int kind, int64_t B, const void *bins, const
     case 1: return launch_hist_cas<SwAddI16>(B, bins, vs, n, out, dest, num_sms, stream);
     default: return launch_hist_cas<SwAddF16>(B, bins, vs, n, out, dest, num_sms, stream);
   }
+}
+
+// ---- 1- and 2-byte integers under min, max, and, or, xor; indices are i32 -----------------------------
+// tests/hist/{min,max,and,or,xor}{8,16}.fut: the same compare-and-swap loop on the containing word under
+// other operators; signed minimum and maximum compare the sign-extended sub-words.
+template <typename VT, int OP>
+struct SwNarrow {
+  using V = VT; using I = int32_t;
+  static __device__ __forceinline__ uint32_t combine(uint32_t cur, uint32_t v) {
+    constexpr int SH = 32 - 8 * (int)sizeof(VT);
+    constexpr uint32_t MASK = 0xffffffffu >> SH;
+    const int32_t sc = (int32_t)(cur << SH) >> SH, sv = (int32_t)(v << SH) >> SH;
+    if (OP == NOP_MIN_S) return (uint32_t)(sv < sc ? sv : sc) & MASK;
+    if (OP == NOP_MAX_S) return (uint32_t)(sv > sc ? sv : sc) & MASK;
+    if (OP == NOP_MIN_U) return v < cur ? v : cur;
+    if (OP == NOP_MAX_U) return v > cur ? v : cur;
+    if (OP == NOP_AND) return cur & v;
+    if (OP == NOP_OR) return cur | v;
+    return cur ^ v;
+  }
+};
+template <typename VT>
+static cudaError_t launch_hist_narrow_t(int op, int64_t B, const void *bins, const void *vs, int64_t n, void *out, const void *dest,
+                                        int num_sms, cudaStream_t stream) {
+  switch (op) {
+    case NOP_MIN_S: return launch_hist_cas<SwNarrow<VT, NOP_MIN_S>>(B, bins, vs, n, out, dest, num_sms, stream);
+    case NOP_MAX_S: return launch_hist_cas<SwNarrow<VT, NOP_MAX_S>>(B, bins, vs, n, out, dest, num_sms, stream);
+    case NOP_MIN_U: return launch_hist_cas<SwNarrow<VT, NOP_MIN_U>>(B, bins, vs, n, out, dest, num_sms, stream);
+    case NOP_MAX_U: return launch_hist_cas<SwNarrow<VT, NOP_MAX_U>>(B, bins, vs, n, out, dest, num_sms, stream);
+    case NOP_AND: return launch_hist_cas<SwNarrow<VT, NOP_AND>>(B, bins, vs, n, out, dest, num_sms, stream, 0xff);
+    case NOP_OR: return launch_hist_cas<SwNarrow<VT, NOP_OR>>(B, bins, vs, n, out, dest, num_sms, stream);
+    case NOP_XOR: return launch_hist_cas<SwNarrow<VT, NOP_XOR>>(B, bins, vs, n, out, dest, num_sms, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+cudaError_t launch_hist_narrow(int op, int elem_bytes, int64_t B, const int32_t *bins, const void *vs, int64_t n, void *out, const void *dest,
+                               int num_sms, cudaStream_t stream) {
+  if (dest == nullptr && op != NOP_AND && op != NOP_OR && op != NOP_XOR) return cudaErrorInvalidValue;
+  if (elem_bytes == 1) return launch_hist_narrow_t<uint8_t>(op, B, bins, vs, n, out, dest, num_sms, stream);
+  if (elem_bytes == 2) return launch_hist_narrow_t<uint16_t>(op, B, bins, vs, n, out, dest, num_sms, stream);
+  return cudaErrorInvalidValue;
+}
+
+// ---- 8-byte integers under and, or, xor, the i32 values widened in the kernel -------------------------
+// hist (i64.&) (-1) n (map i64.i32 is) (map i64.i32 image) (tests/hist/and64.fut, xor64.fut): native 64-bit
+// atomics on the result (Base.hs:720-760), which starts at the operator's neutral element.
+template <int OP>
+__global__ void __launch_bounds__(256) hist_global_bitop_i64_kernel(const int32_t *__restrict__ bins, const int32_t *__restrict__ vs, int64_t n,
+                                                                   int64_t B, unsigned long long *out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int32_t b = bins[i];
+    if (b < 0 || (int64_t)b >= B) continue;
+    const unsigned long long v = (unsigned long long)(long long)vs[i];       // i64.i32 extends the sign
+    if (OP == NOP_AND) atomicAnd(&out[b], v);
+    else if (OP == NOP_OR) atomicOr(&out[b], v);
+    else atomicXor(&out[b], v);
+  }
+}
+cudaError_t launch_hist_bitop_i64(int op, int64_t B, const int32_t *bins, const int32_t *vs, int64_t n, int64_t *out, int num_sms,
+                                  cudaStream_t stream) {
+  if (B <= 0) return cudaSuccess;
+  if (op != NOP_AND && op != NOP_OR && op != NOP_XOR) return cudaErrorInvalidValue;
+  cudaError_t err = cudaMemsetAsync(out, op == NOP_AND ? 0xff : 0x00, (size_t)B * sizeof(int64_t), stream);
+  if (err != cudaSuccess || n <= 0) return err;
+  int64_t grid = (n + 255) / 256;
+  if (grid > (int64_t)num_sms * 8) grid = (int64_t)num_sms * 8;
+  unsigned long long *o = reinterpret_cast<unsigned long long *>(out);
+  if (op == NOP_AND) hist_global_bitop_i64_kernel<NOP_AND><<<(int)grid, 256, 0, stream>>>(bins, vs, n, B, o);
+  else if (op == NOP_OR) hist_global_bitop_i64_kernel<NOP_OR><<<(int)grid, 256, 0, stream>>>(bins, vs, n, B, o);
+  else hist_global_bitop_i64_kernel<NOP_XOR><<<(int)grid, 256, 0, stream>>>(bins, vs, n, B, o);
+  return cudaGetLastError();
 }
 
 }  // namespace fb

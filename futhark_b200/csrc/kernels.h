@@ -111,6 +111,15 @@ enum HistOpKind : int {
 };
 cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
                         const void *dest, int num_sms, cudaStream_t stream);
+// 1- and 2-byte integers (elem_bytes) under an operator of NarrowOp, by compare-and-swap on the containing
+// word; dest == NULL (and, or, xor only): the bins start at the operator's neutral element.  `out` must be
+// readable and writable up to the next multiple of 4 bytes.
+enum NarrowOp : int { NOP_MIN_S = 0, NOP_MAX_S = 1, NOP_MIN_U = 2, NOP_MAX_U = 3, NOP_AND = 4, NOP_OR = 5, NOP_XOR = 6 };
+cudaError_t launch_hist_narrow(int op, int elem_bytes, int64_t B, const int32_t *bins, const void *vs, int64_t n, void *out, const void *dest,
+                               int num_sms, cudaStream_t stream);
+// and / or / xor over i64 bins of sign-extended i32 values, from the neutral element
+cudaError_t launch_hist_bitop_i64(int op, int64_t B, const int32_t *bins, const int32_t *vs, int64_t n, int64_t *out, int num_sms,
+                                  cudaStream_t stream);
 // flat[i] = (is[i] * M + js[i]) * L + ks[i], or -1 out of range: reduce_by_index_3d
 cudaError_t launch_flatten_3d_index(const int64_t *is, const int64_t *js, const int64_t *ks, int64_t n, int64_t K, int64_t M, int64_t L,
                                     int32_t *flat, int num_sms, cudaStream_t stream);

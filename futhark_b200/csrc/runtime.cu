@@ -627,6 +627,8 @@ FB_ARRAY_1D(f64_1d, double)
 FB_ARRAY_1D(i8_1d, int8_t)
 FB_ARRAY_1D(i16_1d, int16_t)
 FB_ARRAY_1D(f16_1d, uint16_t)
+FB_ARRAY_1D(u8_1d, uint8_t)
+FB_ARRAY_1D(u16_1d, uint16_t)
 FB_ARRAY_3D(f32_3d, float)
 FB_ARRAY_3D(i32_3d, int32_t)
 FB_ARRAY_3D(f16_3d, uint16_t)

@@ -146,6 +146,8 @@ FB_DEFINE_ARRAY_STRUCT(f64_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(i8_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(i16_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f16_1d, 1)
+FB_DEFINE_ARRAY_STRUCT(u8_1d, 1)
+FB_DEFINE_ARRAY_STRUCT(u16_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(f32_3d, 3)
 FB_DEFINE_ARRAY_STRUCT(i32_3d, 3)
 FB_DEFINE_ARRAY_STRUCT(f16_3d, 3)

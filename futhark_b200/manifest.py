@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PATH = os.path.join(HERE, "futhark_b200.json")
 
 ELEM = {"i32": "int32_t", "i64": "int64_t", "u32": "uint32_t", "f32": "float", "f64": "double", "bool": "bool", "f16": "uint16_t"}
-ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "f16_1d", "bool_1d", "f32_2d", "i32_2d", "i64_2d", "bool_2d", "f32_3d", "i32_3d", "f16_3d"]
+ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "f16_1d", "u8_1d", "u16_1d", "bool_1d", "f32_2d", "i32_2d", "i64_2d", "bool_2d", "f32_3d", "i32_3d", "f16_3d"]
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
@@ -56,6 +56,11 @@ ENTRIES = {
     "reduce_by_index_add_i8": ([("dest", "[]i8"), ("is", "[]i8"), ("vs", "[]i8")], "[]i8", []),
     "reduce_by_index_add_i16": ([("dest", "[]i16"), ("is", "[]i16"), ("vs", "[]i16")], "[]i16", []),
     "reduce_by_index_add_f16": ([("dest", "[]f16"), ("is", "[]i16"), ("vs", "[]f16")], "[]f16", []),
+    **{"hist_%s_%s" % (o, t): ([("n", "i64"), ("is", "[]i32"), ("vs", "[]" + t)], "[]" + t, [])
+       for o in ("and", "or", "xor") for t in ("i8", "i16")},
+    **{"hist_%s_i64" % o: ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i64", []) for o in ("and", "or", "xor")},
+    **{"reduce_by_index_%s_%s" % (o, t): ([("dest", "[]" + t), ("is", "[]i32"), ("vs", "[]" + t)], "[]" + t, [])
+       for o in ("min", "max") for t in ("i8", "u8", "i16", "u16")},
     "hist_rows_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vss", "[][]i32")], "[][]i32", []),
     "reduce_by_index_2d_add_i32": ([("dest", "[][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("vs", "[]i32")], "[][]i32", []),
     "reduce_by_index_3d_add_i32": ([("dest", "[][][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("ks", "[]i64"), ("vs", "[]i32")], "[][][]i32", []),

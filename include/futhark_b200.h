@@ -141,6 +141,8 @@ FUTHARK_B200_ARRAY_1D(f64_1d, double)
 FUTHARK_B200_ARRAY_1D(i8_1d, int8_t)
 FUTHARK_B200_ARRAY_1D(i16_1d, int16_t)
 FUTHARK_B200_ARRAY_1D(f16_1d, uint16_t)   /* binary16 bit patterns, as for f16_3d */
+FUTHARK_B200_ARRAY_1D(u8_1d, uint8_t)
+FUTHARK_B200_ARRAY_1D(u16_1d, uint16_t)
 FUTHARK_B200_ARRAY_3D(f32_3d, float)
 FUTHARK_B200_ARRAY_3D(i32_3d, int32_t)
 FUTHARK_B200_ARRAY_3D(f16_3d, uint16_t)
@@ -298,6 +300,14 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
  *   1- and 2-byte values have no atomic of their own: a compare-and-swap loop on the 32-bit word that
  *   holds the element (Base.hs:844-905).  f16 values are added as f32 and narrowed by truncation, as
  *   the reference's C code does it (rts/c/scalar_f16.h:16-46, rts/c/half.h:220-228).
+ * entry hist_{and,or,xor}_{i8,i16} (n: i64) (is: []i32) (vs: []t): [n]t = hist (t.&) (-1) n (map i64.i32 is) vs, ...
+ *   (tests/hist/and8.fut, and16.fut, or8.fut, or16.fut, xor8.fut, xor16.fut)
+ * entry reduce_by_index_{min,max}_{i8,u8,i16,u16} (dest: *[n]t) (is: []i32) (vs: []t): [n]t =
+ *   reduce_by_index dest t.min t.highest (map i64.i32 is) vs, ...      (the two results of tests/hist/min8.fut,
+ *   min16.fut, max8.fut, max16.fut; the same compare-and-swap loop, signed operators on the sign-extended sub-word)
+ * entry hist_{and,or,xor}_i64 (n: i64) (is: []i32) (vs: []i32): [n]i64 =
+ *   hist (i64.&) (-1) n (map i64.i32 is) (map i64.i32 vs), ...         (tests/hist/and64.fut, xor64.fut: native
+ *   64-bit atomics on the result, the widening of the values fused into the kernel)
  * entry hist_rows_add_i32 (m: i64) (iss: [][]i32) (vss: [][]i32): [][m]i32 =
  *   map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss           (tests/hist/segmented.fut: the segment
  *   dimension of a SegHist, SegHist.hs:97-148)
@@ -337,6 +347,27 @@ int futhark_entry_reduce_by_index_add_i16(struct futhark_context *ctx, struct fu
 int futhark_entry_reduce_by_index_add_f16(struct futhark_context *ctx, struct futhark_f16_1d **out0,
                                           const struct futhark_f16_1d *in0, const struct futhark_i16_1d *in1,
                                           const struct futhark_f16_1d *in2);
+FUTHARK_B200_HIST_ENTRY(and_i8, i8_1d)
+FUTHARK_B200_HIST_ENTRY(or_i8, i8_1d)
+FUTHARK_B200_HIST_ENTRY(xor_i8, i8_1d)
+FUTHARK_B200_HIST_ENTRY(and_i16, i16_1d)
+FUTHARK_B200_HIST_ENTRY(or_i16, i16_1d)
+FUTHARK_B200_HIST_ENTRY(xor_i16, i16_1d)
+FUTHARK_B200_RBI_ENTRY(min_i8, i8_1d)
+FUTHARK_B200_RBI_ENTRY(max_i8, i8_1d)
+FUTHARK_B200_RBI_ENTRY(min_u8, u8_1d)
+FUTHARK_B200_RBI_ENTRY(max_u8, u8_1d)
+FUTHARK_B200_RBI_ENTRY(min_i16, i16_1d)
+FUTHARK_B200_RBI_ENTRY(max_i16, i16_1d)
+FUTHARK_B200_RBI_ENTRY(min_u16, u16_1d)
+FUTHARK_B200_RBI_ENTRY(max_u16, u16_1d)
+#define FUTHARK_B200_HIST_I64_ENTRY(NAME)                                                           \
+  int futhark_entry_hist_##NAME(struct futhark_context *ctx, struct futhark_i64_1d **out0,          \
+                                const int64_t in0, const struct futhark_i32_1d *in1,               \
+                                const struct futhark_i32_1d *in2);
+FUTHARK_B200_HIST_I64_ENTRY(and_i64)
+FUTHARK_B200_HIST_I64_ENTRY(or_i64)
+FUTHARK_B200_HIST_I64_ENTRY(xor_i64)
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
                                     const int64_t in0, const struct futhark_i32_2d *in1,
                                     const struct futhark_i32_2d *in2);

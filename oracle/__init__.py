@@ -493,6 +493,41 @@ def reduce_by_index_subword(t, dest, is_, vs):
     return dest
 
 
+NARROW_OPS = {"min_i": 0, "max_i": 1, "min_u": 2, "max_u": 3, "and_i": 4, "or_i": 5, "xor_i": 6}
+
+
+def reduce_by_index_narrow(op, dest, is_, vs):
+    """reduce_by_index dest <op> <neutral> (map i64.i32 is) vs for op in {min,max}_{i8,u8,i16,u16}, {and,or,xor}_{i8,i16}."""
+    name, t = op.split("_")
+    dt = np.dtype({"i8": np.int8, "u8": np.uint8, "i16": np.int16, "u16": np.uint16}[t])
+    code = NARROW_OPS[name + "_" + t[0]]
+    signed = np.dtype("int%d" % (8 * dt.itemsize))
+    dest = _c(dest, dt).copy()
+    is_, vs = _c(is_, np.int32), _c(vs, dt)
+    fn = getattr(lib(), "orc_reduce_by_index_narrow%d" % (8 * dt.itemsize))
+    fn.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+    fn(code, _p(dest.view(signed)), dest.size, _p(is_), _p(vs.view(signed)), is_.size)
+    return dest
+
+
+def hist_narrow(op, B, is_, vs):
+    """hist <op> <neutral> B (map i64.i32 is) vs for op in {and,or,xor}_{i8,i16}."""
+    name, t = op.split("_")
+    dt = {"i8": np.int8, "i16": np.int16}[t]
+    return reduce_by_index_narrow(op, np.full(B, -1 if name == "and" else 0, dt), is_, vs)
+
+
+def hist_bitop_i64(op, B, is_, vs):
+    """hist <op> <neutral> B (map i64.i32 is) (map i64.i32 vs) for op in and_i64, or_i64, xor_i64."""
+    name = op.split("_")[0]
+    dest = np.full(B, -1 if name == "and" else 0, np.int64)
+    is_, vs = _c(is_, np.int32), _c(vs, np.int32)
+    fn = lib().orc_hist_bitop_i64
+    fn.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+    fn({"and": 4, "or": 5, "xor": 6}[name], _p(dest), dest.size, _p(is_), _p(vs), is_.size)
+    return dest
+
+
 def float_to_half_trunc(f):
     return int(lib().orc_float_to_half_trunc(float(f)))
 

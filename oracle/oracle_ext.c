@@ -80,6 +80,41 @@ void orc_reduce_by_index_add_i16(int16_t *dest, int64_t n, const int16_t *is, co
     if (is[i] >= 0 && (int64_t)is[i] < n) dest[is[i]] = (int16_t)((uint16_t)dest[is[i]] + (uint16_t)vs[i]);
 }
 
+/* reduce_by_index dest op ne (map i64.i32 is) vs over 1- and 2-byte integers (tests/hist/{min,max,and,or,xor}{8,16}.fut),
+ * sequentially.  op: 0 smin, 1 smax, 2 umin, 3 umax (rts/c/scalar.h:486-505), 4 and, 5 or, 6 xor. */
+#define ORC_RBI_NARROW(NAME, ST, UT)                                                                                      \
+  void NAME(int op, ST *dest, int64_t n, const int32_t *is, const ST *vs, int64_t m) {                                    \
+    for (int64_t i = 0; i < m; i++) {                                                                                     \
+      if (is[i] < 0 || (int64_t)is[i] >= n) continue;                                                                     \
+      const ST a = dest[is[i]], b = vs[i];                                                                                \
+      ST r;                                                                                                               \
+      switch (op) {                                                                                                       \
+        case 0: r = a < b ? a : b; break;                                                                                 \
+        case 1: r = a < b ? b : a; break;                                                                                 \
+        case 2: r = (ST)((UT)a < (UT)b ? (UT)a : (UT)b); break;                                                           \
+        case 3: r = (ST)((UT)a < (UT)b ? (UT)b : (UT)a); break;                                                           \
+        case 4: r = (ST)(a & b); break;                                                                                   \
+        case 5: r = (ST)(a | b); break;                                                                                   \
+        default: r = (ST)(a ^ b); break;                                                                                  \
+      }                                                                                                                   \
+      dest[is[i]] = r;                                                                                                    \
+    }                                                                                                                     \
+  }
+ORC_RBI_NARROW(orc_reduce_by_index_narrow8, int8_t, uint8_t)
+ORC_RBI_NARROW(orc_reduce_by_index_narrow16, int16_t, uint16_t)
+
+/* hist op ne n (map i64.i32 is) (map i64.i32 vs) over i64 (tests/hist/and64.fut, xor64.fut); op: 4 and, 5 or, 6 xor;
+ * dest must hold the neutral element on entry */
+void orc_hist_bitop_i64(int op, int64_t *dest, int64_t n, const int32_t *is, const int32_t *vs, int64_t m) {
+  for (int64_t i = 0; i < m; i++) {
+    if (is[i] < 0 || (int64_t)is[i] >= n) continue;
+    const int64_t v = (int64_t)vs[i];
+    if (op == 4) dest[is[i]] &= v;
+    else if (op == 5) dest[is[i]] |= v;
+    else dest[is[i]] ^= v;
+  }
+}
+
 /* f32 -> binary16 bits the way the reference's C code narrows (rts/c/half.h:220-228: a table lookup whose
  * arithmetic this is): truncation, NaN payloads cut to their top ten bits */
 uint16_t orc_float_to_half_trunc(float f) {

@@ -55,6 +55,18 @@ FILES = [
     "tests/hist/hist3d.fut",
     "tests/hist/segmented_2d.fut",
     "tests/segredomap/segsum-nocomm.fut",
+    "tests/hist/and8.fut",
+    "tests/hist/and16.fut",
+    "tests/hist/and64.fut",
+    "tests/hist/or8.fut",
+    "tests/hist/or16.fut",
+    "tests/hist/xor8.fut",
+    "tests/hist/xor16.fut",
+    "tests/hist/xor64.fut",
+    "tests/hist/min8.fut",
+    "tests/hist/min16.fut",
+    "tests/hist/max8.fut",
+    "tests/hist/max16.fut",
 ]
 
 TOKEN = re.compile(r"\s*(empty\(\[[^\]]*\](?:\[[^\]]*\])*\w+\)|f(?:16|32|64)\.nan|f32\.inf|-f32\.inf|true|false|"

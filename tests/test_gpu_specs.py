@@ -66,6 +66,71 @@ def test_reference_vectors_histograms(ctx):
         assert got.tolist() == c["output"][0]
 
 
+NARROW = {"i8": np.int8, "u8": np.uint8, "i16": np.int16, "u16": np.uint16}
+
+
+def test_reference_vectors_narrow_and_wide_integer_histograms(ctx):
+    for op in ("and", "or", "xor"):
+        for bits in (8, 16):
+            st = NARROW["i%d" % bits]
+            for c in GOLDEN["tests/hist/%s%d.fut" % (op, bits)]:
+                n, is_, image = c["input"]
+                assert fb.hist_op(ctx, "%s_i%d" % (op, bits), n, np.array(is_, np.int32), np.array(image, st)).tolist() == c["output"][0]
+    for op in ("and", "xor"):
+        for c in GOLDEN["tests/hist/%s64.fut" % op]:
+            n, is_, image = c["input"]
+            assert fb.hist_op(ctx, op + "_i64", n, np.array(is_, np.int32), np.array(image, np.int32)).tolist() == c["output"][0]
+    for op in ("min", "max"):
+        for bits in (8, 16):
+            st, ut = NARROW["i%d" % bits], NARROW["u%d" % bits]
+            for c in GOLDEN["tests/hist/%s%d.fut" % (op, bits)]:
+                n, is_, image = c["input"]
+                is_ = np.array(is_, np.int32)
+                assert fb.reduce_by_index(ctx, "%s_i%d" % (op, bits), np.zeros(n, st), is_, np.array(image, st)).tolist() == c["output"][0]
+                got = fb.reduce_by_index(ctx, "%s_u%d" % (op, bits), np.zeros(n, ut), is_, np.array(image, st).view(ut))
+                assert got.view(st).tolist() == c["output"][1]
+
+
+@pytest.mark.parametrize("B", [1, 3, 5, 1000, 70001])
+@pytest.mark.parametrize("t", ["i8", "u8", "i16", "u16"])
+def test_reduce_by_index_narrow_min_max(ctx, t, B):
+    # B not a multiple of 4: the last bins share a word with what lies behind the array
+    n = 200003
+    dt = NARROW[t]
+    info = np.iinfo(dt)
+    bins = datagen.uniform_i32(71, 0, n, -3, B + 3)
+    ws = datagen.uniform_i32(72, 0, n, info.min, info.max).astype(dt)
+    dest = datagen.uniform_i32(73, 0, B, info.min, info.max).astype(dt)
+    for op in ("min", "max"):
+        got = fb.reduce_by_index(ctx, "%s_%s" % (op, t), dest, bins, ws)
+        assert got.dtype == dt and np.array_equal(got, oracle.reduce_by_index_narrow("%s_%s" % (op, t), dest, bins, ws))
+    # every update on one bin: the compare-and-swap loop under full contention
+    hot = np.zeros(n, np.int32)
+    got = fb.reduce_by_index(ctx, "max_" + t, dest, hot, ws)
+    assert np.array_equal(got, oracle.reduce_by_index_narrow("max_" + t, dest, hot, ws))
+
+
+@pytest.mark.parametrize("B", [1, 7, 4099])
+@pytest.mark.parametrize("op", ["and", "or", "xor"])
+def test_hist_bit_operators_narrow_and_i64(ctx, op, B):
+    n = 150001
+    bins = datagen.uniform_i32(74, 0, n, -2, B + 2)
+    for t in ("i8", "i16"):
+        dt = NARROW[t]
+        info = np.iinfo(dt)
+        ws = datagen.uniform_i32(75, 0, n, info.min, info.max).astype(dt)
+        if op == "and":
+            ws |= dt(~0x11)                          # leave some bits standing
+        got = fb.hist_op(ctx, "%s_%s" % (op, t), B, bins, ws)
+        assert got.dtype == dt and np.array_equal(got, oracle.hist_narrow("%s_%s" % (op, t), B, bins, ws))
+    ws = datagen.uniform_i32(76, 0, n, -2 ** 31, 2 ** 31 - 1)
+    if op == "and":
+        ws |= np.int32(~0x01010101)
+    got = fb.hist_op(ctx, op + "_i64", B, bins, ws)
+    assert got.dtype == np.int64 and np.array_equal(got, oracle.hist_bitop_i64(op + "_i64", B, bins, ws))
+    assert fb.hist_op(ctx, op + "_i64", B, bins[:0], ws[:0]).tolist() == [(-1 if op == "and" else 0)] * B
+
+
 def test_reference_vectors_more_types_and_index_spaces(ctx):
     for c in GOLDEN["tests/hist/max64.fut"]:
         n, is_, image = c["input"]

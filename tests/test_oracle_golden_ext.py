@@ -62,6 +62,35 @@ def test_reduce_by_index_min_max_signed_and_unsigned(name, sop, uop):
         assert got_u.view(np.int32).tolist() == c["output"][1]
 
 
+NARROW = {"i8": np.int8, "u8": np.uint8, "i16": np.int16, "u16": np.uint16}
+
+
+@pytest.mark.parametrize("op", ["and", "or", "xor"])
+@pytest.mark.parametrize("bits", [8, 16])
+def test_hist_bit_operators_on_narrow_integers(op, bits):
+    for c in cases("tests/hist/%s%d.fut" % (op, bits)):
+        n, is_, image = c["input"]
+        assert oracle.hist_narrow("%s_i%d" % (op, bits), n, is_, image).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("op", ["and", "xor"])
+def test_hist_bit_operators_on_i64(op):
+    for c in cases("tests/hist/%s64.fut" % op):
+        n, is_, image = c["input"]
+        assert oracle.hist_bitop_i64(op + "_i64", n, is_, image).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("op", ["min", "max"])
+@pytest.mark.parametrize("bits", [8, 16])
+def test_reduce_by_index_min_max_on_narrow_integers(op, bits):
+    st, ut = NARROW["i%d" % bits], NARROW["u%d" % bits]
+    for c in cases("tests/hist/%s%d.fut" % (op, bits)):
+        n, is_, image = c["input"]
+        assert oracle.reduce_by_index_narrow("%s_i%d" % (op, bits), np.zeros(n, st), is_, np.array(image, st)).tolist() == c["output"][0]
+        got_u = oracle.reduce_by_index_narrow("%s_u%d" % (op, bits), np.zeros(n, ut), is_, np.array(image, st).view(ut))
+        assert got_u.view(st).tolist() == c["output"][1]
+
+
 def _f(v):
     return [float("nan") if x == "nan" else float(x) for x in v]
 
