@@ -44,6 +44,7 @@ ARRAY_TYPES = {
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
+PAIR_I32 = "opaque_tup2_arr1d_i32_arr1d_i32"
 SEXTUPLE = "opaque_tup6" + "_arr1d_i32" * 6
 
 _lib = None
@@ -211,6 +212,13 @@ def load():
         getattr(L, "futhark_project_%s_%d" % (TRIPLE, i)).argtypes = [vp, pvp, vp]
     getattr(L, "futhark_free_" + TRIPLE).argtypes = [vp, vp]
     L.futhark_entry_partition2_pairs_i32.argtypes = [vp, pvp, vp, vp]
+    L.futhark_entry_reduce_map2_add_i32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_reduce_by_index_vec_add_i32.argtypes = [vp, pvp, vp, vp, vp]
+    L.futhark_entry_reduce_by_index_minpair_i32.argtypes = [vp, pvp, i64, vp, vp, vp]
+    for i in range(2):
+        getattr(L, "futhark_project_%s_%d" % (PAIR_I32, i)).argtypes = [vp, pvp, vp]
+    getattr(L, "futhark_free_" + PAIR_I32).argtypes = [vp, vp]
+    getattr(L, "futhark_new_" + PAIR_I32).argtypes = [vp, pvp, vp, vp]
     for i in range(6):
         getattr(L, "futhark_project_%s_%d" % (SEXTUPLE, i)).argtypes = [vp, pvp, vp]
     getattr(L, "futhark_free_" + SEXTUPLE).argtypes = [vp, vp]
@@ -556,6 +564,24 @@ class Context:
         self._check(getattr(self.lib, "futhark_free_" + TRIPLE)(self.ptr, obj))
         return parts
 
+    def entry_reduce_map2_add_i32(self, xss):
+        return self._entry_arr("reduce_map2_add_i32", "i32_1d", xss.ptr)
+
+    def entry_reduce_by_index_vec_add_i32(self, dest, is_, vss):
+        return self._entry_arr("reduce_by_index_vec_add_i32", "i32_2d", dest.ptr, is_.ptr, vss.ptr)
+
+    def entry_reduce_by_index_minpair_i32(self, m, is_, vs0, vs1):
+        """The two result arrays (the opaque pair is projected and freed)."""
+        obj = ctypes.c_void_p()
+        self._check(self.lib.futhark_entry_reduce_by_index_minpair_i32(self.ptr, ctypes.byref(obj), int(m), is_.ptr, vs0.ptr, vs1.ptr))
+        parts = []
+        for i in range(2):
+            out = ctypes.c_void_p()
+            self._check(getattr(self.lib, "futhark_project_%s_%d" % (PAIR_I32, i))(self.ptr, ctypes.byref(out), obj))
+            parts.append(Array(self, "i32_1d", out.value))
+        self._check(getattr(self.lib, "futhark_free_" + PAIR_I32)(self.ptr, obj))
+        return parts
+
     def entry_partition2_pairs_i32(self, xs, ys):
         """The six arrays (x1, x2, y1, y2, z1, z2) of the three groups (the opaque 6-tuple is projected and freed)."""
         obj = ctypes.c_void_p()
@@ -782,6 +808,28 @@ def partition2_i32(ctx, xs):
                 p.free()
     finally:
         a.free()
+
+
+def reduce_map2_add_i32(ctx, xss):
+    return _run(ctx, [("i32_2d", xss)], ctx.entry_reduce_map2_add_i32)
+
+
+def reduce_by_index_vec_add_i32(ctx, dest, is_, vss):
+    return _run(ctx, [("i32_2d", dest), ("i64_1d", is_), ("i32_2d", vss)], ctx.entry_reduce_by_index_vec_add_i32)
+
+
+def reduce_by_index_minpair_i32(ctx, m, is_, vs0, vs1):
+    arrs = [ctx.new("i32_1d", a) for a in (is_, vs0, vs1)]
+    try:
+        parts = ctx.entry_reduce_by_index_minpair_i32(m, *arrs)
+        try:
+            return tuple(p.values() for p in parts)
+        finally:
+            for p in parts:
+                p.free()
+    finally:
+        for a in arrs:
+            a.free()
 
 
 def partition2_pairs_i32(ctx, xs, ys):

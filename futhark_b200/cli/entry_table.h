@@ -123,6 +123,18 @@ static const RecordType RECORDS[] = {
      [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
        return futhark_new_opaque_tup2_arr1d_u32_arr1d_u32(c, (futhark_opaque_tup2_arr1d_u32_arr1d_u32 **)obj, (const futhark_u32_1d *)f[0]->arr, (const futhark_u32_1d *)f[1]->arr);
      }},
+    {"([]i32, []i32)", {"[]i32", "[]i32"},
+     [](futhark_context *c, void *o) { return futhark_free_opaque_tup2_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup2_arr1d_i32_arr1d_i32 *)o); },
+     [](futhark_context *c, const void *o, int k, Value &out) {
+       futhark_i32_1d *a = nullptr;
+       const auto *obj = (const futhark_opaque_tup2_arr1d_i32_arr1d_i32 *)o;
+       const int rc = k == 0 ? futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_0(c, &a, obj) : futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_1(c, &a, obj);
+       if (!rc) set_array(out, "[]i32", a);
+       return rc;
+     },
+     [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
+       return futhark_new_opaque_tup2_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup2_arr1d_i32_arr1d_i32 **)obj, (const futhark_i32_1d *)f[0]->arr, (const futhark_i32_1d *)f[1]->arr);
+     }},
     {"([]i32, []i32, []i32)", {"[]i32", "[]i32", "[]i32"},
      [](futhark_context *c, void *o) { return futhark_free_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *)o); },
      [](futhark_context *c, const void *o, int k, Value &out) {
@@ -313,6 +325,9 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"reduce_by_index_3d_add_i32", {"[][][]i32", "[]i64", "[]i64", "[]i64", "[]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_reduce_by_index_3d_add_i32(c, &r, FE_IN(0, i32_3d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i64_1d), FE_IN(4, i32_1d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"hist_rows_2d_add_i32", {"i64", "i64", "[][]i32", "[][]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_hist_rows_2d_add_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int64_t>(*in[1]), FE_IN(2, i32_2d), FE_IN(3, i32_2d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"partition2_i32", {"[]i32"}, "([]i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32)", r); return rc; }},
+      FE_E1(reduce_map2_add_i32, i32_2d, "[][]i32", i32_1d, "[]i32"),
+      FE_E3(reduce_by_index_vec_add_i32, i32_2d, "[][]i32", i64_1d, "[]i64", i32_2d, "[][]i32", i32_2d, "[][]i32"),
+      {"reduce_by_index_minpair_i32", {"i64", "[]i32", "[]i32", "[]i32"}, "([]i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup2_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_reduce_by_index_minpair_i32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_1d), FE_IN(2, i32_1d), FE_IN(3, i32_1d)); if (!rc) set_record(o, "([]i32, []i32)", r); return rc; }},
       {"partition2_pairs_i32", {"[]i32", "[]i32"}, "([]i32, []i32, []i32, []i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_pairs_i32(c, &r, FE_IN(0, i32_1d), FE_IN(1, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32, []i32, []i32, []i32)", r); return rc; }},
       {"replicate_i32", {"i64", "i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_replicate_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int32_t>(*in[1])); if (!rc) set_array(o, "[]i32", r); return rc; }},
       {"iota_i64", {"i64"}, "[]i64", [](C *c, In in, Value &o) { futhark_i64_1d *r = nullptr; int rc = futhark_entry_iota_i64(c, &r, scalar_of<int64_t>(*in[0])); if (!rc) set_array(o, "[]i64", r); return rc; }},

@@ -508,6 +508,129 @@ FB_HIST_I64_ENTRY(and_i64, fb::NOP_AND)
 FB_HIST_I64_ENTRY(or_i64, fb::NOP_OR)
 FB_HIST_I64_ENTRY(xor_i64, fb::NOP_XOR)
 
+// reduce_by_index xs (map2 (+)) (replicate m 0) is vss (tests/hist/array.fut, array_novec.fut): the bins are
+// rows; one histogram over n * m bins behind a kernel that spreads every row index over its m elements
+int futhark_entry_reduce_by_index_vec_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const struct futhark_i32_2d *in0,
+                                              const struct futhark_i64_1d *in1, const struct futhark_i32_2d *in2) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t N = in0->shape[0], M = in0->shape[1], k = in1->shape[0];
+  if (in2->shape[0] != k || in2->shape[1] != M) return bad_sizes(ctx);
+  if (N * M >= (1ll << 31)) { fb_set_error(ctx, "reduce_by_index_vec_add_i32: %lld bins exceed 2^31-1.", (long long)(N * M)); return 1; }
+  memblock_device flat;
+  int rc = fb_alloc(ctx, (size_t)(k * M) * 4, "reduce_by_index_vec.flat_index", &flat);
+  if (rc != 0) return rc;
+  void *o = nullptr;
+  ctx->launch_count++;
+  rc = fb_cuda_check(ctx, fb::launch_flatten_vec_index(dptr<int64_t>(in1->mem), k, N, M, dptr<int32_t>(flat), ctx->num_sms, ctx->stream),
+                     "flatten_vec_index");
+  if (rc == 0) rc = hist_launch(ctx, fb::HOP_ADD_I32, &o, N * M, &in0->mem, dptr<int32_t>(flat), k * M, in2->mem, k * M, "reduce_by_index_vec_add_i32.seghist");
+  fb_unref(ctx, &flat);
+  if (rc != 0) return rc;
+  futhark_i32_1d *h = (futhark_i32_1d *)o;
+  futhark_i32_2d *out = (futhark_i32_2d *)malloc(sizeof(futhark_i32_2d));
+  if (out == nullptr) { fb_unref(ctx, &h->mem); free(h); return 1; }
+  out->mem = h->mem; out->shape[0] = N; out->shape[1] = M;
+  free(h);
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
+// main of tests/hist/tuple_partial.fut:24-28: reduce_by_index (replicate m (-1, -1)) operator (-1, -1) (map i64.i32 is)
+// (zip vs0 vs1), unzipped; the operator keeps the pair with the smaller first component.  A pair is one 64-bit
+// word updated by compare-and-swap (the reference takes a lock per bin for such an operator, Base.hs:769-842).
+int futhark_entry_reduce_by_index_minpair_i32(struct futhark_context *ctx, struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 **out0, const int64_t in0,
+                                              const struct futhark_i32_1d *in1, const struct futhark_i32_1d *in2,
+                                              const struct futhark_i32_1d *in3) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t B = in0, n = in1->shape[0];
+  if (in2->shape[0] != n || in3->shape[0] != n) return bad_sizes(ctx);
+  if (B < 0) { fb_set_error(ctx, "Error: negative histogram size %lld.\n", (long long)B); return FUTHARK_PROGRAM_ERROR; }
+  int rc;
+  futhark_i32_1d *a = make_1d<futhark_i32_1d>(ctx, B, 4, "reduce_by_index_minpair_i32.out0", &rc);
+  if (a == nullptr) return rc;
+  futhark_i32_1d *b = make_1d<futhark_i32_1d>(ctx, B, 4, "reduce_by_index_minpair_i32.out1", &rc);
+  if (b == nullptr) { fb_unref(ctx, &a->mem); free(a); return rc; }
+  auto *p = (futhark_opaque_tup2_arr1d_i32_arr1d_i32 *)malloc(sizeof(futhark_opaque_tup2_arr1d_i32_arr1d_i32));
+  memblock_device packed;
+  rc = p == nullptr ? 1 : fb_alloc(ctx, (size_t)(B > 0 ? B : 1) * 8, "reduce_by_index_minpair_i32.packed", &packed);
+  if (rc == 0) {
+    if (B > 0) {
+      LaunchScope ls(ctx, "reduce_by_index_minpair_i32.seghist", PROV("reduce_by_index dest op (-1, -1) is (zip vs0 vs1)"),
+                     "{" + kv("n", n) + "," + kv("bins", B) + "}");
+      ctx->launch_count += 1;
+      rc = fb_cuda_check(ctx, fb::launch_hist_minpair_i32(B, dptr<int32_t>(in1->mem), dptr<int32_t>(in2->mem), dptr<int32_t>(in3->mem), n,
+                                                          dptr<void>(packed), dptr<int32_t>(a->mem), dptr<int32_t>(b->mem), ctx->num_sms, ctx->stream),
+                         "reduce_by_index_minpair_i32");
+    }
+    fb_unref(ctx, &packed);
+  }
+  if (rc != 0) {
+    fb_unref(ctx, &a->mem); free(a);
+    fb_unref(ctx, &b->mem); free(b);
+    free(p);
+    return rc;
+  }
+  p->v[0] = a; p->v[1] = b;
+  *out0 = p;
+  return FUTHARK_SUCCESS;
+}
+
+int futhark_free_opaque_tup2_arr1d_i32_arr1d_i32(struct futhark_context *ctx, struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj) {
+  if (obj == nullptr) return 0;
+  for (int i = 0; i < 2; i++) futhark_free_i32_1d(ctx, obj->v[i]);
+  free(obj);
+  return 0;
+}
+int futhark_new_opaque_tup2_arr1d_i32_arr1d_i32(struct futhark_context *ctx, struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 **out,
+                                                const struct futhark_i32_1d *v0, const struct futhark_i32_1d *v1) {
+  CtxGuard g(ctx);
+  auto *p = (futhark_opaque_tup2_arr1d_i32_arr1d_i32 *)malloc(sizeof(futhark_opaque_tup2_arr1d_i32_arr1d_i32));
+  if (p == nullptr) return 1;
+  const futhark_i32_1d *src[2] = {v0, v1};
+  for (int i = 0; i < 2; i++) {
+    p->v[i] = (futhark_i32_1d *)malloc(sizeof(futhark_i32_1d));
+    if (p->v[i] == nullptr) return 1;
+    *p->v[i] = *src[i];
+    fb_ref(&p->v[i]->mem);         // the record shares the blocks of its fields (docs/c-api.rst:366-381)
+  }
+  *out = p;
+  return 0;
+}
+static int project_tup2_i32(futhark_context *ctx, futhark_i32_1d **out, const futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj, int i) {
+  CtxGuard g(ctx);
+  futhark_i32_1d *a = (futhark_i32_1d *)malloc(sizeof(futhark_i32_1d));
+  if (a == nullptr) return 1;
+  *a = *obj->v[i];
+  fb_ref(&a->mem);          // the projection shares the block (docs/c-api.rst:383-391)
+  *out = a;
+  return 0;
+}
+int futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_0(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj) { return project_tup2_i32(ctx, out, obj, 0); }
+int futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_1(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj) { return project_tup2_i32(ctx, out, obj, 1); }
+
+// reduce (map2 (+)) (replicate m 0) xss (tests/soacs/reduce4.fut, reduce5.fut): an operator on whole rows; the
+// reduction is interchanged with the inner map (src/Futhark/Transform/ISRWIM.hs) and every column reduced
+int futhark_entry_reduce_map2_add_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_2d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t rows = in0->shape[0], cols = in0->shape[1];
+  int rc;
+  futhark_i32_1d *out = make_1d<futhark_i32_1d>(ctx, cols, 4, "reduce_map2_add_i32.out", &rc);
+  if (out == nullptr) return rc;
+  if (cols > 0) {
+    LaunchScope ls(ctx, "reduce_map2_add_i32.segred", PROV("reduce (map2 (+)) (replicate m 0) xss"), "{" + kv("rows", rows) + "," + kv("cols", cols) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_colsum_i32(dptr<int32_t>(in0->mem), rows, cols, dptr<int32_t>(out->mem), ctx->num_sms, ctx->stream),
+                       "reduce_map2_add_i32");
+    if (rc != 0) { fb_unref(ctx, &out->mem); free(out); return rc; }
+  }
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
 // map2 (\is vs -> hist (+) 0 m (map i64.i32 is) vs) iss vss (tests/hist/segmented.fut: a SegHist with a
 // segment dimension, SegHist.hs:97-148): one histogram over rows * m bins whose index carries the row.
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0, const int64_t in0,

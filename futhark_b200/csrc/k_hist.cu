@@ -698,4 +698,71 @@ cudaError_t launch_hist_bitop_i64(int op, int64_t B, const int32_t *bins, const 
   return cudaGetLastError();
 }
 
+// ---- a vectorised operator: every bin is a row of `m` values ----------------------------------------------
+// reduce_by_index xs (map2 (+)) (replicate m 0) is vss (tests/hist/array.fut; HistOp's operator shape,
+// src/Futhark/IR/SegOp.hs:102-115): the update of row is[i] by the vector vss[i] is m scalar updates, so it is
+// one histogram over n * m bins whose indices this kernel writes: flat[i * m + j] = is[i] * m + j, or -1.
+__global__ void __launch_bounds__(256)
+flatten_vec_index_kernel(const int64_t *__restrict__ is, int64_t k, int64_t n, int64_t m, int32_t *__restrict__ flat) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x, total = k * m;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int64_t i = t / m, j = t - i * m, b = is[i];
+    flat[t] = (b >= 0 && b < n) ? (int32_t)(b * m + j) : -1;
+  }
+}
+cudaError_t launch_flatten_vec_index(const int64_t *is, int64_t k, int64_t n, int64_t m, int32_t *flat, int num_sms, cudaStream_t stream) {
+  if (k * m <= 0) return cudaSuccess;
+  flatten_vec_index_kernel<<<grid_for(k * m, 256, num_sms * 8), 256, 0, stream>>>(is, k, n, m, flat);
+  return cudaGetLastError();
+}
+
+// ---- an operator on pairs: the smaller first component wins and carries its second along ----------------
+// tests/hist/tuple_partial.fut:19-22: op (x0, y0) (x1, y1) = if x0 != -1 && (x1 == -1 || x0 < x1) then (x0, y0)
+// else (x1, y1), neutral (-1, -1).  The reference guards such an update with a lock per bin
+// (atomicUpdateLocking, Base.hs:769-842); here a pair is one 64-bit word, updated by compare-and-swap, and
+// the two result arrays are written from the words afterwards.  Where two updates of a bin have equal first
+// components the operator keeps its right operand, so, as in the reference, the order decides.
+__global__ void __launch_bounds__(256)
+hist_minpair_kernel(const int32_t *__restrict__ bins, const int32_t *__restrict__ v0, const int32_t *__restrict__ v1, int64_t n, int64_t B,
+                    unsigned long long *__restrict__ packed) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int32_t b = bins[i];
+    if (b < 0 || (int64_t)b >= B) continue;
+    const int32_t x1 = v0[i];
+    const unsigned long long mine = ((unsigned long long)(uint32_t)x1 << 32) | (uint32_t)v1[i];
+    unsigned long long old = *reinterpret_cast<volatile unsigned long long *>(&packed[b]), assumed;
+    do {
+      assumed = old;
+      const int32_t x0 = (int32_t)(uint32_t)(assumed >> 32);
+      if (x0 != -1 && (x1 == -1 || x0 < x1)) break;                 // the bin keeps what it has
+      old = atomicCAS(&packed[b], assumed, mine);
+    } while (old != assumed);
+  }
+}
+__global__ void __launch_bounds__(256) unpack_pairs_kernel(const unsigned long long *__restrict__ packed, int64_t B, int32_t *__restrict__ out0,
+                                                          int32_t *__restrict__ out1) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < B; b += stride) {
+    const unsigned long long w = packed[b];
+    out0[b] = (int32_t)(uint32_t)(w >> 32);
+    out1[b] = (int32_t)(uint32_t)w;
+  }
+}
+// `packed`: B 8-byte words of scratch
+cudaError_t launch_hist_minpair_i32(int64_t B, const int32_t *bins, const int32_t *v0, const int32_t *v1, int64_t n, void *packed, int32_t *out0,
+                                    int32_t *out1, int num_sms, cudaStream_t stream) {
+  if (B <= 0) return cudaSuccess;
+  unsigned long long *p = reinterpret_cast<unsigned long long *>(packed);
+  cudaError_t err = cudaMemsetAsync(p, 0xff, (size_t)B * 8, stream);          // (-1, -1) everywhere
+  if (err != cudaSuccess) return err;
+  if (n > 0) {
+    hist_minpair_kernel<<<grid_for(n, 256, num_sms * 8), 256, 0, stream>>>(bins, v0, v1, n, B, p);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+  }
+  unpack_pairs_kernel<<<grid_for(B, 256, num_sms * 8), 256, 0, stream>>>(p, B, out0, out1);
+  return cudaGetLastError();
+}
+
 }  // namespace fb

@@ -111,6 +111,42 @@ cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void
   return cudaGetLastError();
 }
 
+// ---- reduce (map2 (+)) (replicate cols 0) over the rows of [rows][cols] i32 -------------------------
+// A reduction whose operator works on whole rows (tests/soacs/reduce4.fut, reduce5.fut) is interchanged
+// with the inner map (src/Futhark/Transform/ISRWIM.hs, irwim): every column is reduced on its own.  A thread
+// owns a column over a band of rows, so a warp reads 128 consecutive bytes of every row; the bands of a
+// column meet in one atomic addition each (integer addition wraps: any order gives the same bits).
+__global__ void __launch_bounds__(RED_THREADS)
+colsum_i32_kernel(const int32_t *__restrict__ in, int64_t rows, int64_t cols, int64_t band, int32_t *__restrict__ out) {
+  const int64_t c = (int64_t)blockIdx.x * RED_THREADS + threadIdx.x;
+  if (c >= cols) return;
+  const int64_t r0 = (int64_t)blockIdx.y * band, r1 = r0 + band < rows ? r0 + band : rows;
+  uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+  int64_t r = r0;
+  for (; r + 3 < r1; r += 4) {
+    a0 += (uint32_t)in[r * cols + c];
+    a1 += (uint32_t)in[(r + 1) * cols + c];
+    a2 += (uint32_t)in[(r + 2) * cols + c];
+    a3 += (uint32_t)in[(r + 3) * cols + c];
+  }
+  for (; r < r1; r++) a0 += (uint32_t)in[r * cols + c];
+  atomicAdd(reinterpret_cast<uint32_t *>(out) + c, a0 + a1 + a2 + a3);
+}
+cudaError_t launch_colsum_i32(const int32_t *in, int64_t rows, int64_t cols, int32_t *out, int num_sms, cudaStream_t stream) {
+  if (cols <= 0) return cudaSuccess;
+  cudaError_t err = cudaMemsetAsync(out, 0, (size_t)cols * sizeof(int32_t), stream);     // the neutral element
+  if (err != cudaSuccess || rows <= 0) return err;
+  const int64_t col_blocks = (cols + RED_THREADS - 1) / RED_THREADS;
+  int64_t bands = ((int64_t)num_sms * 8 + col_blocks - 1) / col_blocks;                   // enough CTAs to fill the GPU
+  if (bands > (rows + 7) / 8) bands = (rows + 7) / 8;                                     // at least 8 rows per band
+  if (bands > 65535) bands = 65535;
+  if (bands < 1) bands = 1;
+  const int64_t band = (rows + bands - 1) / bands;
+  if (col_blocks > 2147483647) return cudaErrorInvalidValue;
+  colsum_i32_kernel<<<dim3((unsigned)col_blocks, (unsigned)((rows + band - 1) / band)), RED_THREADS, 0, stream>>>(in, rows, cols, band, out);
+  return cudaGetLastError();
+}
+
 // ---- map (reduce (+) 0) over the rows of [rows][cols] f32 -------------------------------
 // One warp per row (persistent, grid-stride over rows): lane l adds the 16-byte
 // vectors l, l+32, ... of the row into four running sums, then a shuffle tree.

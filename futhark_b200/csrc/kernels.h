@@ -88,6 +88,9 @@ cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float
 cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
                                  void *scratch, int *failure, int num_sms, cudaStream_t stream);
 
+// out[c] = sum over the rows of in[r][c] (wrapping): a reduction with an operator on whole rows
+cudaError_t launch_colsum_i32(const int32_t *in, int64_t rows, int64_t cols, int32_t *out, int num_sms, cudaStream_t stream);
+
 // ---- fused redomaps (k_redomap.cu; the kernel template is redomap.cuh) -----------------------
 // `scratch` as for the reductions.  mss: d_out4 receives the operator's 4-tuple (best segment
 // sum first).  sum_i32_f32: d_out2 receives {i32 sum, f32 sum of the converted elements}.
@@ -111,6 +114,11 @@ enum HistOpKind : int {
 };
 cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weights, int64_t n, void *out,
                         const void *dest, int num_sms, cudaStream_t stream);
+// flat[i * m + j] = is[i] * m + j, or -1 where is[i] is outside [0, n): a histogram whose bins are rows of m values
+cudaError_t launch_flatten_vec_index(const int64_t *is, int64_t k, int64_t n, int64_t m, int32_t *flat, int num_sms, cudaStream_t stream);
+// the minimum of the first components carrying the second along, neutral (-1, -1); `packed`: B 8-byte words
+cudaError_t launch_hist_minpair_i32(int64_t B, const int32_t *bins, const int32_t *v0, const int32_t *v1, int64_t n, void *packed, int32_t *out0,
+                                    int32_t *out1, int num_sms, cudaStream_t stream);
 // 1- and 2-byte integers (elem_bytes) under an operator of NarrowOp, by compare-and-swap on the containing
 // word; dest == NULL (and, or, xor only): the bins start at the operator's neutral element.  `out` must be
 // readable and writable up to the next multiple of 4 bytes.

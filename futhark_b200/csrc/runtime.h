@@ -161,6 +161,10 @@ struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 {
   futhark_i32_1d *v[3];
 };
 
+struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 {
+  futhark_i32_1d *v[2];
+};
+
 struct futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 {
   futhark_i32_1d *v[6];
 };

@@ -17,6 +17,7 @@ ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
+PAIR_I32 = "opaque_tup2_arr1d_i32_arr1d_i32"
 SEXTUPLE = "opaque_tup6" + "_arr1d_i32" * 6
 I32F32 = "opaque_tup2_i32_f32"
 
@@ -61,6 +62,9 @@ ENTRIES = {
     **{"hist_%s_i64" % o: ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i64", []) for o in ("and", "or", "xor")},
     **{"reduce_by_index_%s_%s" % (o, t): ([("dest", "[]" + t), ("is", "[]i32"), ("vs", "[]" + t)], "[]" + t, [])
        for o in ("min", "max") for t in ("i8", "u8", "i16", "u16")},
+    "reduce_by_index_vec_add_i32": ([("xs", "[][]i32"), ("is", "[]i64"), ("vss", "[][]i32")], "[][]i32", []),
+    "reduce_by_index_minpair_i32": ([("m", "i64"), ("is", "[]i32"), ("vs0", "[]i32"), ("vs1", "[]i32")], "([]i32, []i32)", []),
+    "reduce_map2_add_i32": ([("xss", "[][]i32")], "[]i32", []),
     "hist_rows_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vss", "[][]i32")], "[][]i32", []),
     "reduce_by_index_2d_add_i32": ([("dest", "[][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("vs", "[]i32")], "[][]i32", []),
     "reduce_by_index_3d_add_i32": ([("dest", "[][][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("ks", "[]i64"), ("vs", "[]i32")], "[][][]i32", []),
@@ -121,6 +125,12 @@ def build():
         "ops": {"free": "futhark_free_" + SEXTUPLE},
         "record": {"new": "futhark_new_" + SEXTUPLE,
                    "fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (SEXTUPLE, i)} for i in range(6)]},
+    }
+    types["([]i32, []i32)"] = {
+        "kind": "opaque", "ctype": "struct futhark_%s *" % PAIR_I32,
+        "ops": {"free": "futhark_free_" + PAIR_I32},
+        "record": {"new": "futhark_new_" + PAIR_I32,
+                   "fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (PAIR_I32, i)} for i in range(2)]},
     }
     entries = {}
     for name, (ins, out, tuning) in ENTRIES.items():

@@ -185,6 +185,18 @@ int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(struct futhark_c
 int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_2(struct futhark_context *ctx, struct futhark_i32_1d **out,
                                                                 const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
 
+/* ---- opaque pair of i32 arrays returned by reduce_by_index_minpair_i32 (same naming rule and functions) ---------- */
+struct futhark_opaque_tup2_arr1d_i32_arr1d_i32;
+int futhark_free_opaque_tup2_arr1d_i32_arr1d_i32(struct futhark_context *ctx,
+                                                 struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj);
+int futhark_new_opaque_tup2_arr1d_i32_arr1d_i32(struct futhark_context *ctx,
+                                                struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 **out,
+                                                const struct futhark_i32_1d *v0, const struct futhark_i32_1d *v1);
+int futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_0(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj);
+int futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_1(struct futhark_context *ctx, struct futhark_i32_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj);
+
 /* ---- opaque 6-tuple of i32 arrays returned by partition2_pairs_i32 (same naming rule, the name
  *      findPrettyName of src/Futhark/CodeGen/Backends/SimpleRep.hs:145-175 gives the type
  *      ([]i32, []i32, []i32, []i32, []i32, []i32)); same functions as the triple ---------- */
@@ -261,6 +273,12 @@ int futhark_entry_segreduce_f32(struct futhark_context *ctx, struct futhark_f32_
 int futhark_entry_rowsum_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0,
                              const struct futhark_f32_2d *in0);
 
+/* entry reduce_map2_add_i32 [n][m] (xss: [n][m]i32): [m]i32 = reduce_comm (map2 (+)) (replicate m 0) xss
+ * (tests/soacs/reduce4.fut, reduce5.fut: a reduction whose operator works on whole rows; it is interchanged
+ * with the inner map, src/Futhark/Transform/ISRWIM.hs, and every column is reduced on its own). */
+int futhark_entry_reduce_map2_add_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0,
+                                      const struct futhark_i32_2d *in0);
+
 /* entry hist_add_i32 (B: i64) (is: []i32) (ws: []i32): [B]i32
  *   = hist (+) 0 B (map i64.i32 is) ws            (prelude/soacs.fut:132-133)
  * entry hist_max_f32 (B: i64) (is: []i32) (ws: []f32): [B]f32
@@ -305,6 +323,13 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
  * entry reduce_by_index_{min,max}_{i8,u8,i16,u16} (dest: *[n]t) (is: []i32) (vs: []t): [n]t =
  *   reduce_by_index dest t.min t.highest (map i64.i32 is) vs, ...      (the two results of tests/hist/min8.fut,
  *   min16.fut, max8.fut, max16.fut; the same compare-and-swap loop, signed operators on the sign-extended sub-word)
+ * entry reduce_by_index_vec_add_i32 [n][m][k] (xs: *[n][m]i32) (is: [k]i64) (vss: [k][m]i32): [n][m]i32 =
+ *   reduce_by_index xs (map2 (+)) (replicate m 0) is vss               (tests/hist/array.fut, array_novec.fut: the
+ *   bins are rows, HistOp's operator shape, src/Futhark/IR/SegOp.hs:102-115; one histogram over n * m bins)
+ * entry reduce_by_index_minpair_i32 (m: i64) (is: []i32) (vs0: []i32) (vs1: []i32): ([m]i32, [m]i32) =
+ *   main of tests/hist/tuple_partial.fut:24-28: an operator on pairs (the smaller first component wins and
+ *   carries its second along; neutral (-1, -1)).  The reference locks the bin (Base.hs:769-842); here the
+ *   pair is one 64-bit word updated by compare-and-swap.
  * entry hist_{and,or,xor}_i64 (n: i64) (is: []i32) (vs: []i32): [n]i64 =
  *   hist (i64.&) (-1) n (map i64.i32 is) (map i64.i32 vs), ...         (tests/hist/and64.fut, xor64.fut: native
  *   64-bit atomics on the result, the widening of the values fused into the kernel)
@@ -368,6 +393,13 @@ FUTHARK_B200_RBI_ENTRY(max_u16, u16_1d)
 FUTHARK_B200_HIST_I64_ENTRY(and_i64)
 FUTHARK_B200_HIST_I64_ENTRY(or_i64)
 FUTHARK_B200_HIST_I64_ENTRY(xor_i64)
+int futhark_entry_reduce_by_index_vec_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
+                                              const struct futhark_i32_2d *in0, const struct futhark_i64_1d *in1,
+                                              const struct futhark_i32_2d *in2);
+int futhark_entry_reduce_by_index_minpair_i32(struct futhark_context *ctx,
+                                              struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 **out0,
+                                              const int64_t in0, const struct futhark_i32_1d *in1,
+                                              const struct futhark_i32_1d *in2, const struct futhark_i32_1d *in3);
 int futhark_entry_hist_rows_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
                                     const int64_t in0, const struct futhark_i32_2d *in1,
                                     const struct futhark_i32_2d *in2);

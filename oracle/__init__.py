@@ -528,6 +528,36 @@ def hist_bitop_i64(op, B, is_, vs):
     return dest
 
 
+def _fn(name, *argtypes):
+    fn = getattr(lib(), name)
+    fn.argtypes = list(argtypes)
+    return fn
+
+
+def reduce_by_index_vec_add_i32(dest, is_, vss):
+    dest = _c(dest, np.int32).copy()
+    is_, vss = _c(is_, np.int64), _c(vss, np.int32)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    _fn("orc_reduce_by_index_vec_add_i32", vp, i64, i64, vp, vp, i64)(_p(dest), dest.shape[0], dest.shape[1], _p(is_), _p(vss), is_.size)
+    return dest
+
+
+def reduce_by_index_minpair_i32(m, is_, vs0, vs1):
+    is_, vs0, vs1 = _c(is_, np.int32), _c(vs0, np.int32), _c(vs1, np.int32)
+    out0, out1 = np.empty(m, np.int32), np.empty(m, np.int32)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    _fn("orc_reduce_by_index_minpair_i32", vp, vp, i64, vp, vp, vp, i64)(_p(out0), _p(out1), m, _p(is_), _p(vs0), _p(vs1), is_.size)
+    return out0, out1
+
+
+def reduce_map2_add_i32(xss):
+    xss = _c(xss, np.int32)
+    out = np.empty(xss.shape[1], np.int32)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    _fn("orc_reduce_map2_add_i32", vp, i64, i64, vp)(_p(xss), xss.shape[0], xss.shape[1], _p(out))
+    return out
+
+
 def float_to_half_trunc(f):
     return int(lib().orc_float_to_half_trunc(float(f)))
 

@@ -103,6 +103,33 @@ void orc_reduce_by_index_add_i16(int16_t *dest, int64_t n, const int16_t *is, co
 ORC_RBI_NARROW(orc_reduce_by_index_narrow8, int8_t, uint8_t)
 ORC_RBI_NARROW(orc_reduce_by_index_narrow16, int16_t, uint16_t)
 
+/* reduce_by_index xs (map2 (+)) (replicate m 0) is vss (tests/hist/array.fut:6-11): the bins are rows of m values */
+void orc_reduce_by_index_vec_add_i32(int32_t *dest, int64_t n, int64_t m, const int64_t *is, const int32_t *vss, int64_t k) {
+  for (int64_t i = 0; i < k; i++) {
+    if (is[i] < 0 || is[i] >= n) continue;
+    for (int64_t j = 0; j < m; j++) dest[is[i] * m + j] = (int32_t)((uint32_t)dest[is[i] * m + j] + (uint32_t)vss[i * m + j]);
+  }
+}
+
+/* tests/hist/tuple_partial.fut:19-28: dest[b] = operator dest[b] (vs0[i], vs1[i]) in the order of the input, from
+ * (-1, -1); operator (x0, y0) (x1, y1) = if x0 != -1 && (x1 == -1 || x0 < x1) then (x0, y0) else (x1, y1) */
+void orc_reduce_by_index_minpair_i32(int32_t *out0, int32_t *out1, int64_t m, const int32_t *is, const int32_t *vs0, const int32_t *vs1,
+                                     int64_t n) {
+  for (int64_t b = 0; b < m; b++) { out0[b] = -1; out1[b] = -1; }
+  for (int64_t i = 0; i < n; i++) {
+    if (is[i] < 0 || (int64_t)is[i] >= m) continue;
+    const int32_t x0 = out0[is[i]], x1 = vs0[i];
+    if (!(x0 != -1 && (x1 == -1 || x0 < x1))) { out0[is[i]] = x1; out1[is[i]] = vs1[i]; }
+  }
+}
+
+/* reduce_comm (map2 (+)) (replicate m 0) xss (tests/soacs/reduce4.fut:6-7): column sums, wrapping */
+void orc_reduce_map2_add_i32(const int32_t *xss, int64_t rows, int64_t cols, int32_t *out) {
+  for (int64_t c = 0; c < cols; c++) out[c] = 0;
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t c = 0; c < cols; c++) out[c] = (int32_t)((uint32_t)out[c] + (uint32_t)xss[r * cols + c]);
+}
+
 /* hist op ne n (map i64.i32 is) (map i64.i32 vs) over i64 (tests/hist/and64.fut, xor64.fut); op: 4 and, 5 or, 6 xor;
  * dest must hold the neutral element on entry */
 void orc_hist_bitop_i64(int op, int64_t *dest, int64_t n, const int32_t *is, const int32_t *vs, int64_t m) {

@@ -55,6 +55,11 @@ FILES = [
     "tests/hist/hist3d.fut",
     "tests/hist/segmented_2d.fut",
     "tests/segredomap/segsum-nocomm.fut",
+    "tests/hist/array.fut",
+    "tests/hist/array_novec.fut",
+    "tests/hist/tuple_partial.fut",
+    "tests/soacs/reduce4.fut",
+    "tests/soacs/reduce5.fut",
     "tests/hist/and8.fut",
     "tests/hist/and16.fut",
     "tests/hist/and64.fut",

@@ -82,6 +82,10 @@ def test_text_in_text_out(cli):
     # the entry points under other specifications, on the reference's own test vectors
     assert run(cli, ["-e", "partition2_i32"], b"[0,1,2,3,4,5,6,7,8,9]").stdout == b"[0i32, 2i32, 4i32, 6i32, 8i32]\n[3i32, 9i32]\n[1i32, 5i32, 7i32]\n"   # tests/soacs/partition1.fut
     assert run(cli, ["-e", "partition2_pairs_i32"], b"[2,7,1,2,8,9,1,5,0,2] [6,1,0,9,8,7,9,4,2,1]").stdout == b"[2i32, 2i32, 1i32, 0i32]\n[6i32, 9i32, 9i32, 2i32]\n[8i32]\n[8i32]\n[7i32, 1i32, 9i32, 5i32, 2i32]\n[1i32, 0i32, 7i32, 4i32, 1i32]\n"   # tests/soacs/partition2.fut
+    assert run(cli, ["-e", "reduce_map2_add_i32"], b"[[1,2],[3,4],[5,6]]").stdout == b"[9i32, 12i32]\n"                                                        # tests/soacs/reduce4.fut
+    assert run(cli, ["-e", "reduce_by_index_minpair_i32"], b"5i64 [1, 3, 1] [4, 1, 3] [5, 6, 7]").stdout == b"[-1i32, 3i32, -1i32, 1i32, -1i32]\n[-1i32, 7i32, -1i32, 6i32, -1i32]\n"   # tests/hist/tuple_partial.fut
+    assert run(cli, ["-e", "reduce_by_index_vec_add_i32"], b"[[1,2,3],[4,5,6]] [0i64,0i64,2i64,1i64] [[0,1,2],[0,1,2],[0,1,2],[0,1,2]]").stdout == b"[[1i32, 4i32, 7i32], [4i32, 6i32, 8i32]]\n"   # tests/hist/array.fut
+    assert run(cli, ["-e", "hist_xor_i8"], b"5i64 [0, 0, 0, 0, 0] [6i8, 1i8, 4i8, 5i8, -1i8]").stdout == b"[-7i8, 0i8, 0i8, 0i8, 0i8]\n"                          # tests/hist/xor8.fut
     assert run(cli, ["-e", "filter_pos_i32"], b"[1,0,2,-5,3,-1]").stdout == b"[1i32, 2i32, 3i32]\n"                                                          # tests/soacs/filter1.fut
     assert run(cli, ["-e", "filter_by_flag_i32"], b"[0, 1, -2, 5, 42] [false, true, true, false, true]").stdout == b"[1i32, -2i32, 42i32]\n"                   # tests/soacs/filter3.fut
     assert run(cli, ["-e", "scanomap_steps_i32"], b"[83, 1, 4, 99, 33, 0, 6, 5]").stdout == b"[4339i32, 4586i32, 4929i32, 5654i32, 6120i32, 6554i32, 7046i32, 7535i32]\n"   # tests/soacs/scan4.fut

@@ -91,6 +91,49 @@ def test_reference_vectors_narrow_and_wide_integer_histograms(ctx):
                 assert got.view(st).tolist() == c["output"][1]
 
 
+def test_reference_vectors_row_bins_pair_operator_row_operator(ctx):
+    for name in ("tests/hist/array.fut", "tests/hist/array_novec.fut"):
+        for c in GOLDEN[name]:
+            xs, image = c["input"]
+            m = len(xs[0])
+            vss = np.tile(np.arange(m, dtype=np.int32), (len(image), 1))
+            assert fb.reduce_by_index_vec_add_i32(ctx, np.array(xs, np.int32), np.array(image, np.int64), vss).tolist() == c["output"][0]
+    for c in GOLDEN["tests/hist/tuple_partial.fut"]:
+        m, is_, vs0, vs1 = c["input"]
+        got = fb.reduce_by_index_minpair_i32(ctx, m, np.array(is_, np.int32), np.array(vs0, np.int32), np.array(vs1, np.int32))
+        assert [g.tolist() for g in got] == c["output"]
+    for name in ("tests/soacs/reduce4.fut", "tests/soacs/reduce5.fut"):
+        for c in GOLDEN[name]:
+            assert fb.reduce_map2_add_i32(ctx, np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("n,m,k", [(1, 1, 1), (3, 5, 0), (0, 4, 7), (17, 3, 4000), (300, 129, 50001), (5, 70000, 37)])
+def test_reduce_by_index_rows_as_bins(ctx, n, m, k):
+    dest = datagen.uniform_i32(81, 0, n * m, -1000, 1000).reshape(n, m)
+    is_ = datagen.uniform_i32(82, 0, k, -2, n + 1).astype(np.int64)
+    vss = datagen.uniform_i32(83, 0, k * m, -2 ** 31, 2 ** 31 - 1).reshape(k, m)
+    got = fb.reduce_by_index_vec_add_i32(ctx, dest, is_, vss)
+    assert got.shape == (n, m) and np.array_equal(got, oracle.reduce_by_index_vec_add_i32(dest, is_, vss))
+
+
+@pytest.mark.parametrize("m,n", [(1, 1), (5, 0), (1, 100000), (1000, 300001), (200000, 100003)])
+def test_reduce_by_index_pair_operator(ctx, m, n):
+    is_ = datagen.uniform_i32(84, 0, n, -2, m + 1)
+    # first components are distinct (a permutation), so no two updates of a bin tie and the order cannot matter;
+    # -1, the neutral element's first component, appears among them
+    vs0 = (np.random.default_rng(85).permutation(n) - 1).astype(np.int32)
+    vs1 = datagen.uniform_i32(86, 0, n, -2 ** 31, 2 ** 31 - 1)
+    got, want = fb.reduce_by_index_minpair_i32(ctx, m, is_, vs0, vs1), oracle.reduce_by_index_minpair_i32(m, is_, vs0, vs1)
+    assert all(np.array_equal(g, w) for g, w in zip(got, want))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (0, 5), (7, 0), (3, 2), (100000, 3), (1000, 1000), (9, 100003), (40001, 257)])
+def test_reduce_with_row_operator(ctx, rows, cols):
+    xss = datagen.uniform_i32(87, 0, rows * cols, -2 ** 31, 2 ** 31 - 1).reshape(rows, cols)
+    got = fb.reduce_map2_add_i32(ctx, xss)
+    assert got.shape == (cols,) and np.array_equal(got, oracle.reduce_map2_add_i32(xss))
+
+
 @pytest.mark.parametrize("B", [1, 3, 5, 1000, 70001])
 @pytest.mark.parametrize("t", ["i8", "u8", "i16", "u16"])
 def test_reduce_by_index_narrow_min_max(ctx, t, B):

@@ -62,6 +62,28 @@ def test_reduce_by_index_min_max_signed_and_unsigned(name, sop, uop):
         assert got_u.view(np.int32).tolist() == c["output"][1]
 
 
+@pytest.mark.parametrize("name", ["tests/hist/array.fut", "tests/hist/array_novec.fut"])
+def test_reduce_by_index_with_rows_as_bins(name):
+    for c in cases(name):
+        xs, image = c["input"]
+        m = len(xs[0])
+        vss = np.tile(np.arange(m, dtype=np.int32), (len(image), 1))           # replicate k (map i32.i64 (iota m))
+        assert oracle.reduce_by_index_vec_add_i32(np.array(xs, np.int32), image, vss).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/tuple_partial.fut"))
+def test_reduce_by_index_with_an_operator_on_pairs(c):
+    m, is_, vs0, vs1 = c["input"]
+    got = oracle.reduce_by_index_minpair_i32(m, is_, vs0, vs1)
+    assert [g.tolist() for g in got] == c["output"]
+
+
+@pytest.mark.parametrize("name", ["tests/soacs/reduce4.fut", "tests/soacs/reduce5.fut"])
+def test_reduce_with_an_operator_on_rows(name):
+    for c in cases(name):
+        assert oracle.reduce_map2_add_i32(np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
+
+
 NARROW = {"i8": np.int8, "u8": np.uint8, "i16": np.int16, "u16": np.uint16}
 
 
