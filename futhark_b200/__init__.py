@@ -197,7 +197,7 @@ def load():
     L.futhark_entry_replicate_i32.argtypes = [vp, pvp, i64, ctypes.c_int32]
     L.futhark_entry_iota_i64.argtypes = [vp, pvp, i64]
     L.futhark_entry_linrec_f32.argtypes = [vp, pvp, vp, vp]
-    for name in ("and_i32", "or_i32", "xor_i32", "mul_i32") + tuple(o + t for o in ("and", "or", "xor") for t in ("_i8", "_i16", "_i64")):
+    for name in ("and_i32", "or_i32", "xor_i32", "mul_i32") + tuple(o + t for o in ("and", "or", "xor") for t in ("_i8", "_i16", "_i64")) + ("or_bool",):
         getattr(L, "futhark_entry_hist_" + name).argtypes = [vp, pvp, i64, vp, vp]
     for name in ("min_i32", "max_i32", "min_u32", "max_u32", "add_f32", "add_f64") + tuple(
             o + t for o in ("min", "max") for t in ("_i8", "_u8", "_i16", "_u16")):

@@ -302,6 +302,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       FE_E3(reduce_by_index_add_f32, f32_1d, "[]f32", i32_1d, "[]i32", f32_1d, "[]f32", f32_1d, "[]f32"),
       FE_E3(reduce_by_index_add_f64, f64_1d, "[]f64", i32_1d, "[]i32", f64_1d, "[]f64", f64_1d, "[]f64"),
       FE_E3(reduce_by_index_add_i8, i8_1d, "[]i8", i8_1d, "[]i8", i8_1d, "[]i8", i8_1d, "[]i8"),
+      FE_EH(hist_or_bool, i32_1d, "[]i32", bool_1d, "[]bool", bool_1d, "[]bool"),
       FE_EH(hist_and_i8, i32_1d, "[]i32", i8_1d, "[]i8", i8_1d, "[]i8"),
       FE_EH(hist_and_i16, i32_1d, "[]i32", i16_1d, "[]i16", i16_1d, "[]i16"),
       FE_EH(hist_and_i64, i32_1d, "[]i32", i32_1d, "[]i32", i64_1d, "[]i64"),

@@ -462,6 +462,7 @@ FB_HIST_NARROW_ENTRY(xor_i8, fb::NOP_XOR, i8_1d, 1)
 FB_HIST_NARROW_ENTRY(and_i16, fb::NOP_AND, i16_1d, 2)
 FB_HIST_NARROW_ENTRY(or_i16, fb::NOP_OR, i16_1d, 2)
 FB_HIST_NARROW_ENTRY(xor_i16, fb::NOP_XOR, i16_1d, 2)
+FB_HIST_NARROW_ENTRY(or_bool, fb::NOP_OR, bool_1d, 1)      // hist (||) false (tests/hist/lor.fut): a bool is one byte holding 0 or 1
 #define FB_RBI_NARROW_ENTRY(NAME, OP, ARR, ES)                                                                                \
   int futhark_entry_reduce_by_index_##NAME(struct futhark_context *ctx, struct futhark_##ARR **out0,                          \
                                            const struct futhark_##ARR *in0, const struct futhark_i32_1d *in1,                 \

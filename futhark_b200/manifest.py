@@ -59,6 +59,7 @@ ENTRIES = {
     "reduce_by_index_add_f16": ([("dest", "[]f16"), ("is", "[]i16"), ("vs", "[]f16")], "[]f16", []),
     **{"hist_%s_%s" % (o, t): ([("n", "i64"), ("is", "[]i32"), ("vs", "[]" + t)], "[]" + t, [])
        for o in ("and", "or", "xor") for t in ("i8", "i16")},
+    "hist_or_bool": ([("n", "i64"), ("is", "[]i32"), ("vs", "[]bool")], "[]bool", []),
     **{"hist_%s_i64" % o: ([("n", "i64"), ("is", "[]i32"), ("vs", "[]i32")], "[]i64", []) for o in ("and", "or", "xor")},
     **{"reduce_by_index_%s_%s" % (o, t): ([("dest", "[]" + t), ("is", "[]i32"), ("vs", "[]" + t)], "[]" + t, [])
        for o in ("min", "max") for t in ("i8", "u8", "i16", "u16")},

@@ -320,6 +320,7 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
  *   the reference's C code does it (rts/c/scalar_f16.h:16-46, rts/c/half.h:220-228).
  * entry hist_{and,or,xor}_{i8,i16} (n: i64) (is: []i32) (vs: []t): [n]t = hist (t.&) (-1) n (map i64.i32 is) vs, ...
  *   (tests/hist/and8.fut, and16.fut, or8.fut, or16.fut, xor8.fut, xor16.fut)
+ * entry hist_or_bool (n: i64) (is: []i32) (vs: []bool): [n]bool = hist (||) false n (map i64.i32 is) vs   (tests/hist/lor.fut)
  * entry reduce_by_index_{min,max}_{i8,u8,i16,u16} (dest: *[n]t) (is: []i32) (vs: []t): [n]t =
  *   reduce_by_index dest t.min t.highest (map i64.i32 is) vs, ...      (the two results of tests/hist/min8.fut,
  *   min16.fut, max8.fut, max16.fut; the same compare-and-swap loop, signed operators on the sign-extended sub-word)
@@ -378,6 +379,7 @@ FUTHARK_B200_HIST_ENTRY(xor_i8, i8_1d)
 FUTHARK_B200_HIST_ENTRY(and_i16, i16_1d)
 FUTHARK_B200_HIST_ENTRY(or_i16, i16_1d)
 FUTHARK_B200_HIST_ENTRY(xor_i16, i16_1d)
+FUTHARK_B200_HIST_ENTRY(or_bool, bool_1d)
 FUTHARK_B200_RBI_ENTRY(min_i8, i8_1d)
 FUTHARK_B200_RBI_ENTRY(max_i8, i8_1d)
 FUTHARK_B200_RBI_ENTRY(min_u8, u8_1d)

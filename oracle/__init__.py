@@ -493,7 +493,7 @@ def reduce_by_index_subword(t, dest, is_, vs):
     return dest
 
 
-NARROW_OPS = {"min_i": 0, "max_i": 1, "min_u": 2, "max_u": 3, "and_i": 4, "or_i": 5, "xor_i": 6}
+NARROW_OPS = {"min_i": 0, "max_i": 1, "min_u": 2, "max_u": 3, "and_i": 4, "or_i": 5, "xor_i": 6, "or_u": 5}
 
 
 def reduce_by_index_narrow(op, dest, is_, vs):
@@ -511,8 +511,10 @@ def reduce_by_index_narrow(op, dest, is_, vs):
 
 
 def hist_narrow(op, B, is_, vs):
-    """hist <op> <neutral> B (map i64.i32 is) vs for op in {and,or,xor}_{i8,i16}."""
+    """hist <op> <neutral> B (map i64.i32 is) vs for op in {and,or,xor}_{i8,i16} and or_bool (hist (||) false)."""
     name, t = op.split("_")
+    if t == "bool":
+        return reduce_by_index_narrow("or_u8", np.zeros(B, np.uint8), is_, np.asarray(vs, np.bool_).view(np.uint8)).view(np.bool_)
     dt = {"i8": np.int8, "i16": np.int16}[t]
     return reduce_by_index_narrow(op, np.full(B, -1 if name == "and" else 0, dt), is_, vs)
 

@@ -60,6 +60,8 @@ FILES = [
     "tests/hist/tuple_partial.fut",
     "tests/soacs/reduce4.fut",
     "tests/soacs/reduce5.fut",
+    "tests/hist/lor.fut",
+    "tests/hist/equiv.fut",
     "tests/hist/and8.fut",
     "tests/hist/and16.fut",
     "tests/hist/and64.fut",

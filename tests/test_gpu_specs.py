@@ -98,6 +98,13 @@ def test_reference_vectors_row_bins_pair_operator_row_operator(ctx):
             m = len(xs[0])
             vss = np.tile(np.arange(m, dtype=np.int32), (len(image), 1))
             assert fb.reduce_by_index_vec_add_i32(ctx, np.array(xs, np.int32), np.array(image, np.int64), vss).tolist() == c["output"][0]
+    for c in GOLDEN["tests/hist/equiv.fut"]:
+        xs, image = c["input"]
+        vss = np.tile(np.array([1, 2, 3], np.int32), (len(image), 1))
+        assert fb.reduce_by_index_vec_add_i32(ctx, np.array(xs, np.int32), np.array(image, np.int64), vss).tolist() == c["output"][0]
+    for c in GOLDEN["tests/hist/lor.fut"]:
+        n, is_, image = c["input"]
+        assert fb.hist_op(ctx, "or_bool", n, np.array(is_, np.int32), np.array(image, np.bool_)).tolist() == c["output"][0]
     for c in GOLDEN["tests/hist/tuple_partial.fut"]:
         m, is_, vs0, vs1 = c["input"]
         got = fb.reduce_by_index_minpair_i32(ctx, m, np.array(is_, np.int32), np.array(vs0, np.int32), np.array(vs1, np.int32))
@@ -166,6 +173,10 @@ def test_hist_bit_operators_narrow_and_i64(ctx, op, B):
             ws |= dt(~0x11)                          # leave some bits standing
         got = fb.hist_op(ctx, "%s_%s" % (op, t), B, bins, ws)
         assert got.dtype == dt and np.array_equal(got, oracle.hist_narrow("%s_%s" % (op, t), B, bins, ws))
+    if op == "or":
+        keep = datagen.uniform_i32(77, 0, n, 0, 999) < 2
+        got = fb.hist_op(ctx, "or_bool", B, bins, keep)
+        assert got.dtype == np.bool_ and np.array_equal(got, oracle.hist_narrow("or_bool", B, bins, keep))
     ws = datagen.uniform_i32(76, 0, n, -2 ** 31, 2 ** 31 - 1)
     if op == "and":
         ws |= np.int32(~0x01010101)

@@ -71,6 +71,20 @@ def test_reduce_by_index_with_rows_as_bins(name):
         assert oracle.reduce_by_index_vec_add_i32(np.array(xs, np.int32), image, vss).tolist() == c["output"][0]
 
 
+@pytest.mark.parametrize("c", cases("tests/hist/lor.fut"))
+def test_hist_logical_or(c):
+    n, is_, image = c["input"]
+    assert oracle.hist_narrow("or_bool", n, is_, image).tolist() == c["output"][0]
+
+
+@pytest.mark.parametrize("c", cases("tests/hist/equiv.fut"))
+def test_reduce_by_index_rows_as_bins_equiv(c):
+    xs, image = c["input"]
+    vss = np.tile(np.array([1, 2, 3], np.int32), (len(image), 1))              # replicate k [1, 2, 3]
+    got = oracle.reduce_by_index_vec_add_i32(np.array(xs, np.int32), image, vss).tolist()
+    assert got == c["output"][0] == c["output"][1]
+
+
 @pytest.mark.parametrize("c", cases("tests/hist/tuple_partial.fut"))
 def test_reduce_by_index_with_an_operator_on_pairs(c):
     m, is_, vs0, vs1 = c["input"]
