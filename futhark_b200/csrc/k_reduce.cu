@@ -25,15 +25,16 @@ size_t reduce_scratch_bytes() {
 }
 
 // ---- reduce (+) 0 over i32 ----------------------------------------------------------
-// Stage one: grid-stride over 16-byte vectors, four loads in flight per thread.
-// Stage two: the CTA that draws the last ticket folds the per-CTA partials
-// (same election as reductionStageTwo, SegRed.hs:923-1047, without the extra barrier
-// rounds).  Integer addition wraps, so any order gives the reference's bits.
+// Stage one: the warps stride over 2 KiB chunks of 16-byte vectors, four loads in flight per thread.
+// Stage two (reductionStageTwo, SegRed.hs:923-1047, elects the last block with a counter and lets it
+// fold the partials): here one 64-bit atomic addition per CTA does both.  The upper half of the word
+// accumulates the partial sums (integer addition wraps, so any order gives the reference's bits, and
+// what overflows the word is dropped), the lower half counts the CTAs and cannot carry into the sum;
+// the CTA whose addition returns the count gridDim.x - 1 has the sum of all the others in the same
+// answer, adds its own, writes the result and clears the word for the next launch.
 __global__ void __launch_bounds__(RED_THREADS)
-reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict__ d_out,
-                  uint32_t *ticket, uint32_t *partials) {
+reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict__ d_out, unsigned long long *sum_and_count) {
   __shared__ uint32_t s_warp[RED_THREADS / 32];
-  __shared__ uint32_t s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t gtid = (int64_t)blockIdx.x * RED_THREADS + tid;
   const int64_t gthreads = (int64_t)gridDim.x * RED_THREADS;
@@ -47,21 +48,25 @@ reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict
   const int64_t tail_start = head + (nvec << 2);
 
   uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-  int64_t i = gtid;
-  for (; i + 3 * gthreads < nvec; i += 4 * gthreads) {
-    int4 v0 = ld_stream_v4(vec + i);
-    int4 v1 = ld_stream_v4(vec + i + gthreads);
-    int4 v2 = ld_stream_v4(vec + i + 2 * gthreads);
-    int4 v3 = ld_stream_v4(vec + i + 3 * gthreads);
+  // a warp takes 2 KiB at a time: four 16-byte loads per lane, 512 bytes apart, all in flight
+  const int64_t nw = gthreads >> 5;
+  int64_t base = (gtid >> 5) * 128 + lane;
+  for (; base + 96 < nvec; base += nw * 128) {
+    int4 v0 = ld_stream_v4(vec + base);
+    int4 v1 = ld_stream_v4(vec + base + 32);
+    int4 v2 = ld_stream_v4(vec + base + 64);
+    int4 v3 = ld_stream_v4(vec + base + 96);
     a0 += (uint32_t)v0.x + (uint32_t)v0.y + (uint32_t)v0.z + (uint32_t)v0.w;
     a1 += (uint32_t)v1.x + (uint32_t)v1.y + (uint32_t)v1.z + (uint32_t)v1.w;
     a2 += (uint32_t)v2.x + (uint32_t)v2.y + (uint32_t)v2.z + (uint32_t)v2.w;
     a3 += (uint32_t)v3.x + (uint32_t)v3.y + (uint32_t)v3.z + (uint32_t)v3.w;
   }
-  for (; i < nvec; i += gthreads) {
-    int4 v0 = ld_stream_v4(vec + i);
-    a0 += (uint32_t)v0.x + (uint32_t)v0.y + (uint32_t)v0.z + (uint32_t)v0.w;
-  }
+#pragma unroll
+  for (int k = 0; k < 4; k++)              // the last, partly filled chunk (every later one lies beyond the end)
+    if (base + 32 * k < nvec) {
+      int4 v0 = ld_stream_v4(vec + base + 32 * k);
+      a0 += (uint32_t)v0.x + (uint32_t)v0.y + (uint32_t)v0.z + (uint32_t)v0.w;
+    }
   uint32_t acc = a0 + a1 + a2 + a3;
   if (gtid < head) acc += (uint32_t)in[gtid];
   if (tail_start + gtid < n) acc += (uint32_t)in[tail_start + gtid];   // fewer than 4 elements
@@ -73,26 +78,11 @@ reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict
     uint32_t b = (lane < RED_THREADS / 32) ? s_warp[lane] : 0u;
     b = warp_sum(b);
     if (lane == 0) {
-      partials[blockIdx.x] = b;
-      __threadfence();
-      uint32_t t = atomicAdd(ticket, 1u);
-      s_last = (t == gridDim.x - 1) ? 1u : 0u;
-    }
-  }
-  __syncthreads();
-  if (s_last) {
-    __threadfence();
-    uint32_t s = 0;
-    for (int j = tid; j < (int)gridDim.x; j += RED_THREADS)
-      s += *reinterpret_cast<volatile uint32_t *>(&partials[j]);
-    s = warp_sum(s);
-    __syncthreads();
-    if (lane == 0) s_warp[warp] = s;
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t b = (lane < RED_THREADS / 32) ? s_warp[lane] : 0u;
-      b = warp_sum(b);
-      if (lane == 0) { *d_out = (int32_t)b; *ticket = 0u; }
+      const unsigned long long old = atomicAdd(sum_and_count, ((unsigned long long)b << 32) | 1ull);
+      if ((uint32_t)old == gridDim.x - 1) {
+        *d_out = (int32_t)((uint32_t)(old >> 32) + b);
+        *sum_and_count = 0ull;
+      }
     }
   }
 }
@@ -100,14 +90,15 @@ reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict
 cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void *scratch, int num_sms,
                               cudaStream_t stream, int block_cap) {
   if (n <= 0) return cudaMemsetAsync(d_out, 0, sizeof(int32_t), stream);   // the neutral element
-  uint32_t *ticket = reinterpret_cast<uint32_t *>(scratch);
-  uint32_t *partials = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(scratch) + 256);
+  // the word lives in the head of the scratch area, beside the ticket of the other reductions; like the
+  // ticket it is zero between launches
+  unsigned long long *sum_and_count = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(scratch) + 64);
   int64_t want = (n / 4 + RED_THREADS - 1) / RED_THREADS;
   int blocks = num_sms * 8;
   if (blocks > RED_MAX_BLOCKS) blocks = RED_MAX_BLOCKS;
   if (want < blocks) blocks = want < 1 ? 1 : (int)want;
   if (block_cap > 0 && block_cap < blocks) blocks = block_cap;       // reduce_i32.segred_num_tblocks
-  reduce_i32_kernel<<<blocks, RED_THREADS, 0, stream>>>(in, n, d_out, ticket, partials);
+  reduce_i32_kernel<<<blocks, RED_THREADS, 0, stream>>>(in, n, d_out, sum_and_count);
   return cudaGetLastError();
 }
 
