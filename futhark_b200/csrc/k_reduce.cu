@@ -32,7 +32,10 @@ size_t reduce_scratch_bytes() {
 // what overflows the word is dropped), the lower half counts the CTAs and cannot carry into the sum;
 // the CTA whose addition returns the count gridDim.x - 1 has the sum of all the others in the same
 // answer, adds its own, writes the result and clears the word for the next launch.
-__global__ void __launch_bounds__(RED_THREADS)
+// Six CTAs per SM, all resident at once (40 registers).  Measured at 2^26 elements: 8 per SM (32 registers,
+// spills) 46.4 us, 6 per SM 45.3 us, 5 per SM 45.2 us, 4 per SM 45.6 us.
+constexpr int RED_I32_CTAS_PER_SM = 6;
+__global__ void __launch_bounds__(RED_THREADS, RED_I32_CTAS_PER_SM)
 reduce_i32_kernel(const int32_t *__restrict__ in, int64_t n, int32_t *__restrict__ d_out, unsigned long long *sum_and_count) {
   __shared__ uint32_t s_warp[RED_THREADS / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -94,7 +97,7 @@ cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void
   // ticket it is zero between launches
   unsigned long long *sum_and_count = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(scratch) + 64);
   int64_t want = (n / 4 + RED_THREADS - 1) / RED_THREADS;
-  int blocks = num_sms * 8;
+  int blocks = num_sms * RED_I32_CTAS_PER_SM;
   if (blocks > RED_MAX_BLOCKS) blocks = RED_MAX_BLOCKS;
   if (want < blocks) blocks = want < 1 ? 1 : (int)want;
   if (block_cap > 0 && block_cap < blocks) blocks = block_cap;       // reduce_i32.segred_num_tblocks
