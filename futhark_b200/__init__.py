@@ -215,6 +215,7 @@ def load():
     L.futhark_entry_reduce_map2_add_i32.argtypes = [vp, pvp, vp]
     L.futhark_entry_reduce_by_index_vec_add_i32.argtypes = [vp, pvp, vp, vp, vp]
     L.futhark_entry_reduce_by_index_minpair_i32.argtypes = [vp, pvp, i64, vp, vp, vp]
+    L.futhark_entry_hist_rows_vec_add_i32.argtypes = [vp, pvp, i64, vp, vp]
     for i in range(2):
         getattr(L, "futhark_project_%s_%d" % (PAIR_I32, i)).argtypes = [vp, pvp, vp]
     getattr(L, "futhark_free_" + PAIR_I32).argtypes = [vp, vp]
@@ -570,6 +571,9 @@ class Context:
     def entry_reduce_by_index_vec_add_i32(self, dest, is_, vss):
         return self._entry_arr("reduce_by_index_vec_add_i32", "i32_2d", dest.ptr, is_.ptr, vss.ptr)
 
+    def entry_hist_rows_vec_add_i32(self, m, iss, vsss):
+        return self._entry_arr("hist_rows_vec_add_i32", "i32_3d", int(m), iss.ptr, vsss.ptr)
+
     def entry_reduce_by_index_minpair_i32(self, m, is_, vs0, vs1):
         """The two result arrays (the opaque pair is projected and freed)."""
         obj = ctypes.c_void_p()
@@ -816,6 +820,10 @@ def reduce_map2_add_i32(ctx, xss):
 
 def reduce_by_index_vec_add_i32(ctx, dest, is_, vss):
     return _run(ctx, [("i32_2d", dest), ("i64_1d", is_), ("i32_2d", vss)], ctx.entry_reduce_by_index_vec_add_i32)
+
+
+def hist_rows_vec_add_i32(ctx, m, iss, vsss):
+    return _run(ctx, [("i32_2d", iss), ("i32_3d", vsss)], lambda i, v: ctx.entry_hist_rows_vec_add_i32(m, i, v))
 
 
 def reduce_by_index_minpair_i32(ctx, m, is_, vs0, vs1):

@@ -328,6 +328,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"partition2_i32", {"[]i32"}, "([]i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32)", r); return rc; }},
       FE_E1(reduce_map2_add_i32, i32_2d, "[][]i32", i32_1d, "[]i32"),
       FE_E3(reduce_by_index_vec_add_i32, i32_2d, "[][]i32", i64_1d, "[]i64", i32_2d, "[][]i32", i32_2d, "[][]i32"),
+      {"hist_rows_vec_add_i32", {"i64", "[][]i32", "[][][]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_hist_rows_vec_add_i32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_2d), FE_IN(2, i32_3d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"reduce_by_index_minpair_i32", {"i64", "[]i32", "[]i32", "[]i32"}, "([]i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup2_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_reduce_by_index_minpair_i32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_1d), FE_IN(2, i32_1d), FE_IN(3, i32_1d)); if (!rc) set_record(o, "([]i32, []i32)", r); return rc; }},
       {"partition2_pairs_i32", {"[]i32", "[]i32"}, "([]i32, []i32, []i32, []i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup6_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_pairs_i32(c, &r, FE_IN(0, i32_1d), FE_IN(1, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32, []i32, []i32, []i32)", r); return rc; }},
       {"replicate_i32", {"i64", "i32"}, "[]i32", [](C *c, In in, Value &o) { futhark_i32_1d *r = nullptr; int rc = futhark_entry_replicate_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int32_t>(*in[1])); if (!rc) set_array(o, "[]i32", r); return rc; }},

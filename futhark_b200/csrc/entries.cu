@@ -537,6 +537,36 @@ int futhark_entry_reduce_by_index_vec_add_i32(struct futhark_context *ctx, struc
   return FUTHARK_SUCCESS;
 }
 
+// map2 (\is vss -> hist (map2 (+)) (replicate k 0) m (map i64.i32 is) vss) iss vsss (tests/hist/segmented_arr.fut): a
+// segment dimension over a histogram whose bins are k-vectors; one histogram over rows * m * k bins
+int futhark_entry_hist_rows_vec_add_i32(struct futhark_context *ctx, struct futhark_i32_3d **out0, const int64_t in0, const struct futhark_i32_2d *in1,
+                                        const struct futhark_i32_3d *in2) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t m = in0, rows = in1->shape[0], cols = in1->shape[1], k = in2->shape[2];
+  if (in2->shape[0] != rows || in2->shape[1] != cols) return bad_sizes(ctx);
+  if (m < 0) { fb_set_error(ctx, "Error: negative histogram size %lld.\n", (long long)m); return FUTHARK_PROGRAM_ERROR; }
+  if (rows * m * k >= (1ll << 31)) { fb_set_error(ctx, "hist_rows_vec_add_i32: %lld bins exceed 2^31-1.", (long long)(rows * m * k)); return 1; }
+  const int64_t n = rows * cols * k;
+  memblock_device flat;
+  int rc = fb_alloc(ctx, (size_t)n * 4, "hist_rows_vec.flat_index", &flat);
+  if (rc != 0) return rc;
+  void *o = nullptr;
+  ctx->launch_count++;
+  rc = fb_cuda_check(ctx, fb::launch_flatten_rows_vec_index(dptr<int32_t>(in1->mem), rows, cols, m, k, dptr<int32_t>(flat), ctx->num_sms, ctx->stream),
+                     "flatten_rows_vec_index");
+  if (rc == 0) rc = hist_launch(ctx, fb::HOP_ADD_I32, &o, rows * m * k, nullptr, dptr<int32_t>(flat), n, in2->mem, n, "hist_rows_vec_add_i32.seghist");
+  fb_unref(ctx, &flat);
+  if (rc != 0) return rc;
+  futhark_i32_1d *h = (futhark_i32_1d *)o;
+  futhark_i32_3d *out = (futhark_i32_3d *)malloc(sizeof(futhark_i32_3d));
+  if (out == nullptr) { fb_unref(ctx, &h->mem); free(h); return 1; }
+  out->mem = h->mem; out->shape[0] = rows; out->shape[1] = m; out->shape[2] = k;
+  free(h);
+  *out0 = out;
+  return FUTHARK_SUCCESS;
+}
+
 // main of tests/hist/tuple_partial.fut:24-28: reduce_by_index (replicate m (-1, -1)) operator (-1, -1) (map i64.i32 is)
 // (zip vs0 vs1), unzipped; the operator keeps the pair with the smaller first component.  A pair is one 64-bit
 // word updated by compare-and-swap (the reference takes a lock per bin for such an operator, Base.hs:769-842).

@@ -716,6 +716,24 @@ cudaError_t launch_flatten_vec_index(const int64_t *is, int64_t k, int64_t n, in
   return cudaGetLastError();
 }
 
+// The same under a segment dimension (tests/hist/segmented_arr.fut): a histogram of k-vectors per row of
+// [rows][cols] indices; flat[(r * cols + i) * k + j] = (r * m + iss[r][i]) * k + j, or -1.
+__global__ void __launch_bounds__(256)
+flatten_rows_vec_index_kernel(const int32_t *__restrict__ iss, int64_t elems, int64_t cols, int64_t m, int64_t k, int32_t *__restrict__ flat) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x, total = elems * k;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int64_t e = t / k, j = t - e * k, r = e / cols, b = iss[e];
+    flat[t] = (b >= 0 && b < m) ? (int32_t)((r * m + b) * k + j) : -1;
+  }
+}
+cudaError_t launch_flatten_rows_vec_index(const int32_t *iss, int64_t rows, int64_t cols, int64_t m, int64_t k, int32_t *flat, int num_sms,
+                                          cudaStream_t stream) {
+  const int64_t total = rows * cols * k;
+  if (total <= 0) return cudaSuccess;
+  flatten_rows_vec_index_kernel<<<grid_for(total, 256, num_sms * 8), 256, 0, stream>>>(iss, rows * cols, cols, m, k, flat);
+  return cudaGetLastError();
+}
+
 // ---- an operator on pairs: the smaller first component wins and carries its second along ----------------
 // tests/hist/tuple_partial.fut:19-22: op (x0, y0) (x1, y1) = if x0 != -1 && (x1 == -1 || x0 < x1) then (x0, y0)
 // else (x1, y1), neutral (-1, -1).  The reference guards such an update with a lock per bin

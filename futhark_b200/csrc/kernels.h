@@ -116,6 +116,9 @@ cudaError_t launch_hist(int op, int64_t B, const int32_t *bins, const void *weig
                         const void *dest, int num_sms, cudaStream_t stream);
 // flat[i * m + j] = is[i] * m + j, or -1 where is[i] is outside [0, n): a histogram whose bins are rows of m values
 cudaError_t launch_flatten_vec_index(const int64_t *is, int64_t k, int64_t n, int64_t m, int32_t *flat, int num_sms, cudaStream_t stream);
+// flat[(r * cols + i) * k + j] = (r * m + iss[r][i]) * k + j, or -1: one histogram of k-vectors per row
+cudaError_t launch_flatten_rows_vec_index(const int32_t *iss, int64_t rows, int64_t cols, int64_t m, int64_t k, int32_t *flat, int num_sms,
+                                          cudaStream_t stream);
 // the minimum of the first components carrying the second along, neutral (-1, -1); `packed`: B 8-byte words
 cudaError_t launch_hist_minpair_i32(int64_t B, const int32_t *bins, const int32_t *v0, const int32_t *v1, int64_t n, void *packed, int32_t *out0,
                                     int32_t *out1, int num_sms, cudaStream_t stream);

@@ -64,6 +64,7 @@ ENTRIES = {
     **{"reduce_by_index_%s_%s" % (o, t): ([("dest", "[]" + t), ("is", "[]i32"), ("vs", "[]" + t)], "[]" + t, [])
        for o in ("min", "max") for t in ("i8", "u8", "i16", "u16")},
     "reduce_by_index_vec_add_i32": ([("xs", "[][]i32"), ("is", "[]i64"), ("vss", "[][]i32")], "[][]i32", []),
+    "hist_rows_vec_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vsss", "[][][]i32")], "[][][]i32", []),
     "reduce_by_index_minpair_i32": ([("m", "i64"), ("is", "[]i32"), ("vs0", "[]i32"), ("vs1", "[]i32")], "([]i32, []i32)", []),
     "reduce_map2_add_i32": ([("xss", "[][]i32")], "[]i32", []),
     "hist_rows_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vss", "[][]i32")], "[][]i32", []),

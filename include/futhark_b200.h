@@ -327,6 +327,9 @@ int futhark_entry_hist_max_f32(struct futhark_context *ctx, struct futhark_f32_1
  * entry reduce_by_index_vec_add_i32 [n][m][k] (xs: *[n][m]i32) (is: [k]i64) (vss: [k][m]i32): [n][m]i32 =
  *   reduce_by_index xs (map2 (+)) (replicate m 0) is vss               (tests/hist/array.fut, array_novec.fut: the
  *   bins are rows, HistOp's operator shape, src/Futhark/IR/SegOp.hs:102-115; one histogram over n * m bins)
+ * entry hist_rows_vec_add_i32 [r][c][k] (m: i64) (iss: [r][c]i32) (vsss: [r][c][k]i32): [r][m][k]i32 =
+ *   map2 (\is vss -> hist (map2 (+)) (replicate k 0) m (map i64.i32 is) vss) iss vsss   (tests/hist/segmented_arr.fut:
+ *   a segment dimension over a histogram whose bins are vectors)
  * entry reduce_by_index_minpair_i32 (m: i64) (is: []i32) (vs0: []i32) (vs1: []i32): ([m]i32, [m]i32) =
  *   main of tests/hist/tuple_partial.fut:24-28: an operator on pairs (the smaller first component wins and
  *   carries its second along; neutral (-1, -1)).  The reference locks the bin (Base.hs:769-842); here the
@@ -398,6 +401,9 @@ FUTHARK_B200_HIST_I64_ENTRY(xor_i64)
 int futhark_entry_reduce_by_index_vec_add_i32(struct futhark_context *ctx, struct futhark_i32_2d **out0,
                                               const struct futhark_i32_2d *in0, const struct futhark_i64_1d *in1,
                                               const struct futhark_i32_2d *in2);
+int futhark_entry_hist_rows_vec_add_i32(struct futhark_context *ctx, struct futhark_i32_3d **out0,
+                                        const int64_t in0, const struct futhark_i32_2d *in1,
+                                        const struct futhark_i32_3d *in2);
 int futhark_entry_reduce_by_index_minpair_i32(struct futhark_context *ctx,
                                               struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 **out0,
                                               const int64_t in0, const struct futhark_i32_1d *in1,

@@ -544,6 +544,16 @@ def reduce_by_index_vec_add_i32(dest, is_, vss):
     return dest
 
 
+def hist_rows_vec_add_i32(m, iss, vsss):
+    iss, vsss = _c(iss, np.int32), _c(vsss, np.int32)
+    rows, cols = iss.shape
+    k = vsss.shape[2]
+    out = np.empty((rows, m, k), np.int32)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    _fn("orc_hist_rows_vec_add_i32", vp, i64, i64, i64, i64, vp, vp)(_p(out), rows, cols, m, k, _p(iss), _p(vsss))
+    return out
+
+
 def reduce_by_index_minpair_i32(m, is_, vs0, vs1):
     is_, vs0, vs1 = _c(is_, np.int32), _c(vs0, np.int32), _c(vs1, np.int32)
     out0, out1 = np.empty(m, np.int32), np.empty(m, np.int32)

@@ -111,6 +111,19 @@ void orc_reduce_by_index_vec_add_i32(int32_t *dest, int64_t n, int64_t m, const 
   }
 }
 
+/* map2 (\is vss -> hist (map2 (+)) (replicate k 0) m (map i64.i32 is) vss) iss vsss (tests/hist/segmented_arr.fut:8-9);
+ * out is [rows][m][k], zeroed here */
+void orc_hist_rows_vec_add_i32(int32_t *out, int64_t rows, int64_t cols, int64_t m, int64_t k, const int32_t *iss, const int32_t *vsss) {
+  for (int64_t t = 0; t < rows * m * k; t++) out[t] = 0;
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t i = 0; i < cols; i++) {
+      const int64_t b = iss[r * cols + i];
+      if (b < 0 || b >= m) continue;
+      for (int64_t j = 0; j < k; j++)
+        out[(r * m + b) * k + j] = (int32_t)((uint32_t)out[(r * m + b) * k + j] + (uint32_t)vsss[(r * cols + i) * k + j]);
+    }
+}
+
 /* tests/hist/tuple_partial.fut:19-28: dest[b] = operator dest[b] (vs0[i], vs1[i]) in the order of the input, from
  * (-1, -1); operator (x0, y0) (x1, y1) = if x0 != -1 && (x1 == -1 || x0 < x1) then (x0, y0) else (x1, y1) */
 void orc_reduce_by_index_minpair_i32(int32_t *out0, int32_t *out1, int64_t m, const int32_t *is, const int32_t *vs0, const int32_t *vs1,

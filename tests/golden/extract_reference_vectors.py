@@ -62,6 +62,7 @@ FILES = [
     "tests/soacs/reduce5.fut",
     "tests/hist/lor.fut",
     "tests/hist/equiv.fut",
+    "tests/hist/segmented_arr.fut",
     "tests/hist/and8.fut",
     "tests/hist/and16.fut",
     "tests/hist/and64.fut",

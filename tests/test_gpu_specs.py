@@ -105,6 +105,10 @@ def test_reference_vectors_row_bins_pair_operator_row_operator(ctx):
     for c in GOLDEN["tests/hist/lor.fut"]:
         n, is_, image = c["input"]
         assert fb.hist_op(ctx, "or_bool", n, np.array(is_, np.int32), np.array(image, np.bool_)).tolist() == c["output"][0]
+    for c in GOLDEN["tests/hist/segmented_arr.fut"]:
+        m, xss = c["input"]
+        xss = np.array(xss, np.int32)
+        assert fb.hist_rows_vec_add_i32(ctx, m, xss, np.ones(xss.shape + (3,), np.int32)).tolist() == c["output"][0]
     for c in GOLDEN["tests/hist/tuple_partial.fut"]:
         m, is_, vs0, vs1 = c["input"]
         got = fb.reduce_by_index_minpair_i32(ctx, m, np.array(is_, np.int32), np.array(vs0, np.int32), np.array(vs1, np.int32))
@@ -121,6 +125,14 @@ def test_reduce_by_index_rows_as_bins(ctx, n, m, k):
     vss = datagen.uniform_i32(83, 0, k * m, -2 ** 31, 2 ** 31 - 1).reshape(k, m)
     got = fb.reduce_by_index_vec_add_i32(ctx, dest, is_, vss)
     assert got.shape == (n, m) and np.array_equal(got, oracle.reduce_by_index_vec_add_i32(dest, is_, vss))
+
+
+@pytest.mark.parametrize("rows,cols,m,k", [(1, 1, 1, 1), (3, 0, 4, 2), (2, 5, 0, 3), (7, 1000, 13, 3), (300, 257, 1000, 5)])
+def test_segmented_histogram_of_vectors(ctx, rows, cols, m, k):
+    iss = datagen.uniform_i32(88, 0, rows * cols, -1, m).reshape(rows, cols)
+    vsss = datagen.uniform_i32(89, 0, rows * cols * k, -2 ** 31, 2 ** 31 - 1).reshape(rows, cols, k)
+    got = fb.hist_rows_vec_add_i32(ctx, m, iss, vsss)
+    assert got.shape == (rows, m, k) and np.array_equal(got, oracle.hist_rows_vec_add_i32(m, iss, vsss))
 
 
 @pytest.mark.parametrize("m,n", [(1, 1), (5, 0), (1, 100000), (1000, 300001), (200000, 100003)])

@@ -85,6 +85,14 @@ def test_reduce_by_index_rows_as_bins_equiv(c):
     assert got == c["output"][0] == c["output"][1]
 
 
+@pytest.mark.parametrize("c", cases("tests/hist/segmented_arr.fut"))
+def test_segmented_histogram_of_vectors(c):
+    m, xss = c["input"]
+    xss = np.array(xss, np.int32)
+    ones = np.ones(xss.shape + (3,), np.int32)                                 # map (const (replicate 3 1)) xs
+    assert oracle.hist_rows_vec_add_i32(m, xss, ones).tolist() == c["output"][0]
+
+
 @pytest.mark.parametrize("c", cases("tests/hist/tuple_partial.fut"))
 def test_reduce_by_index_with_an_operator_on_pairs(c):
     m, is_, vs0, vs1 = c["input"]
