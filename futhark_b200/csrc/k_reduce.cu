@@ -236,12 +236,12 @@ cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float
 }
 
 // ---- irregular segmented sum: out[s] = sum xs[offsets[s] .. offsets[s+1]) ------------------
-// The values are streamed through shared memory in tiles of 5120 elements, each CTA owning a
+// The values are streamed through shared memory in tiles of 7168 elements, each CTA owning a
 // contiguous run of tiles, the next tile's bulk async copy (TMA) in flight while the current
 // one is summed.  Segment boundaries come from the offsets alone (the flags of the entry point
 // are not consulted: what is summed is exactly [offsets[s], offsets[s+1])).
 //
-// A CTA has nine warps.  In the eight worker warps a thread owns a chunk of 20 consecutive
+// A CTA has nine warps.  In the eight worker warps a thread owns a chunk of 28 consecutive
 // elements of the tile; with segments of a few hundred elements nine chunks in ten contain no
 // boundary, so the work is split by who has something to do:
 //
@@ -251,31 +251,33 @@ cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float
 //     use.  For every boundary in the tile one lane notes the boundary's chunk, the elements
 //     of that chunk that lie in front of it (back to the chunk's start or to the previous
 //     boundary, whichever is nearer) and, for the chunk's last boundary, where it lies.
-//   * A worker adds up its chunk: 19 additions and no tests, or, if the chunk has a
+//   * A worker adds up its chunk: 27 additions and no tests, or, if the chunk has a
 //     boundary, the elements behind the last one (they open the next segment).
 //   * Then one segmented scan with the lifted operator (f1|f2, f2 ? v2 : v1+v2) of
 //     Pass/Flatten/Builtins.hs:374-393 runs over the 256 chunk values (a chunk with a
 //     boundary counts as flagged): shuffles inside the warps, the 8 warp totals through
 //     shared memory.  It is the scan-then-pick of genSegRed (Pass/Flatten/Builtins.hs:582-602)
-//     at one value per 20 elements.
+//     at one value per 28 elements.
 //   * Finally worker b finishes boundary b: it sums the elements in front of the boundary
 //     inside the boundary's chunk out of the tile buffer; that, plus the scan value of the
 //     chunk before (with the carry of the earlier tiles), is the segment's total, stored at
 //     the segment's index = cursor + b - 1.
 //   * A tile with equal offsets (empty segments) or more than 256 boundaries takes a general
-//     route: the boundaries become one bit per element, every thread folds its 20 elements
+//     route: the boundaries become one bit per element, every thread folds its 28 elements
 //     under them, the scanned tile goes back into the buffer and one thread per offset picks
 //     its value (0 for an empty segment).
 //   * What crosses a tile edge is carried in registers; what crosses the edge between two
 //     CTAs' runs goes through one record per CTA (sum in front of its first segment end, sum
 //     behind its last, index of the first ending segment), and the CTA that finishes last
 //     joins the records in order.  No atomics on floats: the result is deterministic.
-constexpr int SR_V = 5, SR_ITEMS = SR_V * 4, SR_TILE = RED_THREADS * SR_ITEMS;   // 5120 elements, 20 KiB
+constexpr int SR_V = 7, SR_ITEMS = SR_V * 4, SR_TILE = RED_THREADS * SR_ITEMS;   // 7168 elements, 28 KiB (SR_V odd: conflict-free 16-byte reads; SR_ITEMS <= 31)
 constexpr int SR_WARPS = RED_THREADS / 32;
 constexpr int SR_MAX_CTAS = 2048;
 constexpr int SR_THREADS = RED_THREADS + 32;                       // 8 warps on the chunks, one on the offsets
-// Two tile buffers and four CTAs per SM (measured at 2^27 elements: 103.5 us; three buffers and three CTAs 110.9 us; four and two 121.7 us).
-constexpr int SR_NBUF = 2, SR_CTAS_PER_SM = 4;
+// Two tile buffers and three CTAs per SM.  Measured at 2^27 elements, elements per thread x buffers x CTAs per SM:
+// 28 x 2 x 3 99.1 us; 20 x 2 x 4 103.5 us; 24 x 2 x 4 103.9 us (two-way bank conflicts); 20 x 3 x 3 110.9 us;
+// 20 x 4 x 2 121.7 us.
+constexpr int SR_NBUF = 2, SR_CTAS_PER_SM = 3;
 constexpr int SR_BIG = 1 << 29;
 
 struct SegRedRecord {       // 16 bytes, one per CTA, in the reduce scratch behind the ticket
@@ -300,6 +302,17 @@ __device__ __forceinline__ void scan_warp_totals(const float *s_wv, const uint32
     const float lv = __shfl_up_sync(kFull, wv, o);
     const uint32_t lf = __shfl_up_sync(kFull, wf, o);
     if (lane >= o) seg_combine(lv, lf, wv, wf, wv, wf);
+  }
+}
+
+// s[0] + ... + s[N-1] as a tree: the largest power of two below N on the left, the rest on the right
+template <int N>
+__device__ __forceinline__ float tree_sum(const float *s) {
+  if constexpr (N == 1) return s[0];
+  else {
+    constexpr int H = (N > 4) ? 4 : (N > 2) ? 2 : 1;
+    static_assert(N <= 8, "tree_sum: at most 8 terms");
+    return tree_sum<H>(s) + tree_sum<N - H>(s + H);
   }
 }
 
@@ -460,8 +473,10 @@ segreduce_tiled_kernel(const int64_t *__restrict__ offsets, int64_t nseg, const 
       uint32_t ifl = rl ? 1u : 0u;
       float iv;
       if (rl == 0u) {
-        iv = (((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]))) +
-             (((x[8] + x[9]) + (x[10] + x[11])) + ((x[12] + x[13]) + (x[14] + x[15]))) + ((x[16] + x[17]) + (x[18] + x[19]));
+        float q4[SR_V];
+#pragma unroll
+        for (int j = 0; j < SR_V; j++) q4[j] = (x[4 * j] + x[4 * j + 1]) + (x[4 * j + 2] + x[4 * j + 3]);
+        iv = tree_sum<SR_V>(q4);
       } else {
         s_rl[par][tid] = 0u;
         iv = 0.f;
