@@ -77,7 +77,7 @@ struct SpecDefaults {
   static constexpr bool kStreamHints = false;
   // Measured on 2^26 i32 (scan) / 2^27 f32 with flags (segmented scan), V x CTAS x NBUF x DIST:
   // 5x4x2x1 97 / 213 us; 5x5x2x1 102 / 219 us; 5x3x3x2 102 / 274 us; 5x3x3x1 105 / 295 us;
-  // 3x4x4x2 120 / 318 us; 3x4x3x2 119 / 279 us; 3x5x3x2 123 / 285 us.
+  // 3x4x4x2 120 / 318 us; 3x4x3x2 119 / 279 us; 3x5x3x2 123 / 285 us; 7x3x2x1 112 / 260 us.
   static constexpr int V = 5, CTAS = 4, LEAD = 1024;
   static constexpr int NBUF = 2, DIST = 1;
   static __device__ __forceinline__ uint32_t map(uint32_t x) { return x; }
