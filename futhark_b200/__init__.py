@@ -31,6 +31,7 @@ ARRAY_TYPES = {
     "i32_2d": (np.int32, 2, ctypes.c_int32),
     "bool_2d": (np.bool_, 2, ctypes.c_bool),
     "i64_2d": (np.int64, 2, ctypes.c_int64),
+    "f64_2d": (np.float64, 2, ctypes.c_double),
     "f64_1d": (np.float64, 1, ctypes.c_double),
     "i8_1d": (np.int8, 1, ctypes.c_int8),
     "i16_1d": (np.int16, 1, ctypes.c_int16),
@@ -213,6 +214,11 @@ def load():
     getattr(L, "futhark_free_" + TRIPLE).argtypes = [vp, vp]
     L.futhark_entry_partition2_pairs_i32.argtypes = [vp, pvp, vp, vp]
     L.futhark_entry_reduce_map2_add_i32.argtypes = [vp, pvp, vp]
+    L.futhark_entry_segredomap_sum_neg_f32.argtypes = [vp, pvp, vp]
+    for i in range(2):
+        getattr(L, "futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_%d" % i).argtypes = [vp, pvp, vp]
+    L.futhark_free_opaque_tup2_arr1d_i64_arr2d_f64.argtypes = [vp, vp]
+    L.futhark_new_opaque_tup2_arr1d_i64_arr2d_f64.argtypes = [vp, pvp, vp, vp]
     L.futhark_entry_reduce_by_index_vec_add_i32.argtypes = [vp, pvp, vp, vp, vp]
     L.futhark_entry_reduce_by_index_minpair_i32.argtypes = [vp, pvp, i64, vp, vp, vp]
     L.futhark_entry_hist_rows_vec_add_i32.argtypes = [vp, pvp, i64, vp, vp]
@@ -565,6 +571,18 @@ class Context:
         self._check(getattr(self.lib, "futhark_free_" + TRIPLE)(self.ptr, obj))
         return parts
 
+    def entry_segredomap_sum_neg_f32(self, xss):
+        """The two results ([m]i64, [m][n]f64) as arrays (the opaque pair is projected and freed)."""
+        obj = ctypes.c_void_p()
+        self._check(self.lib.futhark_entry_segredomap_sum_neg_f32(self.ptr, ctypes.byref(obj), xss.ptr))
+        parts = []
+        for i, t in enumerate(("i64_1d", "f64_2d")):
+            out = ctypes.c_void_p()
+            self._check(getattr(self.lib, "futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_%d" % i)(self.ptr, ctypes.byref(out), obj))
+            parts.append(Array(self, t, out.value))
+        self._check(self.lib.futhark_free_opaque_tup2_arr1d_i64_arr2d_f64(self.ptr, obj))
+        return parts
+
     def entry_reduce_map2_add_i32(self, xss):
         return self._entry_arr("reduce_map2_add_i32", "i32_1d", xss.ptr)
 
@@ -805,6 +823,19 @@ def partition2_i32(ctx, xs):
     a = ctx.new("i32_1d", xs)
     try:
         parts = ctx.entry_partition2_i32(a)
+        try:
+            return tuple(p.values() for p in parts)
+        finally:
+            for p in parts:
+                p.free()
+    finally:
+        a.free()
+
+
+def segredomap_sum_neg_f32(ctx, xss):
+    a = ctx.new("f32_2d", xss)
+    try:
+        parts = ctx.entry_segredomap_sum_neg_f32(a)
         try:
             return tuple(p.values() for p in parts)
         finally:

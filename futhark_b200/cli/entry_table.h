@@ -58,6 +58,7 @@ static const ArrayType ARRAYS[] = {
     FE_ARRAY(bool, bool, 2, "[][]bool", "bool"), FE_ARRAY(i8, int8_t, 1, "[]i8", "i8"), FE_ARRAY(i16, int16_t, 1, "[]i16", "i16"),
     FE_ARRAY(f16, uint16_t, 1, "[]f16", "f16"), FE_ARRAY(i32, int32_t, 3, "[][][]i32", "i32"),
     FE_ARRAY(u8, uint8_t, 1, "[]u8", "u8"), FE_ARRAY(u16, uint16_t, 1, "[]u16", "u16"),
+    FE_ARRAY(f64, double, 2, "[][]f64", "f64"),
 };
 inline const ArrayType *array_type(const std::string &name) {
   for (const ArrayType &a : ARRAYS)
@@ -122,6 +123,24 @@ static const RecordType RECORDS[] = {
      },
      [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
        return futhark_new_opaque_tup2_arr1d_u32_arr1d_u32(c, (futhark_opaque_tup2_arr1d_u32_arr1d_u32 **)obj, (const futhark_u32_1d *)f[0]->arr, (const futhark_u32_1d *)f[1]->arr);
+     }},
+    {"([]i64, [][]f64)", {"[]i64", "[][]f64"},
+     [](futhark_context *c, void *o) { return futhark_free_opaque_tup2_arr1d_i64_arr2d_f64(c, (futhark_opaque_tup2_arr1d_i64_arr2d_f64 *)o); },
+     [](futhark_context *c, const void *o, int k, Value &out) {
+       const auto *obj = (const futhark_opaque_tup2_arr1d_i64_arr2d_f64 *)o;
+       if (k == 0) {
+         futhark_i64_1d *a = nullptr;
+         const int rc = futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_0(c, &a, obj);
+         if (!rc) set_array(out, "[]i64", a);
+         return rc;
+       }
+       futhark_f64_2d *a = nullptr;
+       const int rc = futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_1(c, &a, obj);
+       if (!rc) set_array(out, "[][]f64", a);
+       return rc;
+     },
+     [](futhark_context *c, const std::vector<const Value *> &f, void **obj) {
+       return futhark_new_opaque_tup2_arr1d_i64_arr2d_f64(c, (futhark_opaque_tup2_arr1d_i64_arr2d_f64 **)obj, (const futhark_i64_1d *)f[0]->arr, (const futhark_f64_2d *)f[1]->arr);
      }},
     {"([]i32, []i32)", {"[]i32", "[]i32"},
      [](futhark_context *c, void *o) { return futhark_free_opaque_tup2_arr1d_i32_arr1d_i32(c, (futhark_opaque_tup2_arr1d_i32_arr1d_i32 *)o); },
@@ -326,6 +345,7 @@ inline const std::vector<EntryPoint> &entry_points() {
       {"reduce_by_index_3d_add_i32", {"[][][]i32", "[]i64", "[]i64", "[]i64", "[]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_reduce_by_index_3d_add_i32(c, &r, FE_IN(0, i32_3d), FE_IN(1, i64_1d), FE_IN(2, i64_1d), FE_IN(3, i64_1d), FE_IN(4, i32_1d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"hist_rows_2d_add_i32", {"i64", "i64", "[][]i32", "[][]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_hist_rows_2d_add_i32(c, &r, scalar_of<int64_t>(*in[0]), scalar_of<int64_t>(*in[1]), FE_IN(2, i32_2d), FE_IN(3, i32_2d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},
       {"partition2_i32", {"[]i32"}, "([]i32, []i32, []i32)", [](C *c, In in, Value &o) { futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *r = nullptr; int rc = futhark_entry_partition2_i32(c, &r, FE_IN(0, i32_1d)); if (!rc) set_record(o, "([]i32, []i32, []i32)", r); return rc; }},
+      {"segredomap_sum_neg_f32", {"[][]f32"}, "([]i64, [][]f64)", [](C *c, In in, Value &o) { futhark_opaque_tup2_arr1d_i64_arr2d_f64 *r = nullptr; int rc = futhark_entry_segredomap_sum_neg_f32(c, &r, FE_IN(0, f32_2d)); if (!rc) set_record(o, "([]i64, [][]f64)", r); return rc; }},
       FE_E1(reduce_map2_add_i32, i32_2d, "[][]i32", i32_1d, "[]i32"),
       FE_E3(reduce_by_index_vec_add_i32, i32_2d, "[][]i32", i64_1d, "[]i64", i32_2d, "[][]i32", i32_2d, "[][]i32"),
       {"hist_rows_vec_add_i32", {"i64", "[][]i32", "[][][]i32"}, "[][][]i32", [](C *c, In in, Value &o) { futhark_i32_3d *r = nullptr; int rc = futhark_entry_hist_rows_vec_add_i32(c, &r, scalar_of<int64_t>(*in[0]), FE_IN(1, i32_2d), FE_IN(2, i32_3d)); if (!rc) set_array(o, "[][][]i32", r); return rc; }},

@@ -643,6 +643,71 @@ int futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_0(struct futhark_context *ct
 int futhark_project_opaque_tup2_arr1d_i32_arr1d_i32_1(struct futhark_context *ctx, struct futhark_i32_1d **out,
                                                       const struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 *obj) { return project_tup2_i32(ctx, out, obj, 1); }
 
+// main of tests/segredomap/ex1-comm.fut:11-15: unzip (map (\xs -> (reduce_comm (+) 0 (map i64.f32 xs), map (\x -> f64.f32 (-x)) xs)) xss):
+// a segmented redomap whose body also returns a mapped array (a map-out result, SegRed.hs:138-143)
+int futhark_entry_segredomap_sum_neg_f32(struct futhark_context *ctx, struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 **out0,
+                                         const struct futhark_f32_2d *in0) {
+  if (!ctx->ready) return not_ready(ctx);
+  CtxGuard g(ctx);
+  const int64_t rows = in0->shape[0], cols = in0->shape[1];
+  int rc;
+  futhark_i64_1d *sums = make_1d<futhark_i64_1d>(ctx, rows, 8, "segredomap_sum_neg_f32.sums", &rc);
+  if (sums == nullptr) return rc;
+  futhark_f64_2d *neg = (futhark_f64_2d *)malloc(sizeof(futhark_f64_2d));
+  auto *p = (futhark_opaque_tup2_arr1d_i64_arr2d_f64 *)malloc(sizeof(futhark_opaque_tup2_arr1d_i64_arr2d_f64));
+  rc = (neg == nullptr || p == nullptr) ? 1 : fb_alloc(ctx, (size_t)(rows * cols) * 8, "segredomap_sum_neg_f32.neg", &neg->mem);
+  if (rc != 0) { fb_unref(ctx, &sums->mem); free(sums); free(neg); free(p); return rc; }
+  neg->shape[0] = rows; neg->shape[1] = cols;
+  {
+    LaunchScope ls(ctx, "segredomap_sum_neg_f32.segred", PROV("map (\\xs -> (reduce (+) 0 (map i64.f32 xs), map (f64.f32 <-< f32.neg) xs)) xss"),
+                   "{" + kv("rows", rows) + "," + kv("cols", cols) + "}");
+    rc = fb_cuda_check(ctx, fb::launch_rowsum_mapout(dptr<float>(in0->mem), rows, cols, dptr<int64_t>(sums->mem), dptr<double>(neg->mem), ctx->num_sms,
+                                                     ctx->stream), "segredomap_sum_neg_f32");
+  }
+  if (rc != 0) { fb_unref(ctx, &sums->mem); free(sums); fb_unref(ctx, &neg->mem); free(neg); free(p); return rc; }
+  p->v0 = sums; p->v1 = neg;
+  *out0 = p;
+  return FUTHARK_SUCCESS;
+}
+int futhark_free_opaque_tup2_arr1d_i64_arr2d_f64(struct futhark_context *ctx, struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 *obj) {
+  if (obj == nullptr) return 0;
+  futhark_free_i64_1d(ctx, obj->v0);
+  futhark_free_f64_2d(ctx, obj->v1);
+  free(obj);
+  return 0;
+}
+int futhark_new_opaque_tup2_arr1d_i64_arr2d_f64(struct futhark_context *ctx, struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 **out,
+                                                const struct futhark_i64_1d *v0, const struct futhark_f64_2d *v1) {
+  CtxGuard g(ctx);
+  auto *p = (futhark_opaque_tup2_arr1d_i64_arr2d_f64 *)malloc(sizeof(futhark_opaque_tup2_arr1d_i64_arr2d_f64));
+  if (p == nullptr) return 1;
+  p->v0 = (futhark_i64_1d *)malloc(sizeof(futhark_i64_1d));
+  p->v1 = (futhark_f64_2d *)malloc(sizeof(futhark_f64_2d));
+  if (p->v0 == nullptr || p->v1 == nullptr) return 1;
+  *p->v0 = *v0; fb_ref(&p->v0->mem);           // the record shares the blocks of its fields (docs/c-api.rst:366-381)
+  *p->v1 = *v1; fb_ref(&p->v1->mem);
+  *out = p;
+  return 0;
+}
+int futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_0(struct futhark_context *ctx, struct futhark_i64_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 *obj) {
+  CtxGuard g(ctx);
+  futhark_i64_1d *a = (futhark_i64_1d *)malloc(sizeof(futhark_i64_1d));
+  if (a == nullptr) return 1;
+  *a = *obj->v0; fb_ref(&a->mem);              // the projection shares the block (docs/c-api.rst:383-391)
+  *out = a;
+  return 0;
+}
+int futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_1(struct futhark_context *ctx, struct futhark_f64_2d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 *obj) {
+  CtxGuard g(ctx);
+  futhark_f64_2d *a = (futhark_f64_2d *)malloc(sizeof(futhark_f64_2d));
+  if (a == nullptr) return 1;
+  *a = *obj->v1; fb_ref(&a->mem);
+  *out = a;
+  return 0;
+}
+
 // reduce (map2 (+)) (replicate m 0) xss (tests/soacs/reduce4.fut, reduce5.fut): an operator on whole rows; the
 // reduction is interchanged with the inner map (src/Futhark/Transform/ISRWIM.hs) and every column reduced
 int futhark_entry_reduce_map2_add_i32(struct futhark_context *ctx, struct futhark_i32_1d **out0, const struct futhark_i32_2d *in0) {

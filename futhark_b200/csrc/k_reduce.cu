@@ -105,6 +105,39 @@ cudaError_t launch_reduce_i32(const int32_t *in, int64_t n, int32_t *d_out, void
   return cudaGetLastError();
 }
 
+// ---- a segmented redomap with a map-out result ---------------------------------------------------------
+// map (\xs -> (reduce (+) 0 (map i64.f32 xs), map (\x -> f64.f32 (-x)) xs)) xss (tests/segredomap/ex1-comm.fut:11-15):
+// the body's results that are not reduced are written by the thread that computes them while it reads
+// (SegRed.hs:138-143, "write map-out result(s)").  One warp per row; i64.f32 is fptosi_f32_i64
+// (rts/c/scalar.h:975-981): 0 for NaN and infinities.
+__global__ void __launch_bounds__(RED_THREADS)
+rowsum_mapout_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, int64_t *__restrict__ sums, double *__restrict__ neg) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = ((int64_t)blockIdx.x * RED_THREADS + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * RED_THREADS) >> 5;
+  for (int64_t r = warp_global; r < rows; r += nwarps) {
+    const float *row = in + r * cols;
+    double *nrow = neg + r * cols;
+    unsigned long long acc = 0ull;
+    for (int64_t i = lane; i < cols; i += 32) {
+      const float x = row[i];
+      const bool odd = (x != x) || (fabsf(x) == INFINITY);
+      acc += odd ? 0ull : (unsigned long long)(long long)x;
+      nrow[i] = (double)(-x);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(kFull, acc, o);
+    if (lane == 0) sums[r] = (int64_t)acc;
+  }
+}
+cudaError_t launch_rowsum_mapout(const float *in, int64_t rows, int64_t cols, int64_t *sums, double *neg, int num_sms, cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  int64_t want = (rows * 32 + RED_THREADS - 1) / RED_THREADS;
+  const int64_t cap = (int64_t)num_sms * 8;
+  rowsum_mapout_kernel<<<(int)(want < cap ? want : cap), RED_THREADS, 0, stream>>>(in, rows, cols, sums, neg);
+  return cudaGetLastError();
+}
+
 // ---- reduce (map2 (+)) (replicate cols 0) over the rows of [rows][cols] i32 -------------------------
 // A reduction whose operator works on whole rows (tests/soacs/reduce4.fut, reduce5.fut) is interchanged
 // with the inner map (src/Futhark/Transform/ISRWIM.hs, irwim): every column is reduced on its own.  A thread

@@ -88,6 +88,8 @@ cudaError_t launch_rowsum_f32(const float *in, int64_t rows, int64_t cols, float
 cudaError_t launch_segreduce_f32(const int64_t *offsets, int64_t nseg, const float *xs, int64_t n, float *out,
                                  void *scratch, int *failure, int num_sms, cudaStream_t stream);
 
+// sums[r] = sum of i64.f32 of row r (wrapping), neg[r][i] = f64.f32 (-in[r][i]): a segmented redomap with a map-out result
+cudaError_t launch_rowsum_mapout(const float *in, int64_t rows, int64_t cols, int64_t *sums, double *neg, int num_sms, cudaStream_t stream);
 // out[c] = sum over the rows of in[r][c] (wrapping): a reduction with an operator on whole rows
 cudaError_t launch_colsum_i32(const int32_t *in, int64_t rows, int64_t cols, int32_t *out, int num_sms, cudaStream_t stream);
 

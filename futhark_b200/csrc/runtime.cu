@@ -623,6 +623,7 @@ FB_ARRAY_2D(f32_2d, float)
 FB_ARRAY_2D(i32_2d, int32_t)
 FB_ARRAY_2D(bool_2d, bool)
 FB_ARRAY_2D(i64_2d, int64_t)
+FB_ARRAY_2D(f64_2d, double)
 FB_ARRAY_1D(f64_1d, double)
 FB_ARRAY_1D(i8_1d, int8_t)
 FB_ARRAY_1D(i16_1d, int16_t)

@@ -142,6 +142,7 @@ FB_DEFINE_ARRAY_STRUCT(f32_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(i32_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(bool_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(i64_2d, 2)
+FB_DEFINE_ARRAY_STRUCT(f64_2d, 2)
 FB_DEFINE_ARRAY_STRUCT(f64_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(i8_1d, 1)
 FB_DEFINE_ARRAY_STRUCT(i16_1d, 1)
@@ -159,6 +160,11 @@ struct futhark_opaque_tup2_arr1d_u32_arr1d_u32 {
 
 struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 {
   futhark_i32_1d *v[3];
+};
+
+struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 {
+  futhark_i64_1d *v0;
+  futhark_f64_2d *v1;
 };
 
 struct futhark_opaque_tup2_arr1d_i32_arr1d_i32 {

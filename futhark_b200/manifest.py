@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PATH = os.path.join(HERE, "futhark_b200.json")
 
 ELEM = {"i32": "int32_t", "i64": "int64_t", "u32": "uint32_t", "f32": "float", "f64": "double", "bool": "bool", "f16": "uint16_t"}
-ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "f16_1d", "u8_1d", "u16_1d", "bool_1d", "f32_2d", "i32_2d", "i64_2d", "bool_2d", "f32_3d", "i32_3d", "f16_3d"]
+ARRAYS = ["i32_1d", "i64_1d", "u32_1d", "f32_1d", "f64_1d", "i8_1d", "i16_1d", "f16_1d", "u8_1d", "u16_1d", "bool_1d", "f32_2d", "i32_2d", "i64_2d", "f64_2d", "bool_2d", "f32_3d", "i32_3d", "f16_3d"]
 
 PAIR = "opaque_tup2_arr1d_u32_arr1d_u32"
 TRIPLE = "opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32"
@@ -67,6 +67,7 @@ ENTRIES = {
     "hist_rows_vec_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vsss", "[][][]i32")], "[][][]i32", []),
     "reduce_by_index_minpair_i32": ([("m", "i64"), ("is", "[]i32"), ("vs0", "[]i32"), ("vs1", "[]i32")], "([]i32, []i32)", []),
     "reduce_map2_add_i32": ([("xss", "[][]i32")], "[]i32", []),
+    "segredomap_sum_neg_f32": ([("xss", "[][]f32")], "([]i64, [][]f64)", []),
     "hist_rows_add_i32": ([("m", "i64"), ("iss", "[][]i32"), ("vss", "[][]i32")], "[][]i32", []),
     "reduce_by_index_2d_add_i32": ([("dest", "[][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("vs", "[]i32")], "[][]i32", []),
     "reduce_by_index_3d_add_i32": ([("dest", "[][][]i32"), ("is", "[]i64"), ("js", "[]i64"), ("ks", "[]i64"), ("vs", "[]i32")], "[][][]i32", []),
@@ -133,6 +134,13 @@ def build():
         "ops": {"free": "futhark_free_" + PAIR_I32},
         "record": {"new": "futhark_new_" + PAIR_I32,
                    "fields": [{"name": str(i), "type": "[]i32", "project": "futhark_project_%s_%d" % (PAIR_I32, i)} for i in range(2)]},
+    }
+    types["([]i64, [][]f64)"] = {
+        "kind": "opaque", "ctype": "struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 *",
+        "ops": {"free": "futhark_free_opaque_tup2_arr1d_i64_arr2d_f64"},
+        "record": {"new": "futhark_new_opaque_tup2_arr1d_i64_arr2d_f64",
+                   "fields": [{"name": "0", "type": "[]i64", "project": "futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_0"},
+                              {"name": "1", "type": "[][]f64", "project": "futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_1"}]},
     }
     entries = {}
     for name, (ins, out, tuning) in ENTRIES.items():

@@ -137,6 +137,7 @@ FUTHARK_B200_ARRAY_2D(f32_2d, float)
 FUTHARK_B200_ARRAY_2D(i32_2d, int32_t)
 FUTHARK_B200_ARRAY_2D(bool_2d, bool)
 FUTHARK_B200_ARRAY_2D(i64_2d, int64_t)
+FUTHARK_B200_ARRAY_2D(f64_2d, double)
 FUTHARK_B200_ARRAY_1D(f64_1d, double)
 FUTHARK_B200_ARRAY_1D(i8_1d, int8_t)
 FUTHARK_B200_ARRAY_1D(i16_1d, int16_t)
@@ -184,6 +185,18 @@ int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_1(struct futhark_c
                                                                 const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
 int futhark_project_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32_2(struct futhark_context *ctx, struct futhark_i32_1d **out,
                                                                 const struct futhark_opaque_tup3_arr1d_i32_arr1d_i32_arr1d_i32 *obj);
+
+/* ---- opaque pair ([]i64, [][]f64) returned by segredomap_sum_neg_f32 (same naming rule and functions) ---------- */
+struct futhark_opaque_tup2_arr1d_i64_arr2d_f64;
+int futhark_free_opaque_tup2_arr1d_i64_arr2d_f64(struct futhark_context *ctx,
+                                                 struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 *obj);
+int futhark_new_opaque_tup2_arr1d_i64_arr2d_f64(struct futhark_context *ctx,
+                                                struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 **out,
+                                                const struct futhark_i64_1d *v0, const struct futhark_f64_2d *v1);
+int futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_0(struct futhark_context *ctx, struct futhark_i64_1d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 *obj);
+int futhark_project_opaque_tup2_arr1d_i64_arr2d_f64_1(struct futhark_context *ctx, struct futhark_f64_2d **out,
+                                                      const struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 *obj);
 
 /* ---- opaque pair of i32 arrays returned by reduce_by_index_minpair_i32 (same naming rule and functions) ---------- */
 struct futhark_opaque_tup2_arr1d_i32_arr1d_i32;
@@ -272,6 +285,14 @@ int futhark_entry_segreduce_f32(struct futhark_context *ctx, struct futhark_f32_
  * ImpGen/GPU/SegRed.hs:396-636. */
 int futhark_entry_rowsum_f32(struct futhark_context *ctx, struct futhark_f32_1d **out0,
                              const struct futhark_f32_2d *in0);
+
+/* entry segredomap_sum_neg_f32 [m][n] (xss: [m][n]f32): ([m]i64, [m][n]f64) =
+ *   unzip (map (\xs -> (reduce_comm (+) 0 (map i64.f32 xs), map (\x -> f64.f32 (-x)) xs)) xss)
+ * (main of tests/segredomap/ex1-comm.fut:11-15: a segmented redomap whose body also returns a mapped array; the
+ * threads write that map-out result while they read, src/Futhark/CodeGen/ImpGen/GPU/SegRed.hs:138-143). */
+int futhark_entry_segredomap_sum_neg_f32(struct futhark_context *ctx,
+                                         struct futhark_opaque_tup2_arr1d_i64_arr2d_f64 **out0,
+                                         const struct futhark_f32_2d *in0);
 
 /* entry reduce_map2_add_i32 [n][m] (xss: [n][m]i32): [m]i32 = reduce_comm (map2 (+)) (replicate m 0) xss
  * (tests/soacs/reduce4.fut, reduce5.fut: a reduction whose operator works on whole rows; it is interchanged

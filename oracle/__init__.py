@@ -562,6 +562,15 @@ def reduce_by_index_minpair_i32(m, is_, vs0, vs1):
     return out0, out1
 
 
+def segredomap_sum_neg_f32(xss):
+    xss = _c(xss, np.float32)
+    rows, cols = xss.shape
+    sums, neg = np.empty(rows, np.int64), np.empty((rows, cols), np.float64)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    _fn("orc_segredomap_sum_neg_f32", vp, i64, i64, vp, vp)(_p(xss), rows, cols, _p(sums), _p(neg))
+    return sums, neg
+
+
 def reduce_map2_add_i32(xss):
     xss = _c(xss, np.int32)
     out = np.empty(xss.shape[1], np.int32)

@@ -15,6 +15,7 @@
  * (:96-167), and/or/xor (:199-229), fadd32 (:865).  Futhark's x % m is the floored modulus
  * (smod32, scalar.h:352-361): it is 0 exactly when the C remainder is 0.
  */
+#include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -133,6 +134,20 @@ void orc_reduce_by_index_minpair_i32(int32_t *out0, int32_t *out1, int64_t m, co
     if (is[i] < 0 || (int64_t)is[i] >= m) continue;
     const int32_t x0 = out0[is[i]], x1 = vs0[i];
     if (!(x0 != -1 && (x1 == -1 || x0 < x1))) { out0[is[i]] = x1; out1[is[i]] = vs1[i]; }
+  }
+}
+
+/* main of tests/segredomap/ex1-comm.fut:11-15: per row the sum of i64.f32 x (fptosi_f32_i64, rts/c/scalar.h:975-981: 0 for NaN
+ * and infinities; wrapping addition) and the row of f64.f32 (-x) */
+void orc_segredomap_sum_neg_f32(const float *xss, int64_t rows, int64_t cols, int64_t *sums, double *neg) {
+  for (int64_t r = 0; r < rows; r++) {
+    uint64_t acc = 0;
+    for (int64_t i = 0; i < cols; i++) {
+      const float x = xss[r * cols + i];
+      if (!(x != x) && !(x == INFINITY || x == -INFINITY)) acc += (uint64_t)(int64_t)x;
+      neg[r * cols + i] = (double)(-x);
+    }
+    sums[r] = (int64_t)acc;
   }
 }
 

@@ -63,6 +63,8 @@ FILES = [
     "tests/hist/lor.fut",
     "tests/hist/equiv.fut",
     "tests/hist/segmented_arr.fut",
+    "tests/segredomap/ex1-comm.fut",
+    "tests/segredomap/ex1-nocomm.fut",
     "tests/hist/and8.fut",
     "tests/hist/and16.fut",
     "tests/hist/and64.fut",

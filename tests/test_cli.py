@@ -82,6 +82,7 @@ def test_text_in_text_out(cli):
     # the entry points under other specifications, on the reference's own test vectors
     assert run(cli, ["-e", "partition2_i32"], b"[0,1,2,3,4,5,6,7,8,9]").stdout == b"[0i32, 2i32, 4i32, 6i32, 8i32]\n[3i32, 9i32]\n[1i32, 5i32, 7i32]\n"   # tests/soacs/partition1.fut
     assert run(cli, ["-e", "partition2_pairs_i32"], b"[2,7,1,2,8,9,1,5,0,2] [6,1,0,9,8,7,9,4,2,1]").stdout == b"[2i32, 2i32, 1i32, 0i32]\n[6i32, 9i32, 9i32, 2i32]\n[8i32]\n[8i32]\n[7i32, 1i32, 9i32, 5i32, 2i32]\n[1i32, 0i32, 7i32, 4i32, 1i32]\n"   # tests/soacs/partition2.fut
+    assert run(cli, ["-e", "segredomap_sum_neg_f32"], b"[[1.0f32, 2.0f32, 3.0f32], [4.0f32, 5.0f32, 6.0f32]]").stdout == b"[6i64, 15i64]\n[[-1f64, -2f64, -3f64], [-4f64, -5f64, -6f64]]\n"   # tests/segredomap/ex1-comm.fut
     assert run(cli, ["-e", "reduce_map2_add_i32"], b"[[1,2],[3,4],[5,6]]").stdout == b"[9i32, 12i32]\n"                                                        # tests/soacs/reduce4.fut
     assert run(cli, ["-e", "reduce_by_index_minpair_i32"], b"5i64 [1, 3, 1] [4, 1, 3] [5, 6, 7]").stdout == b"[-1i32, 3i32, -1i32, 1i32, -1i32]\n[-1i32, 7i32, -1i32, 6i32, -1i32]\n"   # tests/hist/tuple_partial.fut
     assert run(cli, ["-e", "reduce_by_index_vec_add_i32"], b"[[1,2,3],[4,5,6]] [0i64,0i64,2i64,1i64] [[0,1,2],[0,1,2],[0,1,2],[0,1,2]]").stdout == b"[[1i32, 4i32, 7i32], [4i32, 6i32, 8i32]]\n"   # tests/hist/array.fut

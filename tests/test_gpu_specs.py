@@ -113,6 +113,10 @@ def test_reference_vectors_row_bins_pair_operator_row_operator(ctx):
         m, is_, vs0, vs1 = c["input"]
         got = fb.reduce_by_index_minpair_i32(ctx, m, np.array(is_, np.int32), np.array(vs0, np.int32), np.array(vs1, np.int32))
         assert [g.tolist() for g in got] == c["output"]
+    for name in ("tests/segredomap/ex1-comm.fut", "tests/segredomap/ex1-nocomm.fut"):
+        for c in GOLDEN[name]:
+            sums, neg = fb.segredomap_sum_neg_f32(ctx, np.array(c["input"][-1], np.float32))
+            assert sums.tolist() == c["output"][0] and neg.tolist() == c["output"][1]
     for name in ("tests/soacs/reduce4.fut", "tests/soacs/reduce5.fut"):
         for c in GOLDEN[name]:
             assert fb.reduce_map2_add_i32(ctx, np.array(c["input"][0], np.int32)).tolist() == c["output"][0]
@@ -144,6 +148,17 @@ def test_reduce_by_index_pair_operator(ctx, m, n):
     vs1 = datagen.uniform_i32(86, 0, n, -2 ** 31, 2 ** 31 - 1)
     got, want = fb.reduce_by_index_minpair_i32(ctx, m, is_, vs0, vs1), oracle.reduce_by_index_minpair_i32(m, is_, vs0, vs1)
     assert all(np.array_equal(g, w) for g, w in zip(got, want))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (0, 5), (7, 0), (3, 2), (50000, 3), (1000, 1000), (9, 100003)])
+def test_segmented_redomap_with_map_out(ctx, rows, cols):
+    xss = (datagen.normal_f32(90, 0, rows * cols) * np.float32(1e6)).reshape(rows, cols)
+    if xss.size > 4:
+        xss.reshape(-1)[[0, 1, 2]] = [np.nan, np.inf, -np.inf]           # i64.f32 gives 0 for these
+    sums, neg = fb.segredomap_sum_neg_f32(ctx, xss)
+    wsums, wneg = oracle.segredomap_sum_neg_f32(xss)
+    assert sums.dtype == np.int64 and neg.dtype == np.float64 and neg.shape == (rows, cols)
+    assert np.array_equal(sums, wsums) and np.array_equal(neg, wneg, equal_nan=True)
 
 
 @pytest.mark.parametrize("rows,cols", [(1, 1), (0, 5), (7, 0), (3, 2), (100000, 3), (1000, 1000), (9, 100003), (40001, 257)])

@@ -100,6 +100,16 @@ def test_reduce_by_index_with_an_operator_on_pairs(c):
     assert [g.tolist() for g in got] == c["output"]
 
 
+@pytest.mark.parametrize("name", ["tests/segredomap/ex1-comm.fut", "tests/segredomap/ex1-nocomm.fut"])
+def test_segmented_redomap_with_map_out(name):
+    for c in cases(name):
+        xss = c["input"][-1]                      # ex1-nocomm passes `true` first: its operator is then the same addition
+        if len(c["input"]) == 2:
+            assert c["input"][0] is True
+        sums, neg = oracle.segredomap_sum_neg_f32(np.array(xss, np.float32))
+        assert sums.tolist() == c["output"][0] and neg.tolist() == c["output"][1]
+
+
 @pytest.mark.parametrize("name", ["tests/soacs/reduce4.fut", "tests/soacs/reduce5.fut"])
 def test_reduce_with_an_operator_on_rows(name):
     for c in cases(name):
